@@ -1,0 +1,191 @@
+"""Windowed layout of atoms for the 32-query x 128-key atom attention.
+
+Atoms live in token-major slots ``[N, M]`` (M = 24). For attention the real
+atoms are packed front-first into a flat list padded to ``W * Q`` slots and cut
+into ``W`` query windows of ``Q = 32``; window ``w`` attends to the ``K = 128``
+flat slots centred on it, shifted inward at the two ends (reference:
+model/atom_cross_attn.py:89-204).
+
+Two facts shape this implementation. (1) The key slots of a window depend only
+on ``(N*M, Q, K)``, never on the data, so one ``[W, K]`` index serves every
+molecule of a batch. (2) Real atoms are packed first, so every window past
+``ceil(num_real / Q)`` is empty in all molecules and can be dropped without
+changing any real atom's result; ``trim`` does that (the reference only trims
+in its hoisted sampler, atom_cross_attn.py:65-86).
+"""
+
+from __future__ import annotations
+
+import dataclasses
+import math
+
+import torch
+
+
+@dataclasses.dataclass
+class AtomLayout:
+    """Index tensors between ``[B, N*M]`` slots, ``[B, W, Q]`` queries and ``[W, K]`` keys."""
+
+    num_windows: int  # W
+    Q: int
+    K: int
+    N: int
+    M: int
+    slot_of_query: torch.Tensor  # [B, W, Q] long  index into N*M
+    query_mask: torch.Tensor  # [B, W, Q] bool
+    key_of_window: torch.Tensor  # [W, K] long  index into W*Q (shared by the batch)
+    key_mask: torch.Tensor  # [B, W, K] bool
+    token_of_query: torch.Tensor  # [B, W, Q] long
+    token_of_key: torch.Tensor  # [B, W, K] long
+    query_of_slot: torch.Tensor  # [B, N, M] long  index into W*Q
+    slot_mask: torch.Tensor  # [B, N, M] bool
+
+    # reference field names, for code written against ``AtomSubsets``
+    @property
+    def num_subsets(self):
+        return self.num_windows
+
+    @property
+    def ta_to_q_idx(self):
+        return self.slot_of_query
+
+    @property
+    def ta_to_q_mask(self):
+        return self.query_mask
+
+    @property
+    def q_to_k_idx(self):
+        return self.key_of_window
+
+    @property
+    def q_to_k_mask(self):
+        return self.key_mask
+
+    @property
+    def q_to_ta_idx(self):
+        return self.query_of_slot
+
+    @property
+    def q_to_ta_mask(self):
+        return self.slot_mask
+
+    def trim(self, multiple: int = 1) -> "AtomLayout":
+        """Drop trailing windows that are empty in every molecule (kept count rounded up to ``multiple``)."""
+        most = int(self.slot_mask.flatten(1).sum(-1).max())
+        keep = max(1, math.ceil(most / self.Q))
+        keep = min(self.num_windows, ((keep + multiple - 1) // multiple) * multiple)
+        if keep == self.num_windows:
+            return self
+        key_idx = self.key_of_window[:keep]
+        return dataclasses.replace(
+            self,
+            num_windows=keep,
+            slot_of_query=self.slot_of_query[:, :keep],
+            query_mask=self.query_mask[:, :keep],
+            key_of_window=key_idx.masked_fill(key_idx >= keep * self.Q, 0),
+            key_mask=self.key_mask[:, :keep],
+            token_of_query=self.token_of_query[:, :keep],
+            token_of_key=self.token_of_key[:, :keep],
+        )
+
+
+def _take(flat: torch.Tensor, idx: torch.Tensor, mask: torch.Tensor, sample_axis: bool) -> torch.Tensor:
+    """Batched ``flat[b, (s,) idx[b]]`` with ``mask`` applied.
+
+    ``flat``: ``[B, (S,) L, *F]``; ``idx`` / ``mask``: ``[B, *D]``. Result ``[B, (S,) *D, *F]``.
+    """
+    B = idx.shape[0]
+    D = idx.shape[1:]
+    if sample_axis:
+        S = flat.shape[1]
+        feat = flat.shape[3:]
+        ix = idx.reshape(B, 1, -1, *([1] * len(feat))).expand(B, S, -1, *feat)
+        out = torch.gather(flat, 2, ix).reshape(B, S, *D, *feat)
+        m = mask.reshape(B, 1, *D, *([1] * len(feat)))
+    else:
+        feat = flat.shape[2:]
+        ix = idx.reshape(B, -1, *([1] * len(feat))).expand(B, -1, *feat)
+        out = torch.gather(flat, 1, ix).reshape(B, *D, *feat)
+        m = mask.reshape(B, *D, *([1] * len(feat)))
+    return out * m.to(out.dtype)
+
+
+def slots_to_queries(layout: AtomLayout, slots: torch.Tensor, sample_axis: bool = False) -> torch.Tensor:
+    """``[B, (S,) N, M, *F]`` → ``[B, (S,) W, Q, *F]``."""
+    lead = 2 if sample_axis else 1
+    flat = slots.reshape(*slots.shape[:lead], layout.N * layout.M, *slots.shape[lead + 2 :])
+    return _take(flat, layout.slot_of_query, layout.query_mask, sample_axis)
+
+
+def queries_to_slots(layout: AtomLayout, queries: torch.Tensor, sample_axis: bool = False) -> torch.Tensor:
+    """``[B, (S,) W, Q, *F]`` → ``[B, (S,) N, M, *F]``."""
+    lead = 2 if sample_axis else 1
+    flat = queries.reshape(*queries.shape[:lead], layout.num_windows * layout.Q, *queries.shape[lead + 2 :])
+    return _take(flat, layout.query_of_slot, layout.slot_mask, sample_axis)
+
+
+def queries_to_keys(layout: AtomLayout, queries: torch.Tensor, sample_axis: bool = False) -> torch.Tensor:
+    """``[B, (S,) W, Q, *F]`` → ``[B, (S,) W, K, *F]`` through the shared window index."""
+    lead = 2 if sample_axis else 1
+    flat = queries.reshape(*queries.shape[:lead], layout.num_windows * layout.Q, *queries.shape[lead + 2 :])
+    out = flat.index_select(lead, layout.key_of_window.reshape(-1))
+    out = out.reshape(*queries.shape[:lead], layout.num_windows, layout.K, *queries.shape[lead + 2 :])
+    m = layout.key_mask
+    if sample_axis:
+        m = m.unsqueeze(1)
+    return out * m.reshape(*m.shape, *([1] * (out.dim() - m.dim()))).to(out.dtype)
+
+
+def build_atom_layout(ref_mask: torch.Tensor, Q: int = 32, K: int = 128) -> AtomLayout:
+    """Layout for ``ref_mask`` ``[B, N, M]`` (or ``[N, M]``, promoted to ``B = 1``)."""
+    if ref_mask.dim() == 2:
+        ref_mask = ref_mask.unsqueeze(0)
+    ref_mask = ref_mask.bool()
+    B, N, M = ref_mask.shape
+    dev = ref_mask.device
+    L = N * M
+    W = (L + Q - 1) // Q
+    P = W * Q
+
+    flat = ref_mask.reshape(B, L)
+    # stable sort puts real slots first, in slot order: position p of the packed list holds slot order[b, p]
+    order = torch.sort((~flat).to(torch.int8), dim=1, stable=True).indices
+    count = flat.sum(1, keepdim=True)
+    packed_mask = torch.arange(P, device=dev).unsqueeze(0) < count  # [B, P]
+    slot_of_packed = torch.zeros(B, P, dtype=torch.long, device=dev)
+    slot_of_packed[:, :L] = order
+    slot_of_packed = slot_of_packed * packed_mask  # padded entries point at slot 0 and are masked
+
+    centers = torch.arange(Q // 2, P, Q, device=dev)
+    key = centers.unsqueeze(1) + torch.arange(-(K // 2), K // 2, device=dev).unsqueeze(0)  # [W, K]
+    shift = (-key[:, 0]).clamp(min=0) - (key[:, -1] - (P - 1)).clamp(min=0)
+    key = (key + shift.unsqueeze(1)).clamp(0, P - 1)
+
+    token_of_slot = torch.arange(N, device=dev).repeat_interleave(M)
+    token_of_packed = token_of_slot[slot_of_packed]  # [B, P]
+    key_flat = key.reshape(-1)
+
+    query_of_slot = torch.zeros(B, L, dtype=torch.long, device=dev)
+    pos = torch.arange(P, device=dev).unsqueeze(0).expand(B, P)
+    # scatter only real entries: padded entries all point at slot 0 and must not overwrite it
+    src = torch.where(packed_mask, pos, torch.zeros_like(pos))
+    tgt = torch.where(packed_mask, slot_of_packed, torch.full_like(slot_of_packed, L))
+    buf = torch.zeros(B, L + 1, dtype=torch.long, device=dev)
+    buf.scatter_(1, tgt, src)
+    query_of_slot = buf[:, :L]
+
+    return AtomLayout(
+        num_windows=W,
+        Q=Q,
+        K=K,
+        N=N,
+        M=M,
+        slot_of_query=slot_of_packed.reshape(B, W, Q),
+        query_mask=packed_mask.reshape(B, W, Q),
+        key_of_window=key,
+        key_mask=packed_mask[:, key_flat].reshape(B, W, K),
+        token_of_query=token_of_packed.reshape(B, W, Q),
+        token_of_key=token_of_packed[:, key_flat].reshape(B, W, K),
+        query_of_slot=query_of_slot.reshape(B, N, M),
+        slot_mask=ref_mask,
+    )
