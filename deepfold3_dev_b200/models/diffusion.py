@@ -42,7 +42,7 @@ def _batched(t, batched: bool):
 
 
 class DiffusionHead(nn.Module):
-    def __init__(self, cfg, c_single=384, c_pair=128, rel_feat_dim=139, optim=None):
+    def __init__(self, cfg, c_single=384, c_pair=128, rel_feat_dim=139, optim=None, target_feat_dim=447):
         super().__init__()
         self.cfg = cfg
         aca = cfg.atom_cross_att
@@ -51,6 +51,7 @@ class DiffusionHead(nn.Module):
         self.conditioning = DiffusionConditioningBlock(
             c_pair_in=c_pair, c_single_in=c_single, rel_feat_dim=rel_feat_dim,
             c_pair_out=cfg.conditioning_pair_channel, c_single_out=cfg.conditioning_seq_channel,
+            target_feat_dim=target_feat_dim,
             use_trunk_single=cfg.conditioning_use_trunk_single, sigma_data=cfg.sigma_data,
             fourier_dim=cfg.fourier_dim, num_intermediate_factor=cfg.conditioning_num_intermediate_factor,
             optim=optim,

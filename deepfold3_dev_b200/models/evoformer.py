@@ -182,11 +182,13 @@ class Evoformer(nn.Module):
         self._grad_checkpoint = bool(optim and optim.use_gradient_checkpointing)
         self.pair_chunk_budget = optim.pair_chunk_budget_bytes if optim is not None else 0
         c_msa, c_pair, c_single = cfg.msa_channel, cfg.pair_channel, cfg.seq_channel
+        # raw token features (63) + conditioning-encoder output (seq_channel wide): 447 at the default width
+        tf_dim = 63 + c_single
         self.template_embedding = TemplateEmbedding(template_cfg, optim=optim) if template_cfg is not None else None
         self.msa_activations = LinearNoBias(MSA_FEAT_DIM, c_msa)
-        self.extra_msa_target_feat = LinearNoBias(TARGET_FEAT_DIM, c_msa)
-        self.left_single = LinearNoBias(TARGET_FEAT_DIM, c_pair)
-        self.right_single = LinearNoBias(TARGET_FEAT_DIM, c_pair)
+        self.extra_msa_target_feat = LinearNoBias(tf_dim, c_msa)
+        self.left_single = LinearNoBias(tf_dim, c_pair)
+        self.right_single = LinearNoBias(tf_dim, c_pair)
         self.bond_embedding = LinearNoBias(1, c_pair)
         self.prev_embedding_layer_norm = LayerNorm(c_pair)
         self.prev_embedding = LinearNoBias(c_pair, c_pair, initializer="zeros")
@@ -196,7 +198,7 @@ class Evoformer(nn.Module):
             self.prev_single_embedding = LinearNoBias(c_single, c_single, initializer="zeros")
         rel_dim = 2 * (2 * cfg.max_relative_idx + 2) + 1 + (2 * cfg.max_relative_chain + 2)
         self.position_activations = LinearNoBias(rel_dim, c_pair)
-        self.single_activations = LinearNoBias(TARGET_FEAT_DIM, c_single)
+        self.single_activations = LinearNoBias(tf_dim, c_single)
         self.msa_stack = nn.ModuleList(
             EvoformerBlock(
                 c_msa, c_pair, cfg.msa_attention.num_head, cfg.pair_attention.num_head, cfg.outer_product_num_channel,

@@ -98,9 +98,13 @@ class DeepFold3(nn.Module):
         self.evoformer = Evoformer(ec, pfc, template_cfg=cfg.template, optim=cfg.optim)
         rel_dim = compute_rel_feat_dim(ec.max_relative_idx, ec.max_relative_chain)
         self.diffusion_head = DiffusionHead(
-            dc, c_single=ec.seq_channel, c_pair=ec.pair_channel, rel_feat_dim=rel_dim, optim=cfg.optim
+            dc, c_single=ec.seq_channel, c_pair=ec.pair_channel, rel_feat_dim=rel_dim, optim=cfg.optim,
+            target_feat_dim=RAW_TARGET_FEAT_DIM + ec.seq_channel,
         )
-        self.confidence_head = ConfidenceHead(cc, optim=cfg.optim, fp32=cfg.precision.fp32_confidence_head)
+        self.confidence_head = ConfidenceHead(
+            cc, target_feat_dim=RAW_TARGET_FEAT_DIM + ec.seq_channel, optim=cfg.optim,
+            fp32=cfg.precision.fp32_confidence_head,
+        )
         self.distogram_head = DistogramHead(ec.pair_channel, cfg=cfg.distogram, fp32=cfg.precision.fp32_distogram_head)
         self.distogram_head.pair_chunk_budget = cfg.optim.pair_chunk_budget_bytes
         self.masked_msa_head = (
@@ -289,7 +293,7 @@ class DeepFold3(nn.Module):
            loss is back-propagated through ``backward_fn`` as soon as it is computed;
         4. confidence head on detached trunk outputs; 5. distogram head.
         """
-        from ..training import losses as L
+        from ..training import objective as L
         from ..training.collectives import slice_batch_dict
 
         ref = self._ref_kwargs(features)
@@ -397,7 +401,7 @@ class DeepFold3(nn.Module):
 
     def _diffusion_training(self, pred, features, embeddings, target_feat, rel_feat, seq_mask, ref, gt_pos, gt_mask,
                             diffusion_batch_size, diffusion_chunk_size, backward_fn, loss_cfg):  # fmt: skip
-        from ..training import losses as L
+        from ..training import objective as L
         from .diffusion import (
             build_diffusion_clean_mask,
             cond_drop_stats,
