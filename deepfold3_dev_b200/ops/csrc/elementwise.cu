@@ -1,0 +1,353 @@
+// Memory-bound kernels: LayerNorm (fwd/bwd), SwiGLU (fwd/bwd), shared-mask dropout + residual add
+// (fwd/bwd) and the flat AdamW + EMA step. Each makes one pass over its operands.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/library.h>
+#include <torch/torch.h>
+
+#include "common.cuh"
+
+namespace df3 {
+
+constexpr int kLnMaxPerLane = 32;  // one warp per row, up to 32 * 32 = 1024 channels; kernels are
+                                   // instantiated for 4 / 8 / 16 / 32 values per lane
+
+// ---------------------------------------------------------------------------------------------
+// LayerNorm forward: y = (x - mean) * rstd * w + b with fp32 statistics. One warp per row.
+template <typename T, int K>
+__global__ void __launch_bounds__(256) layer_norm_fwd_kernel(const T* __restrict__ x, const float* __restrict__ w,
+                                                             const float* __restrict__ b, T* __restrict__ y,
+                                                             float* __restrict__ mean_out, float* __restrict__ rstd_out,
+                                                             int64_t rows, int C, float eps) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const T* xr = x + row * C;
+  float v[K];
+  float s = 0.f;
+#pragma unroll
+  for (int k = 0; k < K; ++k) {
+    const int c = lane + 32 * k;
+    v[k] = (c < C) ? to_float<T>(xr[c]) : 0.f;
+    s += v[k];
+  }
+  const float mean = warp_sum(s) / C;
+  float q = 0.f;
+#pragma unroll
+  for (int k = 0; k < K; ++k) {
+    const int c = lane + 32 * k;
+    const float d = (c < C) ? v[k] - mean : 0.f;
+    q += d * d;
+  }
+  const float rstd = rsqrtf(warp_sum(q) / C + eps);
+  T* yr = y + row * C;
+#pragma unroll
+  for (int k = 0; k < K; ++k) {
+    const int c = lane + 32 * k;
+    if (c < C) {
+      float o = (v[k] - mean) * rstd;
+      if (w) o *= w[c];
+      if (b) o += b[c];
+      yr[c] = from_float<T>(o);
+    }
+  }
+  if (lane == 0) {
+    mean_out[row] = mean;
+    rstd_out[row] = rstd;
+  }
+}
+
+// LayerNorm backward. dx per row; dw / db are accumulated per block into partial[blockIdx.x][2][C]
+// (summed on the host side in a fixed order, so the result is deterministic).
+template <typename T, int K>
+__global__ void __launch_bounds__(256) layer_norm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x,
+                                                             const float* __restrict__ w,
+                                                             const float* __restrict__ mean_in,
+                                                             const float* __restrict__ rstd_in, T* __restrict__ dx,
+                                                             float* __restrict__ partial, int64_t rows, int C) {
+  extern __shared__ float smem[];  // [warps][2][C]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+  float aw[K], ab[K];
+#pragma unroll
+  for (int k = 0; k < K; ++k) aw[k] = ab[k] = 0.f;
+  for (int64_t row = (int64_t)blockIdx.x * nwarp + warp; row < rows; row += (int64_t)gridDim.x * nwarp) {
+    const T* xr = x + row * C;
+    const T* gr = dy + row * C;
+    const float mean = mean_in[row], rstd = rstd_in[row];
+    float xh[K], g[K];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+      const int c = lane + 32 * k;
+      if (c < C) {
+        const float go = to_float<T>(gr[c]);
+        xh[k] = (to_float<T>(xr[c]) - mean) * rstd;
+        g[k] = w ? go * w[c] : go;
+        aw[k] += go * xh[k];
+        ab[k] += go;
+        s1 += g[k];
+        s2 += g[k] * xh[k];
+      } else {
+        xh[k] = g[k] = 0.f;
+      }
+    }
+    s1 = warp_sum(s1) / C;
+    s2 = warp_sum(s2) / C;
+    T* dr = dx + row * C;
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+      const int c = lane + 32 * k;
+      if (c < C) dr[c] = from_float<T>(rstd * (g[k] - s1 - xh[k] * s2));
+    }
+  }
+  if (partial == nullptr) return;
+#pragma unroll
+  for (int k = 0; k < K; ++k) {
+    const int c = lane + 32 * k;
+    if (c < C) {
+      smem[(warp * 2 + 0) * C + c] = aw[k];
+      smem[(warp * 2 + 1) * C + c] = ab[k];
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < 2 * C; i += blockDim.x) {
+    float s = 0.f;
+    for (int wi = 0; wi < nwarp; ++wi) s += smem[wi * 2 * C + i];
+    partial[(int64_t)blockIdx.x * 2 * C + i] = s;
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void swiglu_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t rows, int D) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= rows * D) return;
+  const int64_t r = i / D;
+  const int c = (int)(i - r * D);
+  const float a = to_float<T>(x[r * 2 * D + c]), b = to_float<T>(x[r * 2 * D + D + c]);
+  y[i] = from_float<T>(a * sigmoidf_(a) * b);
+}
+
+template <typename T>
+__global__ void swiglu_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, T* __restrict__ dx, int64_t rows,
+                                  int D) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= rows * D) return;
+  const int64_t r = i / D;
+  const int c = (int)(i - r * D);
+  const float a = to_float<T>(x[r * 2 * D + c]), b = to_float<T>(x[r * 2 * D + D + c]), g = to_float<T>(dy[i]);
+  const float s = sigmoidf_(a);
+  dx[r * 2 * D + c] = from_float<T>(g * b * s * (1.f + a * (1.f - s)));
+  dx[r * 2 * D + D + c] = from_float<T>(g * a * s);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Dropout whose Bernoulli draw is shared along one axis of x viewed as [outer, A, B, C]:
+// share_rows: mask index (outer, b, c)  (shared along A);  else: (outer, a, c)  (shared along B).
+// The mask is never stored: it is regenerated from (seed, mask index) in forward and backward.
+__device__ __forceinline__ float drop_scale(const Philox& rng, int64_t mask_idx, float p, float inv_keep) {
+  const uint4 r = rng((uint64_t)(mask_idx >> 2), 0);
+  const uint32_t bits = ((mask_idx & 3) == 0) ? r.x : ((mask_idx & 3) == 1) ? r.y : ((mask_idx & 3) == 2) ? r.z : r.w;
+  return uniform01(bits) >= p ? inv_keep : 0.f;
+}
+
+template <typename T, bool kAdd>
+__global__ void dropout_shared_kernel(const T* __restrict__ res, const T* __restrict__ x, T* __restrict__ out,
+                                      int64_t total, int64_t A, int64_t B, int64_t C, bool share_rows, float p,
+                                      uint64_t seed) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const int64_t c = i % C, ab = i / C, b = ab % B, oa = ab / B, a = oa % A, o = oa / A;
+  const int64_t mi = share_rows ? (o * B + b) * C + c : (o * A + a) * C + c;
+  const Philox rng(seed);
+  const float m = drop_scale(rng, mi, p, 1.f / (1.f - p));
+  const float v = to_float<T>(x[i]) * m;
+  out[i] = from_float<T>(kAdd ? to_float<T>(res[i]) + v : v);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Flat AdamW + EMA: g = grad * scale; decoupled decay; moments; bias-corrected update; shadow lerp.
+__global__ void __launch_bounds__(256) adamw_ema_kernel(float4* __restrict__ p, const float4* __restrict__ g,
+                                                        float4* __restrict__ m, float4* __restrict__ v,
+                                                        float4* __restrict__ ema, const float4* __restrict__ decay,
+                                                        const float* __restrict__ scale_ptr, int64_t n4, float lr,
+                                                        float b1, float b2, float eps, float bc1, float bc2_sqrt,
+                                                        float ema_w) {
+  const float scale = *scale_ptr;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (int64_t)gridDim.x * blockDim.x) {
+    float4 pp = p[i], gg = g[i], mm = m[i], vv = v[i], dd = decay[i];
+    float* P = &pp.x; float* G = &gg.x; float* M = &mm.x; float* V = &vv.x; float* D = &dd.x;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float gk = G[k] * scale;
+      float pk = P[k] * (1.f - lr * D[k]);
+      M[k] = M[k] + (gk - M[k]) * (1.f - b1);
+      V[k] = V[k] * b2 + gk * gk * (1.f - b2);
+      pk -= (lr / bc1) * M[k] / (sqrtf(V[k]) / bc2_sqrt + eps);
+      P[k] = pk;
+    }
+    p[i] = pp; m[i] = mm; v[i] = vv;
+    if (ema) {
+      float4 ee = ema[i];
+      ee.x += (pp.x - ee.x) * ema_w; ee.y += (pp.y - ee.y) * ema_w;
+      ee.z += (pp.z - ee.z) * ema_w; ee.w += (pp.w - ee.w) * ema_w;
+      ema[i] = ee;
+    }
+  }
+}
+
+}  // namespace df3
+
+// ================================================================================================
+// host side
+using torch::Tensor;
+
+static inline cudaStream_t stream() { return at::cuda::getCurrentCUDAStream(); }
+
+std::tuple<Tensor, Tensor, Tensor> df3_layer_norm_fwd(const Tensor& x, const c10::optional<Tensor>& w,
+                                                      const c10::optional<Tensor>& b, double eps) {
+  TORCH_CHECK(x.is_cuda() && x.is_contiguous(), "layer_norm: x must be a contiguous CUDA tensor");
+  const int C = x.size(-1);
+  TORCH_CHECK(C <= 32 * df3::kLnMaxPerLane, "layer_norm: at most 1024 channels");
+  const int64_t rows = x.numel() / C;
+  c10::cuda::CUDAGuard guard(x.device());
+  auto y = torch::empty_like(x);
+  auto opts = x.options().dtype(torch::kFloat32);
+  auto mean = torch::empty({rows}, opts), rstd = torch::empty({rows}, opts);
+  if (rows == 0) return {y, mean, rstd};
+  const float* wp = w.has_value() ? w->data_ptr<float>() : nullptr;
+  const float* bp = b.has_value() ? b->data_ptr<float>() : nullptr;
+  const int warps = 8;
+  const unsigned grid = (unsigned)((rows + warps - 1) / warps);
+  const bool bf16 = x.scalar_type() == torch::kBFloat16;
+  TORCH_CHECK(bf16 || x.scalar_type() == torch::kFloat32, "layer_norm: bf16 or fp32");
+#define DF3_LN_FWD(K)                                                                                              \
+  do {                                                                                                             \
+    if (bf16)                                                                                                      \
+      df3::layer_norm_fwd_kernel<__nv_bfloat16, K><<<grid, warps * 32, 0, stream()>>>(                             \
+          (const __nv_bfloat16*)x.data_ptr(), wp, bp, (__nv_bfloat16*)y.data_ptr(), mean.data_ptr<float>(),        \
+          rstd.data_ptr<float>(), rows, C, (float)eps);                                                            \
+    else                                                                                                           \
+      df3::layer_norm_fwd_kernel<float, K><<<grid, warps * 32, 0, stream()>>>(                                     \
+          x.data_ptr<float>(), wp, bp, y.data_ptr<float>(), mean.data_ptr<float>(), rstd.data_ptr<float>(), rows,  \
+          C, (float)eps);                                                                                          \
+  } while (0)
+  if (C <= 128) DF3_LN_FWD(4); else if (C <= 256) DF3_LN_FWD(8); else if (C <= 512) DF3_LN_FWD(16); else DF3_LN_FWD(32);
+#undef DF3_LN_FWD
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  return {y, mean, rstd};
+}
+
+// returns (dx, partial [blocks, 2, C]); partial is empty when want_wb is false
+std::tuple<Tensor, Tensor> df3_layer_norm_bwd(const Tensor& dy, const Tensor& x, const c10::optional<Tensor>& w,
+                                              const Tensor& mean, const Tensor& rstd, bool want_wb) {
+  const int C = x.size(-1);
+  const int64_t rows = x.numel() / C;
+  c10::cuda::CUDAGuard guard(x.device());
+  auto dx = torch::empty_like(x);
+  const int warps = 8;
+  const int blocks = (int)std::min<int64_t>((rows + warps - 1) / warps, 148 * 4);
+  auto partial = want_wb ? torch::empty({blocks, 2, C}, x.options().dtype(torch::kFloat32)) : torch::empty({0}, x.options().dtype(torch::kFloat32));
+  if (rows == 0) return {dx, partial};
+  const float* wp = w.has_value() ? w->data_ptr<float>() : nullptr;
+  float* pp = want_wb ? partial.data_ptr<float>() : nullptr;
+  const size_t smem = want_wb ? (size_t)warps * 2 * C * sizeof(float) : 0;
+  const bool bf16 = x.scalar_type() == torch::kBFloat16;
+#define DF3_LN_BWD(K)                                                                                              \
+  do {                                                                                                             \
+    if (bf16) {                                                                                                    \
+      auto k = df3::layer_norm_bwd_kernel<__nv_bfloat16, K>;                                                       \
+      if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);       \
+      k<<<blocks, warps * 32, smem, stream()>>>((const __nv_bfloat16*)dy.data_ptr(),                               \
+                                                (const __nv_bfloat16*)x.data_ptr(), wp, mean.data_ptr<float>(),    \
+                                                rstd.data_ptr<float>(), (__nv_bfloat16*)dx.data_ptr(), pp, rows, C); \
+    } else {                                                                                                       \
+      auto k = df3::layer_norm_bwd_kernel<float, K>;                                                               \
+      if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);       \
+      k<<<blocks, warps * 32, smem, stream()>>>(dy.data_ptr<float>(), x.data_ptr<float>(), wp,                     \
+                                                mean.data_ptr<float>(), rstd.data_ptr<float>(),                    \
+                                                dx.data_ptr<float>(), pp, rows, C);                                \
+    }                                                                                                              \
+  } while (0)
+  if (C <= 128) DF3_LN_BWD(4); else if (C <= 256) DF3_LN_BWD(8); else if (C <= 512) DF3_LN_BWD(16); else DF3_LN_BWD(32);
+#undef DF3_LN_BWD
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  return {dx, partial};
+}
+
+Tensor df3_swiglu_fwd(const Tensor& x) {
+  TORCH_CHECK(x.is_cuda() && x.is_contiguous() && x.size(-1) % 2 == 0, "swiglu: contiguous CUDA tensor, even width");
+  c10::cuda::CUDAGuard guard(x.device());
+  const int D = x.size(-1) / 2;
+  const int64_t rows = x.numel() / (2 * D);
+  auto shape = x.sizes().vec();
+  shape.back() = D;
+  auto y = torch::empty(shape, x.options());
+  const int64_t n = rows * D;
+  if (n == 0) return y;
+  const unsigned grid = (unsigned)((n + 255) / 256);
+  if (x.scalar_type() == torch::kBFloat16)
+    df3::swiglu_fwd_kernel<__nv_bfloat16><<<grid, 256, 0, stream()>>>((const __nv_bfloat16*)x.data_ptr(), (__nv_bfloat16*)y.data_ptr(), rows, D);
+  else
+    df3::swiglu_fwd_kernel<float><<<grid, 256, 0, stream()>>>(x.data_ptr<float>(), y.data_ptr<float>(), rows, D);
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  return y;
+}
+
+Tensor df3_swiglu_bwd(const Tensor& dy, const Tensor& x) {
+  c10::cuda::CUDAGuard guard(x.device());
+  const int D = x.size(-1) / 2;
+  const int64_t rows = x.numel() / (2 * D);
+  auto dx = torch::empty_like(x);
+  const int64_t n = rows * D;
+  if (n == 0) return dx;
+  const unsigned grid = (unsigned)((n + 255) / 256);
+  if (x.scalar_type() == torch::kBFloat16)
+    df3::swiglu_bwd_kernel<__nv_bfloat16><<<grid, 256, 0, stream()>>>((const __nv_bfloat16*)dy.data_ptr(), (const __nv_bfloat16*)x.data_ptr(), (__nv_bfloat16*)dx.data_ptr(), rows, D);
+  else
+    df3::swiglu_bwd_kernel<float><<<grid, 256, 0, stream()>>>(dy.data_ptr<float>(), x.data_ptr<float>(), dx.data_ptr<float>(), rows, D);
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  return dx;
+}
+
+// x viewed as [outer, A, B, C]; res may be undefined (then out = dropout(x), used by backward)
+Tensor df3_dropout_shared(const c10::optional<Tensor>& res, const Tensor& x, int64_t A, int64_t B, int64_t C,
+                          bool share_rows, double p, int64_t seed) {
+  TORCH_CHECK(x.is_cuda() && x.is_contiguous(), "dropout_shared: contiguous CUDA tensor");
+  c10::cuda::CUDAGuard guard(x.device());
+  auto out = torch::empty_like(x);
+  const int64_t n = x.numel();
+  if (n == 0) return out;
+  const unsigned grid = (unsigned)((n + 255) / 256);
+  const bool add = res.has_value();
+  if (add) TORCH_CHECK(res->is_contiguous() && res->sizes() == x.sizes() && res->scalar_type() == x.scalar_type(), "dropout_shared: residual mismatch");
+#define DF3_LAUNCH(T, ADD)                                                                                         \
+  df3::dropout_shared_kernel<T, ADD><<<grid, 256, 0, stream()>>>(ADD ? (const T*)res->data_ptr() : nullptr,          \
+                                                                 (const T*)x.data_ptr(), (T*)out.data_ptr(), n, A, B, \
+                                                                 C, share_rows, (float)p, (uint64_t)seed)
+  if (x.scalar_type() == torch::kBFloat16) {
+    if (add) DF3_LAUNCH(__nv_bfloat16, true); else DF3_LAUNCH(__nv_bfloat16, false);
+  } else {
+    TORCH_CHECK(x.scalar_type() == torch::kFloat32, "dropout_shared: bf16 or fp32");
+    if (add) DF3_LAUNCH(float, true); else DF3_LAUNCH(float, false);
+  }
+#undef DF3_LAUNCH
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  return out;
+}
+
+void df3_adamw_ema(Tensor p, const Tensor& g, Tensor m, Tensor v, const c10::optional<Tensor>& ema,
+                   const Tensor& decay, const Tensor& scale, double lr, double b1, double b2, double eps, double bc1,
+                   double bc2, double ema_w) {
+  TORCH_CHECK(p.is_cuda() && p.scalar_type() == torch::kFloat32 && p.numel() % 4 == 0, "adamw_ema: flat fp32, numel % 4 == 0");
+  c10::cuda::CUDAGuard guard(p.device());
+  const int64_t n4 = p.numel() / 4;
+  if (n4 == 0) return;
+  const int blocks = (int)std::min<int64_t>((n4 + 255) / 256, 148 * 8);
+  df3::adamw_ema_kernel<<<blocks, 256, 0, stream()>>>(
+      (float4*)p.data_ptr<float>(), (const float4*)g.data_ptr<float>(), (float4*)m.data_ptr<float>(),
+      (float4*)v.data_ptr<float>(), ema.has_value() ? (float4*)ema->data_ptr<float>() : nullptr,
+      (const float4*)decay.data_ptr<float>(), scale.data_ptr<float>(), n4, (float)lr, (float)b1, (float)b2, (float)eps,
+      (float)bc1, (float)std::sqrt(bc2), (float)ema_w);
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+}
