@@ -1,0 +1,170 @@
+"""Reference arm of ``bench.py``: the unmodified reference package timed on the same config.
+
+Only the reference's own code runs the model here: ``deepfold3.model.model.DeepFold3``,
+``deepfold3.training.step.training_step``, ``wrap_ddp`` / ``build_optimizer`` / ``WrappedOptimizer``
+/ ``EMA``. The package comes from ``baseline/_ref`` (a ``pip install --target`` of the reference
+plus its ``src/deepfold3`` tree). Its data stack imports ``gemmi``, ``rdkit``,
+``zstandard`` and ``pdbeccdutils`` at module import time; none is installable offline and none is
+called on the synthetic-feature path, so inert stand-in modules are registered for the missing ones
+before the import. The synthetic batch comes from this repository's generator (torch only).
+"""
+
+from __future__ import annotations
+
+import importlib
+import json
+import os
+import sys
+import types
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+REF_PATH = os.path.join(HERE, "_ref")
+
+
+class _Inert(types.ModuleType):
+    """Stand-in for an uninstallable dependency: any attribute or call yields another stand-in."""
+
+    def __getattr__(self, name):
+        if name.startswith("__"):
+            raise AttributeError(name)
+        sub = _Inert(f"{self.__name__}.{name}")
+        setattr(self, name, sub)
+        sys.modules[sub.__name__] = sub
+        return sub
+
+    def __call__(self, *args, **kwargs):
+        return _Inert(self.__name__ + "()")
+
+    def __iter__(self):
+        return iter(())
+
+    def __mro_entries__(self, bases):
+        return (object,)
+
+
+def _stub_missing(names=("zstandard", "gemmi", "rdkit", "pdbeccdutils", "wandb")) -> list[str]:
+    done = []
+    for name in names:
+        try:
+            importlib.import_module(name)
+        except Exception:  # noqa: BLE001
+            mod = _Inert(name)
+            mod.__path__ = []
+            sys.modules[name] = mod
+            done.append(name)
+    return done
+
+
+def unavailable(why: str) -> None:
+    print(json.dumps({"impl": "reference", "unavailable": why}), flush=True)
+
+
+def run_reference(args, bench) -> None:
+    if not os.path.isdir(os.path.join(REF_PATH, "deepfold3", "model")):
+        return unavailable("baseline/_ref does not hold the reference package (offline install missing)")
+    sys.path.insert(0, REF_PATH)
+    stubbed = _stub_missing()
+    try:
+        import torch
+        import torch.distributed as dist
+        from deepfold3.model.config import ModelConfig, TrainingConfig
+        from deepfold3.model.model import DeepFold3
+        from deepfold3.training.accumulator import AccumulationLoop
+        from deepfold3.training.distributed import init_process_group
+        from deepfold3.training.ema import EMA
+        from deepfold3.training.optim import WrappedOptimizer, build_optimizer, wrap_ddp
+        from deepfold3.training.scheduler import build_scheduler
+        from deepfold3.training.state import TrainState, seed_everything
+        from deepfold3.training.step import scaled_backward, training_step
+    except Exception as exc:  # noqa: BLE001
+        return unavailable(f"reference import failed: {type(exc).__name__}: {exc}"[:300])
+    if not torch.cuda.is_available():
+        return unavailable("no CUDA device")
+
+    info = init_process_group(timeout_s=1800.0)
+    world = info.world_size
+    seed_everything(bench.SEED, info.rank)
+    model_cfg = ModelConfig()
+    model_cfg.msa_crop_size = bench.N_MSA
+    if args.blocks:
+        model_cfg.pairformer.num_layer = args.blocks
+    opt_mode = os.environ.get("DF3_REF_OPTIM", "train")
+    o = model_cfg.optim
+    o.use_gradient_checkpointing = True
+    if opt_mode == "train":  # the kernel flags of the reference's production recipe (configs/initial.yaml:396-418)
+        try:
+            import triton  # noqa: F401
+
+            o.use_fused_evo_attention = True
+            o.use_fused_swiglu = True
+            o.use_fused_triangle_mul = True
+            o.use_fused_transition_pair = True
+        except ImportError:
+            opt_mode = "none (triton missing)"
+    chunk = int(os.environ.get("DF3_REF_DIFFUSION_CHUNK", "8"))
+    train_cfg = TrainingConfig(**bench.shared_train_settings(args.tokens), diffusion_chunk_size=chunk,
+                               per_rank_grad_clip=False)  # fmt: skip
+    model = DeepFold3(model_cfg).to(info.device)
+    model.train()
+    ddp_model, _ = wrap_ddp(model, info, train_cfg)
+    accumulator = AccumulationLoop(ddp_model=ddp_model, dist=info, num_steps=1, per_rank_clip=False)
+    optimizer = build_optimizer(model, train_cfg)
+    scheduler = build_scheduler(optimizer, train_cfg)
+    ema = EMA(model, decay=train_cfg.ema_decay)
+    scaler = torch.amp.GradScaler("cuda", enabled=False)
+    wrapped = WrappedOptimizer(optimizer=optimizer, scheduler=scheduler, scaler=scaler, model=model, dist_info=info,
+                               cfg=train_cfg)  # fmt: skip
+    state = TrainState()
+    host_batch = bench.make_host_batch(info.rank, args.tokens)
+    dev_batch = {k: v.to(info.device) for k, v in host_batch.items()}
+    flush_buf = torch.zeros(64 * 1024 * 1024, device=info.device)
+
+    def one_step(i, features):
+        state.global_step = i
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            loss, *_ = training_step(ddp_model, features, cfg=train_cfg, model_cfg=model_cfg, global_step=i,
+                                     accumulator=accumulator, scaler=scaler, device=info.device)  # fmt: skip
+        wrapped.add_microstep_loss(loss)
+        with accumulator.step_context(is_sync_step=True):
+            if loss.requires_grad:
+                scaled_backward(scaler, loss, 1)
+        result = wrapped.step_or_skip(state)
+        if result.advanced:
+            ema.update(model)
+        return loss
+
+    def device_step(i):
+        one_step(i, dict(dev_batch))
+
+    def e2e_step(i):
+        loss = one_step(i, {k: v.to(info.device, non_blocking=True) for k, v in host_batch.items()})
+        float(loss.item())
+
+    def sync():
+        if world > 1:
+            dist.barrier()
+
+    try:
+        for i in range(args.warmup):
+            device_step(i)
+        torch.cuda.synchronize()
+        sampler = bench.ClockSampler(info.local_rank)
+        sampler.start()
+        times = bench.timed_loop(device_step, args.steps, args.warmup, sync, flush_buf)
+        clocks = sampler.stop()
+        e2e_times = bench.timed_loop(e2e_step, args.steps, args.warmup, sync, flush_buf)
+    except Exception as exc:  # noqa: BLE001
+        if info.rank == 0:
+            unavailable(f"reference step failed ({opt_mode}): {type(exc).__name__}: {exc}"[:300])
+        return
+    step_ms = bench.reduce_max(sum(times) / len(times), world)
+    e2e_ms = bench.reduce_max(sum(e2e_times) / len(e2e_times), world)
+    peak = torch.cuda.max_memory_allocated() / 2**30
+    if info.rank == 0:
+        bench.emit(args, "reference", step_ms, e2e_ms, clocks, 0, bench.batch_bytes(host_batch),
+                   {"reference_optim": opt_mode, "activation_checkpointing": True, "diffusion_chunk": chunk,
+                    "stubbed_imports": stubbed, "peak_mem_gib": round(peak, 1),
+                    "recycles": [bench.recycles_for(args.warmup + i) for i in range(args.steps)]})  # fmt: skip
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()

@@ -1,0 +1,275 @@
+#!/usr/bin/env python
+"""Headline benchmark: full AF3-size DeepFold3 training throughput (samples/s) at crop 384.
+
+    python bench.py --gpus N --steps K --warmup W [--impl ours|reference]
+
+Config (both arms): default ModelConfig (4 MSA blocks, 48 Pairformer blocks, 24-block diffusion
+transformer, 4 confidence blocks), bf16 autocast with fp32 master weights, one synthetic 2-chain
+protein complex of 384 tokens (~3000 atoms) per GPU, 1024 MSA rows at 30 % mutation, 4 templates,
+48 diffusion samples, 20-step mini-rollout, gradient accumulation 1, AdamW + EMA 0.999. A step is
+forward + loss + backward + gradient reduction + optimizer + EMA; the number of recycles of step i
+is ``Random(seed + i).randint(0, 3)`` in both arms. Weak scaling: one example per GPU.
+
+``--impl reference`` drives the unmodified reference package installed under ``baseline/_ref``
+through its own ``training_step`` / ``WrappedOptimizer`` / DDP path and prints the same JSON line.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+SEED = 101
+N_TOKENS, N_MSA, N_TEMPLATES, N_DIFFUSION = 384, 1024, 4, 48
+BASELINE_VALUE = None  # BASELINE.md publishes no B200 number for this metric
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--tokens", type=int, default=N_TOKENS, help="crop size (the headline config is 384)")
+    ap.add_argument("--blocks", type=int, default=0, help="debug only: override the Pairformer depth")
+    return ap.parse_args()
+
+
+class ClockSampler:
+    """nvidia-smi SM clock / throttle-reason samples every 200 ms while the timed region runs."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")  # fmt: skip
+
+    def __init__(self, gpu_index: int):
+        self.gpu, self.rows, self.proc = gpu_index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "200",
+                 "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)  # fmt: skip
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for r in self.rows:
+            if len(r) < 9:
+                continue
+            try:
+                sm.append(float(r[1]))
+                mx.append(float(r[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, r[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}  # fmt: skip
+
+
+def recycles_for(step: int, max_recycles: int = 3) -> int:
+    import random
+
+    return random.Random(SEED + step).randint(0, max_recycles)
+
+
+def make_host_batch(rank: int, tokens: int):
+    """One synthetic example (batch axis 1) in pinned host memory; the generator imports only torch + tables."""
+    import torch
+
+    from deepfold3_dev_b200.data.synthetic import batch_features, split_lengths, synthetic_complex
+
+    a, b = split_lengths(tokens, 2)
+    feats = synthetic_complex([("protein", a), ("protein", b)], num_msa=N_MSA, num_templates=N_TEMPLATES,
+                              seed=1000 + rank)  # fmt: skip
+    batch = batch_features([feats])
+    if torch.cuda.is_available():
+        batch = {k: (v.pin_memory() if isinstance(v, torch.Tensor) else v) for k, v in batch.items()}
+    return batch
+
+
+def batch_bytes(batch) -> int:
+    import torch
+
+    return int(sum(v.numel() * v.element_size() for v in batch.values() if isinstance(v, torch.Tensor)))
+
+
+def flush_l2(buf):
+    buf.add_(1)  # touches 256 MB, more than the 126 MB L2
+
+
+def timed_loop(step_fn, steps: int, first_step: int, dist_barrier, flush_buf):
+    """K steps bracketed by barrier + synchronize, each timed with CUDA events; returns per-step ms."""
+    import torch
+
+    dist_barrier()
+    torch.cuda.synchronize()
+    times = []
+    for i in range(steps):
+        flush_l2(flush_buf)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        step_fn(first_step + i)
+        e1.record()
+        e1.synchronize()
+        times.append(e0.elapsed_time(e1))
+    dist_barrier()
+    torch.cuda.synchronize()
+    return times
+
+
+def reduce_max(value: float, world: int) -> float:
+    if world <= 1:
+        return value
+    import torch
+    import torch.distributed as dist
+
+    t = torch.tensor([value], device="cuda", dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def emit(args, impl, step_ms, e2e_ms, clocks, launches, bytes_in, extra_cfg):
+    world = args.gpus
+    value = world * 1000.0 / step_ms
+    line = {
+        "metric": "train samples/s @crop384",
+        "value": value,
+        "unit": "samples/s",
+        "n_gpus": world,
+        "steps": args.steps,
+        "warmup": args.warmup,
+        "ms_per_step": step_ms,
+        "higher_is_better": True,
+        "scaling": "weak",
+        "vs_baseline": (value / BASELINE_VALUE) if BASELINE_VALUE else None,
+        "dtype": "bf16",
+        "data": "synthetic (random sequences, random-init weights)",
+        "impl": impl,
+        "config": {
+            "model": "DeepFold3 default ModelConfig (48 Pairformer, 24 diffusion blocks, 368M params)",
+            "global_batch": world,
+            "seq_len": args.tokens,
+            "msa_rows": N_MSA,
+            "templates": N_TEMPLATES,
+            "diffusion_samples": N_DIFFUSION,
+            "parallelism": f"dp{world}",
+            "l2": "256 MB buffer rewritten between timed steps; activations exceed L2",
+            **extra_cfg,
+        },
+        "clocks": clocks,
+        "e2e": {"value": world * 1000.0 / e2e_ms, "unit": "samples/s", "h2d_bytes_per_step": bytes_in,
+                "d2h_bytes_per_step": 8, "ms_per_step": e2e_ms},  # fmt: skip
+        "gpu_launches": launches,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def shared_train_settings(tokens: int) -> dict:
+    """TrainingConfig fields set identically in both arms."""
+    return dict(
+        lr=1.8e-3, weight_decay=0.0, betas=(0.9, 0.95), eps=1e-8, warmup_steps=1000, grad_clip_norm=10.0,
+        grad_norm_fp64=True, accumulate_grad_batches=1, ema_decay=0.999, max_tokens=tokens, max_atoms=4096,
+        max_recycles=3, batch_size_per_rank=1, diffusion_batch_size=N_DIFFUSION, mini_rollout_steps=20,
+        mini_rollout_samples=1, permute_gt_before_noise=True, alpha_diffusion=4.0, alpha_smooth_lddt=1.0,
+        alpha_distogram=0.03, alpha_confidence=1e-4, alpha_pae=1.0, dtype="bf16", seed=SEED, uniform_recycle=True,
+        log_tm_true=True, max_consecutive_nan_skips=100,
+    )  # fmt: skip
+
+
+def run_ours(args):
+    import torch
+
+    sys.path.insert(0, ROOT)
+    from deepfold3_dev_b200.config.schema import ModelConfig, TrainingConfig
+    from deepfold3_dev_b200.ops import autograd_ops
+    from deepfold3_dev_b200.parallel.dist import barrier, init_process_group
+    from deepfold3_dev_b200.training.trainer import Trainer
+
+    info = init_process_group(timeout_s=1800.0)
+    world = info.world_size
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    model_cfg = ModelConfig()
+    model_cfg.msa_crop_size = N_MSA
+    model_cfg.optim.use_gradient_checkpointing = os.environ.get("DF3_CKPT", "1") == "1"
+    if args.blocks:
+        model_cfg.pairformer.num_layer = args.blocks
+    chunk = int(os.environ.get("DF3_DIFFUSION_CHUNK", "0"))
+    train_cfg = TrainingConfig(**shared_train_settings(args.tokens), diffusion_chunk_size=chunk,
+                               per_rank_grad_clip=False, output_dir="/tmp/df3_bench")  # fmt: skip
+    trainer = Trainer(train_cfg, model_cfg, dist_info=info)
+    host_batch = make_host_batch(info.rank, args.tokens)
+    dev_batch = {k: (v.to(info.device) if isinstance(v, torch.Tensor) else v) for k, v in host_batch.items()}
+    flush_buf = torch.zeros(64 * 1024 * 1024, device=info.device)
+
+    def device_step(i):
+        trainer.state.global_step = i
+        loss, _, _ = trainer.micro_step(dict(dev_batch), num_recycles=recycles_for(i))
+        trainer.engine.step_or_skip(trainer.state)
+
+    def e2e_step(i):
+        trainer.state.global_step = i
+        trainer.train_step(dict(host_batch), num_recycles=recycles_for(i))
+
+    for i in range(args.warmup):
+        device_step(i)
+    torch.cuda.synchronize()
+    sampler = ClockSampler(info.local_rank)
+    sampler.start()
+    autograd_ops.launch_count(reset=True)
+    sync = lambda: barrier(info)  # noqa: E731
+    times = timed_loop(device_step, args.steps, args.warmup, sync, flush_buf)
+    launches = autograd_ops.launch_count()
+    clocks = sampler.stop()
+    e2e_step(args.warmup - 1 if args.warmup else 0)  # pinned staging buffers allocated outside the timed region
+    e2e_times = timed_loop(e2e_step, args.steps, args.warmup, sync, flush_buf)
+    step_ms = reduce_max(sum(times) / len(times), world)
+    e2e_ms = reduce_max(sum(e2e_times) / len(e2e_times), world)
+    peak = torch.cuda.max_memory_allocated() / 2**30
+    if info.is_main:
+        emit(args, "ours", step_ms, e2e_ms, clocks, launches, batch_bytes(host_batch),
+             {"activation_checkpointing": model_cfg.optim.use_gradient_checkpointing, "diffusion_chunk": chunk,
+              "peak_mem_gib": round(peak, 1), "recycles": [recycles_for(args.warmup + i) for i in range(args.steps)]})  # fmt: skip
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        from baseline.reference_arm import run_reference
+
+        run_reference(args, sys.modules[__name__])
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()
