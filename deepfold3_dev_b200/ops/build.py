@@ -47,7 +47,6 @@ def build(force: bool = False, verbose: bool = False) -> str:
         sources=srcs,
         extra_cflags=["-O3", "-std=c++17"] + defines,
         extra_cuda_cflags=["-O3", "-std=c++17", "-lineinfo", "--use_fast_math", "-Xptxas", "-v"] + ARCH_FLAGS + defines,
-        extra_ldflags=["-lcuda"],
         build_directory=BUILD_DIR,
         is_python_module=False,
         verbose=verbose,
