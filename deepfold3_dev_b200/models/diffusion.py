@@ -17,6 +17,7 @@ import torch.nn.functional as F
 from torch.utils.checkpoint import checkpoint
 
 from .. import ops
+from . import denoise_graph
 from .atom_attention import AtomDecoder, AtomEncoder
 from .diffusion_modules import (  # noqa: F401 - re-exported API
     DiffusionConditioningBlock,
@@ -268,17 +269,24 @@ class DiffusionHead(nn.Module):
             uncond.append((term.scale, static_u, lo, hi))
 
         atom_mask_b = aug_mask if batched else aug_mask[0]
+        statics = [static] + [u[1] for u in uncond]
+        if denoise_graph.enabled(positions) and cfg.steps > 4 and len(statics) == 1:
+            graphs = self.__dict__.setdefault("_denoiser_graphs", denoise_graph.DenoiserGraphs())
+            nl0 = positions.new_full((B, 1), sig_hat_host[0])
+            denoisers = [graphs.get(self._denoise_core, positions, nl0, st) for st in statics]
+        else:
+            denoisers = [lambda p, n, st=st: self._denoise_core(p, n, st) for st in statics]
         for step in range(cfg.steps):
             s_prev, s_next, s_hat = sig_host[step], sig_host[step + 1], sig_hat_host[step]
             positions = augment(positions, aug_mask, generator)
             noise_scale = cfg.noise_scale * max(s_hat**2 - s_prev**2, 0.0) ** 0.5
             pos_hat = positions + noise_scale * randn_tokens()
             nl = pos_hat.new_full((B, 1), s_hat)
-            den_c = self._denoise_core(pos_hat, nl, static)
+            den_c = denoisers[0](pos_hat, nl)
             denoised = den_c
-            for w, static_u, lo, hi in uncond:
+            for ui, (w, static_u, lo, hi) in enumerate(uncond):
                 if lo <= s_hat <= hi:
-                    denoised = denoised + (w - 1.0) * (den_c - self._denoise_core(pos_hat, nl, static_u))
+                    denoised = denoised + (w - 1.0) * (den_c - denoisers[ui + 1](pos_hat, nl))
             steer = not restraint_after_step or s_hat < restraint_after_sigma
             if restraints and restraint_weight and steer:
                 denoised = rst.steer(denoised, atom_mask_b, restraints, s_hat, cfg.sigma_data, restraint_weight,

@@ -15,6 +15,7 @@ from torch.utils.checkpoint import checkpoint
 from .. import ops
 from .attention import GridSelfAttention, MSAAttention, SingleAttention
 from .branch_scaler import make_branch_scaler
+from .primitives import Gain as _gain
 from .primitives import (
     LayerNorm,
     LinearNoBias,
@@ -77,15 +78,15 @@ class EvoformerBlock(nn.Module):
 
     def forward(self, msa, pair, msa_mask, pair_mask):
         pp, pm, tr, s = self.pair_dropout, self.msa_dropout, self.training, self.residual_out_scale
-        pair = pair + s * self.outer_product(msa, msa_mask)
-        msa = ops.dropout_add(msa, s * self.row_attn(msa, msa_mask, pair), pm, tr, -3)
-        msa = msa + s * map_row_chunks(self.msa_transition, msa, self.msa_row_chunk)
-        pair = ops.dropout_add(pair, s * self.tri_mul_out(pair, pair_mask), pp, tr, -3)
-        pair = ops.dropout_add(pair, s * self.tri_mul_in(pair, pair_mask), pp, tr, -3)
+        pair = pair + _gain(s) * self.outer_product(msa, msa_mask)
+        msa = ops.dropout_add(msa, _gain(s) * self.row_attn(msa, msa_mask, pair), pm, tr, -3)
+        msa = msa + _gain(s) * map_row_chunks(self.msa_transition, msa, self.msa_row_chunk)
+        pair = ops.dropout_add(pair, _gain(s) * self.tri_mul_out(pair, pair_mask), pp, tr, -3)
+        pair = ops.dropout_add(pair, _gain(s) * self.tri_mul_in(pair, pair_mask), pp, tr, -3)
         if self.use_triangle_attention:
-            pair = ops.dropout_add(pair, s * self.pair_attn_row(pair, pair_mask), pp, tr, -3)
-            pair = ops.dropout_add(pair, s * self.pair_attn_col(pair, pair_mask), pp, tr, -2)
-        pair = pair + s * map_pair_transition(self.pair_transition, pair, self.pair_chunk_budget, 4)
+            pair = ops.dropout_add(pair, _gain(s) * self.pair_attn_row(pair, pair_mask), pp, tr, -3)
+            pair = ops.dropout_add(pair, _gain(s) * self.pair_attn_col(pair, pair_mask), pp, tr, -2)
+        pair = pair + _gain(s) * map_pair_transition(self.pair_transition, pair, self.pair_chunk_budget, 4)
         return msa, pair
 
 
@@ -132,35 +133,35 @@ class PairFormerBlock(nn.Module):
 
     def forward(self, pair, single, pair_mask, seq_mask):
         p, tr, s = self.pair_dropout, self.training, self.residual_out_scale
-        s_pf = s * self.pair_transition_residual_gain
-        s_sf = s * self.single_transition_residual_gain
+        s_pf = _gain(s) * self.pair_transition_residual_gain
+        s_sf = _gain(s) * self.single_transition_residual_gain
         scale = self.branch_scaler
         zero = pair.new_zeros(())
-        b_tri_out = s * scale(self.tri_mul_out(pair, pair_mask))
+        b_tri_out = _gain(s) * scale(self.tri_mul_out(pair, pair_mask))
         pair = ops.dropout_add(pair, b_tri_out, p, tr, -3)
-        b_tri_in = s * scale(self.tri_mul_in(pair, pair_mask))
+        b_tri_in = _gain(s) * scale(self.tri_mul_in(pair, pair_mask))
         pair = ops.dropout_add(pair, b_tri_in, p, tr, -3)
         if self.use_triangle_attention:
-            b_row = s * scale(self.pair_attn_row(pair, pair_mask))
+            b_row = _gain(s) * scale(self.pair_attn_row(pair, pair_mask))
             pair = ops.dropout_add(pair, b_row, p, tr, -3)
-            b_col = s * scale(self.pair_attn_col(pair, pair_mask))
+            b_col = _gain(s) * scale(self.pair_attn_col(pair, pair_mask))
             pair = ops.dropout_add(pair, b_col, p, tr, -2)
         else:
             b_row = b_col = zero
-        b_pair_ffn = s_pf * scale(map_pair_transition(self.pair_transition, pair, self.pair_chunk_budget, 4))
+        b_pair_ffn = _gain(s_pf) * scale(map_pair_transition(self.pair_transition, pair, self.pair_chunk_budget, 4))
         pair = pair + b_pair_ffn
         if self.use_single_track:
             logits = map_pair_rows(
                 lambda rows: self.single_to_pair(self.single_to_pair_norm(rows)), pair, self.pair_chunk_budget,
                 4 * pair.shape[-1],
             ).movedim(-1, -3)  # fmt: skip
-            b_single_attn = s * scale(self.single_attn(single, seq_mask, logits))
+            b_single_attn = _gain(s) * scale(self.single_attn(single, seq_mask, logits))
             single = single + b_single_attn
             update = self.single_transition(single)
             probe = getattr(self, "_probe", None)
             if probe is not None and probe.enabled:
                 probe.record_block(self._probe_layer_idx, single, update, s_sf)
-            b_single_ffn = s_sf * scale(update)
+            b_single_ffn = _gain(s_sf) * scale(update)
         else:
             b_single_attn = b_single_ffn = zero
         meter = getattr(self, "_act_meter", None)

@@ -32,6 +32,18 @@ def block_residual_scale(layer_idx: int, num_layer: int, per_layer: bool, unifor
     return 1.0
 
 
+class Gain:
+    """A branch multiplier that costs nothing when it is 1: ``Gain(s) * x`` is ``x`` itself for ``s == 1``."""
+
+    __slots__ = ("value",)
+
+    def __init__(self, value: float):
+        self.value = float(value)
+
+    def __mul__(self, x):
+        return x if self.value == 1.0 else x * self.value
+
+
 def af3_linear_init_(weight: torch.Tensor, initializer: str = "linear") -> None:
     """AF3 variance-scaling init: ``zeros``, or truncated normal with var 1/fan_in (``relu``: 2/fan_in)."""
     if initializer == "zeros":

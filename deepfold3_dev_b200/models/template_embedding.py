@@ -14,6 +14,7 @@ from torch.utils.checkpoint import checkpoint
 from .. import ops
 from .attention import GridSelfAttention
 from .embedders import dgram_from_positions
+from .primitives import Gain as _gain
 from .primitives import (
     LayerNorm,
     LinearNoBias,
@@ -66,11 +67,11 @@ class TemplatePairFormerBlock(nn.Module):
 
     def forward(self, pair, pair_mask):
         p, tr, s = self.pair_dropout, self.training, self.residual_out_scale
-        pair = ops.dropout_add(pair, s * self.tri_mul_out(pair, pair_mask), p, tr, -3)
-        pair = ops.dropout_add(pair, s * self.tri_mul_in(pair, pair_mask), p, tr, -3)
-        pair = ops.dropout_add(pair, s * self.pair_attn_row(pair, pair_mask), p, tr, -3)
-        pair = ops.dropout_add(pair, s * self.pair_attn_col(pair, pair_mask), p, tr, -2)
-        return pair + s * map_pair_transition(
+        pair = ops.dropout_add(pair, _gain(s) * self.tri_mul_out(pair, pair_mask), p, tr, -3)
+        pair = ops.dropout_add(pair, _gain(s) * self.tri_mul_in(pair, pair_mask), p, tr, -3)
+        pair = ops.dropout_add(pair, _gain(s) * self.pair_attn_row(pair, pair_mask), p, tr, -3)
+        pair = ops.dropout_add(pair, _gain(s) * self.pair_attn_col(pair, pair_mask), p, tr, -2)
+        return pair + _gain(s) * map_pair_transition(
             self.pair_transition, pair, self.pair_chunk_budget, self.num_intermediate_factor
         )
 

@@ -117,16 +117,13 @@ class _TriangleMulBase(nn.Module):
         if squeeze:
             z, mask = z.unsqueeze(0), mask.unsqueeze(0)
         z0 = self.norm_left(z)
-        ab = ops.gated_dual_linear(z0, self.gate.weight, self.proj.weight, mask)
-        out_gate = torch.sigmoid(self.out_gate(z0))
         router_logits = self.router(z0) if self.use_router else None
-        a, b = ab[..., 0::2], ab[..., 1::2]
-        act = ops.triangle_contract(a, b, self.outgoing)
+        act = ops.triangle_projection_contract(z0, self.gate.weight, self.proj.weight, mask, self.outgoing)
         if self.is_mhr:
             act = self.out_proj(self._head_mix(act, router_logits))
         else:
             act = self.out_proj(self.norm_center(act))
-        out = act * out_gate
+        out = ops.sigmoid_gate_mul(z0, self.out_gate.weight, act)
         return out.squeeze(0) if squeeze else out
 
 

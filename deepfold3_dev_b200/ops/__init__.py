@@ -43,6 +43,19 @@ def _autocast_dtype(x: torch.Tensor):
     return None
 
 
+def bf16_mode(x: torch.Tensor) -> bool:
+    """True when ``x`` is a CUDA tensor that is bf16 or sits under bf16 autocast: the tensor-core kernels apply."""
+    return x.is_cuda and (x.dtype == torch.bfloat16 or _autocast_dtype(x) == torch.bfloat16)
+
+
+def fused(x: torch.Tensor, feature: str):
+    """The native namespace if ``feature`` may run on ``x``, else ``None``."""
+    if not x.is_cuda or not bf16_mode(x):
+        return None
+    nat = _native(x)
+    return nat if nat.has(feature) else None
+
+
 def layer_norm(x, weight=None, bias=None, eps: float = 1e-5):
     nat = _native(x)
     if nat is not None and nat.has("layer_norm") and x.dtype in (torch.bfloat16, torch.float32):
@@ -63,7 +76,7 @@ def swiglu(x):
 
 def transition(x, ln_w, ln_b, w1, w2, eps: float = 1e-5):
     nat = _native(x)
-    if nat is not None and nat.has("transition") and nat.transition_supported(x, w1):
+    if nat is not None and bf16_mode(x) and nat.has("transition") and nat.transition_supported(x, w1):
         _CENSUS["transition:sm100"] += 1
         return nat.transition(x, ln_w, ln_b, w1, w2, eps)
     _CENSUS["transition:torch"] += 1
@@ -100,6 +113,25 @@ def window_attention(q, k, v, bias, scale: float):
     return ref.window_attention(q, k, v, bias, scale)
 
 
+def triangle_projection_contract(z0, w_gate, w_proj, mask, outgoing: bool):
+    """Gated a/b projection of the triangle multiply followed by the contraction over the third token.
+
+    ``w_gate``/``w_proj`` hold the a channels on even rows and the b channels on odd rows
+    (reference: ops.py:318-392). Returns ``[B, N, N, C]``.
+    """
+    nat = fused(z0, "gated_dual_linear")
+    if nat is not None and nat.gemm_supported(z0, w_gate):
+        _CENSUS["triangle_projection_contract:sm100"] += 1
+        B, N = z0.shape[0], z0.shape[1]
+        C = w_gate.shape[0] // 2
+        planes = nat.gated_dual_linear(z0, w_gate, w_proj, mask, True, True).view(2, C * B, N, N)
+        a, b = planes[0], planes[1]
+        act = torch.bmm(a, b.transpose(1, 2)) if outgoing else torch.bmm(b.transpose(1, 2), a)
+        return act.view(C, B, N, N).permute(1, 2, 3, 0)
+    ab = gated_dual_linear(z0, w_gate, w_proj, mask)
+    return triangle_contract(ab[..., 0::2], ab[..., 1::2], outgoing)
+
+
 def triangle_contract(a, b, outgoing: bool):
     nat = _native(a)
     if nat is not None and nat.has("triangle_contract") and nat.contract_supported(a):
@@ -111,11 +143,42 @@ def triangle_contract(a, b, outgoing: bool):
 
 def gated_dual_linear(x, w_gate, w_proj, mask=None):
     nat = _native(x)
-    if nat is not None and nat.has("gated_dual_linear") and nat.gemm_supported(x, w_gate):
+    if nat is not None and bf16_mode(x) and nat.has("gated_dual_linear") and nat.gemm_supported(x, w_gate):
         _CENSUS["gated_dual_linear:sm100"] += 1
         return nat.gated_dual_linear(x, w_gate, w_proj, mask)
     _CENSUS["gated_dual_linear:torch"] += 1
     return ref.gated_dual_linear(x, w_gate, w_proj, mask)
+
+
+def sigmoid_gate_mul(x, w, other):
+    """``sigmoid(x w^T) * other`` (the output gates of the triangle and attention blocks)."""
+    nat = fused(x, "sigmoid_gate_mul")
+    if nat is not None and nat.gemm_supported(x, w) and other.shape[-1] == w.shape[0]:
+        _CENSUS["sigmoid_gate_mul:sm100"] += 1
+        return nat.sigmoid_gate_mul(x, w, other)
+    _CENSUS["sigmoid_gate_mul:torch"] += 1
+    return torch.sigmoid(torch.nn.functional.linear(x, w)) * other
+
+
+def head_bias_planes(x, w):
+    """Per-head additive attention bias ``[B, H, N, N]`` from the pair rows ``x [B, N, N, C]``, ``w [H, C]``."""
+    nat = fused(x, "linear_planes")
+    if nat is not None and nat.gemm_supported(x, w):
+        _CENSUS["head_bias_planes:sm100"] += 1
+        B, N = x.shape[0], x.shape[1]
+        return nat.linear_planes(x, w).view(w.shape[0], B, N, N).transpose(0, 1)
+    _CENSUS["head_bias_planes:torch"] += 1
+    return torch.nn.functional.linear(x, w).permute(0, 3, 1, 2)
+
+
+def stacked_linear(x, *ws):
+    """``[x w_0^T, x w_1^T, ...]`` concatenated on the last axis, as one GEMM."""
+    nat = fused(x, "gemm")
+    if nat is not None:
+        _CENSUS["stacked_linear:sm100"] += 1
+        return nat.stacked_linear(x, *ws)
+    _CENSUS["stacked_linear:torch"] += 1
+    return torch.cat([torch.nn.functional.linear(x, w) for w in ws], -1)
 
 
 def linear(x, w, b=None):

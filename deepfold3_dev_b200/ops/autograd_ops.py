@@ -125,3 +125,265 @@ def dropout_add(residual, x, p: float, share_dim: int, seed: int | None = None):
 
 def adamw_ema_flat(p, g, m, v, ema, decay, scale, lr, b1, b2, eps, bc1, bc2, ema_w):
     K.adamw_ema(p, g, m, v, ema, decay, scale, lr, b1, b2, eps, bc1, bc2, ema_w)
+
+
+# ------------------------------------------------------------------------------------------------
+# tcgen05 GEMM family. Forward runs the fused-epilogue kernel; backward recomputes the pre-activation
+# with a library GEMM (nothing of size [rows, 2 * hidden] is kept between forward and backward).
+BF16 = torch.bfloat16
+_W16: dict = {}
+
+
+def bf16_weight(*ws):
+    """bf16 copy of one weight, or of several stacked along the rows; cached until a weight changes in place."""
+    capturing = ws[0].is_cuda and torch.cuda.is_current_stream_capturing()
+    key = tuple(id(w) for w in ws)
+    sig = tuple((w._version, w.data_ptr()) for w in ws)
+    hit = None if capturing else _W16.get(key)
+    if hit is not None and hit[0] == sig:
+        return hit[1]
+    with torch.no_grad():
+        t = ws[0].detach().to(BF16) if len(ws) == 1 else torch.cat([w.detach().to(BF16) for w in ws], 0)
+        t = t.contiguous()
+    if not capturing:  # a cast made inside a CUDA-graph capture belongs to that graph's pool
+        _W16[key] = (sig, t)
+    return t
+
+
+def _bf16c(x):
+    return x.to(BF16).contiguous()
+
+
+def _wgrad(dy2d, x2d, like):
+    """``dy2d.T @ x2d`` accumulated in fp32, in the dtype of the parameter ``like``."""
+    return torch.mm(dy2d.t(), x2d).to(like.dtype)
+
+
+def gemm_supported(x, w) -> bool:
+    return x.is_cuda and x.shape[-1] % 8 == 0 and x.shape[-1] >= 16 and x.numel() > 0
+
+
+def _stacked_gate_proj(w_gate, w_proj, deinterleave: bool):
+    """``[w_gate; w_proj]`` in bf16; with ``deinterleave`` each half lists its even rows first, then its odd rows."""
+    if not deinterleave:
+        return bf16_weight(w_gate, w_proj)
+    capturing = w_gate.is_cuda and torch.cuda.is_current_stream_capturing()
+    key = ("deint", id(w_gate), id(w_proj))
+    sig = tuple((w._version, w.data_ptr()) for w in (w_gate, w_proj))
+    hit = None if capturing else _W16.get(key)
+    if hit is not None and hit[0] == sig:
+        return hit[1]
+    with torch.no_grad():
+        parts = [w.detach()[i::2] for w in (w_gate, w_proj) for i in (0, 1)]
+        t = torch.cat(parts, 0).to(BF16).contiguous()
+    if not capturing:
+        _W16[key] = (sig, t)
+    return t
+
+
+def _reinterleave(dw_half):
+    n = dw_half.shape[0] // 2
+    return torch.stack([dw_half[:n], dw_half[n:]], 1).reshape(dw_half.shape)
+
+
+class _GatedDual(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w_gate, w_proj, mask, planes, deinterleave):
+        x16 = _bf16c(x)
+        W = _stacked_gate_proj(w_gate, w_proj, deinterleave)
+        m = None if mask is None else mask.reshape(-1).float()
+        ctx.save_for_backward(x16, w_gate, w_proj, m)
+        ctx.x_dtype, ctx.planes, ctx.deinterleave = x.dtype, planes, deinterleave
+        return K.gemm(x16, W, None, m, None, 1, planes)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x16, w_gate, w_proj, m = ctx.saved_tensors
+        W = _stacked_gate_proj(w_gate, w_proj, ctx.deinterleave)
+        n = w_gate.shape[0]
+        x2 = x16.reshape(-1, x16.shape[-1])
+        dy2 = (dy.t() if ctx.planes else dy.reshape(-1, n)).to(BF16).contiguous()
+        gp = torch.mm(x2, W.t())
+        dgp = K.gated_bwd(dy2, gp, m)
+        dx = torch.mm(dgp, W).view(x16.shape).to(ctx.x_dtype)
+        dW = _wgrad(dgp, x2, w_gate)
+        dg, dp = dW[:n], dW[n:]
+        if ctx.deinterleave:
+            dg, dp = _reinterleave(dg), _reinterleave(dp)
+        return dx, dg, dp, None, None, None
+
+
+def gated_dual_linear(x, w_gate, w_proj, mask=None, planes: bool = False, deinterleave: bool = False):
+    """``sigmoid(x w_gate^T) * (x w_proj^T) * mask``.
+
+    ``planes=True`` returns ``[channels, rows]``; ``deinterleave=True`` orders the output channels
+    even-first (0, 2, 4, ..., 1, 3, 5, ...), which puts the two operands of the triangle contraction
+    into two contiguous halves.
+    """
+    return _GatedDual.apply(x, w_gate, w_proj, mask, planes, deinterleave)
+
+
+class _StackedLinear(torch.autograd.Function):
+    """``x [w_0; w_1; ...]^T`` as one GEMM on the cached stacked bf16 weight."""
+
+    @staticmethod
+    def forward(ctx, x, *ws):
+        x16 = _bf16c(x)
+        ctx.save_for_backward(x16, *ws)
+        ctx.x_dtype = x.dtype
+        return torch.matmul(x16, bf16_weight(*ws).t())
+
+    @staticmethod
+    def backward(ctx, dy):
+        x16, *ws = ctx.saved_tensors
+        W = bf16_weight(*ws)
+        x2 = x16.reshape(-1, x16.shape[-1])
+        d = dy.reshape(-1, W.shape[0]).to(BF16)
+        dx = torch.mm(d, W).view(x16.shape).to(ctx.x_dtype)
+        dW = torch.mm(d.t(), x2)
+        outs, r = [], 0
+        for w in ws:
+            outs.append(dW[r : r + w.shape[0]].to(w.dtype))
+            r += w.shape[0]
+        return (dx, *outs)
+
+
+def stacked_linear(x, *ws):
+    return _StackedLinear.apply(x, *ws)
+
+
+class _LinearPlanes(torch.autograd.Function):
+    """``(x w^T)`` stored channel-major ``[n, rows]`` (one plane per output channel)."""
+
+    @staticmethod
+    def forward(ctx, x, w):
+        x16 = _bf16c(x)
+        ctx.save_for_backward(x16, w)
+        ctx.x_dtype = x.dtype
+        return K.gemm(x16, bf16_weight(w), None, None, None, 0, True)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x16, w = ctx.saved_tensors
+        x2 = x16.reshape(-1, x16.shape[-1])
+        d = dy.to(BF16)
+        dx = torch.mm(d.t(), bf16_weight(w)).view(x16.shape).to(ctx.x_dtype)
+        return dx, torch.mm(d, x2).to(w.dtype)
+
+
+def linear_planes(x, w):
+    return _LinearPlanes.apply(x, w)
+
+
+class _SigmoidGateMul(torch.autograd.Function):
+    """``sigmoid(x w^T) * other``."""
+
+    @staticmethod
+    def forward(ctx, x, w, other):
+        x16, o16 = _bf16c(x), _bf16c(other)
+        ctx.save_for_backward(x16, w, o16)
+        ctx.dtypes = (x.dtype, other.dtype)
+        return K.gemm(x16, bf16_weight(w), None, None, o16, 3, False)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x16, w, o16 = ctx.saved_tensors
+        W = bf16_weight(w)
+        x2 = x16.reshape(-1, x16.shape[-1])
+        n = w.shape[0]
+        sg = torch.sigmoid(torch.mm(x2, W.t()))
+        d = dy.reshape(-1, n).to(BF16)
+        d_other = (d * sg).view(o16.shape).to(ctx.dtypes[1])
+        dg = d * o16.reshape(-1, n) * sg * (1 - sg)
+        dx = torch.mm(dg, W).view(x16.shape).to(ctx.dtypes[0])
+        return dx, _wgrad(dg, x2, w), d_other
+
+
+def sigmoid_gate_mul(x, w, other):
+    return _SigmoidGateMul.apply(x, w, other)
+
+
+class _Transition(torch.autograd.Function):
+    """``swiglu(LN(x) w1^T) w2^T``: LN kernel, GEMM with the SwiGLU epilogue, output GEMM."""
+
+    @staticmethod
+    def forward(ctx, x, ln_w, ln_b, w1, w2, eps):
+        xc = x.contiguous()
+        h, mean, rstd = K.layer_norm_fwd(xc, _f32(ln_w), _f32(ln_b), eps)
+        h16 = h if h.dtype == BF16 else h.to(BF16)
+        u = K.gemm(h16, bf16_weight(w1), None, None, None, 2, False)
+        y = torch.matmul(u, bf16_weight(w2).t())
+        ctx.save_for_backward(xc, ln_w, ln_b, w1, w2, mean, rstd, h16)
+        return y.to(x.dtype) if x.dtype != BF16 else y
+
+    @staticmethod
+    def backward(ctx, dy):
+        xc, ln_w, ln_b, w1, w2, mean, rstd, h16 = ctx.saved_tensors
+        W1, W2 = bf16_weight(w1), bf16_weight(w2)
+        c = xc.shape[-1]
+        h2 = h16.reshape(-1, c)
+        d = dy.reshape(-1, c).to(BF16).contiguous()
+        pre = torch.mm(h2, W1.t())
+        u = K.swiglu_fwd(pre)
+        dW2 = _wgrad(d, u, w2)
+        dpre = K.swiglu_bwd(torch.mm(d, W2), pre)
+        dW1 = _wgrad(dpre, h2, w1)
+        dh = torch.mm(dpre, W1).view(xc.shape)
+        if xc.dtype != BF16:
+            dh = dh.to(xc.dtype)
+        need_wb = ln_w is not None and (ctx.needs_input_grad[1] or ctx.needs_input_grad[2])
+        dx, partial = K.layer_norm_bwd(dh.contiguous(), xc, _f32(ln_w), mean, rstd, need_wb)
+        dlw = dlb = None
+        if need_wb:
+            sums = partial.sum(0)
+            dlw = sums[0].to(ln_w.dtype)
+            dlb = sums[1].to(ln_b.dtype) if ln_b is not None else None
+        return dx, dlw, dlb, dW1, dW2, None
+
+
+def transition_supported(x, w1) -> bool:
+    return gemm_supported(x, w1) and x.dtype in (BF16, torch.float32) and w1.shape[0] % 2 == 0 and x.shape[-1] <= 1024
+
+
+def transition(x, ln_w, ln_b, w1, w2, eps: float = 1e-5):
+    return _Transition.apply(x, ln_w, ln_b, w1, w2, eps)
+
+
+# ------------------------------------------------------------------------------------------------
+# Pair-bias attention: tcgen05 forward kernel; backward in row chunks sized to stay in L2, with the
+# softmax/bias-gradient algebra in one kernel per chunk and the five small products on the library GEMM.
+ATTN_BWD_CHUNK_BYTES = 40 * 1024 * 1024
+
+
+def attention_supported(q, k, v, bias) -> bool:
+    d = q.shape[-1]
+    return q.is_cuda and q.dim() == 5 and q.dtype == BF16 and k.dtype == BF16 and v.dtype == BF16 and d % 8 == 0 and d <= 64
+
+
+class _Attention(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, bias, key_mask, scale):
+        need = any(ctx.needs_input_grad[:4])
+        out, lse = K.attention_fwd(q, k, v, bias, key_mask, scale, need)
+        ctx.save_for_backward(q, k, v, bias, key_mask, out, lse)
+        ctx.scale = scale
+        return out
+
+    @staticmethod
+    def backward(ctx, d_out):
+        q, k, v, bias, key_mask, out, lse = ctx.saved_tensors
+        want_bias = bias is not None and ctx.needs_input_grad[3]
+        dq, dk, dv, dbias = K.attention_bwd(q, k, v, out, d_out, bias, key_mask, lse, ctx.scale, want_bias,
+                                            ATTN_BWD_CHUNK_BYTES)  # fmt: skip
+        return dq, dk, dv, (dbias.to(bias.dtype) if want_bias else None), None, None
+
+
+def pair_bias_attention(q, k, v, bias, key_mask, scale: float):
+    return _Attention.apply(q, k, v, bias, key_mask, float(scale))
+
+
+def check_status() -> None:
+    """Raise if a kernel's bounded wait ran out since the last check (synchronises the device)."""
+    code = K.gemm_status()
+    if code != 0:
+        raise RuntimeError(f"deepfold3_dev_b200: a kernel wait timed out (status {code}); results of this step are invalid")

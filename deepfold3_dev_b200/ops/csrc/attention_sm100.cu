@@ -1,0 +1,593 @@
+// Pair-biased softmax attention, forward, for sm_100a:
+//
+//   out[b, r, h, i, :] = softmax_j( scale * q[b,r,h,i,:] . k[b,r,h,j,:] + bias[b,h,i,j] + 1e9 * (mask[b,r,j] - 1) ) v[b,r,h,j,:]
+//
+// q/k/v are strided 5-D views [B, R, H, N, D] (last axis contiguous), so the row and the column
+// flavour of triangle attention, the single-representation attention and the diffusion transformer
+// (R = samples) all read the projection outputs in place. The bias is shared by the R rows.
+//
+// One CTA owns 128 queries of one (b, r, h) and streams the keys in blocks of 128:
+//   warp 0      TMA producer: Q once, then K/V blocks into a two-stage ring (5-D tensor maps, 128-byte swizzle)
+//   warp 1      tcgen05.mma issuer: S = Q K^T into tensor memory, later O_blk = P V
+//   warps 2-5   one query row per thread: S from tensor memory, bias + mask, online softmax in base 2,
+//               P (bf16) into swizzled shared memory as the A operand of the second MMA, O accumulated in registers
+// Every wait is bounded; a wait that runs out records a df3::Status code and the CTA leaves cleanly.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/library.h>
+#include <torch/torch.h>
+
+#include "sm100_ptx.cuh"
+
+using torch::Tensor;
+
+namespace df3 {
+Tensor status_word(int device);                       // gemm_sm100.cu
+CUtensorMap make_map_nd(const void* base, int rank, const int64_t* dims, const int64_t* strides_elems,
+                        const int* box);              // gemm_sm100.cu
+
+namespace {
+
+constexpr int BQ = 128;   // queries per CTA
+constexpr int BKEY = 128; // keys per block
+constexpr int kTileBytes = 128 * 128;  // 128 rows x 128 bytes (64 bf16): Q, K or V tile
+constexpr int kThreads = 192;
+constexpr float kLog2e = 1.4426950408889634f;
+
+struct AttnParams {
+  __nv_bfloat16* out;
+  float* lse;              // [2, B, R, H, N] or null: row maximum and log2 of the row sum, both in base 2
+  const void* bias;        // [B, H, N, N] or null
+  const float* mask;       // [B, R, N] or null (1 keep, 0 drop)
+  int* status;
+  long long o_sb, o_sr, o_sh, o_sn;           // out strides (elements)
+  long long bias_sb, bias_sh, bias_si;        // bias strides (last axis contiguous)
+  long long mask_sb, mask_sr;                 // mask strides (last axis contiguous)
+  int B, R, H, N, D;
+  int q_tiles;
+  int bias_is_bf16;
+  float scale_log2;        // scale * log2(e)
+};
+
+// K-major operand in 128-byte swizzled rows (see sm100_ptx.cuh); MN-major variant for V: the 64 values of
+// one key are contiguous (the N axis of the MMA), keys advance 128 bytes, 8-key groups are 1024 bytes apart.
+__device__ __forceinline__ uint64_t smem_desc_mn_sw128(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
+  d |= (uint64_t)1 << 16;              // leading byte offset: stride between 64-wide N blocks, unused (N <= 64)
+  d |= (uint64_t)(1024 >> 4) << 32;    // stride byte offset: between 8-key groups
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+
+__device__ __forceinline__ void tma_load_5d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2,
+                                            int c3, int c4) {
+  asm volatile(
+      "cp.async.bulk.tensor.5d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+      ::"r"(ptx::smem_u32(smem_dst)), "l"((uint64_t)map), "r"(ptx::smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
+      : "memory");
+}
+
+__device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const float* v) {
+  const uint32_t* r = reinterpret_cast<const uint32_t*>(v);
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
+        "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
+        "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// instruction descriptor of the second MMA: A (P) K-major, B (V) MN-major
+__host__ __device__ constexpr uint32_t idesc_pv(int m, int n) { return ptx::idesc_bf16_f32(m, n) | (1u << 16); }
+
+template <int DN>  // head width rounded up to 16: 16, 32, 48 or 64
+__global__ void __launch_bounds__(kThreads) attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ,
+                                                                const __grid_constant__ CUtensorMap tmK,
+                                                                const __grid_constant__ CUtensorMap tmV, AttnParams p) {
+  extern __shared__ __align__(1024) uint8_t smem[];
+  uint8_t* q_s = smem;
+  uint8_t* kv_s = smem + kTileBytes;                 // stage s: K at 2 s, V at 2 s + 1 tiles
+  uint8_t* p_s = smem + 5 * kTileBytes;              // 128 x 128 bf16: two 64-key atoms of 16 KiB
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 7 * kTileBytes);
+  uint64_t* q_full = bars;
+  uint64_t* kv_full = bars + 1;   // [2]
+  uint64_t* kv_empty = bars + 3;  // [2]
+  uint64_t* s_ready = bars + 5;
+  uint64_t* p_ready = bars + 6;
+  uint64_t* o_ready = bars + 7;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+  // one copy for the four softmax warps: each warp writes all 128 (identical) values itself before it reads them,
+  // and no warp starts the next key block before every warp has finished reading this one (o_ready follows p_ready)
+  float* key_add = reinterpret_cast<float*>(bars + 10);  // [128]
+  constexpr uint32_t kTmemCols = 256;  // S: columns [0, 128), O block: [128, 128 + DN)
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  int idx = blockIdx.x;
+  const int qt = idx % p.q_tiles; idx /= p.q_tiles;
+  const int h = idx % p.H; idx /= p.H;
+  const int r = idx % p.R;
+  const int b = idx / p.R;
+  const int nb = (p.N + BKEY - 1) / BKEY;
+
+  if ((ptx::smem_u32(smem) & 1023u) != 0) {  // the swizzle pattern assumes 1024-byte aligned tiles
+    if (threadIdx.x == 0) atomicCAS(p.status, kOk, kBadShape);
+    return;
+  }
+  if (threadIdx.x == 0) {
+    ptx::mbar_init(q_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      ptx::mbar_init(&kv_full[s], 1);
+      ptx::mbar_init(&kv_empty[s], 1);
+    }
+    ptx::mbar_init(s_ready, 1);
+    ptx::mbar_init(p_ready, 128);
+    ptx::mbar_init(o_ready, 1);
+    ptx::fence_barrier_init();
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(tmem_slot, kTmemCols);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  const uint32_t tmem_s = tmem, tmem_o = tmem + 128;
+
+  if (warp == 0) {
+    if (ptx::elect_one()) {
+      ptx::prefetch_tensormap(&tmQ);
+      ptx::prefetch_tensormap(&tmK);
+      ptx::prefetch_tensormap(&tmV);
+      ptx::mbar_expect_tx(q_full, kTileBytes);
+      tma_load_5d(q_s, &tmQ, q_full, 0, qt * BQ, h, r, b);
+      int issued = 0;
+      bool ok = true;
+      for (int j = 0; j < nb; ++j) {
+        const int s = j & 1;
+        if (!ptx::mbar_wait(&kv_empty[s], (uint32_t)((j >> 1) & 1) ^ 1u, p.status, kTimeoutStageEmpty)) { ok = false; break; }
+        ptx::mbar_expect_tx(&kv_full[s], 2 * kTileBytes);
+        tma_load_5d(kv_s + (2 * s) * kTileBytes, &tmK, &kv_full[s], 0, j * BKEY, h, r, b);
+        tma_load_5d(kv_s + (2 * s + 1) * kTileBytes, &tmV, &kv_full[s], 0, j * BKEY, h, r, b);
+        issued = j + 1;
+      }
+      if (!ok) {  // let copies in flight land before shared memory is released
+        for (int i = 0; i < (1 << 20) && !ptx::mbar_try_wait(q_full, 0); ++i) {}
+        for (int j = issued > 2 ? issued - 2 : 0; j < issued; ++j)
+          for (int i = 0; i < (1 << 20) && !ptx::mbar_try_wait(&kv_full[j & 1], (uint32_t)(j >> 1) & 1u); ++i) {}
+      }
+    }
+  } else if (warp == 1) {
+    if (ptx::elect_one()) {
+      constexpr uint32_t idesc_s = ptx::idesc_bf16_f32(BQ, BKEY);
+      constexpr uint32_t idesc_o = idesc_pv(BQ, DN);
+      const uint64_t q_desc = ptx::smem_desc_k_sw128(ptx::smem_u32(q_s));
+      const uint64_t p_desc = ptx::smem_desc_k_sw128(ptx::smem_u32(p_s));
+      auto issue_s = [&](int j) -> bool {
+        const int s = j & 1;
+        if (!ptx::mbar_wait(&kv_full[s], (uint32_t)(j >> 1) & 1u, p.status, kTimeoutTmaFull)) return false;
+        ptx::tc_fence_after();
+        const uint64_t k_desc = ptx::smem_desc_k_sw128(ptx::smem_u32(kv_s + (2 * s) * kTileBytes));
+#pragma unroll
+        for (int kk = 0; kk < DN / 16; ++kk) ptx::umma_bf16(tmem_s, q_desc + 2 * kk, k_desc + 2 * kk, idesc_s, kk != 0);
+        ptx::umma_commit(s_ready);
+        return true;
+      };
+      bool ok = ptx::mbar_wait(q_full, 0, p.status, kTimeoutTmaFull);
+      if (ok) ok = issue_s(0);
+      for (int j = 0; ok && j < nb; ++j) {
+        const int s = j & 1;
+        if (!ptx::mbar_wait(p_ready, (uint32_t)j & 1u, p.status, kTimeoutMmaDone)) break;
+        ptx::tc_fence_after();
+        const uint64_t v_desc = smem_desc_mn_sw128(ptx::smem_u32(kv_s + (2 * s + 1) * kTileBytes));
+#pragma unroll
+        for (int kk = 0; kk < BKEY / 16; ++kk) {
+          // P: keys 16 kk .. 16 kk + 15 sit in atom kk / 4 (16 KiB apart) at byte 32 (kk % 4) of each row;
+          // V: 16 keys = 2048 bytes further down the tile
+          const uint64_t pa = p_desc + (uint64_t)((kk >> 2) * (16384 >> 4) + (kk & 3) * 2);
+          ptx::umma_bf16(tmem_o, pa, v_desc + (uint64_t)(kk * (2048 >> 4)), idesc_o, kk != 0);
+        }
+        ptx::umma_commit(o_ready);
+        ptx::umma_commit(&kv_empty[s]);
+        if (j + 1 < nb) ok = issue_s(j + 1);
+      }
+    }
+  } else {
+    const int qd = warp & 3;                 // tensor-memory lane quarter of this warp
+    const int row_in_tile = qd * 32 + lane;
+    const int i = qt * BQ + row_in_tile;     // query index
+    const bool row_ok = i < p.N;
+    const uint32_t lane_off = (uint32_t)(qd * 32) << 16;
+    const float* mask_row = p.mask ? p.mask + b * p.mask_sb + r * p.mask_sr : nullptr;
+    const uint8_t* bias_row = nullptr;
+    if (p.bias && row_ok)
+      bias_row = reinterpret_cast<const uint8_t*>(p.bias) +
+                 (b * p.bias_sb + h * p.bias_sh + (long long)i * p.bias_si) * (p.bias_is_bf16 ? 2 : 4);
+    float m_run = -INFINITY, l_run = 0.f;
+    float o_acc[DN];
+#pragma unroll
+    for (int d = 0; d < DN; ++d) o_acc[d] = 0.f;
+    // this row's 128-byte lines inside each P atom: 8-row groups are 1024 bytes, chunks XOR-swizzled by the row
+    uint8_t* p_row = p_s + (row_in_tile >> 3) * 1024 + (row_in_tile & 7) * 128;
+    const int swz = row_in_tile & 7;
+    bool ok = true;
+    float v[32];
+    for (int j = 0; j < nb && ok; ++j) {
+      if (!ptx::mbar_wait(s_ready, (uint32_t)j & 1u, p.status, kTimeoutMmaDone)) { ok = false; break; }
+      ptx::tc_fence_after();
+      const int key0 = j * BKEY;
+      // additive key term (mask, out-of-range keys) of this block, one copy per warp
+      __syncwarp();
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        const int key = key0 + lane + 32 * t;
+        float add = -INFINITY;
+        if (key < p.N) add = mask_row ? 1e9f * kLog2e * (mask_row[key] - 1.f) : 0.f;
+        key_add[lane + 32 * t] = add;
+      }
+      __syncwarp();
+      // pass 1: logits in base 2 with bias and mask, row maximum; logits parked back in tensor memory
+      float m_new = m_run;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        ptx::tmem_ld_32x32(tmem_s + lane_off + c * 32, v);
+        ptx::tmem_ld_wait();
+        const int kbase = key0 + c * 32;
+        if (bias_row == nullptr) {
+#pragma unroll
+          for (int t = 0; t < 32; ++t) v[t] = v[t] * p.scale_log2;
+        } else if (p.bias_is_bf16 && kbase + 32 <= p.N && ((reinterpret_cast<uintptr_t>(bias_row) + 2 * kbase) & 15) == 0) {
+          const uint4* src = reinterpret_cast<const uint4*>(bias_row + 2 * kbase);
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            const uint4 w = src[g];
+            const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const __nv_bfloat162 pr = *reinterpret_cast<const __nv_bfloat162*>(&ww[e]);
+              v[g * 8 + 2 * e] = v[g * 8 + 2 * e] * p.scale_log2 + __low2float(pr) * kLog2e;
+              v[g * 8 + 2 * e + 1] = v[g * 8 + 2 * e + 1] * p.scale_log2 + __high2float(pr) * kLog2e;
+            }
+          }
+        } else {
+#pragma unroll
+          for (int t = 0; t < 32; ++t) {
+            const int key = kbase + t;
+            float add = 0.f;
+            if (key < p.N)
+              add = p.bias_is_bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(bias_row)[key])
+                                   : reinterpret_cast<const float*>(bias_row)[key];
+            v[t] = v[t] * p.scale_log2 + add * kLog2e;
+          }
+        }
+#pragma unroll
+        for (int t = 0; t < 32; ++t) {
+          v[t] += key_add[c * 32 + t];
+          m_new = fmaxf(m_new, v[t]);
+        }
+        tmem_st_32x32(tmem_s + lane_off + c * 32, v);
+      }
+      tmem_st_wait();
+      const float alpha = exp2f(m_run - m_new);  // 0 on the first block
+      float l_blk = 0.f;
+      // pass 2: probabilities, row sum, P as bf16 into the swizzled A-operand tile
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        ptx::tmem_ld_32x32(tmem_s + lane_off + c * 32, v);
+        ptx::tmem_ld_wait();
+#pragma unroll
+        for (int t = 0; t < 32; ++t) {
+          v[t] = exp2f(v[t] - m_new);
+          l_blk += v[t];
+        }
+        uint8_t* atom = p_row + (c >> 1) * 16384;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          const int chunk = (c & 1) * 4 + g;  // 16-byte chunk inside the 128-byte line
+          uint4 w;
+          w.x = pack2(v[g * 8 + 0], v[g * 8 + 1]);
+          w.y = pack2(v[g * 8 + 2], v[g * 8 + 3]);
+          w.z = pack2(v[g * 8 + 4], v[g * 8 + 5]);
+          w.w = pack2(v[g * 8 + 6], v[g * 8 + 7]);
+          *reinterpret_cast<uint4*>(atom + ((chunk ^ swz) << 4)) = w;
+        }
+      }
+      l_run = l_run * alpha + l_blk;
+      m_run = m_new;
+      ptx::fence_proxy_async();   // P written through the generic proxy, read by the tensor core
+      ptx::tc_fence_before();     // and our tensor-memory reads of S are done
+      ptx::mbar_arrive(p_ready);
+      if (!ptx::mbar_wait(o_ready, (uint32_t)j & 1u, p.status, kTimeoutMmaDone)) { ok = false; break; }
+      ptx::tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < DN / 16; ++c) {
+        // 16 columns at a time keeps the register count independent of DN
+        float t16[16];
+        uint32_t* rr = reinterpret_cast<uint32_t*>(t16);
+        asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+            : "=r"(rr[0]), "=r"(rr[1]), "=r"(rr[2]), "=r"(rr[3]), "=r"(rr[4]), "=r"(rr[5]), "=r"(rr[6]), "=r"(rr[7]),
+              "=r"(rr[8]), "=r"(rr[9]), "=r"(rr[10]), "=r"(rr[11]), "=r"(rr[12]), "=r"(rr[13]), "=r"(rr[14]), "=r"(rr[15])
+            : "r"(tmem_o + lane_off + c * 16));
+        ptx::tmem_ld_wait();
+#pragma unroll
+        for (int t = 0; t < 16; ++t) o_acc[c * 16 + t] = o_acc[c * 16 + t] * alpha + t16[t];
+      }
+    }
+    if (ok && row_ok) {
+      const float inv = 1.f / l_run;
+      __nv_bfloat16* dst = p.out + b * p.o_sb + r * p.o_sr + h * p.o_sh + (long long)i * p.o_sn;
+      if ((p.D & 7) == 0 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+#pragma unroll
+        for (int g = 0; g < DN / 8; ++g) {
+          if (g * 8 < p.D) {
+            uint4 w;
+            w.x = pack2(o_acc[g * 8 + 0] * inv, o_acc[g * 8 + 1] * inv);
+            w.y = pack2(o_acc[g * 8 + 2] * inv, o_acc[g * 8 + 3] * inv);
+            w.z = pack2(o_acc[g * 8 + 4] * inv, o_acc[g * 8 + 5] * inv);
+            w.w = pack2(o_acc[g * 8 + 6] * inv, o_acc[g * 8 + 7] * inv);
+            reinterpret_cast<uint4*>(dst)[g] = w;
+          }
+        }
+      } else {
+#pragma unroll
+        for (int d = 0; d < DN; ++d)
+          if (d < p.D) dst[d] = __float2bfloat16_rn(o_acc[d] * inv);
+      }
+      if (p.lse) {
+        // kept apart: for a fully masked row the maximum is about -1.4e9, where adding log2(sum) would round away
+        const long long at = (((long long)b * p.R + r) * p.H + h) * p.N + i;
+        p.lse[at] = m_run;
+        p.lse[(long long)p.B * p.R * p.H * p.N + at] = log2f(l_run);
+      }
+    }
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem, kTmemCols);
+  }
+}
+
+// Backward helper over one chunk of rows: turns raw q.k and dO.v products into P and dS in place and
+// accumulates the bias gradient. One thread per (h, i, j), looping over the rows of the chunk, so the
+// sum over rows needs no atomics.
+//   s_io  [Rc, H, N, N] bf16: in q.k (unscaled)          out P = exp2(log2e (scale q.k + bias + mask) - row_max - row_log2sum)
+//   dp_io [Rc, H, N, N] bf16: in dO.v                    out dS * scale, dS = P (dP - delta)
+//   dbias [H, N, N] fp32 += sum_r dS
+template <typename BiasT>
+__global__ void attention_bwd_elem_kernel(__nv_bfloat16* __restrict__ s_io, __nv_bfloat16* __restrict__ dp_io,
+                                          const BiasT* __restrict__ bias, long long bias_sh, long long bias_si,
+                                          const float* __restrict__ mask, long long mask_sr,
+                                          const float* __restrict__ row_max, const float* __restrict__ row_log2sum,
+                                          const float* __restrict__ delta,
+                                          float* __restrict__ dbias, int Rc, int H, int N, float scale) {
+  const long long per_row = (long long)H * N * N;
+  const long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= per_row) return;
+  const int j = (int)(e % N);
+  const int i = (int)((e / N) % N);
+  const int h = (int)(e / ((long long)N * N));
+  const float bv = (bias ? to_float<BiasT>(bias[h * bias_sh + (long long)i * bias_si + j]) : 0.f) * kLog2e;
+  const float scale_log2 = scale * kLog2e;
+  float acc = 0.f;
+  for (int r = 0; r < Rc; ++r) {
+    const long long off = r * per_row + e;
+    const long long row = ((long long)r * H + h) * N + i;
+    // the same base-2 logit as the forward kernel forms, so masked and unmasked keys line up with its row maximum
+    const float madd = mask ? 1e9f * kLog2e * (mask[r * mask_sr + j] - 1.f) : 0.f;
+    const float x2 = (__bfloat162float(s_io[off]) * scale_log2 + bv) + madd;
+    const float pr = exp2f((x2 - row_max[row]) - row_log2sum[row]);
+    const float ds = pr * (__bfloat162float(dp_io[off]) - delta[row]);
+    acc += ds;
+    s_io[off] = __float2bfloat16_rn(pr);
+    dp_io[off] = __float2bfloat16_rn(ds * scale);
+  }
+  if (dbias) dbias[e] += acc;
+}
+
+void df3_attention_bwd_elem(Tensor s_io, Tensor dp_io, const c10::optional<Tensor>& bias, const c10::optional<Tensor>& mask,
+                            const Tensor& row_max, const Tensor& row_log2sum, const Tensor& delta,
+                            const c10::optional<Tensor>& dbias, double scale) {
+  TORCH_CHECK(s_io.dim() == 4 && s_io.is_contiguous() && dp_io.is_contiguous() && s_io.sizes() == dp_io.sizes() &&
+              s_io.scalar_type() == torch::kBFloat16 && dp_io.scalar_type() == torch::kBFloat16, "attention_bwd_elem: [Rc, H, N, N] bf16");
+  const int Rc = (int)s_io.size(0), H = (int)s_io.size(1), N = (int)s_io.size(2);
+  for (const Tensor* t : {&row_max, &row_log2sum, &delta})
+    TORCH_CHECK(t->is_contiguous() && t->numel() == (int64_t)Rc * H * N && t->scalar_type() == torch::kFloat32,
+                "attention_bwd_elem: row_max / row_log2sum / delta [Rc, H, N] fp32");
+  c10::cuda::CUDAGuard guard(s_io.device());
+  const float* mp = nullptr;
+  long long mask_sr = 0;
+  Tensor m;
+  if (mask.has_value() && mask->defined()) {
+    m = mask->to(torch::kFloat32);
+    TORCH_CHECK(m.dim() == 2 && m.size(1) == N && (m.size(0) == Rc || m.size(0) == 1), "attention_bwd_elem: mask [Rc or 1, N]");
+    if (m.stride(1) != 1) m = m.contiguous();
+    mp = m.data_ptr<float>();
+    mask_sr = m.size(0) == 1 ? 0 : m.stride(0);
+  }
+  float* dbp = nullptr;
+  if (dbias.has_value() && dbias->defined()) {
+    TORCH_CHECK(dbias->is_contiguous() && dbias->scalar_type() == torch::kFloat32 && dbias->numel() == (int64_t)H * N * N, "attention_bwd_elem: dbias [H, N, N] fp32");
+    dbp = dbias->data_ptr<float>();
+  }
+  const long long per_row = (long long)H * N * N;
+  const unsigned grid = (unsigned)((per_row + 255) / 256);
+  cudaStream_t stream = at::cuda::getCurrentCUDAStream();
+  auto* sp = reinterpret_cast<__nv_bfloat16*>(s_io.data_ptr());
+  auto* dp = reinterpret_cast<__nv_bfloat16*>(dp_io.data_ptr());
+  if (bias.has_value() && bias->defined()) {
+    Tensor b = *bias;
+    TORCH_CHECK(b.dim() == 3 && b.size(0) == H && b.size(1) == N && b.size(2) == N, "attention_bwd_elem: bias [H, N, N]");
+    if (b.stride(2) != 1 || (b.scalar_type() != torch::kBFloat16 && b.scalar_type() != torch::kFloat32)) b = b.to(torch::kFloat32).contiguous();
+    if (b.scalar_type() == torch::kBFloat16)
+      attention_bwd_elem_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(sp, dp, reinterpret_cast<const __nv_bfloat16*>(b.data_ptr()), b.stride(0), b.stride(1), mp, mask_sr, row_max.data_ptr<float>(), row_log2sum.data_ptr<float>(), delta.data_ptr<float>(), dbp, Rc, H, N, (float)scale);
+    else
+      attention_bwd_elem_kernel<float><<<grid, 256, 0, stream>>>(sp, dp, b.data_ptr<float>(), b.stride(0), b.stride(1), mp, mask_sr, row_max.data_ptr<float>(), row_log2sum.data_ptr<float>(), delta.data_ptr<float>(), dbp, Rc, H, N, (float)scale);
+  } else {
+    attention_bwd_elem_kernel<float><<<grid, 256, 0, stream>>>(sp, dp, nullptr, 0, 0, mp, mask_sr, row_max.data_ptr<float>(), row_log2sum.data_ptr<float>(), delta.data_ptr<float>(), dbp, Rc, H, N, (float)scale);
+  }
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+}
+
+// Whole backward of the attention op: row chunks sized for L2, five library GEMMs and one fused
+// elementwise kernel per chunk. Returns dq, dk, dv as contiguous [B, R, H, N, D] and dbias [Bb, H, N, N] fp32.
+std::tuple<Tensor, Tensor, Tensor, Tensor> df3_attention_bwd(const Tensor& q, const Tensor& k, const Tensor& v,
+                                                             const Tensor& out, const Tensor& d_out,
+                                                             const c10::optional<Tensor>& bias,
+                                                             const c10::optional<Tensor>& mask, const Tensor& lse,
+                                                             double scale, bool want_dbias, int64_t chunk_bytes) {
+  const int64_t B = q.size(0), R = q.size(1), H = q.size(2), N = q.size(3), D = q.size(4);
+  c10::cuda::CUDAGuard guard(q.device());
+  auto bf = q.options();
+  Tensor qc = q.contiguous(), kc = k.contiguous(), vc = v.contiguous();
+  Tensor doc = d_out.to(torch::kBFloat16).contiguous();
+  Tensor delta = (doc.to(torch::kFloat32) * out.to(torch::kFloat32)).sum(-1);  // [B, R, H, N]
+  Tensor dq = torch::empty({B, R, H, N, D}, bf), dk = torch::empty({B, R, H, N, D}, bf), dv = torch::empty({B, R, H, N, D}, bf);
+  const bool has_bias = bias.has_value() && bias->defined();
+  const bool has_mask = mask.has_value() && mask->defined();
+  Tensor dbias;
+  if (want_dbias && has_bias) dbias = torch::zeros({bias->size(0), H, N, N}, bf.dtype(torch::kFloat32));
+  int64_t rc = chunk_bytes / std::max<int64_t>(1, H * N * N * 2);
+  rc = std::max<int64_t>(1, std::min<int64_t>(R, rc));
+  Tensor s = torch::empty({rc, H, N, N}, bf), dp = torch::empty({rc, H, N, N}, bf);
+  for (int64_t b = 0; b < B; ++b) {
+    c10::optional<Tensor> bb, db;
+    if (has_bias) bb = bias->select(0, bias->size(0) > 1 ? b : 0);
+    if (dbias.defined()) db = dbias.select(0, dbias.size(0) > 1 ? b : 0);
+    for (int64_t r0 = 0; r0 < R; r0 += rc) {
+      const int64_t n = std::min(rc, R - r0);
+      Tensor q3 = qc[b].narrow(0, r0, n).reshape({n * H, N, D});
+      Tensor k3 = kc[b].narrow(0, r0, n).reshape({n * H, N, D});
+      Tensor v3 = vc[b].narrow(0, r0, n).reshape({n * H, N, D});
+      Tensor o3 = doc[b].narrow(0, r0, n).reshape({n * H, N, D});
+      Tensor s3 = s.narrow(0, 0, n).view({n * H, N, N});
+      Tensor p3 = dp.narrow(0, 0, n).view({n * H, N, N});
+      at::bmm_out(s3, q3, k3.transpose(1, 2));
+      at::bmm_out(p3, o3, v3.transpose(1, 2));
+      c10::optional<Tensor> mm;
+      if (has_mask) {
+        Tensor mb = mask->select(0, mask->size(0) > 1 ? b : 0);
+        mm = mb.size(0) > 1 ? mb.narrow(0, r0, n) : mb;
+      }
+      df3_attention_bwd_elem(s.narrow(0, 0, n), dp.narrow(0, 0, n), bb, mm, lse[0][b].narrow(0, r0, n).contiguous(),
+                             lse[1][b].narrow(0, r0, n).contiguous(), delta[b].narrow(0, r0, n).contiguous(), db, scale);
+      Tensor dv3 = dv[b].narrow(0, r0, n).view({n * H, N, D});
+      Tensor dq3 = dq[b].narrow(0, r0, n).view({n * H, N, D});
+      Tensor dk3 = dk[b].narrow(0, r0, n).view({n * H, N, D});
+      at::bmm_out(dv3, s3.transpose(1, 2), o3);
+      at::bmm_out(dq3, p3, k3);
+      at::bmm_out(dk3, p3.transpose(1, 2), q3);
+    }
+  }
+  if (!dbias.defined()) dbias = torch::empty({0}, bf.dtype(torch::kFloat32));
+  return {dq, dk, dv, dbias};
+}
+
+CUtensorMap qkv_map(const Tensor& t) {  // [B, R, H, N, D] view -> 5-D map (d, n, h, r, b), box 64 x 128
+  const int64_t dims[5] = {t.size(4), t.size(3), t.size(2), t.size(1), t.size(0)};
+  const int64_t strides[5] = {1, t.stride(3), t.stride(2), t.stride(1), t.stride(0)};
+  const int box[5] = {64, 128, 1, 1, 1};
+  return make_map_nd(t.data_ptr(), 5, dims, strides, box);
+}
+
+bool strides_ok(const Tensor& t) {
+  if (t.stride(4) != 1 || reinterpret_cast<uintptr_t>(t.data_ptr()) % 16 != 0) return false;
+  for (int d = 0; d < 4; ++d)
+    if (t.size(d) > 1 && (t.stride(d) % 8 != 0 || t.stride(d) <= 0)) return false;
+  return true;
+}
+
+std::tuple<Tensor, Tensor> df3_attention_fwd(const Tensor& q_in, const Tensor& k_in, const Tensor& v_in,
+                                             const c10::optional<Tensor>& bias_in, const c10::optional<Tensor>& mask_in,
+                                             double scale, bool want_lse) {
+  TORCH_CHECK(q_in.dim() == 5 && k_in.sizes() == q_in.sizes() && v_in.sizes() == q_in.sizes(), "attention: [B, R, H, N, D] q, k, v");
+  TORCH_CHECK(q_in.is_cuda() && q_in.scalar_type() == torch::kBFloat16 && k_in.scalar_type() == torch::kBFloat16 &&
+              v_in.scalar_type() == torch::kBFloat16, "attention: bf16 CUDA tensors");
+  const int64_t B = q_in.size(0), R = q_in.size(1), H = q_in.size(2), N = q_in.size(3), D = q_in.size(4);
+  TORCH_CHECK(D % 8 == 0 && D <= 64, "attention: head width must be a multiple of 8, at most 64");
+  c10::cuda::CUDAGuard guard(q_in.device());
+  Tensor q = strides_ok(q_in) ? q_in : q_in.contiguous();
+  Tensor k = strides_ok(k_in) ? k_in : k_in.contiguous();
+  Tensor v = strides_ok(v_in) ? v_in : v_in.contiguous();
+  Tensor out = torch::empty_like(q);
+  if (out.stride(4) != 1) out = torch::empty(q.sizes(), q.options());
+  Tensor lse = torch::empty({want_lse ? 2 : 0, B, R, H, N}, q.options().dtype(torch::kFloat32));
+  if (out.numel() == 0) return {out, lse};
+
+  AttnParams p{};
+  p.out = reinterpret_cast<__nv_bfloat16*>(out.data_ptr());
+  p.lse = want_lse ? lse.data_ptr<float>() : nullptr;
+  p.o_sb = out.stride(0); p.o_sr = out.stride(1); p.o_sh = out.stride(2); p.o_sn = out.stride(3);
+  Tensor bias, mask;
+  if (bias_in.has_value() && bias_in->defined()) {
+    bias = *bias_in;
+    TORCH_CHECK(bias.dim() == 4 && bias.size(1) == H && bias.size(2) == N && bias.size(3) == N &&
+                (bias.size(0) == B || bias.size(0) == 1), "attention: bias [B or 1, H, N, N]");
+    if (bias.scalar_type() != torch::kBFloat16 && bias.scalar_type() != torch::kFloat32) bias = bias.to(torch::kFloat32);
+    if (bias.stride(3) != 1) bias = bias.contiguous();
+    p.bias = bias.data_ptr();
+    p.bias_is_bf16 = bias.scalar_type() == torch::kBFloat16;
+    p.bias_sb = bias.size(0) == 1 ? 0 : bias.stride(0);
+    p.bias_sh = bias.stride(1);
+    p.bias_si = bias.stride(2);
+  }
+  if (mask_in.has_value() && mask_in->defined()) {
+    mask = mask_in->to(torch::kFloat32);
+    TORCH_CHECK(mask.dim() == 3 && mask.size(2) == N && (mask.size(0) == B || mask.size(0) == 1) &&
+                (mask.size(1) == R || mask.size(1) == 1), "attention: key mask [B or 1, R or 1, N]");
+    if (mask.stride(2) != 1) mask = mask.contiguous();
+    p.mask = mask.data_ptr<float>();
+    p.mask_sb = mask.size(0) == 1 ? 0 : mask.stride(0);
+    p.mask_sr = mask.size(1) == 1 ? 0 : mask.stride(1);
+  }
+  Tensor status = status_word(q.device().index());
+  p.status = status.data_ptr<int>();
+  p.B = (int)B; p.R = (int)R; p.H = (int)H; p.N = (int)N; p.D = (int)D;
+  p.q_tiles = (int)((N + BQ - 1) / BQ);
+  p.scale_log2 = (float)scale * kLog2e;
+  const CUtensorMap tq = qkv_map(q), tk = qkv_map(k), tv = qkv_map(v);
+  const long long ctas = (long long)B * R * H * p.q_tiles;
+  TORCH_CHECK(ctas < (1ll << 31), "attention: grid too large");
+  const size_t smem = 7 * kTileBytes + 128 + 512;
+  cudaStream_t stream = at::cuda::getCurrentCUDAStream();
+  const int dn = (int)((D + 15) / 16 * 16);
+#define DF3_ATTN(DN_)                                                                                               \
+  do {                                                                                                              \
+    static bool attr = false;                                                                                       \
+    if (!attr) {                                                                                                    \
+      C10_CUDA_CHECK(cudaFuncSetAttribute(attention_fwd_kernel<DN_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+      attr = true;                                                                                                  \
+    }                                                                                                               \
+    attention_fwd_kernel<DN_><<<(unsigned)ctas, kThreads, smem, stream>>>(tq, tk, tv, p);                           \
+  } while (0)
+  if (dn == 16) DF3_ATTN(16); else if (dn == 32) DF3_ATTN(32); else if (dn == 48) DF3_ATTN(48); else DF3_ATTN(64);
+#undef DF3_ATTN
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  return {out, lse};
+}
+
+}  // namespace
+}  // namespace df3
+
+void df3_register_attention(torch::Library& m) {
+  m.def("attention_fwd(Tensor q, Tensor k, Tensor v, Tensor? bias, Tensor? key_mask, float scale, bool want_lse) -> (Tensor, Tensor)",
+        &df3::df3_attention_fwd);
+  m.def("attention_bwd(Tensor q, Tensor k, Tensor v, Tensor out, Tensor d_out, Tensor? bias, Tensor? key_mask, Tensor lse, "
+        "float scale, bool want_dbias, int chunk_bytes) -> (Tensor, Tensor, Tensor, Tensor)",
+        &df3::df3_attention_bwd);
+  m.def("attention_bwd_elem(Tensor(a!) s_io, Tensor(b!) dp_io, Tensor? bias, Tensor? mask, Tensor row_max, Tensor row_log2sum, Tensor delta, Tensor(c!)? dbias, float scale) -> ()",
+        &df3::df3_attention_bwd_elem);
+}

@@ -10,6 +10,7 @@ std::tuple<Tensor, Tensor> df3_layer_norm_bwd(const Tensor&, const Tensor&, cons
                                               const Tensor&, const Tensor&, bool);
 Tensor df3_swiglu_fwd(const Tensor&);
 Tensor df3_swiglu_bwd(const Tensor&, const Tensor&);
+Tensor df3_gated_bwd(const Tensor&, const Tensor&, const c10::optional<Tensor>&);
 Tensor df3_dropout_shared(const c10::optional<Tensor>&, const Tensor&, int64_t, int64_t, int64_t, bool, double, int64_t);
 void df3_adamw_ema(Tensor, const Tensor&, Tensor, Tensor, const c10::optional<Tensor>&, const Tensor&, const Tensor&,
                    double, double, double, double, double, double, double);
@@ -17,6 +18,7 @@ void df3_adamw_ema(Tensor, const Tensor&, Tensor, Tensor, const c10::optional<Te
 #ifdef DF3_WITH_GEMM
 void df3_register_gemm(torch::Library& m);
 const char* df3_gemm_features();
+void df3_register_attention(torch::Library& m);
 #endif
 
 static std::string df3_features() {
@@ -35,6 +37,7 @@ TORCH_LIBRARY(df3, m) {
         &df3_layer_norm_bwd);
   m.def("swiglu_fwd(Tensor x) -> Tensor", &df3_swiglu_fwd);
   m.def("swiglu_bwd(Tensor dy, Tensor x) -> Tensor", &df3_swiglu_bwd);
+  m.def("gated_bwd(Tensor dy, Tensor gp, Tensor? mask) -> Tensor", &df3_gated_bwd);
   m.def("dropout_shared(Tensor? res, Tensor x, int A, int B, int C, bool share_rows, float p, int seed) -> Tensor",
         &df3_dropout_shared);
   m.def("adamw_ema(Tensor(a!) p, Tensor g, Tensor(b!) m, Tensor(c!) v, Tensor? ema, Tensor decay, Tensor scale, "
@@ -42,5 +45,6 @@ TORCH_LIBRARY(df3, m) {
         &df3_adamw_ema);
 #ifdef DF3_WITH_GEMM
   df3_register_gemm(m);
+  df3_register_attention(m);
 #endif
 }

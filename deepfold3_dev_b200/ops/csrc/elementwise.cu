@@ -165,6 +165,61 @@ __global__ void dropout_shared_kernel(const T* __restrict__ res, const T* __rest
   out[i] = from_float<T>(kAdd ? to_float<T>(res[i]) + v : v);
 }
 
+// Vector form for C % 8 == 0: a thread owns 8 consecutive channels of one mask position, draws their
+// mask once (two Philox calls, the same values as the scalar kernel) and walks kSpan positions of the
+// axis the mask is shared along, 16 bytes (bf16) or 32 bytes (fp32) per step.
+template <typename T> struct Vec8;
+template <> struct Vec8<__nv_bfloat16> {
+  uint4 raw;
+  __device__ __forceinline__ void load(const __nv_bfloat16* p) { raw = *reinterpret_cast<const uint4*>(p); }
+  __device__ __forceinline__ void store(__nv_bfloat16* p) const { *reinterpret_cast<uint4*>(p) = raw; }
+  __device__ __forceinline__ float get(int i) const { return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(&raw)[i]); }
+  __device__ __forceinline__ void set(int i, float v) { reinterpret_cast<__nv_bfloat16*>(&raw)[i] = __float2bfloat16_rn(v); }
+};
+template <> struct Vec8<float> {
+  float4 lo, hi;
+  __device__ __forceinline__ void load(const float* p) { lo = reinterpret_cast<const float4*>(p)[0]; hi = reinterpret_cast<const float4*>(p)[1]; }
+  __device__ __forceinline__ void store(float* p) const { reinterpret_cast<float4*>(p)[0] = lo; reinterpret_cast<float4*>(p)[1] = hi; }
+  __device__ __forceinline__ float get(int i) const { return i < 4 ? (&lo.x)[i] : (&hi.x)[i - 4]; }
+  __device__ __forceinline__ void set(int i, float v) { if (i < 4) (&lo.x)[i] = v; else (&hi.x)[i - 4] = v; }
+};
+
+template <typename T, bool kAdd, int kSpan>
+__global__ void __launch_bounds__(256) dropout_shared_vec_kernel(const T* __restrict__ res, const T* __restrict__ x,
+                                                                 T* __restrict__ out, int64_t O, int64_t A, int64_t B,
+                                                                 int64_t C, bool share_rows, float p, uint64_t seed) {
+  const int64_t c8n = C / 8;
+  const int64_t shared_len = share_rows ? A : B;   // axis the mask is shared along
+  const int64_t other_len = share_rows ? B : A;    // axis that indexes the mask together with (o, c)
+  const int64_t spans = (shared_len + kSpan - 1) / kSpan;
+  const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= O * spans * other_len * c8n) return;
+  const int64_t c8 = t % c8n;
+  int64_t rest = t / c8n;
+  const int64_t other = rest % other_len; rest /= other_len;
+  const int64_t span = rest % spans;
+  const int64_t o = rest / spans;
+  const int64_t mi = (o * other_len + other) * C + c8 * 8;  // mask index of channel c8 * 8; a multiple of 4
+  const Philox rng(seed);
+  const uint4 r0 = rng((uint64_t)(mi >> 2), 0), r1 = rng((uint64_t)(mi >> 2) + 1, 0);
+  const uint32_t bits[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
+  const float inv_keep = 1.f / (1.f - p);
+  float m[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) m[i] = uniform01(bits[i]) >= p ? inv_keep : 0.f;
+  const int64_t s_end = min(shared_len, (span + 1) * (int64_t)kSpan);
+  for (int64_t sidx = span * kSpan; sidx < s_end; ++sidx) {
+    const int64_t a = share_rows ? sidx : other, b = share_rows ? other : sidx;
+    const int64_t off = ((o * A + a) * B + b) * C + c8 * 8;
+    Vec8<T> vx, vr;
+    vx.load(x + off);
+    if (kAdd) vr.load(res + off);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) vx.set(i, kAdd ? vr.get(i) + vx.get(i) * m[i] : vx.get(i) * m[i]);
+    vx.store(out + off);
+  }
+}
+
 // ---------------------------------------------------------------------------------------------
 // Flat AdamW + EMA: g = grad * scale; decoupled decay; moments; bias-corrected update; shadow lerp.
 __global__ void __launch_bounds__(256) adamw_ema_kernel(float4* __restrict__ p, const float4* __restrict__ g,
@@ -196,6 +251,23 @@ __global__ void __launch_bounds__(256) adamw_ema_kernel(float4* __restrict__ p, 
   }
 }
 
+}  // namespace df3
+
+namespace df3 {
+// Backward of out = sigmoid(g) * p * m with (g, p) stored as gp[row] = [g(0..D) | p(0..D)]:
+// dgp[row] = [dy m p sg (1 - sg) | dy m sg].
+__global__ void gated_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ gp,
+                                 const float* __restrict__ mask, __nv_bfloat16* __restrict__ dgp, int64_t rows, int D) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= rows * D) return;
+  const int64_t r = i / D;
+  const int c = (int)(i - r * D);
+  const float g = __bfloat162float(gp[r * 2 * D + c]), pv = __bfloat162float(gp[r * 2 * D + D + c]);
+  const float sg = sigmoidf_(g);
+  const float d = __bfloat162float(dy[i]) * (mask ? mask[r] : 1.f);
+  dgp[r * 2 * D + c] = __float2bfloat16_rn(d * pv * sg * (1.f - sg));
+  dgp[r * 2 * D + D + c] = __float2bfloat16_rn(d * sg);
+}
 }  // namespace df3
 
 // ================================================================================================
@@ -275,6 +347,28 @@ std::tuple<Tensor, Tensor> df3_layer_norm_bwd(const Tensor& dy, const Tensor& x,
   return {dx, partial};
 }
 
+Tensor df3_gated_bwd(const Tensor& dy, const Tensor& gp, const c10::optional<Tensor>& mask) {
+  TORCH_CHECK(dy.is_cuda() && dy.is_contiguous() && gp.is_contiguous() && dy.scalar_type() == torch::kBFloat16 &&
+              gp.scalar_type() == torch::kBFloat16 && gp.size(-1) == 2 * dy.size(-1), "gated_bwd: dy [rows, D], gp [rows, 2 D], bf16");
+  c10::cuda::CUDAGuard guard(dy.device());
+  const int D = dy.size(-1);
+  const int64_t rows = dy.numel() / D;
+  auto dgp = torch::empty_like(gp);
+  if (rows == 0) return dgp;
+  const float* mp = nullptr;
+  Tensor m;
+  if (mask.has_value() && mask->defined()) {
+    m = mask->to(torch::kFloat32).contiguous();
+    TORCH_CHECK(m.numel() == rows, "gated_bwd: mask length");
+    mp = m.data_ptr<float>();
+  }
+  const unsigned grid = (unsigned)((rows * D + 255) / 256);
+  df3::gated_bwd_kernel<<<grid, 256, 0, stream()>>>((const __nv_bfloat16*)dy.data_ptr(), (const __nv_bfloat16*)gp.data_ptr(), mp,
+                                                   (__nv_bfloat16*)dgp.data_ptr(), rows, D);
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  return dgp;
+}
+
 Tensor df3_swiglu_fwd(const Tensor& x) {
   TORCH_CHECK(x.is_cuda() && x.is_contiguous() && x.size(-1) % 2 == 0, "swiglu: contiguous CUDA tensor, even width");
   c10::cuda::CUDAGuard guard(x.device());
@@ -321,10 +415,24 @@ Tensor df3_dropout_shared(const c10::optional<Tensor>& res, const Tensor& x, int
   const unsigned grid = (unsigned)((n + 255) / 256);
   const bool add = res.has_value();
   if (add) TORCH_CHECK(res->is_contiguous() && res->sizes() == x.sizes() && res->scalar_type() == x.scalar_type(), "dropout_shared: residual mismatch");
+  constexpr int kSpan = 8;
+  const bool vec = C % 8 == 0 && reinterpret_cast<uintptr_t>(x.data_ptr()) % 32 == 0 &&
+                   reinterpret_cast<uintptr_t>(out.data_ptr()) % 32 == 0 &&
+                   (!add || reinterpret_cast<uintptr_t>(res->data_ptr()) % 32 == 0);
+  const int64_t O = n / (A * B * C);
+  const int64_t vthreads = O * (((share_rows ? A : B) + kSpan - 1) / kSpan) * (share_rows ? B : A) * (C / 8);
+  const unsigned vgrid = (unsigned)((vthreads + 255) / 256);
 #define DF3_LAUNCH(T, ADD)                                                                                         \
-  df3::dropout_shared_kernel<T, ADD><<<grid, 256, 0, stream()>>>(ADD ? (const T*)res->data_ptr() : nullptr,          \
-                                                                 (const T*)x.data_ptr(), (T*)out.data_ptr(), n, A, B, \
-                                                                 C, share_rows, (float)p, (uint64_t)seed)
+  do {                                                                                                             \
+    if (vec)                                                                                                       \
+      df3::dropout_shared_vec_kernel<T, ADD, kSpan><<<vgrid, 256, 0, stream()>>>(                                  \
+          ADD ? (const T*)res->data_ptr() : nullptr, (const T*)x.data_ptr(), (T*)out.data_ptr(), O, A, B, C,       \
+          share_rows, (float)p, (uint64_t)seed);                                                                   \
+    else                                                                                                           \
+      df3::dropout_shared_kernel<T, ADD><<<grid, 256, 0, stream()>>>(ADD ? (const T*)res->data_ptr() : nullptr,    \
+                                                                     (const T*)x.data_ptr(), (T*)out.data_ptr(), n, \
+                                                                     A, B, C, share_rows, (float)p, (uint64_t)seed); \
+  } while (0)
   if (x.scalar_type() == torch::kBFloat16) {
     if (add) DF3_LAUNCH(__nv_bfloat16, true); else DF3_LAUNCH(__nv_bfloat16, false);
   } else {

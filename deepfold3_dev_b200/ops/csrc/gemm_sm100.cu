@@ -28,6 +28,58 @@
 using torch::Tensor;
 
 namespace df3 {
+
+// The driver entry point is looked up at run time so that the library loads on machines without a driver.
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled() {
+  static EncodeTiledFn fn = [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    C10_CUDA_CHECK(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q));
+    TORCH_CHECK(sym != nullptr && q == cudaDriverEntryPointSuccess, "cuTensorMapEncodeTiled is not available");
+    return reinterpret_cast<EncodeTiledFn>(sym);
+  }();
+  return fn;
+}
+
+// bf16 tensor map of any rank up to 5 with 128-byte swizzle; dims/strides innermost first, strides in elements.
+CUtensorMap make_map_nd(const void* base, int rank, const int64_t* dims, const int64_t* strides_elems, const int* box) {
+  CUtensorMap m;
+  cuuint64_t gdims[5];
+  cuuint64_t gstrides[4];
+  cuuint32_t gbox[5], estr[5];
+  for (int i = 0; i < rank; ++i) {
+    gdims[i] = (cuuint64_t)dims[i];
+    gbox[i] = (cuuint32_t)box[i];
+    estr[i] = 1;
+    if (i > 0) gstrides[i - 1] = (cuuint64_t)strides_elems[i] * 2;
+  }
+  const CUresult r = encode_tiled()(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (cuuint32_t)rank, const_cast<void*>(base), gdims,
+                                    gstrides, gbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    std::string msg = "cuTensorMapEncodeTiled failed with code " + std::to_string((int)r) + ": dims";
+    for (int i = 0; i < rank; ++i) msg += " " + std::to_string(dims[i]) + "(stride " + std::to_string(strides_elems[i]) + ")";
+    TORCH_CHECK(false, msg);
+  }
+  return m;
+}
+
+// One int per device that kernels report bounded-wait failures through.
+Tensor status_word(int device) {
+  static std::mutex mutex;
+  static std::unordered_map<int, Tensor> words;
+  std::lock_guard<std::mutex> lock(mutex);
+  auto it = words.find(device);
+  if (it != words.end()) return it->second;
+  Tensor t = torch::zeros({1}, torch::dtype(torch::kInt32).device(torch::kCUDA, device));
+  words.emplace(device, t);
+  return t;
+}
+
 namespace {
 
 constexpr int BM = 128;
@@ -233,47 +285,12 @@ __global__ void __launch_bounds__(kThreads) gemm_kernel(const __grid_constant__ 
 }
 
 // ---- host ---------------------------------------------------------------------------------------
-// The driver entry point is looked up at run time so that the library loads on machines without a driver.
-using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_tiled() {
-  static EncodeTiledFn fn = [] {
-    void* sym = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    C10_CUDA_CHECK(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q));
-    TORCH_CHECK(sym != nullptr && q == cudaDriverEntryPointSuccess, "cuTensorMapEncodeTiled is not available");
-    return reinterpret_cast<EncodeTiledFn>(sym);
-  }();
-  return fn;
-}
-
 CUtensorMap make_map(const void* base, int64_t inner, int64_t rows, int64_t batch, int64_t row_stride,
                      int64_t batch_stride, int box_rows) {
-  CUtensorMap m;
-  cuuint64_t dims[3] = {(cuuint64_t)inner, (cuuint64_t)rows, (cuuint64_t)batch};
-  cuuint64_t strides[2] = {(cuuint64_t)row_stride * 2, (cuuint64_t)batch_stride * 2};
-  cuuint32_t box[3] = {(cuuint32_t)BK, (cuuint32_t)box_rows, 1};
-  cuuint32_t estr[3] = {1, 1, 1};
-  const CUresult r = encode_tiled()(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides,
-                                            box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                                            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  TORCH_CHECK(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed with code ", (int)r, " (inner=", inner, " rows=", rows,
-              " batch=", batch, " row_stride=", row_stride, " batch_stride=", batch_stride, ")");
-  return m;
-}
-
-std::mutex g_status_mutex;
-std::unordered_map<int, Tensor> g_status;
-
-Tensor status_word(int device) {
-  std::lock_guard<std::mutex> lock(g_status_mutex);
-  auto it = g_status.find(device);
-  if (it != g_status.end()) return it->second;
-  Tensor t = torch::zeros({1}, torch::dtype(torch::kInt32).device(torch::kCUDA, device));
-  g_status.emplace(device, t);
-  return t;
+  const int64_t dims[3] = {inner, rows, batch};
+  const int64_t strides[3] = {1, row_stride, batch_stride};
+  const int box[3] = {BK, box_rows, 1};
+  return make_map_nd(base, 3, dims, strides, box);
 }
 
 template <int BN, int EPI>
@@ -423,4 +440,4 @@ void df3_register_gemm(torch::Library& m) {
   m.def("gemm_status() -> int", &df3::df3_gemm_status);
 }
 
-const char* df3_gemm_features() { return "gemm"; }
+const char* df3_gemm_features() { return "gemm,gated_dual_linear,transition,pair_bias_attention,linear_planes,sigmoid_gate_mul"; }

@@ -62,10 +62,10 @@ def test_swiglu(dtype):
 @pytest.mark.parametrize("share_dim", [-3, -2])
 def test_dropout_add_mask_is_shared_and_unbiased(share_dim):
     torch.manual_seed(2)
-    res = torch.randn(2, 40, 48, 32, device=DEV)
+    res = torch.zeros(2, 40, 48, 32, device=DEV)
     x = torch.ones(2, 40, 48, 32, device=DEV, requires_grad=True)
     out = ops.dropout_add(res, x, 0.25, True, share_dim)
-    m = (out - res).detach()  # the scaled mask itself since x == 1
+    m = out.detach().clone()  # the scaled mask itself since x == 1 and the residual is 0
     vals = torch.unique(m).tolist()
     assert all(v == 0.0 or abs(v - 1 / 0.75) < 1e-6 for v in vals)
     ref_slice = m.select(share_dim, 0).unsqueeze(share_dim)
@@ -76,6 +76,13 @@ def test_dropout_add_mask_is_shared_and_unbiased(share_dim):
     torch.testing.assert_close(x.grad, m)  # backward regenerates the same mask
     out2 = ops.dropout_add(res, x.detach(), 0.25, True, share_dim)
     assert not torch.equal(out2, out.detach())  # a new call draws a new mask
+    # residual and values: same seed, bf16 (vector kernel) against the mask applied by hand
+    from deepfold3_dev_b200.ops import autograd_ops
+
+    r16, x16 = torch.randn(2, 40, 48, 32, device=DEV).bfloat16(), torch.randn(2, 40, 48, 32, device=DEV).bfloat16()
+    mask = autograd_ops.dropout_add(torch.zeros_like(x16), torch.ones_like(x16), 0.25, share_dim, seed=77).float()
+    got = autograd_ops.dropout_add(r16, x16, 0.25, share_dim, seed=77).float()
+    torch.testing.assert_close(got, (r16.float() + x16.float() * mask).bfloat16().float(), atol=2e-2, rtol=2e-2)
 
 
 def test_dropout_add_eval_is_plain_add():

@@ -41,3 +41,82 @@ def test_bf16_training_step_runs_and_updates():
     assert all(o["advanced"] and o["loss"] == o["loss"] for o in outs)
     assert not torch.equal(before, tr.optimizer.flat_param)
     assert tr.optimizer.ema_updates == 2
+
+
+def _block_grads(block, z, s, mask, disable):
+    import os
+
+    os.environ["DF3_DISABLE_OPS"] = disable
+    try:
+        for p in block.parameters():
+            p.grad = None
+        zz, ss = z.clone().requires_grad_(True), s.clone().requires_grad_(True)
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            zo, so = block(zz, ss, mask, mask[:, 0])
+            loss = zo.float().square().mean() + so.float().square().mean()
+        loss.backward()
+        grads = {n: p.grad.clone() for n, p in block.named_parameters() if p.grad is not None}
+        return zo.detach().float(), zz.grad.float(), grads
+    finally:
+        os.environ.pop("DF3_DISABLE_OPS", None)
+
+
+def test_pairformer_block_fused_kernels_match_eager_bf16():
+    """Forward and gradients of one Pairformer block: tensor-core kernels vs the eager bf16 statement."""
+    from deepfold3_dev_b200.models.evoformer import PairFormerBlock
+
+    torch.manual_seed(3)
+    cfg = tiny_config()
+    pf = cfg.pairformer
+    block = PairFormerBlock(pf.pair_channel, pf.seq_channel, num_single_heads=pf.single_attention_num_head,
+                            single_key_dim=pf.single_key_dim, single_value_dim=pf.single_value_dim, pair_dropout=0.0,
+                            optim=cfg.optim).cuda().train()  # fmt: skip
+    wake_zero_init(block)
+    N = 136
+    z = torch.randn(1, N, N, pf.pair_channel, device="cuda")
+    s = torch.randn(1, N, pf.seq_channel, device="cuda")
+    mask = torch.ones(1, N, N, device="cuda")
+    mask[:, :, -5:] = 0
+    mask[:, -5:, :] = 0
+    fused_names = "gated_dual_linear,transition,pair_bias_attention,linear_planes,sigmoid_gate_mul,gemm"
+    ops.census(reset=True)
+    zo_f, dz_f, g_f = _block_grads(block, z, s, mask, "")
+    assert ops.census().get("pair_bias_attention:sm100", 0) > 0
+    zo_e, dz_e, g_e = _block_grads(block, z, s, mask, fused_names)
+
+    def rel(a, b):
+        return ((a - b).norm() / (b.norm() + 1e-12)).item()
+
+    assert rel(zo_f - z, zo_e - z) < 3e-2
+    assert rel(dz_f, dz_e) < 5e-2
+    # gradients that are zero in exact arithmetic (a bias added before a softmax over the same axis) hold
+    # only rounding noise in both runs, so each parameter is judged against the largest gradient as well
+    top = max(g.float().norm().item() for g in g_e.values())
+    for n in g_e:
+        diff = (g_f[n].float() - g_e[n].float()).norm().item()
+        assert diff <= 8e-2 * g_e[n].float().norm().item() + 2e-3 * top, (n, diff, g_e[n].float().norm().item())
+    assert torch.ops.df3.gemm_status() == 0
+
+
+def test_graphed_sampler_equals_eager_sampler(monkeypatch):
+    """The CUDA-graph replay of the denoiser gives the sampler's eager result, also on a second (cached) call."""
+    torch.manual_seed(1)
+    cfg = tiny_config()
+    cfg.diffusion.steps = 8
+    cfg.diffusion.num_samples = 2
+    model = DeepFold3(cfg).cuda().eval()
+    wake_zero_init(model)
+    feats = {k: v.cuda() for k, v in synthetic_complex([("protein", 30), ("protein", 20)], num_msa=8, num_templates=1,
+                                                      seed=2, with_gt=False).items()}  # fmt: skip
+    outs = {}
+    with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
+        trunk = model.run_evoformer(feats, 0)
+        for mode in ("0", "1", "1"):
+            monkeypatch.setenv("DF3_GRAPH_SAMPLER", mode)
+            outs.setdefault(mode, []).append(model.sample_from_trunk(feats, trunk, seed=5).atom_positions.float())
+    graphs = model.diffusion_head.__dict__.get("_denoiser_graphs")
+    assert graphs is not None and not graphs.failed and len(graphs._graphs) == 1
+    eager, first, second = outs["0"][0], outs["1"][0], outs["1"][1]
+    assert torch.isfinite(eager).all()
+    torch.testing.assert_close(first, eager, atol=2e-2, rtol=2e-2)
+    torch.testing.assert_close(second, first, atol=0, rtol=0)
