@@ -60,7 +60,14 @@ def small_normal_init_(weight: torch.Tensor, target: float) -> None:
     nn.init.trunc_normal_(weight, mean=0.0, std=std, a=-2.0, b=2.0)
 
 
-class LinearNoBias(nn.Linear):
+class Linear(nn.Linear):
+    """``nn.Linear`` whose product goes through ``ops.linear`` (bf16 on cached weight copies on the GPU)."""
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return ops.linear(x, self.weight, self.bias)
+
+
+class LinearNoBias(Linear):
     """Bias-free linear with AF3 initialisation."""
 
     def __init__(self, in_features: int, out_features: int, initializer: str = "linear"):
@@ -69,7 +76,7 @@ class LinearNoBias(nn.Linear):
 
 
 def biased_linear(in_features: int, out_features: int, initializer: str = "linear", bias_value: float = 0.0):
-    lin = nn.Linear(in_features, out_features)
+    lin = Linear(in_features, out_features)
     af3_linear_init_(lin.weight, initializer)
     nn.init.constant_(lin.bias, bias_value)
     return lin

@@ -182,10 +182,12 @@ def stacked_linear(x, *ws):
 
 
 def linear(x, w, b=None):
-    nat = _native(x)
-    if nat is not None and nat.has("linear") and nat.gemm_supported(x, w):
-        _CENSUS["linear:sm100"] += 1
-        return nat.linear(x, w, b)
+    """``x w^T + b``; in bf16 mode on cached bf16 copies of the parameters, else ``F.linear``."""
+    if x.is_cuda and w.dtype == torch.float32 and x.dim() >= 2 and x.numel() > 0:
+        nat = fused(x, "gemm")
+        if nat is not None:
+            _CENSUS["linear:bf16_cached"] += 1
+            return nat.linear(x, w, b)
     _CENSUS["linear:torch"] += 1
     return torch.nn.functional.linear(x, w, b)
 

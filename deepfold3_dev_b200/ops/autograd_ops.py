@@ -7,6 +7,7 @@ inputs are made contiguous here, so callers can pass views.
 from __future__ import annotations
 
 import collections
+import weakref
 
 import torch
 
@@ -123,29 +124,67 @@ def dropout_add(residual, x, p: float, share_dim: int, seed: int | None = None):
     return _DropoutAdd.apply(residual, x, float(p), share_dim == -3, int(seed))
 
 
-def adamw_ema_flat(p, g, m, v, ema, decay, scale, lr, b1, b2, eps, bc1, bc2, ema_w):
-    K.adamw_ema(p, g, m, v, ema, decay, scale, lr, b1, b2, eps, bc1, bc2, ema_w)
+def adamw_ema_flat(p, g, m, v, ema, decay, scale, lr, b1, b2, eps, bc1, bc2, ema_w, p16=None):
+    K.adamw_ema(p, g, m, v, ema, decay, scale, lr, b1, b2, eps, bc1, bc2, ema_w, p16)
+    _W16.clear()  # stacked copies were built from the old values
 
 
 # ------------------------------------------------------------------------------------------------
 # tcgen05 GEMM family. Forward runs the fused-epilogue kernel; backward recomputes the pre-activation
 # with a library GEMM (nothing of size [rows, 2 * hidden] is kept between forward and backward).
 BF16 = torch.bfloat16
-_W16: dict = {}
+_W16: dict = {}  # (data_ptr, shape) per weight -> (versions, bf16 tensor); emptied whenever parameters change
+_MIRROR: dict = {}  # (data_ptr, shape) of an fp32 parameter -> [bf16 view kept current by the optimizer, version]
+
+
+def register_bf16_mirror(param, view16) -> None:
+    """Tell the cache that ``view16`` always holds ``param`` in bf16 (the flat optimizer refreshes it every step)."""
+    _MIRROR[(param.data_ptr(), tuple(param.shape))] = [view16, param._version, weakref.ref(param.untyped_storage())]
+
+
+def invalidate_weight_cache(clear_mirrors: bool = False) -> None:
+    """Drop cached bf16 copies; call after parameters were written in place behind autograd's back."""
+    _W16.clear()
+    if clear_mirrors:
+        _MIRROR.clear()
+
+
+def _one_bf16(w):
+    hit = _MIRROR.get((w.data_ptr(), tuple(w.shape)))
+    if hit is not None and w.dtype == torch.float32 and hit[2]() is w.untyped_storage():
+        if hit[1] != w._version:  # written directly (load_state_dict, init): refresh this view
+            with torch.no_grad():
+                hit[0].copy_(w)
+            hit[1] = w._version
+        return hit[0]
+    return None
 
 
 def bf16_weight(*ws):
-    """bf16 copy of one weight, or of several stacked along the rows; cached until a weight changes in place."""
+    """bf16 copy of one weight, or of several stacked along the rows.
+
+    Parameters owned by the flat optimizer resolve to views of its bf16 mirror (no kernel). Everything else is
+    cast once and cached by storage address and version until ``invalidate_weight_cache``. Keys are storage
+    addresses, not object identities: activation checkpointing hands the backward detached aliases of the
+    parameters.
+    """
+    if len(ws) == 1:
+        m = _one_bf16(ws[0])
+        if m is not None:
+            return m
     capturing = ws[0].is_cuda and torch.cuda.is_current_stream_capturing()
-    key = tuple(id(w) for w in ws)
-    sig = tuple((w._version, w.data_ptr()) for w in ws)
+    key = tuple((w.data_ptr(), tuple(w.shape)) for w in ws)
+    sig = tuple(w._version for w in ws)
     hit = None if capturing else _W16.get(key)
     if hit is not None and hit[0] == sig:
         return hit[1]
     with torch.no_grad():
-        t = ws[0].detach().to(BF16) if len(ws) == 1 else torch.cat([w.detach().to(BF16) for w in ws], 0)
-        t = t.contiguous()
+        parts = [_one_bf16(w) for w in ws]
+        parts = [p if p is not None else w.detach().to(BF16) for p, w in zip(parts, ws)]
+        t = (parts[0] if len(parts) == 1 else torch.cat(parts, 0)).contiguous()
     if not capturing:  # a cast made inside a CUDA-graph capture belongs to that graph's pool
+        if len(_W16) > 50000:
+            _W16.clear()
         _W16[key] = (sig, t)
     return t
 
@@ -168,8 +207,8 @@ def _stacked_gate_proj(w_gate, w_proj, deinterleave: bool):
     if not deinterleave:
         return bf16_weight(w_gate, w_proj)
     capturing = w_gate.is_cuda and torch.cuda.is_current_stream_capturing()
-    key = ("deint", id(w_gate), id(w_proj))
-    sig = tuple((w._version, w.data_ptr()) for w in (w_gate, w_proj))
+    key = ("deint", w_gate.data_ptr(), w_proj.data_ptr(), tuple(w_gate.shape))
+    sig = (w_gate._version, w_proj._version)
     hit = None if capturing else _W16.get(key)
     if hit is not None and hit[0] == sig:
         return hit[1]
@@ -203,8 +242,7 @@ class _GatedDual(torch.autograd.Function):
         n = w_gate.shape[0]
         x2 = x16.reshape(-1, x16.shape[-1])
         dy2 = (dy.t() if ctx.planes else dy.reshape(-1, n)).to(BF16).contiguous()
-        gp = torch.mm(x2, W.t())
-        dgp = K.gated_bwd(dy2, gp, m)
+        dgp = K.gemm(x2, W, None, m, dy2, 5, False)  # pre-activations recomputed in the accumulator
         dx = torch.mm(dgp, W).view(x16.shape).to(ctx.x_dtype)
         dW = _wgrad(dgp, x2, w_gate)
         dg, dp = dW[:n], dW[n:]
@@ -250,6 +288,51 @@ class _StackedLinear(torch.autograd.Function):
 
 def stacked_linear(x, *ws):
     return _StackedLinear.apply(x, *ws)
+
+
+def _linear_fwd(x, w, b):
+    x16 = x if x.dtype == BF16 else x.to(BF16)
+    W = bf16_weight(w)
+    if b is None:
+        return torch.matmul(x16, W.t())
+    return torch.addmm(bf16_weight(b), x16.reshape(-1, x16.shape[-1]), W.t()).view(*x16.shape[:-1], W.shape[0])
+
+
+class _Linear(torch.autograd.Function):
+    """``x w^T + b`` in bf16 on cached bf16 copies of the fp32 parameters (what autocast would compute, without
+    its per-call casts and dispatch)."""
+
+    @staticmethod
+    def forward(ctx, x, w, b):
+        ctx.save_for_backward(x, w)
+        ctx.has_bias = b is not None
+        ctx.b_dtype = b.dtype if b is not None else None
+        return _linear_fwd(x, w, b)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w = ctx.saved_tensors
+        W = bf16_weight(w)
+        d2 = dy.reshape(-1, W.shape[0])
+        if d2.dtype != BF16:
+            d2 = d2.to(BF16)
+        dx = dw = db = None
+        if ctx.needs_input_grad[0]:
+            dx = torch.mm(d2, W).view(x.shape)
+            if dx.dtype != x.dtype:
+                dx = dx.to(x.dtype)
+        if ctx.needs_input_grad[1]:
+            x2 = x.reshape(-1, x.shape[-1])
+            dw = torch.mm(d2.t(), x2 if x2.dtype == BF16 else x2.to(BF16)).to(w.dtype)
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            db = d2.sum(0, dtype=torch.float32).to(ctx.b_dtype)
+        return dx, dw, db
+
+
+def linear(x, w, b=None):
+    if not torch.is_grad_enabled():
+        return _linear_fwd(x, w, b)
+    return _Linear.apply(x, w, b)
 
 
 class _LinearPlanes(torch.autograd.Function):
@@ -323,10 +406,9 @@ class _Transition(torch.autograd.Function):
         c = xc.shape[-1]
         h2 = h16.reshape(-1, c)
         d = dy.reshape(-1, c).to(BF16).contiguous()
-        pre = torch.mm(h2, W1.t())
-        u = K.swiglu_fwd(pre)
+        u = K.gemm(h2, W1, None, None, None, 2, False)
         dW2 = _wgrad(d, u, w2)
-        dpre = K.swiglu_bwd(torch.mm(d, W2), pre)
+        dpre = K.gemm(h2, W1, None, None, torch.mm(d, W2), 4, False)  # pre-activations recomputed in the accumulator
         dW1 = _wgrad(dpre, h2, w1)
         dh = torch.mm(dpre, W1).view(xc.shape)
         if xc.dtype != BF16:

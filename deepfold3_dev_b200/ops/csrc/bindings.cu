@@ -13,7 +13,7 @@ Tensor df3_swiglu_bwd(const Tensor&, const Tensor&);
 Tensor df3_gated_bwd(const Tensor&, const Tensor&, const c10::optional<Tensor>&);
 Tensor df3_dropout_shared(const c10::optional<Tensor>&, const Tensor&, int64_t, int64_t, int64_t, bool, double, int64_t);
 void df3_adamw_ema(Tensor, const Tensor&, Tensor, Tensor, const c10::optional<Tensor>&, const Tensor&, const Tensor&,
-                   double, double, double, double, double, double, double);
+                   double, double, double, double, double, double, double, const c10::optional<Tensor>&);
 
 #ifdef DF3_WITH_GEMM
 void df3_register_gemm(torch::Library& m);
@@ -41,7 +41,7 @@ TORCH_LIBRARY(df3, m) {
   m.def("dropout_shared(Tensor? res, Tensor x, int A, int B, int C, bool share_rows, float p, int seed) -> Tensor",
         &df3_dropout_shared);
   m.def("adamw_ema(Tensor(a!) p, Tensor g, Tensor(b!) m, Tensor(c!) v, Tensor? ema, Tensor decay, Tensor scale, "
-        "float lr, float b1, float b2, float eps, float bc1, float bc2, float ema_w) -> ()",
+        "float lr, float b1, float b2, float eps, float bc1, float bc2, float ema_w, Tensor(d!)? p16=None) -> ()",
         &df3_adamw_ema);
 #ifdef DF3_WITH_GEMM
   df3_register_gemm(m);

@@ -225,6 +225,7 @@ __global__ void __launch_bounds__(256) dropout_shared_vec_kernel(const T* __rest
 __global__ void __launch_bounds__(256) adamw_ema_kernel(float4* __restrict__ p, const float4* __restrict__ g,
                                                         float4* __restrict__ m, float4* __restrict__ v,
                                                         float4* __restrict__ ema, const float4* __restrict__ decay,
+                                                        uint2* __restrict__ p16,  // bf16 mirror of p, 4 values per item, or null
                                                         const float* __restrict__ scale_ptr, int64_t n4, float lr,
                                                         float b1, float b2, float eps, float bc1, float bc2_sqrt,
                                                         float ema_w) {
@@ -242,6 +243,13 @@ __global__ void __launch_bounds__(256) adamw_ema_kernel(float4* __restrict__ p, 
       P[k] = pk;
     }
     p[i] = pp; m[i] = mm; v[i] = vv;
+    if (p16) {
+      __nv_bfloat162 lo = __floats2bfloat162_rn(pp.x, pp.y), hi = __floats2bfloat162_rn(pp.z, pp.w);
+      uint2 w;
+      w.x = *reinterpret_cast<uint32_t*>(&lo);
+      w.y = *reinterpret_cast<uint32_t*>(&hi);
+      p16[i] = w;
+    }
     if (ema) {
       float4 ee = ema[i];
       ee.x += (pp.x - ee.x) * ema_w; ee.y += (pp.y - ee.y) * ema_w;
@@ -446,7 +454,7 @@ Tensor df3_dropout_shared(const c10::optional<Tensor>& res, const Tensor& x, int
 
 void df3_adamw_ema(Tensor p, const Tensor& g, Tensor m, Tensor v, const c10::optional<Tensor>& ema,
                    const Tensor& decay, const Tensor& scale, double lr, double b1, double b2, double eps, double bc1,
-                   double bc2, double ema_w) {
+                   double bc2, double ema_w, const c10::optional<Tensor>& p16) {
   TORCH_CHECK(p.is_cuda() && p.scalar_type() == torch::kFloat32 && p.numel() % 4 == 0, "adamw_ema: flat fp32, numel % 4 == 0");
   c10::cuda::CUDAGuard guard(p.device());
   const int64_t n4 = p.numel() / 4;
@@ -455,7 +463,8 @@ void df3_adamw_ema(Tensor p, const Tensor& g, Tensor m, Tensor v, const c10::opt
   df3::adamw_ema_kernel<<<blocks, 256, 0, stream()>>>(
       (float4*)p.data_ptr<float>(), (const float4*)g.data_ptr<float>(), (float4*)m.data_ptr<float>(),
       (float4*)v.data_ptr<float>(), ema.has_value() ? (float4*)ema->data_ptr<float>() : nullptr,
-      (const float4*)decay.data_ptr<float>(), scale.data_ptr<float>(), n4, (float)lr, (float)b1, (float)b2, (float)eps,
+      (const float4*)decay.data_ptr<float>(),
+      (p16.has_value() && p16->defined()) ? (uint2*)p16->data_ptr() : nullptr, scale.data_ptr<float>(), n4, (float)lr, (float)b1, (float)b2, (float)eps,
       (float)bc1, (float)std::sqrt(bc2), (float)ema_w);
   C10_CUDA_KERNEL_LAUNCH_CHECK();
 }

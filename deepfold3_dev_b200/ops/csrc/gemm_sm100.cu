@@ -13,6 +13,9 @@
 //   kGated       out = sigmoid(acc_gate) * acc_proj * row_mask[m]   (gate and proj rows stacked in W)
 //   kSwiGLU      out = silu(acc_gate) * acc_proj
 //   kSigmoidMul  out = sigmoid(acc + bias[n]) * mul[m, n]
+//   kSwiGLUBwd   out[m, n] = g b s (1 + a (1 - s)),  out[m, N + n] = g a s      with a = acc_gate, b = acc_proj,
+//                s = sigmoid(a), g = mul[m, n]: the gradient of the pre-activation, which is recomputed here
+//   kGatedBwd    out[m, n] = g r b s (1 - s),        out[m, N + n] = g r s       with r = row_mask[m]
 // Output is bf16, row-major [b, m, n] or channel-major [b, n, m] (one plane per output channel, the
 // layout the triangle contraction consumes).
 #include <ATen/cuda/CUDAContext.h>
@@ -86,7 +89,7 @@ constexpr int BM = 128;
 constexpr int BK = 64;  // 64 bf16 = one 128-byte swizzle row
 constexpr int kThreads = 192;
 
-enum Epi : int { kPlain = 0, kGated = 1, kSwiGLU = 2, kSigmoidMul = 3 };
+enum Epi : int { kPlain = 0, kGated = 1, kSwiGLU = 2, kSigmoidMul = 3, kSwiGLUBwd = 4, kGatedBwd = 5 };
 
 struct GemmParams {
   __nv_bfloat16* C;
@@ -156,7 +159,8 @@ template <int BN, int EPI>
 __global__ void __launch_bounds__(kThreads) gemm_kernel(const __grid_constant__ CUtensorMap tmA,
                                                        const __grid_constant__ CUtensorMap tmB, GemmParams p) {
   using S = Smem<BN>;
-  constexpr bool kDual = (EPI == kGated || EPI == kSwiGLU);
+  constexpr bool kDual = (EPI == kGated || EPI == kSwiGLU || EPI == kSwiGLUBwd || EPI == kGatedBwd);
+  constexpr bool kBwd = (EPI == kSwiGLUBwd || EPI == kGatedBwd);
   constexpr int kOutPerTile = kDual ? BN / 2 : BN;  // output columns one CTA produces
   extern __shared__ uint8_t smem_raw[];
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -262,14 +266,63 @@ __global__ void __launch_bounds__(kThreads) gemm_kernel(const __grid_constant__ 
         } else if (EPI == kSwiGLU) {
 #pragma unroll
           for (int j = 0; j < 32; ++j) a[j] = a[j] * sigmoidf_(a[j]) * b[j];
-        } else {
-          const __nv_bfloat16* mrow = p.mul + batch * p.mul_batch_stride + (long long)row * p.ld_mul + n0;
+        } else if (kBwd) {
+          const __nv_bfloat16* grow = p.mul + batch * p.mul_batch_stride + (long long)row * p.ld_mul + n0;
+          float g[32];
+          if (row < p.M && n0 + 32 <= p.N && (reinterpret_cast<uintptr_t>(grow) & 15) == 0) {
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) {
+              const uint4 w = reinterpret_cast<const uint4*>(grow)[q4];
+              const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const __nv_bfloat162 pr = *reinterpret_cast<const __nv_bfloat162*>(&ww[e]);
+                g[q4 * 8 + 2 * e] = __low2float(pr);
+                g[q4 * 8 + 2 * e + 1] = __high2float(pr);
+              }
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) g[j] = (row < p.M && n0 + j < p.N) ? __bfloat162float(grow[j]) : 0.f;
+          }
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
-            const bool in = row < p.M && n0 + j < p.N;
-            const float bv = (p.bias != nullptr && in) ? p.bias[n0 + j] : 0.f;
-            const float mv = in ? __bfloat162float(mrow[j]) : 0.f;
-            a[j] = sigmoidf_(a[j] + bv) * mv;
+            const float sg = sigmoidf_(a[j]);
+            const float gj = g[j] * rm;
+            const float da = EPI == kSwiGLUBwd ? gj * b[j] * sg * (1.f + a[j] * (1.f - sg)) : gj * b[j] * sg * (1.f - sg);
+            const float dbv = EPI == kSwiGLUBwd ? gj * a[j] * sg : gj * sg;
+            a[j] = da;
+            b[j] = dbv;
+          }
+          store_row32(p, batch, row, n0, a);
+          GemmParams p2 = p;
+          p2.C = p.C + p.N;  // second half of the [M, 2 N] output; bounds are those of the first half
+          store_row32(p2, batch, row, n0, b);
+          continue;
+        } else {
+          const __nv_bfloat16* mrow = p.mul + batch * p.mul_batch_stride + (long long)row * p.ld_mul + n0;
+          if (row < p.M && n0 + 32 <= p.N && (reinterpret_cast<uintptr_t>(mrow) & 15) == 0) {
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              const uint4 w = reinterpret_cast<const uint4*>(mrow)[g];
+              const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const __nv_bfloat162 pr = *reinterpret_cast<const __nv_bfloat162*>(&ww[e]);
+                const int j = g * 8 + 2 * e;
+                const float b0 = p.bias ? p.bias[n0 + j] : 0.f, b1 = p.bias ? p.bias[n0 + j + 1] : 0.f;
+                a[j] = sigmoidf_(a[j] + b0) * __low2float(pr);
+                a[j + 1] = sigmoidf_(a[j + 1] + b1) * __high2float(pr);
+              }
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const bool in = row < p.M && n0 + j < p.N;
+              const float bv = (p.bias != nullptr && in) ? p.bias[n0 + j] : 0.f;
+              const float mv = in ? __bfloat162float(mrow[j]) : 0.f;
+              a[j] = sigmoidf_(a[j] + bv) * mv;
+            }
           }
         }
         store_row32(p, batch, row, n0, a);
@@ -325,13 +378,15 @@ Tensor gemm_impl(const Tensor& a3, const Tensor& w3, const c10::optional<Tensor>
   TORCH_CHECK(reinterpret_cast<uintptr_t>(a3.data_ptr()) % 16 == 0 && reinterpret_cast<uintptr_t>(w3.data_ptr()) % 16 == 0,
               "gemm: operands must be 16-byte aligned");
   TORCH_CHECK(batch == 1 || a3.stride(0) % 8 == 0, "gemm: batch stride must be a multiple of 8");
-  const bool dual = (epi == kGated || epi == kSwiGLU);
+  const bool dual = (epi == kGated || epi == kSwiGLU || epi == kSwiGLUBwd || epi == kGatedBwd);
+  const bool bwd = (epi == kSwiGLUBwd || epi == kGatedBwd);
+  TORCH_CHECK(!bwd || !channel_major, "gemm: the backward epilogues store row-major");
   TORCH_CHECK(!dual || Nw % 2 == 0, "gemm: stacked gate/proj weight expected");
   const int64_t N = dual ? Nw / 2 : Nw;
   TORCH_CHECK(M < (1ll << 31) && N < (1 << 24) && K < (1 << 24), "gemm: size out of range");
   c10::cuda::CUDAGuard guard(a3.device());
   auto opts = a3.options();
-  Tensor out = channel_major ? torch::empty({batch, N, M}, opts) : torch::empty({batch, M, N}, opts);
+  Tensor out = channel_major ? torch::empty({batch, N, M}, opts) : torch::empty({batch, M, bwd ? 2 * N : N}, opts);
   if (out.numel() == 0) return out;
 
   // accumulator width: the widest tile that the output needs
@@ -353,7 +408,7 @@ Tensor gemm_impl(const Tensor& a3, const Tensor& w3, const c10::optional<Tensor>
     TORCH_CHECK(mask_f.numel() == batch * M, "gemm: row mask length");
     p.row_mask = mask_f.data_ptr<float>();
   }
-  if (epi == kSigmoidMul) {
+  if (epi == kSigmoidMul || bwd) {
     TORCH_CHECK(mul.has_value() && mul->defined(), "gemm: sigmoid-mul epilogue needs the multiplicand");
     mul_c = mul->contiguous();
     TORCH_CHECK(mul_c.scalar_type() == torch::kBFloat16 && mul_c.numel() == batch * M * N, "gemm: multiplicand shape");
@@ -369,8 +424,8 @@ Tensor gemm_impl(const Tensor& a3, const Tensor& w3, const c10::optional<Tensor>
   p.b_batched = wb > 1;
   p.proj_row_offset = (int)N;
   p.channel_major = channel_major;
-  p.ldc = channel_major ? (int)M : (int)N;
-  p.c_batch_stride = M * N;
+  p.ldc = channel_major ? (int)M : (int)(bwd ? 2 * N : N);
+  p.c_batch_stride = M * (bwd ? 2 * N : N);
 
   const int box_b = dual ? BN / 2 : BN;
   const CUtensorMap ta = make_map(a3.data_ptr(), K, M, batch, a3.stride(1), batch > 1 ? a3.stride(0) : M * a3.stride(1), BM);
@@ -389,6 +444,12 @@ Tensor gemm_impl(const Tensor& a3, const Tensor& w3, const c10::optional<Tensor>
       break;
     case kSwiGLU:
       if (BN == 256) DF3_LAUNCH(256, kSwiGLU); else if (BN == 128) DF3_LAUNCH(128, kSwiGLU); else DF3_LAUNCH(64, kSwiGLU);
+      break;
+    case kSwiGLUBwd:
+      if (BN == 256) DF3_LAUNCH(256, kSwiGLUBwd); else if (BN == 128) DF3_LAUNCH(128, kSwiGLUBwd); else DF3_LAUNCH(64, kSwiGLUBwd);
+      break;
+    case kGatedBwd:
+      if (BN == 256) DF3_LAUNCH(256, kGatedBwd); else if (BN == 128) DF3_LAUNCH(128, kGatedBwd); else DF3_LAUNCH(64, kGatedBwd);
       break;
     default:
       TORCH_CHECK(false, "gemm: unknown epilogue ", epi);

@@ -114,6 +114,15 @@ class FlatAdamW:
                 o = self.offsets[i]
                 self.decay_vec[o : o + p.numel()] = self.param_groups[group_of[i]]["weight_decay"]
         self._group_of = group_of
+        # bf16 mirror of the parameters for the tensor-core kernels: refreshed by the step kernel, so the
+        # forward never casts a weight
+        self.flat_param_bf16 = None
+        if self.flat_param.is_cuda:
+            from ..ops import autograd_ops
+
+            self.flat_param_bf16 = self.flat_param.to(torch.bfloat16)
+            for i, p in enumerate(self.params):
+                autograd_ops.register_bf16_mirror(p, self._view(self.flat_param_bf16, i))
         self.step_count = 0
         self.ema_decay = float(ema_decay)
         self.ema_updates = 0
@@ -160,7 +169,7 @@ class FlatAdamW:
                 scale = grad_scale if torch.is_tensor(grad_scale) else torch.tensor(float(grad_scale), device=self.device)
                 nat.adamw_ema_flat(
                     self.flat_param, self.flat_grad, self.exp_avg, self.exp_avg_sq, ema, self.decay_vec,
-                    scale.reshape(1).float(), lr, b1, b2, eps, bc1, bc2, 1.0 - self.ema_decay,
+                    scale.reshape(1).float(), lr, b1, b2, eps, bc1, bc2, 1.0 - self.ema_decay, self.flat_param_bf16,
                 )  # fmt: skip
                 return
         g = self.flat_grad * grad_scale
@@ -172,6 +181,16 @@ class FlatAdamW:
         self.flat_param.addcdiv_(self.exp_avg, denom, value=-lr / bc1)
         if ema is not None:
             ema.lerp_(self.flat_param, 1.0 - self.ema_decay)
+        self.refresh_bf16()
+
+    @torch.no_grad()
+    def refresh_bf16(self) -> None:
+        """Re-derive the bf16 mirror and drop cached weight copies after the parameters were written in place."""
+        if self.flat_param_bf16 is not None:
+            from ..ops import autograd_ops
+
+            self.flat_param_bf16.copy_(self.flat_param)
+            autograd_ops.invalidate_weight_cache()
 
     def set_lr(self, lr: float) -> None:
         for g in self.param_groups:
@@ -211,6 +230,7 @@ class FlatAdamW:
             tmp = self.flat_param.clone()
             self.flat_param.copy_(self.shadow)
             self.shadow.copy_(tmp)
+        self.refresh_bf16()
 
     # ------------------------------------------------------------------ torch.optim.AdamW checkpoint layout
     def state_dict(self) -> dict:

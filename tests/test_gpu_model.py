@@ -1,6 +1,7 @@
 """Model-level checks on the GPU: the native path agrees with the CPU fp32 path, and a training step runs."""
 
 import copy
+import os
 
 import pytest
 import torch
@@ -41,6 +42,18 @@ def test_bf16_training_step_runs_and_updates():
     assert all(o["advanced"] and o["loss"] == o["loss"] for o in outs)
     assert not torch.equal(before, tr.optimizer.flat_param)
     assert tr.optimizer.ema_updates == 2
+    # the bf16 weight mirror follows the optimizer: the tensor-core path sees the updated parameters
+    torch.testing.assert_close(tr.optimizer.flat_param_bf16.float(), tr.optimizer.flat_param.bfloat16().float())
+    feats = {k: v[0].cuda() if torch.is_tensor(v) else v for k, v in batch.items()}
+    outs = []
+    for disable in ("", "gated_dual_linear,transition,pair_bias_attention,linear_planes,sigmoid_gate_mul,gemm"):
+        os.environ["DF3_DISABLE_OPS"] = disable
+        try:
+            with torch.autocast("cuda", dtype=torch.bfloat16):
+                outs.append(tr.model.compute_distogram(dict(feats), num_recycles=0).float())
+        finally:
+            os.environ.pop("DF3_DISABLE_OPS", None)
+    assert ((outs[0] - outs[1]).norm() / outs[1].norm()).item() < 5e-2
 
 
 def _block_grads(block, z, s, mask, disable):
