@@ -1,0 +1,133 @@
+"""Per-kernel timing of the sm_100a ops against their library / eager counterparts.
+
+    python -m deepfold3_dev_b200.ops.microbench --op attention --iters 10
+    python -m deepfold3_dev_b200.ops.microbench --op all
+
+Each case is timed with CUDA events after three warm-up calls, a 256 MB buffer is rewritten between
+timed calls so inputs do not sit in L2, and the median is printed with the achieved fraction of the
+measured copy bandwidth / GEMM throughput (``MEASURED_PEAKS.json`` beside the repository root when
+present). Shapes are the ones the 384-token training step runs.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+
+from . import native, reference as ref
+
+N = 384
+
+
+def _peaks():
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            d = json.load(f)
+        return float(d.get("hbm_gbs", 6650.0)), float(d.get("bf16_tflops", 1590.0)), "measured"
+    except (OSError, ValueError):
+        return 6650.0, 1590.0, "fallback"
+
+
+class Timer:
+    def __init__(self, iters: int):
+        self.iters = iters
+        self.flush = torch.zeros(64 * 1024 * 1024, device="cuda")
+
+    def __call__(self, fn) -> float:
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(self.iters):
+            self.flush.add_(1)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            e1.synchronize()
+            ts.append(e0.elapsed_time(e1))
+        ts.sort()
+        return ts[len(ts) // 2]
+
+
+def _report(name, ms, other_ms, nbytes, flops):
+    gbs, tfl, kind = _peaks()
+    line = f"{name:34s} {ms * 1e3:9.1f} us   library/eager {other_ms * 1e3:9.1f} us"
+    if nbytes:
+        line += f"   {nbytes / ms / 1e6:7.0f} GB/s ({nbytes / ms / 1e6 / gbs:.2f} of {kind} copy)"
+    if flops:
+        line += f"   {flops / ms / 1e9:7.0f} TFLOP/s ({flops / ms / 1e9 / tfl:.2f} of {kind} cuBLAS)"
+    print(line, flush=True)
+
+
+def bench_gemm(t: Timer):
+    df3 = torch.ops.df3
+    rows = N * N
+    x = torch.randn(rows, 128, device="cuda").bfloat16()
+    w = torch.randn(128, 128, device="cuda").bfloat16() * 0.1
+    w2 = torch.randn(256, 128, device="cuda").bfloat16() * 0.1
+    w1 = torch.randn(1024, 128, device="cuda").bfloat16() * 0.1
+    o = torch.randn(rows, 128, device="cuda").bfloat16()
+    io = lambda *n: 2 * rows * sum(n)  # noqa: E731 - bf16 bytes moved for the given channel counts
+    _report("gemm plain 147456x128->128", t(lambda: df3.gemm(x, w, None, None, None, 0, False)), t(lambda: x @ w.t()),
+            io(128, 128), 2 * rows * 128 * 128)  # fmt: skip
+    _report("gemm gated 147456x128->128", t(lambda: df3.gemm(x, w2, None, None, None, 1, False)),
+            t(lambda: torch.sigmoid(x @ w2[:128].t()) * (x @ w2[128:].t())), io(128, 128), 2 * rows * 128 * 256)  # fmt: skip
+    _report("gemm swiglu 147456x128->512", t(lambda: df3.gemm(x, w1, None, None, None, 2, False)),
+            t(lambda: ref.swiglu(x @ w1.t())), io(128, 512), 2 * rows * 128 * 1024)  # fmt: skip
+    _report("gemm sigmoid-mul 147456x128->128", t(lambda: df3.gemm(x, w, None, None, o, 3, False)),
+            t(lambda: torch.sigmoid(x @ w.t()) * o), io(128, 128, 128), 2 * rows * 128 * 128)  # fmt: skip
+    M = 8192
+    A, B = torch.randn(M, M, device="cuda").bfloat16(), torch.randn(M, M, device="cuda").bfloat16()
+    _report("gemm plain 8192^3", t(lambda: df3.gemm(A, B, None, None, None, 0, False)), t(lambda: A @ B.t()), 0, 2 * M**3)
+
+
+def bench_attention(t: Timer):
+    df3 = torch.ops.df3
+    for B, R, H, D, name in [(1, N, 4, 32, "triangle"), (1, 48, 16, 48, "diffusion"), (1, 1, 16, 24, "single")]:
+        q, k, v = (torch.randn(B, R, H, N, D, device="cuda").bfloat16() for _ in range(3))
+        bias = torch.randn(B, H, N, N, device="cuda").bfloat16()
+        mask = torch.ones(B, R, N, device="cuda")
+        ours = t(lambda: df3.attention_fwd(q, k, v, bias, mask, D**-0.5, True))
+        eager = t(lambda: ref.pair_bias_attention(q, k, v, bias, mask, D**-0.5, False))
+        _report(f"attention fwd {name}", ours, eager, 2 * 4 * B * R * H * N * D, 4 * B * R * H * N * N * D)
+
+
+def bench_elementwise(t: Timer):
+    from . import autograd_ops as ao
+
+    x = torch.randn(1, N, N, 128, device="cuda").bfloat16()
+    r = torch.randn_like(x)
+    w = torch.ones(128, device="cuda")
+    nb = x.numel() * 2
+    _report("layer_norm fwd 147456x128", t(lambda: torch.ops.df3.layer_norm_fwd(x, w, w, 1e-5)),
+            t(lambda: torch.nn.functional.layer_norm(x, (128,), w.bfloat16(), w.bfloat16())), 2 * nb, 0)  # fmt: skip
+    _report("dropout_add rows 147456x128", t(lambda: ao.dropout_add(r, x, 0.25, -3, seed=1)),
+            t(lambda: r + torch.nn.functional.dropout(x, 0.25)), 3 * nb, 0)  # fmt: skip
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--op", default="all", choices=["all", "gemm", "attention", "elementwise"])
+    ap.add_argument("--iters", type=int, default=10)
+    args = ap.parse_args()
+    native.require()
+    t = Timer(args.iters)
+    if args.op in ("all", "gemm"):
+        bench_gemm(t)
+    if args.op in ("all", "attention"):
+        bench_attention(t)
+    if args.op in ("all", "elementwise"):
+        bench_elementwise(t)
+    code = torch.ops.df3.gemm_status()
+    print("kernel status word:", code)
+    if code != 0:
+        raise SystemExit(1)
+
+
+if __name__ == "__main__":
+    main()
