@@ -19,6 +19,7 @@ void df3_adamw_ema(Tensor, const Tensor&, Tensor, Tensor, const c10::optional<Te
 void df3_register_gemm(torch::Library& m);
 const char* df3_gemm_features();
 void df3_register_attention(torch::Library& m);
+void df3_register_peer(torch::Library& m);
 #endif
 
 static std::string df3_features() {
@@ -46,5 +47,6 @@ TORCH_LIBRARY(df3, m) {
 #ifdef DF3_WITH_GEMM
   df3_register_gemm(m);
   df3_register_attention(m);
+  df3_register_peer(m);
 #endif
 }

@@ -501,4 +501,4 @@ void df3_register_gemm(torch::Library& m) {
   m.def("gemm_status() -> int", &df3::df3_gemm_status);
 }
 
-const char* df3_gemm_features() { return "gemm,gated_dual_linear,transition,pair_bias_attention,linear_planes,sigmoid_gate_mul"; }
+const char* df3_gemm_features() { return "gemm,gated_dual_linear,transition,pair_bias_attention,linear_planes,sigmoid_gate_mul,peer_reduce"; }

@@ -33,12 +33,17 @@ class GradSync:
         self.transport = transport or os.environ.get("DF3_COMM", "collective")
         self._peer = None
 
-    def _peer_engine(self, flat_grad: torch.Tensor):
+    def _peer_engine(self, opt):
         if self._peer is None:
             from .peer_reduce import PeerReducer
 
-            self._peer = PeerReducer(self.info, flat_grad)
+            self._peer = PeerReducer(self.info, opt)
         return self._peer
+
+    def attach(self, opt) -> None:
+        """Peer transport: move the optimizer's gradient buffer into symmetric memory now (a collective call)."""
+        if self.transport == "peer" and self.info.is_distributed and opt.flat_grad.is_cuda:
+            self._peer_engine(opt)
 
     @torch.no_grad()
     def clip_and_average(self, opt, clip_norm: float, per_rank_clip: bool, fp64_norm: bool = True):
@@ -67,7 +72,7 @@ class GradSync:
         if per_rank_clip:
             local = opt.grad_norm(fp64_norm)
             if self.transport == "peer" and opt.flat_grad.is_cuda:
-                global_norm = self._peer_engine(opt.flat_grad).all_reduce_mean(opt.flat_grad, coef(local))
+                global_norm = self._peer_engine(opt).all_reduce_mean(opt.flat_grad, coef(local))
             else:
                 opt.flat_grad.mul_(coef(local))
                 self._all_reduce_mean(opt.flat_grad)
@@ -75,7 +80,7 @@ class GradSync:
             return local, global_norm, torch.ones((), device=opt.flat_grad.device)
         if self.transport == "peer" and opt.flat_grad.is_cuda:
             one = torch.ones((), device=opt.flat_grad.device)
-            norm = self._peer_engine(opt.flat_grad).all_reduce_mean(opt.flat_grad, one)
+            norm = self._peer_engine(opt).all_reduce_mean(opt.flat_grad, one)
         else:
             self._all_reduce_mean(opt.flat_grad)
             norm = opt.grad_norm(fp64_norm)
@@ -96,3 +101,4 @@ class GradSync:
         dist.broadcast(opt.flat_param, src=0)
         if opt.shadow is not None:
             dist.broadcast(opt.shadow, src=0)
+        opt.refresh_bf16()

@@ -94,6 +94,7 @@ class Trainer:
         self.scheduler = build_scheduler(self.optimizer, train_cfg)
         self.grad_sync = GradSync(self.dist)
         self.grad_sync.broadcast_parameters(self.optimizer)
+        self.grad_sync.attach(self.optimizer)
         self.engine = OptimizerEngine(self.optimizer, self.scheduler, self.dist, train_cfg, self.grad_sync)
         self.state = TrainState()
         self.ckpt = CheckpointManager(train_cfg.output_dir, self.dist, train_cfg.max_checkpoints,
