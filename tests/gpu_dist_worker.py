@@ -40,11 +40,46 @@ def peer_reduce(info):
     assert all(p.grad.data_ptr() == base + 4 * o for p, o in zip(opt.params, opt.offsets))
 
 
+def peer_bench(info):
+    """Device time of the peer-memory reduction against NCCL all-reduce + norm on a 368 M element buffer."""
+    from deepfold3_dev_b200.parallel.grad_sync import GradSync
+    from deepfold3_dev_b200.training.flat_optimizer import FlatAdamW
+
+    n = 368 * 1024 * 1024
+    model = torch.nn.Linear(1024, n // 1024, bias=False).to(info.device)
+    opt = FlatAdamW(model, lr=1e-3, ema_decay=0.0)
+    opt.flat_grad.normal_()
+    results = {}
+    for transport in ("collective", "peer"):
+        sync = GradSync(info, transport=transport)
+        sync.attach(opt)
+        times = []
+        for it in range(8):
+            opt.flat_grad.normal_()
+            dist.barrier()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            sync.clip_and_average(opt, 10.0, False)
+            e1.record()
+            e1.synchronize()
+            if it >= 3:
+                times.append(e0.elapsed_time(e1))
+        t = torch.tensor([sum(times) / len(times)], device=info.device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        results[transport] = float(t.item())
+    if info.rank == 0:
+        gb = 4 * n / 1e9
+        w = info.world_size
+        for k, ms in results.items():
+            print(f"PEER_BENCH world={w} {k}: {ms:.3f} ms  bus bandwidth {2 * (w - 1) / w * gb / ms * 1e3:.0f} GB/s", flush=True)
+
+
 def main():
     from deepfold3_dev_b200.parallel.dist import init_process_group
 
     info = init_process_group(timeout_s=120.0)
-    {"peer_reduce": peer_reduce}[sys.argv[1]](info)
+    {"peer_reduce": peer_reduce, "peer_bench": peer_bench}[sys.argv[1]](info)
     dist.barrier()
     if info.rank == 0:
         print("WORKER_OK", sys.argv[1], flush=True)
