@@ -1,0 +1,152 @@
+"""Training examples -> batches (reference: data/module/dataset.py:238-602, data/module/collate.py:31-130,
+training/data.py:40-561).
+
+``FeatureDirDataset`` reads examples that were featurised ahead of time (one ``.pt`` feature dict per
+example, optionally inside pack shards, see ``data/pack.py``) and applies the training-time steps:
+crop to the token / atom budget, random rotation of each reference conformer, bookkeeping keys. Building
+those files from mmCIF needs gemmi / RDKit, which are not installable offline; ``SyntheticDataset``
+generates examples of the same schema for benchmarks and tests.
+"""
+
+from __future__ import annotations
+
+import json
+import os
+
+import torch
+
+from . import cropper
+from .synthetic import split_lengths, synthetic_complex
+
+PAD_VALUES = {"msa": 21}
+
+
+def rotate_reference_conformers(feats: dict, gen: torch.Generator) -> dict:
+    """Independent random rotation + small translation of every ``ref_space_uid`` group (AF3 §2.8)."""
+    from ..models.diffusion_modules import random_rigid_transforms
+
+    uid = feats["ref_space_uid"]
+    groups = int(uid.max()) + 1
+    rot, trans = random_rigid_transforms((groups,), uid.device, gen)
+    R, t = rot[uid], trans[uid] * 0.0
+    pos = torch.einsum("nmij,nmj->nmi", R, feats["ref_pos"]) + t
+    return {**feats, "ref_pos": pos * feats["ref_mask"].unsqueeze(-1)}
+
+
+class SyntheticDataset:
+    def __init__(self, num_tokens=384, num_chains=2, num_msa=1024, num_templates=4, length=1 << 30, seed=0):
+        self.cfg = (num_tokens, num_chains, num_msa, num_templates)
+        self.length, self.seed = length, seed
+
+    def __len__(self):
+        return self.length
+
+    def __getitem__(self, i: int) -> dict:
+        n, c, s, t = self.cfg
+        chains = [("protein", L) for L in split_lengths(n, c)]
+        f = synthetic_complex(chains, num_msa=s, num_templates=t, seed=self.seed + i)
+        f["_record_id"] = f"synthetic-{self.seed + i}"
+        return f
+
+
+class FeatureDirDataset:
+    """Directory of ``<id>.pt`` feature dicts plus optional ``manifest.json`` (``[{id, chains, interfaces, ...}]``)."""
+
+    def __init__(self, root: str, max_tokens: int = 384, max_atoms: int = 0, crop_weights: dict | None = None,
+                 is_distillation: bool = False, seed: int = 0, pack=None):  # fmt: skip
+        self.root, self.max_tokens, self.max_atoms = root, max_tokens, max_atoms
+        self.crop_weights, self.is_distillation, self.seed, self.pack = crop_weights, is_distillation, seed, pack
+        man = os.path.join(root, "manifest.json")
+        if os.path.exists(man):
+            with open(man) as f:
+                self.records = json.load(f)
+        else:
+            self.records = [{"id": n[:-3]} for n in sorted(os.listdir(root)) if n.endswith(".pt")]
+        self.bad = 0
+
+    def __len__(self):
+        return len(self.records)
+
+    def weights(self) -> list[float]:
+        from .samplers import example_weight
+
+        return [example_weight(r.get("chains", [{}]), r.get("interfaces")) for r in self.records]
+
+    def _load(self, rec) -> dict:
+        name = rec["id"] + ".pt"
+        if self.pack is not None and self.pack.exists(name):
+            import io
+
+            return torch.load(io.BytesIO(self.pack.read_bytes(name)), map_location="cpu", weights_only=False)
+        return torch.load(os.path.join(self.root, name), map_location="cpu", weights_only=False)
+
+    def __getitem__(self, i: int) -> dict:
+        rec = self.records[i % len(self.records)]
+        gen = torch.Generator().manual_seed(self.seed * 7_654_321 + i)
+        feats = self._load(rec)
+        feats, strategy = cropper.crop(feats, self.max_tokens, self.max_atoms, gen, self.crop_weights)
+        feats = rotate_reference_conformers(feats, gen)
+        feats.setdefault("resolution", torch.tensor(float(rec.get("resolution", 0.0))))
+        feats["is_distillation"] = torch.tensor(bool(self.is_distillation))
+        feats["_record_id"] = rec["id"]
+        feats["_crop"] = strategy
+        return feats
+
+
+def collate(samples: list[dict], pad_tokens_to: int | None = None, pad_msa_to: int | None = None) -> dict:
+    """Right-pad every tensor key to the batch maximum (or to fixed sizes) and stack; keys missing anywhere are dropped."""
+    keys = set(samples[0])
+    for s in samples[1:]:
+        keys &= set(s)
+    out = {}
+    for k in sorted(keys):
+        vals = [s[k] for s in samples]
+        if not isinstance(vals[0], torch.Tensor):
+            out[k] = vals
+            continue
+        if vals[0].dim() == 0:
+            out[k] = torch.stack(vals)
+            continue
+        shape = [max(v.shape[d] for v in vals) for d in range(vals[0].dim())]
+        if pad_tokens_to or pad_msa_to:
+            n = max(int(s["res_type"].shape[0]) for s in samples)
+            m = max(int(s["msa"].shape[0]) for s in samples) if "msa" in samples[0] else 0
+            for d in range(len(shape)):
+                if pad_tokens_to and shape[d] == n and k not in ("template_mask",):
+                    shape[d] = max(shape[d], pad_tokens_to)
+                elif pad_msa_to and d == 0 and shape[d] == m and k in ("msa", "msa_mask", "deletion_matrix"):
+                    shape[d] = max(shape[d], pad_msa_to)
+        padded = []
+        for v in vals:
+            pad = []
+            for d in reversed(range(v.dim())):
+                pad += [0, shape[d] - v.shape[d]]
+            padded.append(torch.nn.functional.pad(v, pad, value=PAD_VALUES.get(k, 0)) if any(pad) else v)
+        out[k] = torch.stack(padded)
+    return out
+
+
+class BatchStream:
+    """Iterator of collated batches: ``sampler`` -> ``dataset[i]`` -> ``collate``; bad examples are skipped and counted."""
+
+    def __init__(self, dataset, sampler, batch_size: int = 1, pad_tokens_to: int | None = None, max_retries: int = 20):
+        self.dataset, self.sampler, self.batch_size = dataset, sampler, batch_size
+        self.pad_tokens_to, self.max_retries, self.dropped = pad_tokens_to, max_retries, 0
+
+    def __iter__(self):
+        return self
+
+    def __next__(self) -> dict:
+        items = []
+        while len(items) < self.batch_size:
+            for _ in range(self.max_retries):
+                try:
+                    items.append(self.dataset[next(self.sampler)])
+                    break
+                except StopIteration:
+                    raise
+                except Exception:  # noqa: BLE001 - a broken example must not stop the run
+                    self.dropped += 1
+            else:
+                raise RuntimeError(f"{self.max_retries} consecutive examples failed to load")
+        return collate(items, self.pad_tokens_to)
