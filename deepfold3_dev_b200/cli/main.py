@@ -1,0 +1,292 @@
+"""``deepfold3`` command line (reference: scripts/cli.py and scripts/{train,inference,inference_batch,export_weights,
+convert_weights}.py).
+
+    python -m deepfold3_dev_b200.cli train --config configs/initial.yaml --output runs/a --dataset pdb:/data/pdb
+    python -m deepfold3_dev_b200.cli inference --json job.json --params weights.safetensors --output out/
+    python -m deepfold3_dev_b200.cli inference-batch --inputs-file jobs.txt --params ... --output-template 'out/{name}'
+    python -m deepfold3_dev_b200.cli export runs/a/checkpoint_1000.pt weights.safetensors --snapshot shadow
+"""
+
+from __future__ import annotations
+
+import logging
+import os
+
+import click
+
+DTYPES = {"bf16": "bfloat16", "fp32": "float32", "fp16": "float16"}
+
+
+def _setup_logging():
+    logging.basicConfig(level=logging.INFO, format="%(asctime)s %(levelname)s %(name)s: %(message)s")
+
+
+def apply_det_recipe() -> None:
+    """Bit-reproducible run: deterministic algorithms, no TF32, cuBLAS workspace pinned."""
+    import torch
+
+    os.environ.setdefault("CUBLAS_WORKSPACE_CONFIG", ":4096:8")
+    torch.use_deterministic_algorithms(True, warn_only=True)
+    torch.backends.cuda.matmul.allow_tf32 = False
+    torch.backends.cudnn.allow_tf32 = False
+    torch.backends.cudnn.benchmark = False
+
+
+@click.group()
+def cli():
+    """DeepFold3 on B200."""
+
+
+# ------------------------------------------------------------------------------------------------ train
+@cli.command()
+@click.option("--data-dir", type=click.Path(), default=None, help="Directory of featurised examples (one dataset).")
+@click.option("--output", type=click.Path(), required=True)
+@click.option("--params", type=click.Path(), default=None, help="Initial weights (.safetensors / .pt).")
+@click.option("--resume", default=None, help="Checkpoint path, or 'auto' for the latest in --output.")
+@click.option("--config", "configs", multiple=True, type=click.Path(exists=True))
+@click.option("--lr", type=float, default=None)
+@click.option("--max-steps", type=int, default=None)
+@click.option("--max-tokens", type=int, default=None)
+@click.option("--grad-accum", type=int, default=None)
+@click.option("--seed", type=int, default=None)
+@click.option("--deterministic", is_flag=True)
+@click.option("--dtype", type=click.Choice(list(DTYPES)), default=None)
+@click.option("--wandb", "wandb_project", default=None)
+@click.option("--wandb-entity", default=None)
+@click.option("--override", "overrides", multiple=True, help="key=value on the training or model config.")
+@click.option("--dataset", "datasets", multiple=True, help="name:path[:weight[:strategy[:distill]]] (repeatable).")
+@click.option("--synthetic", is_flag=True, help="Train on generated examples of the configured crop size.")
+def train(data_dir, output, params, resume, configs, lr, max_steps, max_tokens, grad_accum, seed, deterministic, dtype,
+          wandb_project, wandb_entity, overrides, datasets, synthetic):  # fmt: skip
+    """Train the model (one process per GPU; launch with torch.distributed.run for several)."""
+    _setup_logging()
+    from ..config.loader import build_configs
+    from ..data import datasets as ds
+    from ..data.samplers import MultiDatasetSampler, WeightedClusterSampler
+    from ..parallel.dist import init_process_group
+    from ..training.tracking import build_trackers
+    from ..training.trainer import Trainer, _plain
+
+    tc, mc = build_configs(list(configs), list(overrides))
+    tc.output_dir = output
+    for key, val in (("lr", lr), ("max_steps", max_steps), ("max_tokens", max_tokens), ("accumulate_grad_batches", grad_accum),
+                     ("seed", seed), ("dtype", dtype), ("params_path", params)):  # fmt: skip
+        if val is not None:
+            setattr(tc, key, val)
+    if deterministic:
+        tc.deterministic = True
+        apply_det_recipe()
+    info = init_process_group(tc.collective_timeout_s)
+    specs = list(datasets) or ([f"data:{data_dir}"] if data_dir else [])
+    if synthetic or not specs:
+        if not synthetic:
+            raise click.ClickException("give --dataset / --data-dir, or --synthetic")
+        data = ds.SyntheticDataset(tc.max_tokens, 2, min(mc.msa_crop_size, 1024), 4, seed=tc.seed + info.rank)
+        sampler = iter(range(1 << 62))
+        stream = ds.BatchStream(data, sampler, tc.batch_size_per_rank, tc.max_tokens)
+    else:
+        parts, weights = [], []
+        for spec in specs:
+            f = spec.split(":")
+            name, path = f[0], f[1]
+            weights.append(float(f[2]) if len(f) > 2 and f[2] else 1.0)
+            distill = len(f) > 4 and f[4].lower() in ("1", "true", "distill")
+            parts.append(ds.FeatureDirDataset(path, tc.max_tokens, tc.max_atoms, is_distillation=distill, seed=tc.seed))
+            logging.getLogger(__name__).info("dataset %s: %d examples from %s", name, len(parts[-1]), path)
+        samplers = [WeightedClusterSampler(p.weights(), tc.seed + 17 * i, info.rank, info.world_size) for i, p in enumerate(parts)]
+        sampler = MultiDatasetSampler(samplers, [len(p) for p in parts], weights, tc.seed)
+
+        class _Concat:
+            def __getitem__(self, i):
+                for p, off in zip(parts, sampler.offsets):
+                    if i < off + len(p):
+                        return p[i - off]
+                raise IndexError(i)
+
+        stream = ds.BatchStream(_Concat(), sampler, tc.batch_size_per_rank, tc.max_tokens)
+    trackers = build_trackers(output, info.is_main, wandb_project, wandb_entity, {"training": _plain(tc), "model": _plain(mc)})
+    trainer = Trainer(tc, mc, train_loader=stream, sampler=sampler if hasattr(sampler, "state_dict") else None,
+                      dist_info=info, trackers=trackers)  # fmt: skip
+    if resume == "auto":
+        resume = trainer.ckpt.find_latest()
+    state = trainer.run(resume)
+    for t in trackers:
+        t.close()
+    click.echo(f"finished at step {state.effective_step}")
+
+
+# ------------------------------------------------------------------------------------------------ inference
+def _inference_options(f):
+    opts = [
+        click.option("--params", type=click.Path(), default=None, help=".safetensors / .pt; random weights if omitted."),
+        click.option("--num-recycles", type=int, default=10),
+        click.option("--num-samples", type=int, default=5),
+        click.option("--msa-crop-size", type=int, default=16384),
+        click.option("--snapshot", type=click.Choice(["auto", "shadow", "average", "fast"]), default="auto"),
+        click.option("--seed", "seeds", type=int, multiple=True),
+        click.option("--device", default=None),
+        click.option("--optim", type=click.Choice(["none", "inference", "inference-cueq", "train-matched"]), default="inference"),
+        click.option("--precision", type=click.Choice(list(DTYPES)), default="bf16"),
+        click.option("--logits-scheme", type=click.Choice(["f16", "u8", "f32"]), default="f16"),
+        click.option("--bucket/--no-bucket", default=True),
+        click.option("--sample-chunk", type=int, default=0),
+        click.option("--guidance", "guidance", multiple=True, help="scale[:drop[:sigma_lo-sigma_hi]] (repeatable)."),
+        click.option("--restraint-weight", type=float, default=0.0),
+        click.option("--allow-missing-keys", is_flag=True),
+        click.option("--ccd", type=click.Path(), default=None, help="Conformer table (JSON) for ligands and modified residues."),
+        click.option("--det", is_flag=True, help="Deterministic recipe."),
+    ]
+    for o in reversed(opts):
+        f = o(f)
+    return f
+
+
+def _prepare_model(params, device, optim, snapshot, allow_missing_keys, det, ccd):
+    import torch
+
+    from ..data import ref_conformers
+    from ..inference.weights import build_model
+
+    if det:
+        apply_det_recipe()
+    if ccd:
+        ref_conformers.load_table(ccd)
+    device = device or ("cuda" if torch.cuda.is_available() else "cpu")
+    model, cfg = build_model(params, device, optim, snapshot, allow_missing=allow_missing_keys)
+    return model, cfg, device
+
+
+def _guidance_terms(specs):
+    from ..models.diffusion_modules import GuidanceTerm
+
+    terms = []
+    for s in specs:
+        f = s.split(":")
+        rng = None
+        if len(f) > 2 and f[2]:
+            lo, hi = f[2].split("-")
+            rng = (float(lo), float(hi))
+        terms.append(GuidanceTerm(scale=float(f[0]), sigma_range=rng))
+    return terms or None
+
+
+@cli.command()
+@click.option("--msa", type=click.Path(exists=True), default=None, help="A3M alignment of a single chain.")
+@click.option("--json", "json_path", type=click.Path(exists=True), default=None, help="Job description (any dialect).")
+@click.option("--sequence", default=None, help="A single sequence, no alignment.")
+@click.option("--mol-type", type=click.Choice(["protein", "dna", "rna"]), default="protein")
+@click.option("--output", type=click.Path(), required=True)
+@_inference_options
+def inference(msa, json_path, sequence, mol_type, output, params, num_recycles, num_samples, msa_crop_size, snapshot,
+              seeds, device, optim, precision, logits_scheme, bucket, sample_chunk, guidance, restraint_weight,
+              allow_missing_keys, ccd, det):  # fmt: skip
+    """Predict the structure of one job."""
+    _setup_logging()
+    import torch
+
+    from ..data.inference_input import InferenceInput
+    from ..inference.runner import run_job
+
+    model, cfg, device = _prepare_model(params, device, optim, snapshot, allow_missing_keys, det, ccd)
+    if json_path:
+        inputs = InferenceInput.from_json(json_path, msa_crop_size)
+    elif msa:
+        inputs = [InferenceInput.from_a3m(msa, mol_type, msa_crop_size=msa_crop_size)]
+    elif sequence:
+        inputs = [InferenceInput.from_sequence(sequence, mol_type, msa_crop_size=msa_crop_size)]
+    else:
+        raise click.ClickException("one of --json, --msa, --sequence is required")
+    model.cfg.msa_crop_size = msa_crop_size
+    for inp in inputs:
+        out_dir = output if len(inputs) == 1 else os.path.join(output, inp.name)
+        summaries = run_job(model, inp, out_dir, device, list(seeds) or None, num_recycles, num_samples,
+                            getattr(torch, DTYPES[precision]), bucket, sample_chunk, logits_scheme=logits_scheme,
+                            guidance_terms=_guidance_terms(guidance), manifest_fields={"params": params, "optim": optim})  # fmt: skip
+        best = max(summaries, key=lambda s: s["ranking_score"])
+        click.echo(f"{inp.name}: {len(summaries)} samples, best ranking score {best['ranking_score']:.3f} "
+                   f"(seed {best['seed']}, sample {best['sample']}) -> {out_dir}")  # fmt: skip
+
+
+@cli.command("inference-batch")
+@click.option("--inputs-file", type=click.Path(exists=True), required=True, help="One JSON path per line.")
+@click.option("--output-template", default="out/{name}", help="Output directory per job; {name} is the job name.")
+@click.option("--skip-existing/--no-skip-existing", default=True)
+@click.option("--save-distogram/--no-save-distogram", default=True)
+@_inference_options
+def inference_batch(inputs_file, output_template, skip_existing, save_distogram, params, num_recycles, num_samples,
+                    msa_crop_size, snapshot, seeds, device, optim, precision, logits_scheme, bucket, sample_chunk,
+                    guidance, restraint_weight, allow_missing_keys, ccd, det):  # fmt: skip
+    """Predict many jobs with one model load; finished seeds are skipped on a re-run."""
+    _setup_logging()
+    import torch
+
+    from ..data.inference_input import InferenceInput
+    from ..inference.runner import run_job
+
+    model, cfg, device = _prepare_model(params, device, optim, snapshot, allow_missing_keys, det, ccd)
+    model.cfg.msa_crop_size = msa_crop_size
+    with open(inputs_file) as f:
+        paths = [line.strip() for line in f if line.strip() and not line.startswith("#")]
+    done = failed = 0
+    for p in paths:
+        try:
+            for inp in InferenceInput.from_json(p, msa_crop_size):
+                run_job(model, inp, output_template.format(name=inp.name), device, list(seeds) or None, num_recycles,
+                        num_samples, getattr(torch, DTYPES[precision]), bucket, sample_chunk, skip_existing, logits_scheme,
+                        save_distogram, _guidance_terms(guidance), manifest_fields={"params": params, "input": p})  # fmt: skip
+                done += 1
+        except Exception as exc:  # noqa: BLE001 - one bad job must not stop the batch
+            failed += 1
+            logging.getLogger(__name__).exception("job %s failed: %s", p, exc)
+    click.echo(f"{done} jobs done, {failed} failed")
+    if failed:
+        raise SystemExit(1)
+
+
+# ------------------------------------------------------------------------------------------------ weights
+@cli.command()
+@click.argument("checkpoint", type=click.Path(exists=True))
+@click.argument("output", type=click.Path())
+@click.option("--snapshot", type=click.Choice(["auto", "shadow", "average", "fast"]), default="auto")
+def export(checkpoint, output, snapshot):
+    """Write one weight snapshot of a ``.pt`` checkpoint as ``.safetensors`` with the model config embedded."""
+    from ..inference.weights import load_state
+    from ..training.checkpointing import save_safetensors
+
+    state, cfg = load_state(checkpoint, snapshot)
+    save_safetensors(output, state, cfg)
+    click.echo(f"{len(state)} tensors -> {output}")
+
+
+@cli.command()
+@click.argument("af3_params", type=click.Path(exists=True))
+@click.argument("output", type=click.Path())
+def convert(af3_params, output):
+    """Convert an AlphaFold 3 parameter file (``.bin`` / ``.bin.zst``) to ``.safetensors``."""
+    from ..config.schema import ModelConfig
+    from ..convert.af3 import convert_file
+    from ..training.checkpointing import save_safetensors
+
+    state = convert_file(af3_params)
+    save_safetensors(output, state, ModelConfig())
+    click.echo(f"{len(state)} tensors -> {output}")
+
+
+@cli.command("bench-kernels")
+@click.option("--op", default="all")
+def bench_kernels(op):
+    """Per-kernel timings on the current GPU."""
+    import sys
+
+    from ..ops import microbench
+
+    sys.argv = ["microbench", "--op", op]
+    microbench.main()
+
+
+def main():
+    cli()
+
+
+if __name__ == "__main__":
+    main()
