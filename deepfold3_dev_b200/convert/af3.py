@@ -79,14 +79,14 @@ def apply_name_map(params: dict, rules: list[dict]) -> dict[str, torch.Tensor]:
                 ms, mn = sre.fullmatch(scope), nre.fullmatch(name)
                 if not (ms and mn):
                     continue
-                groups = {str(i + 1): g for i, g in enumerate(ms.groups() + mn.groups())}
-                t = torch.from_numpy(np.ascontiguousarray(arr)).float()
+                groups = (None,) + ms.groups() + mn.groups()  # "{1}" is the first regex group
+                t = torch.from_numpy(np.array(arr, copy=True)).float()
                 axis = rule.get("stack_axis")
                 pieces = [(None, t)] if axis is None else list(enumerate(t.unbind(axis)))
                 for layer, piece in pieces:
                     if rule.get("transpose"):
                         piece = piece.transpose(-1, -2)
-                    key = rule["key"].format(layer=layer, **groups)
+                    key = rule["key"].format(*groups, layer=layer)
                     out[key] = piece.contiguous()
                 break
             else:

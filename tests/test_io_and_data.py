@@ -1,0 +1,245 @@
+"""CPU tests of the output layer and the data side; metric formulas are checked against the reference package."""
+
+import json
+import os
+import struct
+
+import numpy as np
+import pytest
+import torch
+
+from deepfold3_dev_b200.data import cropper, datasets, pack, samplers
+from deepfold3_dev_b200.data.inference_input import InferenceInput
+from deepfold3_dev_b200.data.parse.a3m import parse_a3m
+from deepfold3_dev_b200.data.parse.json_input import parse_json_input
+from deepfold3_dev_b200.data.synthetic import synthetic_complex
+from deepfold3_dev_b200.io import confidences as conf
+from deepfold3_dev_b200.io import logit_codec, mmcif
+from deepfold3_dev_b200.io.background_writer import BackgroundWriter
+from deepfold3_dev_b200.models import bucket
+
+
+def _feats():
+    return synthetic_complex([("protein", 14), ("protein", 11), ("ligand", 5)], num_msa=6, num_templates=1, seed=3, with_gt=False)
+
+
+def test_confidence_metrics_match_reference(reference_package):
+    from deepfold3.io import confidences as R
+
+    torch.manual_seed(0)
+    f = _feats()
+    N = f["res_type"].shape[0]
+    pae, pde, plddt = torch.randn(2, N, N, 64) * 2, torch.randn(2, N, N, 64), torch.randn(2, N, 24 * 50)
+    seq = f["seq_mask"].float()
+    pm = seq[:, None] * seq[None, :]
+    am = f["ref_mask"].float()
+    torch.testing.assert_close(conf.error_bin_centers(), R._error_bin_centers())
+    for mine, ref in zip(conf.compute_plddt(plddt, am), R.compute_plddt(plddt, am)):
+        torch.testing.assert_close(mine, ref)
+    torch.testing.assert_close(conf.compute_pae(pae, pm), R.compute_pae(pae, pm))
+    for mine, ref in zip(conf.compute_pde(pde, pm), R.compute_pde(pde, pm)):
+        torch.testing.assert_close(mine, ref)
+    assert conf.compute_ptm(pae[0], seq, pm) == pytest.approx(R.compute_ptm(pae[0], seq, pm), rel=1e-5)
+    assert conf.compute_iptm(pae[0], seq, pm, f["asym_id"]) == pytest.approx(R.compute_iptm(pae[0], seq, pm, f["asym_id"]), rel=1e-5)
+    assert conf.compute_ranking_score(0.5, 0.7, 0.1, True) == pytest.approx(R.compute_ranking_score(0.5, 0.7, 0.1, True))
+    assert conf.compute_ranking_score(0.5, float("nan")) == pytest.approx(R.compute_ranking_score(0.5, float("nan")))
+
+
+def test_clash_and_single_chain_iptm():
+    f = synthetic_complex([("protein", 10)], num_msa=2, num_templates=0, seed=1, with_gt=False)
+    pae = torch.randn(10, 10, 64)
+    assert np.isnan(conf.compute_iptm(pae, f["seq_mask"].float(), torch.ones(10, 10), f["asym_id"]))
+    spread = torch.arange(10 * 24 * 3).float().view(10, 24, 3)
+    poly = f["mol_type"] != 3
+    assert not conf.has_clash(spread, f["ref_mask"].float(), f["residue_index"], f["asym_id"], poly)
+    collapsed = torch.zeros(10, 24, 3)
+    assert conf.has_clash(collapsed, f["ref_mask"].float(), f["residue_index"], f["asym_id"], poly)
+
+
+def test_mmcif_text_and_logit_codec(tmp_path):
+    f = _feats()
+    N = f["res_type"].shape[0]
+    txt = mmcif.structure_to_mmcif(torch.randn(2, N, 24, 3), torch.rand(2, N, 24) * 100, f, chain_names=["A", "B", "L"])
+    atoms = [ln for ln in txt.splitlines() if ln.startswith(("ATOM", "HETATM"))]
+    assert len(atoms) == 2 * int(f["ref_mask"].sum())
+    assert atoms[0].split()[3] == "N" and atoms[0].split()[6] == "A" and atoms[-1].split()[-1] == "2"
+    assert mmcif.asym_id_to_chain_name(0) == "A" and mmcif.asym_id_to_chain_name(26) == "AA"
+    logits = np.random.RandomState(0).randn(5, 7, 64).astype(np.float32) * 4
+    for scheme, tol in (("f32", 1e-7), ("f16", 1e-2), ("u8", 3e-2)):
+        path = str(tmp_path / f"l_{scheme}.npz")
+        logit_codec.save_logits(path, {"pae": logits}, scheme, attrs={"job": "x"})
+        back = logit_codec.load_logits(path)
+        assert back.attrs["job"] == "x" and logit_codec.head_names(path) == ["pae"]
+        assert np.abs(logit_codec.softmax(back["pae"]) - logit_codec.softmax(logits)).max() < tol
+
+
+def test_background_writer_orders_and_reports_errors(tmp_path):
+    seen = []
+    with BackgroundWriter() as w:
+        for i in range(5):
+            w.submit(seen.append, i)
+    assert seen == [0, 1, 2, 3, 4]
+    w = BackgroundWriter()
+    w.submit(lambda: 1 / 0)
+    with pytest.raises(RuntimeError, match="background write failed"):
+        w.close()
+
+
+def test_a3m_and_json_dialects(tmp_path):
+    m = parse_a3m(">q\nACDE\n>h1\nAC-aaE\n>dup\nACDE\n")
+    assert m.sequences == ["ACDE", "AC-E"] and m.deletions.tolist() == [[0, 0, 0, 0], [0, 0, 0, 2]]
+    af3 = {"name": "t", "modelSeeds": [4], "sequences": [
+        {"protein": {"id": ["A", "B"], "sequence": "ACDEFGHIK", "unpairedMsa": ">q\nACDEFGHIK\n>h\nAC-EFGHaIK\n"}},
+        {"rna": {"id": "R", "sequence": "ACGU"}}, {"ligand": {"id": "Z", "ccdCodes": ["ZN"]}}]}  # fmt: skip
+    p = tmp_path / "j.json"
+    p.write_text(json.dumps(af3))
+    (job,) = parse_json_input(str(p))
+    assert job.dialect == "alphafold3" and job.num_chains == 4 and job.seeds == [4]
+    inp = InferenceInput.from_job(job)
+    f = inp.features
+    assert inp.num_tokens == 9 + 9 + 4 + 1 and inp.chain_names == ["A", "B", "R", "Z"]
+    assert f["entity_id"].tolist() == [0] * 18 + [1] * 4 + [2] and f["sym_id"][9:18].tolist() == [1] * 9
+    assert f["msa"].shape == (3, 23) and f["msa"][1, 9:].eq(21).all() and f["deletion_matrix"][1, 7] == 1
+    assert f["ref_mask"][0].sum() == 5 and f["ref_mask"][-1].sum() == 1 and int(f["ref_element"][-1, 0]) == 30
+    server = [{"name": "s", "sequences": [{"proteinChain": {"sequence": "ACD", "count": 2}}, {"ion": {"ion": "MG", "count": 1}}]}]
+    (sjob,) = parse_json_input(server)
+    assert sjob.dialect == "alphafoldserver" and sjob.num_chains == 3
+    ptx = [{"name": "p", "sequences": [{"proteinChain": {"sequence": "ACD", "count": 1, "msa": {}}}]}]
+    assert parse_json_input(ptx)[0].dialect == "protenix"
+    with pytest.raises(ValueError, match="conformer"):
+        InferenceInput.from_job(parse_json_input({"name": "l", "sequences": [{"ligand": {"id": "L", "ccdCodes": ["ATP"]}}]})[0])
+
+
+def test_crops_keep_consistency():
+    f = synthetic_complex([("protein", 60), ("protein", 50), ("ligand", 6)], num_msa=8, num_templates=2, seed=1)
+    for strategy in ("contiguous", "spatial", "spatial_interface"):
+        c, used = cropper.crop(f, 48, 300, torch.Generator().manual_seed(3), strategy=strategy)
+        n = c["res_type"].shape[0]
+        assert used == strategy and n <= 48 and int(c["ref_mask"].sum()) <= 300
+        assert c["msa"].shape == (8, n) and c["template_aatype"].shape == (2, n) and c["pair_mask"].shape == (n, n)
+        assert c["token_index"].tolist() == list(range(n)) and int(c["frame_token_index"].max()) < n
+    inter, _ = cropper.crop(f, 48, 0, torch.Generator().manual_seed(5), strategy="spatial_interface")
+    assert len(torch.unique(inter["asym_id"])) >= 2
+    same, used = cropper.crop(f, 500)
+    assert used == "none" and same is f
+
+
+def test_sampler_resume_sharding_collate_pack(tmp_path):
+    w = [1.0, 3.0, 0.5, 2.0]
+    full = samplers.WeightedClusterSampler(w, seed=2, rank=0, world_size=1, block=8)
+    r0 = samplers.WeightedClusterSampler(w, seed=2, rank=0, world_size=2, block=4)
+    r1 = samplers.WeightedClusterSampler(w, seed=2, rank=1, world_size=2, block=4)
+    stream = [next(full) for _ in range(8)]
+    assert [next(r0) for _ in range(4)] == stream[0::2] and [next(r1) for _ in range(4)] == stream[1::2]
+    st = full.state_dict()
+    nxt = [next(full) for _ in range(10)]
+    full.load_state_dict(st)
+    assert [next(full) for _ in range(10)] == nxt
+    src = tmp_path / "src"
+    src.mkdir()
+    for i in range(3):
+        torch.save(synthetic_complex([("protein", 40 + 5 * i), ("protein", 30)], num_msa=4, num_templates=0, seed=i), src / f"ex{i}.pt")
+    assert pack.build_pack(str(src), str(tmp_path / "pk")) == 3
+    pk = pack.Pack(str(tmp_path / "pk"))
+    assert pk.exists("ex2.pt") and not pk.exists("nope") and pk.read_bytes("ex1.pt") == (src / "ex1.pt").read_bytes()
+    ds = datasets.FeatureDirDataset(str(src), max_tokens=48, pack=pk)
+    batch = next(datasets.BatchStream(ds, samplers.WeightedClusterSampler(ds.weights(), seed=1), batch_size=2, pad_tokens_to=64))
+    assert batch["res_type"].shape == (2, 64) and batch["msa"].shape == (2, 4, 64) and batch["seq_mask"].sum(-1).tolist() == [48, 48]
+    assert (batch["msa"][:, :, 48:] == 21).all() and len(batch["_record_id"]) == 2
+
+
+def test_bucket_pad_unpad_preserves_prediction():
+    from deepfold3_dev_b200.models.model import DeepFold3
+    from tests.helpers import tiny_config, wake_zero_init
+
+    assert bucket.bucket_size(130) == 160 and bucket.bucket_size(4097) == 4608
+    torch.manual_seed(0)
+    cfg = tiny_config()
+    cfg.diffusion.steps = 2
+    cfg.diffusion.num_samples = 1
+    model = DeepFold3(cfg).eval()
+    wake_zero_init(model)
+    f = synthetic_complex([("protein", 20), ("protein", 13)], num_msa=5, num_templates=1, seed=2, with_gt=False)
+    padded, n = bucket.pad_features(f, 40)
+    assert n == 33 and padded["res_type"].shape[0] == 40 and padded["msa"].shape == (5, 40) and not padded["seq_mask"][33:].any()
+    with torch.no_grad():
+        a = model(f, seed=1, num_recycles=1)
+        b = bucket.unpad_output(model(padded, seed=1, num_recycles=1), n)
+    assert b.pae.shape == a.pae.shape and b.distogram.shape == a.distogram.shape
+    torch.testing.assert_close(b.distogram, a.distogram, atol=2e-4, rtol=1e-3)
+    torch.testing.assert_close(b.atom_positions, a.atom_positions, atol=2e-3, rtol=1e-3)
+
+
+def test_af3_record_reader_and_name_map(tmp_path):
+    from deepfold3_dev_b200.convert import af3
+
+    def record(scope, name, arr, dtype=None):
+        dt = (dtype or str(arr.dtype)).encode()
+        raw = arr.tobytes()
+        return struct.pack(f"<5i{len(scope)}s{len(name)}s{len(dt)}s{arr.ndim}i", len(scope), len(name), len(dt), arr.ndim,
+                           len(raw), scope.encode(), name.encode(), dt, *arr.shape) + raw  # fmt: skip
+
+    w = np.arange(24, dtype=np.float32).reshape(2, 3, 4)
+    bf = (np.asarray([1.5, -2.0], dtype=np.float32).view(np.uint32) >> 16).astype(np.uint16)
+    path = tmp_path / "p.bin"
+    path.write_bytes(record("trunk/stack/linear", "weights", w) + record("head/norm", "scale", bf, "bfloat16"))
+    params = af3.read_af3_params(str(path))
+    assert params["head/norm"]["scale"].tolist() == [1.5, -2.0]
+    rules = [{"scope": r"trunk/stack/(\w+)", "name": "weights", "key": "blocks.{layer}.{1}.weight", "transpose": True, "stack_axis": 0},
+             {"scope": "head/norm", "name": "scale", "key": "head.norm.weight"}]  # fmt: skip
+    state = af3.apply_name_map(params, rules)
+    assert set(state) == {"blocks.0.linear.weight", "blocks.1.linear.weight", "head.norm.weight"}
+    assert state["blocks.1.linear.weight"].shape == (4, 3) and state["blocks.1.linear.weight"][0, 0] == 12
+    with pytest.raises(KeyError):
+        af3.apply_name_map(params, rules[:1])
+
+
+def test_inference_runner_writes_the_output_tree(tmp_path):
+    from deepfold3_dev_b200.inference.runner import run_job, sample_chunk_seed, sample_chunks
+    from deepfold3_dev_b200.models.model import DeepFold3
+    from tests.helpers import tiny_config, wake_zero_init
+
+    assert sample_chunks(5, 2) == [2, 2, 1] and sample_chunks(5, 0) == [5] and sample_chunk_seed(7, 0) == 7
+    cfg = tiny_config()
+    cfg.diffusion.steps = 2
+    model = DeepFold3(cfg).eval()
+    wake_zero_init(model)
+    inp = InferenceInput.from_sequence("MKTAYIAKQRQISFVK")
+    out = str(tmp_path / "o")
+    s = run_job(model, inp, out, "cpu", seeds=[1, 2], num_recycles=0, num_samples=2, dtype=torch.float32, use_bucket=False, sample_chunk=1)
+    assert len(s) == 4 and os.path.exists(os.path.join(out, "ranking_scores.csv"))
+    for seed in (1, 2):
+        assert os.path.exists(os.path.join(out, f"seed-{seed}_distogram.npz"))
+        for i in (0, 1):
+            assert sorted(os.listdir(os.path.join(out, f"seed-{seed}_sample-{i}"))) == ["confidences.json", "logits.npz", "model.cif"]
+    man = json.load(open(os.path.join(out, "run_manifest.json")))
+    assert man["status"] == "done" and "kernel_census" in man
+    again = run_job(model, inp, out, "cpu", seeds=[1, 2], num_recycles=0, num_samples=2, dtype=torch.float32, use_bucket=False, skip_existing=True)
+    assert again == []
+
+
+def test_schedule_free_matches_reference(reference_package):
+    from deepfold3.training.schedule_free import AdamWScheduleFree
+
+    from deepfold3_dev_b200.training.schedule_free import FlatAdamWScheduleFree
+
+    torch.manual_seed(0)
+    a = torch.nn.Sequential(torch.nn.Linear(6, 5), torch.nn.Linear(5, 1))
+    b = torch.nn.Sequential(torch.nn.Linear(6, 5), torch.nn.Linear(5, 1))
+    b.load_state_dict(a.state_dict())
+    kw = dict(lr=3e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.0, warmup_steps=3)
+    ref = AdamWScheduleFree(a.parameters(), **kw)
+    ref.train()
+    mine = FlatAdamWScheduleFree(b, **kw)
+    x, y = torch.randn(32, 6), torch.randn(32, 1)
+    for _ in range(6):
+        for model, opt in ((a, ref), (b, mine)):
+            opt.zero_grad()
+            ((model(x) - y) ** 2).mean().backward()
+            opt.step()
+    for pa, pb in zip(a.parameters(), b.parameters()):
+        torch.testing.assert_close(pb, pa, atol=1e-6, rtol=1e-5)
+    ref.eval()
+    mine.eval()
+    for pa, pb in zip(a.parameters(), b.parameters()):
+        torch.testing.assert_close(pb, pa, atol=1e-6, rtol=1e-5)
