@@ -243,3 +243,40 @@ def test_schedule_free_matches_reference(reference_package):
     mine.eval()
     for pa, pb in zip(a.parameters(), b.parameters()):
         torch.testing.assert_close(pb, pa, atol=1e-6, rtol=1e-5)
+
+
+def test_extra_losses_match_reference_and_differentiate(reference_package):
+    from deepfold3.training import loss as R
+
+    from deepfold3_dev_b200.training import extra_losses as X
+
+    torch.manual_seed(0)
+    f = synthetic_complex([("protein", 12), ("protein", 9)], num_msa=2, num_templates=0, seed=4)
+    N = 21
+    pred = (f["atom_gt_positions"][None] + 0.5 * torch.randn(3, N, 24, 3)).requires_grad_(True)
+    cb = torch.full((N,), 4)
+    target = torch.where(f["ref_mask"][:, 4], torch.tensor(1.2), torch.tensor(0.0))
+    args = (pred, f["frame_token_index"], f["frame_atom_index"], cb, target)
+    torch.testing.assert_close(X.chirality_loss(*args), R.chirality_loss(*args))
+    mine, ref = X.chirality_violation_rates(*args), R.chirality_violation_rates(*args)
+    for k in ref:
+        torch.testing.assert_close(mine[k], ref[k])
+    bb = (pred, f["atom_gt_positions"], f["atom_gt_mask"], f["seq_mask"], f["asym_id"], f["mol_type"])
+    torch.testing.assert_close(X.backbone_chirality_loss(*bb), R.backbone_chirality_loss(*bb))
+    # FAPE: zero at the ground truth, positive and differentiable away from it, chunking does not change it
+    tok = torch.arange(N)[:, None].expand(N, 3).contiguous()
+    slots = torch.tensor([0, 1, 2]).expand(N, 3).contiguous()
+    ok = torch.ones(N, 3, dtype=torch.bool)
+    pm = torch.ones(N, N, dtype=torch.bool)
+    common = (tok, slots, ok, f["frame_atom_index"], f["frame_token_index"], pm)
+    zero, _ = X.fape_loss(f["atom_gt_positions"][None], f["atom_gt_positions"], *common)
+    assert float(zero) < 2e-3
+    a, _ = X.fape_loss(pred, f["atom_gt_positions"], *common)
+    b, _ = X.fape_loss(pred, f["atom_gt_positions"], *common, chunk_size=5)
+    torch.testing.assert_close(a, b)
+    intra, inter = X.fape_loss(pred, f["atom_gt_positions"], *common, asym_id=f["asym_id"], mode="both")
+    assert float(a) > 0 and float(inter) > 0
+    sc, parts = X.shape_complementarity_loss(pred, f["atom_gt_positions"], f["atom_gt_mask"], f["token_to_rep_atom"], f["asym_id"],
+                                             f["mol_type"], f["seq_mask"])  # fmt: skip
+    (a + intra + sc).backward()
+    assert torch.isfinite(pred.grad).all() and float(pred.grad.abs().sum()) > 0 and set(parts) >= {"shape_comp_token"}
