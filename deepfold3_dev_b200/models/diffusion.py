@@ -8,6 +8,7 @@ denoiser call runs all samples of all molecules as ``[B, S, ...]``.
 
 from __future__ import annotations
 
+import os
 from collections.abc import Sequence
 from contextlib import nullcontext
 
@@ -48,7 +49,9 @@ class DiffusionHead(nn.Module):
         self.cfg = cfg
         aca = cfg.atom_cross_att
         c_diff = aca.per_token_channels
-        self._grad_checkpoint = True  # recompute each denoiser call in backward, as the reference does
+        # recompute each denoiser call in backward (what the reference does) unless memory is plentiful:
+        # DF3_DIFFUSION_CKPT=0 keeps the activations of all samples instead
+        self._grad_checkpoint = os.environ.get("DF3_DIFFUSION_CKPT", "1") != "0"
         self.conditioning = DiffusionConditioningBlock(
             c_pair_in=c_pair, c_single_in=c_single, rel_feat_dim=rel_feat_dim,
             c_pair_out=cfg.conditioning_pair_channel, c_single_out=cfg.conditioning_seq_channel,

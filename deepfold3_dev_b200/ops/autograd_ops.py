@@ -439,7 +439,8 @@ ATTN_BWD_CHUNK_BYTES = 40 * 1024 * 1024
 
 def attention_supported(q, k, v, bias) -> bool:
     d = q.shape[-1]
-    return q.is_cuda and q.dim() == 5 and q.dtype == BF16 and k.dtype == BF16 and v.dtype == BF16 and d % 8 == 0 and d <= 64
+    even = q.shape[-2] % 2 == 0 or not torch.is_grad_enabled()  # the backward kernel handles keys in pairs
+    return q.is_cuda and q.dim() == 5 and q.dtype == BF16 and k.dtype == BF16 and v.dtype == BF16 and d % 8 == 0 and d <= 64 and even
 
 
 class _Attention(torch.autograd.Function):

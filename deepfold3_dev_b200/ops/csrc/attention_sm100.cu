@@ -368,34 +368,53 @@ __global__ void __launch_bounds__(kThreads) attention_fwd_kernel(const __grid_co
 //   dp_io [Rc, H, N, N] bf16: in dO.v                    out dS * scale, dS = P (dP - delta)
 //   dbias [H, N, N] fp32 += sum_r dS
 template <typename BiasT>
-__global__ void attention_bwd_elem_kernel(__nv_bfloat16* __restrict__ s_io, __nv_bfloat16* __restrict__ dp_io,
-                                          const BiasT* __restrict__ bias, long long bias_sh, long long bias_si,
-                                          const float* __restrict__ mask, long long mask_sr,
-                                          const float* __restrict__ row_max, const float* __restrict__ row_log2sum,
-                                          const float* __restrict__ delta,
-                                          float* __restrict__ dbias, int Rc, int H, int N, float scale) {
+__global__ void __launch_bounds__(256) attention_bwd_elem_kernel(
+    __nv_bfloat16* __restrict__ s_io, __nv_bfloat16* __restrict__ dp_io, const BiasT* __restrict__ bias, long long bias_sh,
+    long long bias_si, const float* __restrict__ mask, long long mask_sr, const float* __restrict__ row_max,
+    const float* __restrict__ row_log2sum, const float* __restrict__ delta, float* __restrict__ dbias, int Rc, int H, int N,
+    float scale) {
+  // one thread per (h, i, pair of keys): N is even (head rows are 16-byte aligned), so a pair never crosses a row
   const long long per_row = (long long)H * N * N;
-  const long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long e = 2 * ((long long)blockIdx.x * blockDim.x + threadIdx.x);
   if (e >= per_row) return;
   const int j = (int)(e % N);
   const int i = (int)((e / N) % N);
   const int h = (int)(e / ((long long)N * N));
-  const float bv = (bias ? to_float<BiasT>(bias[h * bias_sh + (long long)i * bias_si + j]) : 0.f) * kLog2e;
+  float bv0 = 0.f, bv1 = 0.f;
+  if (bias) {
+    const BiasT* bp = bias + h * bias_sh + (long long)i * bias_si + j;
+    bv0 = to_float<BiasT>(bp[0]) * kLog2e;
+    bv1 = to_float<BiasT>(bp[1]) * kLog2e;
+  }
   const float scale_log2 = scale * kLog2e;
-  float acc = 0.f;
+  float acc0 = 0.f, acc1 = 0.f;
+#pragma unroll 4
   for (int r = 0; r < Rc; ++r) {
     const long long off = r * per_row + e;
     const long long row = ((long long)r * H + h) * N + i;
+    float m0 = 0.f, m1 = 0.f;
+    if (mask) {
+      m0 = 1e9f * kLog2e * (mask[r * mask_sr + j] - 1.f);
+      m1 = 1e9f * kLog2e * (mask[r * mask_sr + j + 1] - 1.f);
+    }
+    const __nv_bfloat162 sv = *reinterpret_cast<const __nv_bfloat162*>(s_io + off);
+    const __nv_bfloat162 dv = *reinterpret_cast<const __nv_bfloat162*>(dp_io + off);
+    const float mx = row_max[row], ls = row_log2sum[row], dl = delta[row];
     // the same base-2 logit as the forward kernel forms, so masked and unmasked keys line up with its row maximum
-    const float madd = mask ? 1e9f * kLog2e * (mask[r * mask_sr + j] - 1.f) : 0.f;
-    const float x2 = (__bfloat162float(s_io[off]) * scale_log2 + bv) + madd;
-    const float pr = exp2f((x2 - row_max[row]) - row_log2sum[row]);
-    const float ds = pr * (__bfloat162float(dp_io[off]) - delta[row]);
-    acc += ds;
-    s_io[off] = __float2bfloat16_rn(pr);
-    dp_io[off] = __float2bfloat16_rn(ds * scale);
+    const float p0 = exp2f(((__low2float(sv) * scale_log2 + bv0) + m0 - mx) - ls);
+    const float p1 = exp2f(((__high2float(sv) * scale_log2 + bv1) + m1 - mx) - ls);
+    const float d0 = p0 * (__low2float(dv) - dl), d1 = p1 * (__high2float(dv) - dl);
+    acc0 += d0;
+    acc1 += d1;
+    *reinterpret_cast<__nv_bfloat162*>(s_io + off) = __floats2bfloat162_rn(p0, p1);
+    *reinterpret_cast<__nv_bfloat162*>(dp_io + off) = __floats2bfloat162_rn(d0 * scale, d1 * scale);
   }
-  if (dbias) dbias[e] += acc;
+  if (dbias) {
+    float2 cur = *reinterpret_cast<float2*>(dbias + e);
+    cur.x += acc0;
+    cur.y += acc1;
+    *reinterpret_cast<float2*>(dbias + e) = cur;
+  }
 }
 
 void df3_attention_bwd_elem(Tensor s_io, Tensor dp_io, const c10::optional<Tensor>& bias, const c10::optional<Tensor>& mask,
@@ -424,7 +443,8 @@ void df3_attention_bwd_elem(Tensor s_io, Tensor dp_io, const c10::optional<Tenso
     dbp = dbias->data_ptr<float>();
   }
   const long long per_row = (long long)H * N * N;
-  const unsigned grid = (unsigned)((per_row + 255) / 256);
+  TORCH_CHECK(N % 2 == 0, "attention_bwd_elem: an even number of keys is expected");
+  const unsigned grid = (unsigned)((per_row / 2 + 255) / 256);
   cudaStream_t stream = at::cuda::getCurrentCUDAStream();
   auto* sp = reinterpret_cast<__nv_bfloat16*>(s_io.data_ptr());
   auto* dp = reinterpret_cast<__nv_bfloat16*>(dp_io.data_ptr());
