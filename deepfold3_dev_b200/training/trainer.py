@@ -58,7 +58,7 @@ def freeze_modules(model, names: list[str]) -> None:
 class Trainer:
     def __init__(self, train_cfg: TrainingConfig, model_cfg: ModelConfig | None = None, *, train_loader=None,
                  eval_loader=None, sampler=None, dist_info: DistInfo | None = None, device: str | None = None,
-                 trackers=None):  # fmt: skip
+                 trackers=None, callbacks=None):  # fmt: skip
         self.cfg = train_cfg
         self.model_cfg = model_cfg or ModelConfig()
         self.dist = dist_info or init_process_group(train_cfg.collective_timeout_s, device)
@@ -103,6 +103,9 @@ class Trainer:
         self.timer = StepTimeMeter()
         self.train_loader, self.eval_loader, self.sampler = train_loader, eval_loader, sampler
         self.trackers = trackers or []
+        from .callbacks import CallbackList
+
+        self.callbacks = CallbackList(callbacks or [])
         self._pinned: dict[str, torch.Tensor] = {}
 
     # ------------------------------------------------------------------ one optimizer step
@@ -165,6 +168,7 @@ class Trainer:
     # ------------------------------------------------------------------ checkpoints
     def save_checkpoint(self, name: str | None = None, background: bool = True):
         name = name or f"checkpoint_{self.state.effective_step}.pt"
+        self.callbacks.fire("on_checkpoint_save", self, name)
         return self.ckpt.save(
             name, model=self.model, optimizer=self.optimizer, scheduler=self.scheduler, state=self.state,
             model_cfg=self.model_cfg, train_cfg=self.cfg, sampler=self.sampler, background=background,
@@ -245,6 +249,7 @@ class Trainer:
         data_wait = 0.0
         it = iter(self.train_loader)
         stopped = False
+        self.callbacks.fire("on_train_start", self)
         while st.effective_step < cfg.max_steps and not stopped:
             t0 = time.perf_counter()
             try:
@@ -255,6 +260,7 @@ class Trainer:
                 batch = next(it)
             data_wait += time.perf_counter() - t0
             record_ids = batch.pop("_record_id", None) if isinstance(batch, dict) else None
+            self.callbacks.fire("on_step_start", self, batch)
             self.timer.start()
             t_step = time.perf_counter()
             _, loss_dict, counts = self.micro_step(batch, record_ids)
@@ -262,6 +268,7 @@ class Trainer:
                                {f"train/{k}": c for k, c in counts.items()})  # fmt: skip
             if st.global_step % acc == 0:
                 result = self.engine.step_or_skip(st)
+                self.callbacks.fire("on_step_end" if result.advanced else "on_skip_step", self, result)
                 if result.advanced:
                     if result.grad_norm is not None:
                         self.meters.update({"train/grad_norm": result.grad_norm})
@@ -287,6 +294,7 @@ class Trainer:
                 self._log(vals)
                 data_wait = 0.0
             stopped = shutdown.tick()
+        self.callbacks.fire("on_train_end", self)
         self.save_checkpoint("checkpoint_final.pt" if not stopped else None, background=False)
         self.ckpt.wait_for_io()
         self.ckpt.close()
@@ -305,7 +313,9 @@ class Trainer:
         if want:
             self.save_checkpoint()
         if self.eval_loader is not None and st.effective_step % cfg.eval_interval == 0:
+            self.callbacks.fire("on_eval_start", self)
             vals = self.evaluate()
+            self.callbacks.fire("on_eval_end", self, vals)
             self._log(vals)
             total = vals.get("eval/total")
             if total is not None and total < st.best_eval_loss:
