@@ -26,8 +26,8 @@ def provenance() -> dict:
         "git_commit": _git("rev-parse", "HEAD"),
         "git_dirty": bool(_git("status", "--porcelain")),
         "python": platform.python_version(),
-        "torch": torch.__version__,
-        "cuda": torch.version.cuda,
+        "torch": str(torch.__version__),
+        "cuda": None if torch.version.cuda is None else str(torch.version.cuda),
         "gpu": gpu,
         "hostname": platform.node(),
     }
