@@ -25,7 +25,7 @@ namespace df3 {
 namespace {
 
 constexpr int kMaxWorld = 16;
-constexpr uint32_t kFlagSpinLimit = 200u * 1000u * 1000u;  // polls of a local word: a few seconds, then give up
+constexpr int64_t kDefaultSpinLimit = 20 * 1000 * 1000;  // polls (each sleeps ~64 ns) of a local word: about two seconds, then give up
 
 // Layout of the symmetric control block of one rank (all offsets in bytes).
 constexpr int kCoefOff = 0;      // float: this rank's clip coefficient, read by peers
@@ -86,14 +86,14 @@ __global__ void __launch_bounds__(512) peer_reduce_kernel(Peers peers, double* _
 
 // Waits for the flags of all ranks, then norm = sqrt(sum of partial squared norms). status: kTimeoutPeerFlag on give-up.
 __global__ void peer_norm_kernel(const unsigned char* __restrict__ ctrl, float* __restrict__ norm_out, int* __restrict__ status,
-                                 int world, unsigned long long seq) {
+                                 int world, unsigned long long seq, unsigned int spin_limit) {
   const int r = threadIdx.x;
   bool ok = true;
   if (r < world) {
     const volatile unsigned long long* flag = reinterpret_cast<const volatile unsigned long long*>(ctrl + kFlagsOff) + r;
     uint32_t spins = 0;
     while (*flag < seq) {
-      if (++spins > kFlagSpinLimit) { ok = false; break; }
+      if (++spins > spin_limit) { ok = false; break; }
       __nanosleep(64);
     }
   }
@@ -114,7 +114,7 @@ __global__ void peer_norm_kernel(const unsigned char* __restrict__ ctrl, float* 
 // grad: this rank's symmetric flat gradient (numel % 4 == 0); grad_ptrs / ctrl_ptrs: peer addresses by rank;
 // scratch: local 16 zero bytes (double + counter); returns the norm of the averaged gradient (fp32 scalar tensor).
 Tensor df3_peer_allreduce_mean(Tensor grad, const std::vector<int64_t>& grad_ptrs, const std::vector<int64_t>& ctrl_ptrs,
-                               Tensor scratch, Tensor status, int64_t rank, int64_t world, int64_t seq) {
+                               Tensor scratch, Tensor status, int64_t rank, int64_t world, int64_t seq, int64_t spin_limit) {
   TORCH_CHECK(grad.is_cuda() && grad.scalar_type() == torch::kFloat32 && grad.is_contiguous() && grad.numel() % 4 == 0,
               "peer_allreduce_mean: contiguous fp32 CUDA buffer, numel % 4 == 0");
   TORCH_CHECK(world >= 1 && world <= kMaxWorld && (int64_t)grad_ptrs.size() == world && (int64_t)ctrl_ptrs.size() == world &&
@@ -139,7 +139,8 @@ Tensor df3_peer_allreduce_mean(Tensor grad, const std::vector<int64_t>& grad_ptr
   peer_reduce_kernel<<<blocks, 512, 0, stream>>>(peers, acc, done, begin4, end4, (int)rank, (int)world, (unsigned long long)seq);
   C10_CUDA_KERNEL_LAUNCH_CHECK();
   peer_norm_kernel<<<1, 32, 0, stream>>>(peers.ctrl[rank], norm.data_ptr<float>(), status.data_ptr<int>(), (int)world,
-                                        (unsigned long long)seq);
+                                        (unsigned long long)seq,
+                                        (unsigned int)(spin_limit > 0 ? spin_limit : kDefaultSpinLimit));
   C10_CUDA_KERNEL_LAUNCH_CHECK();
   return norm;
 }
@@ -149,5 +150,5 @@ Tensor df3_peer_allreduce_mean(Tensor grad, const std::vector<int64_t>& grad_ptr
 
 void df3_register_peer(torch::Library& m) {
   m.def("peer_allreduce_mean(Tensor(a!) grad, int[] grad_ptrs, int[] ctrl_ptrs, Tensor(b!) scratch, Tensor(c!) status, int rank, "
-        "int world, int seq) -> Tensor", &df3::df3_peer_allreduce_mean);
+        "int world, int seq, int spin_limit=0) -> Tensor", &df3::df3_peer_allreduce_mean);
 }

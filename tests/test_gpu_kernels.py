@@ -111,3 +111,26 @@ def test_flat_adamw_kernel_matches_reference_math():
     torch.testing.assert_close(og.flat_param.cpu(), oc.flat_param, atol=1e-6, rtol=1e-5)
     torch.testing.assert_close(og.shadow.cpu(), oc.shadow, atol=1e-6, rtol=1e-5)
     torch.testing.assert_close(og.exp_avg_sq.cpu(), oc.exp_avg_sq, atol=1e-8, rtol=1e-5)
+
+
+def test_peer_flag_wait_runs_out_and_reports_status():
+    """A wait for a flag that nothing sets ends after its poll limit with a status code; the context stays usable.
+
+    One GPU plays rank 0 of a world of two whose second rank never runs: its control block is plain local memory.
+    """
+    from deepfold3_dev_b200.ops import native
+
+    native.require()
+    n = 4096
+    grads = [torch.randn(n, device=DEV), torch.randn(n, device=DEV)]
+    ctrls = [torch.zeros(128, device=DEV), torch.zeros(128, device=DEV)]
+    ctrls[0][0] = 1.0
+    ctrls[1][0] = 1.0
+    scratch = torch.zeros(4, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    norm = torch.ops.df3.peer_allreduce_mean(grads[0], [g.data_ptr() for g in grads], [c.data_ptr() for c in ctrls], scratch,
+                                             status, 0, 2, 1, 20000)  # fmt: skip
+    torch.cuda.synchronize()
+    assert int(status.item()) == 4  # kTimeoutPeerFlag
+    assert torch.isnan(norm)
+    assert float((torch.ones(8, device=DEV) * 2).sum()) == 16.0  # the device still answers
