@@ -7,12 +7,12 @@ already live in one flat fp32 buffer (``FlatAdamW.flat_grad``), so a reduction
 is one collective with no packing. Two transports:
 
 * ``collective``: ``torch.distributed.all_reduce`` (NCCL on GPUs, gloo on CPU).
-  Always available; the correctness oracle for the other.
+  Always available; the correctness oracle for the other and the default on CPU.
 * ``peer``: the sm_100a kernel in ``ops/csrc/peer_reduce.cu`` working on
   NVLink peer mappings of every rank's buffer: each rank sums its slice of all
   ranks' gradients (applying each source rank's clip coefficient), writes the
   averaged slice back to every rank and accumulates the squared norm, in one
-  launch. Selected with ``DF3_COMM=peer`` or ``transport="peer"``.
+  launch. The default for NCCL process groups; ``DF3_COMM=collective`` switches it off.
 
 Both give every rank the same averaged gradient and its global norm.
 """
@@ -30,7 +30,9 @@ from .dist import DistInfo
 class GradSync:
     def __init__(self, info: DistInfo, transport: str | None = None):
         self.info = info
-        self.transport = transport or os.environ.get("DF3_COMM", "collective")
+        # NCCL ranks on one node default to the peer-memory kernel; everything else to the collective
+        default = "peer" if (info.is_distributed and info.backend == "nccl") else "collective"
+        self.transport = transport or os.environ.get("DF3_COMM", default)
         self._peer = None
 
     def _peer_engine(self, opt):
@@ -43,7 +45,13 @@ class GradSync:
     def attach(self, opt) -> None:
         """Peer transport: move the optimizer's gradient buffer into symmetric memory now (a collective call)."""
         if self.transport == "peer" and self.info.is_distributed and opt.flat_grad.is_cuda:
-            self._peer_engine(opt)
+            try:
+                self._peer_engine(opt)
+            except Exception as exc:  # noqa: BLE001 - symmetric memory unavailable (same on every rank): use NCCL
+                import logging
+
+                logging.getLogger(__name__).warning("peer-memory gradient transport unavailable (%r); using NCCL", exc)
+                self.transport, self._peer = "collective", None
 
     @torch.no_grad()
     def clip_and_average(self, opt, clip_norm: float, per_rank_clip: bool, fp64_norm: bool = True):
