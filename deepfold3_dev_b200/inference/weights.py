@@ -15,6 +15,8 @@ import logging
 
 import torch
 
+from ..compat import torch_load_compat
+
 from ..config.schema import ModelConfig, OptimConfig
 from ..training.checkpointing import load_safetensors, strip_module_prefix
 
@@ -53,7 +55,7 @@ def load_state(path: str, snapshot: str = "auto"):
     if path.endswith(".safetensors"):
         return load_safetensors(path)
     if path.endswith((".pt", ".pth", ".ckpt")):
-        ckpt = torch.load(path, map_location="cpu", weights_only=False, mmap=True)
+        ckpt = torch_load_compat(path, map_location="cpu", weights_only=False, mmap=True)
         if isinstance(ckpt, dict) and "model" in ckpt:
             return select_snapshot(ckpt, snapshot), ckpt.get("model_cfg")
         return strip_module_prefix(ckpt), None

@@ -23,6 +23,8 @@ import threading
 
 import numpy as np
 import torch
+
+from ..compat import torch_load_compat
 import torch.distributed as dist
 
 from ..parallel.dist import DistInfo
@@ -71,7 +73,7 @@ def load_pretrained_weights(model, path: str, strict: bool = True) -> None:
     if path.endswith(".safetensors"):
         state, _ = load_safetensors(path)
     else:
-        blob = torch.load(path, map_location="cpu", weights_only=False, mmap=True)
+        blob = torch_load_compat(path, map_location="cpu", weights_only=False, mmap=True)
         state = blob["model"] if isinstance(blob, dict) and "model" in blob else blob
     missing = model.load_state_dict(strip_module_prefix(state), strict=strict)
     if not strict and (missing.missing_keys or missing.unexpected_keys):
@@ -205,7 +207,7 @@ class CheckpointManager:
     def load(self, path: str, *, model, optimizer=None, scheduler=None, state=None, sampler=None, strict=True,
              skip_optimizer=False, skip_scheduler=False, skip_step=False) -> dict:  # fmt: skip
         """Restore from ``path`` on every rank; returns the blob (minus tensors already consumed)."""
-        blob = torch.load(path, map_location="cpu", weights_only=False, mmap=True)
+        blob = torch_load_compat(path, map_location="cpu", weights_only=False, mmap=True)
         model.load_state_dict(strip_module_prefix(blob["model"]), strict=strict)
         if optimizer is not None:
             # parameters are views into the flat buffer, load_state_dict copied into them in place

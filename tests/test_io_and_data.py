@@ -280,3 +280,85 @@ def test_extra_losses_match_reference_and_differentiate(reference_package):
                                              f["mol_type"], f["seq_mask"])  # fmt: skip
     (a + intra + sc).backward()
     assert torch.isfinite(pred.grad).all() and float(pred.grad.abs().sum()) > 0 and set(parts) >= {"shape_comp_token"}
+
+
+HHR = """Query         q
+Match_columns 10
+
+ No Hit                             Prob E-value P-value  Score    SS Cols Query HMM  Template HMM
+  1 1ABC_A some protein             99.9 1.2E-30 1E-34  200.0   0.0   8    2-9      5-12 (100)
+
+No 1
+>1ABC_A some protein
+Probab=99.90  E-value=1.2e-30  Score=200.00  Aligned_cols=8  Identities=50%  Similarity=0.9  Sum_probs=7.5  Template_Neff=5.0
+
+Q q                 2 ACDE-FGH    8 (10)
+Q Consensus         2 acde-fgh    8 (10)
+T Consensus         5 ac~eKfgh   12 (100)
+T 1ABC_A            5 AC-EKFGH   11 (100)
+
+"""
+
+
+def test_hhr_hits_and_template_features():
+    from deepfold3_dev_b200.data.parse.hhr import parse_hhr
+    from deepfold3_dev_b200.data.templates import TemplateChain, template_features
+
+    (hit,) = parse_hhr(HHR)
+    assert (hit.pdb_id, hit.chain_id, hit.aligned_cols, hit.sum_probs) == ("1ABC", "A", 8, 7.5)
+    assert hit.query_to_hit_mapping == {1: 4, 2: 5, 4: 6, 5: 8, 6: 9, 7: 10}
+    rng = np.random.RandomState(0)
+    tpl = TemplateChain(["GLY"] * 12, rng.randn(12, 24, 3).astype(np.float32), np.ones((12, 24), bool), hit.query_to_hit_mapping)
+    f = template_features(10, [tpl], max_templates=4, token_offset=3, num_tokens=20)
+    assert f["template_mask"].tolist() == [1, 0, 0, 0] and f["template_aatype"].shape == (4, 20)
+    assert f["template_backbone_mask"][0].nonzero().flatten().tolist() == [4, 5, 7, 8, 9, 10]
+    R = f["template_backbone_frame"][0, 4]
+    torch.testing.assert_close(R @ R.T, torch.eye(3), atol=1e-5, rtol=0)
+    torch.testing.assert_close(f["template_pseudo_beta"][0, 4], f["template_ca"][0, 4])  # glycine: CA stands in for CB
+
+
+def test_msa_search_cache_and_fake_binary(tmp_path, monkeypatch):
+    from deepfold3_dev_b200.data.msa import search
+
+    cache = search.MsaCache(str(tmp_path / "cache"))
+    fake = tmp_path / "mmseqs"
+    fake.write_text("#!/bin/sh\nif [ \"$1\" = result2msa ]; then printf '>query\\nACDE\\n>hit\\nAC-E\\n' > \"$5\"; fi\nexit 0\n")
+    fake.chmod(0o755)
+    a3m = search.search_local("ACDE", "/db/uniref", cache, binary=str(fake))
+    assert parse_a3m(a3m).sequences == ["ACDE", "AC-E"]
+    fake.unlink()  # the second call must come from the cache
+    assert search.search_local("ACDE", "/db/uniref", cache, binary=str(fake)) == a3m
+    with pytest.raises(RuntimeError, match="not on PATH"):
+        search.search_local("WWWW", "/db/uniref", cache, binary=str(fake))
+
+
+def test_tiled_linear_is_transparent():
+    from deepfold3_dev_b200.models.tiled_linear import TiledLinear
+
+    lin = torch.nn.Linear(8, 4)
+    tiled = TiledLinear(lin, 3).train()
+    x = torch.randn(10, 5, 8)
+    torch.testing.assert_close(tiled(x), lin(x))
+    assert list(tiled.state_dict()) == ["weight", "bias"]
+    other = TiledLinear(torch.nn.Linear(8, 4), 0)
+    other.load_state_dict(tiled.state_dict())
+    torch.testing.assert_close(other.inner.weight, lin.weight)
+
+
+def test_reference_pickled_config_loads_without_the_reference(reference_package, tmp_path):
+    """A blob that pickles the reference's config classes loads in a process that cannot import the reference."""
+    import subprocess
+    import sys
+
+    import deepfold3.model.config as RC
+
+    path = tmp_path / "ckpt.pt"
+    cfg = RC.ModelConfig()
+    cfg.num_recycles = 7
+    torch.save({"model": {"w": torch.ones(2)}, "model_cfg": cfg, "ema": None}, path)
+    code = ("import sys; from deepfold3_dev_b200.inference.weights import load_state; "
+            f"s, c = load_state({str(path)!r}); print(type(c).__module__, c.num_recycles, s['w'].tolist())")  # fmt: skip
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, cwd=root, env={**os.environ, "PYTHONPATH": root})
+    assert out.returncode == 0, out.stderr[-2000:]
+    assert out.stdout.split() == ["deepfold3_dev_b200.config.schema", "7", "[1.0,", "1.0]"]
