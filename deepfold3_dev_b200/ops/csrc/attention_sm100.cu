@@ -222,31 +222,34 @@ __global__ void __launch_bounds__(kThreads) attention_fwd_kernel(const __grid_co
     uint8_t* p_row = p_s + (row_in_tile >> 3) * 1024 + (row_in_tile & 7) * 128;
     const int swz = row_in_tile & 7;
     bool ok = true;
+    constexpr bool kPair = false;  // pairing measured slower (367 vs 326 us on the triangle shape): kept for reference
     float v[32];
+    float v2[kPair ? 32 : 1];
     for (int j = 0; j < nb && ok; ++j) {
       if (!ptx::mbar_wait(s_ready, (uint32_t)j & 1u, p.status, kTimeoutMmaDone)) { ok = false; break; }
       ptx::tc_fence_after();
       const int key0 = j * BKEY;
-      // additive key term (mask, out-of-range keys) of this block, one copy per warp
+      // additive key term (mask, out-of-range keys) of this block; skipped altogether when every key of the block counts
       __syncwarp();
+      bool plain_block = true;
 #pragma unroll
       for (int t = 0; t < 4; ++t) {
         const int key = key0 + lane + 32 * t;
         float add = -INFINITY;
         if (key < p.N) add = mask_row ? 1e9f * kLog2e * (mask_row[key] - 1.f) : 0.f;
         key_add[lane + 32 * t] = add;
+        plain_block = plain_block && (add == 0.f);
       }
+      plain_block = __all_sync(0xffffffffu, plain_block);
       __syncwarp();
-      // pass 1: logits in base 2 with bias and mask, row maximum; logits parked back in tensor memory
+      // pass 1: logits in base 2 with bias and mask, row maximum; logits parked back in tensor memory.
+      // kPair: two 32-column chunks per tensor-memory round trip (more loads in flight; the registers allow it for DN <= 32)
       float m_new = m_run;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        ptx::tmem_ld_32x32(tmem_s + lane_off + c * 32, v);
-        ptx::tmem_ld_wait();
+      auto logits_chunk = [&](float* vv, int c) {
         const int kbase = key0 + c * 32;
         if (bias_row == nullptr) {
 #pragma unroll
-          for (int t = 0; t < 32; ++t) v[t] = v[t] * p.scale_log2;
+          for (int t = 0; t < 32; ++t) vv[t] = vv[t] * p.scale_log2;
         } else if (p.bias_is_bf16 && kbase + 32 <= p.N && ((reinterpret_cast<uintptr_t>(bias_row) + 2 * kbase) & 15) == 0) {
           const uint4* src = reinterpret_cast<const uint4*>(bias_row + 2 * kbase);
 #pragma unroll
@@ -256,8 +259,8 @@ __global__ void __launch_bounds__(kThreads) attention_fwd_kernel(const __grid_co
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
               const __nv_bfloat162 pr = *reinterpret_cast<const __nv_bfloat162*>(&ww[e]);
-              v[g * 8 + 2 * e] = v[g * 8 + 2 * e] * p.scale_log2 + __low2float(pr) * kLog2e;
-              v[g * 8 + 2 * e + 1] = v[g * 8 + 2 * e + 1] * p.scale_log2 + __high2float(pr) * kLog2e;
+              vv[g * 8 + 2 * e] = vv[g * 8 + 2 * e] * p.scale_log2 + __low2float(pr) * kLog2e;
+              vv[g * 8 + 2 * e + 1] = vv[g * 8 + 2 * e + 1] * p.scale_log2 + __high2float(pr) * kLog2e;
             }
           }
         } else {
@@ -268,39 +271,77 @@ __global__ void __launch_bounds__(kThreads) attention_fwd_kernel(const __grid_co
             if (key < p.N)
               add = p.bias_is_bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(bias_row)[key])
                                    : reinterpret_cast<const float*>(bias_row)[key];
-            v[t] = v[t] * p.scale_log2 + add * kLog2e;
+            vv[t] = vv[t] * p.scale_log2 + add * kLog2e;
           }
         }
+        if (plain_block) {
 #pragma unroll
-        for (int t = 0; t < 32; ++t) {
-          v[t] += key_add[c * 32 + t];
-          m_new = fmaxf(m_new, v[t]);
+          for (int t = 0; t < 32; ++t) m_new = fmaxf(m_new, vv[t]);
+        } else {
+#pragma unroll
+          for (int t = 0; t < 32; ++t) {
+            vv[t] += key_add[c * 32 + t];
+            m_new = fmaxf(m_new, vv[t]);
+          }
         }
-        tmem_st_32x32(tmem_s + lane_off + c * 32, v);
+      };
+      if (kPair) {
+#pragma unroll 1
+        for (int c = 0; c < 4; c += 2) {
+          ptx::tmem_ld_32x32(tmem_s + lane_off + c * 32, v);
+          ptx::tmem_ld_32x32(tmem_s + lane_off + (c + 1) * 32, v2);
+          ptx::tmem_ld_wait();
+          logits_chunk(v, c);
+          logits_chunk(v2, c + 1);
+          tmem_st_32x32(tmem_s + lane_off + c * 32, v);
+          tmem_st_32x32(tmem_s + lane_off + (c + 1) * 32, v2);
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          ptx::tmem_ld_32x32(tmem_s + lane_off + c * 32, v);
+          ptx::tmem_ld_wait();
+          logits_chunk(v, c);
+          tmem_st_32x32(tmem_s + lane_off + c * 32, v);
+        }
       }
       tmem_st_wait();
       const float alpha = exp2f(m_run - m_new);  // 0 on the first block
       float l_blk = 0.f;
       // pass 2: probabilities, row sum, P as bf16 into the swizzled A-operand tile
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        ptx::tmem_ld_32x32(tmem_s + lane_off + c * 32, v);
-        ptx::tmem_ld_wait();
+      auto probs_chunk = [&](float* vv, int c) {
 #pragma unroll
         for (int t = 0; t < 32; ++t) {
-          v[t] = exp2f(v[t] - m_new);
-          l_blk += v[t];
+          vv[t] = exp2f(vv[t] - m_new);
+          l_blk += vv[t];
         }
         uint8_t* atom = p_row + (c >> 1) * 16384;
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
           const int chunk = (c & 1) * 4 + g;  // 16-byte chunk inside the 128-byte line
           uint4 w;
-          w.x = pack2(v[g * 8 + 0], v[g * 8 + 1]);
-          w.y = pack2(v[g * 8 + 2], v[g * 8 + 3]);
-          w.z = pack2(v[g * 8 + 4], v[g * 8 + 5]);
-          w.w = pack2(v[g * 8 + 6], v[g * 8 + 7]);
+          w.x = pack2(vv[g * 8 + 0], vv[g * 8 + 1]);
+          w.y = pack2(vv[g * 8 + 2], vv[g * 8 + 3]);
+          w.z = pack2(vv[g * 8 + 4], vv[g * 8 + 5]);
+          w.w = pack2(vv[g * 8 + 6], vv[g * 8 + 7]);
           *reinterpret_cast<uint4*>(atom + ((chunk ^ swz) << 4)) = w;
+        }
+      };
+      if (kPair) {
+#pragma unroll 1
+        for (int c = 0; c < 4; c += 2) {
+          ptx::tmem_ld_32x32(tmem_s + lane_off + c * 32, v);
+          ptx::tmem_ld_32x32(tmem_s + lane_off + (c + 1) * 32, v2);
+          ptx::tmem_ld_wait();
+          probs_chunk(v, c);
+          probs_chunk(v2, c + 1);
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          ptx::tmem_ld_32x32(tmem_s + lane_off + c * 32, v);
+          ptx::tmem_ld_wait();
+          probs_chunk(v, c);
         }
       }
       l_run = l_run * alpha + l_blk;
@@ -401,8 +442,10 @@ __global__ void __launch_bounds__(256) attention_bwd_elem_kernel(
     const __nv_bfloat162 dv = *reinterpret_cast<const __nv_bfloat162*>(dp_io + off);
     const float mx = row_max[row], ls = row_log2sum[row], dl = delta[row];
     // the same base-2 logit as the forward kernel forms, so masked and unmasked keys line up with its row maximum
-    const float p0 = exp2f(((__low2float(sv) * scale_log2 + bv0) + m0 - mx) - ls);
-    const float p1 = exp2f(((__high2float(sv) * scale_log2 + bv1) + m1 - mx) - ls);
+    // a logit cannot exceed its row maximum: the clamp only acts on fully masked rows, where the 1e9 offset leaves
+    // 128-wide rounding steps and the recomputed logit may land one step above the stored maximum
+    const float p0 = exp2f(fminf(((__low2float(sv) * scale_log2 + bv0) + m0) - mx, 0.f) - ls);
+    const float p1 = exp2f(fminf(((__high2float(sv) * scale_log2 + bv1) + m1) - mx, 0.f) - ls);
     const float d0 = p0 * (__low2float(dv) - dl), d1 = p1 * (__high2float(dv) - dl);
     acc0 += d0;
     acc1 += d1;

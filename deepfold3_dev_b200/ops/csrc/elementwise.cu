@@ -57,6 +57,74 @@ __global__ void __launch_bounds__(256) layer_norm_fwd_kernel(const T* __restrict
   }
 }
 
+// LayerNorm forward for bf16 rows whose length is a multiple of 128: a lane owns groups of 4 consecutive channels
+// (8-byte loads and stores, a warp covers 256 contiguous bytes per step). Same math as the generic kernel.
+template <int G, int R>  // G groups of 4 channels per lane (C = 128 * G); R rows per warp in flight
+__global__ void __launch_bounds__(256) layer_norm_fwd_vec_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ w,
+                                                                 const float* __restrict__ b, __nv_bfloat16* __restrict__ y,
+                                                                 float* __restrict__ mean_out, float* __restrict__ rstd_out,
+                                                                 int64_t rows, float eps) {
+  constexpr int C = 128 * G;
+  const int lane = threadIdx.x & 31;
+  const int64_t row0 = ((int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * R;
+  if (row0 >= rows) return;
+  uint2 raw[R][G];
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    const int64_t row = row0 + r < rows ? row0 + r : rows - 1;  // tail rows re-read the last row; their stores are skipped
+    const uint2* xr = reinterpret_cast<const uint2*>(x + row * C);
+#pragma unroll
+    for (int g = 0; g < G; ++g) raw[r][g] = xr[lane + 32 * g];
+  }
+  float wv[4 * G], bv[4 * G];
+#pragma unroll
+  for (int g = 0; g < G; ++g)
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int c = 4 * (lane + 32 * g) + k;
+      wv[4 * g + k] = w ? w[c] : 1.f;
+      bv[4 * g + k] = b ? b[c] : 0.f;
+    }
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    float v[4 * G];
+    float s = 0.f;
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&raw[r][g].x);
+      const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162*>(&raw[r][g].y);
+      v[4 * g + 0] = __low2float(lo); v[4 * g + 1] = __high2float(lo);
+      v[4 * g + 2] = __low2float(hi); v[4 * g + 3] = __high2float(hi);
+      s += (v[4 * g + 0] + v[4 * g + 1]) + (v[4 * g + 2] + v[4 * g + 3]);
+    }
+    const float mean = warp_sum(s) / C;
+    float q = 0.f;
+#pragma unroll
+    for (int k = 0; k < 4 * G; ++k) {
+      const float d = v[k] - mean;
+      q += d * d;
+    }
+    const float rstd = rsqrtf(warp_sum(q) / C + eps);
+    if (row0 + r >= rows) continue;
+    uint2* yr = reinterpret_cast<uint2*>(y + (row0 + r) * C);
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      float o[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) o[k] = (v[4 * g + k] - mean) * rstd * wv[4 * g + k] + bv[4 * g + k];
+      __nv_bfloat162 lo = __floats2bfloat162_rn(o[0], o[1]), hi = __floats2bfloat162_rn(o[2], o[3]);
+      uint2 out;
+      out.x = *reinterpret_cast<uint32_t*>(&lo);
+      out.y = *reinterpret_cast<uint32_t*>(&hi);
+      yr[lane + 32 * g] = out;
+    }
+    if (lane == 0) {
+      mean_out[row0 + r] = mean;
+      rstd_out[row0 + r] = rstd;
+    }
+  }
+}
+
 // LayerNorm backward. dx per row; dw / db are accumulated per block into partial[blockIdx.x][2][C]
 // (summed on the host side in a fixed order, so the result is deterministic).
 template <typename T, int K>
@@ -312,7 +380,19 @@ std::tuple<Tensor, Tensor, Tensor> df3_layer_norm_fwd(const Tensor& x, const c10
           x.data_ptr<float>(), wp, bp, y.data_ptr<float>(), mean.data_ptr<float>(), rstd.data_ptr<float>(), rows,  \
           C, (float)eps);                                                                                          \
   } while (0)
-  if (C <= 128) DF3_LN_FWD(4); else if (C <= 256) DF3_LN_FWD(8); else if (C <= 512) DF3_LN_FWD(16); else DF3_LN_FWD(32);
+  const bool vec_ok = bf16 && C % 128 == 0 && C <= 768 && reinterpret_cast<uintptr_t>(x.data_ptr()) % 8 == 0;
+#define DF3_LN_VEC(G)                                                                                              \
+  df3::layer_norm_fwd_vec_kernel<G, (G <= 2 ? 4 : 2)><<<(unsigned)((rows + warps * (G <= 2 ? 4 : 2) - 1) / (warps * (G <= 2 ? 4 : 2))), \
+                                                       warps * 32, 0, stream()>>>(                                   \
+      (const __nv_bfloat16*)x.data_ptr(), wp, bp, (__nv_bfloat16*)y.data_ptr(), mean.data_ptr<float>(),            \
+      rstd.data_ptr<float>(), rows, (float)eps)
+  if (vec_ok && C == 128) DF3_LN_VEC(1);
+  else if (vec_ok && C == 256) DF3_LN_VEC(2);
+  else if (vec_ok && C == 384) DF3_LN_VEC(3);
+  else if (vec_ok && C == 512) DF3_LN_VEC(4);
+  else if (vec_ok && C == 768) DF3_LN_VEC(6);
+  else if (C <= 128) DF3_LN_FWD(4); else if (C <= 256) DF3_LN_FWD(8); else if (C <= 512) DF3_LN_FWD(16); else DF3_LN_FWD(32);
+#undef DF3_LN_VEC
 #undef DF3_LN_FWD
   C10_CUDA_KERNEL_LAUNCH_CHECK();
   return {y, mean, rstd};
