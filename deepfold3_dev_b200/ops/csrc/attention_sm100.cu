@@ -7,10 +7,12 @@
 // (R = samples) all read the projection outputs in place. The bias is shared by the R rows.
 //
 // One CTA owns 128 queries of one (b, r, h) and streams the keys in blocks of 128:
-//   warp 0      TMA producer: Q once, then K/V blocks into a two-stage ring (5-D tensor maps, 128-byte swizzle)
+//   warp 0      TMA producer: Q once, then K blocks into a two-stage ring and V blocks into one stage (5-D tensor maps,
+//               128-byte swizzle)
 //   warp 1      tcgen05.mma issuer: S = Q K^T into tensor memory, later O_blk = P V
-//   warps 2-5   one query row per thread: S from tensor memory, bias + mask, online softmax in base 2,
-//               P (bf16) into swizzled shared memory as the A operand of the second MMA, O accumulated in registers
+//   warps 2-9   two threads per query row (64 keys and half of the output columns each): S from tensor memory,
+//               bias + mask, online softmax in base 2, P (bf16) into swizzled shared memory as the A operand of the
+//               second MMA, O accumulated in registers; the pair exchanges row maximum and row sum through shared memory
 // Every wait is bounded; a wait that runs out records a df3::Status code and the CTA leaves cleanly.
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
@@ -31,7 +33,8 @@ namespace {
 constexpr int BQ = 128;   // queries per CTA
 constexpr int BKEY = 128; // keys per block
 constexpr int kTileBytes = 128 * 128;  // 128 rows x 128 bytes (64 bf16): Q, K or V tile
-constexpr int kThreads = 192;
+constexpr int kThreads = 320;         // TMA warp, MMA warp, eight softmax warps
+constexpr int kSoftmaxThreads = 256;
 constexpr float kLog2e = 1.4426950408889634f;
 
 struct AttnParams {
@@ -92,25 +95,32 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
 __host__ __device__ constexpr uint32_t idesc_pv(int m, int n) { return ptx::idesc_bf16_f32(m, n) | (1u << 16); }
 
 template <int DN>  // head width rounded up to 16: 16, 32, 48 or 64
-__global__ void __launch_bounds__(kThreads) attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ,
-                                                                const __grid_constant__ CUtensorMap tmK,
-                                                                const __grid_constant__ CUtensorMap tmV, AttnParams p) {
+__global__ void __launch_bounds__(kThreads, 2) attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ,
+                                                                   const __grid_constant__ CUtensorMap tmK,
+                                                                   const __grid_constant__ CUtensorMap tmV, AttnParams p) {
+  // shared memory: Q | K stage 0 | K stage 1 | V | P (two 64-key atoms) | barriers | key term | row exchange
   extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* q_s = smem;
-  uint8_t* kv_s = smem + kTileBytes;                 // stage s: K at 2 s, V at 2 s + 1 tiles
-  uint8_t* p_s = smem + 5 * kTileBytes;              // 128 x 128 bf16: two 64-key atoms of 16 KiB
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 7 * kTileBytes);
+  uint8_t* k_s = smem + kTileBytes;                  // two stages
+  uint8_t* v_s = smem + 3 * kTileBytes;              // one stage: V of block j + 1 is fetched while softmax j + 1 runs
+  uint8_t* p_s = smem + 4 * kTileBytes;              // 128 x 128 bf16: two 64-key atoms of 16 KiB
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 6 * kTileBytes);
   uint64_t* q_full = bars;
-  uint64_t* kv_full = bars + 1;   // [2]
-  uint64_t* kv_empty = bars + 3;  // [2]
-  uint64_t* s_ready = bars + 5;
-  uint64_t* p_ready = bars + 6;
-  uint64_t* o_ready = bars + 7;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
-  // one copy for the four softmax warps: each warp writes all 128 (identical) values itself before it reads them,
+  uint64_t* k_full = bars + 1;    // [2]
+  uint64_t* k_empty = bars + 3;   // [2]
+  uint64_t* v_full = bars + 5;
+  uint64_t* v_empty = bars + 6;
+  uint64_t* s_ready = bars + 7;
+  uint64_t* p_ready = bars + 8;
+  uint64_t* o_ready = bars + 9;
+  uint64_t* x_ready = bars + 10;  // [2]: row-maximum exchange between the two threads of a row, by block parity
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+  // one copy for the eight softmax warps: each warp writes all 128 (identical) values itself before it reads them,
   // and no warp starts the next key block before every warp has finished reading this one (o_ready follows p_ready)
-  float* key_add = reinterpret_cast<float*>(bars + 10);  // [128]
+  float* key_add = reinterpret_cast<float*>(bars + 16);  // [128]
+  float* xchg = key_add + 128;                           // [2 parities][2 halves][128 rows]
   constexpr uint32_t kTmemCols = 256;  // S: columns [0, 128), O block: [128, 128 + DN)
+  constexpr int DH = DN / 2;           // output columns per thread
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   int idx = blockIdx.x;
@@ -127,11 +137,14 @@ __global__ void __launch_bounds__(kThreads) attention_fwd_kernel(const __grid_co
   if (threadIdx.x == 0) {
     ptx::mbar_init(q_full, 1);
     for (int s = 0; s < 2; ++s) {
-      ptx::mbar_init(&kv_full[s], 1);
-      ptx::mbar_init(&kv_empty[s], 1);
+      ptx::mbar_init(&k_full[s], 1);
+      ptx::mbar_init(&k_empty[s], 1);
+      ptx::mbar_init(&x_ready[s], kSoftmaxThreads);
     }
+    ptx::mbar_init(v_full, 1);
+    ptx::mbar_init(v_empty, 1);
     ptx::mbar_init(s_ready, 1);
-    ptx::mbar_init(p_ready, 128);
+    ptx::mbar_init(p_ready, kSoftmaxThreads);
     ptx::mbar_init(o_ready, 1);
     ptx::fence_barrier_init();
   }
@@ -152,20 +165,25 @@ __global__ void __launch_bounds__(kThreads) attention_fwd_kernel(const __grid_co
       ptx::prefetch_tensormap(&tmV);
       ptx::mbar_expect_tx(q_full, kTileBytes);
       tma_load_5d(q_s, &tmQ, q_full, 0, qt * BQ, h, r, b);
-      int issued = 0;
+      int k_issued = 0, v_issued = 0;
       bool ok = true;
       for (int j = 0; j < nb; ++j) {
         const int s = j & 1;
-        if (!ptx::mbar_wait(&kv_empty[s], (uint32_t)((j >> 1) & 1) ^ 1u, p.status, kTimeoutStageEmpty)) { ok = false; break; }
-        ptx::mbar_expect_tx(&kv_full[s], 2 * kTileBytes);
-        tma_load_5d(kv_s + (2 * s) * kTileBytes, &tmK, &kv_full[s], 0, j * BKEY, h, r, b);
-        tma_load_5d(kv_s + (2 * s + 1) * kTileBytes, &tmV, &kv_full[s], 0, j * BKEY, h, r, b);
-        issued = j + 1;
+        if (!ptx::mbar_wait(&k_empty[s], (uint32_t)((j >> 1) & 1) ^ 1u, p.status, kTimeoutStageEmpty)) { ok = false; break; }
+        ptx::mbar_expect_tx(&k_full[s], kTileBytes);
+        tma_load_5d(k_s + s * kTileBytes, &tmK, &k_full[s], 0, j * BKEY, h, r, b);
+        k_issued = j + 1;
+        if (!ptx::mbar_wait(v_empty, (uint32_t)(j & 1) ^ 1u, p.status, kTimeoutStageEmpty)) { ok = false; break; }
+        ptx::mbar_expect_tx(v_full, kTileBytes);
+        tma_load_5d(v_s, &tmV, v_full, 0, j * BKEY, h, r, b);
+        v_issued = j + 1;
       }
       if (!ok) {  // let copies in flight land before shared memory is released
         for (int i = 0; i < (1 << 20) && !ptx::mbar_try_wait(q_full, 0); ++i) {}
-        for (int j = issued > 2 ? issued - 2 : 0; j < issued; ++j)
-          for (int i = 0; i < (1 << 20) && !ptx::mbar_try_wait(&kv_full[j & 1], (uint32_t)(j >> 1) & 1u); ++i) {}
+        for (int j = k_issued > 2 ? k_issued - 2 : 0; j < k_issued; ++j)
+          for (int i = 0; i < (1 << 20) && !ptx::mbar_try_wait(&k_full[j & 1], (uint32_t)(j >> 1) & 1u); ++i) {}
+        if (v_issued > 0)
+          for (int i = 0; i < (1 << 20) && !ptx::mbar_try_wait(v_full, (uint32_t)(v_issued - 1) & 1u); ++i) {}
       }
     }
   } else if (warp == 1) {
@@ -174,23 +192,24 @@ __global__ void __launch_bounds__(kThreads) attention_fwd_kernel(const __grid_co
       constexpr uint32_t idesc_o = idesc_pv(BQ, DN);
       const uint64_t q_desc = ptx::smem_desc_k_sw128(ptx::smem_u32(q_s));
       const uint64_t p_desc = ptx::smem_desc_k_sw128(ptx::smem_u32(p_s));
+      const uint64_t v_desc = smem_desc_mn_sw128(ptx::smem_u32(v_s));
       auto issue_s = [&](int j) -> bool {
         const int s = j & 1;
-        if (!ptx::mbar_wait(&kv_full[s], (uint32_t)(j >> 1) & 1u, p.status, kTimeoutTmaFull)) return false;
+        if (!ptx::mbar_wait(&k_full[s], (uint32_t)(j >> 1) & 1u, p.status, kTimeoutTmaFull)) return false;
         ptx::tc_fence_after();
-        const uint64_t k_desc = ptx::smem_desc_k_sw128(ptx::smem_u32(kv_s + (2 * s) * kTileBytes));
+        const uint64_t k_desc = ptx::smem_desc_k_sw128(ptx::smem_u32(k_s + s * kTileBytes));
 #pragma unroll
         for (int kk = 0; kk < DN / 16; ++kk) ptx::umma_bf16(tmem_s, q_desc + 2 * kk, k_desc + 2 * kk, idesc_s, kk != 0);
         ptx::umma_commit(s_ready);
+        ptx::umma_commit(&k_empty[s]);
         return true;
       };
       bool ok = ptx::mbar_wait(q_full, 0, p.status, kTimeoutTmaFull);
       if (ok) ok = issue_s(0);
       for (int j = 0; ok && j < nb; ++j) {
-        const int s = j & 1;
         if (!ptx::mbar_wait(p_ready, (uint32_t)j & 1u, p.status, kTimeoutMmaDone)) break;
+        if (!ptx::mbar_wait(v_full, (uint32_t)j & 1u, p.status, kTimeoutTmaFull)) break;
         ptx::tc_fence_after();
-        const uint64_t v_desc = smem_desc_mn_sw128(ptx::smem_u32(kv_s + (2 * s + 1) * kTileBytes));
 #pragma unroll
         for (int kk = 0; kk < BKEY / 16; ++kk) {
           // P: keys 16 kk .. 16 kk + 15 sit in atom kk / 4 (16 KiB apart) at byte 32 (kk % 4) of each row;
@@ -199,12 +218,15 @@ __global__ void __launch_bounds__(kThreads) attention_fwd_kernel(const __grid_co
           ptx::umma_bf16(tmem_o, pa, v_desc + (uint64_t)(kk * (2048 >> 4)), idesc_o, kk != 0);
         }
         ptx::umma_commit(o_ready);
-        ptx::umma_commit(&kv_empty[s]);
+        ptx::umma_commit(v_empty);
         if (j + 1 < nb) ok = issue_s(j + 1);
       }
     }
   } else {
+    // two threads per query row: warps 2-5 take keys [0, 64) of each block and output columns [0, DN/2),
+    // warps 6-9 the other halves; the pair meets through shared memory for the row maximum and the row sum
     const int qd = warp & 3;                 // tensor-memory lane quarter of this warp
+    const int half = (warp - 2) >> 2;
     const int row_in_tile = qd * 32 + lane;
     const int i = qt * BQ + row_in_tile;     // query index
     const bool row_ok = i < p.N;
@@ -215,16 +237,14 @@ __global__ void __launch_bounds__(kThreads) attention_fwd_kernel(const __grid_co
       bias_row = reinterpret_cast<const uint8_t*>(p.bias) +
                  (b * p.bias_sb + h * p.bias_sh + (long long)i * p.bias_si) * (p.bias_is_bf16 ? 2 : 4);
     float m_run = -INFINITY, l_run = 0.f;
-    float o_acc[DN];
+    float o_acc[DH];
 #pragma unroll
-    for (int d = 0; d < DN; ++d) o_acc[d] = 0.f;
-    // this row's 128-byte lines inside each P atom: 8-row groups are 1024 bytes, chunks XOR-swizzled by the row
-    uint8_t* p_row = p_s + (row_in_tile >> 3) * 1024 + (row_in_tile & 7) * 128;
+    for (int d = 0; d < DH; ++d) o_acc[d] = 0.f;
+    // this row's 128-byte line inside this thread's P atom: 8-row groups are 1024 bytes, chunks XOR-swizzled by the row
+    uint8_t* p_row = p_s + half * 16384 + (row_in_tile >> 3) * 1024 + (row_in_tile & 7) * 128;
     const int swz = row_in_tile & 7;
     bool ok = true;
-    constexpr bool kPair = false;  // pairing measured slower (367 vs 326 us on the triangle shape): kept for reference
     float v[32];
-    float v2[kPair ? 32 : 1];
     for (int j = 0; j < nb && ok; ++j) {
       if (!ptx::mbar_wait(s_ready, (uint32_t)j & 1u, p.status, kTimeoutMmaDone)) { ok = false; break; }
       ptx::tc_fence_after();
@@ -242,14 +262,17 @@ __global__ void __launch_bounds__(kThreads) attention_fwd_kernel(const __grid_co
       }
       plain_block = __all_sync(0xffffffffu, plain_block);
       __syncwarp();
-      // pass 1: logits in base 2 with bias and mask, row maximum; logits parked back in tensor memory.
-      // kPair: two 32-column chunks per tensor-memory round trip (more loads in flight; the registers allow it for DN <= 32)
-      float m_new = m_run;
-      auto logits_chunk = [&](float* vv, int c) {
+      // pass 1: logits in base 2 with bias and mask, maximum over this thread's 64 keys; logits parked back in tensor memory
+      float m_half = -INFINITY;
+#pragma unroll 1
+      for (int cc = 0; cc < 2; ++cc) {
+        const int c = 2 * half + cc;
+        ptx::tmem_ld_32x32(tmem_s + lane_off + c * 32, v);
+        ptx::tmem_ld_wait();
         const int kbase = key0 + c * 32;
         if (bias_row == nullptr) {
 #pragma unroll
-          for (int t = 0; t < 32; ++t) vv[t] = vv[t] * p.scale_log2;
+          for (int t = 0; t < 32; ++t) v[t] = v[t] * p.scale_log2;
         } else if (p.bias_is_bf16 && kbase + 32 <= p.N && ((reinterpret_cast<uintptr_t>(bias_row) + 2 * kbase) & 15) == 0) {
           const uint4* src = reinterpret_cast<const uint4*>(bias_row + 2 * kbase);
 #pragma unroll
@@ -259,8 +282,8 @@ __global__ void __launch_bounds__(kThreads) attention_fwd_kernel(const __grid_co
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
               const __nv_bfloat162 pr = *reinterpret_cast<const __nv_bfloat162*>(&ww[e]);
-              vv[g * 8 + 2 * e] = vv[g * 8 + 2 * e] * p.scale_log2 + __low2float(pr) * kLog2e;
-              vv[g * 8 + 2 * e + 1] = vv[g * 8 + 2 * e + 1] * p.scale_log2 + __high2float(pr) * kLog2e;
+              v[g * 8 + 2 * e] = v[g * 8 + 2 * e] * p.scale_log2 + __low2float(pr) * kLog2e;
+              v[g * 8 + 2 * e + 1] = v[g * 8 + 2 * e + 1] * p.scale_log2 + __high2float(pr) * kLog2e;
             }
           }
         } else {
@@ -271,77 +294,51 @@ __global__ void __launch_bounds__(kThreads) attention_fwd_kernel(const __grid_co
             if (key < p.N)
               add = p.bias_is_bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(bias_row)[key])
                                    : reinterpret_cast<const float*>(bias_row)[key];
-            vv[t] = vv[t] * p.scale_log2 + add * kLog2e;
+            v[t] = v[t] * p.scale_log2 + add * kLog2e;
           }
         }
         if (plain_block) {
 #pragma unroll
-          for (int t = 0; t < 32; ++t) m_new = fmaxf(m_new, vv[t]);
+          for (int t = 0; t < 32; ++t) m_half = fmaxf(m_half, v[t]);
         } else {
 #pragma unroll
           for (int t = 0; t < 32; ++t) {
-            vv[t] += key_add[c * 32 + t];
-            m_new = fmaxf(m_new, vv[t]);
+            v[t] += key_add[c * 32 + t];
+            m_half = fmaxf(m_half, v[t]);
           }
         }
-      };
-      if (kPair) {
-#pragma unroll 1
-        for (int c = 0; c < 4; c += 2) {
-          ptx::tmem_ld_32x32(tmem_s + lane_off + c * 32, v);
-          ptx::tmem_ld_32x32(tmem_s + lane_off + (c + 1) * 32, v2);
-          ptx::tmem_ld_wait();
-          logits_chunk(v, c);
-          logits_chunk(v2, c + 1);
-          tmem_st_32x32(tmem_s + lane_off + c * 32, v);
-          tmem_st_32x32(tmem_s + lane_off + (c + 1) * 32, v2);
-        }
-      } else {
-#pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
-          ptx::tmem_ld_32x32(tmem_s + lane_off + c * 32, v);
-          ptx::tmem_ld_wait();
-          logits_chunk(v, c);
-          tmem_st_32x32(tmem_s + lane_off + c * 32, v);
-        }
+        tmem_st_32x32(tmem_s + lane_off + c * 32, v);
       }
+      // the row maximum needs the other half of the row
+      float* x_mine = xchg + ((j & 1) * 2 + half) * 128 + row_in_tile;
+      const float* x_other = xchg + ((j & 1) * 2 + (half ^ 1)) * 128 + row_in_tile;
+      *x_mine = m_half;
+      ptx::mbar_arrive(&x_ready[j & 1]);
       tmem_st_wait();
+      if (!ptx::mbar_wait(&x_ready[j & 1], (uint32_t)(j >> 1) & 1u, p.status, kTimeoutMmaDone)) { ok = false; break; }
+      const float m_new = fmaxf(m_run, fmaxf(m_half, *x_other));
       const float alpha = exp2f(m_run - m_new);  // 0 on the first block
       float l_blk = 0.f;
-      // pass 2: probabilities, row sum, P as bf16 into the swizzled A-operand tile
-      auto probs_chunk = [&](float* vv, int c) {
+      // pass 2: probabilities, partial row sum, P as bf16 into this thread's 64-key atom of the A-operand tile
+#pragma unroll 1
+      for (int cc = 0; cc < 2; ++cc) {
+        const int c = 2 * half + cc;
+        ptx::tmem_ld_32x32(tmem_s + lane_off + c * 32, v);
+        ptx::tmem_ld_wait();
 #pragma unroll
         for (int t = 0; t < 32; ++t) {
-          vv[t] = exp2f(vv[t] - m_new);
-          l_blk += vv[t];
+          v[t] = exp2f(v[t] - m_new);
+          l_blk += v[t];
         }
-        uint8_t* atom = p_row + (c >> 1) * 16384;
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
-          const int chunk = (c & 1) * 4 + g;  // 16-byte chunk inside the 128-byte line
+          const int chunk = cc * 4 + g;  // 16-byte chunk inside the 128-byte line
           uint4 w;
-          w.x = pack2(vv[g * 8 + 0], vv[g * 8 + 1]);
-          w.y = pack2(vv[g * 8 + 2], vv[g * 8 + 3]);
-          w.z = pack2(vv[g * 8 + 4], vv[g * 8 + 5]);
-          w.w = pack2(vv[g * 8 + 6], vv[g * 8 + 7]);
-          *reinterpret_cast<uint4*>(atom + ((chunk ^ swz) << 4)) = w;
-        }
-      };
-      if (kPair) {
-#pragma unroll 1
-        for (int c = 0; c < 4; c += 2) {
-          ptx::tmem_ld_32x32(tmem_s + lane_off + c * 32, v);
-          ptx::tmem_ld_32x32(tmem_s + lane_off + (c + 1) * 32, v2);
-          ptx::tmem_ld_wait();
-          probs_chunk(v, c);
-          probs_chunk(v2, c + 1);
-        }
-      } else {
-#pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
-          ptx::tmem_ld_32x32(tmem_s + lane_off + c * 32, v);
-          ptx::tmem_ld_wait();
-          probs_chunk(v, c);
+          w.x = pack2(v[g * 8 + 0], v[g * 8 + 1]);
+          w.y = pack2(v[g * 8 + 2], v[g * 8 + 3]);
+          w.z = pack2(v[g * 8 + 4], v[g * 8 + 5]);
+          w.w = pack2(v[g * 8 + 6], v[g * 8 + 7]);
+          *reinterpret_cast<uint4*>(p_row + ((chunk ^ swz) << 4)) = w;
         }
       }
       l_run = l_run * alpha + l_blk;
@@ -352,27 +349,34 @@ __global__ void __launch_bounds__(kThreads) attention_fwd_kernel(const __grid_co
       if (!ptx::mbar_wait(o_ready, (uint32_t)j & 1u, p.status, kTimeoutMmaDone)) { ok = false; break; }
       ptx::tc_fence_after();
 #pragma unroll
-      for (int c = 0; c < DN / 16; ++c) {
-        // 16 columns at a time keeps the register count independent of DN
-        float t16[16];
-        uint32_t* rr = reinterpret_cast<uint32_t*>(t16);
+      for (int c = 0; c < DH / 8; ++c) {
+        float t8[8];
+        uint32_t* rr = reinterpret_cast<uint32_t*>(t8);
         asm volatile(
-            "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-            : "=r"(rr[0]), "=r"(rr[1]), "=r"(rr[2]), "=r"(rr[3]), "=r"(rr[4]), "=r"(rr[5]), "=r"(rr[6]), "=r"(rr[7]),
-              "=r"(rr[8]), "=r"(rr[9]), "=r"(rr[10]), "=r"(rr[11]), "=r"(rr[12]), "=r"(rr[13]), "=r"(rr[14]), "=r"(rr[15])
-            : "r"(tmem_o + lane_off + c * 16));
+            "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+            : "=r"(rr[0]), "=r"(rr[1]), "=r"(rr[2]), "=r"(rr[3]), "=r"(rr[4]), "=r"(rr[5]), "=r"(rr[6]), "=r"(rr[7])
+            : "r"(tmem_o + lane_off + half * DH + c * 8));
         ptx::tmem_ld_wait();
 #pragma unroll
-        for (int t = 0; t < 16; ++t) o_acc[c * 16 + t] = o_acc[c * 16 + t] * alpha + t16[t];
+        for (int t = 0; t < 8; ++t) o_acc[c * 8 + t] = o_acc[c * 8 + t] * alpha + t8[t];
       }
+    }
+    // total row sum: one more exchange through the slot of the parity after the last block
+    if (ok) {
+      const int par = nb & 1;
+      xchg[(par * 2 + half) * 128 + row_in_tile] = l_run;
+      ptx::mbar_arrive(&x_ready[par]);
+      ok = ptx::mbar_wait(&x_ready[par], (uint32_t)(nb >> 1) & 1u, p.status, kTimeoutMmaDone);
+      if (ok) l_run += xchg[(par * 2 + (half ^ 1)) * 128 + row_in_tile];
     }
     if (ok && row_ok) {
       const float inv = 1.f / l_run;
-      __nv_bfloat16* dst = p.out + b * p.o_sb + r * p.o_sr + h * p.o_sh + (long long)i * p.o_sn;
+      const int d0 = half * DH;
+      __nv_bfloat16* dst = p.out + b * p.o_sb + r * p.o_sr + h * p.o_sh + (long long)i * p.o_sn + d0;
       if ((p.D & 7) == 0 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
 #pragma unroll
-        for (int g = 0; g < DN / 8; ++g) {
-          if (g * 8 < p.D) {
+        for (int g = 0; g < DH / 8; ++g) {
+          if (d0 + g * 8 < p.D) {
             uint4 w;
             w.x = pack2(o_acc[g * 8 + 0] * inv, o_acc[g * 8 + 1] * inv);
             w.y = pack2(o_acc[g * 8 + 2] * inv, o_acc[g * 8 + 3] * inv);
@@ -383,10 +387,10 @@ __global__ void __launch_bounds__(kThreads) attention_fwd_kernel(const __grid_co
         }
       } else {
 #pragma unroll
-        for (int d = 0; d < DN; ++d)
-          if (d < p.D) dst[d] = __float2bfloat16_rn(o_acc[d] * inv);
+        for (int d = 0; d < DH; ++d)
+          if (d0 + d < p.D) dst[d] = __float2bfloat16_rn(o_acc[d] * inv);
       }
-      if (p.lse) {
+      if (p.lse && half == 0) {
         // kept apart: for a fully masked row the maximum is about -1.4e9, where adding log2(sum) would round away
         const long long at = (((long long)b * p.R + r) * p.H + h) * p.N + i;
         p.lse[at] = m_run;
@@ -624,7 +628,7 @@ std::tuple<Tensor, Tensor> df3_attention_fwd(const Tensor& q_in, const Tensor& k
   const CUtensorMap tq = qkv_map(q), tk = qkv_map(k), tv = qkv_map(v);
   const long long ctas = (long long)B * R * H * p.q_tiles;
   TORCH_CHECK(ctas < (1ll << 31), "attention: grid too large");
-  const size_t smem = 7 * kTileBytes + 128 + 512;
+  const size_t smem = 6 * kTileBytes + 128 + 512 + 2048;
   cudaStream_t stream = at::cuda::getCurrentCUDAStream();
   const int dn = (int)((D + 15) / 16 * 16);
 #define DF3_ATTN(DN_)                                                                                               \
