@@ -49,6 +49,7 @@ struct AttnParams {
   int B, R, H, N, D;
   int q_tiles;
   int bias_is_bf16;
+  int bias_tma;            // bias tiles are staged through shared memory by TMA (bf16, contiguous keys, N % 8 == 0)
   float scale_log2;        // scale * log2(e)
 };
 
@@ -69,6 +70,13 @@ __device__ __forceinline__ void tma_load_5d(void* smem_dst, const CUtensorMap* m
   asm volatile(
       "cp.async.bulk.tensor.5d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
       ::"r"(ptx::smem_u32(smem_dst)), "l"((uint64_t)map), "r"(ptx::smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
+      : "memory");
+}
+
+__device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(ptx::smem_u32(smem_dst)), "l"((uint64_t)map), "r"(ptx::smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
       : "memory");
 }
 
@@ -97,7 +105,8 @@ __host__ __device__ constexpr uint32_t idesc_pv(int m, int n) { return ptx::ides
 template <int DN>  // head width rounded up to 16: 16, 32, 48 or 64
 __global__ void __launch_bounds__(kThreads, 2) attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ,
                                                                    const __grid_constant__ CUtensorMap tmK,
-                                                                   const __grid_constant__ CUtensorMap tmV, AttnParams p) {
+                                                                   const __grid_constant__ CUtensorMap tmV,
+                                                                   const __grid_constant__ CUtensorMap tmBias, AttnParams p) {
   // shared memory: Q | K stage 0 | K stage 1 | V | P (two 64-key atoms) | barriers | key term | row exchange
   extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* q_s = smem;
@@ -114,6 +123,8 @@ __global__ void __launch_bounds__(kThreads, 2) attention_fwd_kernel(const __grid
   uint64_t* p_ready = bars + 8;
   uint64_t* o_ready = bars + 9;
   uint64_t* x_ready = bars + 10;  // [2]: row-maximum exchange between the two threads of a row, by block parity
+  uint64_t* bias_full = bars + 13;  // the bias tile of the next block sits in the P buffer (each thread reads its own
+                                    // 128 bytes in pass 1 and overwrites exactly those with P in pass 2)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
   // one copy for the eight softmax warps: each warp writes all 128 (identical) values itself before it reads them,
   // and no warp starts the next key block before every warp has finished reading this one (o_ready follows p_ready)
@@ -146,6 +157,7 @@ __global__ void __launch_bounds__(kThreads, 2) attention_fwd_kernel(const __grid
     ptx::mbar_init(s_ready, 1);
     ptx::mbar_init(p_ready, kSoftmaxThreads);
     ptx::mbar_init(o_ready, 1);
+    ptx::mbar_init(bias_full, 1);
     ptx::fence_barrier_init();
   }
   if (warp == 1) {
@@ -165,14 +177,23 @@ __global__ void __launch_bounds__(kThreads, 2) attention_fwd_kernel(const __grid
       ptx::prefetch_tensormap(&tmV);
       ptx::mbar_expect_tx(q_full, kTileBytes);
       tma_load_5d(q_s, &tmQ, q_full, 0, qt * BQ, h, r, b);
-      int k_issued = 0, v_issued = 0;
+      int k_issued = 0, v_issued = 0, bias_issued = 0;
       bool ok = true;
+      if (p.bias_tma) ptx::prefetch_tensormap(&tmBias);
       for (int j = 0; j < nb; ++j) {
         const int s = j & 1;
         if (!ptx::mbar_wait(&k_empty[s], (uint32_t)((j >> 1) & 1) ^ 1u, p.status, kTimeoutStageEmpty)) { ok = false; break; }
         ptx::mbar_expect_tx(&k_full[s], kTileBytes);
         tma_load_5d(k_s + s * kTileBytes, &tmK, &k_full[s], 0, j * BKEY, h, r, b);
         k_issued = j + 1;
+        if (p.bias_tma) {
+          // the P buffer is free once the second MMA of the previous block has finished reading it
+          if (j > 0 && !ptx::mbar_wait(o_ready, (uint32_t)(j - 1) & 1u, p.status, kTimeoutMmaDone)) { ok = false; break; }
+          ptx::mbar_expect_tx(bias_full, 2 * kTileBytes);
+          tma_load_4d(p_s, &tmBias, bias_full, j * BKEY, qt * BQ, h, p.bias_sb ? b : 0);
+          tma_load_4d(p_s + kTileBytes, &tmBias, bias_full, j * BKEY + 64, qt * BQ, h, p.bias_sb ? b : 0);
+          bias_issued = j + 1;
+        }
         if (!ptx::mbar_wait(v_empty, (uint32_t)(j & 1) ^ 1u, p.status, kTimeoutStageEmpty)) { ok = false; break; }
         ptx::mbar_expect_tx(v_full, kTileBytes);
         tma_load_5d(v_s, &tmV, v_full, 0, j * BKEY, h, r, b);
@@ -184,6 +205,8 @@ __global__ void __launch_bounds__(kThreads, 2) attention_fwd_kernel(const __grid
           for (int i = 0; i < (1 << 20) && !ptx::mbar_try_wait(&k_full[j & 1], (uint32_t)(j >> 1) & 1u); ++i) {}
         if (v_issued > 0)
           for (int i = 0; i < (1 << 20) && !ptx::mbar_try_wait(v_full, (uint32_t)(v_issued - 1) & 1u); ++i) {}
+        if (bias_issued > 0)
+          for (int i = 0; i < (1 << 20) && !ptx::mbar_try_wait(bias_full, (uint32_t)(bias_issued - 1) & 1u); ++i) {}
       }
     }
   } else if (warp == 1) {
@@ -262,6 +285,7 @@ __global__ void __launch_bounds__(kThreads, 2) attention_fwd_kernel(const __grid
       }
       plain_block = __all_sync(0xffffffffu, plain_block);
       __syncwarp();
+      if (p.bias_tma && !ptx::mbar_wait(bias_full, (uint32_t)j & 1u, p.status, kTimeoutTmaFull)) { ok = false; break; }
       // pass 1: logits in base 2 with bias and mask, maximum over this thread's 64 keys; logits parked back in tensor memory
       float m_half = -INFINITY;
 #pragma unroll 1
@@ -270,7 +294,19 @@ __global__ void __launch_bounds__(kThreads, 2) attention_fwd_kernel(const __grid
         ptx::tmem_ld_32x32(tmem_s + lane_off + c * 32, v);
         ptx::tmem_ld_wait();
         const int kbase = key0 + c * 32;
-        if (bias_row == nullptr) {
+        if (p.bias_tma) {  // this row's 64 bytes of the staged tile (out-of-range keys were zero-filled)
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            const uint4 w = *reinterpret_cast<const uint4*>(p_row + (((cc * 4 + g) ^ swz) << 4));
+            const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const __nv_bfloat162 pr = *reinterpret_cast<const __nv_bfloat162*>(&ww[e]);
+              v[g * 8 + 2 * e] = v[g * 8 + 2 * e] * p.scale_log2 + __low2float(pr) * kLog2e;
+              v[g * 8 + 2 * e + 1] = v[g * 8 + 2 * e + 1] * p.scale_log2 + __high2float(pr) * kLog2e;
+            }
+          }
+        } else if (bias_row == nullptr) {
 #pragma unroll
           for (int t = 0; t < 32; ++t) v[t] = v[t] * p.scale_log2;
         } else if (p.bias_is_bf16 && kbase + 32 <= p.N && ((reinterpret_cast<uintptr_t>(bias_row) + 2 * kbase) & 15) == 0) {
@@ -626,6 +662,15 @@ std::tuple<Tensor, Tensor> df3_attention_fwd(const Tensor& q_in, const Tensor& k
   p.q_tiles = (int)((N + BQ - 1) / BQ);
   p.scale_log2 = (float)scale * kLog2e;
   const CUtensorMap tq = qkv_map(q), tk = qkv_map(k), tv = qkv_map(v);
+  CUtensorMap tbias = tq;  // placeholder when the bias is not staged by TMA
+  if (p.bias && p.bias_is_bf16 && N % 8 == 0 && bias.stride(3) == 1 && bias.stride(2) % 8 == 0 && bias.stride(1) % 8 == 0 &&
+      (bias.size(0) == 1 || bias.stride(0) % 8 == 0) && reinterpret_cast<uintptr_t>(bias.data_ptr()) % 16 == 0) {
+    const int64_t dims[4] = {N, N, H, bias.size(0)};
+    const int64_t strides[4] = {1, bias.stride(2), bias.stride(1), bias.size(0) > 1 ? bias.stride(0) : H * bias.stride(1)};
+    const int box[4] = {64, 128, 1, 1};
+    tbias = make_map_nd(bias.data_ptr(), 4, dims, strides, box);
+    p.bias_tma = 1;
+  }
   const long long ctas = (long long)B * R * H * p.q_tiles;
   TORCH_CHECK(ctas < (1ll << 31), "attention: grid too large");
   const size_t smem = 6 * kTileBytes + 128 + 512 + 2048;
@@ -638,7 +683,7 @@ std::tuple<Tensor, Tensor> df3_attention_fwd(const Tensor& q_in, const Tensor& k
       C10_CUDA_CHECK(cudaFuncSetAttribute(attention_fwd_kernel<DN_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
       attr = true;                                                                                                  \
     }                                                                                                               \
-    attention_fwd_kernel<DN_><<<(unsigned)ctas, kThreads, smem, stream>>>(tq, tk, tv, p);                           \
+    attention_fwd_kernel<DN_><<<(unsigned)ctas, kThreads, smem, stream>>>(tq, tk, tv, tbias, p);                           \
   } while (0)
   if (dn == 16) DF3_ATTN(16); else if (dn == 32) DF3_ATTN(32); else if (dn == 48) DF3_ATTN(48); else DF3_ATTN(64);
 #undef DF3_ATTN
