@@ -22,57 +22,17 @@ replays). Used only without autograd; ``DF3_GRAPH_SAMPLER=0`` switches it off.
 from __future__ import annotations
 
 import collections
-import dataclasses
 import os
 
 import torch
+
+from ..utils.cuda_graph import tree_map, tree_signature, tree_tensors
 
 MAX_GRAPHS = 3
 
 
 def enabled(example: torch.Tensor) -> bool:
     return example.is_cuda and not torch.is_grad_enabled() and os.environ.get("DF3_GRAPH_SAMPLER", "1") != "0"
-
-
-def tree_map(fn, obj):
-    """Apply ``fn`` to every tensor of a tree of dataclasses / dicts / lists / tuples; other leaves pass through."""
-    if isinstance(obj, torch.Tensor):
-        return fn(obj)
-    if dataclasses.is_dataclass(obj) and not isinstance(obj, type):
-        return dataclasses.replace(obj, **{f.name: tree_map(fn, getattr(obj, f.name)) for f in dataclasses.fields(obj)})
-    if isinstance(obj, dict):
-        return {k: tree_map(fn, v) for k, v in obj.items()}
-    if isinstance(obj, (list, tuple)):
-        return type(obj)(tree_map(fn, v) for v in obj)
-    return obj
-
-
-def tree_tensors(obj) -> list:
-    out: list = []
-    tree_map(lambda t: out.append(t) or t, obj)
-    return out
-
-
-def tree_signature(obj) -> tuple:
-    sig: list = []
-
-    def visit(o):
-        if isinstance(o, torch.Tensor):
-            sig.append((tuple(o.shape), o.dtype, tuple(o.stride())))
-        elif dataclasses.is_dataclass(o) and not isinstance(o, type):
-            for f in dataclasses.fields(o):
-                visit(getattr(o, f.name))
-        elif isinstance(o, dict):
-            for k in o:
-                visit(o[k])
-        elif isinstance(o, (list, tuple)):
-            for v in o:
-                visit(v)
-        else:
-            sig.append(o if isinstance(o, (int, float, bool, str, type(None))) else type(o).__name__)
-
-    visit(obj)
-    return tuple(sig)
 
 
 class GraphedDenoiser:

@@ -46,6 +46,6 @@ def create_relative_encoding(
 def dgram_from_positions(positions, min_bin=DGRAM_MIN_BIN, max_bin=DGRAM_MAX_BIN, num_bins=DGRAM_NUM_BINS):
     """One-hot histogram ``[..., N, N, num_bins]`` of pairwise squared distances between bin edges."""
     lower = torch.linspace(min_bin, max_bin, num_bins, device=positions.device) ** 2
-    upper = torch.cat([lower[1:], lower.new_tensor([1e8])])
+    upper = torch.cat([lower[1:], torch.full((1,), 1e8, device=positions.device, dtype=lower.dtype)])  # no host copy
     d2 = (positions.unsqueeze(-2) - positions.unsqueeze(-3)).pow(2).sum(-1, keepdim=True)
     return ((d2 > lower) & (d2 < upper)).float()

@@ -9,6 +9,7 @@ from __future__ import annotations
 
 import dataclasses
 from collections.abc import Sequence
+import os
 from contextlib import nullcontext
 
 import torch
@@ -17,6 +18,7 @@ import torch.nn.functional as F
 from torch.utils.checkpoint import checkpoint
 
 from ..config.schema import DistogramConfig, ModelConfig, OptimConfig
+from ..utils.cuda_graph import GraphCache
 from .atom_attention import EvoformerConditioningEncoder
 from .confidence import ConfidenceHead
 from .diffusion import DiffusionHead, GuidanceTerm
@@ -195,6 +197,12 @@ class DeepFold3(nn.Module):
                 mask = mask * active.view(*shape)
         return msa, mask, dele
 
+    def _graph_trunk(self, dev) -> bool:
+        if dev.type != "cuda" or torch.is_grad_enabled() or os.environ.get("DF3_GRAPH_TRUNK", "1") == "0":
+            return False
+        meter = getattr(self.evoformer, "_act_meter", None)
+        return not (meter is not None and getattr(meter, "enabled", False))
+
     def run_evoformer(self, features, num_recycles, seed=0, msa_precropped=False, crop_offset=0, mask_msa=False):
         """Feature building + ``num_recycles + 1`` trunk passes.
 
@@ -269,11 +277,17 @@ class DeepFold3(nn.Module):
                 gen = torch.Generator(device=dev).manual_seed(int(seed) + r + 0x5EED)
                 msa, true_msa, hit = apply_bert_mask(msa, msa_mask, features.get("profile"), self.cfg.masked_msa, gen)
                 bert = (true_msa, hit, msa_mask)
-            embeddings = self.evoformer(
+            trunk_in = dict(
                 target_feat=target_feat, msa_feat=self._build_msa_feat_from_tensors(msa, dele), rel_feat=rel_feat,
                 pair_mask=pair_mask, seq_mask=seq_mask, msa_mask=msa_mask.float(), prev_pair=prev_pair,
                 prev_single=prev_single, bond_matrix=bond_matrix, multichain_mask=multichain_mask, **tmpl,
             )  # fmt: skip
+            if self._graph_trunk(dev):
+                # no autograd on this pass: replay the whole trunk from a CUDA graph (captured once per shape)
+                graphs = self.__dict__.setdefault("_trunk_graphs", GraphCache(max_graphs=2))
+                embeddings = graphs.run(self.evoformer, trunk_in)
+            else:
+                embeddings = self.evoformer(**trunk_in)
             if r < num_recycles:
                 prev_pair, prev_single = embeddings["pair"].detach(), embeddings["single"].detach()
         if bert is not None:

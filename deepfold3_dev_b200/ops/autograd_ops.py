@@ -106,19 +106,27 @@ class _DropoutAdd(torch.autograd.Function):
         xc = x.contiguous()
         A, B, C = xc.shape[-3], xc.shape[-2], xc.shape[-1]
         ctx.meta = (A, B, C, share_rows, p, seed)
-        return K.dropout_shared(residual.contiguous(), xc, A, B, C, share_rows, p, seed)
+        return K.dropout_shared(residual.contiguous(), xc, A, B, C, share_rows, p, seed, None)
 
     @staticmethod
     def backward(ctx, dy):
         A, B, C, share_rows, p, seed = ctx.meta
         dyc = dy.contiguous()
-        return dyc, K.dropout_shared(None, dyc, A, B, C, share_rows, p, seed), None, None, None
+        return dyc, K.dropout_shared(None, dyc, A, B, C, share_rows, p, seed, None), None, None, None
 
 
 def dropout_add(residual, x, p: float, share_dim: int, seed: int | None = None):
     """``residual + dropout(x)`` with the draw shared along ``share_dim`` (-3 rows, -2 columns)."""
     if share_dim not in (-3, -2):
         raise ValueError("share_dim must be -3 or -2")
+    from ..utils.cuda_graph import GraphSeed
+
+    gs = GraphSeed.current
+    if gs is not None and seed is None and not torch.is_grad_enabled():
+        # inside a region that is captured into a CUDA graph: the base seed lives on the device and is refreshed per replay
+        xc = x.contiguous()
+        return K.dropout_shared(residual.contiguous(), xc, xc.shape[-3], xc.shape[-2], xc.shape[-1], share_dim == -3, float(p),
+                                gs.offset(), gs.tensor)  # fmt: skip
     if seed is None:
         seed = next_mask_seed()
     return _DropoutAdd.apply(residual, x, float(p), share_dim == -3, int(seed))

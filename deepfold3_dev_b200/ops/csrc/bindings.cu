@@ -11,7 +11,8 @@ std::tuple<Tensor, Tensor> df3_layer_norm_bwd(const Tensor&, const Tensor&, cons
 Tensor df3_swiglu_fwd(const Tensor&);
 Tensor df3_swiglu_bwd(const Tensor&, const Tensor&);
 Tensor df3_gated_bwd(const Tensor&, const Tensor&, const c10::optional<Tensor>&);
-Tensor df3_dropout_shared(const c10::optional<Tensor>&, const Tensor&, int64_t, int64_t, int64_t, bool, double, int64_t);
+Tensor df3_dropout_shared(const c10::optional<Tensor>&, const Tensor&, int64_t, int64_t, int64_t, bool, double, int64_t,
+                          const c10::optional<Tensor>&);
 void df3_adamw_ema(Tensor, const Tensor&, Tensor, Tensor, const c10::optional<Tensor>&, const Tensor&, const Tensor&,
                    double, double, double, double, double, double, double, const c10::optional<Tensor>&);
 
@@ -39,7 +40,7 @@ TORCH_LIBRARY(df3, m) {
   m.def("swiglu_fwd(Tensor x) -> Tensor", &df3_swiglu_fwd);
   m.def("swiglu_bwd(Tensor dy, Tensor x) -> Tensor", &df3_swiglu_bwd);
   m.def("gated_bwd(Tensor dy, Tensor gp, Tensor? mask) -> Tensor", &df3_gated_bwd);
-  m.def("dropout_shared(Tensor? res, Tensor x, int A, int B, int C, bool share_rows, float p, int seed) -> Tensor",
+  m.def("dropout_shared(Tensor? res, Tensor x, int A, int B, int C, bool share_rows, float p, int seed, Tensor? seed_dev=None) -> Tensor",
         &df3_dropout_shared);
   m.def("adamw_ema(Tensor(a!) p, Tensor g, Tensor(b!) m, Tensor(c!) v, Tensor? ema, Tensor decay, Tensor scale, "
         "float lr, float b1, float b2, float eps, float bc1, float bc2, float ema_w, Tensor(d!)? p16=None) -> ()",

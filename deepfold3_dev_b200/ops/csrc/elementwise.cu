@@ -222,7 +222,8 @@ __device__ __forceinline__ float drop_scale(const Philox& rng, int64_t mask_idx,
 template <typename T, bool kAdd>
 __global__ void dropout_shared_kernel(const T* __restrict__ res, const T* __restrict__ x, T* __restrict__ out,
                                       int64_t total, int64_t A, int64_t B, int64_t C, bool share_rows, float p,
-                                      uint64_t seed) {
+                                      uint64_t seed, const long long* __restrict__ seed_dev) {
+  if (seed_dev) seed += (uint64_t)*seed_dev;  // base seed kept on the device: a captured launch draws a new mask per replay
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= total) return;
   const int64_t c = i % C, ab = i / C, b = ab % B, oa = ab / B, a = oa % A, o = oa / A;
@@ -255,7 +256,9 @@ template <> struct Vec8<float> {
 template <typename T, bool kAdd, int kSpan>
 __global__ void __launch_bounds__(256) dropout_shared_vec_kernel(const T* __restrict__ res, const T* __restrict__ x,
                                                                  T* __restrict__ out, int64_t O, int64_t A, int64_t B,
-                                                                 int64_t C, bool share_rows, float p, uint64_t seed) {
+                                                                 int64_t C, bool share_rows, float p, uint64_t seed,
+                                                                 const long long* __restrict__ seed_dev) {
+  if (seed_dev) seed += (uint64_t)*seed_dev;
   const int64_t c8n = C / 8;
   const int64_t shared_len = share_rows ? A : B;   // axis the mask is shared along
   const int64_t other_len = share_rows ? B : A;    // axis that indexes the mask together with (o, c)
@@ -494,7 +497,12 @@ Tensor df3_swiglu_bwd(const Tensor& dy, const Tensor& x) {
 
 // x viewed as [outer, A, B, C]; res may be undefined (then out = dropout(x), used by backward)
 Tensor df3_dropout_shared(const c10::optional<Tensor>& res, const Tensor& x, int64_t A, int64_t B, int64_t C,
-                          bool share_rows, double p, int64_t seed) {
+                          bool share_rows, double p, int64_t seed, const c10::optional<Tensor>& seed_dev) {
+  const long long* sd = nullptr;
+  if (seed_dev.has_value() && seed_dev->defined()) {
+    TORCH_CHECK(seed_dev->is_cuda() && seed_dev->scalar_type() == torch::kInt64 && seed_dev->numel() >= 1, "dropout_shared: seed_dev is an int64 CUDA tensor");
+    sd = reinterpret_cast<const long long*>(seed_dev->data_ptr());
+  }
   TORCH_CHECK(x.is_cuda() && x.is_contiguous(), "dropout_shared: contiguous CUDA tensor");
   c10::cuda::CUDAGuard guard(x.device());
   auto out = torch::empty_like(x);
@@ -515,11 +523,11 @@ Tensor df3_dropout_shared(const c10::optional<Tensor>& res, const Tensor& x, int
     if (vec)                                                                                                       \
       df3::dropout_shared_vec_kernel<T, ADD, kSpan><<<vgrid, 256, 0, stream()>>>(                                  \
           ADD ? (const T*)res->data_ptr() : nullptr, (const T*)x.data_ptr(), (T*)out.data_ptr(), O, A, B, C,       \
-          share_rows, (float)p, (uint64_t)seed);                                                                   \
+          share_rows, (float)p, (uint64_t)seed, sd);                                                               \
     else                                                                                                           \
       df3::dropout_shared_kernel<T, ADD><<<grid, 256, 0, stream()>>>(ADD ? (const T*)res->data_ptr() : nullptr,    \
                                                                      (const T*)x.data_ptr(), (T*)out.data_ptr(), n, \
-                                                                     A, B, C, share_rows, (float)p, (uint64_t)seed); \
+                                                                     A, B, C, share_rows, (float)p, (uint64_t)seed, sd); \
   } while (0)
   if (x.scalar_type() == torch::kBFloat16) {
     if (add) DF3_LAUNCH(__nv_bfloat16, true); else DF3_LAUNCH(__nv_bfloat16, false);
