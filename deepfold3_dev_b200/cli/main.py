@@ -272,6 +272,66 @@ def convert(af3_params, output):
     click.echo(f"{len(state)} tensors -> {output}")
 
 
+@cli.command()
+@click.argument("fasta_or_sequence")
+@click.option("--output", type=click.Path(), required=True, help="A3M file to write.")
+@click.option("--db", default=None, help="Local MMseqs2 target database; without it the ColabFold API is used.")
+@click.option("--cache-dir", type=click.Path(), default="~/.cache/deepfold3/msa")
+@click.option("--host", default=None, help="MSA server URL.")
+def msa(fasta_or_sequence, output, db, cache_dir, host):
+    """Search an alignment for one sequence (local mmseqs pipeline or the ColabFold MMseqs2 API)."""
+    from ..data.msa import search
+    from ..data.parse.a3m import read_fasta_like
+
+    seq = fasta_or_sequence
+    if os.path.exists(seq):
+        with open(seq) as f:
+            seq = read_fasta_like(f.read())[1][0]
+    cache = search.MsaCache(os.path.expanduser(cache_dir))
+    a3m = search.search_local(seq, db, cache) if db else search.search_server([seq], cache, host or search.DEFAULT_HOST)[0]
+    with open(output, "w") as f:
+        f.write(a3m)
+    click.echo(f"{a3m.count('>')} rows -> {output}")
+
+
+@cli.command("msa-batch")
+@click.option("--inputs-file", type=click.Path(exists=True), required=True, help="One job JSON per line.")
+@click.option("--output-dir", type=click.Path(), required=True)
+@click.option("--db", default=None)
+@click.option("--cache-dir", type=click.Path(), default="~/.cache/deepfold3/msa")
+def msa_batch(inputs_file, output_dir, db, cache_dir):
+    """Search alignments for every distinct protein sequence of many jobs; writes ``{sha1}.a3m`` per sequence."""
+    import hashlib
+
+    from ..data.msa import search
+    from ..data.parse.json_input import ProteinChainInput, parse_json_input
+
+    os.makedirs(output_dir, exist_ok=True)
+    cache = search.MsaCache(os.path.expanduser(cache_dir))
+    seqs = set()
+    with open(inputs_file) as f:
+        for line in f:
+            if line.strip() and not line.startswith("#"):
+                for job in parse_json_input(line.strip()):
+                    seqs.update(c.sequence for c in job.chains if isinstance(c, ProteinChainInput) and not c.unpaired_msa)
+    for s in sorted(seqs):
+        a3m = search.search_local(s, db, cache) if db else search.search_server([s], cache)[0]
+        with open(os.path.join(output_dir, hashlib.sha1(s.encode()).hexdigest() + ".a3m"), "w") as f:
+            f.write(a3m)
+    click.echo(f"{len(seqs)} sequences searched")
+
+
+@cli.command()
+@click.argument("confidences_json", type=click.Path(exists=True))
+@click.option("--output", type=click.Path(), default=None, help="PNG path (default: next to the JSON).")
+def plot(confidences_json, output):
+    """Plot pLDDT per token and the PAE matrix of one sample."""
+    from ..io.plot import plot_confidences
+
+    path = plot_confidences(confidences_json, output)
+    click.echo(path)
+
+
 @cli.command("bench-kernels")
 @click.option("--op", default="all")
 def bench_kernels(op):

@@ -53,7 +53,7 @@ class InferenceInput:
         return [cls.from_job(job, msa_crop_size=msa_crop_size) for job in parse_json_input(path)]
 
     @classmethod
-    def from_job(cls, job: JobInput, msa_crop_size: int = 16384) -> InferenceInput:
+    def from_job(cls, job: JobInput, msa_crop_size: int = 16384, msa_pairing: str = "auto") -> InferenceInput:
         if job.user_ccd:
             ref_conformers.load_table(job.user_ccd)
         tok: dict[str, list] = {k: [] for k in ("res_type", "mol_type", "asym", "entity", "sym", "res_idx", "atoms")}
@@ -74,7 +74,7 @@ class InferenceInput:
                 chain_names.append(cid)
                 asym += 1
         feats = _token_features(tok)
-        feats.update(_msa_features(feats, chain_cols, chain_msas, msa_crop_size))
+        feats.update(_msa_features(feats, chain_cols, chain_msas, msa_crop_size, msa_pairing))
         return cls(feats, chain_names, job.name, list(job.seeds))
 
 
@@ -168,13 +168,23 @@ def _token_features(tok) -> dict:
     }  # fmt: skip
 
 
-def _msa_features(feats, chain_cols, chains, max_rows: int) -> dict:
+def _msa_features(feats, chain_cols, chains, max_rows: int, msa_pairing: str = "auto") -> dict:
     N = feats["res_type"].shape[0]
     query = feats["res_type"].clone()
     rows, dels = [query.numpy()], [np.zeros(N, dtype=np.int64)]
     # paired rows first (row i of every chain that has a paired alignment), then per-chain blocks
     paired = [(cols, a3m_mod.parse_a3m(c.paired_msa)) for cols, c in zip(chain_cols, chains)
               if getattr(c, "paired_msa", None) and cols[1] - cols[0] == len(getattr(c, "sequence", ""))]  # fmt: skip
+    if len(paired) <= 1 and msa_pairing in ("auto", "species"):
+        # no explicit paired alignments: pair the unpaired ones by species when several distinct chains carry headers
+        cand = [(cols, a3m_mod.parse_a3m(c.unpaired_msa, dedup=False)) for cols, c in zip(chain_cols, chains)
+                if getattr(c, "unpaired_msa", None) and cols[1] - cols[0] == len(getattr(c, "sequence", ""))]  # fmt: skip
+        if len({m.sequences[0] for _, m in cand}) > 1:
+            from .msa.pairing import pair_by_species
+
+            joined, res = pair_by_species([m for _, m in cand], max_rows=min(max_rows, 8191))
+            if len(res.rows) > 1:
+                paired = [(cols, m) for (cols, _), m in zip(cand, joined)]
     if len(paired) > 1:
         depth = min(len(m) for _, m in paired)
         for r in range(1, depth):

@@ -362,3 +362,38 @@ def test_reference_pickled_config_loads_without_the_reference(reference_package,
     out = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, cwd=root, env={**os.environ, "PYTHONPATH": root})
     assert out.returncode == 0, out.stderr[-2000:]
     assert out.stdout.split() == ["deepfold3_dev_b200.config.schema", "7", "[1.0,", "1.0]"]
+
+
+def test_species_pairing_atomisation_masks_and_io_cache(tmp_path):
+    from deepfold3_dev_b200.data import io_cache
+    from deepfold3_dev_b200.data.atomize import atomize_tokens, maybe_atomize
+    from deepfold3_dev_b200.data.masking import TokenMask
+    from deepfold3_dev_b200.data.msa.pairing import pair_by_species, species_id, unpaired_rows_not_in_paired
+
+    a = parse_a3m(">q\nACDE\n>tr|A1|X_HUMAN OX=9606\nACDD\n>tr|A2|X_MOUSE OX=10090\nACEE\n>tr|A3|Y_HUMAN OX=9606\nAADE\n", dedup=False)
+    b = parse_a3m(">q\nKLM\n>tr|B1|Z_MOUSE OX=10090\nKLL\n>tr|B2|Z_HUMAN OX=9606\nKMM\n>tr|B3|Z_RAT OX=10116\nKKK\n", dedup=False)
+    (pa, pb), res = pair_by_species([a, b])
+    assert res.rows.tolist() == [[0, 0], [1, 2], [2, 1]] and res.species == ["query", "9606", "10090"]
+    assert pa.sequences == ["ACDE", "ACDD", "ACEE"] and pb.sequences == ["KLM", "KMM", "KLL"]
+    assert species_id("sp|P1|ABC_YEAST desc") == "YEAST" and species_id(">x") == ""
+    assert unpaired_rows_not_in_paired(a, pa).tolist() == [0, 3]
+    job = {"name": "c", "sequences": [
+        {"protein": {"id": "A", "sequence": "ACDE", "unpairedMsa": ">q\nACDE\n>tr|A1|X_HUMAN OX=9606\nACDD\n>tr|A2|X_MOUSE OX=10090\nACEE\n"}},
+        {"protein": {"id": "B", "sequence": "KLM", "unpairedMsa": ">q\nKLM\n>tr|B1|Z_MOUSE OX=10090\nKLL\n>tr|B2|Z_HUMAN OX=9606\nKMM\n"}}]}  # fmt: skip
+    inp = InferenceInput.from_job(parse_json_input(job)[0])
+    msa = inp.features["msa"]
+    # rows 1-2 are paired across both chains (no gap block), later rows are the per-chain blocks
+    assert not (msa[1] == 21).any() and not (msa[2] == 21).any() and (msa[3, 4:] == 21).all()
+    f = synthetic_complex([("protein", 10)], num_msa=3, num_templates=1, seed=1)
+    g = atomize_tokens(f, torch.tensor([2, 5]))
+    k = int(f["ref_mask"][2].sum() + f["ref_mask"][5].sum())
+    assert g["res_type"].shape[0] == 8 + k and g["msa"].shape == (3, 8 + k) and int(g["ref_mask"].sum()) == int(f["ref_mask"].sum())
+    assert int(g["is_atomized"].sum()) == k and not g["frames_mask"][g["is_atomized"]].any()
+    torch.testing.assert_close(g["atom_gt_positions"][g["is_atomized"], 0][0], f["atom_gt_positions"][2, 0])
+    assert maybe_atomize(f, torch.Generator().manual_seed(0), p_example=0.0) is f
+    tm = TokenMask.fixed_from_chains(np.asarray([0, 0, 1, 1, 2]), [1])
+    assert tm.loss_weight(5).tolist() == [1, 1, 0, 0, 1] and tm.select(np.asarray([2, 4])).get("fixed").tolist() == [True, False]
+    io_cache.set_drop_page_cache(True)
+    np.savez(tmp_path / "x.npz", a=np.arange(4))
+    assert io_cache.read_npz(str(tmp_path / "x.npz"))["a"].tolist() == [0, 1, 2, 3]
+    io_cache.set_drop_page_cache(False)
