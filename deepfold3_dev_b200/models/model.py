@@ -284,8 +284,8 @@ class DeepFold3(nn.Module):
             )  # fmt: skip
             if self._graph_trunk(dev):
                 # no autograd on this pass: replay the whole trunk from a CUDA graph (captured once per shape)
-                graphs = self.__dict__.setdefault("_trunk_graphs", GraphCache(max_graphs=2))
-                embeddings = graphs.run(self.evoformer, trunk_in)
+                graphs = self.__dict__.setdefault("_trunk_graphs", GraphCache(max_graphs=4))
+                embeddings = graphs.run(self.evoformer, trunk_in, mode=self.evoformer.training)
             else:
                 embeddings = self.evoformer(**trunk_in)
             if r < num_recycles:

@@ -545,6 +545,35 @@ void df3_attention_bwd_elem(Tensor s_io, Tensor dp_io, const c10::optional<Tenso
   C10_CUDA_KERNEL_LAUNCH_CHECK();
 }
 
+// delta[b, r, h, n] = sum_d out * d_out, straight from the (strided) bf16 tensors.
+__global__ void attention_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o, float* __restrict__ delta,
+                                       long long o_sb, long long o_sr, long long o_sh, long long o_sn, long long g_sb, long long g_sr,
+                                       long long g_sh, long long g_sn, int R, int H, int N, int D, long long total) {
+  const long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= total) return;
+  const int n = (int)(e % N);
+  const int h = (int)((e / N) % H);
+  const int r = (int)((e / ((long long)N * H)) % R);
+  const long long b = e / ((long long)N * H * R);
+  const __nv_bfloat16* po = o + b * o_sb + r * o_sr + h * o_sh + (long long)n * o_sn;
+  const __nv_bfloat16* pg = d_o + b * g_sb + r * g_sr + h * g_sh + (long long)n * g_sn;
+  float acc = 0.f;
+  if ((D & 7) == 0 && (reinterpret_cast<uintptr_t>(po) & 15) == 0 && (reinterpret_cast<uintptr_t>(pg) & 15) == 0) {
+    for (int d = 0; d < D; d += 8) {
+      const uint4 a = *reinterpret_cast<const uint4*>(po + d), c = *reinterpret_cast<const uint4*>(pg + d);
+      const uint32_t aa[4] = {a.x, a.y, a.z, a.w}, cc[4] = {c.x, c.y, c.z, c.w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const __nv_bfloat162 x = *reinterpret_cast<const __nv_bfloat162*>(&aa[k]), y = *reinterpret_cast<const __nv_bfloat162*>(&cc[k]);
+        acc += __low2float(x) * __low2float(y) + __high2float(x) * __high2float(y);
+      }
+    }
+  } else {
+    for (int d = 0; d < D; ++d) acc += __bfloat162float(po[d]) * __bfloat162float(pg[d]);
+  }
+  delta[e] = acc;
+}
+
 // Whole backward of the attention op: row chunks sized for L2, five library GEMMs and one fused
 // elementwise kernel per chunk. Returns dq, dk, dv as contiguous [B, R, H, N, D] and dbias [Bb, H, N, N] fp32.
 std::tuple<Tensor, Tensor, Tensor, Tensor> df3_attention_bwd(const Tensor& q, const Tensor& k, const Tensor& v,
@@ -557,7 +586,17 @@ std::tuple<Tensor, Tensor, Tensor, Tensor> df3_attention_bwd(const Tensor& q, co
   auto bf = q.options();
   Tensor qc = q.contiguous(), kc = k.contiguous(), vc = v.contiguous();
   Tensor doc = d_out.to(torch::kBFloat16).contiguous();
-  Tensor delta = (doc.to(torch::kFloat32) * out.to(torch::kFloat32)).sum(-1);  // [B, R, H, N]
+  Tensor delta = torch::empty({B, R, H, N}, bf.dtype(torch::kFloat32));
+  if (out.scalar_type() == torch::kBFloat16 && out.stride(4) == 1 && delta.numel() > 0) {
+    const long long total = delta.numel();
+    attention_delta_kernel<<<(unsigned)((total + 255) / 256), 256, 0, at::cuda::getCurrentCUDAStream()>>>(
+        reinterpret_cast<const __nv_bfloat16*>(out.data_ptr()), reinterpret_cast<const __nv_bfloat16*>(doc.data_ptr()),
+        delta.data_ptr<float>(), out.stride(0), out.stride(1), out.stride(2), out.stride(3), doc.stride(0), doc.stride(1),
+        doc.stride(2), doc.stride(3), (int)R, (int)H, (int)N, (int)D, total);
+    C10_CUDA_KERNEL_LAUNCH_CHECK();
+  } else {
+    delta = (doc.to(torch::kFloat32) * out.to(torch::kFloat32)).sum(-1);
+  }
   Tensor dq = torch::empty({B, R, H, N, D}, bf), dk = torch::empty({B, R, H, N, D}, bf), dv = torch::empty({B, R, H, N, D}, bf);
   const bool has_bias = bias.has_value() && bias->defined();
   const bool has_mask = mask.has_value() && mask->defined();

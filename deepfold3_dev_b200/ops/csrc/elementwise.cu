@@ -185,6 +185,95 @@ __global__ void __launch_bounds__(256) layer_norm_bwd_kernel(const T* __restrict
   }
 }
 
+// LayerNorm backward for bf16 rows of 128 * G channels: 8-byte loads, R rows per warp in flight; same math and the
+// same per-block (dw, db) partials as the generic kernel.
+template <int G, int R>
+__global__ void __launch_bounds__(256) layer_norm_bwd_vec_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                                                                 const float* __restrict__ w, const float* __restrict__ mean_in,
+                                                                 const float* __restrict__ rstd_in, __nv_bfloat16* __restrict__ dx,
+                                                                 float* __restrict__ partial, int64_t rows) {
+  constexpr int C = 128 * G;
+  extern __shared__ float smem[];  // [warps][2][C]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+  float aw[4 * G], ab[4 * G], wv[4 * G];
+#pragma unroll
+  for (int g = 0; g < G; ++g)
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      aw[4 * g + k] = ab[4 * g + k] = 0.f;
+      wv[4 * g + k] = w ? w[4 * (lane + 32 * g) + k] : 1.f;
+    }
+  for (int64_t row0 = ((int64_t)blockIdx.x * nwarp + warp) * R; row0 < rows; row0 += (int64_t)gridDim.x * nwarp * R) {
+    uint2 rx[R][G], rg[R][G];
+    float mean[R], rstd[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const int64_t row = row0 + r < rows ? row0 + r : rows - 1;
+      const uint2* xr = reinterpret_cast<const uint2*>(x + row * C);
+      const uint2* gr = reinterpret_cast<const uint2*>(dy + row * C);
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        rx[r][g] = xr[lane + 32 * g];
+        rg[r][g] = gr[lane + 32 * g];
+      }
+      mean[r] = mean_in[row];
+      rstd[r] = rstd_in[row];
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      if (row0 + r >= rows) continue;
+      float xh[4 * G], gg[4 * G];
+      float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        const __nv_bfloat162 x0 = *reinterpret_cast<const __nv_bfloat162*>(&rx[r][g].x), x1 = *reinterpret_cast<const __nv_bfloat162*>(&rx[r][g].y);
+        const __nv_bfloat162 g0 = *reinterpret_cast<const __nv_bfloat162*>(&rg[r][g].x), g1 = *reinterpret_cast<const __nv_bfloat162*>(&rg[r][g].y);
+        const float xs[4] = {__low2float(x0), __high2float(x0), __low2float(x1), __high2float(x1)};
+        const float gs[4] = {__low2float(g0), __high2float(g0), __low2float(g1), __high2float(g1)};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const int i = 4 * g + k;
+          xh[i] = (xs[k] - mean[r]) * rstd[r];
+          gg[i] = gs[k] * wv[i];
+          aw[i] += gs[k] * xh[i];
+          ab[i] += gs[k];
+          s1 += gg[i];
+          s2 += gg[i] * xh[i];
+        }
+      }
+      s1 = warp_sum(s1) / C;
+      s2 = warp_sum(s2) / C;
+      uint2* dr = reinterpret_cast<uint2*>(dx + (row0 + r) * C);
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        float o[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) o[k] = rstd[r] * (gg[4 * g + k] - s1 - xh[4 * g + k] * s2);
+        __nv_bfloat162 lo = __floats2bfloat162_rn(o[0], o[1]), hi = __floats2bfloat162_rn(o[2], o[3]);
+        uint2 out;
+        out.x = *reinterpret_cast<uint32_t*>(&lo);
+        out.y = *reinterpret_cast<uint32_t*>(&hi);
+        dr[lane + 32 * g] = out;
+      }
+    }
+  }
+  if (partial == nullptr) return;
+#pragma unroll
+  for (int g = 0; g < G; ++g)
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int c = 4 * (lane + 32 * g) + k;
+      smem[(warp * 2 + 0) * C + c] = aw[4 * g + k];
+      smem[(warp * 2 + 1) * C + c] = ab[4 * g + k];
+    }
+  __syncthreads();
+  for (int i = threadIdx.x; i < 2 * C; i += blockDim.x) {
+    float s = 0.f;
+    for (int wi = 0; wi < nwarp; ++wi) s += smem[wi * 2 * C + i];
+    partial[(int64_t)blockIdx.x * 2 * C + i] = s;
+  }
+}
+
 // ---------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void swiglu_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t rows, int D) {
@@ -432,7 +521,17 @@ std::tuple<Tensor, Tensor> df3_layer_norm_bwd(const Tensor& dy, const Tensor& x,
                                                 dx.data_ptr<float>(), pp, rows, C);                                \
     }                                                                                                              \
   } while (0)
-  if (C <= 128) DF3_LN_BWD(4); else if (C <= 256) DF3_LN_BWD(8); else if (C <= 512) DF3_LN_BWD(16); else DF3_LN_BWD(32);
+  const bool vec_ok = bf16 && (C == 128 || C == 256 || C == 384) && reinterpret_cast<uintptr_t>(x.data_ptr()) % 8 == 0 &&
+                      reinterpret_cast<uintptr_t>(dy.data_ptr()) % 8 == 0 && dy.scalar_type() == torch::kBFloat16;
+#define DF3_LN_BWD_VEC(G)                                                                                          \
+  df3::layer_norm_bwd_vec_kernel<G, 2><<<blocks, warps * 32, smem, stream()>>>(                                    \
+      (const __nv_bfloat16*)dy.data_ptr(), (const __nv_bfloat16*)x.data_ptr(), wp, mean.data_ptr<float>(),         \
+      rstd.data_ptr<float>(), (__nv_bfloat16*)dx.data_ptr(), pp, rows)
+  if (vec_ok && C == 128) DF3_LN_BWD_VEC(1);
+  else if (vec_ok && C == 256) DF3_LN_BWD_VEC(2);
+  else if (vec_ok && C == 384) DF3_LN_BWD_VEC(3);
+  else if (C <= 128) DF3_LN_BWD(4); else if (C <= 256) DF3_LN_BWD(8); else if (C <= 512) DF3_LN_BWD(16); else DF3_LN_BWD(32);
+#undef DF3_LN_BWD_VEC
 #undef DF3_LN_BWD
   C10_CUDA_KERNEL_LAUNCH_CHECK();
   return {dx, partial};

@@ -128,10 +128,11 @@ class GraphCache:
         self.failed = False
         self.error: Exception | None = None
 
-    def run(self, fn, inputs: dict):
+    def run(self, fn, inputs: dict, mode=None):
+        """``mode``: anything else the captured work depends on (for a module: its training flag)."""
         if self.failed:
             return fn(**inputs)
-        key = (torch.is_autocast_enabled("cuda"), tree_signature(inputs))
+        key = (mode, torch.is_autocast_enabled("cuda"), tree_signature(inputs))
         g = self._graphs.get(key)
         if g is None:
             if self._pool is None:

@@ -154,9 +154,11 @@ def test_graphed_trunk_pass_equals_eager_and_redraws_dropout(monkeypatch):
     graphs = model.__dict__.get("_trunk_graphs")
     # two shape signatures: the first pass starts from fp32 zeros, later passes from the bf16 output of the previous one
     assert graphs is not None and not graphs.failed and 1 <= len(graphs._graphs) <= 2
+    n_eval = len(graphs._graphs)
     torch.testing.assert_close(first, eager, atol=3e-2, rtol=3e-2)
     torch.testing.assert_close(second, first, atol=0, rtol=0)
     model.train()  # dropout on: replays must not repeat the mask
     a, b = trunk("1"), trunk("1")
+    assert len(graphs._graphs) > n_eval  # the training flag is part of the cache key
     assert not torch.equal(a, b)
     assert torch.isfinite(a).all() and torch.isfinite(b).all()
