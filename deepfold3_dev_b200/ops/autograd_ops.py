@@ -72,10 +72,12 @@ class _LayerNorm(torch.autograd.Function):
         dw = db = None
         if need_wb:
             sums = partial.sum(0)
-            if ctx.has_w:
-                dw = sums[0].to(ctx.w_dtype)
-            if ctx.has_b:
-                db = sums[1].to(ctx.b_dtype)
+            dw = sums[0] if ctx.has_w else None
+            db = sums[1] if ctx.has_b else None
+            if dw is not None and dw.dtype != ctx.w_dtype:
+                dw = dw.to(ctx.w_dtype)
+            if db is not None and db.dtype != ctx.b_dtype:
+                db = db.to(ctx.b_dtype)
         return dx, dw, db, None
 
 
@@ -320,21 +322,10 @@ class _Linear(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dy):
         x, w = ctx.saved_tensors
-        W = bf16_weight(w)
-        d2 = dy.reshape(-1, W.shape[0])
-        if d2.dtype != BF16:
-            d2 = d2.to(BF16)
-        dx = dw = db = None
-        if ctx.needs_input_grad[0]:
-            dx = torch.mm(d2, W).view(x.shape)
-            if dx.dtype != x.dtype:
-                dx = dx.to(x.dtype)
-        if ctx.needs_input_grad[1]:
-            x2 = x.reshape(-1, x.shape[-1])
-            dw = torch.mm(d2.t(), x2 if x2.dtype == BF16 else x2.to(BF16)).to(w.dtype)
-        if ctx.has_bias and ctx.needs_input_grad[2]:
-            db = d2.sum(0, dtype=torch.float32).to(ctx.b_dtype)
-        return dx, dw, db
+        need_db = ctx.has_bias and ctx.needs_input_grad[2]
+        dx, dw, db = K.linear_bwd(dy, x, bf16_weight(w), ctx.needs_input_grad[0], ctx.needs_input_grad[1], need_db)
+        return (dx if ctx.needs_input_grad[0] else None, dw.to(w.dtype) if ctx.needs_input_grad[1] else None,
+                db.to(ctx.b_dtype) if need_db else None)  # fmt: skip
 
 
 def linear(x, w, b=None):

@@ -481,6 +481,29 @@ Tensor df3_bmm_nt(const Tensor& a, const Tensor& b) {
   return gemm_impl(ac, bc, c10::nullopt, c10::nullopt, c10::nullopt, kPlain, false);
 }
 
+// Backward of y = x w^T (+ b) with bf16 operands: dx = dy w (in x's dtype), dw = dy^T x and db = sum dy in fp32.
+// One call from Python instead of six small ones; the products run on the library GEMM.
+std::tuple<Tensor, Tensor, Tensor> df3_linear_bwd(const Tensor& dy, const Tensor& x, const Tensor& w16, bool need_dx, bool need_dw,
+                                                   bool need_db) {
+  const int64_t n = w16.size(0), k = w16.size(1);
+  Tensor d2 = dy.reshape({-1, n});
+  if (d2.scalar_type() != torch::kBFloat16) d2 = d2.to(torch::kBFloat16);
+  Tensor dx, dw, db;
+  if (need_dx) {
+    dx = at::mm(d2, w16).view(x.sizes());
+    if (dx.scalar_type() != x.scalar_type()) dx = dx.to(x.scalar_type());
+  }
+  if (need_dw) {
+    Tensor x2 = x.reshape({-1, k});
+    if (x2.scalar_type() != torch::kBFloat16) x2 = x2.to(torch::kBFloat16);
+    dw = at::mm(d2.t(), x2).to(torch::kFloat32);
+  }
+  if (need_db) db = d2.sum(0, false, torch::kFloat32);
+  auto undef = [&](Tensor& t) { if (!t.defined()) t = torch::empty({0}, dy.options()); };
+  undef(dx); undef(dw); undef(db);
+  return {dx, dw, db};
+}
+
 // Reads the status word of the current device (synchronises) and clears it.
 int64_t df3_gemm_status() {
   int device = 0;
@@ -499,6 +522,8 @@ void df3_register_gemm(torch::Library& m) {
         &df3::df3_gemm);
   m.def("bmm_nt(Tensor a, Tensor b) -> Tensor", &df3::df3_bmm_nt);
   m.def("gemm_status() -> int", &df3::df3_gemm_status);
+  m.def("linear_bwd(Tensor dy, Tensor x, Tensor w16, bool need_dx, bool need_dw, bool need_db) -> (Tensor, Tensor, Tensor)",
+        &df3::df3_linear_bwd);
 }
 
 const char* df3_gemm_features() { return "gemm,gated_dual_linear,transition,pair_bias_attention,linear_planes,sigmoid_gate_mul,peer_reduce"; }
