@@ -81,43 +81,49 @@ def run_reference(args, bench) -> None:
     if not torch.cuda.is_available():
         return unavailable("no CUDA device")
 
-    info = init_process_group(timeout_s=1800.0)
-    world = info.world_size
-    seed_everything(bench.SEED, info.rank)
-    model_cfg = ModelConfig()
-    model_cfg.msa_crop_size = bench.N_MSA
-    if args.blocks:
-        model_cfg.pairformer.num_layer = args.blocks
-    opt_mode = os.environ.get("DF3_REF_OPTIM", "train")
-    o = model_cfg.optim
-    o.use_gradient_checkpointing = True
-    if opt_mode == "train":  # the kernel flags of the reference's production recipe (configs/initial.yaml:396-418)
-        try:
-            import triton  # noqa: F401
+    try:
+        info = init_process_group(timeout_s=1800.0)
+        world = info.world_size
+        seed_everything(bench.SEED, info.rank)
+        model_cfg = ModelConfig()
+        model_cfg.msa_crop_size = bench.N_MSA
+        if args.blocks:
+            model_cfg.pairformer.num_layer = args.blocks
+        opt_mode = os.environ.get("DF3_REF_OPTIM", "train")
+        o = model_cfg.optim
+        o.use_gradient_checkpointing = True
+        if opt_mode == "train":  # the kernel flags of the reference's production recipe (configs/initial.yaml:396-418)
+            try:
+                import triton  # noqa: F401
 
-            o.use_fused_evo_attention = True
-            o.use_fused_swiglu = True
-            o.use_fused_triangle_mul = True
-            o.use_fused_transition_pair = True
-        except ImportError:
-            opt_mode = "none (triton missing)"
-    chunk = int(os.environ.get("DF3_REF_DIFFUSION_CHUNK", "8"))
-    train_cfg = TrainingConfig(**bench.shared_train_settings(args.tokens), diffusion_chunk_size=chunk,
-                               per_rank_grad_clip=False)  # fmt: skip
-    model = DeepFold3(model_cfg).to(info.device)
-    model.train()
-    ddp_model, _ = wrap_ddp(model, info, train_cfg)
-    accumulator = AccumulationLoop(ddp_model=ddp_model, dist=info, num_steps=1, per_rank_clip=False)
-    optimizer = build_optimizer(model, train_cfg)
-    scheduler = build_scheduler(optimizer, train_cfg)
-    ema = EMA(model, decay=train_cfg.ema_decay)
-    scaler = torch.amp.GradScaler("cuda", enabled=False)
-    wrapped = WrappedOptimizer(optimizer=optimizer, scheduler=scheduler, scaler=scaler, model=model, dist_info=info,
-                               cfg=train_cfg)  # fmt: skip
-    state = TrainState()
-    host_batch = bench.make_host_batch(info.rank, args.tokens)
-    dev_batch = {k: v.to(info.device) for k, v in host_batch.items()}
-    flush_buf = torch.zeros(64 * 1024 * 1024, device=info.device)
+                o.use_fused_evo_attention = True
+                o.use_fused_swiglu = True
+                o.use_fused_triangle_mul = True
+                o.use_fused_transition_pair = True
+            except ImportError:
+                opt_mode = "none (triton missing)"
+        chunk = int(os.environ.get("DF3_REF_DIFFUSION_CHUNK", "8"))
+        train_cfg = TrainingConfig(**bench.shared_train_settings(args.tokens), diffusion_chunk_size=chunk,
+                                   per_rank_grad_clip=False)  # fmt: skip
+        model = DeepFold3(model_cfg).to(info.device)
+        model.train()
+        ddp_model, _ = wrap_ddp(model, info, train_cfg)
+        accumulator = AccumulationLoop(ddp_model=ddp_model, dist=info, num_steps=1, per_rank_clip=False)
+        optimizer = build_optimizer(model, train_cfg)
+        scheduler = build_scheduler(optimizer, train_cfg)
+        ema = EMA(model, decay=train_cfg.ema_decay)
+        scaler = torch.amp.GradScaler("cuda", enabled=False)
+        wrapped = WrappedOptimizer(optimizer=optimizer, scheduler=scheduler, scaler=scaler, model=model, dist_info=info,
+                                   cfg=train_cfg)  # fmt: skip
+        state = TrainState()
+        host_batch = bench.make_host_batch(info.rank, args.tokens)
+        dev_batch = {k: v.to(info.device) for k, v in host_batch.items()}
+        flush_buf = torch.zeros(64 * 1024 * 1024, device=info.device)
+
+    except Exception as exc:  # noqa: BLE001 - set-up of the reference's own stack failed: report, do not crash
+        if int(os.environ.get("RANK", "0")) == 0:
+            unavailable(f"reference set-up failed: {type(exc).__name__}: {exc}"[:300])
+        return
 
     def one_step(i, features):
         state.global_step = i

@@ -56,8 +56,9 @@ def cli():
 @click.option("--override", "overrides", multiple=True, help="key=value on the training or model config.")
 @click.option("--dataset", "datasets", multiple=True, help="name:path[:weight[:strategy[:distill]]] (repeatable).")
 @click.option("--synthetic", is_flag=True, help="Train on generated examples of the configured crop size.")
+@click.option("--num-workers", type=int, default=None, help="Background data threads (default: training.num_workers).")
 def train(data_dir, output, params, resume, configs, lr, max_steps, max_tokens, grad_accum, seed, deterministic, dtype,
-          wandb_project, wandb_entity, overrides, datasets, synthetic):  # fmt: skip
+          wandb_project, wandb_entity, overrides, datasets, synthetic, num_workers):  # fmt: skip
     """Train the model (one process per GPU; launch with torch.distributed.run for several)."""
     _setup_logging()
     from ..config.loader import build_configs
@@ -104,6 +105,10 @@ def train(data_dir, output, params, resume, configs, lr, max_steps, max_tokens, 
                 raise IndexError(i)
 
         stream = ds.BatchStream(_Concat(), sampler, tc.batch_size_per_rank, tc.max_tokens)
+    workers = tc.num_workers if num_workers is None else num_workers
+    if workers > 0 and not synthetic:
+        base = stream
+        stream = ds.PrefetchStream(lambda w: base, depth=max(2, getattr(tc, "prefetch_factor", 2) * workers), workers=1)
     trackers = build_trackers(output, info.is_main, wandb_project, wandb_entity, {"training": _plain(tc), "model": _plain(mc)})
     trainer = Trainer(tc, mc, train_loader=stream, sampler=sampler if hasattr(sampler, "state_dict") else None,
                       dist_info=info, trackers=trackers)  # fmt: skip

@@ -150,3 +150,53 @@ class BatchStream:
             else:
                 raise RuntimeError(f"{self.max_retries} consecutive examples failed to load")
         return collate(items, self.pad_tokens_to)
+
+
+class PrefetchStream:
+    """Runs an iterator of batches on background threads, ``depth`` batches ahead (reference: training/data.py DataLoader
+    wiring with ``num_workers`` / ``prefetch_factor``).
+
+    Loading, cropping and collating are file reads and torch ops, both of which release the interpreter lock, so
+    threads overlap them with the training step without the copy through worker processes. Order is preserved with
+    one worker; with several workers batches arrive in completion order.
+    """
+
+    def __init__(self, make_stream, depth: int = 4, workers: int = 1):
+        import queue
+        import threading
+
+        self._q: queue.Queue = queue.Queue(maxsize=max(1, depth))
+        self._stop = threading.Event()
+        self._err: BaseException | None = None
+        self._threads = []
+        for w in range(max(1, workers)):
+            t = threading.Thread(target=self._run, args=(make_stream(w),), name=f"df3-data-{w}", daemon=True)
+            t.start()
+            self._threads.append(t)
+
+    def _run(self, stream):
+        try:
+            for batch in stream:
+                while not self._stop.is_set():
+                    try:
+                        self._q.put(batch, timeout=0.2)
+                        break
+                    except Exception:  # noqa: BLE001 - queue.Full: keep waiting unless stopped
+                        continue
+                if self._stop.is_set():
+                    return
+        except BaseException as exc:  # noqa: BLE001 - surfaced by the consumer
+            self._err = exc
+            self._q.put(None)
+
+    def __iter__(self):
+        return self
+
+    def __next__(self):
+        item = self._q.get()
+        if item is None:
+            raise RuntimeError(f"data worker failed: {self._err!r}") from self._err
+        return item
+
+    def close(self) -> None:
+        self._stop.set()
