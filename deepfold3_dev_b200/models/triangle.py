@@ -118,11 +118,15 @@ class _TriangleMulBase(nn.Module):
             z, mask = z.unsqueeze(0), mask.unsqueeze(0)
         z0 = self.norm_left(z)
         router_logits = self.router(z0) if self.use_router else None
-        act = ops.triangle_projection_contract(z0, self.gate.weight, self.proj.weight, mask, self.outgoing)
         if self.is_mhr:
+            act = ops.triangle_projection_contract(z0, self.gate.weight, self.proj.weight, mask, self.outgoing)
             act = self.out_proj(self._head_mix(act, router_logits))
         else:
-            act = self.out_proj(self.norm_center(act))
+            nc = self.norm_center
+            act = ops.triangle_contract_norm(z0, self.gate.weight, self.proj.weight, mask, self.outgoing, nc.weight, nc.bias, nc.eps)
+            if nc.output_scale != 1.0:
+                act = act * nc.output_scale
+            act = self.out_proj(act)
         out = ops.sigmoid_gate_mul(z0, self.out_gate.weight, act)
         return out.squeeze(0) if squeeze else out
 

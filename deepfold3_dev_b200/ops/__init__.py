@@ -113,6 +113,21 @@ def window_attention(q, k, v, bias, scale: float):
     return ref.window_attention(q, k, v, bias, scale)
 
 
+def triangle_contract_norm(z0, w_gate, w_proj, mask, outgoing: bool, ln_w, ln_b, eps: float = 1e-5):
+    """``LN_c(triangle_projection_contract(...))``: on the GPU the contraction result stays channel-major and one kernel
+    normalises and transposes it to channel-last."""
+    nat = fused(z0, "gated_dual_linear")
+    C = w_gate.shape[0] // 2
+    if nat is not None and nat.has("plane_layer_norm") and nat.gemm_supported(z0, w_gate) and C in (32, 64, 128, 256):
+        _CENSUS["triangle_contract_norm:sm100"] += 1
+        B, N = z0.shape[0], z0.shape[1]
+        planes = nat.gated_dual_linear(z0, w_gate, w_proj, mask, True, True).view(2, C * B, N, N)
+        a, b = planes[0], planes[1]
+        act = torch.bmm(a, b.transpose(1, 2)) if outgoing else torch.bmm(b.transpose(1, 2), a)
+        return nat.plane_layer_norm(act.view(C, B * N * N), ln_w, ln_b, eps).view(B, N, N, C)
+    return layer_norm(triangle_projection_contract(z0, w_gate, w_proj, mask, outgoing), ln_w, ln_b, eps)
+
+
 def triangle_projection_contract(z0, w_gate, w_proj, mask, outgoing: bool):
     """Gated a/b projection of the triangle multiply followed by the contraction over the third token.
 

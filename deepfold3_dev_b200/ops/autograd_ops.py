@@ -85,6 +85,40 @@ def layer_norm(x, weight=None, bias=None, eps: float = 1e-5):
     return _LayerNorm.apply(x, weight, bias, eps)
 
 
+class _PlaneLayerNorm(torch.autograd.Function):
+    """LayerNorm over the channel axis of channel-major ``x [C, M]``, returned channel-last ``[M, C]``."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, eps):
+        xc = x.contiguous()
+        w, b = _f32(weight), _f32(bias)
+        y, mean, rstd = K.plane_layer_norm_fwd(xc, w, b, eps)
+        ctx.save_for_backward(xc, w, mean, rstd)
+        ctx.has_w, ctx.has_b = weight is not None, bias is not None
+        ctx.w_dtype = None if weight is None else weight.dtype
+        ctx.b_dtype = None if bias is None else bias.dtype
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w, mean, rstd = ctx.saved_tensors
+        need_wb = (ctx.has_w and ctx.needs_input_grad[1]) or (ctx.has_b and ctx.needs_input_grad[2])
+        dyc = dy.contiguous()
+        if dyc.dtype != torch.bfloat16:
+            dyc = dyc.to(torch.bfloat16)
+        dx, partial = K.plane_layer_norm_bwd(dyc, x, w, mean, rstd, need_wb)
+        dw = db = None
+        if need_wb:
+            sums = partial.sum(0)
+            dw = sums[0].to(ctx.w_dtype) if ctx.has_w else None
+            db = sums[1].to(ctx.b_dtype) if ctx.has_b else None
+        return dx, dw, db, None
+
+
+def plane_layer_norm(x, weight=None, bias=None, eps: float = 1e-5):
+    return _PlaneLayerNorm.apply(x, weight, bias, eps)
+
+
 class _SwiGLU(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x):

@@ -8,6 +8,10 @@ std::tuple<Tensor, Tensor, Tensor> df3_layer_norm_fwd(const Tensor&, const c10::
                                                       const c10::optional<Tensor>&, double);
 std::tuple<Tensor, Tensor> df3_layer_norm_bwd(const Tensor&, const Tensor&, const c10::optional<Tensor>&,
                                               const Tensor&, const Tensor&, bool);
+std::tuple<Tensor, Tensor, Tensor> df3_plane_layer_norm_fwd(const Tensor&, const c10::optional<Tensor>&,
+                                                            const c10::optional<Tensor>&, double);
+std::tuple<Tensor, Tensor> df3_plane_layer_norm_bwd(const Tensor&, const Tensor&, const c10::optional<Tensor>&, const Tensor&,
+                                                    const Tensor&, bool);
 Tensor df3_swiglu_fwd(const Tensor&);
 Tensor df3_swiglu_bwd(const Tensor&, const Tensor&);
 Tensor df3_gated_bwd(const Tensor&, const Tensor&, const c10::optional<Tensor>&);
@@ -24,7 +28,7 @@ void df3_register_peer(torch::Library& m);
 #endif
 
 static std::string df3_features() {
-  std::string f = "layer_norm,swiglu,dropout_add,adamw_ema";
+  std::string f = "layer_norm,swiglu,dropout_add,adamw_ema,plane_layer_norm";
 #ifdef DF3_WITH_GEMM
   f += ",";
   f += df3_gemm_features();
@@ -37,6 +41,9 @@ TORCH_LIBRARY(df3, m) {
   m.def("layer_norm_fwd(Tensor x, Tensor? w, Tensor? b, float eps) -> (Tensor, Tensor, Tensor)", &df3_layer_norm_fwd);
   m.def("layer_norm_bwd(Tensor dy, Tensor x, Tensor? w, Tensor mean, Tensor rstd, bool want_wb) -> (Tensor, Tensor)",
         &df3_layer_norm_bwd);
+  m.def("plane_layer_norm_fwd(Tensor x, Tensor? w, Tensor? b, float eps) -> (Tensor, Tensor, Tensor)", &df3_plane_layer_norm_fwd);
+  m.def("plane_layer_norm_bwd(Tensor dy, Tensor x, Tensor? w, Tensor mean, Tensor rstd, bool want_wb) -> (Tensor, Tensor)",
+        &df3_plane_layer_norm_bwd);
   m.def("swiglu_fwd(Tensor x) -> Tensor", &df3_swiglu_fwd);
   m.def("swiglu_bwd(Tensor dy, Tensor x) -> Tensor", &df3_swiglu_bwd);
   m.def("gated_bwd(Tensor dy, Tensor gp, Tensor? mask) -> Tensor", &df3_gated_bwd);

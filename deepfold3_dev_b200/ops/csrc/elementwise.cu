@@ -274,6 +274,131 @@ __global__ void __launch_bounds__(256) layer_norm_bwd_vec_kernel(const __nv_bflo
   }
 }
 
+// LayerNorm over the channel axis of a channel-major tensor, fused with the transpose to channel-last:
+//   x [C, M] (one plane per channel)  ->  y [M, C] = LN_c(x[:, m]) * w + b,   C = 32 * KC.
+// A block owns 64 consecutive positions: planes are read in 128-byte rows into a [C][65] fp32 tile (the odd pitch makes
+// the column reads conflict-free), then each warp normalises positions with lanes over channels and writes channel-last.
+constexpr int kPlaneTile = 64;
+
+template <int KC>
+__global__ void __launch_bounds__(256) plane_layer_norm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ w,
+                                                                   const float* __restrict__ b, __nv_bfloat16* __restrict__ y,
+                                                                   float* __restrict__ mean_out, float* __restrict__ rstd_out,
+                                                                   int64_t M, float eps) {
+  constexpr int C = 32 * KC;
+  extern __shared__ float tile[];  // [C][65]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t m0 = (int64_t)blockIdx.x * kPlaneTile;
+  for (int c = warp; c < C; c += 8) {
+    const __nv_bfloat16* src = x + (int64_t)c * M + m0;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int pidx = lane + 32 * h;
+      tile[c * 65 + pidx] = (m0 + pidx < M) ? __bfloat162float(src[pidx]) : 0.f;
+    }
+  }
+  __syncthreads();
+  for (int pidx = warp; pidx < kPlaneTile; pidx += 8) {
+    if (m0 + pidx >= M) break;
+    float v[KC];
+    float s = 0.f;
+#pragma unroll
+    for (int k = 0; k < KC; ++k) {
+      v[k] = tile[(lane + 32 * k) * 65 + pidx];
+      s += v[k];
+    }
+    const float mean = warp_sum(s) / C;
+    float q = 0.f;
+#pragma unroll
+    for (int k = 0; k < KC; ++k) q += (v[k] - mean) * (v[k] - mean);
+    const float rstd = rsqrtf(warp_sum(q) / C + eps);
+    __nv_bfloat16* yr = y + (m0 + pidx) * C;
+#pragma unroll
+    for (int k = 0; k < KC; ++k) {
+      const int c = lane + 32 * k;
+      float o = (v[k] - mean) * rstd;
+      if (w) o *= w[c];
+      if (b) o += b[c];
+      yr[c] = __float2bfloat16_rn(o);
+    }
+    if (lane == 0) {
+      mean_out[m0 + pidx] = mean;
+      rstd_out[m0 + pidx] = rstd;
+    }
+  }
+}
+
+// Backward of the above: dy [M, C] channel-last, x planes [C, M] -> dx planes [C, M]; (dw, db) partials per block.
+template <int KC>
+__global__ void __launch_bounds__(256) plane_layer_norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                                                                   const float* __restrict__ w, const float* __restrict__ mean_in,
+                                                                   const float* __restrict__ rstd_in, __nv_bfloat16* __restrict__ dx,
+                                                                   float* __restrict__ partial, int64_t M) {
+  constexpr int C = 32 * KC;
+  extern __shared__ float tile[];  // [C][65], then [8 warps][2][C] for the parameter gradients
+  float* red = tile + C * 65;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t m0 = (int64_t)blockIdx.x * kPlaneTile;
+  for (int c = warp; c < C; c += 8) {
+    const __nv_bfloat16* src = x + (int64_t)c * M + m0;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int pidx = lane + 32 * h;
+      tile[c * 65 + pidx] = (m0 + pidx < M) ? __bfloat162float(src[pidx]) : 0.f;
+    }
+  }
+  __syncthreads();
+  float aw[KC], ab[KC], wv[KC];
+#pragma unroll
+  for (int k = 0; k < KC; ++k) {
+    aw[k] = ab[k] = 0.f;
+    wv[k] = w ? w[lane + 32 * k] : 1.f;
+  }
+  for (int pidx = warp; pidx < kPlaneTile; pidx += 8) {
+    if (m0 + pidx >= M) break;
+    const float mean = mean_in[m0 + pidx], rstd = rstd_in[m0 + pidx];
+    const __nv_bfloat16* gr = dy + (m0 + pidx) * C;
+    float xh[KC], g[KC];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int k = 0; k < KC; ++k) {
+      const float go = __bfloat162float(gr[lane + 32 * k]);
+      xh[k] = (tile[(lane + 32 * k) * 65 + pidx] - mean) * rstd;
+      g[k] = go * wv[k];
+      aw[k] += go * xh[k];
+      ab[k] += go;
+      s1 += g[k];
+      s2 += g[k] * xh[k];
+    }
+    s1 = warp_sum(s1) / C;
+    s2 = warp_sum(s2) / C;
+#pragma unroll
+    for (int k = 0; k < KC; ++k) tile[(lane + 32 * k) * 65 + pidx] = rstd * (g[k] - s1 - xh[k] * s2);  // own column only
+  }
+  if (partial != nullptr) {
+#pragma unroll
+    for (int k = 0; k < KC; ++k) {
+      red[(warp * 2 + 0) * C + lane + 32 * k] = aw[k];
+      red[(warp * 2 + 1) * C + lane + 32 * k] = ab[k];
+    }
+  }
+  __syncthreads();
+  for (int c = warp; c < C; c += 8) {
+    __nv_bfloat16* dst = dx + (int64_t)c * M + m0;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int pidx = lane + 32 * h;
+      if (m0 + pidx < M) dst[pidx] = __float2bfloat16_rn(tile[c * 65 + pidx]);
+    }
+  }
+  if (partial != nullptr)
+    for (int i = threadIdx.x; i < 2 * C; i += blockDim.x) {
+      float s = 0.f;
+      for (int wi = 0; wi < 8; ++wi) s += red[wi * 2 * C + i];
+      partial[(int64_t)blockIdx.x * 2 * C + i] = s;
+    }
+}
+
 // ---------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void swiglu_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t rows, int D) {
@@ -533,6 +658,62 @@ std::tuple<Tensor, Tensor> df3_layer_norm_bwd(const Tensor& dy, const Tensor& x,
   else if (C <= 128) DF3_LN_BWD(4); else if (C <= 256) DF3_LN_BWD(8); else if (C <= 512) DF3_LN_BWD(16); else DF3_LN_BWD(32);
 #undef DF3_LN_BWD_VEC
 #undef DF3_LN_BWD
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  return {dx, partial};
+}
+
+// x [C, M] bf16 planes -> (y [M, C], mean [M], rstd [M])
+std::tuple<Tensor, Tensor, Tensor> df3_plane_layer_norm_fwd(const Tensor& x, const c10::optional<Tensor>& w,
+                                                            const c10::optional<Tensor>& b, double eps) {
+  TORCH_CHECK(x.is_cuda() && x.is_contiguous() && x.dim() == 2 && x.scalar_type() == torch::kBFloat16, "plane_layer_norm: contiguous bf16 [C, M]");
+  const int C = x.size(0);
+  const int64_t M = x.size(1);
+  TORCH_CHECK(C == 32 || C == 64 || C == 128 || C == 256, "plane_layer_norm: 32, 64, 128 or 256 channels");
+  c10::cuda::CUDAGuard guard(x.device());
+  auto y = torch::empty({M, C}, x.options());
+  auto opts = x.options().dtype(torch::kFloat32);
+  auto mean = torch::empty({M}, opts), rstd = torch::empty({M}, opts);
+  if (M == 0) return {y, mean, rstd};
+  const float* wp = w.has_value() ? w->data_ptr<float>() : nullptr;
+  const float* bp = b.has_value() ? b->data_ptr<float>() : nullptr;
+  const unsigned grid = (unsigned)((M + df3::kPlaneTile - 1) / df3::kPlaneTile);
+  const size_t smem = (size_t)C * 65 * sizeof(float);
+#define DF3_PLN(KC)                                                                                                \
+  do {                                                                                                             \
+    auto k = df3::plane_layer_norm_fwd_kernel<KC>;                                                                 \
+    if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);         \
+    k<<<grid, 256, smem, stream()>>>((const __nv_bfloat16*)x.data_ptr(), wp, bp, (__nv_bfloat16*)y.data_ptr(),     \
+                                     mean.data_ptr<float>(), rstd.data_ptr<float>(), M, (float)eps);               \
+  } while (0)
+  if (C == 32) DF3_PLN(1); else if (C == 64) DF3_PLN(2); else if (C == 128) DF3_PLN(4); else DF3_PLN(8);
+#undef DF3_PLN
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  return {y, mean, rstd};
+}
+
+// dy [M, C], x planes [C, M] -> (dx planes [C, M], partial [blocks, 2, C])
+std::tuple<Tensor, Tensor> df3_plane_layer_norm_bwd(const Tensor& dy, const Tensor& x, const c10::optional<Tensor>& w,
+                                                    const Tensor& mean, const Tensor& rstd, bool want_wb) {
+  TORCH_CHECK(dy.is_contiguous() && dy.scalar_type() == torch::kBFloat16 && x.is_contiguous(), "plane_layer_norm_bwd: contiguous bf16");
+  const int C = x.size(0);
+  const int64_t M = x.size(1);
+  c10::cuda::CUDAGuard guard(x.device());
+  auto dx = torch::empty_like(x);
+  const int blocks = (int)((M + df3::kPlaneTile - 1) / df3::kPlaneTile);
+  auto partial = torch::empty({want_wb ? blocks : 0, 2, C}, x.options().dtype(torch::kFloat32));
+  if (M == 0) return {dx, partial};
+  const float* wp = w.has_value() ? w->data_ptr<float>() : nullptr;
+  float* pp = want_wb ? partial.data_ptr<float>() : nullptr;
+  const size_t smem = ((size_t)C * 65 + 8 * 2 * C) * sizeof(float);
+#define DF3_PLNB(KC)                                                                                               \
+  do {                                                                                                             \
+    auto k = df3::plane_layer_norm_bwd_kernel<KC>;                                                                 \
+    if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);         \
+    k<<<blocks, 256, smem, stream()>>>((const __nv_bfloat16*)dy.data_ptr(), (const __nv_bfloat16*)x.data_ptr(), wp, \
+                                       mean.data_ptr<float>(), rstd.data_ptr<float>(), (__nv_bfloat16*)dx.data_ptr(), pp, M); \
+  } while (0)
+  if (C == 32) DF3_PLNB(1); else if (C == 64) DF3_PLNB(2); else if (C == 128) DF3_PLNB(4); else DF3_PLNB(8);
+#undef DF3_PLNB
   C10_CUDA_KERNEL_LAUNCH_CHECK();
   return {dx, partial};
 }

@@ -130,3 +130,11 @@ def test_triangle_projection_contract(outgoing):
         return torch.einsum("bikc,bjkc->bijc", a, b) if outgoing else torch.einsum("bkjc,bkic->bijc", a, b)
 
     _compare(lambda z0, wg, wp: ops.triangle_projection_contract(z0, wg, wp, mask, outgoing), eager, [z0, wg, wp], tol=4e-2)
+
+
+@pytest.mark.parametrize("C,M", [(128, 5000), (32, 777), (64, 64)])
+def test_plane_layer_norm(nat, C, M):
+    x = _leaf(C, M, seed=40, dtype=torch.bfloat16)
+    w, b = _leaf(C, seed=41), _leaf(C, seed=42, scale=0.1)
+    _compare(lambda x, w, b: nat.plane_layer_norm(x, w, b, 1e-5),
+             lambda x, w, b: F.layer_norm(x.float().t(), (C,), w, b), [x, w, b], tol=3e-2)
