@@ -15,6 +15,8 @@
 //               second MMA, O accumulated in registers; the pair exchanges row maximum and row sum through shared memory
 // Every wait is bounded; a wait that runs out records a df3::Status code and the CTA leaves cleanly.
 #include <ATen/cuda/CUDAContext.h>
+#include <algorithm>
+#include <vector>
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/library.h>
 #include <torch/torch.h>
@@ -664,8 +666,20 @@ std::tuple<Tensor, Tensor> df3_attention_fwd(const Tensor& q_in, const Tensor& k
   Tensor q = strides_ok(q_in) ? q_in : q_in.contiguous();
   Tensor k = strides_ok(k_in) ? k_in : k_in.contiguous();
   Tensor v = strides_ok(v_in) ? v_in : v_in.contiguous();
-  Tensor out = torch::empty_like(q);
-  if (out.stride(4) != 1) out = torch::empty(q.sizes(), q.options());
+  // the output takes q's dimension order in memory (q is usually a non-dense view of a packed projection, for which
+  // empty_like would fall back to the logical order and force a transposing copy on the way back to [.., tokens, H * D])
+  Tensor out;
+  {
+    std::vector<int64_t> order = {0, 1, 2, 3, 4};
+    std::stable_sort(order.begin(), order.end(), [&](int64_t a, int64_t b) { return q.stride(a) > q.stride(b); });
+    std::vector<int64_t> sizes_perm(5), inverse(5);
+    for (int i = 0; i < 5; ++i) {
+      sizes_perm[i] = q.size(order[i]);
+      inverse[order[i]] = i;
+    }
+    out = torch::empty(sizes_perm, q.options()).permute(inverse);
+    if (out.stride(4) != 1) out = torch::empty(q.sizes(), q.options());
+  }
   Tensor lse = torch::empty({want_lse ? 2 : 0, B, R, H, N}, q.options().dtype(torch::kFloat32));
   if (out.numel() == 0) return {out, lse};
 
