@@ -349,6 +349,11 @@ def bench_kernels(op):
     microbench.main()
 
 
+from . import prepare as _prepare  # noqa: E402
+
+_prepare.register(cli)
+
+
 def main():
     cli()
 

@@ -1,0 +1,244 @@
+"""``prepare`` command group and the dataset-inspection commands.
+
+Reference: scripts/prepare.py:316-1546 (sub-commands ``structures``, ``filter``, ``cluster``, ``msa`` ...),
+scripts/scan_mmcif.py, scripts/refilter.py, scripts/inspect_example.py, scripts/build_masks.py, scripts/pack.py.
+"""
+
+from __future__ import annotations
+
+import json
+import os
+
+import click
+
+
+@click.group()
+def prepare():
+    """Turn mmCIF archives into training examples: structures -> filter -> cluster -> features -> pack."""
+
+
+def _filter_cfg(max_resolution, max_release_date, min_release_date, max_chains, max_unk_fraction, max_tight_clashes):
+    from ..data.prepare import StructureFilterConfig
+
+    return StructureFilterConfig(max_resolution=max_resolution, max_release_date=max_release_date,
+                                 min_release_date=min_release_date, max_chains=max_chains,
+                                 max_unk_fraction=max_unk_fraction, max_tight_clashes=max_tight_clashes)  # fmt: skip
+
+
+_FILTER_OPTIONS = [
+    click.option("--max-resolution", type=float, default=9.0),
+    click.option("--max-release-date", default=None, help="YYYY-MM-DD; entries without a date fail this filter."),
+    click.option("--min-release-date", default=None),
+    click.option("--max-chains", type=int, default=300),
+    click.option("--max-unk-fraction", type=float, default=None),
+    click.option("--max-tight-clashes", type=int, default=None),
+]
+
+
+def _with(options):
+    def deco(f):
+        for o in reversed(options):
+            f = o(f)
+        return f
+
+    return deco
+
+
+@prepare.command("structures")
+@click.argument("mmcif_dir", type=click.Path(exists=True))
+@click.argument("out_dir", type=click.Path())
+@click.option("--workers", type=int, default=max(1, (os.cpu_count() or 2) // 2))
+@click.option("--no-assembly", is_flag=True, help="Keep the asymmetric unit instead of biological assembly 1.")
+@click.option("--limit", type=int, default=0)
+@_with(_FILTER_OPTIONS)
+def structures(mmcif_dir, out_dir, workers, no_assembly, limit, **filt):
+    """Parse and filter every mmCIF under MMCIF_DIR; writes structures/*.npz, manifest.json, sequences.fasta."""
+    from ..data.prepare import prepare_directory
+
+    counts = prepare_directory(mmcif_dir, out_dir, _filter_cfg(**filt), workers, not no_assembly, limit)
+    click.echo(json.dumps(counts))
+
+
+@prepare.command("filter")
+@click.argument("data_dir", type=click.Path(exists=True))
+@click.option("--output", type=click.Path(), default=None, help="Manifest to write (default: in place).")
+@_with(_FILTER_OPTIONS)
+def refilter(data_dir, output, **filt):
+    """Re-apply the filters to an existing manifest from the stored structures (no mmCIF parsing)."""
+    from ..data.prepare import filter_structure, filter_structure_metadata
+    from ..data.types import Structure, load_manifest, save_manifest
+
+    cfg = _filter_cfg(**filt)
+    path = os.path.join(data_dir, "manifest.json")
+    kept, dropped = [], 0
+    for rec in load_manifest(path):
+        for c in rec.chains:
+            c.valid = True
+        for i in rec.interfaces:
+            i.valid = True
+        st = Structure.load(os.path.join(data_dir, "structures", f"{rec.id}.npz"))
+        if filter_structure_metadata(rec.structure_info, cfg, len(rec.chains), len(st.residues)) is not None:
+            dropped += 1
+            continue
+        rec, _ = filter_structure(st, rec, cfg)
+        if any(c.valid for c in rec.chains):
+            kept.append(rec)
+        else:
+            dropped += 1
+    save_manifest(kept, output or path)
+    click.echo(f"{len(kept)} kept, {dropped} dropped")
+
+
+@prepare.command("cluster")
+@click.argument("data_dir", type=click.Path(exists=True))
+@click.option("--pdb-clusters", type=click.Path(exists=True), default=None, help="wwPDB clusters-by-entity-40.txt.")
+@click.option("--identity", type=float, default=0.4)
+def cluster(data_dir, pdb_clusters, identity):
+    """Assign cluster ids (sampling weights use them) to every chain of the manifest."""
+    from ..data.prepare import cluster_records
+    from ..data.prepare.clustering import load_pdb_clusters
+    from ..data.prepare.pipeline import load_fasta
+    from ..data.types import load_manifest, save_manifest
+
+    path = os.path.join(data_dir, "manifest.json")
+    recs = load_manifest(path)
+    fasta = os.path.join(data_dir, "sequences.fasta")
+    seqs = load_fasta(fasta) if os.path.exists(fasta) else {}
+    cluster_records(recs, seqs, load_pdb_clusters(pdb_clusters) if pdb_clusters else None, identity)
+    save_manifest(recs, path)
+    click.echo(f"{len({str(c.cluster_id) for r in recs for c in r.chains})} clusters over {len(recs)} entries")
+
+
+@prepare.command("features")
+@click.argument("data_dir", type=click.Path(exists=True))
+@click.option("--msa-dir", type=click.Path(), default=None, help="Directory of <msa_id>.a3m (or .npz) alignments.")
+@click.option("--max-msa-rows", type=int, default=16384)
+def features(data_dir, msa_dir, max_msa_rows):
+    """Featurise every manifest entry into features/<id>.pt plus the flat manifest the training datasets read."""
+    import torch
+
+    from ..data.featurize import featurize_structure
+    from ..data.parse.a3m import msa_from_a3m_file
+    from ..data.types import MSA, Structure, load_manifest
+
+    out = os.path.join(data_dir, "features")
+    os.makedirs(out, exist_ok=True)
+    flat = []
+    for rec in load_manifest(os.path.join(data_dir, "manifest.json")):
+        st = Structure.load(os.path.join(data_dir, "structures", f"{rec.id}.npz"))
+        msas = {}
+        for c in rec.chains:
+            if not msa_dir:
+                continue
+            base = os.path.join(msa_dir, str(c.msa_id))
+            if os.path.exists(base + ".npz"):
+                msas[c.chain_id] = MSA.load(base + ".npz")
+            elif os.path.exists(base + ".a3m"):
+                msas[c.chain_id] = msa_from_a3m_file(base + ".a3m", c.mol_type, max_msa_rows)
+        try:
+            feats = featurize_structure(st, rec, unpaired_msa=msas, max_msa_rows=max_msa_rows)
+        except ValueError as exc:
+            click.echo(f"skip {rec.id}: {exc}")
+            continue
+        torch.save(feats, os.path.join(out, f"{rec.id}.pt"))
+        d = rec.to_dict()
+        flat.append({"id": rec.id, "chains": d["chains"], "interfaces": d["interfaces"],
+                     "resolution": (d.get("structure_info") or {}).get("resolution") or 0.0})  # fmt: skip
+    with open(os.path.join(out, "manifest.json"), "w") as f:
+        json.dump(flat, f)
+    click.echo(f"{len(flat)} examples -> {out}")
+
+
+@prepare.command("pack")
+@click.argument("src_dir", type=click.Path(exists=True))
+@click.argument("out_dir", type=click.Path())
+@click.option("--shard-size", default="1G")
+def pack(src_dir, out_dir, shard_size):
+    """Bundle a directory of small files into tar shards with an index (read back transparently by the datasets)."""
+    from ..data.pack import build_pack
+
+    units = {"K": 1 << 10, "M": 1 << 20, "G": 1 << 30}
+    size = int(float(shard_size[:-1]) * units[shard_size[-1].upper()]) if shard_size[-1].upper() in units else int(shard_size)
+    click.echo(f"{build_pack(src_dir, out_dir, size)} shards -> {out_dir}")
+
+
+@prepare.command("masks")
+@click.argument("data_dir", type=click.Path(exists=True))
+@click.option("--exclude-mol-type", "exclude", multiple=True, type=click.Choice(["protein", "dna", "rna", "ligand"]))
+def masks(data_dir, exclude):
+    """Write masks/<id>.npz token masks (loss weight 0 for the excluded molecule classes)."""
+    import numpy as np
+
+    from ..data import const
+    from ..data.featurize import tokenize_structure
+    from ..data.types import Structure, load_manifest
+
+    ids = {"protein": const.MOL_PROTEIN, "dna": const.MOL_DNA, "rna": const.MOL_RNA, "ligand": const.MOL_NONPOLYMER}
+    drop = {ids[e] for e in exclude}
+    out = os.path.join(data_dir, "masks")
+    os.makedirs(out, exist_ok=True)
+    n = 0
+    for rec in load_manifest(os.path.join(data_dir, "manifest.json")):
+        st = Structure.load(os.path.join(data_dir, "structures", f"{rec.id}.npz"))
+        tok, _, _ = tokenize_structure(st, {c.chain_id for c in rec.chains if c.valid})
+        mt = np.asarray(tok["mol_type"])
+        np.savez_compressed(os.path.join(out, f"{rec.id}.npz"), loss_weight=(~np.isin(mt, list(drop))).astype(np.float32))
+        n += 1
+    click.echo(f"{n} masks -> {out}")
+
+
+@click.command("scan-mmcif")
+@click.argument("mmcif_dir", type=click.Path(exists=True))
+@click.option("--output", type=click.Path(), default=None, help="TSV to write (default: stdout).")
+def scan_mmcif(mmcif_dir, output):
+    """Table of id, resolution, method, deposition and release date for every mmCIF under a directory."""
+    from ..data.parse.mmcif import read_structure_info
+    from ..data.prepare.pipeline import find_mmcif_files
+
+    lines = ["id\tresolution\tmethod\tdeposited\treleased"]
+    for path in find_mmcif_files(mmcif_dir):
+        info = read_structure_info(path)
+        name = os.path.basename(path).split(".")[0]
+        lines.append(f"{name}\tunreadable\t\t\t" if info is None else
+                     f"{name}\t{info.resolution}\t{info.method}\t{info.deposited}\t{info.released}")  # fmt: skip
+    text = "\n".join(lines) + "\n"
+    if output:
+        with open(output, "w") as f:
+            f.write(text)
+    else:
+        click.echo(text, nl=False)
+
+
+@click.command("inspect-example")
+@click.argument("path", type=click.Path(exists=True))
+def inspect_example(path):
+    """Summarise one stored example: a ``.npz`` structure, a ``.pt`` feature dict or an mmCIF file."""
+    from ..data import const
+
+    if path.endswith(".pt"):
+        import torch
+
+        feats = torch.load(path, map_location="cpu", weights_only=False)
+        for k, v in feats.items():
+            click.echo(f"{k:28s} {tuple(v.shape) if hasattr(v, 'shape') else v!r} {getattr(v, 'dtype', '')}")
+        return
+    if path.endswith(".npz"):
+        from ..data.types import Structure
+
+        st = Structure.load(path)
+    else:
+        from ..data.parse.mmcif import parse_mmcif
+
+        st, rec = parse_mmcif(path)
+        click.echo(f"info: {rec.structure_info}")
+    click.echo(f"{st.name}: {len(st.chains)} chains, {len(st.residues)} residues, {len(st.atoms)} atoms "
+               f"({int(st.atoms['is_present'].sum())} resolved), {len(st.bonds)} bonds")  # fmt: skip
+    for c in st.chains:
+        click.echo(f"  chain {c['name'].decode():4s} asym {int(c['asym_id']):3d} entity {int(c['entity_id']):3d} copy {int(c['sym_id']):2d} "
+                   f"{const.MOL_TYPE_NAMES[int(c['mol_type'])]:10s} {int(c['res_num']):5d} residues {int(c['atom_num']):6d} atoms")  # fmt: skip
+
+
+def register(cli) -> None:
+    cli.add_command(prepare)
+    cli.add_command(scan_mmcif)
+    cli.add_command(inspect_example)

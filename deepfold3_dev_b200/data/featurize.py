@@ -1,0 +1,157 @@
+"""``Structure`` (+ per-chain MSAs, templates) -> the training feature dict.
+
+Reference: data/tokenize/tokenizer.py (one token per standard residue, one per heavy atom for ligands and modified
+residues) and data/feature/featurizer.py:37-1760 (feature table plus the training extras: ground-truth positions and
+masks in the dense token-atom layout, token bonds, resolution). The output has the keys the model and the losses read
+and is what ``FeatureDirDataset`` stores as ``<id>.pt``; cropping happens later, on the features.
+
+Reference conformers of standard residues come from ``ref_conformers``. A ligand or modified residue that the
+conformer table does not list uses its own observed coordinates (centred) as the conformer; the per-sample random
+rotation applied by the dataset removes the pose. Unresolved atoms of such a component have no conformer entry and are
+left out of the token list.
+"""
+
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from . import const, ref_conformers
+from .inference_input import _token_features
+from .types import MSA, Record, Structure
+
+M = const.MAX_ATOMS_PER_TOKEN
+
+
+def tokenize_structure(st: Structure, keep_asym: set[int] | None = None):
+    """Token table (the dict ``_token_features`` consumes) plus, per token, the rows of ``st.atoms`` it covers."""
+    tok: dict[str, list] = {k: [] for k in ("res_type", "mol_type", "asym", "entity", "sym", "res_idx", "atoms")}
+    atom_rows: list[np.ndarray] = []
+    chain_cols: dict[int, tuple[int, int]] = {}
+    for c in st.chains:
+        asym = int(c["asym_id"])
+        if keep_asym is not None and asym not in keep_asym:
+            continue
+        start = len(tok["res_type"])
+        mt = int(c["mol_type"])
+        for r in st.residues[int(c["res_idx"]) : int(c["res_idx"]) + int(c["res_num"])]:
+            a0, n = int(r["atom_idx"]), int(r["atom_num"])
+            rows = np.arange(a0, a0 + n)
+            name = r["name"].decode().strip()
+            common = (int(r["res_type"]), mt, asym, int(c["entity_id"]), int(c["sym_id"]), int(r["res_id"]))
+            if bool(r["is_standard"]) and mt != const.MOL_NONPOLYMER and name in const.RESIDUE_ATOMS:
+                names, elements, charges, coords = ref_conformers.get_ref_atoms(name)
+                _push(tok, common, (name, names, elements, charges, coords))
+                atom_rows.append(rows[:M])
+                continue
+            # per-atom tokens
+            ref = ref_conformers.get_ref_atoms(name)
+            atoms = st.atoms[rows]
+            if ref is not None:
+                by_name = {an: k for k, an in enumerate(ref[0])}
+            present = atoms["is_present"]
+            centre = np.zeros(3) if not present.any() else np.stack([atoms["x"], atoms["y"], atoms["z"]], -1)[present].mean(0)
+            for k, a in enumerate(atoms):
+                an = a["name"].decode().strip()
+                if ref is not None and an in by_name:
+                    j = by_name[an]
+                    entry = (name, [an], [ref[1][j]], [ref[2][j]], ref[3][j : j + 1])
+                elif a["is_present"]:
+                    xyz = np.array([[a["x"], a["y"], a["z"]]], dtype=np.float32) - centre.astype(np.float32)
+                    entry = (name, [an], [int(a["element"])], [float(a["charge"])], xyz)
+                else:
+                    continue
+                _push(tok, common, entry)
+                atom_rows.append(rows[k : k + 1])
+        if len(tok["res_type"]) > start:
+            chain_cols[asym] = (start, len(tok["res_type"]))
+    return tok, atom_rows, chain_cols
+
+
+def _push(tok, common, atoms):
+    for key, v in zip(("res_type", "mol_type", "asym", "entity", "sym", "res_idx"), common):
+        tok[key].append(v)
+    tok["atoms"].append(atoms)
+
+
+def token_bonds(st: Structure, atom_rows: list[np.ndarray], feats: dict) -> torch.Tensor:
+    """[N, N] bool: bonds between tokens where at least one side is an atom token (ligand / modified residue)."""
+    N = len(atom_rows)
+    owner = np.full(len(st.atoms), -1, dtype=np.int64)
+    for t, rows in enumerate(atom_rows):
+        owner[rows] = t
+    out = torch.zeros(N, N, dtype=torch.bool)
+    single = np.array([len(r) == 1 for r in atom_rows])
+    a, b = owner[st.bonds["atom_1"]], owner[st.bonds["atom_2"]]
+    ok = (a >= 0) & (b >= 0) & (a != b)
+    a, b = a[ok], b[ok]
+    ok = single[a] | single[b]
+    out[a[ok], b[ok]] = True
+    out[b[ok], a[ok]] = True
+    return out
+
+
+def msa_block(feats: dict, chain_cols: dict[int, tuple[int, int]], paired: dict[int, MSA] | None,
+              unpaired: dict[int, MSA] | None, max_rows: int = const.MAX_MSA_ROWS) -> dict:  # fmt: skip
+    """Query row, then paired rows (row i of every chain), then each chain's own rows in its own columns."""
+    N = feats["res_type"].shape[0]
+    rows = [feats["res_type"].numpy().astype(np.int64)]
+    dels = [np.zeros(N, dtype=np.int64)]
+
+    def fits(asym, msa):
+        s, e = chain_cols[asym]
+        return msa is not None and not msa.is_empty and msa.sequences.shape[1] == e - s
+
+    pm = {a: m for a, m in (paired or {}).items() if a in chain_cols and fits(a, m)}
+    if len(pm) > 1:
+        for r in range(1, min(m.sequences.shape[0] for m in pm.values())):
+            row, d = np.full(N, const.MSA_GAP, dtype=np.int64), np.zeros(N, dtype=np.int64)
+            for a, m in pm.items():
+                s, e = chain_cols[a]
+                row[s:e], d[s:e] = m.sequences[r], m.deletion_matrix[r]
+            rows.append(row), dels.append(d)
+    for a, m in (unpaired or {}).items():
+        if a not in chain_cols or not fits(a, m):
+            continue
+        s, e = chain_cols[a]
+        for r in range(1, m.sequences.shape[0]):
+            if len(rows) >= max_rows:
+                break
+            row, d = np.full(N, const.MSA_GAP, dtype=np.int64), np.zeros(N, dtype=np.int64)
+            row[s:e], d[s:e] = m.sequences[r], m.deletion_matrix[r]
+            rows.append(row), dels.append(d)
+    msa = torch.as_tensor(np.stack(rows[:max_rows]))
+    deletion = torch.as_tensor(np.stack(dels[:max_rows]))
+    onehot = torch.nn.functional.one_hot(msa.clamp(max=const.MSA_VOCAB_SIZE - 1), const.MSA_VOCAB_SIZE).float()
+    return {"msa": msa, "msa_mask": torch.ones_like(msa, dtype=torch.bool), "deletion_matrix": deletion,
+            "profile": onehot.mean(0)[:, : const.RES_TYPE_COUNT], "deletion_mean": deletion.float().mean(0)}  # fmt: skip
+
+
+def featurize_structure(st: Structure, record: Record | None = None, paired_msa: dict[int, MSA] | None = None,
+                        unpaired_msa: dict[int, MSA] | None = None, only_valid: bool = True,
+                        max_msa_rows: int = const.MAX_MSA_ROWS) -> dict:  # fmt: skip
+    """The unbatched, uncropped feature dict of one entry (tensors on CPU)."""
+    keep = None
+    if record is not None and only_valid:
+        keep = {c.chain_id for c in record.chains if c.valid}
+    tok, atom_rows, chain_cols = tokenize_structure(st, keep)
+    if not tok["res_type"]:
+        raise ValueError(f"{st.name}: no tokens after filtering")
+    feats = _token_features(tok)
+    N = len(atom_rows)
+    gt = torch.zeros(N, M, 3)
+    gt_mask = torch.zeros(N, M, dtype=torch.bool)
+    xyz = st.coords()
+    for t, rows in enumerate(atom_rows):
+        k = len(rows)
+        gt[t, :k] = torch.as_tensor(xyz[rows])
+        gt_mask[t, :k] = torch.as_tensor(st.atoms["is_present"][rows])
+    gt_mask &= feats["ref_mask"]
+    feats["atom_gt_positions"] = gt * gt_mask.unsqueeze(-1)
+    feats["atom_gt_mask"] = gt_mask
+    feats["bond_matrix"] = token_bonds(st, atom_rows, feats).float().unsqueeze(-1)  # [N, N, 1], read by the trunk
+    feats.update(msa_block(feats, chain_cols, paired_msa, unpaired_msa, max_msa_rows))
+    info = record.structure_info if record is not None else None
+    feats["resolution"] = torch.tensor(float(info.resolution) if info and info.resolution else const.RESOLUTION_UNKNOWN)
+    feats["is_distillation"] = torch.tensor(False)
+    return feats

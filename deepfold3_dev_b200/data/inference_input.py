@@ -75,7 +75,34 @@ class InferenceInput:
                 asym += 1
         feats = _token_features(tok)
         feats.update(_msa_features(feats, chain_cols, chain_msas, msa_crop_size, msa_pairing))
+        feats.update(_template_features(feats, chain_cols, chain_msas))
         return cls(feats, chain_names, job.name, list(job.seeds))
+
+
+def _template_features(feats, chain_cols, chains, max_templates: int = 4) -> dict:
+    """Template features of the protein chains that list hits; each chain fills its own token columns."""
+    from . import templates as tpl
+
+    N = int(feats["res_type"].shape[0])
+    merged = None
+    for (s, e), c in zip(chain_cols, chains):
+        hits = getattr(c, "templates", None)
+        if not hits or e - s != len(getattr(c, "sequence", "")):
+            continue
+        loaded = tpl.load_json_templates(hits, hits[0].get("_base_dir", "."), max_templates)
+        if not loaded:
+            continue
+        part = tpl.template_features(e - s, loaded, max_templates, token_offset=s, num_tokens=N)
+        if merged is None:
+            merged = part
+            continue
+        cols = slice(s, e)
+        for k, v in part.items():
+            if k == "template_mask":
+                merged[k] = torch.maximum(merged[k], v)
+            else:
+                merged[k][:, cols] = v[:, cols]
+    return merged or {}
 
 
 def _component(name: str):
@@ -154,8 +181,11 @@ def _token_features(tok) -> dict:
         if key != last:
             nxt, last = nxt + 1, key
         uid[i] = nxt
-    center = ref_pos.sum(1, keepdim=True) / ref_mask.sum(1, keepdim=True).clamp(min=1).unsqueeze(-1)
-    ref_pos = (ref_pos - center) * ref_mask.unsqueeze(-1)  # conformers are expressed around their centroid
+    # conformers are expressed around the centroid of their residue (atom tokens of one ligand share one frame)
+    total = torch.zeros(nxt + 1, 3).index_add_(0, uid, ref_pos.sum(1))
+    count = torch.zeros(nxt + 1).index_add_(0, uid, ref_mask.sum(1).float())
+    center = (total / count.clamp(min=1).unsqueeze(-1))[uid].unsqueeze(1)
+    ref_pos = (ref_pos - center) * ref_mask.unsqueeze(-1)
     return {
         "res_type": torch.tensor(tok["res_type"]), "mol_type": torch.tensor(tok["mol_type"]),
         "asym_id": torch.tensor(tok["asym"]), "entity_id": torch.tensor(tok["entity"]), "sym_id": torch.tensor(tok["sym"]),

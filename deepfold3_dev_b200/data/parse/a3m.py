@@ -59,7 +59,11 @@ def parse_a3m(text: str, max_rows: int | None = None, dedup: bool = True) -> MSA
                 row_del.append(pending)
                 pending = 0
         if len(aligned) != n:
-            raise ValueError(f"A3M row {name!r} has {len(aligned)} aligned columns, the query has {n}")
+            # concatenated search results can leave a row with a second block glued on (a lost header) or cut short:
+            # keep the first n columns, fill a short row with gaps (same outcome as the reference's fixed-width fill)
+            aligned, row_del = aligned[:n], row_del[:n]
+            row_del += [0] * (n - len(aligned))
+            aligned += ["-"] * (n - len(aligned))
         s = "".join(aligned)
         if dedup and s in seen:
             continue
@@ -82,3 +86,13 @@ def encode_sequence(seq: str, mol_type: int) -> np.ndarray:
     table = {const.MOL_PROTEIN: _PROT, const.MOL_RNA: _RNA, const.MOL_DNA: _DNA}[mol_type]
     unk = const.RES_TYPE_ORDER["UNK"] if mol_type == const.MOL_PROTEIN else const.RES_TYPE_ORDER["N"]
     return np.asarray([const.MSA_GAP if c == "-" else table.get(c.upper(), unk) for c in seq], dtype=np.int64)
+
+
+def msa_from_a3m_file(path: str, mol_type: int, max_rows: int | None = None):
+    """A3M file -> the array form stored next to prepared structures (``data.types.MSA``: int8 rows, mask, deletions)."""
+    from ..types import MSA as ArrayMSA
+
+    with open(path) as f:
+        m = parse_a3m(f.read(), max_rows=max_rows)
+    rows = np.stack([encode_sequence(s, mol_type) for s in m.sequences]).astype(np.int8)
+    return ArrayMSA(rows, rows != const.MSA_GAP, np.clip(m.deletions, 0, 127).astype(np.int8))

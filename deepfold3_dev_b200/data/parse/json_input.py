@@ -106,6 +106,18 @@ def detect_dialect(entry: dict) -> str:
     return "deepfold3"
 
 
+def _templates(spec: dict, base_dir: str) -> list[dict]:
+    """Inline ``templates`` or the hit list behind ``templatesPath``; every hit remembers where relative paths start."""
+    hits, root = list(spec.get("templates") or []), base_dir
+    path = spec.get("templatesPath")
+    if not hits and path:
+        full = path if os.path.isabs(path) else os.path.join(base_dir, path)
+        if os.path.exists(full):
+            with open(full) as f:
+                hits, root = json.load(f), os.path.dirname(full)
+    return [dict(h, _base_dir=root) for h in hits if isinstance(h, dict)]
+
+
 def _parse_entry(entry: dict, base_dir: str, dialect: str) -> JobInput:
     chains, next_id = [], 0
 
@@ -130,7 +142,7 @@ def _parse_entry(entry: dict, base_dir: str, dialect: str) -> JobInput:
                                     spec.get("pairedMsa"))  # fmt: skip
                 mods = _mods(spec.get("modifications"), "ptmType", "ptmPosition")
                 chains.append(ProteinChainInput(take_ids(spec), spec["sequence"].upper(), unpaired, paired, mods,
-                                                list(spec.get("templates") or [])))  # fmt: skip
+                                                _templates(spec, base_dir)))  # fmt: skip
             elif k in ("rna", "rnasequence", "dna", "dnasequence"):
                 mt = const.MOL_RNA if k.startswith("rna") else const.MOL_DNA
                 mods = _mods(spec.get("modifications"), "modificationType", "basePosition")

@@ -66,3 +66,111 @@ def template_features(query_len: int, templates: list[TemplateChain], max_templa
                 out["template_pseudo_beta"][t, i] = torch.as_tensor(xyz[idx[pb]], dtype=torch.float32)
                 out["template_pseudo_beta_mask"][t, i] = 1.0
     return out
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# template hits from files (reference: data/parse/templates.py:85-125 CIGAR pairs, :730-760 mmCIF hits,
+# :911-990 the JSON hit lists that accompany prediction jobs)
+# ---------------------------------------------------------------------------------------------------------------
+def cigar_to_index_pairs(cigar: str, query_start: int, target_start: int) -> tuple[list[int], list[int]]:
+    """CIGAR of an m8 hit (1-based starts) -> parallel 0-based ``(query indices, template indices)`` of matches."""
+    import re
+
+    q, t = query_start - 1, target_start - 1
+    qi, ti = [], []
+    for count, op in re.findall(r"(\d+)([MIDX=])", cigar):
+        n = int(count)
+        if op in "MX=":
+            qi.extend(range(q, q + n)), ti.extend(range(t, t + n))
+            q, t = q + n, t + n
+        elif op == "I":  # present in the query only
+            q += n
+        else:  # "D": present in the target only
+            t += n
+    return qi, ti
+
+
+def parse_m8(text: str) -> list[dict]:
+    """Rows of an mmseqs ``.m8`` file with a trailing CIGAR column -> ``[{name, chainId, queryIndices, templateIndices,
+    identity, evalue}]`` in file order."""
+    hits = []
+    for line in text.splitlines():
+        f = line.split("\t")
+        if len(f) < 13:
+            continue
+        qi, ti = cigar_to_index_pairs(f[12], int(f[6]), int(f[8]))
+        pdb, _, chain = f[1].partition("_")
+        hits.append({"name": f[1], "pdb_id": pdb.lower(), "chainId": chain, "queryIndices": qi, "templateIndices": ti,
+                     "identity": float(f[2]), "evalue": float(f[10])})  # fmt: skip
+    return hits
+
+
+def template_chain_from_mmcif(path: str, chain_id: str | None, query_indices, template_indices) -> TemplateChain | None:
+    """One hit: ``template_indices`` count positions of the chain's full (SEQRES) sequence, 0-based.
+
+    ``chain_id`` is matched against author chain names first, then label names; ``None`` takes the first protein chain.
+    Only protein chains give templates. Returns ``None`` when the chain is absent.
+    """
+    from .parse.mmcif import parse_mmcif
+
+    st, rec = parse_mmcif(path, use_assembly=False)
+    pick = None
+    for ci in rec.chains:
+        if ci.mol_type != const.MOL_PROTEIN:
+            continue
+        if chain_id is None or ci.auth_chain_name == chain_id or ci.chain_name == chain_id:
+            pick = ci
+            break
+    if pick is None:
+        return None
+    c = st.chains[pick.chain_id]
+    res = st.residues[int(c["res_idx"]) : int(c["res_idx"]) + int(c["res_num"])]
+    L, A = len(res), const.MAX_ATOMS_PER_TOKEN
+    coords, mask, names = np.zeros((L, A, 3), np.float32), np.zeros((L, A), bool), []
+    xyz = st.coords()
+    for k, r in enumerate(res):
+        name = const.RES_TYPE_INDEX_TO_NAME.get(int(r["res_type"]), "UNK")
+        names.append(name)
+        a0, n = int(r["atom_idx"]), int(r["atom_num"])
+        atoms = st.atoms[a0 : a0 + n]
+        if bool(r["is_standard"]):
+            m = min(n, A)
+            coords[k, :m], mask[k, :m] = xyz[a0 : a0 + m], atoms["is_present"][:m]
+            continue
+        order = {a: j for j, a in enumerate(const.RESIDUE_ATOMS.get(name, const.RESIDUE_ATOMS["UNK"]))}
+        for j, a in enumerate(atoms):  # modified residue: copy the atoms its parent also has
+            slot = order.get(a["name"].decode().strip())
+            if slot is not None and a["is_present"]:
+                coords[k, slot], mask[k, slot] = xyz[a0 + j], True
+    return TemplateChain(names, coords, mask, {int(q): int(t) for q, t in zip(query_indices, template_indices)})
+
+
+def load_json_templates(entries: list[dict], base_dir: str = ".", max_templates: int = 4) -> list[TemplateChain]:
+    """Hit list of a prediction job: ``[{"name" | "mmcifPath": file, "chainId", "queryIndices", "templateIndices"}]``
+    (an entry may instead carry the file's text under ``"mmcif"``). Unreadable hits are skipped."""
+    import os
+    import tempfile
+
+    out = []
+    for e in entries:
+        if len(out) >= max_templates:
+            break
+        path = e.get("mmcifPath") or e.get("name")
+        tmp = None
+        if "mmcif" in e and e["mmcif"]:
+            tmp = tempfile.NamedTemporaryFile("w", suffix=".cif", delete=False)
+            tmp.write(e["mmcif"]), tmp.close()
+            path = tmp.name
+        elif path and not os.path.isabs(path):
+            path = os.path.join(base_dir, path)
+        try:
+            if path and os.path.exists(path):
+                hit = template_chain_from_mmcif(path, e.get("chainId"), e["queryIndices"], e["templateIndices"])
+                if hit is not None:
+                    out.append(hit)
+        except (ValueError, KeyError, IndexError):
+            pass
+        finally:
+            if tmp is not None:
+                os.unlink(tmp.name)
+    return out

@@ -1,0 +1,187 @@
+"""mmCIF reader, structure containers, filters, clustering, surface targets and the structure featuriser (CPU)."""
+
+import math
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from deepfold3_dev_b200.data import const, sasa
+from deepfold3_dev_b200.data.featurize import featurize_structure
+from deepfold3_dev_b200.data.parse.cif import parse_cif
+from deepfold3_dev_b200.data.parse.mmcif import parse_mmcif, parse_oper_expression
+from deepfold3_dev_b200.data.prepare import StructureFilterConfig, cluster_records, filter_structure, prepare_directory
+from deepfold3_dev_b200.data.prepare.clustering import greedy_kmer_clusters
+from deepfold3_dev_b200.data.prepare.filters import filter_structure_metadata, select_interface_chains
+from deepfold3_dev_b200.data.templates import cigar_to_index_pairs, parse_m8
+from deepfold3_dev_b200.data.types import ATOM_DTYPE, MSA, Record, Structure, StructureInfo, load_manifest
+
+EXAMPLES = "/root/reference/examples"
+
+
+def _mini_cif(shift=(0.0, 0.0, 0.0), second_far=True) -> str:
+    """Two copies of GLY-ALA-SER-GLY (chains A, B), one zinc ion (chain C), a water, an altloc, a two-operator assembly."""
+    seq = ["GLY", "ALA", "SER", "GLY"]
+    lines = ["data_TEST", "_entry.id TEST", "_exptl.method 'X-RAY DIFFRACTION'", "_refine.ls_d_res_high 1.8",
+             "_pdbx_database_status.recvd_initial_deposition_date 2020-01-02",
+             "loop_", "_entity.id", "_entity.type", "1 polymer", "2 non-polymer", "3 water",
+             "loop_", "_entity_poly.entity_id", "_entity_poly.type", "_entity_poly.pdbx_seq_one_letter_code_can",
+             "1 'polypeptide(L)'", ";GASG", ";",
+             "loop_", "_entity_poly_seq.entity_id", "_entity_poly_seq.num", "_entity_poly_seq.mon_id"]  # fmt: skip
+    lines += [f"1 {i + 1} {r}" for i, r in enumerate(seq)]
+    lines += ["loop_", "_struct_asym.id", "_struct_asym.entity_id", "A 1", "B 1", "C 2", "D 3"]
+    lines += ["loop_", "_pdbx_struct_assembly_gen.assembly_id", "_pdbx_struct_assembly_gen.oper_expression",
+              "_pdbx_struct_assembly_gen.asym_id_list", "1 1 A,B,C,D"]  # fmt: skip
+    lines += ["loop_", "_pdbx_struct_oper_list.id"] + [f"_pdbx_struct_oper_list.matrix[{i}][{j}]" for i in (1, 2, 3) for j in (1, 2, 3)]
+    lines += [f"_pdbx_struct_oper_list.vector[{i}]" for i in (1, 2, 3)] + ["1 1 0 0 0 1 0 0 0 1 0 0 0"]
+    cols = ["group_PDB", "id", "type_symbol", "label_atom_id", "label_alt_id", "label_comp_id", "label_asym_id",
+            "label_entity_id", "label_seq_id", "Cartn_x", "Cartn_y", "Cartn_z", "occupancy", "B_iso_or_equiv",
+            "auth_seq_id", "auth_asym_id", "pdbx_PDB_model_num"]  # fmt: skip
+    lines += ["loop_"] + [f"_atom_site.{c}" for c in cols]
+    k = 0
+    for chain, off in (("A", 0.0), ("B", 30.0 if second_far else 0.3)):
+        for i, r in enumerate(seq[:3]):  # the 4th residue is unresolved
+            for name in const.RESIDUE_ATOMS[r]:
+                k += 1
+                x, y, z = 3.8 * i + shift[0] + off, 1.2 * (k % 5) + shift[1], 0.9 * (k % 3) + shift[2]
+                alt = "A" if (name == "CB" and r == "ALA") else "."
+                lines.append(f"ATOM {k} {name[0]} {name} {alt} {r} {chain} 1 {i + 1} {x:.3f} {y:.3f} {z:.3f} 0.6 10.0 {i + 1} {chain} 1")
+                if alt == "A":
+                    k += 1
+                    lines.append(f"ATOM {k} C CB B ALA {chain} 1 {i + 1} 99.0 99.0 99.0 0.4 10.0 {i + 1} {chain} 1")
+            k += 1
+            lines.append(f"ATOM {k} H H . {r} {chain} 1 {i + 1} 0 0 0 1.0 10.0 {i + 1} {chain} 1")
+    lines.append(f"HETATM {k + 1} ZN ZN . ZN C 2 . 2.0 2.0 4.0 1.0 10.0 101 A 1")
+    lines.append(f"HETATM {k + 2} O O . HOH D 3 . 9.0 9.0 9.0 1.0 10.0 201 A 1")
+    return "\n".join(lines) + "\n"
+
+
+def test_cif_grammar():
+    text = "data_x\n_a.b 'it''s ok'\n_a.c \"q r\"\nloop_\n_t.i\n_t.v\n1 'a b'\n2 ?\n# comment\n_z.text\n;line one\nline two\n;\n"
+    b = parse_cif(text)[0]
+    assert b.name == "x" and b.value("a", "c") == "q r"
+    assert b.column("t", "v") == ["a b", "?"] and b.rows("t") == 2
+    assert b.value("z", "text") == "line one\nline two"
+
+
+def test_oper_expression():
+    assert parse_oper_expression("1") == [["1"]]
+    assert parse_oper_expression("(1-3)") == [["1"], ["2"], ["3"]]
+    assert len(parse_oper_expression("(1,2)(3-5)")) == 6
+
+
+def test_parse_mmcif_and_roundtrip(tmp_path):
+    p = tmp_path / "test.cif"
+    p.write_text(_mini_cif())
+    st, rec = parse_mmcif(str(p))
+    assert [c["name"] for c in st.chains] == [b"A", b"B", b"C"]  # water dropped
+    assert [int(c["entity_id"]) for c in st.chains] == [0, 0, 1] and [int(c["sym_id"]) for c in st.chains] == [0, 1, 0]
+    a = st.chains[0]
+    assert int(a["res_num"]) == 4 and not st.residues[3]["is_present"]  # unresolved residue kept from the sequence
+    assert int(a["atom_num"]) == 4 + 5 + 6 + 4
+    ala_cb = st.atoms[4 + 4]
+    assert ala_cb["name"] == b"CB" and ala_cb["x"] < 50  # the higher-occupancy alternate location was taken
+    assert st.chain_canonical_seqs[0] == "GASG"
+    assert rec.structure_info.resolution == pytest.approx(1.8) and rec.structure_info.method == "X-RAY DIFFRACTION"
+    assert rec.chains[0].msa_id == rec.chains[1].msa_id and rec.chains[2].res_name == "ZN"
+    assert {(i.chain_1, i.chain_2) for i in rec.interfaces} == {(0, 2)}
+    st.save(tmp_path / "s.npz")
+    back = Structure.load(tmp_path / "s.npz")
+    assert back.atoms.dtype == ATOM_DTYPE and np.array_equal(back.atoms, st.atoms) and back.chain_canonical_seqs == st.chain_canonical_seqs
+    st.save_split(tmp_path / "split")
+    split = Structure.load_split(tmp_path / "split")
+    assert np.allclose(split.coords(), st.coords()) and np.array_equal(split.residues, st.residues)
+    sub = st.select_chains([1, 2])
+    assert len(sub.chains) == 2 and int(sub.chains[1]["atom_idx"]) == int(sub.chains[0]["atom_num"])
+    assert Record.from_dict(rec.to_dict()).to_dict() == rec.to_dict()
+
+
+def test_filters(tmp_path):
+    p = tmp_path / "clash.cif"
+    p.write_text(_mini_cif(second_far=False))  # chain B sits on chain A
+    st, rec = parse_mmcif(str(p))
+    rec, why = filter_structure(st, rec, StructureFilterConfig(min_residues=2))
+    assert sum(c.valid for c in rec.chains[:2]) == 1 and "chain clashing" in why.values()
+    assert not any(f.valid for f in rec.interfaces if not (rec.chains[f.chain_1].valid and rec.chains[f.chain_2].valid))
+    st2, rec2 = parse_mmcif(str(p))
+    rec2, why2 = filter_structure(st2, rec2, StructureFilterConfig(min_residues=4))
+    assert not rec2.chains[0].valid and why2["A"].startswith("length 3")
+    cfg = StructureFilterConfig(max_resolution=1.5, max_release_date="2021-01-01")
+    assert "resolution" in filter_structure_metadata(StructureInfo(resolution=1.8, released="2020-01-01"), cfg)
+    assert "released" in filter_structure_metadata(StructureInfo(resolution=1.0, released=None), cfg)
+    assert filter_structure_metadata(StructureInfo(resolution=1.0, released="2020-05-05"), cfg) is None
+
+
+def test_interface_chain_selection(tmp_path):
+    p = tmp_path / "t.cif"
+    p.write_text(_mini_cif())
+    st, _ = parse_mmcif(str(p))
+    assert select_interface_chains(st, ("chain", 0, 0), max_chains=5) == {0, 1, 2}
+    keep = select_interface_chains(st, ("chain", 0, 0), max_chains=1)
+    assert keep == {0, 2}  # the far copy is dropped, the ion next to chain A comes back in
+
+
+def test_clustering():
+    seqs = {"a": "MKTAYIAKQRQISFVKSHFSRQ", "b": "MKTAYIAKQRQISFVKSHFSRA", "c": "GGGGSGGGGSGGGGSGGGGSGG"}
+    rep = greedy_kmer_clusters(seqs, 0.4)
+    assert rep["a"] == rep["b"] and rep["c"] != rep["a"]
+
+
+def test_prepare_directory_and_cluster(tmp_path):
+    src = tmp_path / "src"
+    src.mkdir()
+    (src / "one.cif").write_text(_mini_cif())
+    (src / "bad.cif").write_text("data_bad\n_entry.id bad\n")
+    counts = prepare_directory(str(src), str(tmp_path / "out"), StructureFilterConfig(min_residues=2))
+    assert counts == {"ok": 1, "rejected": 0, "error": 1}
+    recs = load_manifest(str(tmp_path / "out" / "manifest.json"))
+    cluster_records(recs, {str(recs[0].chains[0].msa_id): "GASG"})
+    assert recs[0].chains[2].cluster_id == "lig:ZN" and recs[0].chains[0].cluster_id == recs[0].chains[1].cluster_id
+    assert os.path.exists(tmp_path / "out" / "structures" / "test.npz")
+
+
+def test_sasa_sphere_and_burial():
+    r = sasa.VDW_BY_Z[6]
+    one = sasa.atom_sasa(np.zeros((1, 3)), np.array([r]))
+    assert one[0] == pytest.approx(4 * math.pi * (r + sasa.PROBE) ** 2)
+    two = sasa.atom_sasa(np.array([[0.0, 0, 0], [2.0, 0, 0]]), np.array([r, r]), n_points=400)
+    # two equal spheres of radius R at distance d each lose a cap of height R - d/2
+    R = r + sasa.PROBE
+    assert two[0] == pytest.approx(4 * math.pi * R * R - 2 * math.pi * R * (R - 1.0), rel=0.03)
+    pos = np.zeros((2, 1, 3))
+    pos[1, 0, 0] = 3.0
+    t = sasa.burial_targets(pos, np.ones((2, 1), bool), np.full((2, 1), 6), np.array([0, 1]), np.ones(2, bool))
+    assert t.dsasa[0, 1] > 1.0 and t.dsasa[0, 0] == 0 and t.n_contact[0, 1] == 1
+    assert list(t.buried_area()) == [(0, 1)]
+
+
+def test_featurize_structure(tmp_path):
+    p = tmp_path / "t.cif"
+    p.write_text(_mini_cif())
+    st, rec = parse_mmcif(str(p))
+    msa = MSA(np.array([[7, 0, 15, 7], [7, 0, 21, 7]], np.int8), np.ones((2, 4), bool), np.zeros((2, 4), np.int8))
+    f = featurize_structure(st, rec, unpaired_msa={0: msa})
+    N = 4 + 4 + 1
+    assert f["res_type"].shape == (N,) and f["msa"].shape == (2, N) and int(f["msa"][1, 2]) == const.MSA_GAP
+    assert f["bond_matrix"].shape == (N, N, 1) and f["profile"].shape == (N, const.RES_TYPE_COUNT)
+    assert f["atom_gt_mask"][3].sum() == 0 and f["atom_gt_mask"][0].sum() == 4  # unresolved residue, glycine
+    assert int(f["mol_type"][-1]) == const.MOL_NONPOLYMER and f["ref_mask"][-1].sum() == 1
+    assert torch.allclose(f["atom_gt_positions"][-1, 0], torch.tensor([2.0, 2.0, 4.0]))
+
+
+def test_cigar_pairs_and_m8():
+    q, t = cigar_to_index_pairs("3M2I2M1D1M", 1, 5)
+    assert q == [0, 1, 2, 5, 6, 7] and t == [4, 5, 6, 7, 8, 10]
+    hits = parse_m8("101\t7yf1_A\t0.856\t132\t19\t0\t1\t132\t2\t133\t6.1E-53\t183\t132M\n")
+    assert hits[0]["chainId"] == "A" and hits[0]["templateIndices"][0] == 1 and len(hits[0]["queryIndices"]) == 132
+
+
+@pytest.mark.skipif(not os.path.isdir(EXAMPLES), reason="reference example files not mounted")
+def test_reference_example_job_features():
+    from deepfold3_dev_b200.data.inference_input import InferenceInput
+
+    inp = InferenceInput.from_json(os.path.join(EXAMPLES, "9j1y.json"))[0]
+    f = inp.features
+    assert inp.num_tokens == 245 and f["msa"].shape[1] == 245 and f["msa"].shape[0] > 1000
+    assert f["template_mask"].sum() == 4 and f["template_backbone_mask"][0].sum() > 100
