@@ -238,7 +238,73 @@ def inspect_example(path):
                    f"{const.MOL_TYPE_NAMES[int(c['mol_type'])]:10s} {int(c['res_num']):5d} residues {int(c['atom_num']):6d} atoms")  # fmt: skip
 
 
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# side language model (reference: scripts/plm_prepare.py, scripts/plm_train.py)
+# ---------------------------------------------------------------------------------------------------------------
+@click.group("plm-prepare")
+def plm_prepare():
+    """Build, cluster and inspect the stores the complex language model trains on."""
+
+
+@plm_prepare.command("structure")
+@click.option("--data-dir", type=click.Path(exists=True), required=True, help="Output of `prepare structures`.")
+@click.option("--output", type=click.Path(), required=True)
+@click.option("--source", required=True)
+def plm_structure(data_dir, output, source):
+    from ..complexlm.prepare import build_from_structures
+
+    click.echo(json.dumps(build_from_structures(data_dir, output, source)))
+
+
+@plm_prepare.command("pairs")
+@click.option("--fasta", type=click.Path(exists=True), required=True)
+@click.option("--pairs", type=click.Path(exists=True), required=True, help="Two sequence ids per line.")
+@click.option("--output", type=click.Path(), required=True)
+@click.option("--source", required=True)
+def plm_pairs(fasta, pairs, output, source):
+    from ..complexlm.prepare import build_from_pairs
+
+    click.echo(json.dumps(build_from_pairs(fasta, pairs, output, source)))
+
+
+@plm_prepare.command("cluster")
+@click.option("--store", "stores", multiple=True, required=True, type=click.Path(exists=True))
+@click.option("--identity", type=float, default=0.4)
+def plm_cluster(stores, identity):
+    from ..complexlm.prepare import cluster_stores
+
+    click.echo(json.dumps(cluster_stores(list(stores), identity)))
+
+
+@plm_prepare.command("stats")
+@click.option("--store", type=click.Path(exists=True), required=True)
+def plm_stats(store):
+    from ..complexlm.prepare import store_stats
+
+    click.echo(json.dumps(store_stats(store)))
+
+
+@click.command("plm-train")
+@click.option("--config", type=click.Path(exists=True), default=None)
+@click.option("--output", type=click.Path(), required=True)
+@click.option("--resume", type=click.Path(exists=True), default=None)
+@click.option("--override", "overrides", multiple=True, help="section.key=value (repeatable).")
+@click.option("--dry-run", is_flag=True, help="Build everything, run one step, write nothing but the config.")
+def plm_train(config, output, resume, overrides, dry_run):
+    """Train the complex language model (launch under torch.distributed.run for several GPUs)."""
+    from ..complexlm.config import load_experiment
+    from ..complexlm.trainer import ComplexLMTrainer
+
+    cfg = load_experiment(config, dict(o.split("=", 1) for o in overrides))
+    trainer = ComplexLMTrainer(cfg, output, resume)
+    if dry_run:
+        click.echo(json.dumps(trainer.train_step([next(iter(trainer.stream))])))
+        return
+    click.echo(json.dumps(trainer.train()))
+
+
 def register(cli) -> None:
-    cli.add_command(prepare)
-    cli.add_command(scan_mmcif)
-    cli.add_command(inspect_example)
+    for cmd in (prepare, scan_mmcif, inspect_example, plm_prepare, plm_train):
+        cli.add_command(cmd)
