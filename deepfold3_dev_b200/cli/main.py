@@ -92,7 +92,7 @@ def train(data_dir, output, params, resume, configs, lr, max_steps, max_tokens, 
             name, path = f[0], f[1]
             weights.append(float(f[2]) if len(f) > 2 and f[2] else 1.0)
             distill = len(f) > 4 and f[4].lower() in ("1", "true", "distill")
-            parts.append(ds.FeatureDirDataset(path, tc.max_tokens, tc.max_atoms, is_distillation=distill, seed=tc.seed))
+            parts.append(ds.open_dataset(path, max_tokens=tc.max_tokens, max_atoms=tc.max_atoms, is_distillation=distill, seed=tc.seed))
             logging.getLogger(__name__).info("dataset %s: %d examples from %s", name, len(parts[-1]), path)
         samplers = [WeightedClusterSampler(p.weights(), tc.seed + 17 * i, info.rank, info.world_size) for i, p in enumerate(parts)]
         sampler = MultiDatasetSampler(samplers, [len(p) for p in parts], weights, tc.seed)

@@ -306,5 +306,16 @@ def plm_train(config, output, resume, overrides, dry_run):
 
 
 def register(cli) -> None:
-    for cmd in (prepare, scan_mmcif, inspect_example, plm_prepare, plm_train):
+    for cmd in (prepare, scan_mmcif, inspect_example, plm_prepare, plm_train, evaluate):
         cli.add_command(cmd)
+
+
+@click.command("evaluate")
+@click.argument("predicted", type=click.Path(exists=True))
+@click.argument("experimental", type=click.Path(exists=True))
+@click.option("--assembly", is_flag=True, help="Expand biological assembly 1 of the experimental entry.")
+def evaluate(predicted, experimental, assembly):
+    """lDDT, TM-score, GDT-TS, RMSD and DockQ of a predicted mmCIF against an experimental one."""
+    from ..evaluation.compare import compare_files
+
+    click.echo(json.dumps(compare_files(predicted, experimental, assembly), indent=1))

@@ -200,3 +200,103 @@ class PrefetchStream:
 
     def close(self) -> None:
         self._stop.set()
+
+
+class StructureDataset:
+    """Prepared structures featurised on the fly (reference: data/module/dataset.py:238-602, ``TrainingDataset``).
+
+    ``root`` is the output of ``prepare structures``: ``manifest.json``, ``structures/<id>.npz`` and optionally
+    ``msa/<msa_id>.npz`` / ``.a3m``. Per sample: pick the anchor chain or interface, pre-crop large assemblies to the
+    chains around it, featurise, crop to the token budget, then rotate the reference conformers. MSAs are read only for
+    chains that survive the chain pre-crop.
+    """
+
+    def __init__(self, root: str, max_tokens: int = 384, max_atoms: int = 0, crop_weights: dict | None = None,
+                 is_distillation: bool = False, seed: int = 0, max_chains: int = 20, max_msa_rows: int = 16384,
+                 msa_dir: str | None = None):  # fmt: skip
+        from .types import load_manifest
+
+        self.root, self.max_tokens, self.max_atoms = root, max_tokens, max_atoms
+        self.crop_weights, self.is_distillation, self.seed = crop_weights, is_distillation, seed
+        self.max_chains, self.max_msa_rows = max_chains, max_msa_rows
+        self.msa_dir = msa_dir or os.path.join(root, "msa")
+        self.records = [r for r in load_manifest(os.path.join(root, "manifest.json")) if any(c.valid for c in r.chains)]
+
+    def __len__(self):
+        return len(self.records)
+
+    def weights(self) -> list[float]:
+        from . import const
+        from .samplers import example_weight
+
+        sizes: dict = {}
+        for r in self.records:
+            for c in r.chains:
+                if c.valid:
+                    sizes[c.cluster_id] = sizes.get(c.cluster_id, 0) + 1
+        kind = {const.MOL_PROTEIN: "protein", const.MOL_DNA: "nucleic", const.MOL_RNA: "nucleic", const.MOL_NONPOLYMER: "ligand"}
+        out = []
+        for r in self.records:
+            chains = [{"type": kind[c.mol_type], "cluster_size": sizes[c.cluster_id]} for c in r.chains if c.valid]
+            faces = []
+            for f in r.interfaces:
+                if f.valid:
+                    a, b = r.chains[f.chain_1], r.chains[f.chain_2]
+                    t = "ligand" if "ligand" in (kind[a.mol_type], kind[b.mol_type]) else kind[a.mol_type]
+                    faces.append({"type": t, "cluster_size": min(sizes[a.cluster_id], sizes[b.cluster_id])})
+            out.append(example_weight(chains, faces))
+        return out
+
+    def _msa(self, chain):
+        from .parse.a3m import msa_from_a3m_file
+        from .types import MSA
+
+        base = os.path.join(self.msa_dir, str(chain.msa_id))
+        if os.path.exists(base + ".npz"):
+            return MSA.load(base + ".npz")
+        if os.path.exists(base + ".a3m"):
+            return msa_from_a3m_file(base + ".a3m", chain.mol_type, self.max_msa_rows)
+        return None
+
+    def __getitem__(self, i: int) -> dict:
+        import random
+
+        from .featurize import featurize_structure
+        from .prepare.filters import select_interface_chains
+        from .types import Structure
+
+        rec = self.records[i % len(self.records)]
+        gen = torch.Generator().manual_seed(self.seed * 7_654_321 + i)
+        rng = random.Random(self.seed * 7_654_321 + i)
+        st = Structure.load(os.path.join(self.root, "structures", f"{rec.id}.npz"))
+        valid = [c for c in rec.chains if c.valid]
+        faces = [f for f in rec.interfaces if f.valid]
+        if faces and rng.random() < 0.5:
+            f = rng.choice(faces)
+            anchor = ("interface", f.chain_1, f.chain_2)
+        else:
+            anchor = ("chain", rng.choice(valid).chain_id, -1)
+        keep = select_interface_chains(st, anchor, self.max_chains, rng=rng) & {c.chain_id for c in valid}
+        old_ids = sorted(keep)
+        sub = st.select_chains(old_ids)
+        msas = {}
+        for new_id, old in enumerate(old_ids):
+            m = self._msa(rec.chains[old])
+            if m is not None:
+                msas[new_id] = m
+        feats = featurize_structure(sub, None, unpaired_msa=msas, max_msa_rows=self.max_msa_rows)
+        feats, strategy = cropper.crop(feats, self.max_tokens, self.max_atoms, gen, self.crop_weights)
+        feats = rotate_reference_conformers(feats, gen)
+        info = rec.structure_info
+        feats["resolution"] = torch.tensor(float(info.resolution) if info and info.resolution else 0.0)
+        feats["is_distillation"] = torch.tensor(bool(self.is_distillation))
+        feats["_record_id"] = rec.id
+        feats["_crop"] = strategy
+        return feats
+
+
+def open_dataset(path: str, **kw):
+    """A directory of ``.pt`` features, or the output of ``prepare structures`` (featurised on the fly)."""
+    if os.path.isdir(os.path.join(path, "structures")) and os.path.exists(os.path.join(path, "manifest.json")):
+        return StructureDataset(path, **kw)
+    return FeatureDirDataset(path, **kw)

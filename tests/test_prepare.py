@@ -52,7 +52,7 @@ def _mini_cif(shift=(0.0, 0.0, 0.0), second_far=True) -> str:
                     lines.append(f"ATOM {k} C CB B ALA {chain} 1 {i + 1} 99.0 99.0 99.0 0.4 10.0 {i + 1} {chain} 1")
             k += 1
             lines.append(f"ATOM {k} H H . {r} {chain} 1 {i + 1} 0 0 0 1.0 10.0 {i + 1} {chain} 1")
-    lines.append(f"HETATM {k + 1} ZN ZN . ZN C 2 . 2.0 2.0 4.0 1.0 10.0 101 A 1")
+    lines.append(f"HETATM {k + 1} ZN ZN . ZN C 2 . {2.0 + shift[0]:.3f} {2.0 + shift[1]:.3f} {4.0 + shift[2]:.3f} 1.0 10.0 101 A 1")
     lines.append(f"HETATM {k + 2} O O . HOH D 3 . 9.0 9.0 9.0 1.0 10.0 201 A 1")
     return "\n".join(lines) + "\n"
 
@@ -185,3 +185,23 @@ def test_reference_example_job_features():
     f = inp.features
     assert inp.num_tokens == 245 and f["msa"].shape[1] == 245 and f["msa"].shape[0] > 1000
     assert f["template_mask"].sum() == 4 and f["template_backbone_mask"][0].sum() > 100
+
+
+def test_structure_dataset_on_the_fly(tmp_path):
+    from deepfold3_dev_b200.data.datasets import StructureDataset, collate, open_dataset
+
+    src = tmp_path / "src"
+    src.mkdir()
+    (src / "one.cif").write_text(_mini_cif())
+    prepare_directory(str(src), str(tmp_path / "out"), StructureFilterConfig(min_residues=2))
+    recs = load_manifest(str(tmp_path / "out" / "manifest.json"))
+    os.makedirs(tmp_path / "out" / "msa")
+    MSA(np.array([[7, 0, 15, 7], [7, 0, 21, 7], [7, 1, 15, 7]], np.int8), np.ones((3, 4), bool), np.zeros((3, 4), np.int8)).save(
+        tmp_path / "out" / "msa" / f"{recs[0].chains[0].msa_id}.npz")
+    d = open_dataset(str(tmp_path / "out"), max_tokens=6)
+    assert isinstance(d, StructureDataset) and len(d) == 1 and len(d.weights()) == 1
+    x = d[0]
+    assert x["res_type"].shape == (6,) and x["msa"].shape[1] == 6 and x["_record_id"] == "test"
+    assert x["msa"].shape[0] == 5  # query + two alignment rows for each of the two copies
+    b = collate([x, d[1]])
+    assert b["res_type"].shape == (2, 6) and b["bond_matrix"].shape == (2, 6, 6, 1)
