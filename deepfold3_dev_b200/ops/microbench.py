@@ -56,7 +56,8 @@ class Timer:
 
 def _report(name, ms, other_ms, nbytes, flops):
     gbs, tfl, kind = _peaks()
-    line = f"{name:34s} {ms * 1e3:9.1f} us   library/eager {other_ms * 1e3:9.1f} us"
+    line = f"{name:34s} {ms * 1e3:9.1f} us"
+    line += f"   library/eager {other_ms * 1e3:9.1f} us" if other_ms is not None else " " * 28
     if nbytes:
         line += f"   {nbytes / ms / 1e6:7.0f} GB/s ({nbytes / ms / 1e6 / gbs:.2f} of {kind} copy)"
     if flops:
@@ -110,9 +111,34 @@ def bench_elementwise(t: Timer):
             t(lambda: r + torch.nn.functional.dropout(x, 0.25)), 3 * nb, 0)  # fmt: skip
 
 
+def bench_streaming(t: Timer):
+    """Bandwidth-bound kernels on tensors larger than L2 (768-token pair tensor, 151 MB in bf16; 92 M-element optimizer)."""
+    n = 768
+    x = torch.randn(n * n, 128, device="cuda").bfloat16()
+    w = torch.ones(128, device="cuda")
+    nb = x.numel() * 2
+    y, mean, rstd = torch.ops.df3.layer_norm_fwd(x, w, w, 1e-5)
+    _report("layer_norm fwd 589824x128", t(lambda: torch.ops.df3.layer_norm_fwd(x, w, w, 1e-5)),
+            t(lambda: torch.nn.functional.layer_norm(x, (128,), w.bfloat16(), w.bfloat16())), 2 * nb, 0)  # fmt: skip
+    _report("layer_norm bwd 589824x128", t(lambda: torch.ops.df3.layer_norm_bwd(y, x, w, mean, rstd, True)), None, 3 * nb, 0)
+    planes = torch.randn(128, n * n, device="cuda").bfloat16()
+    _report("plane_layer_norm fwd 128x589824", t(lambda: torch.ops.df3.plane_layer_norm_fwd(planes, w, w, 1e-5)),
+            t(lambda: torch.nn.functional.layer_norm(planes.t(), (128,), w.bfloat16(), w.bfloat16())), 2 * nb, 0)  # fmt: skip
+    h = torch.randn(n * n // 4, 1024, device="cuda").bfloat16()
+    _report("swiglu fwd 147456x1024", t(lambda: torch.ops.df3.swiglu_fwd(h)),
+            t(lambda: torch.nn.functional.silu(h[:, :512]) * h[:, 512:]), h.numel() * 3, 0)  # fmt: skip
+    m = 92_000_000
+    p, g, m1, m2, ema = (torch.randn(m, device="cuda") * 0.01 for _ in range(5))
+    m2.abs_()
+    p16 = torch.empty(m, device="cuda", dtype=torch.bfloat16)
+    decay, scale = torch.zeros(m, device="cuda"), torch.ones(1, device="cuda")
+    _report("adamw+ema+bf16 mirror 92M", t(lambda: torch.ops.df3.adamw_ema(p, g, m1, m2, ema, decay, scale, 1e-3, 0.9, 0.95, 1e-8,
+                                                                            0.1, 0.05, 1e-3, p16)), None, m * (4 * 10 + 2), 0)  # fmt: skip
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", default="all", choices=["all", "gemm", "attention", "elementwise"])
+    ap.add_argument("--op", default="all", choices=["all", "gemm", "attention", "elementwise", "streaming"])
     ap.add_argument("--iters", type=int, default=10)
     args = ap.parse_args()
     native.require()
@@ -123,6 +149,8 @@ def main():
         bench_attention(t)
     if args.op in ("all", "elementwise"):
         bench_elementwise(t)
+    if args.op in ("all", "streaming"):
+        bench_streaming(t)
     code = torch.ops.df3.gemm_status()
     print("kernel status word:", code)
     if code != 0:
