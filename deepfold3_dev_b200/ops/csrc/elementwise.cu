@@ -66,17 +66,7 @@ __global__ void __launch_bounds__(256) layer_norm_fwd_vec_kernel(const __nv_bflo
                                                                  int64_t rows, float eps) {
   constexpr int C = 128 * G;
   const int lane = threadIdx.x & 31;
-  const int64_t row0 = ((int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * R;
-  if (row0 >= rows) return;
-  uint2 raw[R][G];
-#pragma unroll
-  for (int r = 0; r < R; ++r) {
-    const int64_t row = row0 + r < rows ? row0 + r : rows - 1;  // tail rows re-read the last row; their stores are skipped
-    const uint2* xr = reinterpret_cast<const uint2*>(x + row * C);
-#pragma unroll
-    for (int g = 0; g < G; ++g) raw[r][g] = xr[lane + 32 * g];
-  }
-  float wv[4 * G], bv[4 * G];
+  float wv[4 * G], bv[4 * G];  // gain and bias stay in registers for every row this warp visits
 #pragma unroll
   for (int g = 0; g < G; ++g)
 #pragma unroll
@@ -85,6 +75,16 @@ __global__ void __launch_bounds__(256) layer_norm_fwd_vec_kernel(const __nv_bflo
       wv[4 * g + k] = w ? w[c] : 1.f;
       bv[4 * g + k] = b ? b[c] : 0.f;
     }
+  const int64_t warp_stride = (int64_t)gridDim.x * (blockDim.x >> 5) * R;
+  for (int64_t row0 = ((int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * R; row0 < rows; row0 += warp_stride) {
+  uint2 raw[R][G];
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    const int64_t row = row0 + r < rows ? row0 + r : rows - 1;  // tail rows re-read the last row; their stores are skipped
+    const uint2* xr = reinterpret_cast<const uint2*>(x + row * C);
+#pragma unroll
+    for (int g = 0; g < G; ++g) raw[r][g] = xr[lane + 32 * g];
+  }
 #pragma unroll
   for (int r = 0; r < R; ++r) {
     float v[4 * G];
@@ -122,6 +122,7 @@ __global__ void __launch_bounds__(256) layer_norm_fwd_vec_kernel(const __nv_bflo
       mean_out[row0 + r] = mean;
       rstd_out[row0 + r] = rstd;
     }
+  }
   }
 }
 
@@ -423,6 +424,56 @@ __global__ void swiglu_bwd_kernel(const T* __restrict__ dy, const T* __restrict_
   dx[r * 2 * D + D + c] = from_float<T>(g * a * s);
 }
 
+// bf16 rows with D a multiple of 8: a thread owns 8 consecutive channels (16-byte loads and stores).
+__device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    f[2 * k] = __low2float(h[k]);
+    f[2 * k + 1] = __high2float(h[k]);
+  }
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+  uint4 u;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) h[k] = __floats2bfloat162_rn(f[2 * k], f[2 * k + 1]);
+  return u;
+}
+
+__global__ void __launch_bounds__(256) swiglu_fwd_vec_kernel(const uint4* __restrict__ x, uint4* __restrict__ y, int64_t rows, int D8) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= rows * D8) return;
+  const int64_t r = i / D8;
+  const int c = (int)(i - r * D8);
+  float a[8], b[8], o[8];
+  unpack8(x[r * 2 * D8 + c], a);
+  unpack8(x[r * 2 * D8 + D8 + c], b);
+#pragma unroll
+  for (int k = 0; k < 8; ++k) o[k] = a[k] * sigmoidf_(a[k]) * b[k];
+  y[i] = pack8(o);
+}
+
+__global__ void __launch_bounds__(256) swiglu_bwd_vec_kernel(const uint4* __restrict__ dy, const uint4* __restrict__ x,
+                                                              uint4* __restrict__ dx, int64_t rows, int D8) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= rows * D8) return;
+  const int64_t r = i / D8;
+  const int c = (int)(i - r * D8);
+  float a[8], b[8], g[8], da[8], db[8];
+  unpack8(x[r * 2 * D8 + c], a);
+  unpack8(x[r * 2 * D8 + D8 + c], b);
+  unpack8(dy[i], g);
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    const float s = sigmoidf_(a[k]);
+    da[k] = g[k] * b[k] * s * (1.f + a[k] * (1.f - s));
+    db[k] = g[k] * a[k] * s;
+  }
+  dx[r * 2 * D8 + c] = pack8(da);
+  dx[r * 2 * D8 + D8 + c] = pack8(db);
+}
+
 // ---------------------------------------------------------------------------------------------
 // Dropout whose Bernoulli draw is shared along one axis of x viewed as [outer, A, B, C]:
 // share_rows: mask index (outer, b, c)  (shared along A);  else: (outer, a, c)  (shared along B).
@@ -599,7 +650,7 @@ std::tuple<Tensor, Tensor, Tensor> df3_layer_norm_fwd(const Tensor& x, const c10
   } while (0)
   const bool vec_ok = bf16 && C % 128 == 0 && C <= 768 && reinterpret_cast<uintptr_t>(x.data_ptr()) % 8 == 0;
 #define DF3_LN_VEC(G)                                                                                              \
-  df3::layer_norm_fwd_vec_kernel<G, (G <= 2 ? 4 : 2)><<<(unsigned)((rows + warps * (G <= 2 ? 4 : 2) - 1) / (warps * (G <= 2 ? 4 : 2))), \
+  df3::layer_norm_fwd_vec_kernel<G, (G <= 2 ? 4 : 2)><<<(unsigned)std::min<int64_t>((rows + warps * (G <= 2 ? 4 : 2) - 1) / (warps * (G <= 2 ? 4 : 2)), 148 * 16), \
                                                        warps * 32, 0, stream()>>>(                                   \
       (const __nv_bfloat16*)x.data_ptr(), wp, bp, (__nv_bfloat16*)y.data_ptr(), mean.data_ptr<float>(),            \
       rstd.data_ptr<float>(), rows, (float)eps)
@@ -751,7 +802,10 @@ Tensor df3_swiglu_fwd(const Tensor& x) {
   const int64_t n = rows * D;
   if (n == 0) return y;
   const unsigned grid = (unsigned)((n + 255) / 256);
-  if (x.scalar_type() == torch::kBFloat16)
+  if (x.scalar_type() == torch::kBFloat16 && D % 8 == 0 && reinterpret_cast<uintptr_t>(x.data_ptr()) % 16 == 0)
+    df3::swiglu_fwd_vec_kernel<<<(unsigned)((rows * (D / 8) + 255) / 256), 256, 0, stream()>>>(
+        (const uint4*)x.data_ptr(), (uint4*)y.data_ptr(), rows, D / 8);
+  else if (x.scalar_type() == torch::kBFloat16)
     df3::swiglu_fwd_kernel<__nv_bfloat16><<<grid, 256, 0, stream()>>>((const __nv_bfloat16*)x.data_ptr(), (__nv_bfloat16*)y.data_ptr(), rows, D);
   else
     df3::swiglu_fwd_kernel<float><<<grid, 256, 0, stream()>>>(x.data_ptr<float>(), y.data_ptr<float>(), rows, D);
@@ -767,7 +821,11 @@ Tensor df3_swiglu_bwd(const Tensor& dy, const Tensor& x) {
   const int64_t n = rows * D;
   if (n == 0) return dx;
   const unsigned grid = (unsigned)((n + 255) / 256);
-  if (x.scalar_type() == torch::kBFloat16)
+  if (x.scalar_type() == torch::kBFloat16 && D % 8 == 0 && reinterpret_cast<uintptr_t>(x.data_ptr()) % 16 == 0 &&
+      reinterpret_cast<uintptr_t>(dy.data_ptr()) % 16 == 0)
+    df3::swiglu_bwd_vec_kernel<<<(unsigned)((rows * (D / 8) + 255) / 256), 256, 0, stream()>>>(
+        (const uint4*)dy.data_ptr(), (const uint4*)x.data_ptr(), (uint4*)dx.data_ptr(), rows, D / 8);
+  else if (x.scalar_type() == torch::kBFloat16)
     df3::swiglu_bwd_kernel<__nv_bfloat16><<<grid, 256, 0, stream()>>>((const __nv_bfloat16*)dy.data_ptr(), (const __nv_bfloat16*)x.data_ptr(), (__nv_bfloat16*)dx.data_ptr(), rows, D);
   else
     df3::swiglu_bwd_kernel<float><<<grid, 256, 0, stream()>>>(dy.data_ptr<float>(), x.data_ptr<float>(), dx.data_ptr<float>(), rows, D);
