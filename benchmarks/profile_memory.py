@@ -45,6 +45,8 @@ def main():
 
     dev = torch.device("cuda")
     cfg = ModelConfig()
+    cfg.msa_crop_size = args.msa
+    cfg.diffusion.steps = 4  # the footprint does not depend on the number of sampler steps
     model = DeepFold3(cfg).to(dev)
     points: list[tuple[int, float]] = []
     for n in sorted(args.tokens):
@@ -52,21 +54,25 @@ def main():
         if guess > args.limit_gib:
             print(json.dumps({"tokens": n, "skipped": f"predicted {guess:.0f} GiB > limit {args.limit_gib:.0f} GiB"}))
             continue
-        feats = synthetic_complex(split_lengths(n, 2), num_msa=args.msa, num_templates=4, seed=0, with_ground_truth=args.mode == "train")
-        batch = {k: (v.to(dev) if torch.is_tensor(v) else v) for k, v in collate([feats]).items()}
+        feats = synthetic_complex([("protein", m) for m in split_lengths(n, 2)], num_msa=args.msa, num_templates=4, seed=0,
+                                  with_gt=args.mode == "train")
+        if args.mode == "train":
+            batch = {k: (v.to(dev) if torch.is_tensor(v) else v) for k, v in collate([feats]).items()}
+        else:
+            batch = {k: v.to(dev) for k, v in feats.items()}
         torch.cuda.empty_cache()
         torch.cuda.reset_peak_memory_stats()
         if args.mode == "inference":
             model.eval()
             with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
-                model(batch, seed=0, num_recycles=1, num_samples=1, num_steps=2)
+                model(dict(batch), seed=0, num_recycles=1, num_samples=1)
         else:
             from deepfold3_dev_b200.training.engine import training_step
 
             model.train()
-            tc = TrainingConfig()
+            tc = TrainingConfig(max_tokens=n)
             with torch.autocast("cuda", dtype=torch.bfloat16):
-                loss, _ = training_step(model, batch, cfg=tc, model_cfg=cfg, global_step=0, device=dev, num_recycles=1)
+                loss, *_ = training_step(model, batch, cfg=tc, model_cfg=cfg, global_step=0, device=dev, num_recycles=1)
             loss.backward()
             model.zero_grad(set_to_none=True)
         torch.cuda.synchronize()

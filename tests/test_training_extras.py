@@ -1,0 +1,76 @@
+"""Collapse-free softmax family and the single-track probe."""
+
+import json
+
+import torch
+import torch.nn.functional as F
+
+from deepfold3_dev_b200.training import stable_softmax as ss
+from deepfold3_dev_b200.training.single_track_probe import SingleTrackProbe
+
+
+def test_matches_reference_functions_at_ordinary_margins():
+    torch.manual_seed(0)
+    z = torch.randn(5, 7, 11, dtype=torch.float64)
+    t = torch.randint(0, 11, (5, 7))
+    assert torch.allclose(ss.log_softmax(z), F.log_softmax(z, -1)) and torch.allclose(ss.softmax(z, 1), F.softmax(z, 1))
+    want = F.cross_entropy(z.reshape(-1, 11), t.reshape(-1), reduction="none").reshape(5, 7)
+    assert torch.allclose(ss.cross_entropy(z, t), want)
+    m = ss.logit_margin(z, t)
+    assert torch.allclose(want, F.softplus(-m))
+
+
+def test_target_gradient_survives_large_margin_in_fp32():
+    z = torch.tensor([[30.0, 0.0, -1.0, 2.0]], requires_grad=True)
+    t = torch.tensor([0])
+    ss.cross_entropy(z, t).sum().backward()
+    g = z.grad.clone()
+    assert g[0, 0] < 0 and abs(float(g.sum())) < 1e-18  # gradients still sum to zero
+    z2 = z.detach().clone().requires_grad_(True)
+    F.cross_entropy(z2, t).backward()
+    assert z2.grad[0, 0] == 0  # the standard form has lost the target gradient here
+    exact = torch.softmax(z.detach().double(), -1)[0, 0] - 1
+    assert abs(float(g[0, 0]) - float(exact)) / abs(float(exact)) < 1e-3
+
+
+class _Block(torch.nn.Module):
+    def __init__(self):
+        super().__init__()
+        self.single_transition = torch.nn.Linear(8, 8)
+        self.use_single_track = True
+
+    def forward(self, s):
+        u = self.single_transition(s)
+        p = getattr(self, "_probe", None)
+        if p is not None and p.enabled:
+            p.record_block(self._probe_layer_idx, s, u, 0.5)
+        return s + 0.5 * u
+
+
+class _Model(torch.nn.Module):
+    def __init__(self):
+        super().__init__()
+        self.evoformer = torch.nn.Module()
+        self.evoformer.trunk_pairformer = torch.nn.ModuleList(_Block() for _ in range(3))
+
+    def forward(self, s):
+        for b in self.evoformer.trunk_pairformer:
+            s = b(s)
+        return s
+
+
+def test_probe_writes_one_row_per_probed_step(tmp_path):
+    torch.manual_seed(0)
+    model = _Model()
+    probe = SingleTrackProbe(model, str(tmp_path / "probe.jsonl"))
+    x = torch.randn(2, 5, 8)
+    model(x)  # not probed
+    probe.begin_step(7)
+    model(x)
+    probe.end_step({"loss": 1.5})
+    probe.begin_step(8)
+    probe.discard_step()
+    rows = [json.loads(line) for line in open(tmp_path / "probe.jsonl")]
+    assert len(rows) == 1 and rows[0]["step"] == 7 and rows[0]["loss"] == 1.5
+    assert rows[0]["rms_s_l0"] > 0 and -1 <= rows[0]["cos_su_mean"] <= 1 and "sum_gamma_alpha" in rows[0]
+    assert "w_norm_single_transition_l_last" in rows[0]
