@@ -407,12 +407,11 @@ class _SigmoidGateMul(torch.autograd.Function):
         W = bf16_weight(w)
         x2 = x16.reshape(-1, x16.shape[-1])
         n = w.shape[0]
-        sg = torch.sigmoid(torch.mm(x2, W.t()))
-        d = dy.reshape(-1, n).to(BF16)
-        d_other = (d * sg).view(o16.shape).to(ctx.dtypes[1])
-        dg = d * o16.reshape(-1, n) * sg * (1 - sg)
+        g = torch.mm(x2, W.t())
+        d = dy.reshape(-1, n).to(BF16).contiguous()
+        dg, d_other = K.sigmoid_gate_bwd(d, g, o16.reshape(-1, n))  # one pass: dy other s (1 - s) and dy s
         dx = torch.mm(dg, W).view(x16.shape).to(ctx.dtypes[0])
-        return dx, _wgrad(dg, x2, w), d_other
+        return dx, _wgrad(dg, x2, w), d_other.view(o16.shape).to(ctx.dtypes[1])
 
 
 def sigmoid_gate_mul(x, w, other):

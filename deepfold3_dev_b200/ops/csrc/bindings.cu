@@ -15,6 +15,7 @@ std::tuple<Tensor, Tensor> df3_plane_layer_norm_bwd(const Tensor&, const Tensor&
 Tensor df3_swiglu_fwd(const Tensor&);
 Tensor df3_swiglu_bwd(const Tensor&, const Tensor&);
 Tensor df3_gated_bwd(const Tensor&, const Tensor&, const c10::optional<Tensor>&);
+std::tuple<Tensor, Tensor> df3_sigmoid_gate_bwd(const Tensor&, const Tensor&, const Tensor&);
 Tensor df3_dropout_shared(const c10::optional<Tensor>&, const Tensor&, int64_t, int64_t, int64_t, bool, double, int64_t,
                           const c10::optional<Tensor>&);
 void df3_adamw_ema(Tensor, const Tensor&, Tensor, Tensor, const c10::optional<Tensor>&, const Tensor&, const Tensor&,
@@ -47,6 +48,7 @@ TORCH_LIBRARY(df3, m) {
   m.def("swiglu_fwd(Tensor x) -> Tensor", &df3_swiglu_fwd);
   m.def("swiglu_bwd(Tensor dy, Tensor x) -> Tensor", &df3_swiglu_bwd);
   m.def("gated_bwd(Tensor dy, Tensor gp, Tensor? mask) -> Tensor", &df3_gated_bwd);
+  m.def("sigmoid_gate_bwd(Tensor dy, Tensor g, Tensor other) -> (Tensor, Tensor)", &df3_sigmoid_gate_bwd);
   m.def("dropout_shared(Tensor? res, Tensor x, int A, int B, int C, bool share_rows, float p, int seed, Tensor? seed_dev=None) -> Tensor",
         &df3_dropout_shared);
   m.def("adamw_ema(Tensor(a!) p, Tensor g, Tensor(b!) m, Tensor(c!) v, Tensor? ema, Tensor decay, Tensor scale, "

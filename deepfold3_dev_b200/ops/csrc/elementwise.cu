@@ -612,6 +612,48 @@ __global__ void gated_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __n
   dgp[r * 2 * D + c] = __float2bfloat16_rn(d * pv * sg * (1.f - sg));
   dgp[r * 2 * D + D + c] = __float2bfloat16_rn(d * sg);
 }
+// Same as gated_bwd_kernel for D a multiple of 8: a thread owns 8 consecutive channels (16-byte accesses).
+__global__ void __launch_bounds__(256) gated_bwd_vec_kernel(const uint4* __restrict__ dy, const uint4* __restrict__ gp,
+                                                             const float* __restrict__ mask, uint4* __restrict__ dgp, int64_t rows,
+                                                             int D8) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= rows * D8) return;
+  const int64_t r = i / D8;
+  const int c = (int)(i - r * D8);
+  float g[8], pv[8], d[8], dg[8], dp[8];
+  unpack8(gp[r * 2 * D8 + c], g);
+  unpack8(gp[r * 2 * D8 + D8 + c], pv);
+  unpack8(dy[i], d);
+  const float m = mask ? mask[r] : 1.f;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    const float sg = sigmoidf_(g[k]);
+    dg[k] = d[k] * m * pv[k] * sg * (1.f - sg);
+    dp[k] = d[k] * m * sg;
+  }
+  dgp[r * 2 * D8 + c] = pack8(dg);
+  dgp[r * 2 * D8 + D8 + c] = pack8(dp);
+}
+
+// Backward of out = sigmoid(g) * other, elementwise: dg = dy other sg (1 - sg), d_other = dy sg. n8 = elements / 8.
+__global__ void __launch_bounds__(256) sigmoid_gate_bwd_kernel(const uint4* __restrict__ dy, const uint4* __restrict__ g,
+                                                                const uint4* __restrict__ other, uint4* __restrict__ dg,
+                                                                uint4* __restrict__ d_other, int64_t n8) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n8) return;
+  float d[8], gv[8], o[8], a[8], b[8];
+  unpack8(dy[i], d);
+  unpack8(g[i], gv);
+  unpack8(other[i], o);
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    const float sg = sigmoidf_(gv[k]);
+    a[k] = d[k] * o[k] * sg * (1.f - sg);
+    b[k] = d[k] * sg;
+  }
+  dg[i] = pack8(a);
+  d_other[i] = pack8(b);
+}
 }  // namespace df3
 
 // ================================================================================================
@@ -785,10 +827,34 @@ Tensor df3_gated_bwd(const Tensor& dy, const Tensor& gp, const c10::optional<Ten
     mp = m.data_ptr<float>();
   }
   const unsigned grid = (unsigned)((rows * D + 255) / 256);
+  if (D % 8 == 0 && reinterpret_cast<uintptr_t>(dy.data_ptr()) % 16 == 0 && reinterpret_cast<uintptr_t>(gp.data_ptr()) % 16 == 0)
+    df3::gated_bwd_vec_kernel<<<(unsigned)((rows * (D / 8) + 255) / 256), 256, 0, stream()>>>(
+        (const uint4*)dy.data_ptr(), (const uint4*)gp.data_ptr(), mp, (uint4*)dgp.data_ptr(), rows, D / 8);
+  else
   df3::gated_bwd_kernel<<<grid, 256, 0, stream()>>>((const __nv_bfloat16*)dy.data_ptr(), (const __nv_bfloat16*)gp.data_ptr(), mp,
                                                    (__nv_bfloat16*)dgp.data_ptr(), rows, D);
   C10_CUDA_KERNEL_LAUNCH_CHECK();
   return dgp;
+}
+
+// (dg, d_other) of out = sigmoid(g) * other for contiguous bf16 tensors of one shape whose size is a multiple of 8
+std::tuple<Tensor, Tensor> df3_sigmoid_gate_bwd(const Tensor& dy, const Tensor& g, const Tensor& other) {
+  TORCH_CHECK(dy.is_cuda() && dy.is_contiguous() && g.is_contiguous() && other.is_contiguous(), "sigmoid_gate_bwd: contiguous CUDA tensors");
+  TORCH_CHECK(dy.scalar_type() == torch::kBFloat16 && g.scalar_type() == torch::kBFloat16 && other.scalar_type() == torch::kBFloat16,
+              "sigmoid_gate_bwd: bf16 tensors");
+  TORCH_CHECK(dy.numel() == g.numel() && dy.numel() == other.numel() && dy.numel() % 8 == 0, "sigmoid_gate_bwd: equal sizes, multiple of 8");
+  c10::cuda::CUDAGuard guard(dy.device());
+  auto dg = torch::empty_like(g), d_other = torch::empty_like(other);
+  const int64_t n8 = dy.numel() / 8;
+  if (n8 == 0) return {dg, d_other};
+  const Tensor* all[5] = {&dy, &g, &other, &dg, &d_other};
+  for (const Tensor* t : all)
+    TORCH_CHECK(reinterpret_cast<uintptr_t>(t->data_ptr()) % 16 == 0, "sigmoid_gate_bwd: 16-byte aligned tensors");
+  df3::sigmoid_gate_bwd_kernel<<<(unsigned)((n8 + 255) / 256), 256, 0, stream()>>>(
+      (const uint4*)dy.data_ptr(), (const uint4*)g.data_ptr(), (const uint4*)other.data_ptr(), (uint4*)dg.data_ptr(),
+      (uint4*)d_other.data_ptr(), n8);
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  return {dg, d_other};
 }
 
 Tensor df3_swiglu_fwd(const Tensor& x) {
