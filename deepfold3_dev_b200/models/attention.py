@@ -54,12 +54,8 @@ class GridSelfAttention(nn.Module):
         bias = ops.head_bias_planes(zn, self.pair_bias.weight)  # [B, H, N, N] (query, key)
         qkv = ops.stacked_linear(zn, self.to_q.weight, self.to_k.weight, self.to_v.weight).view(B, N, N, 3, H, D)
 
-        def heads(t):  # [B, N1, N2, H, D] -> [B, R, H, L, D] with R the independent axis
-            return t.permute(0, 2, 3, 1, 4) if self.transpose else t.permute(0, 1, 3, 2, 4)
-
         key_mask = mask.transpose(1, 2) if self.transpose else mask
-        out = ops.pair_bias_attention(heads(qkv[:, :, :, 0]), heads(qkv[:, :, :, 1]), heads(qkv[:, :, :, 2]), bias,
-                                      key_mask, self.scale)  # fmt: skip
+        out = ops.grid_attention(qkv, bias, key_mask, self.scale, self.transpose)
         out = out.permute(0, 3, 1, 2, 4) if self.transpose else out.permute(0, 1, 3, 2, 4)
         out = out.reshape(B, N, N, H * D)
         out = self.out_proj(ops.sigmoid_gate_mul(zn, self.to_g.weight, out))

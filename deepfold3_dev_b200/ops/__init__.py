@@ -14,6 +14,8 @@ from __future__ import annotations
 
 import collections
 
+import os
+
 import torch
 
 from . import reference as ref
@@ -102,6 +104,21 @@ def pair_bias_attention(q, k, v, bias, key_mask, scale: float, fp32_qk: bool = F
         return nat.pair_bias_attention(q, k, v, bias, key_mask, scale)
     _CENSUS["pair_bias_attention:torch"] += 1
     return ref.pair_bias_attention(q, k, v, bias, key_mask, scale, fp32_qk)
+
+
+def grid_attention(qkv, bias, key_mask, scale: float, transpose: bool):
+    """Row (``transpose=False``) or column attention of the pair tensor from the packed projection [B, N, N, 3, H, D].
+
+    Returns [B, R, H, L, D] like ``pair_bias_attention`` on the three permuted slices, which is also the fallback.
+    """
+    nat = _native(qkv)
+    heads = (lambda t: t.permute(0, 2, 3, 1, 4)) if transpose else (lambda t: t.permute(0, 1, 3, 2, 4))
+    q, k, v = (heads(qkv[:, :, :, i]) for i in range(3))
+    if (nat is not None and nat.has("pair_bias_attention") and "grid_attention_packed" not in os.environ.get("DF3_DISABLE_OPS", "") and qkv.is_contiguous()
+            and torch.is_grad_enabled() and qkv.requires_grad and nat.attention_supported(q, k, v, bias)):
+        _CENSUS["pair_bias_attention:sm100"] += 1
+        return nat.grid_attention_packed(qkv, bias, key_mask, scale, transpose)
+    return pair_bias_attention(q, k, v, bias, key_mask, scale)
 
 
 def window_attention(q, k, v, bias, scale: float):

@@ -9,6 +9,8 @@ from __future__ import annotations
 import collections
 import weakref
 
+import os
+
 import torch
 
 LAUNCHES: collections.Counter = collections.Counter()
@@ -466,7 +468,8 @@ def transition(x, ln_w, ln_b, w1, w2, eps: float = 1e-5):
 # ------------------------------------------------------------------------------------------------
 # Pair-bias attention: tcgen05 forward kernel; backward in row chunks sized to stay in L2, with the
 # softmax/bias-gradient algebra in one kernel per chunk and the five small products on the library GEMM.
-ATTN_BWD_CHUNK_BYTES = 40 * 1024 * 1024
+# bytes of one score chunk of the attention backward (two such buffers stay L2-resident at the default)
+ATTN_BWD_CHUNK_BYTES = int(os.environ.get("DF3_ATTN_BWD_CHUNK_MB", "40")) * 1024 * 1024
 
 
 def attention_supported(q, k, v, bias) -> bool:
@@ -495,6 +498,45 @@ class _Attention(torch.autograd.Function):
 
 def pair_bias_attention(q, k, v, bias, key_mask, scale: float):
     return _Attention.apply(q, k, v, bias, key_mask, float(scale))
+
+
+def _grid_heads(t, transpose: bool):
+    """[B, N1, N2, H, D] -> [B, R, H, L, D] (a view): R is the axis attention does not mix."""
+    return t.permute(0, 2, 3, 1, 4) if transpose else t.permute(0, 1, 3, 2, 4)
+
+
+class _GridAttentionPacked(torch.autograd.Function):
+    """Row / column attention on the packed projection ``qkv`` [B, N, N, 3, H, D].
+
+    Taking the packed tensor keeps the split out of autograd: backward writes dq, dk and dv straight into the three
+    slots of one gradient tensor (three strided copies) instead of three zero-filled full-size tensors that are then
+    added together.
+    """
+
+    @staticmethod
+    def forward(ctx, qkv, bias, key_mask, scale, transpose):
+        q, k, v = (_grid_heads(qkv[:, :, :, i], transpose) for i in range(3))
+        need = ctx.needs_input_grad[0] or ctx.needs_input_grad[1]
+        out, lse = K.attention_fwd(q, k, v, bias, key_mask, scale, need)
+        ctx.save_for_backward(qkv, bias, key_mask, out, lse)
+        ctx.scale, ctx.transpose = scale, transpose
+        return out
+
+    @staticmethod
+    def backward(ctx, d_out):
+        qkv, bias, key_mask, out, lse = ctx.saved_tensors
+        q, k, v = (_grid_heads(qkv[:, :, :, i], ctx.transpose) for i in range(3))
+        want_bias = bias is not None and ctx.needs_input_grad[1]
+        dq, dk, dv, dbias = K.attention_bwd(q, k, v, out, d_out, bias, key_mask, lse, ctx.scale, want_bias,
+                                            ATTN_BWD_CHUNK_BYTES)  # fmt: skip
+        dqkv = torch.empty_like(qkv)
+        for i, g in enumerate((dq, dk, dv)):
+            _grid_heads(dqkv[:, :, :, i], ctx.transpose).copy_(g)
+        return dqkv, (dbias.to(bias.dtype) if want_bias else None), None, None, None
+
+
+def grid_attention_packed(qkv, bias, key_mask, scale: float, transpose: bool):
+    return _GridAttentionPacked.apply(qkv, bias, key_mask, float(scale), bool(transpose))
 
 
 def check_status() -> None:

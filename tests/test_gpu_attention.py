@@ -62,3 +62,41 @@ def test_strided_views_no_bias_fp32_bias(df3):
     ref, _ = _reference(qc, kc, vc, bias, None, D**-0.5)
     assert (out.float() - ref).abs().max().item() < 3e-2
     assert df3.gemm_status() == 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("transpose", [False, True])
+def test_grid_attention_packed_gradients(transpose, monkeypatch):
+    """The packed-projection path gives the gradients of the three-slice path and of the fp32 statement."""
+    import torch
+
+    from deepfold3_dev_b200 import ops
+    from deepfold3_dev_b200.ops import reference as ref
+
+    torch.manual_seed(0)
+    B, N, H, D = 1, 64, 4, 32
+    qkv0 = torch.randn(B, N, N, 3, H, D, device="cuda")
+    bias0 = torch.randn(B, H, N, N, device="cuda")
+    mask = (torch.rand(B, N, N, device="cuda") > 0.1).float()
+    w = torch.randn(B, N, H, N, D, device="cuda")
+
+    def run(packed: bool, fp32: bool = False):
+        monkeypatch.setenv("DF3_DISABLE_OPS", "" if packed else "grid_attention_packed")
+        qkv = (qkv0.clone() if fp32 else qkv0.bfloat16()).requires_grad_(True)
+        bias = (bias0.clone() if fp32 else bias0.bfloat16()).requires_grad_(True)
+        if fp32:
+            heads = (lambda t: t.permute(0, 2, 3, 1, 4)) if transpose else (lambda t: t.permute(0, 1, 3, 2, 4))
+            out = ref.pair_bias_attention(heads(qkv[:, :, :, 0]), heads(qkv[:, :, :, 1]), heads(qkv[:, :, :, 2]), bias, mask, D**-0.5)
+        else:
+            out = ops.grid_attention(qkv, bias, mask, D**-0.5, transpose)
+        (out.float() * w).sum().backward()
+        return out.float().detach(), qkv.grad.float(), bias.grad.float()
+
+    ops.census(reset=True)
+    o1, g1, b1 = run(True)
+    o2, g2, b2 = run(False)
+    o3, g3, b3 = run(True, fp32=True)
+    assert ops.census().get("pair_bias_attention:sm100", 0) == 2
+    assert torch.equal(o1, o2) and torch.allclose(g1, g2, atol=1e-6) and torch.allclose(b1, b2, atol=1e-6)
+    for got, want in ((o1, o3), (g1, g3), (b1, b3)):
+        assert (got - want).abs().max() <= 0.03 * want.abs().max() + 1e-3
