@@ -138,7 +138,7 @@ def _inference_options(f):
         click.option("--guidance", "guidance", multiple=True, help="scale[:drop[:sigma_lo-sigma_hi]] (repeatable)."),
         click.option("--restraint-weight", type=float, default=0.0),
         click.option("--allow-missing-keys", is_flag=True),
-        click.option("--ccd", type=click.Path(), default=None, help="Conformer table (JSON) for ligands and modified residues."),
+        click.option("--ccd", type=click.Path(), default=None, help="components.cif[.gz] or a JSON conformer table, for ligands and modified residues."),
         click.option("--det", is_flag=True, help="Deterministic recipe."),
     ]
     for o in reversed(opts):
@@ -155,7 +155,7 @@ def _prepare_model(params, device, optim, snapshot, allow_missing_keys, det, ccd
     if det:
         apply_det_recipe()
     if ccd:
-        ref_conformers.load_table(ccd)
+        ref_conformers.set_ccd_source(ccd)
     device = device or ("cuda" if torch.cuda.is_available() else "cpu")
     model, cfg = build_model(params, device, optim, snapshot, allow_missing=allow_missing_keys)
     return model, cfg, device

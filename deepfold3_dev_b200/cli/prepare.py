@@ -59,6 +59,17 @@ def structures(mmcif_dir, out_dir, workers, no_assembly, limit, **filt):
     click.echo(json.dumps(counts))
 
 
+@prepare.command("ccd-table")
+@click.argument("components_cif", type=click.Path(exists=True))
+@click.argument("out_json", type=click.Path())
+@click.option("--code", "codes", multiple=True, help="Only these component codes (default: all).")
+def ccd_table(components_cif, out_json, codes):
+    """Export reference conformers (ideal coordinates, charges, leaving atoms, bonds) from components.cif[.gz] to JSON."""
+    from ..data.ccd import export_table
+
+    click.echo(f"{export_table(components_cif, out_json, set(codes) or None)} components -> {out_json}")
+
+
 @prepare.command("filter")
 @click.argument("data_dir", type=click.Path(exists=True))
 @click.option("--output", type=click.Path(), default=None, help="Manifest to write (default: in place).")

@@ -55,7 +55,15 @@ class InferenceInput:
     @classmethod
     def from_job(cls, job: JobInput, msa_crop_size: int = 16384, msa_pairing: str = "auto") -> InferenceInput:
         if job.user_ccd:
-            ref_conformers.load_table(job.user_ccd)
+            if "data_" in job.user_ccd and "\n" in job.user_ccd:
+                ref_conformers.load_component_text(job.user_ccd)
+            else:
+                ref_conformers.load_table(job.user_ccd)
+        needed = set()
+        for chain in job.chains:
+            needed.update(getattr(chain, "ccd_codes", ()) or ())
+            needed.update(code for code, _ in (getattr(chain, "modifications", ()) or ()))
+        ref_conformers.ensure_components(needed)
         tok: dict[str, list] = {k: [] for k in ("res_type", "mol_type", "asym", "entity", "sym", "res_idx", "atoms")}
         chain_names, chain_cols, chain_msas = [], [], []
         entity_of: dict = {}

@@ -34,6 +34,40 @@ def load_table(path: str) -> int:
     return len(data)
 
 
+CCD_PATH: str | None = None  # components.cif[.gz]; looked up lazily, one streaming pass per batch of missing codes
+
+
+def set_ccd_source(path: str | None) -> None:
+    """A ``.json`` conformer table is loaded at once; ``components.cif[.gz]`` is remembered and read on demand."""
+    global CCD_PATH
+    if path and str(path).endswith(".json"):
+        load_table(path)
+    else:
+        CCD_PATH = path
+
+
+def ensure_components(codes) -> None:
+    """Load the listed component codes from the dictionary file if they are not known yet."""
+    missing = {c.upper() for c in codes if c and c.upper() not in _TABLE and c.upper() not in const.RESIDUE_ATOMS}
+    if missing and CCD_PATH:
+        from . import ccd
+
+        ccd.register(ccd.load_components(CCD_PATH, missing))
+
+
+def load_component_text(text: str) -> int:
+    """Custom components given inline as CIF text (the ``userCCD`` field of a prediction job)."""
+    from . import ccd
+
+    found = {}
+    for block in text.split("\ndata_"):
+        block = block if block.startswith("data_") else "data_" + block
+        comp = ccd.parse_component(block)
+        if comp is not None and comp.atoms:
+            found[comp.code] = comp
+    return ccd.register(found)
+
+
 def _zigzag(start, n: int, step: float = 1.5):
     """``n`` points leaving ``start`` along -z with alternating lateral offsets (a schematic carbon chain)."""
     pts, p = [], np.asarray(start, dtype=np.float64)

@@ -205,3 +205,73 @@ def test_structure_dataset_on_the_fly(tmp_path):
     assert x["msa"].shape[0] == 5  # query + two alignment rows for each of the two copies
     b = collate([x, d[1]])
     assert b["res_type"].shape == (2, 6) and b["bond_matrix"].shape == (2, 6, 6, 1)
+
+
+_PLM_CIF = """data_ZZ1
+_chem_comp.id ZZ1
+_chem_comp.name 'TEST ACID'
+loop_
+_chem_comp_atom.comp_id
+_chem_comp_atom.atom_id
+_chem_comp_atom.type_symbol
+_chem_comp_atom.charge
+_chem_comp_atom.pdbx_leaving_atom_flag
+_chem_comp_atom.model_Cartn_x
+_chem_comp_atom.model_Cartn_y
+_chem_comp_atom.model_Cartn_z
+_chem_comp_atom.pdbx_model_Cartn_x_ideal
+_chem_comp_atom.pdbx_model_Cartn_y_ideal
+_chem_comp_atom.pdbx_model_Cartn_z_ideal
+ZZ1 C1  C 0  N 9.0 9.0 9.0 0.000 0.000 0.000
+ZZ1 O1  O -1 N 9.0 9.0 9.0 1.250 0.000 0.000
+ZZ1 O2  O 0  Y 9.0 9.0 9.0 -0.600 1.100 0.000
+ZZ1 "C1'" C 0 N 9.0 9.0 9.0 -0.800 -1.200 0.300
+ZZ1 H1  H 0  N 9.0 9.0 9.0 -1.800 -1.200 0.300
+loop_
+_chem_comp_bond.comp_id
+_chem_comp_bond.atom_id_1
+_chem_comp_bond.atom_id_2
+_chem_comp_bond.value_order
+ZZ1 C1 O1 SING
+ZZ1 C1 O2 DOUB
+ZZ1 C1 "C1'" SING
+ZZ1 "C1'" H1 SING
+data_ZZ2
+_chem_comp.id ZZ2
+loop_
+_chem_comp_atom.comp_id
+_chem_comp_atom.atom_id
+_chem_comp_atom.type_symbol
+_chem_comp_atom.charge
+_chem_comp_atom.model_Cartn_x
+_chem_comp_atom.model_Cartn_y
+_chem_comp_atom.model_Cartn_z
+ZZ2 MG MG 2 1.0 2.0 3.0
+"""
+
+
+def test_component_dictionary_lookup(tmp_path):
+    from deepfold3_dev_b200.data import ccd, ref_conformers
+    from deepfold3_dev_b200.data.inference_input import InferenceInput
+    from deepfold3_dev_b200.data.parse.json_input import JobInput, LigandChainInput, ProteinChainInput
+
+    path = tmp_path / "components.cif"
+    path.write_text(_PLM_CIF)
+    comps = ccd.load_components(str(path), {"zz1"})
+    assert list(comps) == ["ZZ1"]
+    c = comps["ZZ1"]
+    assert c.atoms == ["C1", "O1", "O2", "C1'"] and c.elements == [6, 8, 8, 6] and c.charges == [0, -1, 0, 0]
+    assert c.leaving == [False, False, True, False] and c.bonds == [(0, 1, 1), (0, 2, 2), (0, 3, 1)]
+    assert np.allclose(c.coords[1], [1.25, 0, 0])  # ideal coordinates, not the model ones
+    assert ccd.leaving_atom_sets(comps)["ZZ1"] == {"O2"} and ccd.atom_name_sets(comps)["ZZ1"] == {"C1", "O1", "O2", "C1'"}
+    assert np.allclose(ccd.load_components(str(path))["ZZ2"].coords[0], [1, 2, 3])  # model coordinates as the fallback
+    ref_conformers.set_ccd_source(str(path))
+    try:
+        job = JobInput("lig", [ProteinChainInput(["A"], "GASG"), LigandChainInput(["L"], ["ZZ1"])])
+        inp = InferenceInput.from_job(job)
+        assert inp.num_tokens == 4 + 4 and int(inp.features["ref_element"][-3, 0]) == 8
+        assert ccd.export_table(str(path), str(tmp_path / "t.json")) == 2
+    finally:
+        ref_conformers.set_ccd_source(None)
+        ref_conformers._TABLE.pop("ZZ1", None)
+        ref_conformers._TABLE.pop("ZZ2", None)
