@@ -84,7 +84,44 @@ class InferenceInput:
         feats = _token_features(tok)
         feats.update(_msa_features(feats, chain_cols, chain_msas, msa_crop_size, msa_pairing))
         feats.update(_template_features(feats, chain_cols, chain_msas))
+        feats["bond_matrix"] = _bond_matrix(tok, chain_names, job.bonded_atom_pairs)
         return cls(feats, chain_names, job.name, list(job.seeds))
+
+
+def _bond_matrix(tok, chain_names, bonded_atom_pairs) -> torch.Tensor:
+    """[N, N, 1] float: bonds between atom tokens of one component (from its dictionary entry) and the job's explicit
+    ``bondedAtomPairs`` (chain id, 1-based residue, atom name), where at least one end is an atom token."""
+    N = len(tok["res_type"])
+    out = torch.zeros(N, N, 1)
+    where: dict[tuple[int, int, str], int] = {}
+    groups: dict[tuple[int, int], list[int]] = {}
+    for i in range(N):
+        names = tok["atoms"][i][1]
+        key = (tok["asym"][i], tok["res_idx"][i])
+        if len(names) == 1:  # an atom token (ligand, ion or atomised residue)
+            where[(key[0], key[1], names[0])] = i
+            groups.setdefault(key, []).append(i)
+        else:
+            for a in names:
+                where.setdefault((key[0], key[1], a), i)
+    for key, members in groups.items():
+        code = tok["atoms"][members[0]][0]
+        entry = ref_conformers._TABLE.get(str(code).upper())
+        if not entry or not entry.get("bonds"):
+            continue
+        atom_names = entry["atoms"]
+        for a, b, _order in entry["bonds"]:
+            i, j = where.get((key[0], key[1], atom_names[a])), where.get((key[0], key[1], atom_names[b]))
+            if i is not None and j is not None and i != j:
+                out[i, j, 0] = out[j, i, 0] = 1.0
+    asym_of = {name: k for k, name in enumerate(chain_names)}
+    for pair in bonded_atom_pairs or ():
+        ends = []
+        for chain, res, atom in (pair.a, pair.b):
+            ends.append(where.get((asym_of.get(chain, -1), int(res) - 1, atom)))
+        if None not in ends and ends[0] != ends[1]:
+            out[ends[0], ends[1], 0] = out[ends[1], ends[0], 0] = 1.0
+    return out
 
 
 def _template_features(feats, chain_cols, chains, max_templates: int = 4) -> dict:

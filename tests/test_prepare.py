@@ -270,6 +270,13 @@ def test_component_dictionary_lookup(tmp_path):
         job = JobInput("lig", [ProteinChainInput(["A"], "GASG"), LigandChainInput(["L"], ["ZZ1"])])
         inp = InferenceInput.from_job(job)
         assert inp.num_tokens == 4 + 4 and int(inp.features["ref_element"][-3, 0]) == 8
+        bm = inp.features["bond_matrix"][..., 0]
+        assert bm.shape == (8, 8) and bm[4, 5] == 1 and bm[5, 4] == 1 and bm[4, 6] == 1 and bm[4, 7] == 1 and bm.sum() == 6
+        from deepfold3_dev_b200.data.parse.json_input import BondedAtomPair
+
+        job.bonded_atom_pairs = [BondedAtomPair(("A", 3, "OG"), ("L", 1, "O1"))]
+        bm2 = InferenceInput.from_job(job).features["bond_matrix"][..., 0]
+        assert bm2[2, 5] == 1 and bm2[5, 2] == 1 and bm2.sum() == 8
         assert ccd.export_table(str(path), str(tmp_path / "t.json")) == 2
     finally:
         ref_conformers.set_ccd_source(None)
