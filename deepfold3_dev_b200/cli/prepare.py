@@ -316,11 +316,6 @@ def plm_train(config, output, resume, overrides, dry_run):
     click.echo(json.dumps(trainer.train()))
 
 
-def register(cli) -> None:
-    for cmd in (prepare, scan_mmcif, inspect_example, plm_prepare, plm_train, evaluate):
-        cli.add_command(cmd)
-
-
 @click.command("evaluate")
 @click.argument("predicted", type=click.Path(exists=True))
 @click.argument("experimental", type=click.Path(exists=True))
@@ -330,3 +325,36 @@ def evaluate(predicted, experimental, assembly):
     from ..evaluation.compare import compare_files
 
     click.echo(json.dumps(compare_files(predicted, experimental, assembly), indent=1))
+
+
+@click.command("prepare-templates")
+@click.option("--m8", "m8_path", type=click.Path(exists=True), required=True, help="Template search hits (mmseqs .m8 with CIGAR).")
+@click.option("--pdb-mmcif-dir", type=click.Path(exists=True), required=True)
+@click.option("--output-dir", type=click.Path(), required=True)
+@click.option("--index", type=int, default=0, help="Chain index in the job (names the JSON file).")
+@click.option("--max-templates", type=int, default=4)
+@click.option("--max-template-date", default=None, help="YYYY-MM-DD release cut-off.")
+def prepare_templates(m8_path, pdb_mmcif_dir, output_dir, index, max_templates, max_template_date):
+    """Turn template search hits into the templates JSON and mmCIF files a prediction job points at."""
+    from ..data.templates import prepare_job_templates
+
+    with open(m8_path) as f:
+        hits = prepare_job_templates(f.read(), pdb_mmcif_dir, output_dir, index, max_templates, max_template_date)
+    click.echo(f"{len(hits)} templates -> {output_dir}/templates_{index}.json")
+
+
+@click.command("build-pdb-cache")
+@click.argument("mmcif_dir", type=click.Path(exists=True))
+@click.argument("out_dir", type=click.Path())
+@click.option("--limit", type=int, default=0)
+def build_pdb_cache(mmcif_dir, out_dir, limit):
+    """Cache dense per-chain coordinates of every protein chain under MMCIF_DIR for template featurisation."""
+    from ..data.templates import build_chain_cache
+
+    click.echo(f"{build_chain_cache(mmcif_dir, out_dir, limit)} chains -> {out_dir}")
+
+
+def register(cli) -> None:
+    for cmd in (prepare, scan_mmcif, inspect_example, plm_prepare, plm_train, evaluate, prepare_templates, build_pdb_cache):
+        cli.add_command(cmd)
+

@@ -174,3 +174,96 @@ def load_json_templates(entries: list[dict], base_dir: str = ".", max_templates:
             if tmp is not None:
                 os.unlink(tmp.name)
     return out
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# template preparation for prediction jobs and a per-chain coordinate cache
+# (reference: scripts/prepare_templates.py, scripts/build_pdb_cache.py, data/parse/pdb_chain_cache.py)
+# ---------------------------------------------------------------------------------------------------------------
+def find_pdb_mmcif(pdb_id: str, root: str) -> str | None:
+    """``root/<id>.cif[.gz]`` or the wwPDB divided layout ``root/<middle two characters>/<id>.cif[.gz]``."""
+    import os
+
+    pid = pdb_id.lower()
+    for base in (root, os.path.join(root, pid[1:3])):
+        for ext in (".cif", ".cif.gz"):
+            path = os.path.join(base, pid + ext)
+            if os.path.exists(path):
+                return path
+    return None
+
+
+def save_template_chain(chain: TemplateChain, path: str) -> None:
+    np.savez_compressed(path, res_names=np.array(chain.res_names), coords=chain.coords.astype(np.float32), atom_mask=chain.atom_mask)
+
+
+def load_template_chain(path: str, query_indices, template_indices) -> TemplateChain:
+    z = np.load(path)
+    return TemplateChain([str(x) for x in z["res_names"]], z["coords"], z["atom_mask"],
+                         {int(q): int(t) for q, t in zip(query_indices, template_indices)})  # fmt: skip
+
+
+def build_chain_cache(mmcif_dir: str, out_dir: str, limit: int = 0) -> int:
+    """One ``<pdb>_<chain>.npz`` (residue names, dense atom coordinates, mask) per protein chain of every entry."""
+    import os
+
+    from .parse.mmcif import parse_mmcif
+    from .prepare.pipeline import find_mmcif_files
+
+    os.makedirs(out_dir, exist_ok=True)
+    n = 0
+    for path in find_mmcif_files(mmcif_dir)[: limit or None]:
+        try:
+            _st, rec = parse_mmcif(path, use_assembly=False)
+        except Exception:  # noqa: BLE001 - unreadable entries are skipped
+            continue
+        for ci in rec.chains:
+            if ci.mol_type != const.MOL_PROTEIN:
+                continue
+            chain = template_chain_from_mmcif(path, ci.auth_chain_name or ci.chain_name, [], [])
+            if chain is not None:
+                save_template_chain(chain, os.path.join(out_dir, f"{rec.id}_{ci.auth_chain_name or ci.chain_name}.npz"))
+                n += 1
+    return n
+
+
+def prepare_job_templates(m8_text: str, mmcif_dir: str, out_dir: str, index: int = 0, max_templates: int = 4,
+                          max_release_date: str | None = None, min_aligned: int = 10, query_length: int | None = None) -> list[dict]:  # fmt: skip
+    """Hits of one query -> ``out_dir/templates_<index>.json`` plus a copy of each hit's mmCIF next to it.
+
+    Hits are taken in file order (best first). A hit is skipped when its entry is missing, released after
+    ``max_release_date`` (entries without a date are skipped when a cut-off is set), aligned over fewer than
+    ``min_aligned`` positions, or repeats an entry and chain already taken.
+    """
+    import json
+    import os
+    import shutil
+
+    from .parse.mmcif import read_structure_info
+
+    os.makedirs(out_dir, exist_ok=True)
+    taken, seen = [], set()
+    for hit in parse_m8(m8_text):
+        if len(taken) >= max_templates:
+            break
+        key = (hit["pdb_id"], hit["chainId"])
+        if key in seen or len(hit["queryIndices"]) < min_aligned:
+            continue
+        if query_length is not None and max(hit["queryIndices"], default=0) >= query_length:
+            continue
+        src = find_pdb_mmcif(hit["pdb_id"], mmcif_dir)
+        if src is None:
+            continue
+        if max_release_date is not None:
+            info = read_structure_info(src)
+            if info is None or info.released is None or info.released > max_release_date:
+                continue
+        if template_chain_from_mmcif(src, hit["chainId"], hit["queryIndices"], hit["templateIndices"]) is None:
+            continue
+        seen.add(key)
+        name = f"{hit['pdb_id']}_{hit['chainId']}.cif" + (".gz" if src.endswith(".gz") else "")
+        shutil.copyfile(src, os.path.join(out_dir, name))
+        taken.append({"name": name, "chainId": hit["chainId"], "queryIndices": hit["queryIndices"], "templateIndices": hit["templateIndices"]})
+    with open(os.path.join(out_dir, f"templates_{index}.json"), "w") as f:
+        json.dump(taken, f)
+    return taken

@@ -282,3 +282,24 @@ def test_component_dictionary_lookup(tmp_path):
         ref_conformers.set_ccd_source(None)
         ref_conformers._TABLE.pop("ZZ1", None)
         ref_conformers._TABLE.pop("ZZ2", None)
+
+
+@pytest.mark.skipif(not os.path.isdir(EXAMPLES), reason="reference example files not mounted")
+def test_prepare_job_templates_from_hits(tmp_path):
+    from deepfold3_dev_b200.data.templates import build_chain_cache, load_json_templates, load_template_chain, prepare_job_templates
+
+    src = tmp_path / "pdb"
+    src.mkdir()
+    import shutil
+
+    for name in ("7yf1_A.cif", "5hz8_A.cif"):
+        shutil.copy(os.path.join(EXAMPLES, "9m22_msa", "templates", name), src / (name.split("_")[0] + ".cif"))
+    m8 = open(os.path.join(EXAMPLES, "9m22_msa", "pdb70.m8")).read()
+    hits = prepare_job_templates(m8, str(src), str(tmp_path / "out"), max_release_date="2022-12-31")
+    assert [h["name"] for h in hits] == ["7yf1_A.cif", "5hz8_A.cif"]  # the two entries on disk, best first
+    assert prepare_job_templates(m8, str(src), str(tmp_path / "old"), max_release_date="2020-01-01")[0]["name"] == "5hz8_A.cif"
+    chains = load_json_templates(hits, str(tmp_path / "out"))
+    assert len(chains) == 2 and chains[0].atom_mask.sum() > 500
+    assert build_chain_cache(str(src), str(tmp_path / "cache")) >= 2
+    cached = load_template_chain(str(tmp_path / "cache" / "7yf1_A.npz"), hits[0]["queryIndices"], hits[0]["templateIndices"])
+    assert cached.res_names == chains[0].res_names and np.allclose(cached.coords, chains[0].coords)
