@@ -303,3 +303,21 @@ def test_prepare_job_templates_from_hits(tmp_path):
     assert build_chain_cache(str(src), str(tmp_path / "cache")) >= 2
     cached = load_template_chain(str(tmp_path / "cache" / "7yf1_A.npz"), hits[0]["queryIndices"], hits[0]["templateIndices"])
     assert cached.res_names == chains[0].res_names and np.allclose(cached.coords, chains[0].coords)
+
+
+def test_structure_mmcif_write_read_cycle(tmp_path):
+    from deepfold3_dev_b200.data.featurize import tokenize_structure
+    from deepfold3_dev_b200.io.structure_mmcif import with_coordinates, write_structure
+
+    p = tmp_path / "t.cif"
+    p.write_text(_mini_cif())
+    st, _ = parse_mmcif(str(p))
+    write_structure(st, str(tmp_path / "w.cif"))
+    back, _ = parse_mmcif(str(tmp_path / "w.cif"), use_assembly=False)
+    assert len(back.chains) == len(st.chains) and np.array_equal(back.residues["name"], st.residues["name"])
+    assert np.array_equal(back.atoms["is_present"], st.atoms["is_present"])
+    ok = st.atoms["is_present"]
+    assert np.allclose(back.coords()[ok], st.coords()[ok], atol=2e-3) and back.chain_canonical_seqs[0] == "GASG"
+    tok, rows, _ = tokenize_structure(st)
+    moved = with_coordinates(st, np.ones((len(rows), 24, 3), np.float32), rows, np.full((len(rows), 24), 77.0))
+    assert moved.atoms["is_present"].all() and float(moved.atoms["b_factor"].min()) == 77.0 and float(moved.coords().max()) == 1.0
