@@ -17,7 +17,9 @@ from deepfold3_dev_b200.data.prepare.filters import filter_structure_metadata, s
 from deepfold3_dev_b200.data.templates import cigar_to_index_pairs, parse_m8
 from deepfold3_dev_b200.data.types import ATOM_DTYPE, MSA, Record, Structure, StructureInfo, load_manifest
 
-EXAMPLES = "/root/reference/examples"
+# example jobs of the reference distribution (JSON + alignments + template mmCIF files); tests that need them are skipped
+# when DF3_REFERENCE_EXAMPLES does not point at a copy
+EXAMPLES = os.environ.get("DF3_REFERENCE_EXAMPLES", os.path.join(os.path.dirname(__file__), "..", "..", "reference", "examples"))
 
 
 def _mini_cif(shift=(0.0, 0.0, 0.0), second_far=True) -> str:
