@@ -135,8 +135,20 @@ def _inference_options(f):
         click.option("--logits-scheme", type=click.Choice(["f16", "u8", "f32"]), default="f16"),
         click.option("--bucket/--no-bucket", default=True),
         click.option("--sample-chunk", type=int, default=0),
-        click.option("--guidance", "guidance", multiple=True, help="scale[:drop[:sigma_lo-sigma_hi]] (repeatable)."),
+        click.option("--guidance", "guidance", multiple=True,
+                     help="W[@TARGET[@LO..HI]] with TARGET full | all (every interface) | A:B[,C:D] (repeatable); scale[:drop[:lo-hi]] also accepted."),
+        click.option("--allow-guidance-overlap", is_flag=True),
+        click.option("--restraint", "restraints", multiple=True, help="SEL:SEL[@DIST[@LO..HI]] pulls two residue groups together (repeatable)."),
+        click.option("--restraint-pair", "restraint_pairs", multiple=True, help="Like --restraint, residue i of one side with residue i of the other."),
+        click.option("--repel", "repels", multiple=True, help="SEL:SEL[@DIST[@LO..HI]] keeps two groups at least DIST apart."),
+        click.option("--restraint-rigid/--restraint-residues", default=True, help="Move whole chains rigidly, or the named residues alone."),
+        click.option("--restraint-after-step/--restraint-before-step", default=False),
+        click.option("--restraint-after-sigma", type=float, default=16.0),
+        click.option("--restraint-max-step", type=float, default=2.0),
         click.option("--restraint-weight", type=float, default=0.0),
+        click.option("--msa-pairing", type=click.Choice(["auto", "species", "none"]), default="auto"),
+        click.option("--matmul-precision", type=click.Choice(["highest", "high", "medium"]), default=None),
+        click.option("--plot-confidences", is_flag=True, help="Write a pLDDT / PAE figure next to every confidences JSON."),
         click.option("--allow-missing-keys", is_flag=True),
         click.option("--ccd", type=click.Path(), default=None, help="components.cif[.gz] or a JSON conformer table, for ligands and modified residues."),
         click.option("--det", is_flag=True, help="Deterministic recipe."),
@@ -161,6 +173,43 @@ def _prepare_model(params, device, optim, snapshot, allow_missing_keys, det, ccd
     return model, cfg, device
 
 
+def _job_steering(inp, guidance, allow_overlap, restraints, restraint_pairs, repels, weight, rigid, after_step, after_sigma, max_step):
+    """Guidance terms and restraint arguments of one job (selectors are resolved against the job's chains)."""
+    from ..models.guidance import build_guidance_terms, parse_guidance_spec
+    from ..models.restraints import build_restraints, parse_restraint_spec
+
+    feats = inp.features
+    chain_index = {name: i for i, name in enumerate(inp.chain_names)}
+    n = int(feats["res_type"].shape[0])
+    terms = None
+    if guidance:
+        if all("@" in g or g.replace(".", "", 1).replace("-", "", 1).isdigit() for g in guidance) and not any(":" in g.split("@")[0] for g in guidance):
+            specs = [parse_guidance_spec(g) for g in guidance]
+            terms = build_guidance_terms(specs, feats["asym_id"], chain_index, n, feats["residue_index"], allow_overlap)
+        else:
+            terms = _guidance_terms(guidance)
+    specs = [parse_restraint_spec(t) for t in restraints] + [parse_restraint_spec(t, paired=True) for t in restraint_pairs]
+    specs += [parse_restraint_spec(t, repel=True) for t in repels]
+    kwargs = None
+    if specs:
+        built = build_restraints(specs, feats["asym_id"], chain_index, n, feats["residue_index"])
+        kwargs = dict(restraints=built, restraint_weight=weight or 1.0, restraint_rigid=rigid, restraint_max_step=max_step,
+                      restraint_after_step=after_step, restraint_after_sigma=after_sigma)  # fmt: skip
+    return terms, kwargs
+
+
+def _plot_outputs(out_dir: str) -> None:
+    from ..io.plot import plot_confidences
+
+    for base, _dirs, files in os.walk(out_dir):
+        for f in files:
+            if (f == "confidences.json" or f.endswith("_confidences.json")) and "summary" not in f:
+                try:
+                    plot_confidences(os.path.join(base, f))
+                except Exception as exc:  # noqa: BLE001 - a figure must not fail the prediction
+                    logging.getLogger(__name__).warning("plot of %s failed: %r", f, exc)
+
+
 def _guidance_terms(specs):
     from ..models.diffusion_modules import GuidanceTerm
 
@@ -183,7 +232,9 @@ def _guidance_terms(specs):
 @click.option("--output", type=click.Path(), required=True)
 @_inference_options
 def inference(msa, json_path, sequence, mol_type, output, params, num_recycles, num_samples, msa_crop_size, snapshot,
-              seeds, device, optim, precision, logits_scheme, bucket, sample_chunk, guidance, restraint_weight,
+              seeds, device, optim, precision, logits_scheme, bucket, sample_chunk, guidance, allow_guidance_overlap,
+              restraints, restraint_pairs, repels, restraint_rigid, restraint_after_step, restraint_after_sigma,
+              restraint_max_step, restraint_weight, msa_pairing, matmul_precision, plot_confidences,
               allow_missing_keys, ccd, det):  # fmt: skip
     """Predict the structure of one job."""
     _setup_logging()
@@ -193,8 +244,12 @@ def inference(msa, json_path, sequence, mol_type, output, params, num_recycles, 
     from ..inference.runner import run_job
 
     model, cfg, device = _prepare_model(params, device, optim, snapshot, allow_missing_keys, det, ccd)
+    if matmul_precision:
+        torch.set_float32_matmul_precision(matmul_precision)
     if json_path:
-        inputs = InferenceInput.from_json(json_path, msa_crop_size)
+        from ..data.parse.json_input import parse_json_input
+
+        inputs = [InferenceInput.from_job(job, msa_crop_size, msa_pairing) for job in parse_json_input(json_path)]
     elif msa:
         inputs = [InferenceInput.from_a3m(msa, mol_type, msa_crop_size=msa_crop_size)]
     elif sequence:
@@ -204,9 +259,13 @@ def inference(msa, json_path, sequence, mol_type, output, params, num_recycles, 
     model.cfg.msa_crop_size = msa_crop_size
     for inp in inputs:
         out_dir = output if len(inputs) == 1 else os.path.join(output, inp.name)
+        terms, rkw = _job_steering(inp, guidance, allow_guidance_overlap, restraints, restraint_pairs, repels, restraint_weight,
+                                   restraint_rigid, restraint_after_step, restraint_after_sigma, restraint_max_step)  # fmt: skip
         summaries = run_job(model, inp, out_dir, device, list(seeds) or None, num_recycles, num_samples,
                             getattr(torch, DTYPES[precision]), bucket, sample_chunk, logits_scheme=logits_scheme,
-                            guidance_terms=_guidance_terms(guidance), manifest_fields={"params": params, "optim": optim})  # fmt: skip
+                            guidance_terms=terms, restraint_kwargs=rkw, manifest_fields={"params": params, "optim": optim})  # fmt: skip
+        if plot_confidences:
+            _plot_outputs(out_dir)
         best = max(summaries, key=lambda s: s["ranking_score"])
         click.echo(f"{inp.name}: {len(summaries)} samples, best ranking score {best['ranking_score']:.3f} "
                    f"(seed {best['seed']}, sample {best['sample']}) -> {out_dir}")  # fmt: skip
@@ -220,7 +279,9 @@ def inference(msa, json_path, sequence, mol_type, output, params, num_recycles, 
 @_inference_options
 def inference_batch(inputs_file, output_template, skip_existing, save_distogram, params, num_recycles, num_samples,
                     msa_crop_size, snapshot, seeds, device, optim, precision, logits_scheme, bucket, sample_chunk,
-                    guidance, restraint_weight, allow_missing_keys, ccd, det):  # fmt: skip
+                    guidance, allow_guidance_overlap, restraints, restraint_pairs, repels, restraint_rigid,
+                    restraint_after_step, restraint_after_sigma, restraint_max_step, restraint_weight, msa_pairing,
+                    matmul_precision, plot_confidences, allow_missing_keys, ccd, det):  # fmt: skip
     """Predict many jobs with one model load; finished seeds are skipped on a re-run."""
     _setup_logging()
     import torch
@@ -230,15 +291,26 @@ def inference_batch(inputs_file, output_template, skip_existing, save_distogram,
 
     model, cfg, device = _prepare_model(params, device, optim, snapshot, allow_missing_keys, det, ccd)
     model.cfg.msa_crop_size = msa_crop_size
+    if matmul_precision:
+        torch.set_float32_matmul_precision(matmul_precision)
+    from ..data.parse.json_input import parse_json_input
+
     with open(inputs_file) as f:
         paths = [line.strip() for line in f if line.strip() and not line.startswith("#")]
     done = failed = 0
     for p in paths:
         try:
-            for inp in InferenceInput.from_json(p, msa_crop_size):
-                run_job(model, inp, output_template.format(name=inp.name), device, list(seeds) or None, num_recycles,
-                        num_samples, getattr(torch, DTYPES[precision]), bucket, sample_chunk, skip_existing, logits_scheme,
-                        save_distogram, _guidance_terms(guidance), manifest_fields={"params": params, "input": p})  # fmt: skip
+            for job in parse_json_input(p):
+                inp = InferenceInput.from_job(job, msa_crop_size, msa_pairing)
+                terms, rkw = _job_steering(inp, guidance, allow_guidance_overlap, restraints, restraint_pairs, repels,
+                                           restraint_weight, restraint_rigid, restraint_after_step, restraint_after_sigma,
+                                           restraint_max_step)  # fmt: skip
+                out_dir = output_template.format(name=inp.name)
+                run_job(model, inp, out_dir, device, list(seeds) or None, num_recycles, num_samples,
+                        getattr(torch, DTYPES[precision]), bucket, sample_chunk, skip_existing, logits_scheme,
+                        save_distogram, terms, rkw, manifest_fields={"params": params, "input": p})  # fmt: skip
+                if plot_confidences:
+                    _plot_outputs(out_dir)
                 done += 1
         except Exception as exc:  # noqa: BLE001 - one bad job must not stop the batch
             failed += 1

@@ -1,0 +1,43 @@
+"""The prediction command end to end on CPU with a tiny model: steering flags, outputs, figures."""
+
+import importlib
+import importlib.util
+import json
+import os
+
+import torch
+from click.testing import CliRunner
+from helpers import tiny_config
+
+
+def test_inference_command_with_restraints_and_guidance(tmp_path, monkeypatch):
+    main = importlib.import_module("deepfold3_dev_b200.cli.main")
+
+    def tiny(params, device, optim, snapshot, allow_missing_keys, det, ccd):
+        from deepfold3_dev_b200.models.model import DeepFold3
+
+        cfg = tiny_config()
+        cfg.diffusion.steps = 3
+        torch.manual_seed(0)
+        return DeepFold3(cfg).eval(), cfg, torch.device("cpu")
+
+    monkeypatch.setattr(main, "_prepare_model", tiny)
+    job = [{"name": "rjob", "dialect": "deepfold3", "modelSeeds": [1],
+            "sequences": [{"protein": {"id": "A", "sequence": "MKTAYIAKQRQISFVKSH"}}, {"protein": {"id": "B", "sequence": "GSHMSEQNNTEMTFQ"}}]}]  # fmt: skip
+    (tmp_path / "job.json").write_text(json.dumps(job))
+    out = tmp_path / "out"
+    res = CliRunner().invoke(main.cli, [
+        "inference", "--json", str(tmp_path / "job.json"), "--output", str(out), "--num-recycles", "1", "--num-samples", "2",
+        "--precision", "fp32", "--restraint", "A/3-6:B/2-5@8", "--repel", "A/10:B/10@12", "--restraint-pair", "A/1-2:B/1-2",
+        "--guidance", "1.5@all@1..100", "--plot-confidences", "--msa-pairing", "none", "--no-bucket"])  # fmt: skip
+    assert res.exit_code == 0, res.output + repr(res.exception)
+    assert "2 samples" in res.output
+    for k in (0, 1):
+        files = set(os.listdir(out / f"seed-1_sample-{k}"))
+        assert {"confidences.json", "logits.npz", "model.cif"} <= files
+        if importlib.util.find_spec("matplotlib") is not None:  # without it the figure is skipped with a warning
+            assert any(f.endswith(".png") for f in files)
+    manifest = json.loads((out / "run_manifest.json").read_text())
+    assert manifest["status"] == "done" and manifest["num_tokens"] == 33
+    bad = CliRunner().invoke(main.cli, ["inference", "--json", str(tmp_path / "job.json"), "--output", str(out), "--restraint", "A/3-6"])
+    assert bad.exit_code != 0  # a restraint needs two selectors
