@@ -198,6 +198,42 @@ def _job_steering(inp, guidance, allow_overlap, restraints, restraint_pairs, rep
     return terms, kwargs
 
 
+def _attach_templates(inp, hits_path: str, mmcif_dir: str | None, cache_dir: str) -> None:
+    """Template features of a single-chain job from a hit file (.m8 / .hhr / templates JSON)."""
+    import json
+
+    from ..data import templates as tpl
+
+    n = inp.num_tokens
+    if hits_path.endswith(".json"):
+        with open(hits_path) as f:
+            chains = tpl.load_json_templates(json.load(f), os.path.dirname(os.path.abspath(hits_path)))
+    else:
+        if not mmcif_dir:
+            raise click.ClickException("--templates with .m8 / .hhr hits needs --pdb-mmcif-dir")
+        with open(hits_path) as f:
+            text = f.read()
+        if hits_path.endswith(".hhr"):
+            from ..data.parse.hhr import parse_hhr
+
+            rows = []
+            for h in parse_hhr(text):
+                pairs = sorted(h.query_to_hit_mapping.items())
+                rows.append({"pdb_id": h.pdb_id.lower(), "chainId": h.chain_id, "queryIndices": [q for q, _ in pairs],
+                             "templateIndices": [t for _, t in pairs]})  # fmt: skip
+            chains = []
+            for r in rows:
+                src = tpl.find_pdb_mmcif(r["pdb_id"], mmcif_dir)
+                hit = tpl.template_chain_from_mmcif(src, r["chainId"], r["queryIndices"], r["templateIndices"]) if src else None
+                if hit is not None:
+                    chains.append(hit)
+        else:
+            hits = tpl.prepare_job_templates(text, mmcif_dir, cache_dir, query_length=n)
+            chains = tpl.load_json_templates(hits, cache_dir)
+    if chains:
+        inp.features.update(tpl.template_features(n, chains))
+
+
 def _plot_outputs(out_dir: str) -> None:
     from ..io.plot import plot_confidences
 
@@ -230,8 +266,12 @@ def _guidance_terms(specs):
 @click.option("--sequence", default=None, help="A single sequence, no alignment.")
 @click.option("--mol-type", type=click.Choice(["protein", "dna", "rna"]), default="protein")
 @click.option("--output", type=click.Path(), required=True)
+@click.option("--templates", "templates_path", type=click.Path(exists=True), default=None,
+              help="Template hits for a single-chain job: mmseqs .m8 with CIGAR, HHsearch .hhr, or a templates JSON.")
+@click.option("--pdb-mmcif-dir", type=click.Path(exists=True), default=None, help="Where the hits' mmCIF files are.")
+@click.option("--template-cache", type=click.Path(), default=None, help="Directory for the prepared template files.")
 @_inference_options
-def inference(msa, json_path, sequence, mol_type, output, params, num_recycles, num_samples, msa_crop_size, snapshot,
+def inference(msa, json_path, sequence, mol_type, output, templates_path, pdb_mmcif_dir, template_cache, params, num_recycles, num_samples, msa_crop_size, snapshot,
               seeds, device, optim, precision, logits_scheme, bucket, sample_chunk, guidance, allow_guidance_overlap,
               restraints, restraint_pairs, repels, restraint_rigid, restraint_after_step, restraint_after_sigma,
               restraint_max_step, restraint_weight, msa_pairing, matmul_precision, plot_confidences,
@@ -256,6 +296,8 @@ def inference(msa, json_path, sequence, mol_type, output, params, num_recycles, 
         inputs = [InferenceInput.from_sequence(sequence, mol_type, msa_crop_size=msa_crop_size)]
     else:
         raise click.ClickException("one of --json, --msa, --sequence is required")
+    if templates_path and not json_path:
+        _attach_templates(inputs[0], templates_path, pdb_mmcif_dir, template_cache or os.path.join(output, "templates"))
     model.cfg.msa_crop_size = msa_crop_size
     for inp in inputs:
         out_dir = output if len(inputs) == 1 else os.path.join(output, inp.name)
