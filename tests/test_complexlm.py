@@ -174,3 +174,18 @@ def test_diagnostics_permutation_and_sinks():
     assert dep["token_cosine_min"] < 0.9999  # rotary positions over the concatenation see the order
     stats = attention_sink_stats(ComplexLM(_small(layer_pattern="cg")), pack([ex]))
     assert [s["kind"] for s in stats] == ["c", "g", "c", "g"] and all(s["x_uniform"] >= 1.0 for s in stats)
+
+
+@pytest.mark.gpu
+def test_packed_segment_attention_matches_dense_on_gpu():
+    """The variable-length path (CUDA, bf16) and the dense masked path give the same logits."""
+    torch.manual_seed(0)
+    batch = pack([_example([A, B], [0, 1]), _example([A, A], [0, 0], 1)]).to("cuda")
+    cfg_v = ComplexLMConfig(d_model=64, n_heads=4, n_layers=4, layer_pattern="cg", attn_impl="varlen")
+    model = ComplexLM(cfg_v).cuda().bfloat16().eval()
+    with torch.no_grad():
+        packed = model(batch).logits.float()
+        for blk in model.blocks:
+            blk.attn.cfg = ComplexLMConfig(d_model=64, n_heads=4, n_layers=4, layer_pattern="cg", attn_impl="sdpa")
+        dense = model(batch).logits.float()
+    assert (packed - dense).abs().max() < 0.05 * dense.abs().max() + 1e-2
