@@ -79,6 +79,12 @@ def train(data_dir, output, params, resume, configs, lr, max_steps, max_tokens, 
         apply_det_recipe()
     info = init_process_group(tc.collective_timeout_s)
     specs = list(datasets) or ([f"data:{data_dir}"] if data_dir else [])
+    extra = {}  # per-dataset settings that only the config file carries (date cut-off, crop weights)
+    if not specs and not synthetic:
+        for d in getattr(tc, "extra_datasets", []) or []:
+            if d.data_dir:
+                specs.append(f"{d.name or 'data'}:{d.data_dir}:{d.weight}:{d.strategy}:{int(d.is_distillation)}")
+                extra[d.data_dir] = {"cutoff_date": d.cutoff_date, "crop_weights": d.crop_weights}
     if synthetic or not specs:
         if not synthetic:
             raise click.ClickException("give --dataset / --data-dir, or --synthetic")
@@ -92,7 +98,11 @@ def train(data_dir, output, params, resume, configs, lr, max_steps, max_tokens, 
             name, path = f[0], f[1]
             weights.append(float(f[2]) if len(f) > 2 and f[2] else 1.0)
             distill = len(f) > 4 and f[4].lower() in ("1", "true", "distill")
-            parts.append(ds.open_dataset(path, max_tokens=tc.max_tokens, max_atoms=tc.max_atoms, is_distillation=distill, seed=tc.seed))
+            kw = {k: v for k, v in extra.get(path, {}).items() if v}
+            if "cutoff_date" in kw and not os.path.isdir(os.path.join(path, "structures")):
+                kw.pop("cutoff_date")  # feature directories carry no dates; the cut-off is applied when they are prepared
+            parts.append(ds.open_dataset(path, max_tokens=tc.max_tokens, max_atoms=tc.max_atoms, is_distillation=distill,
+                                         seed=tc.seed, **kw))  # fmt: skip
             logging.getLogger(__name__).info("dataset %s: %d examples from %s", name, len(parts[-1]), path)
         samplers = [WeightedClusterSampler(p.weights(), tc.seed + 17 * i, info.rank, info.world_size) for i, p in enumerate(parts)]
         sampler = MultiDatasetSampler(samplers, [len(p) for p in parts], weights, tc.seed)

@@ -202,6 +202,22 @@ class PrefetchStream:
         self._stop.set()
 
 
+def apply_date_cutoff(records: list, cutoff: str, keep_after: bool = False) -> list:
+    """Release-date split (reference: training/data.py:64-92). ``keep_after=False`` keeps entries released on or before
+    ``cutoff`` (training side), ``True`` those released after it (evaluation side). An entry without a release date is
+    dropped on both sides: it cannot be shown to be on the right side. An empty ``cutoff`` keeps everything."""
+    if not cutoff:
+        return list(records)
+    out = []
+    for r in records:
+        released = r.structure_info.released if r.structure_info is not None else None
+        if not released:
+            continue
+        if (released > cutoff) == keep_after:
+            out.append(r)
+    return out
+
+
 class StructureDataset:
     """Prepared structures featurised on the fly (reference: data/module/dataset.py:238-602, ``TrainingDataset``).
 
@@ -213,7 +229,7 @@ class StructureDataset:
 
     def __init__(self, root: str, max_tokens: int = 384, max_atoms: int = 0, crop_weights: dict | None = None,
                  is_distillation: bool = False, seed: int = 0, max_chains: int = 20, max_msa_rows: int = 16384,
-                 msa_dir: str | None = None):  # fmt: skip
+                 msa_dir: str | None = None, cutoff_date: str = "", keep_after: bool = False):  # fmt: skip
         from .types import load_manifest
 
         self.root, self.max_tokens, self.max_atoms = root, max_tokens, max_atoms
@@ -221,6 +237,7 @@ class StructureDataset:
         self.max_chains, self.max_msa_rows = max_chains, max_msa_rows
         self.msa_dir = msa_dir or os.path.join(root, "msa")
         self.records = [r for r in load_manifest(os.path.join(root, "manifest.json")) if any(c.valid for c in r.chains)]
+        self.records = apply_date_cutoff(self.records, cutoff_date, keep_after)
 
     def __len__(self):
         return len(self.records)

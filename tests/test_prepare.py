@@ -323,3 +323,16 @@ def test_structure_mmcif_write_read_cycle(tmp_path):
     tok, rows, _ = tokenize_structure(st)
     moved = with_coordinates(st, np.ones((len(rows), 24, 3), np.float32), rows, np.full((len(rows), 24), 77.0))
     assert moved.atoms["is_present"].all() and float(moved.atoms["b_factor"].min()) == 77.0 and float(moved.coords().max()) == 1.0
+
+
+def test_date_cutoff_is_fail_closed():
+    from deepfold3_dev_b200.data.datasets import apply_date_cutoff
+    from deepfold3_dev_b200.data.types import ChainInfo
+
+    def rec(i, date):
+        return Record(str(i), [ChainInfo(0, "A", 0, "c", "m", 10)], [], StructureInfo(released=date) if date != "none" else None)
+
+    recs = [rec(0, "2020-01-01"), rec(1, "2022-05-05"), rec(2, None), rec(3, "none"), rec(4, "2021-09-30")]
+    assert [r.id for r in apply_date_cutoff(recs, "2021-09-30")] == ["0", "4"]
+    assert [r.id for r in apply_date_cutoff(recs, "2021-09-30", keep_after=True)] == ["1"]
+    assert len(apply_date_cutoff(recs, "")) == 5
