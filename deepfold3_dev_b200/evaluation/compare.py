@@ -23,6 +23,25 @@ def _chain_table(st):
     return out
 
 
+def _restrict(chain: dict, keep: list[int]) -> dict:
+    res = chain["res"][keep]
+    return dict(chain, res=res, seq=tuple(r["name"] for r in res))
+
+
+def _numbering_overlap(p: dict, t: dict, min_identity: float = 0.9):
+    """Residue rows of ``p`` and ``t`` paired by the identical blocks of a sequence alignment, when those cover at least
+    ``min_identity`` of the shorter chain (constructs that differ by tags, numbering or a few mutations)."""
+    import difflib
+
+    a, b = [r["name"] for r in p["res"]], [r["name"] for r in t["res"]]
+    blocks = difflib.SequenceMatcher(None, a, b, autojunk=False).get_matching_blocks()
+    kp = [i + k for i, _, n in blocks for k in range(n)]
+    kt = [j + k for _, j, n in blocks for k in range(n)]
+    if len(kp) < 4 or len(kp) / max(min(len(a), len(b)), 1) < min_identity:
+        return None
+    return kp, kt
+
+
 def _trace(st, chain) -> tuple[np.ndarray, np.ndarray]:
     want = b"CA" if chain["mol"] == const.MOL_PROTEIN else b"C1'"
     pts, ok = np.zeros((len(chain["res"]), 3)), np.zeros(len(chain["res"]), bool)
@@ -47,6 +66,26 @@ def match_chains(pred, true) -> list[tuple[dict, dict]]:
         if c["seq"] in groups:
             groups[c["seq"]][1].append(c)
     pairs = []
+    # polymer chains without an identical partner: fall back to the overlap of their residue numbering
+    used_t = {id(c) for _, ts in groups.values() for c in ts}
+    for seq, (ps, ts) in list(groups.items()):
+        if ts or not ps or ps[0]["mol"] == const.MOL_NONPOLYMER:
+            continue
+        for p in ps:
+            best = None
+            for t in tt:
+                if id(t) in used_t or t["mol"] != p["mol"]:
+                    continue
+                hit = _numbering_overlap(p, t)
+                if hit is not None and (best is None or len(hit[0]) > len(best[1][0])):
+                    best = (t, hit)
+            if best is not None:
+                t, (kp, kt) = best
+                used_t.add(id(t))
+                pr, tr = _restrict(p, kp), _restrict(t, kt)
+                groups.setdefault(pr["seq"], ([], []))
+                groups[pr["seq"]][0].append(pr), groups[pr["seq"]][1].append(tr)
+        groups.pop(seq, None)
     anchors = [(a[0], b[0]) for a, b in groups.values() if a and b]
     if not anchors:
         return []

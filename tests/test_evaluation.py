@@ -66,3 +66,18 @@ def test_compare_files_roundtrip(tmp_path):
     b.write_text(_mini_cif(shift=(5.0, -3.0, 2.0)))
     out = compare_files(str(a), str(b))
     assert out["matched_chains"] == 3 and out["lddt"] == pytest.approx(1.0) and out["rmsd_all_atom"] < 1e-3
+
+
+def test_homologous_constructs_match_through_alignment():
+    import os
+
+    from test_prepare import EXAMPLES
+
+    from deepfold3_dev_b200.evaluation.compare import compare_files
+
+    a = os.path.join(EXAMPLES, "9m22_msa", "templates", "7v2g_A.cif")
+    b = os.path.join(EXAMPLES, "9m22_msa", "templates", "6aq1_B.cif")
+    if not (os.path.exists(a) and os.path.exists(b)):
+        pytest.skip("reference example files not available")
+    out = compare_files(a, b)  # two crystal forms of one protein whose constructs differ at the termini
+    assert out["matched_chains"] >= 1 and out["tm_score"] > 0.9 and out["lddt"] > 0.8 and out["matched_atoms"] > 900
