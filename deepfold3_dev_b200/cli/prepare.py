@@ -354,7 +354,26 @@ def build_pdb_cache(mmcif_dir, out_dir, limit):
     click.echo(f"{build_chain_cache(mmcif_dir, out_dir, limit)} chains -> {out_dir}")
 
 
+@click.command("inspect-checkpoint")
+@click.argument("path", type=click.Path(exists=True))
+@click.option("--depth", type=int, default=2, help="Module-name depth of the grouping.")
+def inspect_checkpoint(path, depth):
+    """Parameter counts, norms, non-finite values and EMA distance of a .pt / .safetensors checkpoint, by module."""
+    from ..utils.run_tools import checkpoint_report
+
+    click.echo(json.dumps(checkpoint_report(path, depth), indent=1, default=str))
+
+
+@click.command("run-status")
+@click.argument("run_dir", type=click.Path(exists=True))
+def run_status_cmd(run_dir):
+    """Progress, throughput, loss trend and skipped steps of a training run directory."""
+    from ..utils.run_tools import run_status
+
+    click.echo(json.dumps(run_status(run_dir), indent=1))
+
+
 def register(cli) -> None:
-    for cmd in (prepare, scan_mmcif, inspect_example, plm_prepare, plm_train, evaluate, prepare_templates, build_pdb_cache):
+    for cmd in (prepare, scan_mmcif, inspect_example, plm_prepare, plm_train, evaluate, prepare_templates, build_pdb_cache, inspect_checkpoint, run_status_cmd):
         cli.add_command(cmd)
 

@@ -74,3 +74,23 @@ def test_probe_writes_one_row_per_probed_step(tmp_path):
     assert len(rows) == 1 and rows[0]["step"] == 7 and rows[0]["loss"] == 1.5
     assert rows[0]["rms_s_l0"] > 0 and -1 <= rows[0]["cos_su_mean"] <= 1 and "sum_gamma_alpha" in rows[0]
     assert "w_norm_single_transition_l_last" in rows[0]
+
+
+def test_checkpoint_report_and_run_status(tmp_path):
+    from deepfold3_dev_b200.utils.run_tools import checkpoint_report, run_status
+
+    model = {"evoformer.a.weight": torch.ones(4, 4), "evoformer.a.bias": torch.tensor([float("nan"), 1.0]), "head.w": torch.full((3,), 2.0)}
+    torch.save({"model": model, "ema": {"evoformer.a.weight": torch.zeros(4, 4)}, "global_step": 12}, tmp_path / "c.pt")
+    rep = checkpoint_report(str(tmp_path / "c.pt"))
+    assert rep["total_parameters"] == 21 and rep["meta"]["global_step"] == 12 and rep["non_finite"][0]["name"] == "evoformer.a.bias"
+    rows = {r["module"]: r for r in rep["modules"]}
+    assert rows["evoformer.a"]["ema_distance"] == 4.0 and abs(rows["head.w"]["norm"] - 12**0.5) < 1e-6
+    os_dir = tmp_path / "run" / "logs"
+    os_dir.mkdir(parents=True)
+    with open(os_dir / "metrics.jsonl", "w") as f:
+        for i in range(10):
+            f.write(json.dumps({"step": i, "time": 100.0 + 2 * i, "train/loss": 5.0 - 0.3 * i}) + "\n")
+        f.write('{"step": 10, "ti')  # a torn last line
+    st = run_status(str(tmp_path / "run"))
+    assert st["rows"] == 10 and st["last_step"] == 9 and abs(st["steps_per_hour"] - 1800.0) < 1e-6
+    assert st["loss_recent_mean"] < st["loss_earlier_mean"] and st["non_finite_losses"] == 0
