@@ -328,8 +328,9 @@ def inference(msa, json_path, sequence, mol_type, output, templates_path, pdb_mm
 @click.option("--output-template", default="out/{name}", help="Output directory per job; {name} is the job name.")
 @click.option("--skip-existing/--no-skip-existing", default=True)
 @click.option("--save-distogram/--no-save-distogram", default=True)
+@click.option("--shard", default=None, help="I/N: take every N-th job starting at I (one process per GPU; default from RANK / WORLD_SIZE).")
 @_inference_options
-def inference_batch(inputs_file, output_template, skip_existing, save_distogram, params, num_recycles, num_samples,
+def inference_batch(inputs_file, output_template, skip_existing, save_distogram, shard, params, num_recycles, num_samples,
                     msa_crop_size, snapshot, seeds, device, optim, precision, logits_scheme, bucket, sample_chunk,
                     guidance, allow_guidance_overlap, restraints, restraint_pairs, repels, restraint_rigid,
                     restraint_after_step, restraint_after_sigma, restraint_max_step, restraint_weight, msa_pairing,
@@ -341,6 +342,15 @@ def inference_batch(inputs_file, output_template, skip_existing, save_distogram,
     from ..data.inference_input import InferenceInput
     from ..inference.runner import run_job
 
+    part = None
+    if shard is None and int(os.environ.get("WORLD_SIZE", "1")) > 1:
+        shard = f"{os.environ.get('RANK', '0')}/{os.environ['WORLD_SIZE']}"
+    if shard:
+        part = tuple(int(x) for x in shard.split("/"))
+        if len(part) != 2 or not 0 <= part[0] < part[1]:
+            raise click.ClickException(f"--shard {shard}: need I/N with 0 <= I < N")
+        if device is None and torch.cuda.is_available():
+            device = f"cuda:{int(os.environ.get('LOCAL_RANK', part[0] % max(torch.cuda.device_count(), 1)))}"
     model, cfg, device = _prepare_model(params, device, optim, snapshot, allow_missing_keys, det, ccd)
     model.cfg.msa_crop_size = msa_crop_size
     if matmul_precision:
@@ -349,6 +359,8 @@ def inference_batch(inputs_file, output_template, skip_existing, save_distogram,
 
     with open(inputs_file) as f:
         paths = [line.strip() for line in f if line.strip() and not line.startswith("#")]
+    if part is not None:
+        paths = paths[part[0] :: part[1]]
     done = failed = 0
     for p in paths:
         try:

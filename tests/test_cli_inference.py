@@ -41,3 +41,29 @@ def test_inference_command_with_restraints_and_guidance(tmp_path, monkeypatch):
     assert manifest["status"] == "done" and manifest["num_tokens"] == 33
     bad = CliRunner().invoke(main.cli, ["inference", "--json", str(tmp_path / "job.json"), "--output", str(out), "--restraint", "A/3-6"])
     assert bad.exit_code != 0  # a restraint needs two selectors
+
+
+def test_inference_batch_shards_jobs(tmp_path, monkeypatch):
+    main = importlib.import_module("deepfold3_dev_b200.cli.main")
+
+    def tiny(params, device, optim, snapshot, allow_missing_keys, det, ccd):
+        from deepfold3_dev_b200.models.model import DeepFold3
+
+        cfg = tiny_config()
+        cfg.diffusion.steps = 2
+        return DeepFold3(cfg).eval(), cfg, torch.device("cpu")
+
+    monkeypatch.setattr(main, "_prepare_model", tiny)
+    paths = []
+    for k in range(3):
+        job = [{"name": f"j{k}", "dialect": "deepfold3", "modelSeeds": [0], "sequences": [{"protein": {"id": "A", "sequence": "MKTAYIAKQR"}}]}]
+        (tmp_path / f"j{k}.json").write_text(json.dumps(job))
+        paths.append(str(tmp_path / f"j{k}.json"))
+    (tmp_path / "list.txt").write_text("\n".join(paths) + "\n")
+    res = CliRunner().invoke(main.cli, ["inference-batch", "--inputs-file", str(tmp_path / "list.txt"), "--output-template",
+                                        str(tmp_path / "out" / "{name}"), "--num-recycles", "0", "--num-samples", "1", "--precision", "fp32",
+                                        "--no-bucket", "--shard", "1/2"])  # fmt: skip
+    assert res.exit_code == 0, res.output + repr(res.exception)
+    assert sorted(os.listdir(tmp_path / "out")) == ["j1"] and "1 jobs done" in res.output
+    bad = CliRunner().invoke(main.cli, ["inference-batch", "--inputs-file", str(tmp_path / "list.txt"), "--shard", "2/2"])
+    assert bad.exit_code != 0
