@@ -314,6 +314,8 @@ class StructureDataset:
 
 def open_dataset(path: str, **kw):
     """A directory of ``.pt`` features, or the output of ``prepare structures`` (featurised on the fly)."""
-    if os.path.isdir(os.path.join(path, "structures")) and os.path.exists(os.path.join(path, "manifest.json")):
+    from . import paths
+
+    if paths.is_prepared_root(path):
         return StructureDataset(path, **kw)
     return FeatureDirDataset(path, **kw)
