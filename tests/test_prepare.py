@@ -336,3 +336,25 @@ def test_date_cutoff_is_fail_closed():
     assert [r.id for r in apply_date_cutoff(recs, "2021-09-30")] == ["0", "4"]
     assert [r.id for r in apply_date_cutoff(recs, "2021-09-30", keep_after=True)] == ["1"]
     assert len(apply_date_cutoff(recs, "")) == 5
+
+
+def test_component_dictionary_gz_and_json_table(tmp_path):
+    import gzip
+
+    from deepfold3_dev_b200.data import ccd, ref_conformers
+
+    gz = tmp_path / "components.cif.gz"
+    with gzip.open(gz, "wt") as f:
+        f.write(_PLM_CIF)
+    assert [c for c, _ in ccd.iter_blocks(str(gz), {"ZZ2"})] == ["ZZ2"]
+    assert sorted(ccd.load_components(str(gz))) == ["ZZ1", "ZZ2"]
+    table = tmp_path / "t.json"
+    assert ccd.export_table(str(gz), str(table), {"ZZ1"}) == 1
+    try:
+        ref_conformers.set_ccd_source(str(table))  # a JSON table is loaded at once
+        names, elements, charges, coords = ref_conformers.get_ref_atoms("zz1")
+        assert names == ["C1", "O1", "O2", "C1'"] and charges[1] == -1 and coords.shape == (4, 3)
+        assert ref_conformers.load_component_text(_PLM_CIF) == 2 and ref_conformers.get_ref_atoms("ZZ2")[0] == ["MG"]
+    finally:
+        ref_conformers._TABLE.pop("ZZ1", None)
+        ref_conformers._TABLE.pop("ZZ2", None)
