@@ -124,9 +124,15 @@ def cluster(data_dir, pdb_clusters, identity):
 @click.argument("data_dir", type=click.Path(exists=True))
 @click.option("--msa-dir", type=click.Path(), default=None, help="Directory of <msa_id>.a3m (or .npz) alignments.")
 @click.option("--max-msa-rows", type=int, default=16384)
-def features(data_dir, msa_dir, max_msa_rows):
+@click.option("--ccd", type=click.Path(exists=True), default=None,
+              help="components.cif[.gz] or a JSON conformer table: reference conformers of ligands and modified residues.")
+def features(data_dir, msa_dir, max_msa_rows, ccd):
     """Featurise every manifest entry into features/<id>.pt plus the flat manifest the training datasets read."""
     import torch
+
+    from ..data import ref_conformers
+
+    ref_conformers.set_ccd_source(ccd)
 
     from ..data.featurize import featurize_structure
     from ..data.parse.a3m import msa_from_a3m_file
@@ -137,6 +143,8 @@ def features(data_dir, msa_dir, max_msa_rows):
     flat = []
     for rec in load_manifest(os.path.join(data_dir, "manifest.json")):
         st = Structure.load(os.path.join(data_dir, "structures", f"{rec.id}.npz"))
+        if ccd:  # one pass over the dictionary for the components this entry needs and does not know yet
+            ref_conformers.ensure_components({r["name"].decode().strip() for r in st.residues if not r["is_standard"]})
         msas = {}
         for c in rec.chains:
             if not msa_dir:
