@@ -130,6 +130,17 @@ def window_attention(q, k, v, bias, scale: float):
     return ref.window_attention(q, k, v, bias, scale)
 
 
+def _plane_contract(nat, planes, outgoing: bool):
+    """One N x N x N product per channel plane (reference: model/triton/fused_trimul.py:264-279, there a library
+    batched GEMM); on the tcgen05 kernel when the token count keeps plane rows 16-byte aligned."""
+    if nat.has("matmul") and planes.shape[-1] % 8 == 0:
+        _CENSUS["triangle_plane_contract:sm100"] += 1
+        return nat.plane_contract(planes, outgoing)
+    _CENSUS["triangle_plane_contract:torch"] += 1
+    a, b = planes[0], planes[1]
+    return torch.bmm(a, b.transpose(1, 2)) if outgoing else torch.bmm(b.transpose(1, 2), a)
+
+
 def triangle_contract_norm(z0, w_gate, w_proj, mask, outgoing: bool, ln_w, ln_b, eps: float = 1e-5):
     """``LN_c(triangle_projection_contract(...))``: on the GPU the contraction result stays channel-major and one kernel
     normalises and transposes it to channel-last."""
@@ -139,8 +150,7 @@ def triangle_contract_norm(z0, w_gate, w_proj, mask, outgoing: bool, ln_w, ln_b,
         _CENSUS["triangle_contract_norm:sm100"] += 1
         B, N = z0.shape[0], z0.shape[1]
         planes = nat.gated_dual_linear(z0, w_gate, w_proj, mask, True, True).view(2, C * B, N, N)
-        a, b = planes[0], planes[1]
-        act = torch.bmm(a, b.transpose(1, 2)) if outgoing else torch.bmm(b.transpose(1, 2), a)
+        act = _plane_contract(nat, planes, outgoing)
         return nat.plane_layer_norm(act.view(C, B * N * N), ln_w, ln_b, eps).view(B, N, N, C)
     return layer_norm(triangle_projection_contract(z0, w_gate, w_proj, mask, outgoing), ln_w, ln_b, eps)
 
@@ -157,8 +167,7 @@ def triangle_projection_contract(z0, w_gate, w_proj, mask, outgoing: bool):
         B, N = z0.shape[0], z0.shape[1]
         C = w_gate.shape[0] // 2
         planes = nat.gated_dual_linear(z0, w_gate, w_proj, mask, True, True).view(2, C * B, N, N)
-        a, b = planes[0], planes[1]
-        act = torch.bmm(a, b.transpose(1, 2)) if outgoing else torch.bmm(b.transpose(1, 2), a)
+        act = _plane_contract(nat, planes, outgoing)
         return act.view(C, B, N, N).permute(1, 2, 3, 0)
     ab = gated_dual_linear(z0, w_gate, w_proj, mask)
     return triangle_contract(ab[..., 0::2], ab[..., 1::2], outgoing)

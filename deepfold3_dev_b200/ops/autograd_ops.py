@@ -239,9 +239,38 @@ def _bf16c(x):
     return x.to(BF16).contiguous()
 
 
+def _mm_ok(*ts) -> bool:
+    """Operands the tcgen05 product takes as they are: bf16 CUDA, every extent a multiple of 8."""
+    return all(t.is_cuda and t.dtype == BF16 and t.numel() > 0 and all(d % 8 == 0 for d in t.shape[-2:]) for t in ts)
+
+
+def mm(a, b, trans_a: bool = False, trans_b: bool = False, out_fp32: bool = False, splits: int = 1, out=None):
+    """``op(a) @ op(b)`` (2-D, or 3-D batched) on the tcgen05 kernel; ``trans_*`` hands an operand over transposed
+    instead of copying it. Falls back to torch for shapes the kernel does not take (extents not multiples of 8)."""
+    if _mm_ok(a, b):
+        return K.matmul(a, b, trans_a, trans_b, out_fp32, splits, out)
+    A = a.transpose(-1, -2) if trans_a else a
+    B = b.transpose(-1, -2) if trans_b else b
+    r = torch.matmul(A, B)
+    r = r.float() if out_fp32 else r
+    if out is not None:
+        out.copy_(r.view(out.shape))
+        return out
+    return r
+
+
 def _wgrad(dy2d, x2d, like):
-    """``dy2d.T @ x2d`` accumulated in fp32, in the dtype of the parameter ``like``."""
-    return torch.mm(dy2d.t(), x2d).to(like.dtype)
+    """``dy2d.T @ x2d`` accumulated in fp32 (split along the rows, partial sums added in a fixed order), in the dtype
+    of the parameter ``like``."""
+    return mm(dy2d, x2d, True, False, True, 0).to(like.dtype)
+
+
+def _plain_gemm(x16, W, bias=None):
+    """``x16 W^T (+ bias)`` with x16 [..., K] bf16 and W [N, K] bf16."""
+    if x16.is_cuda and x16.shape[-1] % 8 == 0 and x16.numel() > 0:
+        return K.gemm(x16, W, bias, None, None, 0, False)
+    y = torch.matmul(x16, W.t())
+    return y if bias is None else y + bias.to(y.dtype)
 
 
 def gemm_supported(x, w) -> bool:
@@ -289,7 +318,7 @@ class _GatedDual(torch.autograd.Function):
         x2 = x16.reshape(-1, x16.shape[-1])
         dy2 = (dy.t() if ctx.planes else dy.reshape(-1, n)).to(BF16).contiguous()
         dgp = K.gemm(x2, W, None, m, dy2, 5, False)  # pre-activations recomputed in the accumulator
-        dx = torch.mm(dgp, W).view(x16.shape).to(ctx.x_dtype)
+        dx = mm(dgp, W).view(x16.shape).to(ctx.x_dtype)
         dW = _wgrad(dgp, x2, w_gate)
         dg, dp = dW[:n], dW[n:]
         if ctx.deinterleave:
@@ -315,7 +344,7 @@ class _StackedLinear(torch.autograd.Function):
         x16 = _bf16c(x)
         ctx.save_for_backward(x16, *ws)
         ctx.x_dtype = x.dtype
-        return torch.matmul(x16, bf16_weight(*ws).t())
+        return _plain_gemm(x16, bf16_weight(*ws))
 
     @staticmethod
     def backward(ctx, dy):
@@ -323,8 +352,8 @@ class _StackedLinear(torch.autograd.Function):
         W = bf16_weight(*ws)
         x2 = x16.reshape(-1, x16.shape[-1])
         d = dy.reshape(-1, W.shape[0]).to(BF16)
-        dx = torch.mm(d, W).view(x16.shape).to(ctx.x_dtype)
-        dW = torch.mm(d.t(), x2)
+        dx = mm(d, W).view(x16.shape).to(ctx.x_dtype)
+        dW = mm(d, x2, True, False, True, 0)
         outs, r = [], 0
         for w in ws:
             outs.append(dW[r : r + w.shape[0]].to(w.dtype))
@@ -339,6 +368,8 @@ def stacked_linear(x, *ws):
 def _linear_fwd(x, w, b):
     x16 = x if x.dtype == BF16 else x.to(BF16)
     W = bf16_weight(w)
+    if x16.shape[-1] % 8 == 0 and x16.numel() > 0:
+        return K.gemm(x16, W, b, None, None, 0, False)  # bias added in fp32 in the epilogue
     if b is None:
         return torch.matmul(x16, W.t())
     return torch.addmm(bf16_weight(b), x16.reshape(-1, x16.shape[-1]), W.t()).view(*x16.shape[:-1], W.shape[0])
@@ -384,9 +415,9 @@ class _LinearPlanes(torch.autograd.Function):
     def backward(ctx, dy):
         x16, w = ctx.saved_tensors
         x2 = x16.reshape(-1, x16.shape[-1])
-        d = dy.to(BF16)
-        dx = torch.mm(d.t(), bf16_weight(w)).view(x16.shape).to(ctx.x_dtype)
-        return dx, torch.mm(d, x2).to(w.dtype)
+        d = dy.to(BF16).contiguous()
+        dx = mm(d, bf16_weight(w), True, False).view(x16.shape).to(ctx.x_dtype)  # d is [n, rows]: handed over transposed
+        return dx, mm(d, x2, False, False, True, 0).to(w.dtype)
 
 
 def linear_planes(x, w):
@@ -409,10 +440,10 @@ class _SigmoidGateMul(torch.autograd.Function):
         W = bf16_weight(w)
         x2 = x16.reshape(-1, x16.shape[-1])
         n = w.shape[0]
-        g = torch.mm(x2, W.t())
+        g = _plain_gemm(x2, W)
         d = dy.reshape(-1, n).to(BF16).contiguous()
         dg, d_other = K.sigmoid_gate_bwd(d, g, o16.reshape(-1, n))  # one pass: dy other s (1 - s) and dy s
-        dx = torch.mm(dg, W).view(x16.shape).to(ctx.dtypes[0])
+        dx = mm(dg, W).view(x16.shape).to(ctx.dtypes[0])
         return dx, _wgrad(dg, x2, w), d_other.view(o16.shape).to(ctx.dtypes[1])
 
 
@@ -429,7 +460,7 @@ class _Transition(torch.autograd.Function):
         h, mean, rstd = K.layer_norm_fwd(xc, _f32(ln_w), _f32(ln_b), eps)
         h16 = h if h.dtype == BF16 else h.to(BF16)
         u = K.gemm(h16, bf16_weight(w1), None, None, None, 2, False)
-        y = torch.matmul(u, bf16_weight(w2).t())
+        y = _plain_gemm(u, bf16_weight(w2))
         ctx.save_for_backward(xc, ln_w, ln_b, w1, w2, mean, rstd, h16)
         return y.to(x.dtype) if x.dtype != BF16 else y
 
@@ -442,9 +473,9 @@ class _Transition(torch.autograd.Function):
         d = dy.reshape(-1, c).to(BF16).contiguous()
         u = K.gemm(h2, W1, None, None, None, 2, False)
         dW2 = _wgrad(d, u, w2)
-        dpre = K.gemm(h2, W1, None, None, torch.mm(d, W2), 4, False)  # pre-activations recomputed in the accumulator
+        dpre = K.gemm(h2, W1, None, None, mm(d, W2), 4, False)  # pre-activations recomputed in the accumulator
         dW1 = _wgrad(dpre, h2, w1)
-        dh = torch.mm(dpre, W1).view(xc.shape)
+        dh = mm(dpre, W1).view(xc.shape)
         if xc.dtype != BF16:
             dh = dh.to(xc.dtype)
         need_wb = ln_w is not None and (ctx.needs_input_grad[1] or ctx.needs_input_grad[2])
@@ -465,16 +496,50 @@ def transition(x, ln_w, ln_b, w1, w2, eps: float = 1e-5):
     return _Transition.apply(x, ln_w, ln_b, w1, w2, eps)
 
 
+class _PlaneContract(torch.autograd.Function):
+    """Triangle contraction on channel-major planes ``[2, P, N, N]`` (a = planes[0], b = planes[1], P = channels x
+    batch): outgoing ``act[p] = a[p] b[p]^T``, incoming ``act[p] = b[p]^T a[p]``. Forward and both operand gradients
+    are batched tcgen05 products that read the planes as they lie (transposed operands are MN-major MMA operands);
+    the two gradients are written straight into the halves of one ``[2, P, N, N]`` tensor."""
+
+    @staticmethod
+    def forward(ctx, planes, outgoing):
+        a, b = planes[0], planes[1]
+        ctx.save_for_backward(planes)
+        ctx.outgoing = outgoing
+        return mm(a, b, False, True) if outgoing else mm(b, a, True, False)
+
+    @staticmethod
+    def backward(ctx, d_act):
+        (planes,) = ctx.saved_tensors
+        a, b = planes[0], planes[1]
+        d = d_act if d_act.dtype == BF16 else d_act.to(BF16)
+        d = d.contiguous()
+        grads = torch.empty_like(planes)
+        if ctx.outgoing:  # act = a b^T: da = d b, db = d^T a
+            mm(d, b, False, False, out=grads[0])
+            mm(d, a, True, False, out=grads[1])
+        else:  # act = b^T a: da = b d, db = a d^T
+            mm(b, d, False, False, out=grads[0])
+            mm(a, d, False, True, out=grads[1])
+        return grads, None
+
+
+def plane_contract(planes, outgoing: bool):
+    return _PlaneContract.apply(planes, bool(outgoing))
+
+
 # ------------------------------------------------------------------------------------------------
-# Pair-bias attention: tcgen05 forward kernel; backward in row chunks sized to stay in L2, with the
-# softmax/bias-gradient algebra in one kernel per chunk and the five small products on the library GEMM.
-# bytes of one score chunk of the attention backward (two such buffers stay L2-resident at the default)
+# Pair-bias attention: tcgen05 forward kernel and one fused tcgen05 backward kernel (dQ, dK, dV accumulated in tensor
+# memory, logits recomputed in fp32). Shapes beyond the tensor-memory budget of the fused backward (long rows) fall back
+# to row chunks sized for L2; a negative DF3_ATTN_BWD_CHUNK_MB forces that chunked form everywhere (for comparisons).
 ATTN_BWD_CHUNK_BYTES = int(os.environ.get("DF3_ATTN_BWD_CHUNK_MB", "40")) * 1024 * 1024
 
 
 def attention_supported(q, k, v, bias) -> bool:
     d = q.shape[-1]
-    even = q.shape[-2] % 2 == 0 or not torch.is_grad_enabled()  # the backward kernel handles keys in pairs
+    # the chunked backward (rows beyond the fused kernel's tensor-memory budget) handles keys in pairs
+    even = q.shape[-2] % 2 == 0 or not torch.is_grad_enabled() or K.attention_bwd_fused_supported(q.shape[-2], d)
     return q.is_cuda and q.dim() == 5 and q.dtype == BF16 and k.dtype == BF16 and v.dtype == BF16 and d % 8 == 0 and d <= 64 and even
 
 
@@ -527,11 +592,16 @@ class _GridAttentionPacked(torch.autograd.Function):
         qkv, bias, key_mask, out, lse = ctx.saved_tensors
         q, k, v = (_grid_heads(qkv[:, :, :, i], ctx.transpose) for i in range(3))
         want_bias = bias is not None and ctx.needs_input_grad[1]
-        dq, dk, dv, dbias = K.attention_bwd(q, k, v, out, d_out, bias, key_mask, lse, ctx.scale, want_bias,
-                                            ATTN_BWD_CHUNK_BYTES)  # fmt: skip
         dqkv = torch.empty_like(qkv)
-        for i, g in enumerate((dq, dk, dv)):
-            _grid_heads(dqkv[:, :, :, i], ctx.transpose).copy_(g)
+        if ATTN_BWD_CHUNK_BYTES >= 0 and K.attention_bwd_fused_supported(q.shape[3], q.shape[4]):
+            # the fused kernel writes the three gradients straight into their slots of the packed tensor
+            dq, dk, dv = (_grid_heads(dqkv[:, :, :, i], ctx.transpose) for i in range(3))
+            dbias = K.attention_bwd_into(q, k, v, out, d_out, bias, key_mask, lse, ctx.scale, want_bias, dq, dk, dv)
+        else:
+            dq, dk, dv, dbias = K.attention_bwd(q, k, v, out, d_out, bias, key_mask, lse, ctx.scale, want_bias,
+                                                ATTN_BWD_CHUNK_BYTES)  # fmt: skip
+            for i, g in enumerate((dq, dk, dv)):
+                _grid_heads(dqkv[:, :, :, i], ctx.transpose).copy_(g)
         return dqkv, (dbias.to(bias.dtype) if want_bias else None), None, None, None
 
 

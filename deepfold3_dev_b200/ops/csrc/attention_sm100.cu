@@ -26,9 +26,29 @@
 using torch::Tensor;
 
 namespace df3 {
+bool attention_bwd_fused_supported(int64_t N, int64_t D);  // attention_bwd_sm100.cu
+std::tuple<Tensor, Tensor, Tensor, Tensor> attention_bwd_fused(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& out,
+                                                               const Tensor& d_out, const c10::optional<Tensor>& bias,
+                                                               const c10::optional<Tensor>& mask, const Tensor& lse, double scale,
+                                                               bool want_dbias, const c10::optional<Tensor>& dq_out,
+                                                               const c10::optional<Tensor>& dk_out, const c10::optional<Tensor>& dv_out);
 Tensor status_word(int device);                       // gemm_sm100.cu
 CUtensorMap make_map_nd(const void* base, int rank, const int64_t* dims, const int64_t* strides_elems,
                         const int* box);              // gemm_sm100.cu
+
+CUtensorMap qkv_map(const Tensor& t) {  // [B, R, H, N, D] view -> 5-D map (d, n, h, r, b), box 64 x 128
+  const int64_t dims[5] = {t.size(4), t.size(3), t.size(2), t.size(1), t.size(0)};
+  const int64_t strides[5] = {1, t.stride(3), t.stride(2), t.stride(1), t.stride(0)};
+  const int box[5] = {64, 128, 1, 1, 1};
+  return make_map_nd(t.data_ptr(), 5, dims, strides, box);
+}
+
+bool strides_ok(const Tensor& t) {
+  if (t.stride(4) != 1 || reinterpret_cast<uintptr_t>(t.data_ptr()) % 16 != 0) return false;
+  for (int d = 0; d < 4; ++d)
+    if (t.size(d) > 1 && (t.stride(d) % 8 != 0 || t.stride(d) <= 0)) return false;
+  return true;
+}
 
 namespace {
 
@@ -55,51 +75,13 @@ struct AttnParams {
   float scale_log2;        // scale * log2(e)
 };
 
-// K-major operand in 128-byte swizzled rows (see sm100_ptx.cuh); MN-major variant for V: the 64 values of
-// one key are contiguous (the N axis of the MMA), keys advance 128 bytes, 8-key groups are 1024 bytes apart.
-__device__ __forceinline__ uint64_t smem_desc_mn_sw128(uint32_t smem_addr) {
-  uint64_t d = 0;
-  d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
-  d |= (uint64_t)1 << 16;              // leading byte offset: stride between 64-wide N blocks, unused (N <= 64)
-  d |= (uint64_t)(1024 >> 4) << 32;    // stride byte offset: between 8-key groups
-  d |= (uint64_t)1 << 46;
-  d |= (uint64_t)2 << 61;
-  return d;
-}
-
-__device__ __forceinline__ void tma_load_5d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2,
-                                            int c3, int c4) {
-  asm volatile(
-      "cp.async.bulk.tensor.5d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
-      ::"r"(ptx::smem_u32(smem_dst)), "l"((uint64_t)map), "r"(ptx::smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
-      : "memory");
-}
-
-__device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2, int c3) {
-  asm volatile(
-      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
-      ::"r"(ptx::smem_u32(smem_dst)), "l"((uint64_t)map), "r"(ptx::smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
-      : "memory");
-}
-
-__device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const float* v) {
-  const uint32_t* r = reinterpret_cast<const uint32_t*>(v);
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
-      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
-      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
-        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
-        "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
-        "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
-      : "memory");
-}
-__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
-
-__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
-  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-  return *reinterpret_cast<uint32_t*>(&v);
-}
+using ptx::pack2_bf16;
+using ptx::smem_desc_mn_sw128;
+using ptx::tma_load_4d;
+using ptx::tma_load_5d;
+using ptx::tmem_st_32x32;
+using ptx::tmem_st_wait;
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) { return pack2_bf16(lo, hi); }
 
 // instruction descriptor of the second MMA: A (P) K-major, B (V) MN-major
 __host__ __device__ constexpr uint32_t idesc_pv(int m, int n) { return ptx::idesc_bf16_f32(m, n) | (1u << 16); }
@@ -584,6 +566,9 @@ std::tuple<Tensor, Tensor, Tensor, Tensor> df3_attention_bwd(const Tensor& q, co
                                                              const c10::optional<Tensor>& mask, const Tensor& lse,
                                                              double scale, bool want_dbias, int64_t chunk_bytes) {
   const int64_t B = q.size(0), R = q.size(1), H = q.size(2), N = q.size(3), D = q.size(4);
+  if (chunk_bytes >= 0 && attention_bwd_fused_supported(N, D))  // a negative chunk size asks for the chunked form
+    return attention_bwd_fused(q, k, v, out, d_out, bias, mask, lse, scale, want_dbias, c10::nullopt, c10::nullopt, c10::nullopt);
+  if (chunk_bytes < 0) chunk_bytes = -chunk_bytes;
   c10::cuda::CUDAGuard guard(q.device());
   auto bf = q.options();
   Tensor qc = q.contiguous(), kc = k.contiguous(), vc = v.contiguous();
@@ -638,20 +623,6 @@ std::tuple<Tensor, Tensor, Tensor, Tensor> df3_attention_bwd(const Tensor& q, co
   }
   if (!dbias.defined()) dbias = torch::empty({0}, bf.dtype(torch::kFloat32));
   return {dq, dk, dv, dbias};
-}
-
-CUtensorMap qkv_map(const Tensor& t) {  // [B, R, H, N, D] view -> 5-D map (d, n, h, r, b), box 64 x 128
-  const int64_t dims[5] = {t.size(4), t.size(3), t.size(2), t.size(1), t.size(0)};
-  const int64_t strides[5] = {1, t.stride(3), t.stride(2), t.stride(1), t.stride(0)};
-  const int box[5] = {64, 128, 1, 1, 1};
-  return make_map_nd(t.data_ptr(), 5, dims, strides, box);
-}
-
-bool strides_ok(const Tensor& t) {
-  if (t.stride(4) != 1 || reinterpret_cast<uintptr_t>(t.data_ptr()) % 16 != 0) return false;
-  for (int d = 0; d < 4; ++d)
-    if (t.size(d) > 1 && (t.stride(d) % 8 != 0 || t.stride(d) <= 0)) return false;
-  return true;
 }
 
 std::tuple<Tensor, Tensor> df3_attention_fwd(const Tensor& q_in, const Tensor& k_in, const Tensor& v_in,
@@ -753,6 +724,13 @@ void df3_register_attention(torch::Library& m) {
   m.def("attention_bwd(Tensor q, Tensor k, Tensor v, Tensor out, Tensor d_out, Tensor? bias, Tensor? key_mask, Tensor lse, "
         "float scale, bool want_dbias, int chunk_bytes) -> (Tensor, Tensor, Tensor, Tensor)",
         &df3::df3_attention_bwd);
+  m.def("attention_bwd_into(Tensor q, Tensor k, Tensor v, Tensor out, Tensor d_out, Tensor? bias, Tensor? key_mask, Tensor lse, "
+        "float scale, bool want_dbias, Tensor(a!) dq, Tensor(b!) dk, Tensor(c!) dv) -> Tensor",
+        [](const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& out, const Tensor& d_out, const c10::optional<Tensor>& bias,
+           const c10::optional<Tensor>& mask, const Tensor& lse, double scale, bool want_dbias, Tensor dq, Tensor dk, Tensor dv) {
+          return std::get<3>(df3::attention_bwd_fused(q, k, v, out, d_out, bias, mask, lse, scale, want_dbias, dq, dk, dv));
+        });
+  m.def("attention_bwd_fused_supported(int n, int d) -> bool", [](int64_t n, int64_t d) { return df3::attention_bwd_fused_supported(n, d); });
   m.def("attention_bwd_elem(Tensor(a!) s_io, Tensor(b!) dp_io, Tensor? bias, Tensor? mask, Tensor row_max, Tensor row_log2sum, Tensor delta, Tensor(c!)? dbias, float scale) -> ()",
         &df3::df3_attention_bwd_elem);
 }

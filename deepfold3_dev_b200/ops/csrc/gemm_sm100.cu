@@ -23,6 +23,7 @@
 #include <torch/library.h>
 #include <torch/torch.h>
 
+#include <algorithm>
 #include <mutex>
 #include <unordered_map>
 
@@ -88,39 +89,41 @@ namespace {
 constexpr int BM = 128;
 constexpr int BK = 64;  // 64 bf16 = one 128-byte swizzle row
 constexpr int kThreads = 192;
+constexpr int kEpiThreads = 128;
+constexpr int kGroupM = 8;  // tiles walk the output in bands of 8 tile rows so that concurrent CTAs share operands in L2
 
-enum Epi : int { kPlain = 0, kGated = 1, kSwiGLU = 2, kSigmoidMul = 3, kSwiGLUBwd = 4, kGatedBwd = 5 };
+enum Epi : int { kPlain = 0, kGated = 1, kSwiGLU = 2, kSigmoidMul = 3, kSwiGLUBwd = 4, kGatedBwd = 5, kGatedT = 6 };
 
 struct GemmParams {
-  __nv_bfloat16* C;
-  const float* bias;          // [n] or null
-  const float* row_mask;      // [batch * M] or null
+  void* C;                    // bf16 or fp32
+  const float* bias;          // per output column n (or per output row m when bias_on_m) or null
+  const float* row_mask;      // per output row m (or per column n when mask_on_n), one entry per batch row, or null
   const __nv_bfloat16* mul;   // [batch, M, N] (row stride ld_mul) or null
   int* status;
   long long c_batch_stride;   // elements
+  long long c_split_stride;   // elements between the partial results of a split-K launch
   long long mul_batch_stride;
-  int ldc;                    // row stride (row-major) or plane stride (channel-major), elements
+  long long ldc;              // row stride (row-major) or plane stride (channel-major), elements
   int ld_mul;
-  int M, N, K;                // N = output channels (half the accumulator width for the gated epilogues)
-  int m_tiles, n_tiles;
+  int M, N, K;                // N = output channels (half the accumulator width for the dual-B epilogues)
+  int m_tiles, n_tiles, batch, splits;
+  int kb_total, kb_per_split; // k blocks of 64
   int stages;
-  int b_batched;              // W has a batch axis
+  int b_batched, a_batched;   // operand has a batch axis
   int proj_row_offset;        // first row of the proj half inside the stacked weight
-  int channel_major;
+  int channel_major;          // legacy transposed store of the row-major tile (small shapes only)
+  int a_mn, b_mn;             // operand is MN-major (its M / N index is the contiguous one)
+  int c_fp32;
+  int bias_on_m, mask_on_n;
+  long long mask_batch_stride;
 };
 
-template <int BN>
+template <int BN, bool DUAL_A>
 struct Smem {
-  static constexpr int kABytes = BM * BK * 2;
+  static constexpr int kABytes = (DUAL_A ? 2 : 1) * BM * BK * 2;
   static constexpr int kBBytes = BN * BK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
 };
-
-__device__ __forceinline__ bool wait_quiet(uint64_t* bar, uint32_t parity) {
-  for (uint32_t i = 0; i < (1u << 20); ++i)
-    if (ptx::mbar_try_wait(bar, parity)) return true;
-  return false;
-}
 
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
@@ -128,17 +131,30 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 }
 
 // 32 consecutive outputs of one row, already final values.
-__device__ __forceinline__ void store_row32(const GemmParams& p, long long batch, int row, int n0, const float* v) {
+__device__ __forceinline__ void store_row32(const GemmParams& p, void* cbase, long long batch_off, int row, int n0, const float* v) {
   if (row >= p.M) return;
+  if (p.c_fp32) {
+    float* dst = reinterpret_cast<float*>(cbase) + batch_off + (long long)row * p.ldc + n0;
+    if (n0 + 32 <= p.N && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+#pragma unroll
+      for (int g = 0; g < 8; ++g) reinterpret_cast<float4*>(dst)[g] = make_float4(v[4 * g], v[4 * g + 1], v[4 * g + 2], v[4 * g + 3]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (n0 + j < p.N) dst[j] = v[j];
+    }
+    return;
+  }
+  __nv_bfloat16* cb = reinterpret_cast<__nv_bfloat16*>(cbase) + batch_off;
   if (p.channel_major) {
-    __nv_bfloat16* base = p.C + batch * p.c_batch_stride + (long long)n0 * p.ldc + row;
+    __nv_bfloat16* base = cb + (long long)n0 * p.ldc + row;
 #pragma unroll
     for (int j = 0; j < 32; ++j)
       if (n0 + j < p.N) base[(long long)j * p.ldc] = __float2bfloat16_rn(v[j]);
     return;
   }
-  __nv_bfloat16* dst = p.C + batch * p.c_batch_stride + (long long)row * p.ldc + n0;
-  if (n0 + 32 <= p.N && (p.ldc & 7) == 0) {
+  __nv_bfloat16* dst = cb + (long long)row * p.ldc + n0;
+  if (n0 + 32 <= p.N && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
 #pragma unroll
     for (int g = 0; g < 4; ++g) {
       uint4 q;
@@ -155,36 +171,82 @@ __device__ __forceinline__ void store_row32(const GemmParams& p, long long batch
   }
 }
 
+__device__ __forceinline__ void load_row32(const __nv_bfloat16* src, bool row_ok, int n0, int N, float* g) {
+  if (row_ok && n0 + 32 <= N && (reinterpret_cast<uintptr_t>(src) & 15) == 0) {
+#pragma unroll
+    for (int q4 = 0; q4 < 4; ++q4) {
+      const uint4 w = reinterpret_cast<const uint4*>(src)[q4];
+      const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const __nv_bfloat162 pr = *reinterpret_cast<const __nv_bfloat162*>(&ww[e]);
+        g[q4 * 8 + 2 * e] = __low2float(pr);
+        g[q4 * 8 + 2 * e + 1] = __high2float(pr);
+      }
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) g[j] = (row_ok && n0 + j < N) ? __bfloat162float(src[j]) : 0.f;
+  }
+}
+
+struct TileCoord {
+  int split, batch, m_tile, n_tile;
+};
+
+__device__ __forceinline__ TileCoord decode_tile(const GemmParams& p, long long t) {
+  TileCoord c;
+  const long long per_batch = (long long)p.m_tiles * p.n_tiles;
+  const long long bt = t / per_batch;
+  const int r = (int)(t - bt * per_batch);
+  c.batch = (int)(bt % p.batch);
+  c.split = (int)(bt / p.batch);
+  const int band = kGroupM * p.n_tiles;
+  const int g = r / band, q = r - g * band;
+  const int gm = min(kGroupM, p.m_tiles - g * kGroupM);
+  c.m_tile = g * kGroupM + q % gm;
+  c.n_tile = q / gm;
+  return c;
+}
+
+// Persistent kernel: each CTA walks tiles t = blockIdx.x, blockIdx.x + gridDim.x, ... The accumulator is double
+// buffered in tensor memory, so the epilogue warps drain tile t while the MMA warp already works on tile t + 1, and
+// the shared-memory ring keeps running across tile boundaries.
 template <int BN, int EPI>
 __global__ void __launch_bounds__(kThreads) gemm_kernel(const __grid_constant__ CUtensorMap tmA,
                                                        const __grid_constant__ CUtensorMap tmB, GemmParams p) {
-  using S = Smem<BN>;
+  constexpr bool kDualA = (EPI == kGatedT);   // gate and proj rows of the stacked weight as two A tiles: transposed (channel-major) output
+  using S = Smem<BN, kDualA>;
   constexpr bool kDual = (EPI == kGated || EPI == kSwiGLU || EPI == kSwiGLUBwd || EPI == kGatedBwd);
   constexpr bool kBwd = (EPI == kSwiGLUBwd || EPI == kGatedBwd);
-  constexpr int kOutPerTile = kDual ? BN / 2 : BN;  // output columns one CTA produces
+  constexpr int kOutPerTile = kDual ? BN / 2 : BN;  // output columns one tile produces
+  constexpr int kAccCols = (kDualA ? 2 : 1) * BN;   // tensor-memory columns of one accumulator buffer
+  constexpr uint32_t kTmemCols = 2 * kAccCols < 32 ? 32 : 2 * kAccCols;
+  static_assert(kTmemCols <= 512, "accumulator buffers exceed tensor memory");
   extern __shared__ uint8_t smem_raw[];
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full = reinterpret_cast<uint64_t*>(tiles + (size_t)p.stages * S::kStageBytes);
   uint64_t* empty = full + p.stages;
-  uint64_t* acc_ready = empty + p.stages;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_ready + 1);
+  uint64_t* acc_full = empty + p.stages;   // [2]
+  uint64_t* acc_empty = acc_full + 2;      // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n_tile = blockIdx.x % p.n_tiles;
-  const int m_tile = (blockIdx.x / p.n_tiles) % p.m_tiles;
-  const int batch = blockIdx.x / (p.n_tiles * p.m_tiles);
-  const int num_k = (p.K + BK - 1) / BK;
+  const long long total_tiles = (long long)p.m_tiles * p.n_tiles * p.batch * p.splits;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.stages; ++s) {
       ptx::mbar_init(&full[s], 1);
       ptx::mbar_init(&empty[s], 1);
     }
-    ptx::mbar_init(acc_ready, 1);
+    for (int s = 0; s < 2; ++s) {
+      ptx::mbar_init(&acc_full[s], 1);
+      ptx::mbar_init(&acc_empty[s], kEpiThreads);
+    }
     ptx::fence_barrier_init();
   }
   if (warp == 1) {
-    ptx::tmem_alloc(tmem_slot, BN);
+    ptx::tmem_alloc(tmem_slot, kTmemCols);
     ptx::tmem_relinquish();
   }
   ptx::tc_fence_before();
@@ -196,95 +258,135 @@ __global__ void __launch_bounds__(kThreads) gemm_kernel(const __grid_constant__ 
     if (ptx::elect_one()) {
       ptx::prefetch_tensormap(&tmA);
       ptx::prefetch_tensormap(&tmB);
-      int issued = 0;
+      long long it = 0;  // k blocks issued so far by this CTA (the ring position)
       bool ok = true;
-      for (int kb = 0; kb < num_k; ++kb) {
-        const int s = kb % p.stages;
-        const uint32_t ph = (uint32_t)(kb / p.stages) & 1u;
-        if (!ptx::mbar_wait(&empty[s], ph ^ 1u, p.status, kTimeoutStageEmpty)) { ok = false; break; }
-        uint8_t* a_s = tiles + (size_t)s * S::kStageBytes;
-        uint8_t* b_s = a_s + S::kABytes;
-        ptx::mbar_expect_tx(&full[s], S::kStageBytes);
-        ptx::tma_load_3d(a_s, &tmA, &full[s], kb * BK, m_tile * BM, batch);
-        const int bz = p.b_batched ? batch : 0;
-        if (kDual) {
-          ptx::tma_load_3d(b_s, &tmB, &full[s], kb * BK, n_tile * (BN / 2), bz);
-          ptx::tma_load_3d(b_s + S::kBBytes / 2, &tmB, &full[s], kb * BK, p.proj_row_offset + n_tile * (BN / 2), bz);
-        } else {
-          ptx::tma_load_3d(b_s, &tmB, &full[s], kb * BK, n_tile * BN, bz);
+      for (long long t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        const TileCoord c = decode_tile(p, t);
+        const int kb0 = c.split * p.kb_per_split, kb1 = min(p.kb_total, kb0 + p.kb_per_split);
+        const int az = p.a_batched ? c.batch : 0, bz = p.b_batched ? c.batch : 0;
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
+          const int s = (int)(it % p.stages);
+          const uint32_t ph = (uint32_t)(it / p.stages) & 1u;
+          if (!ptx::mbar_wait(&empty[s], ph ^ 1u, p.status, kTimeoutStageEmpty)) { ok = false; break; }
+          uint8_t* a_s = tiles + (size_t)s * S::kStageBytes;
+          uint8_t* b_s = a_s + S::kABytes;
+          ptx::mbar_expect_tx(&full[s], S::kStageBytes);
+          if (p.a_mn) {  // [k][m] with m contiguous: two 64-wide column blocks of 64 k rows
+            ptx::tma_load_3d(a_s, &tmA, &full[s], c.m_tile * BM, kb * BK, az);
+            ptx::tma_load_3d(a_s + 8192, &tmA, &full[s], c.m_tile * BM + 64, kb * BK, az);
+          } else {
+            ptx::tma_load_3d(a_s, &tmA, &full[s], kb * BK, c.m_tile * BM, az);
+            if (kDualA) ptx::tma_load_3d(a_s + BM * BK * 2, &tmA, &full[s], kb * BK, p.proj_row_offset + c.m_tile * BM, az);
+          }
+          if (p.b_mn) {
+#pragma unroll
+            for (int blk = 0; blk < BN / 64; ++blk)
+              ptx::tma_load_3d(b_s + blk * 8192, &tmB, &full[s], c.n_tile * BN + blk * 64, kb * BK, bz);
+          } else if (kDual) {
+            ptx::tma_load_3d(b_s, &tmB, &full[s], kb * BK, c.n_tile * (BN / 2), bz);
+            ptx::tma_load_3d(b_s + S::kBBytes / 2, &tmB, &full[s], kb * BK, p.proj_row_offset + c.n_tile * (BN / 2), bz);
+          } else {
+            ptx::tma_load_3d(b_s, &tmB, &full[s], kb * BK, c.n_tile * BN, bz);
+          }
         }
-        issued = kb + 1;
       }
       if (!ok) {  // give up: let the copies already in flight land before the CTA's shared memory goes away
-        const int first = issued > p.stages ? issued - p.stages : 0;
-        for (int kb = first; kb < issued; ++kb) wait_quiet(&full[kb % p.stages], (uint32_t)(kb / p.stages) & 1u);
+        const long long first = it > p.stages ? it - p.stages : 0;
+        for (long long k = first; k < it; ++k) ptx::mbar_wait_quiet(&full[k % p.stages], (uint32_t)(k / p.stages) & 1u);
       }
     }
   } else if (warp == 1) {
     if (ptx::elect_one()) {
-      constexpr uint32_t idesc = ptx::idesc_bf16_f32(BM, BN);
+      const uint32_t idesc = ptx::idesc_bf16_f32(BM, BN) | (p.a_mn ? ptx::kIdescAMnMajor : 0u) | (p.b_mn ? ptx::kIdescBMnMajor : 0u);
+      long long it = 0;
       bool ok = true;
-      for (int kb = 0; kb < num_k; ++kb) {
-        const int s = kb % p.stages;
-        const uint32_t ph = (uint32_t)(kb / p.stages) & 1u;
-        if (!ptx::mbar_wait(&full[s], ph, p.status, kTimeoutTmaFull)) { ok = false; break; }
+      int local = 0;
+      for (long long t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++local) {
+        const TileCoord c = decode_tile(p, t);
+        const int kb0 = c.split * p.kb_per_split, kb1 = min(p.kb_total, kb0 + p.kb_per_split);
+        const int ab = local & 1;
+        if (!ptx::mbar_wait(&acc_empty[ab], (uint32_t)((local >> 1) & 1) ^ 1u, p.status, kTimeoutStageEmpty)) { ok = false; break; }
         ptx::tc_fence_after();
-        const uint32_t a_addr = ptx::smem_u32(tiles + (size_t)s * S::kStageBytes);
-        const uint64_t a_desc = ptx::smem_desc_k_sw128(a_addr);
-        const uint64_t b_desc = ptx::smem_desc_k_sw128(a_addr + S::kABytes);
+        const uint32_t acc = tmem + ab * kAccCols;
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
+          const int s = (int)(it % p.stages);
+          const uint32_t ph = (uint32_t)(it / p.stages) & 1u;
+          if (!ptx::mbar_wait(&full[s], ph, p.status, kTimeoutTmaFull)) { ok = false; break; }
+          ptx::tc_fence_after();
+          const uint32_t a_addr = ptx::smem_u32(tiles + (size_t)s * S::kStageBytes);
+          const uint32_t b_addr = a_addr + S::kABytes;
+          const uint64_t a_desc = p.a_mn ? ptx::smem_desc_mn_sw128(a_addr, 8192) : ptx::smem_desc_k_sw128(a_addr);
+          const uint64_t b_desc = p.b_mn ? ptx::smem_desc_mn_sw128(b_addr, 8192) : ptx::smem_desc_k_sw128(b_addr);
+          // 16 bf16 along K per MMA: 32 bytes inside the swizzled row (K-major) or 16 rows of 128 bytes (MN-major)
+          const uint64_t a_step = p.a_mn ? (2048 >> 4) : 2, b_step = p.b_mn ? (2048 >> 4) : 2;
 #pragma unroll
-        for (int k = 0; k < BK / 16; ++k)  // 16 bf16 = 32 bytes per MMA along K: descriptor address advances by 2
-          ptx::umma_bf16(tmem, a_desc + (uint64_t)(2 * k), b_desc + (uint64_t)(2 * k), idesc, (kb | k) != 0);
-        ptx::umma_commit(&empty[s]);
+          for (int k = 0; k < BK / 16; ++k) {
+            const uint32_t accum = (kb != kb0 || k != 0) ? 1u : 0u;
+            ptx::umma_bf16(acc, a_desc + a_step * k, b_desc + b_step * k, idesc, accum);
+            if (kDualA) {
+              const uint64_t a2 = ptx::smem_desc_k_sw128(a_addr + BM * BK * 2);
+              ptx::umma_bf16(acc + BN, a2 + 2 * k, b_desc + b_step * k, idesc, accum);
+            }
+          }
+          ptx::umma_commit(&empty[s]);
+        }
+        if (ok) ptx::umma_commit(&acc_full[ab]);
       }
-      if (ok) ptx::umma_commit(acc_ready);
     }
   } else {
     const int q = warp & 3;  // TMEM lane quarter this warp may read
-    if (ptx::mbar_wait(acc_ready, 0, p.status, kTimeoutMmaDone)) {
+    int local = 0;
+    bool ok = true;
+    for (long long t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++local) {
+      const TileCoord c = decode_tile(p, t);
+      const int ab = local & 1;
+      if (!ptx::mbar_wait(&acc_full[ab], (uint32_t)(local >> 1) & 1u, p.status, kTimeoutMmaDone)) { ok = false; break; }
       ptx::tc_fence_after();
-      const int row = m_tile * BM + q * 32 + lane;
-      const uint32_t t_row = tmem + ((uint32_t)(q * 32) << 16);
-      const float rm = (p.row_mask != nullptr && row < p.M) ? p.row_mask[(long long)batch * p.M + row] : 1.f;
+      const int row = c.m_tile * BM + q * 32 + lane;
+      const uint32_t t_row = tmem + ab * kAccCols + ((uint32_t)(q * 32) << 16);
+      const long long batch = c.batch;
+      const long long c_off = batch * p.c_batch_stride + (long long)c.split * p.c_split_stride;
+      const float* mask_b = p.row_mask ? p.row_mask + batch * p.mask_batch_stride : nullptr;
+      const float rm = (mask_b != nullptr && !p.mask_on_n && row < p.M) ? mask_b[row] : 1.f;
+      const float bm = (p.bias != nullptr && p.bias_on_m && row < p.M) ? p.bias[row] : 0.f;
       float a[32], b[32];
 #pragma unroll 1
-      for (int c = 0; c < kOutPerTile / 32; ++c) {
-        const int n0 = n_tile * kOutPerTile + c * 32;
+      for (int cc = 0; cc < kOutPerTile / 32; ++cc) {
+        const int n0 = c.n_tile * kOutPerTile + cc * 32;
         if (n0 >= p.N) break;
-        ptx::tmem_ld_32x32(t_row + c * 32, a);
-        if (kDual) ptx::tmem_ld_32x32(t_row + BN / 2 + c * 32, b);
+        ptx::tmem_ld_32x32(t_row + cc * 32, a);
+        if (kDual) ptx::tmem_ld_32x32(t_row + BN / 2 + cc * 32, b);
+        if (kDualA) ptx::tmem_ld_32x32(t_row + BN + cc * 32, b);
         ptx::tmem_ld_wait();
         if (EPI == kPlain) {
+          if (p.bias != nullptr && !p.bias_on_m) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const float bv = (p.bias != nullptr && n0 + j < p.N) ? p.bias[n0 + j] : 0.f;
-            a[j] = (a[j] + bv) * rm;
+            for (int j = 0; j < 32; ++j) a[j] += (n0 + j < p.N) ? p.bias[n0 + j] : 0.f;
+          }
+          if (mask_b != nullptr && p.mask_on_n) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) a[j] = (a[j] + bm) * ((n0 + j < p.N) ? mask_b[n0 + j] : 0.f);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) a[j] = (a[j] + bm) * rm;
           }
         } else if (EPI == kGated) {
 #pragma unroll
           for (int j = 0; j < 32; ++j) a[j] = sigmoidf_(a[j]) * b[j] * rm;
+        } else if (EPI == kGatedT) {
+          // rows are output channels, columns are the input rows: the mask runs along the columns
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const float mk = mask_b ? ((n0 + j < p.N) ? mask_b[n0 + j] : 0.f) : 1.f;
+            a[j] = sigmoidf_(a[j]) * b[j] * mk;
+          }
         } else if (EPI == kSwiGLU) {
 #pragma unroll
           for (int j = 0; j < 32; ++j) a[j] = a[j] * sigmoidf_(a[j]) * b[j];
         } else if (kBwd) {
           const __nv_bfloat16* grow = p.mul + batch * p.mul_batch_stride + (long long)row * p.ld_mul + n0;
           float g[32];
-          if (row < p.M && n0 + 32 <= p.N && (reinterpret_cast<uintptr_t>(grow) & 15) == 0) {
-#pragma unroll
-            for (int q4 = 0; q4 < 4; ++q4) {
-              const uint4 w = reinterpret_cast<const uint4*>(grow)[q4];
-              const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                const __nv_bfloat162 pr = *reinterpret_cast<const __nv_bfloat162*>(&ww[e]);
-                g[q4 * 8 + 2 * e] = __low2float(pr);
-                g[q4 * 8 + 2 * e + 1] = __high2float(pr);
-              }
-            }
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) g[j] = (row < p.M && n0 + j < p.N) ? __bfloat162float(grow[j]) : 0.f;
-          }
+          load_row32(grow, row < p.M, n0, p.N, g);
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
             const float sg = sigmoidf_(a[j]);
@@ -294,64 +396,83 @@ __global__ void __launch_bounds__(kThreads) gemm_kernel(const __grid_constant__ 
             a[j] = da;
             b[j] = dbv;
           }
-          store_row32(p, batch, row, n0, a);
-          GemmParams p2 = p;
-          p2.C = p.C + p.N;  // second half of the [M, 2 N] output; bounds are those of the first half
-          store_row32(p2, batch, row, n0, b);
+          store_row32(p, p.C, c_off, row, n0, a);
+          store_row32(p, reinterpret_cast<__nv_bfloat16*>(p.C) + p.N, c_off, row, n0, b);  // second half of the [M, 2 N] output
           continue;
-        } else {
+        } else {  // kSigmoidMul
           const __nv_bfloat16* mrow = p.mul + batch * p.mul_batch_stride + (long long)row * p.ld_mul + n0;
-          if (row < p.M && n0 + 32 <= p.N && (reinterpret_cast<uintptr_t>(mrow) & 15) == 0) {
+          float g[32];
+          load_row32(mrow, row < p.M, n0, p.N, g);
 #pragma unroll
-            for (int g = 0; g < 4; ++g) {
-              const uint4 w = reinterpret_cast<const uint4*>(mrow)[g];
-              const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                const __nv_bfloat162 pr = *reinterpret_cast<const __nv_bfloat162*>(&ww[e]);
-                const int j = g * 8 + 2 * e;
-                const float b0 = p.bias ? p.bias[n0 + j] : 0.f, b1 = p.bias ? p.bias[n0 + j + 1] : 0.f;
-                a[j] = sigmoidf_(a[j] + b0) * __low2float(pr);
-                a[j + 1] = sigmoidf_(a[j + 1] + b1) * __high2float(pr);
-              }
-            }
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const bool in = row < p.M && n0 + j < p.N;
-              const float bv = (p.bias != nullptr && in) ? p.bias[n0 + j] : 0.f;
-              const float mv = in ? __bfloat162float(mrow[j]) : 0.f;
-              a[j] = sigmoidf_(a[j] + bv) * mv;
-            }
+          for (int j = 0; j < 32; ++j) {
+            const float bv = (p.bias != nullptr && n0 + j < p.N) ? p.bias[n0 + j] : 0.f;
+            a[j] = sigmoidf_(a[j] + bv) * g[j];
           }
         }
-        store_row32(p, batch, row, n0, a);
+        store_row32(p, p.C, c_off, row, n0, a);
       }
+      ptx::tc_fence_before();
+      ptx::mbar_arrive(&acc_empty[ab]);
     }
   }
   ptx::tc_fence_before();
   __syncthreads();
   if (warp == 1) {
     ptx::tc_fence_after();
-    ptx::tmem_dealloc(tmem, BN);
+    ptx::tmem_dealloc(tmem, kTmemCols);
+  }
+}
+
+// out[e] = sum over the splits of partial[s][e] (+ nothing else: split launches use the plain epilogue without bias).
+template <typename OutT>
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restrict__ partial, OutT* __restrict__ out, long long n,
+                                                            int splits) {
+  const long long e = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  if (e >= n) return;
+  if (e + 4 <= n) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s = 0; s < splits; ++s) {
+      const float4 v = *reinterpret_cast<const float4*>(partial + (long long)s * n + e);
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    out[e] = from_float<OutT>(acc.x); out[e + 1] = from_float<OutT>(acc.y);
+    out[e + 2] = from_float<OutT>(acc.z); out[e + 3] = from_float<OutT>(acc.w);
+  } else {
+    for (long long k = e; k < n; ++k) {
+      float acc = 0.f;
+      for (int s = 0; s < splits; ++s) acc += partial[(long long)s * n + k];
+      out[k] = from_float<OutT>(acc);
+    }
   }
 }
 
 // ---- host ---------------------------------------------------------------------------------------
-CUtensorMap make_map(const void* base, int64_t inner, int64_t rows, int64_t batch, int64_t row_stride,
-                     int64_t batch_stride, int box_rows) {
+int sm_count() {
+  static int n = [] {
+    int dev = 0, v = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
+    return v > 0 ? v : 148;
+  }();
+  return n;
+}
+
+// K-major operand [batch, rows, K]: box = 64 k x box_rows; MN-major operand [batch, K, cols]: box = 64 cols x 64 k.
+CUtensorMap operand_map(const Tensor& t3, bool mn_major, int box_rows) {
+  const int64_t inner = t3.size(2), rows = t3.size(1), batch = t3.size(0);
   const int64_t dims[3] = {inner, rows, batch};
-  const int64_t strides[3] = {1, row_stride, batch_stride};
-  const int box[3] = {BK, box_rows, 1};
-  return make_map_nd(base, 3, dims, strides, box);
+  const int64_t strides[3] = {1, t3.stride(1), batch > 1 ? t3.stride(0) : rows * t3.stride(1)};
+  const int box[3] = {BK, mn_major ? BK : box_rows, 1};
+  return make_map_nd(t3.data_ptr(), 3, dims, strides, box);
 }
 
 template <int BN, int EPI>
-void launch(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams& p, int64_t batch, cudaStream_t stream) {
-  using S = Smem<BN>;
-  const int num_k = (p.K + BK - 1) / BK;
-  // enough stages to cover a short K loop without spending shared memory that a second resident CTA could use
-  const int stages = num_k < 2 ? 2 : (num_k > 4 ? 4 : num_k);
+void launch(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams& p, cudaStream_t stream) {
+  using S = Smem<BN, EPI == kGatedT>;
+  const int per_tile_k = p.kb_per_split;
+  // a deep ring when the K loop is long; short loops (pair-shaped GEMMs, two k blocks) still get four stages so that
+  // the loads of the next tiles run ahead of the epilogue
+  int stages = per_tile_k >= 8 ? 6 : 4;
+  while (stages > 2 && (size_t)stages * S::kStageBytes + 2048 > 220 * 1024) --stages;
   p.stages = stages;
   const size_t smem = (size_t)stages * S::kStageBytes + 1024 + 256;
   static bool attr_set = false;
@@ -359,44 +480,100 @@ void launch(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams& p, int64_t
     C10_CUDA_CHECK(cudaFuncSetAttribute(gemm_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
     attr_set = true;
   }
-  const long long ctas = (long long)p.m_tiles * p.n_tiles * batch;
-  TORCH_CHECK(ctas > 0 && ctas < (1ll << 31), "gemm: grid too large");
+  const long long tiles = (long long)p.m_tiles * p.n_tiles * p.batch * p.splits;
+  TORCH_CHECK(tiles > 0 && tiles < (1ll << 40), "gemm: grid too large");
+  // one CTA per SM, or two when both the shared memory and the tensor-memory columns allow it
+  constexpr int acc_cols = (EPI == kGatedT ? 2 : 1) * BN * 2;
+  const int per_sm = (smem <= 110 * 1024 && acc_cols <= 256) ? 2 : 1;
+  const long long ctas = std::min<long long>(tiles, (long long)sm_count() * per_sm);
   gemm_kernel<BN, EPI><<<(unsigned)ctas, kThreads, smem, stream>>>(ta, tb, p);
   C10_CUDA_KERNEL_LAUNCH_CHECK();
 }
 
-// a: [batch, M, K] view (last dim contiguous); w: [wb, Nw, K]; returns [batch, M, N] or [batch, N, M].
-Tensor gemm_impl(const Tensor& a3, const Tensor& w3, const c10::optional<Tensor>& bias,
-                 const c10::optional<Tensor>& row_mask, const c10::optional<Tensor>& mul, int epi, bool channel_major) {
+struct GemmOpts {
+  Tensor out;                        // optional preallocated contiguous [batch, M, N] result of the plain epilogue
+  bool a_mn = false, b_mn = false;   // a3 is [batch, K, M] / w3 is [wb, K, N] (contiguous M / N) instead of [.., rows, K]
+  bool out_fp32 = false;
+  bool channel_major = false;        // return [batch, N, M]
+  int splits = 1;                    // split the K loop; partial sums are added in a fixed order afterwards
+};
+
+// a: [batch or 1, M, K] (or [.., K, M] when a_mn); w: [wb, Nw, K] (or [wb, K, Nw] when b_mn); returns [batch, M, N]
+// (or [batch, N, M] when channel_major), bf16 or fp32.
+Tensor gemm_impl(const Tensor& a3, const Tensor& w3, const c10::optional<Tensor>& bias, const c10::optional<Tensor>& row_mask,
+                 const c10::optional<Tensor>& mul, int epi, GemmOpts o) {
   TORCH_CHECK(a3.is_cuda() && a3.scalar_type() == torch::kBFloat16 && w3.scalar_type() == torch::kBFloat16,
               "gemm: bf16 CUDA tensors expected");
-  TORCH_CHECK(a3.dim() == 3 && w3.dim() == 3 && a3.stride(2) == 1 && w3.stride(2) == 1, "gemm: [b, rows, k] operands");
-  const int64_t batch = a3.size(0), M = a3.size(1), K = a3.size(2);
-  const int64_t wb = w3.size(0), Nw = w3.size(1);
-  TORCH_CHECK(w3.size(2) == K && (wb == 1 || wb == batch), "gemm: operand shapes disagree");
-  TORCH_CHECK(K % 8 == 0 && a3.stride(1) % 8 == 0 && w3.stride(1) % 8 == 0, "gemm: K and row strides must be multiples of 8");
+  TORCH_CHECK(a3.dim() == 3 && w3.dim() == 3 && a3.stride(2) == 1 && w3.stride(2) == 1, "gemm: 3-D operands with a contiguous last axis");
+  const int64_t ab = a3.size(0), wb = w3.size(0);
+  const int64_t M = o.a_mn ? a3.size(2) : a3.size(1), K = o.a_mn ? a3.size(1) : a3.size(2);
+  const int64_t Nw = o.b_mn ? w3.size(2) : w3.size(1), Kw = o.b_mn ? w3.size(1) : w3.size(2);
+  const int64_t batch = std::max(ab, wb);
+  TORCH_CHECK(Kw == K && (wb == 1 || wb == batch) && (ab == 1 || ab == batch), "gemm: operand shapes disagree");
+  TORCH_CHECK(a3.size(2) % 8 == 0 && w3.size(2) % 8 == 0 && a3.stride(1) % 8 == 0 && w3.stride(1) % 8 == 0,
+              "gemm: contiguous extents and row strides must be multiples of 8");
   TORCH_CHECK(reinterpret_cast<uintptr_t>(a3.data_ptr()) % 16 == 0 && reinterpret_cast<uintptr_t>(w3.data_ptr()) % 16 == 0,
               "gemm: operands must be 16-byte aligned");
-  TORCH_CHECK(batch == 1 || a3.stride(0) % 8 == 0, "gemm: batch stride must be a multiple of 8");
+  TORCH_CHECK((ab == 1 || a3.stride(0) % 8 == 0) && (wb == 1 || w3.stride(0) % 8 == 0), "gemm: batch strides must be multiples of 8");
   const bool dual = (epi == kGated || epi == kSwiGLU || epi == kSwiGLUBwd || epi == kGatedBwd);
   const bool bwd = (epi == kSwiGLUBwd || epi == kGatedBwd);
-  TORCH_CHECK(!bwd || !channel_major, "gemm: the backward epilogues store row-major");
+  TORCH_CHECK(!bwd || !o.channel_major, "gemm: the backward epilogues store row-major");
   TORCH_CHECK(!dual || Nw % 2 == 0, "gemm: stacked gate/proj weight expected");
+  TORCH_CHECK(epi == kPlain || (!o.a_mn && !o.b_mn && !o.out_fp32 && o.splits == 1), "gemm: fused epilogues take K-major operands");
   const int64_t N = dual ? Nw / 2 : Nw;
-  TORCH_CHECK(M < (1ll << 31) && N < (1 << 24) && K < (1 << 24), "gemm: size out of range");
+  TORCH_CHECK(M < (1ll << 31) && N < (1ll << 31) && K < (1 << 24), "gemm: size out of range");
   c10::cuda::CUDAGuard guard(a3.device());
   auto opts = a3.options();
-  Tensor out = channel_major ? torch::empty({batch, N, M}, opts) : torch::empty({batch, M, bwd ? 2 * N : N}, opts);
-  if (out.numel() == 0) return out;
+  cudaStream_t stream = at::cuda::getCurrentCUDAStream();
+
+  // Channel-major output of the plain and gated epilogues: compute the transposed product instead (the weight becomes
+  // the A operand, so a tensor-memory lane is an output channel and every thread stores contiguous runs of one plane).
+  if (o.channel_major && (epi == kPlain || epi == kGated) && !o.a_mn && !o.b_mn && M >= 64) {
+    TORCH_CHECK(ab == batch || batch == 1, "gemm: channel-major output with a broadcast input");
+    Tensor out = torch::empty({batch, N, M}, opts);
+    if (out.numel() == 0) return out;
+    GemmParams p{};
+    p.C = out.data_ptr();
+    Tensor bias_f, mask_f;
+    if (bias.has_value() && bias->defined()) {
+      bias_f = bias->to(torch::kFloat32).contiguous();
+      TORCH_CHECK(bias_f.numel() == N, "gemm: bias length");
+      p.bias = bias_f.data_ptr<float>();
+      p.bias_on_m = 1;
+    }
+    if (row_mask.has_value() && row_mask->defined()) {
+      mask_f = row_mask->to(torch::kFloat32).contiguous();
+      TORCH_CHECK(mask_f.numel() == batch * M, "gemm: row mask length");
+      p.row_mask = mask_f.data_ptr<float>();
+      p.mask_on_n = 1;
+      p.mask_batch_stride = M;
+    }
+    Tensor status = status_word(a3.device().index());
+    p.status = status.data_ptr<int>();
+    p.M = (int)N; p.N = (int)M; p.K = (int)K;   // roles swapped
+    constexpr int BN = 128;
+    p.m_tiles = (int)((N + BM - 1) / BM);
+    p.n_tiles = (int)((M + BN - 1) / BN);
+    p.batch = (int)batch; p.splits = 1;
+    p.kb_total = p.kb_per_split = (int)((K + BK - 1) / BK);
+    p.a_batched = wb > 1; p.b_batched = ab > 1;
+    p.proj_row_offset = (int)N;
+    p.ldc = M;
+    p.c_batch_stride = N * M;
+    const CUtensorMap ta = operand_map(w3, false, BM);
+    const CUtensorMap tb = operand_map(a3, false, BN);
+    if (epi == kPlain) launch<BN, kPlain>(ta, tb, p, stream); else launch<BN, kGatedT>(ta, tb, p, stream);
+    return out;
+  }
 
   // accumulator width: the widest tile that the output needs
   int BN;
   if (dual) BN = N >= 128 ? 256 : (N >= 64 ? 128 : 64);
-  else BN = N > 64 ? 128 : (N > 32 ? 64 : 32);
+  else BN = (epi == kPlain && N > 128 && K >= 512 && M > 2048) ? 256 : (N > 64 ? 128 : (N > 32 ? 64 : 32));
+  if (o.b_mn && BN < 64) BN = 64;
   const int out_per_tile = dual ? BN / 2 : BN;
 
   GemmParams p{};
-  p.C = reinterpret_cast<__nv_bfloat16*>(out.data_ptr());
   Tensor bias_f, mask_f, mul_c;
   if (bias.has_value() && bias->defined()) {
     bias_f = bias->to(torch::kFloat32).contiguous();
@@ -407,6 +584,7 @@ Tensor gemm_impl(const Tensor& a3, const Tensor& w3, const c10::optional<Tensor>
     mask_f = row_mask->to(torch::kFloat32).contiguous();
     TORCH_CHECK(mask_f.numel() == batch * M, "gemm: row mask length");
     p.row_mask = mask_f.data_ptr<float>();
+    p.mask_batch_stride = M;
   }
   if (epi == kSigmoidMul || bwd) {
     TORCH_CHECK(mul.has_value() && mul->defined(), "gemm: sigmoid-mul epilogue needs the multiplicand");
@@ -421,20 +599,45 @@ Tensor gemm_impl(const Tensor& a3, const Tensor& w3, const c10::optional<Tensor>
   p.M = (int)M; p.N = (int)N; p.K = (int)K;
   p.m_tiles = (int)((M + BM - 1) / BM);
   p.n_tiles = (int)((N + out_per_tile - 1) / out_per_tile);
-  p.b_batched = wb > 1;
+  p.batch = (int)batch;
+  p.kb_total = (int)((K + BK - 1) / BK);
+  int splits = std::max(1, std::min(o.splits, p.kb_total));
+  p.kb_per_split = (p.kb_total + splits - 1) / splits;
+  splits = (p.kb_total + p.kb_per_split - 1) / p.kb_per_split;
+  p.splits = splits;
+  p.a_batched = ab > 1; p.b_batched = wb > 1;
   p.proj_row_offset = (int)N;
-  p.channel_major = channel_major;
-  p.ldc = channel_major ? (int)M : (int)(bwd ? 2 * N : N);
-  p.c_batch_stride = M * (bwd ? 2 * N : N);
+  p.a_mn = o.a_mn; p.b_mn = o.b_mn;
+  const int64_t out_cols = bwd ? 2 * N : N;
+  if (o.out.defined())
+    TORCH_CHECK(epi == kPlain && !o.channel_major && o.out.is_contiguous() && o.out.numel() == batch * M * N &&
+                o.out.scalar_type() == (o.out_fp32 ? torch::kFloat32 : torch::kBFloat16), "gemm: preallocated output shape / dtype");
+  Tensor out, partial;
+  if (splits > 1) {
+    TORCH_CHECK(!o.channel_major && epi == kPlain && !p.bias && !p.row_mask, "gemm: split-K takes the plain epilogue");
+    partial = torch::empty({splits, batch, M, N}, opts.dtype(torch::kFloat32));
+    out = o.out.defined() ? o.out : torch::empty({batch, M, N}, o.out_fp32 ? opts.dtype(torch::kFloat32) : opts);
+    p.C = partial.data_ptr();
+    p.c_fp32 = 1;
+    p.c_split_stride = batch * M * N;
+  } else {
+    out = o.out.defined() ? o.out
+          : o.channel_major ? torch::empty({batch, N, M}, opts)
+                            : torch::empty({batch, M, out_cols}, o.out_fp32 ? opts.dtype(torch::kFloat32) : opts);
+    p.C = out.data_ptr();
+    p.c_fp32 = o.out_fp32;
+  }
+  if (out.numel() == 0) return out;
+  p.channel_major = o.channel_major;
+  p.ldc = o.channel_major ? M : out_cols;
+  p.c_batch_stride = M * out_cols;
 
-  const int box_b = dual ? BN / 2 : BN;
-  const CUtensorMap ta = make_map(a3.data_ptr(), K, M, batch, a3.stride(1), batch > 1 ? a3.stride(0) : M * a3.stride(1), BM);
-  const CUtensorMap tb = make_map(w3.data_ptr(), K, Nw, wb, w3.stride(1), wb > 1 ? w3.stride(0) : Nw * w3.stride(1), box_b);
-  cudaStream_t stream = at::cuda::getCurrentCUDAStream();
-#define DF3_LAUNCH(BN_, EPI_) launch<BN_, EPI_>(ta, tb, p, batch, stream)
+  const CUtensorMap ta = operand_map(a3, o.a_mn, BM);
+  const CUtensorMap tb = operand_map(w3, o.b_mn, dual ? BN / 2 : BN);
+#define DF3_LAUNCH(BN_, EPI_) launch<BN_, EPI_>(ta, tb, p, stream)
   switch (epi) {
     case kPlain:
-      if (BN == 128) DF3_LAUNCH(128, kPlain); else if (BN == 64) DF3_LAUNCH(64, kPlain); else DF3_LAUNCH(32, kPlain);
+      if (BN == 256) DF3_LAUNCH(256, kPlain); else if (BN == 128) DF3_LAUNCH(128, kPlain); else if (BN == 64) DF3_LAUNCH(64, kPlain); else DF3_LAUNCH(32, kPlain);
       break;
     case kSigmoidMul:
       if (BN == 128) DF3_LAUNCH(128, kSigmoidMul); else if (BN == 64) DF3_LAUNCH(64, kSigmoidMul); else DF3_LAUNCH(32, kSigmoidMul);
@@ -455,6 +658,15 @@ Tensor gemm_impl(const Tensor& a3, const Tensor& w3, const c10::optional<Tensor>
       TORCH_CHECK(false, "gemm: unknown epilogue ", epi);
   }
 #undef DF3_LAUNCH
+  if (splits > 1) {
+    const long long n = out.numel();
+    const unsigned grid = (unsigned)((n / 4 + 256) / 256);
+    if (o.out_fp32)
+      splitk_reduce_kernel<float><<<grid, 256, 0, stream>>>(partial.data_ptr<float>(), out.data_ptr<float>(), n, splits);
+    else
+      splitk_reduce_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(partial.data_ptr<float>(), reinterpret_cast<__nv_bfloat16*>(out.data_ptr()), n, splits);
+    C10_CUDA_KERNEL_LAUNCH_CHECK();
+  }
   return out;
 }
 
@@ -466,37 +678,76 @@ Tensor df3_gemm(const Tensor& x, const Tensor& w, const c10::optional<Tensor>& b
   const int64_t K = xc.size(-1);
   Tensor a3 = xc.view({1, -1, K});
   Tensor w3 = w.contiguous().view({1, w.size(0), K});
-  Tensor out = gemm_impl(a3, w3, bias, row_mask, mul, (int)epi, channel_major);
+  GemmOpts o;
+  o.channel_major = channel_major;
+  Tensor out = gemm_impl(a3, w3, bias, row_mask, mul, (int)epi, o);
   if (channel_major) return out.view({out.size(1), out.size(2)});
   auto shape = xc.sizes().vec();
   shape.back() = out.size(2);
   return out.view(shape);
 }
 
+Tensor as3d(const Tensor& t) {
+  Tensor c = t.dim() == 2 ? t.unsqueeze(0) : t;
+  TORCH_CHECK(c.dim() == 3, "bmm: 2-D or 3-D operands");
+  if (c.stride(2) != 1 || c.stride(1) % 8 != 0 || (c.size(0) > 1 && c.stride(0) % 8 != 0) ||
+      reinterpret_cast<uintptr_t>(c.data_ptr()) % 16 != 0)
+    c = c.contiguous();
+  return c.scalar_type() == torch::kBFloat16 ? c : c.to(torch::kBFloat16);
+}
+
 // a: [B, M, K], b: [B, N, K] -> [B, M, N]: sum over the shared last axis (both K-major).
 Tensor df3_bmm_nt(const Tensor& a, const Tensor& b) {
   TORCH_CHECK(a.dim() == 3 && b.dim() == 3 && a.size(0) == b.size(0), "bmm_nt: [B, M, K] x [B, N, K]");
-  Tensor ac = a.stride(2) == 1 ? a : a.contiguous();
-  Tensor bc = b.stride(2) == 1 ? b : b.contiguous();
-  return gemm_impl(ac, bc, c10::nullopt, c10::nullopt, c10::nullopt, kPlain, false);
+  return gemm_impl(as3d(a), as3d(b), c10::nullopt, c10::nullopt, c10::nullopt, kPlain, GemmOpts{});
+}
+
+// General product on the tcgen05 kernel: out[b, m, n] = sum_k A[b, m, k] B[b, k, n] with either operand given transposed.
+//   a: [B or 1, M, K], or [B or 1, K, M] with trans_a;  b: [B or 1, K, N], or [B or 1, N, K] with trans_b.
+// No operand is copied as long as its last axis is contiguous. `splits` > 1 cuts the K loop into that many pieces whose
+// fp32 partial results are added in a fixed order (long-K products with few output tiles: weight gradients); 0 picks
+// a count that fills the GPU.
+Tensor df3_matmul(const Tensor& a, const Tensor& b, bool trans_a, bool trans_b, bool out_fp32, int64_t splits,
+                  const c10::optional<Tensor>& out_given = c10::nullopt) {
+  Tensor a3 = as3d(a), b3 = as3d(b);
+  GemmOpts o;
+  if (out_given.has_value() && out_given->defined()) o.out = *out_given;
+  o.a_mn = trans_a;          // [K, M] with M contiguous
+  o.b_mn = !trans_b;         // [K, N] with N contiguous
+  o.out_fp32 = out_fp32;
+  const int64_t M = trans_a ? a3.size(2) : a3.size(1), K = trans_a ? a3.size(1) : a3.size(2);
+  const int64_t N = trans_b ? b3.size(1) : b3.size(2);
+  if (splits == 0) {
+    const int64_t tiles = ((M + 127) / 128) * ((N + 127) / 128) * std::max(a3.size(0), b3.size(0));
+    const int64_t kb = (K + BK - 1) / BK;
+    splits = 1;
+    if (tiles < sm_count() && kb >= 16) splits = std::min<int64_t>(std::max<int64_t>(1, sm_count() / tiles), kb / 4);
+  }
+  o.splits = (int)std::max<int64_t>(1, splits);
+  Tensor out = gemm_impl(a3, b3, c10::nullopt, c10::nullopt, c10::nullopt, kPlain, o);
+  if (o.out.defined()) return out;
+  return (a.dim() == 2 && b.dim() == 2) ? out.squeeze(0) : out;
 }
 
 // Backward of y = x w^T (+ b) with bf16 operands: dx = dy w (in x's dtype), dw = dy^T x and db = sum dy in fp32.
-// One call from Python instead of six small ones; the products run on the library GEMM.
+// Both products run on the tcgen05 kernel without transposing anything: dy is the K-major A operand of dx and the
+// MN-major A operand of dw; w and x are MN-major B operands. dw is a split-K launch with an order-fixed reduction.
 std::tuple<Tensor, Tensor, Tensor> df3_linear_bwd(const Tensor& dy, const Tensor& x, const Tensor& w16, bool need_dx, bool need_dw,
                                                    bool need_db) {
   const int64_t n = w16.size(0), k = w16.size(1);
   Tensor d2 = dy.reshape({-1, n});
   if (d2.scalar_type() != torch::kBFloat16) d2 = d2.to(torch::kBFloat16);
   Tensor dx, dw, db;
+  const bool own = n % 8 == 0 && k % 8 == 0 && d2.size(0) > 0;
   if (need_dx) {
-    dx = at::mm(d2, w16).view(x.sizes());
+    dx = own ? df3_matmul(d2, w16, false, false, false, 1) : at::mm(d2, w16);
+    dx = dx.view(x.sizes());
     if (dx.scalar_type() != x.scalar_type()) dx = dx.to(x.scalar_type());
   }
   if (need_dw) {
     Tensor x2 = x.reshape({-1, k});
     if (x2.scalar_type() != torch::kBFloat16) x2 = x2.to(torch::kBFloat16);
-    dw = at::mm(d2.t(), x2).to(torch::kFloat32);
+    dw = own ? df3_matmul(d2, x2, true, false, true, 0) : at::mm(d2.t(), x2).to(torch::kFloat32);
   }
   if (need_db) db = d2.sum(0, false, torch::kFloat32);
   auto undef = [&](Tensor& t) { if (!t.defined()) t = torch::empty({0}, dy.options()); };
@@ -521,9 +772,13 @@ void df3_register_gemm(torch::Library& m) {
   m.def("gemm(Tensor x, Tensor w, Tensor? bias, Tensor? row_mask, Tensor? mul, int epi, bool channel_major) -> Tensor",
         &df3::df3_gemm);
   m.def("bmm_nt(Tensor a, Tensor b) -> Tensor", &df3::df3_bmm_nt);
+  m.def("matmul(Tensor a, Tensor b, bool trans_a, bool trans_b, bool out_fp32, int splits, Tensor(a!)? out=None) -> Tensor",
+        &df3::df3_matmul);
   m.def("gemm_status() -> int", &df3::df3_gemm_status);
   m.def("linear_bwd(Tensor dy, Tensor x, Tensor w16, bool need_dx, bool need_dw, bool need_db) -> (Tensor, Tensor, Tensor)",
         &df3::df3_linear_bwd);
 }
 
-const char* df3_gemm_features() { return "gemm,gated_dual_linear,transition,pair_bias_attention,linear_planes,sigmoid_gate_mul,peer_reduce"; }
+const char* df3_gemm_features() {
+  return "gemm,matmul,gated_dual_linear,transition,pair_bias_attention,linear_planes,sigmoid_gate_mul,peer_reduce";
+}

@@ -82,9 +82,24 @@ def bench_gemm(t: Timer):
             t(lambda: ref.swiglu(x @ w1.t())), io(128, 512), 2 * rows * 128 * 1024)  # fmt: skip
     _report("gemm sigmoid-mul 147456x128->128", t(lambda: df3.gemm(x, w, None, None, o, 3, False)),
             t(lambda: torch.sigmoid(x @ w.t()) * o), io(128, 128, 128), 2 * rows * 128 * 128)  # fmt: skip
+    w3 = torch.randn(384, 128, device="cuda").bfloat16() * 0.1
+    _report("gemm plain 147456x128->384", t(lambda: df3.gemm(x, w3, None, None, None, 0, False)), t(lambda: x @ w3.t()),
+            io(128, 384), 2 * rows * 128 * 384)  # fmt: skip
+    _report("gemm gated planes 147456x128->128", t(lambda: df3.gemm(x, w2, None, None, None, 1, True)),
+            t(lambda: (torch.sigmoid(x @ w2[:128].t()) * (x @ w2[128:].t())).t().contiguous()), io(128, 128), 2 * rows * 128 * 256)  # fmt: skip
+    _report("matmul dx 147456x128 . 128x128", t(lambda: df3.matmul(o, w, False, False, False, 1)), t(lambda: o @ w),
+            io(128, 128), 2 * rows * 128 * 128)  # fmt: skip
+    _report("matmul dw (147456x128)^T . 147456x128", t(lambda: df3.matmul(o, x, True, False, True, 0)), t(lambda: (o.t() @ x).float()),
+            io(128, 128), 2 * rows * 128 * 128)  # fmt: skip
+    pa, pb = torch.randn(128, N, N, device="cuda").bfloat16(), torch.randn(128, N, N, device="cuda").bfloat16()
+    _report("triangle contraction out 128x384^3", t(lambda: df3.matmul(pa, pb, False, True, False, 1)),
+            t(lambda: torch.bmm(pa, pb.transpose(1, 2))), 3 * 2 * 128 * N * N, 2 * 128 * N**3)  # fmt: skip
+    _report("triangle contraction in 128x384^3", t(lambda: df3.matmul(pb, pa, True, False, False, 1)),
+            t(lambda: torch.bmm(pb.transpose(1, 2), pa)), 3 * 2 * 128 * N * N, 2 * 128 * N**3)  # fmt: skip
     M = 8192
     A, B = torch.randn(M, M, device="cuda").bfloat16(), torch.randn(M, M, device="cuda").bfloat16()
     _report("gemm plain 8192^3", t(lambda: df3.gemm(A, B, None, None, None, 0, False)), t(lambda: A @ B.t()), 0, 2 * M**3)
+    _report("matmul NN 8192^3", t(lambda: df3.matmul(A, B, False, False, False, 1)), t(lambda: A @ B), 0, 2 * M**3)
 
 
 def bench_attention(t: Timer):
@@ -96,6 +111,12 @@ def bench_attention(t: Timer):
         ours = t(lambda: df3.attention_fwd(q, k, v, bias, mask, D**-0.5, True))
         eager = t(lambda: ref.pair_bias_attention(q, k, v, bias, mask, D**-0.5, False))
         _report(f"attention fwd {name}", ours, eager, 2 * 4 * B * R * H * N * D, 4 * B * R * H * N * N * D)
+        out, lse = df3.attention_fwd(q, k, v, bias, mask, D**-0.5, True)
+        d_out = torch.randn_like(out)
+        fused = t(lambda: df3.attention_bwd(q, k, v, out, d_out, bias, mask, lse, D**-0.5, True, 40 << 20))
+        chunked = t(lambda: df3.attention_bwd(q, k, v, out, d_out, bias, mask, lse, D**-0.5, True, -(40 << 20)))
+        # five products of 2 N N D per (b, r, h); the chunked form (library GEMMs + one kernel per chunk) is the comparison
+        _report(f"attention bwd {name}", fused, chunked, 2 * 8 * B * R * H * N * D, 10 * B * R * H * N * N * D)
 
 
 def bench_elementwise(t: Timer):

@@ -109,4 +109,6 @@ class GradSync:
         dist.broadcast(opt.flat_param, src=0)
         if opt.shadow is not None:
             dist.broadcast(opt.shadow, src=0)
+        if getattr(opt, "z", None) is not None:  # schedule-free: the second sequence starts from the same point
+            opt.reseed_z()
         opt.refresh_bf16()

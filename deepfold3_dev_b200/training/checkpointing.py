@@ -1,7 +1,8 @@
 """``.pt`` checkpoints (model + EMA + optimizer) and weight loading.
 
 Blob layout follows the reference (training/checkpointing.py:246-536) key for
-key so checkpoints interchange: ``model`` (no ``module.`` prefix),
+key so checkpoints interchange (schedule-free runs are written under eval mode:
+``model`` = the averaged iterate, ``snapshot_kind`` "x", ``train_mode`` False): ``model`` (no ``module.`` prefix),
 ``optimizer`` (``torch.optim.AdamW`` layout), ``optimizer_param_names``,
 ``scheduler``, ``global_step``, ``effective_step``, ``epoch``,
 ``best_eval_loss``, ``rng_states`` (one per rank), ``model_cfg`` / ``train_cfg``
@@ -173,14 +174,21 @@ class CheckpointManager:
     def save(self, name: str, *, model, optimizer, scheduler, state, model_cfg, train_cfg, sampler=None,
              snapshot_kind: str = "live", scaler_state: dict | None = None, background: bool = True) -> str | None:  # fmt: skip
         """All ranks call this (the RNG gather is collective); rank 0 writes ``{dir}/{name}``."""
+        from .schedule_free import FlatAdamWScheduleFree, optimizer_eval_mode
+
         rng_states = gather_rng_states(self.info)
         if not self.info.is_main:
             return None
         if self._error is not None:
             self.wait_for_io()
+        if isinstance(optimizer, FlatAdamWScheduleFree):
+            snapshot_kind = "x"  # written under eval mode: ``model`` holds the averaged iterate, train_mode False
+        with optimizer_eval_mode(optimizer):
+            model_state = {k: v.detach().cpu().clone() for k, v in strip_module_prefix(model.state_dict()).items()}
+            optimizer_state = optimizer.state_dict()
         blob = {
-            "model": {k: v.detach().cpu().clone() for k, v in strip_module_prefix(model.state_dict()).items()},
-            "optimizer": optimizer.state_dict(),
+            "model": model_state,
+            "optimizer": optimizer_state,
             "optimizer_param_names": optimizer.param_names_by_index(),
             "scheduler": scheduler.state_dict(),
             "global_step": state.global_step,
@@ -213,6 +221,20 @@ class CheckpointManager:
             # parameters are views into the flat buffer, load_state_dict copied into them in place
             if not skip_optimizer and blob.get("optimizer"):
                 optimizer.load_state_dict(blob["optimizer"])
+            from .schedule_free import FlatAdamWScheduleFree
+
+            if isinstance(optimizer, FlatAdamWScheduleFree):
+                groups = (blob.get("optimizer") or {}).get("param_groups") or [{}]
+                if not skip_optimizer and blob.get("optimizer"):
+                    if groups[0].get("train_mode", False):
+                        raise RuntimeError(f"Schedule-Free checkpoint at {path} was saved with train_mode=True; expected False "
+                                           "(checkpoints are written under optimizer_eval_mode)")
+                    if blob["optimizer"].get("state"):
+                        optimizer.train()  # parameters were loaded as x; back to y for training
+                    else:
+                        optimizer.reseed_z()  # saved before the first step: x = y = z
+                else:
+                    optimizer.reseed_z()  # no optimizer state: both sequences start from the loaded weights
             ema = blob.get("ema")
             if optimizer.shadow is not None:
                 if ema and ema.get("shadow"):

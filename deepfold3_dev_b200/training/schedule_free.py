@@ -14,7 +14,26 @@ import math
 
 import torch
 
+import contextlib
+
 from .flat_optimizer import FlatAdamW
+
+
+@contextlib.contextmanager
+def optimizer_eval_mode(optimizer):
+    """Parameters hold the averaged iterate ``x`` inside the block (schedule-free only; a no-op for AdamW).
+
+    Checkpoints are written and evaluations run under this, as in the reference
+    (training/schedule_free.py ``optimizer_eval_mode``, training/checkpointing.py:291).
+    """
+    flip = isinstance(optimizer, FlatAdamWScheduleFree) and optimizer.train_mode
+    if flip:
+        optimizer.eval()
+    try:
+        yield
+    finally:
+        if flip:
+            optimizer.train()
 
 
 class FlatAdamWScheduleFree(FlatAdamW):
@@ -75,9 +94,18 @@ class FlatAdamWScheduleFree(FlatAdamW):
         y.add_(gn, alpha=lr * (b1 * (1.0 - c) - 1.0))
         self.z.sub_(gn, alpha=lr)
         if update_ema and self.shadow is not None:
+            # the shadow follows the averaged iterate x = (y - (1 - b1) z) / b1, as the reference's EMA callback does
+            # under optimizer_eval_mode
             self.ema_updates += 1
-            self.shadow.lerp_(self.flat_param, 1.0 - self.ema_decay)
+            x = torch.lerp(self.flat_param, self.z, 1.0 - 1.0 / b1)
+            self.shadow.lerp_(x, 1.0 - self.ema_decay)
         self.refresh_bf16()
+
+    @torch.no_grad()
+    def reseed_z(self) -> None:
+        """``z := parameters``: after a broadcast or a weight load that did not restore the optimizer state."""
+        self.z.copy_(self.flat_param)
+        self.train_mode = True
 
     # ---- checkpoint layout: torch-style per-parameter state with z
     def state_dict(self) -> dict:
@@ -104,6 +132,8 @@ class FlatAdamWScheduleFree(FlatAdamW):
         self.step_count = int(g.get("k", 0))
         self.weight_sum, self.lr_max = float(g.get("weight_sum", 0.0)), float(g.get("lr_max", -1.0))
         self.scheduled_lr = float(g.get("scheduled_lr", 0.0))
+        # the reference saves under eval mode (parameters = x, train_mode False) and switches back with train()
+        # after loading; the caller (CheckpointManager.load) does the same here
         self.train_mode = bool(g.get("train_mode", True))
         for mine, theirs in zip(self.param_groups, sd.get("param_groups", [])):
             for key in ("lr", "initial_lr", "betas", "eps", "weight_decay"):

@@ -205,7 +205,12 @@ class Trainer:
         """Mean losses over ``eval_loader`` with the EMA weights swapped in (``eval_snapshot='shadow'``)."""
         if self.eval_loader is None:
             return {}
+        from .schedule_free import FlatAdamWScheduleFree
+
         use_shadow = self.cfg.eval_snapshot == "shadow" and self.optimizer.shadow is not None
+        sf_flip = isinstance(self.optimizer, FlatAdamWScheduleFree) and self.optimizer.train_mode
+        if sf_flip:
+            self.optimizer.eval()  # schedule-free: evaluate the averaged iterate x, as the reference does
         if use_shadow:
             self.optimizer.ema_swap()
         self.model.eval()
@@ -226,6 +231,8 @@ class Trainer:
             self.model.train()
             if use_shadow:
                 self.optimizer.ema_swap()
+            if sf_flip:
+                self.optimizer.train()
         return meters.sync()
 
     # ------------------------------------------------------------------ main loop
@@ -245,7 +252,7 @@ class Trainer:
         acc = cfg.accumulate_grad_batches
         if cfg.eval_before and self.eval_loader is not None:
             self._log(self.evaluate())
-        last_ckpt_wall = time.time()
+        self._last_ckpt_wall = time.time()
         data_wait = 0.0
         it = iter(self.train_loader)
         stopped = False
@@ -272,9 +279,7 @@ class Trainer:
                 if result.advanced:
                     if result.grad_norm is not None:
                         self.meters.update({"train/grad_norm": result.grad_norm})
-                    self._after_optimizer_step(ckpt_request, last_ckpt_wall)
-                    if st.effective_step % cfg.checkpoint_interval == 0:
-                        last_ckpt_wall = time.time()
+                    self._after_optimizer_step(ckpt_request)
             self.timer.stop()
             if cfg.slow_step_log_threshold_s > 0:
                 if self.device.type == "cuda":
@@ -295,23 +300,31 @@ class Trainer:
                 data_wait = 0.0
             stopped = shutdown.tick()
         self.callbacks.fire("on_train_end", self)
+        if stopped and st.global_step % acc != 0:
+            # shutdown inside an accumulation window: drop the partial gradients and go back to the last boundary, so the
+            # resumed run starts on a full window (reference: training/trainer.py:1322-1345)
+            self.optimizer.zero_grad()
+            st.global_step -= st.global_step % acc
         self.save_checkpoint("checkpoint_final.pt" if not stopped else None, background=False)
         self.ckpt.wait_for_io()
         self.ckpt.close()
         destroy_process_group_safely(self.dist)
         return st
 
-    def _after_optimizer_step(self, ckpt_request, last_ckpt_wall) -> None:
+    def _after_optimizer_step(self, ckpt_request) -> None:
         cfg, st = self.cfg, self.state
-        want = st.effective_step % cfg.checkpoint_interval == 0 or ckpt_request.consume()
-        if cfg.checkpoint_every_hours > 0 and time.time() - last_ckpt_wall > cfg.checkpoint_every_hours * 3600:
-            want = True
+        want = st.effective_step % cfg.checkpoint_interval == 0
+        if self.dist.is_main:  # wall clock and signals are rank 0's alone; the others follow its broadcast
+            want = want or ckpt_request.consume()
+            if cfg.checkpoint_every_hours > 0 and time.time() - self._last_ckpt_wall > cfg.checkpoint_every_hours * 3600:
+                want = True
         if self.dist.is_distributed:  # rank 0 decides, every rank takes part in the RNG gather
             flag = torch.tensor([int(want)], device=self.device)
             torch.distributed.broadcast(flag, src=0)
             want = bool(flag.item())
         if want:
             self.save_checkpoint()
+            self._last_ckpt_wall = time.time()  # whatever triggered it, the hourly timer starts over
         if self.eval_loader is not None and st.effective_step % cfg.eval_interval == 0:
             self.callbacks.fire("on_eval_start", self)
             vals = self.evaluate()

@@ -58,6 +58,17 @@ def main():
             same_noise_step(tr, batch_features([example(i)]))
             total = tr.optimizer.flat_grad.clone() if total is None else total + tr.optimizer.flat_grad
         torch.save({"grad": total / 2}, os.path.join(out_dir, "single.pt"))
+    elif scenario == "schedule_free_lockstep":
+        # ranks are seeded differently (seed + rank); after the broadcast both sequences (parameters and z) must agree
+        info = init_process_group(timeout_s=120, device="cpu")
+        tr = make_trainer(info, out_dir, optimizer_type="schedule_free")
+        for step in range(2):
+            same_noise_step(tr, batch_features([example(info.rank + 2 * step)]))
+            tr.engine.step_or_skip(tr.state)
+        torch.save({"params": tr.optimizer.flat_param.clone(), "z": tr.optimizer.z.clone()},
+                   os.path.join(out_dir, f"sf_rank{info.rank}.pt"))  # fmt: skip
+        torch.distributed.barrier()
+        torch.distributed.destroy_process_group()
     elif scenario == "nan_consensus":
         info = init_process_group(timeout_s=60, device="cpu")
         tr = make_trainer(info, out_dir, max_consecutive_nan_skips=0)

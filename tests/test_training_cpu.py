@@ -131,3 +131,86 @@ def test_gloo_two_ranks_match_single_process(tmp_path):
     assert single.returncode == 0
     ref = torch.load(tmp_path / "single.pt")
     torch.testing.assert_close(a["grad"], ref["grad"], atol=2e-5, rtol=1e-3)
+
+
+@pytest.mark.slow
+def test_schedule_free_ranks_stay_in_lock_step(tmp_path):
+    script = os.path.join(ROOT, "tests", "dist_worker.py")
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT="29613", PYTHONPATH=ROOT)
+    procs = [subprocess.Popen([sys.executable, script, "schedule_free_lockstep", str(tmp_path)],
+                              env=dict(env, RANK=str(r), WORLD_SIZE="2", LOCAL_RANK=str(r))) for r in range(2)]  # fmt: skip
+    for p in procs:
+        assert p.wait(timeout=600) == 0
+    a, b = (torch.load(tmp_path / f"sf_rank{r}.pt") for r in range(2))
+    torch.testing.assert_close(a["params"], b["params"], atol=0, rtol=0)
+    torch.testing.assert_close(a["z"], b["z"], atol=0, rtol=0)
+
+
+def test_schedule_free_checkpoint_follows_reference_layout(tmp_path):
+    """Saved under eval mode: ``model`` = x, snapshot_kind "x", train_mode False; loading returns to y and can step."""
+    from deepfold3_dev_b200.training.checkpointing import CheckpointManager
+    from deepfold3_dev_b200.training.schedule_free import FlatAdamWScheduleFree
+    from deepfold3_dev_b200.training.state import TrainState
+
+    def make():
+        m = _mlp()
+        return m, FlatAdamWScheduleFree(m, lr=1e-2, warmup_steps=2)
+
+    m, opt = make()
+    x = torch.randn(5, 7)
+    for _ in range(3):
+        m(x).pow(2).sum().backward()
+        opt.step()
+        opt.zero_grad()
+    y_before, z_before = opt.flat_param.clone(), opt.z.clone()
+    b1 = opt.param_groups[0]["betas"][0]
+    x_iter = torch.lerp(y_before, z_before, 1.0 - 1.0 / b1)
+    sched = build_scheduler(opt, TrainingConfig(lr=1e-2))
+    mgr = CheckpointManager(str(tmp_path), DistInfo())
+    path = mgr.save("checkpoint_3.pt", model=m, optimizer=opt, scheduler=sched, state=TrainState(), model_cfg=None,
+                    train_cfg=None, background=False)  # fmt: skip
+    torch.testing.assert_close(opt.flat_param, y_before)  # back in train mode after the save
+    blob = torch.load(path, weights_only=False)
+    assert blob["snapshot_kind"] == "x" and blob["optimizer"]["param_groups"][0]["train_mode"] is False
+    saved = torch.cat([blob["model"][n].reshape(-1) for n, _ in m.named_parameters()])
+    live_x = torch.cat([opt._view(x_iter, i).reshape(-1) for i in range(len(opt.params))])
+    torch.testing.assert_close(saved, live_x)
+    m2, opt2 = make()
+    mgr.load(path, model=m2, optimizer=opt2, scheduler=build_scheduler(opt2, TrainingConfig(lr=1e-2)), state=TrainState())
+    assert opt2.train_mode
+    torch.testing.assert_close(opt2.flat_param, y_before, atol=1e-6, rtol=1e-5)
+    torch.testing.assert_close(opt2.z, z_before)
+    m2(x).pow(2).sum().backward()
+    opt2.step()  # does not raise
+    mgr.close()
+
+
+@pytest.mark.slow
+def test_hourly_checkpoint_timer_restarts_after_each_save(tmp_path):
+    """With the wall-clock trigger due at once, exactly one checkpoint is written per elapsed period, not one per step."""
+    from deepfold3_dev_b200.data.datasets import SyntheticDataset
+
+    mc = tiny_config()
+    tc = TrainingConfig(diffusion_batch_size=2, dtype="fp32", mini_rollout_steps=1, max_recycles=0, warmup_steps=0,
+                        output_dir=str(tmp_path), seed=3, max_steps=3, checkpoint_interval=1000, checkpoint_every_hours=1.0,
+                        log_interval=100, alpha_confidence=0.0)  # fmt: skip
+    batch = batch_features([synthetic_complex([("protein", 10)], num_msa=4, num_templates=0, seed=1)])
+    tr = Trainer(tc, mc, dist_info=DistInfo(), train_loader=[batch, batch, batch, batch])
+    saved = []
+    real = tr.save_checkpoint
+    tr.save_checkpoint = lambda name=None, background=True: (saved.append(name), real(name, background))[1]
+    import time as _time
+
+    tr_run_time = _time.time
+    # first optimizer step sees a timer that ran out long ago; later ones see a fresh timer
+    orig_after = tr._after_optimizer_step
+
+    def after(req):
+        if tr.state.effective_step == 1:
+            tr._last_ckpt_wall = tr_run_time() - 7200
+        return orig_after(req)
+
+    tr._after_optimizer_step = after
+    tr.run()
+    periodic = [n for n in saved if n is None]
+    assert len(periodic) == 1, saved
