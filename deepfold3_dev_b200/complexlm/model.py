@@ -103,21 +103,25 @@ class PackedBatch:
 
 
 class RMSNorm(nn.Module):
+    """Root-mean-square normalisation with a learned gain, evaluated in fp32 whatever the activation dtype."""
+
     def __init__(self, dim: int, eps: float = 1e-5):
         super().__init__()
-        self.weight = nn.Parameter(torch.ones(dim))
         self.eps = eps
+        self.weight = nn.Parameter(torch.ones(dim))
 
     def forward(self, x):
-        y = x.float()
-        y = y * torch.rsqrt(y.pow(2).mean(-1, keepdim=True) + self.eps)
-        return (y * self.weight.float()).to(x.dtype)
+        return F.rms_norm(x.float(), self.weight.shape, self.weight.float(), self.eps).to(x.dtype)
 
 
 def build_norm(cfg: ComplexLMConfig, dim: int, bias: bool | None = None) -> nn.Module:
-    if cfg.norm == "rmsnorm":
-        return RMSNorm(dim, cfg.norm_eps)
-    return nn.LayerNorm(dim, eps=cfg.norm_eps, bias=cfg.bias if bias is None else bias)
+    """The normalisation layer the configuration names; ``bias`` overrides the configured bias switch of a LayerNorm
+    (the ESM-C compatible layout wants some norms with and some without)."""
+    makers = {
+        "rmsnorm": lambda: RMSNorm(dim, cfg.norm_eps),
+        "layernorm": lambda: nn.LayerNorm(dim, eps=cfg.norm_eps, bias=cfg.bias if bias is None else bias),
+    }
+    return makers.get(cfg.norm, makers["layernorm"])()
 
 
 def rope(x: torch.Tensor, positions: torch.Tensor, theta: float) -> torch.Tensor:
@@ -182,20 +186,23 @@ class Attention(nn.Module):
 
 
 def swiglu_hidden(d_model: int, expansion_ratio: float) -> int:
-    return int((expansion_ratio * d_model + 255) // 256 * 256)
+    """Hidden width of the gated feed-forward: ``expansion_ratio * d_model`` rounded up to a multiple of 256."""
+    return 256 * math.ceil(expansion_ratio * d_model / 256)
 
 
 class SwiGLUFFN(nn.Module):
+    """Pre-norm gated feed-forward: ``w_out(silu(g) * u)`` with ``[g, u] = w_in(norm(x))``."""
+
     def __init__(self, cfg: ComplexLMConfig):
         super().__init__()
-        hidden = swiglu_hidden(cfg.d_model, cfg.expansion_ratio)
+        self.hidden = swiglu_hidden(cfg.d_model, cfg.expansion_ratio)
         self.norm = build_norm(cfg, cfg.d_model, bias=True if cfg.esmc_compat else None)
-        self.w_in = nn.Linear(cfg.d_model, 2 * hidden, bias=cfg.bias)
-        self.w_out = nn.Linear(hidden, cfg.d_model, bias=cfg.bias)
+        self.w_in = nn.Linear(cfg.d_model, 2 * self.hidden, bias=cfg.bias)
+        self.w_out = nn.Linear(self.hidden, cfg.d_model, bias=cfg.bias)
 
     def forward(self, x):
-        gate, up = self.w_in(self.norm(x)).chunk(2, dim=-1)
-        return self.w_out(F.silu(gate) * up)
+        h = self.w_in(self.norm(x))
+        return self.w_out(F.silu(h[..., : self.hidden]) * h[..., self.hidden :])
 
 
 class Block(nn.Module):
@@ -213,14 +220,18 @@ class Block(nn.Module):
 
 
 class MLMHead(nn.Module):
+    """Masked-token read-out: dense + GELU + norm, then the vocabulary projection."""
+
     def __init__(self, cfg: ComplexLMConfig):
         super().__init__()
-        self.dense = nn.Linear(cfg.d_model, cfg.d_model, bias=cfg.bias or cfg.esmc_compat)
-        self.norm = build_norm(cfg, cfg.d_model, bias=True if cfg.esmc_compat else None)
-        self.out = nn.Linear(cfg.d_model, cfg.vocab_size, bias=True)
+        width = cfg.d_model
+        self.dense = nn.Linear(width, width, bias=cfg.bias or cfg.esmc_compat)
+        self.norm = build_norm(cfg, width, bias=True if cfg.esmc_compat else None)
+        self.out = nn.Linear(width, cfg.vocab_size, bias=True)
 
     def forward(self, x):
-        return self.out(self.norm(F.gelu(self.dense(x))))
+        hidden = self.norm(F.gelu(self.dense(x)))
+        return self.out(hidden)
 
 
 @dataclass
@@ -286,17 +297,23 @@ class ComplexLM(nn.Module):
         return ComplexLMOutput(self.head(x) * self.readout_mult, hidden, attns or None)
 
     def param_groups(self, weight_decay: float) -> list[dict]:
-        """Groups with ``lr_scale`` (1/width multiple for hidden matrices under muP) and a decay that keeps lr x decay
-        width-invariant; gains, biases and the embedding table do not decay."""
-        buckets: dict[tuple[str, bool], list] = {}
-        for name, p in self.named_parameters():
-            if p.requires_grad:
-                role = mup_role(name, p)
-                buckets.setdefault((role, p.dim() >= 2 and role != "embedding"), []).append(p)
-        wm = self.cfg.width_mult
-        return [{"params": ps, "role": role, "lr_scale": 1.0 / wm if role == "hidden" else 1.0,
-                 "weight_decay": (weight_decay * (wm if role == "hidden" else 1.0)) if decays else 0.0}
-                for (role, decays), ps in buckets.items()]  # fmt: skip
+        """Optimizer groups by muP role. Hidden matrices step with ``lr / width_mult`` and decay with
+        ``weight_decay * width_mult`` (so lr x decay does not depend on the width); matrices of the other roles decay
+        plainly; vectors (gains, biases) and the embedding table do not decay."""
+        mult = float(self.cfg.width_mult)
+        groups: dict[tuple[str, bool], dict] = {}
+        for name, param in self.named_parameters():
+            if not param.requires_grad:
+                continue
+            role = mup_role(name, param)
+            decays = role in ("hidden", "readout")
+            group = groups.get((role, decays))
+            if group is None:
+                scale = 1.0 / mult if role == "hidden" else 1.0
+                decay = 0.0 if not decays else weight_decay * (mult if role == "hidden" else 1.0)
+                group = groups[(role, decays)] = {"params": [], "role": role, "lr_scale": scale, "weight_decay": decay}
+            group["params"].append(param)
+        return list(groups.values())
 
     @torch.no_grad()
     def warm_start_from_esm2(self, embedding: torch.Tensor) -> None:

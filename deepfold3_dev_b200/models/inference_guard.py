@@ -1,39 +1,44 @@
-"""Refusals by name: an op that cannot serve a call says so instead of falling back silently.
+"""Kernels that say no.
 
-Same contract as the reference (model/inference_guard.py:48-75): an
-inference-only entry point raises as soon as autograd could record through it.
+Two ways an op can decline a call, both loud: ``NotActive`` ("this kernel does not take this call", with the name of
+the switch and the reason, so that the kernel census can report why a requested path did not run), and the
+``inference_only`` decorator for entry points that have no backward (they must never be reached while autograd is
+recording; reference: model/inference_guard.py:48-75).
 """
 
 from __future__ import annotations
 
-import functools
+from functools import wraps
 
 import torch
 
 
 class InferenceOnlyKernelError(RuntimeError):
-    """An inference-only kernel was reached with grad enabled."""
+    """Autograd was recording when an entry point without a backward was called."""
 
 
 class NotActive(Exception):
-    """A kernel cannot serve this call; ``lever`` names it and ``reason`` says why."""
+    """``lever`` (the configuration switch of a kernel) cannot serve the call, for ``reason``."""
 
     def __init__(self, lever: str, reason: str):
-        self.lever, self.reason = lever, reason
         super().__init__(f"NOT ACTIVE: {lever}: {reason}")
+        self.lever = lever
+        self.reason = reason
 
 
 def inference_only(lever: str):
-    def decorate(fn):
-        @functools.wraps(fn)
-        def wrapper(*args, **kwargs):
+    """Decorator: the wrapped function raises ``InferenceOnlyKernelError`` when called with grad mode on."""
+
+    def wrap(fn):
+        message = (f"{lever} has no backward pass; it may only run under torch.no_grad() or torch.inference_mode() "
+                   "(grad mode was on)")  # fmt: skip
+
+        @wraps(fn)
+        def guarded(*args, **kwargs):
             if torch.is_grad_enabled():
-                raise InferenceOnlyKernelError(
-                    f"{lever} is inference-only and has no backward: call it under torch.no_grad() "
-                    "or torch.inference_mode()."
-                )
+                raise InferenceOnlyKernelError(message)
             return fn(*args, **kwargs)
 
-        return wrapper
+        return guarded
 
-    return decorate
+    return wrap

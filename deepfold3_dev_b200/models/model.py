@@ -18,7 +18,7 @@ import torch.nn.functional as F
 from torch.utils.checkpoint import checkpoint
 
 from ..config.schema import DistogramConfig, ModelConfig, OptimConfig
-from ..utils.cuda_graph import GraphCache
+from ..utils.cuda_graph import GraphCache, TrainGraphCache
 from .atom_attention import EvoformerConditioningEncoder
 from .confidence import ConfidenceHead
 from .diffusion import DiffusionHead, GuidanceTerm
@@ -203,6 +203,16 @@ class DeepFold3(nn.Module):
         meter = getattr(self.evoformer, "_act_meter", None)
         return not (meter is not None and getattr(meter, "enabled", False))
 
+    def _graph_trunk_training(self, dev) -> bool:
+        """Graph the gradient-carrying trunk pass: a CUDA device, bf16 kernels (autocast), every activation kept (no
+        checkpointing, whose recomputation re-enters Python), no activation meter, and not switched off."""
+        if dev.type != "cuda" or not torch.is_grad_enabled() or os.environ.get("DF3_GRAPH_TRAIN", "1") == "0":
+            return False
+        if self.cfg.optim.use_gradient_checkpointing or not torch.is_autocast_enabled("cuda"):
+            return False
+        meter = getattr(self.evoformer, "_act_meter", None)
+        return not (meter is not None and getattr(meter, "enabled", False))
+
     def run_evoformer(self, features, num_recycles, seed=0, msa_precropped=False, crop_offset=0, mask_msa=False):
         """Feature building + ``num_recycles + 1`` trunk passes.
 
@@ -286,6 +296,10 @@ class DeepFold3(nn.Module):
                 # no autograd on this pass: replay the whole trunk from a CUDA graph (captured once per shape)
                 graphs = self.__dict__.setdefault("_trunk_graphs", GraphCache(max_graphs=4))
                 embeddings = graphs.run(self.evoformer, trunk_in, mode=self.evoformer.training)
+            elif self._graph_trunk_training(dev):
+                # the pass that carries gradients: forward and backward each replay one captured graph
+                graphs = self.__dict__.setdefault("_trunk_train_graphs", TrainGraphCache(max_graphs=1))
+                embeddings = graphs.run(self.evoformer, trunk_in, self.evoformer.parameters(), mode=self.evoformer.training)
             else:
                 embeddings = self.evoformer(**trunk_in)
             if r < num_recycles:

@@ -20,6 +20,42 @@ from .primitives import LayerNorm, LinearNoBias
 _HEAD_NORMS = ("channel", "head_rms", "head_ln", "post_channel")
 
 
+class _RouterWindow:
+    """Running means of router read-outs between two log lines (host floats; one update per routed forward).
+
+    Read-outs of a gain tensor ``g [..., H]``: entropy of the per-position head distribution and of its average over
+    positions (both divided by log H, so 1 = uniform), RMS / spread / mean of the gains, and the largest and smallest
+    average share of any head.
+    """
+
+    def __init__(self, num_heads: int):
+        self.h = max(int(num_heads), 1)
+        self.count, self.totals = 0, {}
+
+    @torch.no_grad()
+    def add(self, gains: torch.Tensor) -> None:
+        g = gains.reshape(-1, self.h)
+        dist = g / g.sum(dim=-1, keepdim=True).clamp_min(1e-9)
+        avg = dist.mean(dim=0)
+        norm = math.log(self.h) if self.h > 1 else 1.0
+        ent = lambda p: -(p * (p + 1e-9).log()).sum(dim=-1)  # noqa: E731
+        sample = {
+            "entropy": ent(dist).mean() / norm, "marginal_entropy": ent(avg) / norm, "g_rms": g.square().mean(dim=-1).sqrt().mean(),
+            "g_std": g.std(dim=0).mean(), "g_mean": g.mean(), "occupancy_max": avg.max(), "occupancy_min": avg.min(),
+        }  # fmt: skip
+        for key, value in sample.items():
+            self.totals[key] = self.totals.get(key, 0.0) + float(value)
+        self.count += 1
+
+    def means(self, reset: bool = True):
+        if self.count == 0:
+            return None
+        out = {key: total / self.count for key, total in self.totals.items()}
+        if reset:
+            self.count, self.totals = 0, {}
+        return out
+
+
 class _TriangleMulBase(nn.Module):
     outgoing: bool = True
 
@@ -51,66 +87,45 @@ class _TriangleMulBase(nn.Module):
         self.is_mhr = head_norm != "channel" or self.use_router
         self.router = LinearNoBias(c_z, num_heads, initializer="zeros") if self.use_router else None
         self.router_stats_enabled = False
-        self._router_stats = None
+        self._router_window = _RouterWindow(self.num_heads)
 
-    # ---- multi-head routing between contraction and out_proj (reference: ops.py:475-549) ----
-    def _route(self, t, router_logits):
-        if router_logits is None:
-            return t
-        r = router_logits.float()
-        h = self.num_heads
-        g = float(h) * torch.softmax(r, dim=-1) if self.router_kind == "softmax" else 2.0 * torch.sigmoid(r)
+    # ---- multi-head variants: the contraction result is cut into heads between the contraction and out_proj.
+    # Each head may get its own normalisation (instead of one LayerNorm over all channels) and, with a router, a
+    # per-position gain predicted from the input (behaviour of the reference's model/ops.py:475-549).
+    def _head_gains(self, router_logits):
+        """``[..., H]`` gains with mean 1 at initialisation (zero router weights): H * softmax, or 2 * sigmoid."""
+        logits = router_logits.float()
+        if self.router_kind == "softmax":
+            gains = torch.softmax(logits, dim=-1) * float(self.num_heads)
+        else:
+            gains = torch.sigmoid(logits) * 2.0
         if self.router_stats_enabled:
-            self._record_router_stats(g)
-        return t * g.to(t.dtype).unsqueeze(-1)
+            self._router_window.add(gains)
+        return gains
+
+    def _per_head_norm(self, heads):
+        """``heads [..., H, d]`` normalised inside each head in fp32, with norm_center's weight (and bias) cut per head."""
+        nc, shape = self.norm_center, (self.num_heads, self.head_dim)
+        x = heads.float()
+        if self.head_norm == "head_ln":
+            x = x - x.mean(dim=-1, keepdim=True)
+        x = x * torch.rsqrt(x.square().mean(dim=-1, keepdim=True) + nc.eps)
+        x = x.to(heads.dtype) * nc.weight.view(shape)
+        return x + nc.bias.view(shape) if self.head_norm == "head_ln" else x
 
     def _head_mix(self, act, router_logits):
-        h, d = self.num_heads, self.head_dim
-        if self.head_norm == "post_channel":
-            return self.norm_center(self._route(act.unflatten(-1, (h, d)), router_logits).flatten(-2))
-        if self.head_norm == "channel":
-            t = self.norm_center(act).unflatten(-1, (h, d))
-        else:
-            t32 = act.unflatten(-1, (h, d)).float()
-            w = self.norm_center.weight.view(h, d)
-            eps = self.norm_center.eps
-            if self.head_norm == "head_rms":
-                t = (t32 * torch.rsqrt(t32.pow(2).mean(-1, keepdim=True) + eps)).to(act.dtype) * w
-            else:
-                mu = t32.mean(-1, keepdim=True)
-                t32 = (t32 - mu) * torch.rsqrt(t32.var(-1, keepdim=True, unbiased=False) + eps)
-                t = t32.to(act.dtype) * w + self.norm_center.bias.view(h, d)
-        return self._route(t, router_logits).flatten(-2)
-
-    @torch.no_grad()
-    def _record_router_stats(self, g):
-        H = self.num_heads
-        g = g.reshape(-1, H)
-        p = g / g.sum(-1, keepdim=True).clamp_min(1e-9)
-        share = p.mean(0)
-        vals = dict(
-            entropy=float(-(p * (p + 1e-9).log()).sum(-1).mean() / math.log(H)),
-            marginal_entropy=float(-(share * (share + 1e-9).log()).sum() / math.log(H)),
-            g_rms=float(g.pow(2).mean(-1).sqrt().mean()),
-            g_std=float(g.std(0).mean()),
-            g_mean=float(g.mean()),
-            occupancy_max=float(share.max()),
-            occupancy_min=float(share.min()),
-            n=1.0,
-        )
-        if self._router_stats is None:
-            self._router_stats = {k: 0.0 for k in vals}
-        for k, v in vals.items():
-            self._router_stats[k] += v
+        split = (self.num_heads, self.head_dim)
+        gains = None if router_logits is None else self._head_gains(router_logits).to(act.dtype).unsqueeze(-1)
+        if self.head_norm == "post_channel":  # route first, one LayerNorm over all channels afterwards
+            routed = act.unflatten(-1, split) * gains
+            return self.norm_center(routed.flatten(-2))
+        heads = self.norm_center(act).unflatten(-1, split) if self.head_norm == "channel" else self._per_head_norm(act.unflatten(-1, split))
+        if gains is not None:
+            heads = heads * gains
+        return heads.flatten(-2)
 
     def _flush_router_stats(self, reset=True):
-        acc = self._router_stats
-        if acc is None or acc["n"] == 0:
-            return None
-        out = {k: v / acc["n"] for k, v in acc.items() if k != "n"}
-        if reset:
-            self._router_stats = None
-        return out
+        return self._router_window.means(reset)
 
     def forward(self, z: torch.Tensor, mask: torch.Tensor) -> torch.Tensor:
         squeeze = z.dim() == 3
@@ -139,40 +154,38 @@ class TriangleMulIncoming(_TriangleMulBase):
     outgoing = False
 
 
+def _routed_modules(model: nn.Module):
+    return [(name, m) for name, m in model.named_modules() if isinstance(m, _TriangleMulBase) and m.use_router]
+
+
 def set_router_stats_enabled(model: nn.Module, enabled: bool) -> None:
-    for mod in model.modules():
-        if isinstance(mod, _TriangleMulBase) and mod.use_router:
-            mod.router_stats_enabled = bool(enabled)
+    """Switch the router read-outs of every routed triangle multiply on or off (they cost a few host reads per forward)."""
+    for _, module in _routed_modules(model):
+        module.router_stats_enabled = bool(enabled)
+
+
+# (log key, read-out, how to combine the per-module window means)
+_ROUTER_SUMMARY = (
+    ("entropy", "entropy", "mean"), ("entropy_min", "entropy", "min"), ("marginal_entropy", "marginal_entropy", "mean"),
+    ("g_std", "g_std", "mean"), ("g_std_max", "g_std", "max"), ("g_mean", "g_mean", "mean"), ("g_rms", "g_rms", "mean"),
+    ("g_rms_max", "g_rms", "max"), ("occupancy_max", "occupancy_max", "max"), ("occupancy_min", "occupancy_min", "min"),
+)  # fmt: skip
+_COMBINE = {"mean": lambda xs: sum(xs) / len(xs), "min": min, "max": max}
 
 
 def collect_router_stats(model: nn.Module, prefix: str = "router", reset: bool = True) -> dict[str, float]:
-    """Window means of the router read-outs over all routed triangle multiplies (reference: ops.py:117-168)."""
-    rows = []
-    for name, mod in model.named_modules():
-        if isinstance(mod, _TriangleMulBase) and mod.use_router:
-            r = mod._flush_router_stats(reset)
-            if r is not None:
-                rows.append((name, r))
-    if not rows:
+    """Log entries for the routed triangle multiplies: their window means combined over modules (mean, and worst case
+    where that is the interesting one), the gap between marginal and per-position entropy (how much heads specialise by
+    position), and four read-outs per module (reference: model/ops.py:110-170)."""
+    per_module = {name: m._flush_router_stats(reset) for name, m in _routed_modules(model)}
+    per_module = {name: r for name, r in per_module.items() if r is not None}
+    if not per_module:
         return {}
-    n = len(rows)
-    mean = lambda k: sum(r[k] for _, r in rows) / n  # noqa: E731
-    out = {
-        f"{prefix}/entropy": mean("entropy"),
-        f"{prefix}/entropy_min": min(r["entropy"] for _, r in rows),
-        f"{prefix}/marginal_entropy": mean("marginal_entropy"),
-        f"{prefix}/specialization_gap": sum(r["marginal_entropy"] - r["entropy"] for _, r in rows) / n,
-        f"{prefix}/g_std": mean("g_std"),
-        f"{prefix}/g_std_max": max(r["g_std"] for _, r in rows),
-        f"{prefix}/g_mean": mean("g_mean"),
-        f"{prefix}/occupancy_max": max(r["occupancy_max"] for _, r in rows),
-        f"{prefix}/occupancy_min": min(r["occupancy_min"] for _, r in rows),
-        f"{prefix}/g_rms": mean("g_rms"),
-        f"{prefix}/g_rms_max": max(r["g_rms"] for _, r in rows),
-    }
-    for name, r in rows:
-        for k in ("entropy", "marginal_entropy", "g_rms", "g_std"):
-            out[f"{prefix}/{k}_by_module/{name}"] = r[k]
+    rows = list(per_module.values())
+    out = {f"{prefix}/{key}": _COMBINE[how]([r[field] for r in rows]) for key, field, how in _ROUTER_SUMMARY}
+    out[f"{prefix}/specialization_gap"] = _COMBINE["mean"]([r["marginal_entropy"] - r["entropy"] for r in rows])
+    for name, r in per_module.items():
+        out.update({f"{prefix}/{field}_by_module/{name}": r[field] for field in ("entropy", "marginal_entropy", "g_rms", "g_std")})
     return out
 
 

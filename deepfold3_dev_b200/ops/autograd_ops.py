@@ -153,6 +153,26 @@ class _DropoutAdd(torch.autograd.Function):
         return dyc, K.dropout_shared(None, dyc, A, B, C, share_rows, p, seed, None), None, None, None
 
 
+class _DropoutAddDeviceSeed(torch.autograd.Function):
+    """Dropout-add whose mask derives from a device-resident base seed plus a fixed offset: the form a CUDA-graph
+    capture can hold. Backward regenerates the mask from the same seed tensor, which the owner of the graph changes
+    only before a forward replay."""
+
+    @staticmethod
+    def forward(ctx, residual, x, p, share_rows, offset, seed_dev):
+        xc = x.contiguous()
+        A, B, C = xc.shape[-3], xc.shape[-2], xc.shape[-1]
+        ctx.meta = (A, B, C, share_rows, p, offset)
+        ctx.seed_dev = seed_dev
+        return K.dropout_shared(residual.contiguous(), xc, A, B, C, share_rows, p, offset, seed_dev)
+
+    @staticmethod
+    def backward(ctx, dy):
+        A, B, C, share_rows, p, offset = ctx.meta
+        dyc = dy.contiguous()
+        return dyc, K.dropout_shared(None, dyc, A, B, C, share_rows, p, offset, ctx.seed_dev), None, None, None, None
+
+
 def dropout_add(residual, x, p: float, share_dim: int, seed: int | None = None):
     """``residual + dropout(x)`` with the draw shared along ``share_dim`` (-3 rows, -2 columns)."""
     if share_dim not in (-3, -2):
@@ -165,6 +185,8 @@ def dropout_add(residual, x, p: float, share_dim: int, seed: int | None = None):
         xc = x.contiguous()
         return K.dropout_shared(residual.contiguous(), xc, xc.shape[-3], xc.shape[-2], xc.shape[-1], share_dim == -3, float(p),
                                 gs.offset(), gs.tensor)  # fmt: skip
+    if gs is not None and seed is None:
+        return _DropoutAddDeviceSeed.apply(residual, x, float(p), share_dim == -3, gs.offset(), gs.tensor)
     if seed is None:
         seed = next_mask_seed()
     return _DropoutAdd.apply(residual, x, float(p), share_dim == -3, int(seed))
@@ -546,9 +568,12 @@ def attention_supported(q, k, v, bias) -> bool:
 class _Attention(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, bias, key_mask, scale):
-        need = any(ctx.needs_input_grad[:4])
-        out, lse = K.attention_fwd(q, k, v, bias, key_mask, scale, need)
-        ctx.save_for_backward(q, k, v, bias, key_mask, out, lse)
+        if any(ctx.needs_input_grad[:4]):
+            out, lse, out32 = K.attention_fwd_train(q, k, v, bias, key_mask, scale)  # out32: unrounded O for the row sums
+        else:
+            out, lse = K.attention_fwd(q, k, v, bias, key_mask, scale, False)
+            out32 = out
+        ctx.save_for_backward(q, k, v, bias, key_mask, out32, lse)
         ctx.scale = scale
         return out
 
@@ -581,9 +606,12 @@ class _GridAttentionPacked(torch.autograd.Function):
     @staticmethod
     def forward(ctx, qkv, bias, key_mask, scale, transpose):
         q, k, v = (_grid_heads(qkv[:, :, :, i], transpose) for i in range(3))
-        need = ctx.needs_input_grad[0] or ctx.needs_input_grad[1]
-        out, lse = K.attention_fwd(q, k, v, bias, key_mask, scale, need)
-        ctx.save_for_backward(qkv, bias, key_mask, out, lse)
+        if ctx.needs_input_grad[0] or ctx.needs_input_grad[1]:
+            out, lse, out32 = K.attention_fwd_train(q, k, v, bias, key_mask, scale)
+        else:
+            out, lse = K.attention_fwd(q, k, v, bias, key_mask, scale, False)
+            out32 = out
+        ctx.save_for_backward(qkv, bias, key_mask, out32, lse)
         ctx.scale, ctx.transpose = scale, transpose
         return out
 

@@ -112,13 +112,17 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attention_bwd_kernel(const __g
   uint64_t* q_empty = bars + 6;     // [2]
   uint64_t* sdp_ready = bars + 8;   // [2]
   uint64_t* sdp_free = bars + 10;   // [2]
+  // [2], by step parity. One barrier would not do: a softmax thread that is a whole half-step ahead of a slow one would
+  // arrive a second time into the phase the slow thread has not reached yet, and the MMA warp would read an incomplete tile.
+  // With two, the fast thread's next arrival goes to the other barrier, and it cannot reach the step after that before
+  // the MMA warp has seen this one complete (that step's S and dP are only issued afterwards).
   uint64_t* pds_ready = bars + 12;
-  uint64_t* pds_free = bars + 13;
-  uint64_t* kv_acc_ready = bars + 14;
-  uint64_t* kv_acc_free = bars + 15;
-  uint64_t* dq_ready = bars + 16;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 17);
-  float* key_add = reinterpret_cast<float*>(bars + 18);  // [T * 128]: additive key term in base 2, -inf beyond N
+  uint64_t* pds_free = bars + 14;
+  uint64_t* kv_acc_ready = bars + 15;
+  uint64_t* kv_acc_free = bars + 16;
+  uint64_t* dq_ready = bars + 17;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 18);
+  float* key_add = reinterpret_cast<float*>(bars + 20);  // [T * 128]: additive key term in base 2, -inf beyond N
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   int idx = blockIdx.x;
@@ -141,7 +145,8 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attention_bwd_kernel(const __g
       ptx::mbar_init(&sdp_ready[s], 1);
       ptx::mbar_init(&sdp_free[s], kSoftmaxThreads);
     }
-    ptx::mbar_init(pds_ready, kSoftmaxThreads);
+    ptx::mbar_init(&pds_ready[0], kSoftmaxThreads);
+    ptx::mbar_init(&pds_ready[1], kSoftmaxThreads);
     ptx::mbar_init(pds_free, 1);
     ptx::mbar_init(kv_acc_ready, 1);
     ptx::mbar_init(kv_acc_free, kSoftmaxThreads);
@@ -232,7 +237,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attention_bwd_kernel(const __g
         if (s + 1 < steps && !issue_sdp(s + 1)) { ok = false; break; }
         const int hh = s & 1, pair = s >> 1, j = pair / T, i = pair - j * T;
         const int kvs = j & 1, qs = pair & 1;
-        if (!ptx::mbar_wait(pds_ready, (uint32_t)s & 1u, p.status, kTimeoutMmaDone)) { ok = false; break; }
+        if (!ptx::mbar_wait(&pds_ready[hh], (uint32_t)(s >> 1) & 1u, p.status, kTimeoutMmaDone)) { ok = false; break; }
         ptx::tc_fence_after();
         // dQ_i += dS[:, 64 hh ..] K[64 hh .., :]
         {
@@ -378,7 +383,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attention_bwd_kernel(const __g
         }
       }
       ptx::fence_proxy_async();   // P and dS written through the generic proxy, read by the tensor core
-      ptx::mbar_arrive(pds_ready);
+      ptx::mbar_arrive(&pds_ready[hh]);
       if (hh == 1 && i == T - 1) {
         // dK_j and dV_j are complete: this thread's key row, 8-column chunks sub, sub + 4, ...
         if (!ptx::mbar_wait(kv_acc_ready, (uint32_t)j & 1u, p.status, kTimeoutMmaDone)) { ok = false; break; }
@@ -470,6 +475,23 @@ __global__ void __launch_bounds__(256) attention_dbias_reduce_kernel(const __hal
     if (e + k < hn) dst[k] = acc[k];
 }
 
+// fp32 O (contiguous [B, R, H, N, D]) against strided bf16 dO
+__global__ void attention_delta_kernel_f32(const float* __restrict__ o, const __nv_bfloat16* __restrict__ d_o, float* __restrict__ delta,
+                                           long long g_sb, long long g_sr, long long g_sh, long long g_sn, int R, int H, int N, int D,
+                                           long long total) {
+  const long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= total) return;
+  const int n = (int)(e % N);
+  const int h = (int)((e / N) % H);
+  const int r = (int)((e / ((long long)N * H)) % R);
+  const long long b = e / ((long long)N * H * R);
+  const float* po = o + e * D;
+  const __nv_bfloat16* pg = d_o + b * g_sb + r * g_sr + h * g_sh + (long long)n * g_sn;
+  float acc = 0.f;
+  for (int d = 0; d < D; ++d) acc += po[d] * __bfloat162float(pg[d]);
+  delta[e] = acc;
+}
+
 __global__ void attention_delta_kernel2(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o, float* __restrict__ delta,
                                         long long o_sb, long long o_sr, long long o_sh, long long o_sn, long long g_sb, long long g_sr,
                                         long long g_sh, long long g_sn, int R, int H, int N, int D, long long total) {
@@ -529,7 +551,14 @@ std::tuple<Tensor, Tensor, Tensor, Tensor> attention_bwd_fused(const Tensor& q_i
   if (!strides_ok(d_o)) d_o = d_o.contiguous();
   cudaStream_t stream = at::cuda::getCurrentCUDAStream();
   Tensor delta = torch::empty({B, R, H, N}, bf.dtype(torch::kFloat32));
-  if (out.scalar_type() == torch::kBFloat16 && out.stride(4) == 1) {
+  if (out.scalar_type() == torch::kFloat32 && out.is_contiguous()) {
+    const long long total = delta.numel();
+    if (total > 0)
+      attention_delta_kernel_f32<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(
+          out.data_ptr<float>(), reinterpret_cast<const __nv_bfloat16*>(d_o.data_ptr()), delta.data_ptr<float>(), d_o.stride(0),
+          d_o.stride(1), d_o.stride(2), d_o.stride(3), (int)R, (int)H, (int)N, (int)D, total);
+    C10_CUDA_KERNEL_LAUNCH_CHECK();
+  } else if (out.scalar_type() == torch::kBFloat16 && out.stride(4) == 1) {
     const long long total = delta.numel();
     attention_delta_kernel2<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(
         reinterpret_cast<const __nv_bfloat16*>(out.data_ptr()), reinterpret_cast<const __nv_bfloat16*>(d_o.data_ptr()),
@@ -603,7 +632,7 @@ std::tuple<Tensor, Tensor, Tensor, Tensor> attention_bwd_fused(const Tensor& q_i
     const CUtensorMap tq = qkv_map(q), tk = qkv_map(k), tv = qkv_map(v), tdo = qkv_map(d_o);
     const long long ctas = (long long)B * R * H;
     TORCH_CHECK(ctas < (1ll << 31), "attention_bwd_fused: grid too large");
-    const size_t smem = 12 * kTileBytes + 18 * 8 + (size_t)p.T * kTile * 4 + 16;
+    const size_t smem = 12 * kTileBytes + 20 * 8 + (size_t)p.T * kTile * 4 + 16;
     const int dn = (int)((D + 15) / 16 * 16);
 #define DF3_ATTN_BWD(DN_)                                                                                              \
   do {                                                                                                                 \

@@ -61,6 +61,7 @@ constexpr float kLog2e = 1.4426950408889634f;
 
 struct AttnParams {
   __nv_bfloat16* out;
+  float* out32;            // [B, R, H, N, D] contiguous fp32 copy of the output for the backward's row sums, or null
   float* lse;              // [2, B, R, H, N] or null: row maximum and log2 of the row sum, both in base 2
   const void* bias;        // [B, H, N, N] or null
   const float* mask;       // [B, R, N] or null (1 keep, 0 drop)
@@ -410,6 +411,12 @@ __global__ void __launch_bounds__(kThreads, 2) attention_fwd_kernel(const __grid
         for (int d = 0; d < DH; ++d)
           if (d0 + d < p.D) dst[d] = __float2bfloat16_rn(o_acc[d] * inv);
       }
+      if (p.out32) {  // unrounded copy: delta = rowsum(dO o O) of the backward must not see the bf16 rounding of O
+        float* d32 = p.out32 + ((((long long)b * p.R + r) * p.H + h) * p.N + i) * p.D + d0;
+#pragma unroll
+        for (int d = 0; d < DH; ++d)
+          if (d0 + d < p.D) d32[d] = o_acc[d] * inv;
+      }
       if (p.lse && half == 0) {
         // kept apart: for a fully masked row the maximum is about -1.4e9, where adding log2(sum) would round away
         const long long at = (((long long)b * p.R + r) * p.H + h) * p.N + i;
@@ -625,9 +632,9 @@ std::tuple<Tensor, Tensor, Tensor, Tensor> df3_attention_bwd(const Tensor& q, co
   return {dq, dk, dv, dbias};
 }
 
-std::tuple<Tensor, Tensor> df3_attention_fwd(const Tensor& q_in, const Tensor& k_in, const Tensor& v_in,
-                                             const c10::optional<Tensor>& bias_in, const c10::optional<Tensor>& mask_in,
-                                             double scale, bool want_lse) {
+std::tuple<Tensor, Tensor, Tensor> attention_fwd_impl(const Tensor& q_in, const Tensor& k_in, const Tensor& v_in,
+                                                      const c10::optional<Tensor>& bias_in, const c10::optional<Tensor>& mask_in,
+                                                      double scale, bool want_lse, bool want_out32) {
   TORCH_CHECK(q_in.dim() == 5 && k_in.sizes() == q_in.sizes() && v_in.sizes() == q_in.sizes(), "attention: [B, R, H, N, D] q, k, v");
   TORCH_CHECK(q_in.is_cuda() && q_in.scalar_type() == torch::kBFloat16 && k_in.scalar_type() == torch::kBFloat16 &&
               v_in.scalar_type() == torch::kBFloat16, "attention: bf16 CUDA tensors");
@@ -652,11 +659,13 @@ std::tuple<Tensor, Tensor> df3_attention_fwd(const Tensor& q_in, const Tensor& k
     if (out.stride(4) != 1) out = torch::empty(q.sizes(), q.options());
   }
   Tensor lse = torch::empty({want_lse ? 2 : 0, B, R, H, N}, q.options().dtype(torch::kFloat32));
-  if (out.numel() == 0) return {out, lse};
+  Tensor out32 = want_out32 ? torch::empty({B, R, H, N, D}, q.options().dtype(torch::kFloat32)) : torch::empty({0}, q.options().dtype(torch::kFloat32));
+  if (out.numel() == 0) return {out, lse, out32};
 
   AttnParams p{};
   p.out = reinterpret_cast<__nv_bfloat16*>(out.data_ptr());
   p.lse = want_lse ? lse.data_ptr<float>() : nullptr;
+  p.out32 = want_out32 ? out32.data_ptr<float>() : nullptr;
   p.o_sb = out.stride(0); p.o_sr = out.stride(1); p.o_sh = out.stride(2); p.o_sn = out.stride(3);
   Tensor bias, mask;
   if (bias_in.has_value() && bias_in->defined()) {
@@ -712,7 +721,22 @@ std::tuple<Tensor, Tensor> df3_attention_fwd(const Tensor& q_in, const Tensor& k
   if (dn == 16) DF3_ATTN(16); else if (dn == 32) DF3_ATTN(32); else if (dn == 48) DF3_ATTN(48); else DF3_ATTN(64);
 #undef DF3_ATTN
   C10_CUDA_KERNEL_LAUNCH_CHECK();
-  return {out, lse};
+  return {out, lse, out32};
+}
+
+std::tuple<Tensor, Tensor> df3_attention_fwd(const Tensor& q, const Tensor& k, const Tensor& v, const c10::optional<Tensor>& bias,
+                                             const c10::optional<Tensor>& mask, double scale, bool want_lse) {
+  auto r = attention_fwd_impl(q, k, v, bias, mask, scale, want_lse, false);
+  return {std::get<0>(r), std::get<1>(r)};
+}
+
+// Training forward: also returns the output before its rounding to bf16 ([B, R, H, N, D] fp32), which the backward
+// takes as `out` so that delta = rowsum(dO o O) keeps the cancellation with dP (docs/optimizations.md:409-493 of the
+// reference names the bf16 O store as the first of the roundings that destroy dS at a saturated row).
+std::tuple<Tensor, Tensor, Tensor> df3_attention_fwd_train(const Tensor& q, const Tensor& k, const Tensor& v,
+                                                           const c10::optional<Tensor>& bias, const c10::optional<Tensor>& mask,
+                                                           double scale) {
+  return attention_fwd_impl(q, k, v, bias, mask, scale, true, true);
 }
 
 }  // namespace
@@ -721,6 +745,8 @@ std::tuple<Tensor, Tensor> df3_attention_fwd(const Tensor& q_in, const Tensor& k
 void df3_register_attention(torch::Library& m) {
   m.def("attention_fwd(Tensor q, Tensor k, Tensor v, Tensor? bias, Tensor? key_mask, float scale, bool want_lse) -> (Tensor, Tensor)",
         &df3::df3_attention_fwd);
+  m.def("attention_fwd_train(Tensor q, Tensor k, Tensor v, Tensor? bias, Tensor? key_mask, float scale) -> (Tensor, Tensor, Tensor)",
+        &df3::df3_attention_fwd_train);
   m.def("attention_bwd(Tensor q, Tensor k, Tensor v, Tensor out, Tensor d_out, Tensor? bias, Tensor? key_mask, Tensor lse, "
         "float scale, bool want_dbias, int chunk_bytes) -> (Tensor, Tensor, Tensor, Tensor)",
         &df3::df3_attention_bwd);

@@ -51,6 +51,16 @@ static EncodeTiledFn encode_tiled() {
 
 // bf16 tensor map of any rank up to 5 with 128-byte swizzle; dims/strides innermost first, strides in elements.
 CUtensorMap make_map_nd(const void* base, int rank, const int64_t* dims, const int64_t* strides_elems, const int* box) {
+  // cuTensorMapEncodeTiled is a driver call and wants a context bound to the calling thread. A thread whose first CUDA
+  // work is this call (an autograd worker starting a backward pass with one of these kernels) has none yet: the runtime
+  // binds the primary context lazily, on its own calls. cudaSetDevice binds it.
+  thread_local bool bound = false;
+  if (!bound) {
+    int dev = 0;
+    C10_CUDA_CHECK(cudaGetDevice(&dev));
+    C10_CUDA_CHECK(cudaSetDevice(dev));
+    bound = true;
+  }
   CUtensorMap m;
   cuuint64_t gdims[5];
   cuuint64_t gstrides[4];
@@ -88,8 +98,9 @@ namespace {
 
 constexpr int BM = 128;
 constexpr int BK = 64;  // 64 bf16 = one 128-byte swizzle row
-constexpr int kThreads = 192;
-constexpr int kEpiThreads = 128;
+constexpr int kThreads = 320;      // TMA warp, MMA warp, eight epilogue warps (two per tensor-memory lane quarter)
+constexpr int kEpiThreads = 256;
+constexpr int kMaxResidentK = 4;   // k blocks of the weight tile a CTA may keep in shared memory for its whole life
 constexpr int kGroupM = 8;  // tiles walk the output in bands of 8 tile rows so that concurrent CTAs share operands in L2
 
 enum Epi : int { kPlain = 0, kGated = 1, kSwiGLU = 2, kSigmoidMul = 3, kSwiGLUBwd = 4, kGatedBwd = 5, kGatedT = 6 };
@@ -109,11 +120,13 @@ struct GemmParams {
   int m_tiles, n_tiles, batch, splits;
   int kb_total, kb_per_split; // k blocks of 64
   int stages;
+  int b_resident;             // the CTA's B tile (all of K) stays in shared memory; the ring then holds A only
   int b_batched, a_batched;   // operand has a batch axis
   int proj_row_offset;        // first row of the proj half inside the stacked weight
   int channel_major;          // legacy transposed store of the row-major tile (small shapes only)
   int a_mn, b_mn;             // operand is MN-major (its M / N index is the contiguous one)
   int c_fp32;
+  int tma_store;              // bf16 row-major output with 16-byte aligned rows: tiles leave through shared memory and TMA
   int bias_on_m, mask_on_n;
   long long mask_batch_stride;
 };
@@ -209,12 +222,33 @@ __device__ __forceinline__ TileCoord decode_tile(const GemmParams& p, long long 
   return c;
 }
 
+// Tile i of this CTA. Streaming mode: tiles blockIdx.x, blockIdx.x + gridDim.x, ... in banded order. Resident-B mode
+// (tall products against a small weight): the CTA keeps one n tile for its whole life and walks down the rows, so the
+// weight tile is fetched once per CTA instead of once per output tile.
+__device__ __forceinline__ bool tile_at(const GemmParams& p, long long i, TileCoord& c) {
+  if (p.b_resident) {
+    const int G = gridDim.x / p.n_tiles;
+    const long long u = blockIdx.x / p.n_tiles + i * G;
+    if (u >= (long long)p.m_tiles * p.batch) return false;
+    c.split = 0;
+    c.n_tile = blockIdx.x % p.n_tiles;
+    c.m_tile = (int)(u % p.m_tiles);
+    c.batch = (int)(u / p.m_tiles);
+    return true;
+  }
+  const long long t = blockIdx.x + i * gridDim.x;
+  if (t >= (long long)p.m_tiles * p.n_tiles * p.batch * p.splits) return false;
+  c = decode_tile(p, t);
+  return true;
+}
+
 // Persistent kernel: each CTA walks tiles t = blockIdx.x, blockIdx.x + gridDim.x, ... The accumulator is double
 // buffered in tensor memory, so the epilogue warps drain tile t while the MMA warp already works on tile t + 1, and
 // the shared-memory ring keeps running across tile boundaries.
 template <int BN, int EPI>
 __global__ void __launch_bounds__(kThreads) gemm_kernel(const __grid_constant__ CUtensorMap tmA,
-                                                       const __grid_constant__ CUtensorMap tmB, GemmParams p) {
+                                                       const __grid_constant__ CUtensorMap tmB,
+                                                       const __grid_constant__ CUtensorMap tmC, GemmParams p) {
   constexpr bool kDualA = (EPI == kGatedT);   // gate and proj rows of the stacked weight as two A tiles: transposed (channel-major) output
   using S = Smem<BN, kDualA>;
   constexpr bool kDual = (EPI == kGated || EPI == kSwiGLU || EPI == kSwiGLUBwd || EPI == kGatedBwd);
@@ -225,14 +259,17 @@ __global__ void __launch_bounds__(kThreads) gemm_kernel(const __grid_constant__ 
   static_assert(kTmemCols <= 512, "accumulator buffers exceed tensor memory");
   extern __shared__ uint8_t smem_raw[];
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* full = reinterpret_cast<uint64_t*>(tiles + (size_t)p.stages * S::kStageBytes);
+  const int stage_bytes = p.b_resident ? S::kABytes : S::kStageBytes;
+  uint8_t* b_res = tiles + (size_t)p.stages * stage_bytes;   // resident weight tile: kb_total blocks of kBBytes
+  uint8_t* c_stage = b_res + (p.b_resident ? (size_t)p.kb_total * S::kBBytes : 0);   // two 128 x 64 bf16 boxes when tma_store
+  uint64_t* full = reinterpret_cast<uint64_t*>(c_stage + (p.tma_store ? 2 * 16384 : 0));
   uint64_t* empty = full + p.stages;
   uint64_t* acc_full = empty + p.stages;   // [2]
   uint64_t* acc_empty = acc_full + 2;      // [2]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  uint64_t* b_full = acc_empty + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(b_full + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const long long total_tiles = (long long)p.m_tiles * p.n_tiles * p.batch * p.splits;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.stages; ++s) {
@@ -243,6 +280,7 @@ __global__ void __launch_bounds__(kThreads) gemm_kernel(const __grid_constant__ 
       ptx::mbar_init(&acc_full[s], 1);
       ptx::mbar_init(&acc_empty[s], kEpiThreads);
     }
+    ptx::mbar_init(b_full, 1);
     ptx::fence_barrier_init();
   }
   if (warp == 1) {
@@ -260,17 +298,32 @@ __global__ void __launch_bounds__(kThreads) gemm_kernel(const __grid_constant__ 
       ptx::prefetch_tensormap(&tmB);
       long long it = 0;  // k blocks issued so far by this CTA (the ring position)
       bool ok = true;
-      for (long long t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-        const TileCoord c = decode_tile(p, t);
+      TileCoord c;
+      auto load_b = [&](uint8_t* b_s, uint64_t* bar, int kb, int n_tile, int bz) {
+        if (p.b_mn) {
+#pragma unroll
+          for (int blk = 0; blk < BN / 64; ++blk) ptx::tma_load_3d(b_s + blk * 8192, &tmB, bar, n_tile * BN + blk * 64, kb * BK, bz);
+        } else if (kDual) {
+          ptx::tma_load_3d(b_s, &tmB, bar, kb * BK, n_tile * (BN / 2), bz);
+          ptx::tma_load_3d(b_s + S::kBBytes / 2, &tmB, bar, kb * BK, p.proj_row_offset + n_tile * (BN / 2), bz);
+        } else {
+          ptx::tma_load_3d(b_s, &tmB, bar, kb * BK, n_tile * BN, bz);
+        }
+      };
+      if (p.b_resident && tile_at(p, 0, c)) {
+        ptx::mbar_expect_tx(b_full, (uint32_t)(p.kb_total * S::kBBytes));
+        for (int kb = 0; kb < p.kb_total; ++kb) load_b(b_res + (size_t)kb * S::kBBytes, b_full, kb, c.n_tile, 0);
+      }
+      for (long long i = 0; ok && tile_at(p, i, c); ++i) {
         const int kb0 = c.split * p.kb_per_split, kb1 = min(p.kb_total, kb0 + p.kb_per_split);
         const int az = p.a_batched ? c.batch : 0, bz = p.b_batched ? c.batch : 0;
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = (int)(it % p.stages);
           const uint32_t ph = (uint32_t)(it / p.stages) & 1u;
           if (!ptx::mbar_wait(&empty[s], ph ^ 1u, p.status, kTimeoutStageEmpty)) { ok = false; break; }
-          uint8_t* a_s = tiles + (size_t)s * S::kStageBytes;
+          uint8_t* a_s = tiles + (size_t)s * stage_bytes;
           uint8_t* b_s = a_s + S::kABytes;
-          ptx::mbar_expect_tx(&full[s], S::kStageBytes);
+          ptx::mbar_expect_tx(&full[s], (uint32_t)stage_bytes);
           if (p.a_mn) {  // [k][m] with m contiguous: two 64-wide column blocks of 64 k rows
             ptx::tma_load_3d(a_s, &tmA, &full[s], c.m_tile * BM, kb * BK, az);
             ptx::tma_load_3d(a_s + 8192, &tmA, &full[s], c.m_tile * BM + 64, kb * BK, az);
@@ -278,21 +331,13 @@ __global__ void __launch_bounds__(kThreads) gemm_kernel(const __grid_constant__ 
             ptx::tma_load_3d(a_s, &tmA, &full[s], kb * BK, c.m_tile * BM, az);
             if (kDualA) ptx::tma_load_3d(a_s + BM * BK * 2, &tmA, &full[s], kb * BK, p.proj_row_offset + c.m_tile * BM, az);
           }
-          if (p.b_mn) {
-#pragma unroll
-            for (int blk = 0; blk < BN / 64; ++blk)
-              ptx::tma_load_3d(b_s + blk * 8192, &tmB, &full[s], c.n_tile * BN + blk * 64, kb * BK, bz);
-          } else if (kDual) {
-            ptx::tma_load_3d(b_s, &tmB, &full[s], kb * BK, c.n_tile * (BN / 2), bz);
-            ptx::tma_load_3d(b_s + S::kBBytes / 2, &tmB, &full[s], kb * BK, p.proj_row_offset + c.n_tile * (BN / 2), bz);
-          } else {
-            ptx::tma_load_3d(b_s, &tmB, &full[s], kb * BK, c.n_tile * BN, bz);
-          }
+          if (!p.b_resident) load_b(b_s, &full[s], kb, c.n_tile, bz);
         }
       }
       if (!ok) {  // give up: let the copies already in flight land before the CTA's shared memory goes away
         const long long first = it > p.stages ? it - p.stages : 0;
         for (long long k = first; k < it; ++k) ptx::mbar_wait_quiet(&full[k % p.stages], (uint32_t)(k / p.stages) & 1u);
+        if (p.b_resident) ptx::mbar_wait_quiet(b_full, 0);
       }
     }
   } else if (warp == 1) {
@@ -300,11 +345,11 @@ __global__ void __launch_bounds__(kThreads) gemm_kernel(const __grid_constant__ 
       const uint32_t idesc = ptx::idesc_bf16_f32(BM, BN) | (p.a_mn ? ptx::kIdescAMnMajor : 0u) | (p.b_mn ? ptx::kIdescBMnMajor : 0u);
       long long it = 0;
       bool ok = true;
-      int local = 0;
-      for (long long t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++local) {
-        const TileCoord c = decode_tile(p, t);
+      TileCoord c;
+      if (p.b_resident && tile_at(p, 0, c)) ok = ptx::mbar_wait(b_full, 0, p.status, kTimeoutTmaFull);
+      for (long long local = 0; ok && tile_at(p, local, c); ++local) {
         const int kb0 = c.split * p.kb_per_split, kb1 = min(p.kb_total, kb0 + p.kb_per_split);
-        const int ab = local & 1;
+        const int ab = (int)(local & 1);
         if (!ptx::mbar_wait(&acc_empty[ab], (uint32_t)((local >> 1) & 1) ^ 1u, p.status, kTimeoutStageEmpty)) { ok = false; break; }
         ptx::tc_fence_after();
         const uint32_t acc = tmem + ab * kAccCols;
@@ -313,8 +358,8 @@ __global__ void __launch_bounds__(kThreads) gemm_kernel(const __grid_constant__ 
           const uint32_t ph = (uint32_t)(it / p.stages) & 1u;
           if (!ptx::mbar_wait(&full[s], ph, p.status, kTimeoutTmaFull)) { ok = false; break; }
           ptx::tc_fence_after();
-          const uint32_t a_addr = ptx::smem_u32(tiles + (size_t)s * S::kStageBytes);
-          const uint32_t b_addr = a_addr + S::kABytes;
+          const uint32_t a_addr = ptx::smem_u32(tiles + (size_t)s * stage_bytes);
+          const uint32_t b_addr = p.b_resident ? ptx::smem_u32(b_res + (size_t)kb * S::kBBytes) : a_addr + S::kABytes;
           const uint64_t a_desc = p.a_mn ? ptx::smem_desc_mn_sw128(a_addr, 8192) : ptx::smem_desc_k_sw128(a_addr);
           const uint64_t b_desc = p.b_mn ? ptx::smem_desc_mn_sw128(b_addr, 8192) : ptx::smem_desc_k_sw128(b_addr);
           // 16 bf16 along K per MMA: 32 bytes inside the swizzled row (K-major) or 16 rows of 128 bytes (MN-major)
@@ -334,15 +379,34 @@ __global__ void __launch_bounds__(kThreads) gemm_kernel(const __grid_constant__ 
       }
     }
   } else {
-    const int q = warp & 3;  // TMEM lane quarter this warp may read
-    int local = 0;
+    const int q = warp & 3;           // TMEM lane quarter this warp may read
+    const int chalf = (warp - 2) >> 2;  // which half of the 32-column chunks this warp takes
+    constexpr bool kCanTmaStore = kOutPerTile >= 64;
+    const bool tma_out = kCanTmaStore && p.tma_store;
+    const bool issuer = threadIdx.x == 64;  // first epilogue thread: issues and tracks the TMA stores
+    const int row_in_tile = q * 32 + lane;
+    // this thread's 128-byte line inside a staged 128 x 64 box; 16-byte chunks are XOR-swizzled by the row
+    uint8_t* stage_row = c_stage + (row_in_tile >> 3) * 1024 + (row_in_tile & 7) * 128;
+    const int swz = row_in_tile & 7;
+    auto stage32 = [&](int buf, const float* v) {  // 32 values -> this thread's half of the staged line
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        uint4 w;
+        w.x = pack_bf16(v[g * 8 + 0], v[g * 8 + 1]);
+        w.y = pack_bf16(v[g * 8 + 2], v[g * 8 + 3]);
+        w.z = pack_bf16(v[g * 8 + 4], v[g * 8 + 5]);
+        w.w = pack_bf16(v[g * 8 + 6], v[g * 8 + 7]);
+        *reinterpret_cast<uint4*>(stage_row + buf * 16384 + (((chalf * 4 + g) ^ swz) << 4)) = w;
+      }
+    };
+    int boxes = 0;  // 64-column boxes staged so far by this CTA (buffer = boxes & 1 for single-output epilogues)
     bool ok = true;
-    for (long long t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++local) {
-      const TileCoord c = decode_tile(p, t);
-      const int ab = local & 1;
+    TileCoord c;
+    for (long long local = 0; ok && tile_at(p, local, c); ++local) {
+      const int ab = (int)(local & 1);
       if (!ptx::mbar_wait(&acc_full[ab], (uint32_t)(local >> 1) & 1u, p.status, kTimeoutMmaDone)) { ok = false; break; }
       ptx::tc_fence_after();
-      const int row = c.m_tile * BM + q * 32 + lane;
+      const int row = c.m_tile * BM + row_in_tile;
       const uint32_t t_row = tmem + ab * kAccCols + ((uint32_t)(q * 32) << 16);
       const long long batch = c.batch;
       const long long c_off = batch * p.c_batch_stride + (long long)c.split * p.c_split_stride;
@@ -351,69 +415,94 @@ __global__ void __launch_bounds__(kThreads) gemm_kernel(const __grid_constant__ 
       const float bm = (p.bias != nullptr && p.bias_on_m && row < p.M) ? p.bias[row] : 0.f;
       float a[32], b[32];
 #pragma unroll 1
-      for (int cc = 0; cc < kOutPerTile / 32; ++cc) {
+      for (int cc = (kOutPerTile >= 64 ? chalf : 0); cc < kOutPerTile / 32; cc += (kOutPerTile >= 64 ? 2 : 1)) {
         const int n0 = c.n_tile * kOutPerTile + cc * 32;
-        if (n0 >= p.N) break;
-        ptx::tmem_ld_32x32(t_row + cc * 32, a);
-        if (kDual) ptx::tmem_ld_32x32(t_row + BN / 2 + cc * 32, b);
-        if (kDualA) ptx::tmem_ld_32x32(t_row + BN + cc * 32, b);
-        ptx::tmem_ld_wait();
-        if (EPI == kPlain) {
-          if (p.bias != nullptr && !p.bias_on_m) {
+        const bool live = n0 < p.N && !(kOutPerTile < 64 && chalf != 0);   // uniform over the warp
+        if (!live && !tma_out) break;
+        if (live) {
+          ptx::tmem_ld_32x32(t_row + cc * 32, a);
+          if (kDual) ptx::tmem_ld_32x32(t_row + BN / 2 + cc * 32, b);
+          if (kDualA) ptx::tmem_ld_32x32(t_row + BN + cc * 32, b);
+          ptx::tmem_ld_wait();
+          if (EPI == kPlain) {
+            if (p.bias != nullptr && !p.bias_on_m) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) a[j] += (n0 + j < p.N) ? p.bias[n0 + j] : 0.f;
-          }
-          if (mask_b != nullptr && p.mask_on_n) {
+              for (int j = 0; j < 32; ++j) a[j] += (n0 + j < p.N) ? p.bias[n0 + j] : 0.f;
+            }
+            if (mask_b != nullptr && p.mask_on_n) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) a[j] = (a[j] + bm) * ((n0 + j < p.N) ? mask_b[n0 + j] : 0.f);
-          } else {
+              for (int j = 0; j < 32; ++j) a[j] = (a[j] + bm) * ((n0 + j < p.N) ? mask_b[n0 + j] : 0.f);
+            } else {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) a[j] = (a[j] + bm) * rm;
-          }
-        } else if (EPI == kGated) {
+              for (int j = 0; j < 32; ++j) a[j] = (a[j] + bm) * rm;
+            }
+          } else if (EPI == kGated) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) a[j] = sigmoidf_(a[j]) * b[j] * rm;
-        } else if (EPI == kGatedT) {
-          // rows are output channels, columns are the input rows: the mask runs along the columns
+            for (int j = 0; j < 32; ++j) a[j] = sigmoidf_(a[j]) * b[j] * rm;
+          } else if (EPI == kGatedT) {
+            // rows are output channels, columns are the input rows: the mask runs along the columns
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const float mk = mask_b ? ((n0 + j < p.N) ? mask_b[n0 + j] : 0.f) : 1.f;
-            a[j] = sigmoidf_(a[j]) * b[j] * mk;
-          }
-        } else if (EPI == kSwiGLU) {
+            for (int j = 0; j < 32; ++j) {
+              const float mk = mask_b ? ((n0 + j < p.N) ? mask_b[n0 + j] : 0.f) : 1.f;
+              a[j] = sigmoidf_(a[j]) * b[j] * mk;
+            }
+          } else if (EPI == kSwiGLU) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) a[j] = a[j] * sigmoidf_(a[j]) * b[j];
-        } else if (kBwd) {
-          const __nv_bfloat16* grow = p.mul + batch * p.mul_batch_stride + (long long)row * p.ld_mul + n0;
-          float g[32];
-          load_row32(grow, row < p.M, n0, p.N, g);
+            for (int j = 0; j < 32; ++j) a[j] = a[j] * sigmoidf_(a[j]) * b[j];
+          } else if (kBwd) {
+            const __nv_bfloat16* grow = p.mul + batch * p.mul_batch_stride + (long long)row * p.ld_mul + n0;
+            float g[32];
+            load_row32(grow, row < p.M, n0, p.N, g);
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const float sg = sigmoidf_(a[j]);
-            const float gj = g[j] * rm;
-            const float da = EPI == kSwiGLUBwd ? gj * b[j] * sg * (1.f + a[j] * (1.f - sg)) : gj * b[j] * sg * (1.f - sg);
-            const float dbv = EPI == kSwiGLUBwd ? gj * a[j] * sg : gj * sg;
-            a[j] = da;
-            b[j] = dbv;
-          }
-          store_row32(p, p.C, c_off, row, n0, a);
-          store_row32(p, reinterpret_cast<__nv_bfloat16*>(p.C) + p.N, c_off, row, n0, b);  // second half of the [M, 2 N] output
-          continue;
-        } else {  // kSigmoidMul
-          const __nv_bfloat16* mrow = p.mul + batch * p.mul_batch_stride + (long long)row * p.ld_mul + n0;
-          float g[32];
-          load_row32(mrow, row < p.M, n0, p.N, g);
+            for (int j = 0; j < 32; ++j) {
+              const float sg = sigmoidf_(a[j]);
+              const float gj = g[j] * rm;
+              const float da = EPI == kSwiGLUBwd ? gj * b[j] * sg * (1.f + a[j] * (1.f - sg)) : gj * b[j] * sg * (1.f - sg);
+              const float dbv = EPI == kSwiGLUBwd ? gj * a[j] * sg : gj * sg;
+              a[j] = da;
+              b[j] = dbv;
+            }
+          } else {  // kSigmoidMul
+            const __nv_bfloat16* mrow = p.mul + batch * p.mul_batch_stride + (long long)row * p.ld_mul + n0;
+            float g[32];
+            load_row32(mrow, row < p.M, n0, p.N, g);
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const float bv = (p.bias != nullptr && n0 + j < p.N) ? p.bias[n0 + j] : 0.f;
-            a[j] = sigmoidf_(a[j] + bv) * g[j];
+            for (int j = 0; j < 32; ++j) {
+              const float bv = (p.bias != nullptr && n0 + j < p.N) ? p.bias[n0 + j] : 0.f;
+              a[j] = sigmoidf_(a[j] + bv) * g[j];
+            }
           }
         }
-        store_row32(p, p.C, c_off, row, n0, a);
+        if (tma_out) {
+          // the 64-column box this chunk belongs to leaves through shared memory: both column halves (the two warps of a
+          // lane quarter) stage their 32 columns, then one thread hands the box to the TMA unit, which clips it at the
+          // tensor's bounds. The backward epilogues stage two boxes (both output halves) per round.
+          if ((c.n_tile * kOutPerTile + (cc & ~1) * 32) >= p.N) break;  // whole box beyond the output: the same for all threads
+          const int buf = kBwd ? 0 : (boxes & 1);
+          if (issuer) { if (kBwd) ptx::tma_store_wait_read<0>(); else ptx::tma_store_wait_read<1>(); }
+          ptx::named_barrier(1, kEpiThreads);   // the buffer's previous box has been read out
+          stage32(buf, a);
+          if (kBwd) stage32(1, b);
+          ptx::fence_proxy_async();
+          ptx::named_barrier(1, kEpiThreads);   // the box is complete
+          if (issuer) {
+            const int x0 = c.n_tile * kOutPerTile + (cc & ~1) * 32;
+            ptx::tma_store_3d(&tmC, c_stage + buf * 16384, x0, c.m_tile * BM, c.batch);
+            if (kBwd) ptx::tma_store_3d(&tmC, c_stage + 16384, p.N + x0, c.m_tile * BM, c.batch);
+            ptx::tma_store_commit();
+          }
+          ++boxes;
+        } else if (kBwd) {
+          store_row32(p, p.C, c_off, row, n0, a);
+          store_row32(p, reinterpret_cast<__nv_bfloat16*>(p.C) + p.N, c_off, row, n0, b);  // second half of the [M, 2 N] output
+        } else {
+          store_row32(p, p.C, c_off, row, n0, a);
+        }
       }
       ptx::tc_fence_before();
       ptx::mbar_arrive(&acc_empty[ab]);
     }
+    if (tma_out && issuer) ptx::tma_store_wait_read<0>();  // shared memory stays valid until the last box has been read
   }
   ptx::tc_fence_before();
   __syncthreads();
@@ -465,28 +554,57 @@ CUtensorMap operand_map(const Tensor& t3, bool mn_major, int box_rows) {
   return make_map_nd(t3.data_ptr(), 3, dims, strides, box);
 }
 
+// bf16 output [batch, rows, cols] (contiguous) as a store target: boxes of 64 columns x 128 rows
+CUtensorMap output_map(const Tensor& out, int64_t rows, int64_t cols, int64_t batch) {
+  const int64_t dims[3] = {cols, rows, batch};
+  const int64_t strides[3] = {1, cols, rows * cols};
+  const int box[3] = {64, BM, 1};
+  return make_map_nd(out.data_ptr(), 3, dims, strides, box);
+}
+
 template <int BN, int EPI>
-void launch(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams& p, cudaStream_t stream) {
+void launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, GemmParams& p, cudaStream_t stream) {
   using S = Smem<BN, EPI == kGatedT>;
   const int per_tile_k = p.kb_per_split;
-  // a deep ring when the K loop is long; short loops (pair-shaped GEMMs, two k blocks) still get four stages so that
-  // the loads of the next tiles run ahead of the epilogue
-  int stages = per_tile_k >= 8 ? 6 : 4;
-  while (stages > 2 && (size_t)stages * S::kStageBytes + 2048 > 220 * 1024) --stages;
+  const long long tiles = (long long)p.m_tiles * p.n_tiles * p.batch * p.splits;
+  TORCH_CHECK(tiles > 0 && tiles < (1ll << 40), "gemm: grid too large");
+  constexpr int acc_cols = (EPI == kGatedT ? 2 : 1) * BN * 2;
+  const int sms = sm_count();
+  // Tall product against a small broadcast weight (the pair-shaped linears: K <= 256, hundreds of row tiles): each CTA
+  // keeps its weight tile in shared memory and streams row tiles through a ring that holds A only. Otherwise every
+  // output tile would fetch the weight tile again and the L2-to-SM traffic of the weights would exceed the traffic of
+  // the activations.
+  p.b_resident = (!p.b_batched && p.splits == 1 && p.kb_total <= kMaxResidentK && EPI != kGatedT &&
+                  (long long)p.m_tiles * p.batch >= 4ll * sms / std::max(1, p.n_tiles) && p.n_tiles <= sms) ? 1 : 0;
+  constexpr bool dual_b = (EPI == kGated || EPI == kSwiGLU || EPI == kSwiGLUBwd || EPI == kGatedBwd);
+  if ((dual_b ? BN / 2 : BN) < 64) p.tma_store = 0;  // narrow tiles store from registers
+  const size_t extra = (p.tma_store ? 2 * 16384 : 0) + 1024 + 256;
+  int stages;
+  size_t smem;
+  if (p.b_resident) {
+    stages = 6;
+    smem = (size_t)stages * S::kABytes + (size_t)p.kb_total * S::kBBytes + extra;
+  } else {
+    // a deep ring when the K loop is long; short loops still get enough stages for the loads of the next tile to run
+    // ahead of the epilogue, but few enough for two CTAs per SM when the accumulators allow it
+    stages = per_tile_k >= 8 ? 6 : (acc_cols <= 256 && 3 * S::kStageBytes + extra <= 110 * 1024 ? 3 : 4);
+    while (stages > 2 && (size_t)stages * S::kStageBytes + extra > 226 * 1024) --stages;
+    smem = (size_t)stages * S::kStageBytes + extra;
+  }
   p.stages = stages;
-  const size_t smem = (size_t)stages * S::kStageBytes + 1024 + 256;
   static bool attr_set = false;
   if (!attr_set) {
     C10_CUDA_CHECK(cudaFuncSetAttribute(gemm_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
     attr_set = true;
   }
-  const long long tiles = (long long)p.m_tiles * p.n_tiles * p.batch * p.splits;
-  TORCH_CHECK(tiles > 0 && tiles < (1ll << 40), "gemm: grid too large");
   // one CTA per SM, or two when both the shared memory and the tensor-memory columns allow it
-  constexpr int acc_cols = (EPI == kGatedT ? 2 : 1) * BN * 2;
   const int per_sm = (smem <= 110 * 1024 && acc_cols <= 256) ? 2 : 1;
-  const long long ctas = std::min<long long>(tiles, (long long)sm_count() * per_sm);
-  gemm_kernel<BN, EPI><<<(unsigned)ctas, kThreads, smem, stream>>>(ta, tb, p);
+  long long ctas = std::min<long long>(tiles, (long long)sms * per_sm);
+  if (p.b_resident) {
+    const long long groups = std::max<long long>(1, std::min<long long>((long long)sms * per_sm / p.n_tiles, (long long)p.m_tiles * p.batch));
+    ctas = groups * p.n_tiles;
+  }
+  gemm_kernel<BN, EPI><<<(unsigned)ctas, kThreads, smem, stream>>>(ta, tb, tc, p);
   C10_CUDA_KERNEL_LAUNCH_CHECK();
 }
 
@@ -562,7 +680,9 @@ Tensor gemm_impl(const Tensor& a3, const Tensor& w3, const c10::optional<Tensor>
     p.c_batch_stride = N * M;
     const CUtensorMap ta = operand_map(w3, false, BM);
     const CUtensorMap tb = operand_map(a3, false, BN);
-    if (epi == kPlain) launch<BN, kPlain>(ta, tb, p, stream); else launch<BN, kGatedT>(ta, tb, p, stream);
+    p.tma_store = (M % 8 == 0) ? 1 : 0;
+    const CUtensorMap tc = p.tma_store ? output_map(out, N, M, batch) : ta;
+    if (epi == kPlain) launch<BN, kPlain>(ta, tb, tc, p, stream); else launch<BN, kGatedT>(ta, tb, tc, p, stream);
     return out;
   }
 
@@ -634,7 +754,10 @@ Tensor gemm_impl(const Tensor& a3, const Tensor& w3, const c10::optional<Tensor>
 
   const CUtensorMap ta = operand_map(a3, o.a_mn, BM);
   const CUtensorMap tb = operand_map(w3, o.b_mn, dual ? BN / 2 : BN);
-#define DF3_LAUNCH(BN_, EPI_) launch<BN_, EPI_>(ta, tb, p, stream)
+  p.tma_store = (splits == 1 && !p.c_fp32 && !o.channel_major && out_cols % 8 == 0 && N % 8 == 0 &&
+                 reinterpret_cast<uintptr_t>(out.data_ptr()) % 16 == 0) ? 1 : 0;
+  const CUtensorMap tc = p.tma_store ? output_map(out, M, out_cols, batch) : ta;
+#define DF3_LAUNCH(BN_, EPI_) launch<BN_, EPI_>(ta, tb, tc, p, stream)
   switch (epi) {
     case kPlain:
       if (BN == 256) DF3_LAUNCH(256, kPlain); else if (BN == 128) DF3_LAUNCH(128, kPlain); else if (BN == 64) DF3_LAUNCH(64, kPlain); else DF3_LAUNCH(32, kPlain);

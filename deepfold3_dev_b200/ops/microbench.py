@@ -111,9 +111,9 @@ def bench_attention(t: Timer):
         ours = t(lambda: df3.attention_fwd(q, k, v, bias, mask, D**-0.5, True))
         eager = t(lambda: ref.pair_bias_attention(q, k, v, bias, mask, D**-0.5, False))
         _report(f"attention fwd {name}", ours, eager, 2 * 4 * B * R * H * N * D, 4 * B * R * H * N * N * D)
-        out, lse = df3.attention_fwd(q, k, v, bias, mask, D**-0.5, True)
+        out, lse, out32 = df3.attention_fwd_train(q, k, v, bias, mask, D**-0.5)
         d_out = torch.randn_like(out)
-        fused = t(lambda: df3.attention_bwd(q, k, v, out, d_out, bias, mask, lse, D**-0.5, True, 40 << 20))
+        fused = t(lambda: df3.attention_bwd(q, k, v, out32, d_out, bias, mask, lse, D**-0.5, True, 40 << 20))
         chunked = t(lambda: df3.attention_bwd(q, k, v, out, d_out, bias, mask, lse, D**-0.5, True, -(40 << 20)))
         # five products of 2 N N D per (b, r, h); the chunked form (library GEMMs + one kernel per chunk) is the comparison
         _report(f"attention bwd {name}", fused, chunked, 2 * 8 * B * R * H * N * D, 10 * B * R * H * N * N * D)

@@ -32,6 +32,7 @@ class GradSync:
         self.info = info
         # NCCL ranks on one node default to the peer-memory kernel; everything else to the collective
         default = "peer" if (info.is_distributed and info.backend == "nccl") else "collective"
+        self.explicit = transport is not None or "DF3_COMM" in os.environ
         self.transport = transport or os.environ.get("DF3_COMM", default)
         self._peer = None
 
@@ -43,15 +44,38 @@ class GradSync:
         return self._peer
 
     def attach(self, opt) -> None:
-        """Peer transport: move the optimizer's gradient buffer into symmetric memory now (a collective call)."""
+        """Peer transport: move the optimizer's gradient buffer into peer-mapped memory now (a collective call).
+
+        When the transport was asked for explicitly (``DF3_COMM=peer`` or the ``transport`` argument) a failure to set it
+        up is an error; only the implicit default falls back to the collective, and says so.
+        """
         if self.transport == "peer" and self.info.is_distributed and opt.flat_grad.is_cuda:
             try:
                 self._peer_engine(opt)
-            except Exception as exc:  # noqa: BLE001 - symmetric memory unavailable (same on every rank): use NCCL
+            except Exception as exc:  # noqa: BLE001
+                if self.explicit:
+                    raise RuntimeError(f"DF3_COMM=peer: the peer-memory gradient transport could not be set up: {exc!r}") from exc
                 import logging
 
                 logging.getLogger(__name__).warning("peer-memory gradient transport unavailable (%r); using NCCL", exc)
                 self.transport, self._peer = "collective", None
+
+    def fused_step_engine(self, opt):
+        """The peer engine when the whole optimizer step can run as its one fused kernel, else ``None``: CUDA buffers,
+        plain ``FlatAdamW`` (the schedule-free update has its own sequence), the peer transport (or a single process),
+        and not switched off with ``DF3_FUSED_STEP=0``."""
+        from ..training.flat_optimizer import FlatAdamW
+
+        if type(opt) is not FlatAdamW or not opt.flat_grad.is_cuda or os.environ.get("DF3_FUSED_STEP", "1") == "0":
+            return None
+        if self.info.is_distributed and self.transport != "peer":
+            return None
+        try:
+            return self._peer_engine(opt)
+        except Exception:  # noqa: BLE001 - single process without the extension: the classic sequence still works
+            if self.info.is_distributed:
+                raise
+            return None
 
     @torch.no_grad()
     def clip_and_average(self, opt, clip_norm: float, per_rank_clip: bool, fp64_norm: bool = True):

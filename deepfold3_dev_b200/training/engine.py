@@ -122,10 +122,100 @@ class OptimizerEngine:
             if rid is not None:
                 self._window_record_ids.append(rid)
 
+    # ------------------------------------------------------------------ one-kernel step (CUDA)
+    def resolve(self, state: TrainState) -> StepResult | None:
+        """Settle the outcome of the last fused step on the host (its result block was copied back asynchronously).
+
+        The fused step is launched without waiting for its verdict and booked as advanced. If the device-side consensus
+        skipped it (non-finite loss or gradient on any rank, an outlier norm, a wait for a peer that ran out), the
+        bookkeeping is taken back here: step counters, bias-correction count, EMA count and schedule position. Called
+        at the start of the next optimizer step - a whole forward/backward later, when the copy has long landed - and by
+        the trainer before it takes a decision that depends on the step number.
+        """
+        pending, self._pending = getattr(self, "_pending", None), None
+        if pending is None:
+            return None
+        res = pending["peer"].read_result()
+        state.last_grad_norm = torch.tensor(res["norm"])
+        if self.cfg.per_rank_grad_clip and self.dist.is_distributed:
+            finite = [n for n in res["local_norms"] if n == n and abs(n) != float("inf")]
+            if finite:
+                state.last_grad_norm_rank_mean = torch.tensor(sum(finite) / len(finite))
+                state.last_grad_norm_rank_max = torch.tensor(max(finite))
+        if res["advanced"]:
+            return StepResult(True, False, None, state.last_grad_norm, [])
+        opt, attempted = self.optimizer, pending["attempted"]
+        opt.step_count -= 1
+        if pending["ema"]:
+            opt.ema_updates -= 1
+        self.scheduler.last_epoch -= 1
+        self.scheduler._apply()
+        state.effective_step -= 1
+        state.consecutive_nan_skips = pending["skips_before"]
+        self._window_record_ids = pending["records"]
+        if res["reason"] == "timeout":
+            pending["peer"].status.zero_()
+            raise RuntimeError(f"Step {attempted}: a bounded wait for another rank ran out inside the fused optimizer step "
+                               "(a rank left or fell far behind); parameters were not updated")
+        if res["reason"] == "loss":
+            ranks = [r for r, f in enumerate(res["loss_flags"]) if f != 0.0]
+            if self.dist.is_main:
+                logger.warning("Step %d: NaN/Inf loss in accumulation window (ranks=%s), skipped", attempted, ranks)
+            self._report_records(attempted, ranks, "NaN/Inf loss window")
+            self._account_skip(state, attempted, "loss")
+            return StepResult(False, True, "loss", None, ranks)
+        norms = res["local_norms"] if (self.cfg.per_rank_grad_clip and self.dist.is_distributed) else [res["norm"]] * self.dist.world_size
+        thr = self.cfg.grad_norm_skip_threshold
+        ranks = [r for r, n in enumerate(norms) if not (n == n and abs(n) != float("inf")) or (thr > 0 and n > thr)]
+        if self.dist.is_main:
+            logger.warning("Step %d: non-finite or outlier gradient norm (ranks=%s, norm of the average %.3e), skipped",
+                           attempted, ranks, res["norm"])  # fmt: skip
+        self._report_records(attempted, ranks, "bad gradient")
+        self._account_skip(state, attempted, "grad")
+        return StepResult(False, True, "grad", state.last_grad_norm, ranks)
+
+    def _step_fused(self, state: TrainState, peer) -> StepResult:
+        cfg, opt = self.cfg, self.optimizer
+        self.resolve(state)  # the previous step's verdict first: it fixes this step's counters
+        per_rank = bool(cfg.per_rank_grad_clip and self.dist.is_distributed)
+        dev = opt.flat_grad.device
+        clip = cfg.grad_clip_norm if cfg.grad_clip_norm and cfg.grad_clip_norm > 0 else 0.0
+        if per_rank:
+            local = opt.grad_norm(True)
+            c = torch.clamp(clip / (local + 1e-6), max=1.0) if clip > 0 else torch.ones((), device=dev)
+            coef = torch.where(torch.isfinite(local), c, torch.ones_like(c))
+        else:
+            local, coef = torch.zeros((), device=dev), torch.ones((), device=dev)
+        g0 = opt.param_groups[0]
+        step = opt.step_count + 1
+        b1, b2 = g0["betas"]
+        ema = opt.shadow
+        peer.fused_step(opt, coef=coef, loss_flag=self._nan_accum, local_norm=local, lr=g0["lr"], betas=(b1, b2), eps=g0["eps"],
+                        bc1=1.0 - b1**step, bc2=1.0 - b2**step, ema=ema, ema_w=1.0 - opt.ema_decay, clip_norm=clip,
+                        skip_threshold=cfg.grad_norm_skip_threshold, per_rank_clip=per_rank)  # fmt: skip
+        self._nan_accum.zero_()
+        from ..ops import autograd_ops
+
+        autograd_ops.invalidate_weight_cache()  # stacked bf16 copies were built from the old parameter values
+        self._pending = {"peer": peer, "attempted": state.effective_step + 1, "ema": ema is not None,
+                         "skips_before": state.consecutive_nan_skips, "records": list(self._window_record_ids)}  # fmt: skip
+        opt.step_count = step
+        if ema is not None:
+            opt.ema_updates += 1
+        self.scheduler.step()
+        self._window_record_ids.clear()
+        state.effective_step += 1
+        state.consecutive_nan_skips = 0
+        state.last_grad_norm = peer.result[2]  # device scalar, no host read here
+        return StepResult(True, False, None, peer.result[2], [])
+
     def step_or_skip(self, state: TrainState) -> StepResult:
         """MUST be called by every rank on every sync step."""
         assert self._nan_accum is not None, "add_microstep_loss must run at least once before step_or_skip"
         cfg, opt = self.cfg, self.optimizer
+        peer = self.grad_sync.fused_step_engine(opt)
+        if peer is not None:
+            return self._step_fused(state, peer)
         with collective_guard("step_or_skip", self.dist):
             flags = all_gather_scalar(self._nan_accum, self.dist)
             bad = bool(flags.any().item())
@@ -146,7 +236,22 @@ class OptimizerEngine:
             state.last_grad_norm = local.detach()
             if global_norm is not None:
                 state.last_grad_norm_global = global_norm.detach()
-            norms = all_gather_scalar(local.float(), self.dist)
+            check = local.float()
+            if global_norm is not None:  # per-rank mode: a reduction that failed returns a NaN norm of the average
+                check = torch.where(torch.isfinite(global_norm.float()), check, global_norm.float())
+            if opt.flat_grad.is_cuda:  # a kernel whose bounded wait ran out left garbage behind: skip on every rank
+                from ..ops import native
+
+                if native.available():
+                    bad_kernel = torch.ops.df3.gemm_status() != 0
+                    peer_eng = getattr(self.grad_sync, "_peer", None)
+                    if peer_eng is not None:
+                        bad_kernel = bad_kernel or int(peer_eng.status.item()) != 0
+                        peer_eng.status.zero_()
+                    if bad_kernel:
+                        logger.error("Step %d: a kernel reported a wait that ran out on rank %d; the step is skipped", attempted, self.dist.rank)
+                        check = torch.full_like(check, float("nan"))
+            norms = all_gather_scalar(check, self.dist)
             finite = torch.isfinite(norms)
             if bool(finite.any().item()):
                 state.last_grad_norm_rank_mean = norms[finite].mean()

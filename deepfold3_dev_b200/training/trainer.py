@@ -95,6 +95,9 @@ class Trainer:
         self.grad_sync = GradSync(self.dist)
         self.grad_sync.broadcast_parameters(self.optimizer)
         self.grad_sync.attach(self.optimizer)
+        # the one-kernel optimizer step adopts the gradient buffer; do it now so that nothing captured later (CUDA graphs
+        # of the training pass write into the gradient views) points at a buffer that is about to be replaced
+        self.grad_sync.fused_step_engine(self.optimizer)
         self.engine = OptimizerEngine(self.optimizer, self.scheduler, self.dist, train_cfg, self.grad_sync)
         self.state = TrainState()
         self.ckpt = CheckpointManager(train_cfg.output_dir, self.dist, train_cfg.max_checkpoints,
@@ -158,9 +161,11 @@ class Trainer:
         """
         loss, _, _ = self.micro_step(features, num_recycles=num_recycles)
         result = self.engine.step_or_skip(self.state)
+        loss_value = float(loss.item())  # the one host read of the step; the fused step's verdict has landed by then
+        result = self.engine.resolve(self.state) or result
         norm = result.grad_norm
         return {
-            "loss": float(loss.item()),
+            "loss": loss_value,
             "grad_norm": float(norm.item()) if norm is not None else float("nan"),
             "advanced": result.advanced,
         }
@@ -275,6 +280,10 @@ class Trainer:
                                {f"train/{k}": c for k, c in counts.items()})  # fmt: skip
             if st.global_step % acc == 0:
                 result = self.engine.step_or_skip(st)
+                boundary = any(iv > 0 and st.effective_step % iv == 0 for iv in (cfg.checkpoint_interval, cfg.eval_interval))
+                if boundary or st.global_step % (cfg.log_interval * acc) == 0 or st.effective_step >= cfg.max_steps:
+                    # a decision that depends on the step number follows: settle the fused step's verdict first
+                    result = self.engine.resolve(st) or result
                 self.callbacks.fire("on_step_end" if result.advanced else "on_skip_step", self, result)
                 if result.advanced:
                     if result.grad_norm is not None:
@@ -299,6 +308,7 @@ class Trainer:
                 self._log(vals)
                 data_wait = 0.0
             stopped = shutdown.tick()
+        self.engine.resolve(st)
         self.callbacks.fire("on_train_end", self)
         if stopped and st.global_step % acc != 0:
             # shutdown inside an accumulation window: drop the partial gradients and go back to the last boundary, so the

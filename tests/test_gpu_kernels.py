@@ -123,14 +123,107 @@ def test_peer_flag_wait_runs_out_and_reports_status():
     native.require()
     n = 4096
     grads = [torch.randn(n, device=DEV), torch.randn(n, device=DEV)]
-    ctrls = [torch.zeros(128, device=DEV), torch.zeros(128, device=DEV)]
+    ctrls = [torch.zeros(256, device=DEV), torch.zeros(256, device=DEV)]
     ctrls[0][0] = 1.0
     ctrls[1][0] = 1.0
     scratch = torch.zeros(4, device=DEV)
     status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    before = grads[0].clone()
     norm = torch.ops.df3.peer_allreduce_mean(grads[0], [g.data_ptr() for g in grads], [c.data_ptr() for c in ctrls], scratch,
                                              status, 0, 2, 1, 20000)  # fmt: skip
     torch.cuda.synchronize()
     assert int(status.item()) == 4  # kTimeoutPeerFlag
     assert torch.isnan(norm)
+    assert torch.equal(grads[0], before)  # the entry wait ran out: no gradient was read or written
+    assert float((torch.ones(8, device=DEV) * 2).sum()) == 16.0  # the device still answers
+
+
+def _fused_step_setup(ema_decay=0.9, weight_decay=0.1):
+    from deepfold3_dev_b200.parallel.dist import DistInfo
+    from deepfold3_dev_b200.parallel.peer_reduce import PeerReducer
+    from deepfold3_dev_b200.training.flat_optimizer import FlatAdamW
+
+    def build(dev):
+        torch.manual_seed(5)
+        return torch.nn.Sequential(torch.nn.Linear(64, 200), torch.nn.LayerNorm(200), torch.nn.Linear(200, 33)).to(dev)
+
+    gpu, cpu = build(DEV), build("cpu")
+    og = FlatAdamW(gpu, lr=1e-2, weight_decay=weight_decay, ema_decay=ema_decay)
+    oc = FlatAdamW(cpu, lr=1e-2, weight_decay=weight_decay, ema_decay=ema_decay)
+    peer = PeerReducer(DistInfo(device=torch.device(DEV)), og)
+    return gpu, cpu, og, oc, peer
+
+
+def _launch_fused(og, peer, loss_flag=0.0, clip=0.0, thr=0.0):
+    step = og.step_count + 1
+    b1, b2 = og.param_groups[0]["betas"]
+    one = torch.ones((), device=DEV)
+    peer.fused_step(og, coef=one, loss_flag=torch.tensor(loss_flag, device=DEV), local_norm=torch.zeros((), device=DEV),
+                    lr=og.param_groups[0]["lr"], betas=(b1, b2), eps=og.param_groups[0]["eps"], bc1=1 - b1**step, bc2=1 - b2**step,
+                    ema=og.shadow, ema_w=1 - og.ema_decay, clip_norm=clip, skip_threshold=thr, per_rank_clip=False)  # fmt: skip
+    res = peer.read_result()
+    if res["advanced"]:
+        og.step_count = step
+    return res
+
+
+def test_fused_optimizer_step_matches_flat_adamw():
+    """One cooperative kernel (entry, reduce, norm, consensus, AdamW, EMA, bf16 mirror, gradient zeroing) on a world of
+    one against the CPU statement of clip + AdamW + EMA lerp, three steps."""
+    gpu, cpu, og, oc, peer = _fused_step_setup()
+    x = torch.randn(16, 64)
+    for _ in range(3):
+        cpu(x).pow(2).sum().backward()
+        og.flat_grad.copy_(oc.flat_grad)  # the same gradient bits on both sides: only the update is under test
+        norm = oc.grad_norm(True)
+        scale = min(1.0, 0.5 / (float(norm) + 1e-6))
+        res = _launch_fused(og, peer, clip=0.5)
+        assert res["advanced"] and res["reason"] is None
+        assert abs(res["norm"] - float(norm)) < 1e-4 * float(norm) and abs(res["scale"] - scale) < 1e-5
+        oc.step(grad_scale=scale)
+        oc.zero_grad()
+        assert float(og.flat_grad.abs().max()) == 0.0  # zeroed by the kernel for the next window
+    torch.testing.assert_close(og.flat_param.cpu(), oc.flat_param, atol=1e-6, rtol=1e-5)
+    torch.testing.assert_close(og.shadow.cpu(), oc.shadow, atol=1e-6, rtol=1e-5)
+    torch.testing.assert_close(og.exp_avg.cpu(), oc.exp_avg, atol=1e-7, rtol=1e-5)
+    torch.testing.assert_close(og.exp_avg_sq.cpu(), oc.exp_avg_sq, atol=1e-8, rtol=1e-5)
+    torch.testing.assert_close(og.flat_param_bf16.float().cpu(), oc.flat_param.bfloat16().float(), atol=1e-2, rtol=1e-2)
+    peer.check()
+
+
+@pytest.mark.parametrize("case", ["loss", "grad", "outlier"])
+def test_fused_optimizer_step_skips_on_device(case):
+    """The skip decision is taken inside the kernel: parameters, moments and EMA stay untouched, gradients are cleared."""
+    gpu, cpu, og, oc, peer = _fused_step_setup()
+    gpu(torch.randn(16, 64, device=DEV)).pow(2).sum().backward()
+    if case == "grad":
+        og.flat_grad[7] = float("nan")
+    before = [t.clone() for t in (og.flat_param, og.exp_avg, og.exp_avg_sq, og.shadow)]
+    res = _launch_fused(og, peer, loss_flag=1.0 if case == "loss" else 0.0, thr=1e-3 if case == "outlier" else 0.0)
+    assert not res["advanced"] and res["reason"] == ("loss" if case == "loss" else "grad")
+    for a, b in zip(before, (og.flat_param, og.exp_avg, og.exp_avg_sq, og.shadow)):
+        assert torch.equal(a, b)
+    assert float(og.flat_grad.nan_to_num().abs().max()) == 0.0
+
+
+def test_fused_step_entry_wait_runs_out_and_reports_status():
+    """Rank 0 of a world of two whose second rank never arrives: the entry wait ends after its poll limit, the kernel
+    records the status and leaves without reading or writing any gradient or parameter; the context stays usable."""
+    from deepfold3_dev_b200.ops import native
+
+    native.require()
+    n = 4096
+    grads = [torch.randn(n, device=DEV), torch.randn(n, device=DEV)]
+    ctrls = [torch.zeros(256, device=DEV), torch.zeros(256, device=DEV)]
+    p, m, v, ema, decay = (torch.randn(n, device=DEV) for _ in range(5))
+    before = [t.clone() for t in (grads[0], p, m, v, ema)]
+    scratch, status = torch.zeros(4, device=DEV), torch.zeros(1, dtype=torch.int32, device=DEV)
+    result = torch.full((36,), -1.0, device=DEV)
+    torch.ops.df3.peer_fused_step(grads[0], [g.data_ptr() for g in grads], [c.data_ptr() for c in ctrls], scratch, status, result,
+                                  p, m, v, ema, decay, None, 0, 2, 1, 1e-3, 0.9, 0.95, 1e-8, 0.1, 0.05, 0.001, 1.0, 0.0, False, 20000)  # fmt: skip
+    torch.cuda.synchronize()
+    assert int(status.item()) == 4  # kTimeoutPeerFlag
+    assert float(result[0]) == 0.0 and float(result[1]) == 3.0
+    for a, b in zip(before, (grads[0], p, m, v, ema)):
+        assert torch.equal(a, b)
     assert float((torch.ones(8, device=DEV) * 2).sum()) == 16.0  # the device still answers

@@ -23,3 +23,9 @@ def _run(scenario: str, nproc: int, port: int) -> str:
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
 def test_peer_memory_gradient_reduction_matches_nccl():
     assert "WORKER_OK peer_reduce" in _run("peer_reduce", 2, 29631)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_fused_optimizer_step_matches_nccl_and_torch_adamw():
+    out = _run("fused_step", 2, 29633)
+    assert "WORKER_OK fused_step" in out and out.count("FUSED_STEP ok") == 2

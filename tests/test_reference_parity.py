@@ -95,3 +95,29 @@ def test_training_loss_and_gradients_match(pair, chunk):
     for k, v in pa.items():
         assert abs(v - pb[k]) < 1e-4 * max(1.0, abs(v)), k
     assert (ga - gb).abs().max() < 1e-4 * ga.abs().max()
+
+
+@pytest.mark.parametrize("head_norm,router,kind", [("channel", True, "softmax"), ("head_rms", False, "softmax"), ("head_rms", True, "sigmoid"),
+                                                   ("head_ln", True, "softmax"), ("post_channel", True, "softmax")])  # fmt: skip
+def test_multi_head_triangle_multiply_matches(reference_package, head_norm, router, kind):
+    """Per-head normalisation and routing of the triangle multiply against the reference module, router statistics included."""
+    import deepfold3.model.ops as RO
+
+    from deepfold3_dev_b200.models import triangle as T
+
+    torch.manual_seed(1)
+    kw = dict(num_heads=4, head_norm=head_norm, router=router, router_kind=kind)
+    ref = RO.TriangleMulOutgoing(32, **kw)
+    wake_zero_init(ref)
+    mine = T.TriangleMulOutgoing(32, **kw)
+    mine.load_state_dict(ref.state_dict(), strict=True)
+    z, mask = torch.randn(1, 9, 9, 32), (torch.rand(1, 9, 9) > 0.2).float()
+    if router:
+        RO.set_router_stats_enabled(ref, True)
+        T.set_router_stats_enabled(mine, True)
+    torch.testing.assert_close(mine(z, mask), ref(z, mask), atol=1e-5, rtol=1e-4)
+    if router:
+        a, b = RO.collect_router_stats(ref), T.collect_router_stats(mine)
+        assert a.keys() == b.keys()
+        for k in a:
+            assert abs(a[k] - b[k]) < 1e-5 * max(1.0, abs(a[k])), k
