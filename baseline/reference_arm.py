@@ -3,10 +3,15 @@
 Only the reference's own code runs the model here: ``deepfold3.model.model.DeepFold3``,
 ``deepfold3.training.step.training_step``, ``wrap_ddp`` / ``build_optimizer`` / ``WrappedOptimizer``
 / ``EMA``. The package comes from ``baseline/_ref`` (a ``pip install --target`` of the reference
-plus its ``src/deepfold3`` tree, see DESIGN.md). Its data stack imports ``gemmi``, ``rdkit``,
+plus its ``src/deepfold3`` tree). Its data stack imports ``gemmi``, ``rdkit``,
 ``zstandard`` and ``pdbeccdutils`` at module import time; none is installable offline and none is
 called on the synthetic-feature path, so inert stand-in modules are registered for the missing ones
 before the import. The synthetic batch comes from this repository's generator (torch only).
+
+Memory policy: the reference is given its fastest setting that fits the GPU. It is tried without activation
+checkpointing and without diffusion chunking first (what this package's arm runs), then without checkpointing but
+with its production diffusion chunk of 8, then with its production recipe (checkpointing + chunk 8); an attempt that
+runs out of memory during warm-up is torn down and the next one is built. The JSON line says which one ran.
 """
 
 from __future__ import annotations
@@ -85,13 +90,24 @@ def run_reference(args, bench) -> None:
         info = init_process_group(timeout_s=1800.0)
         world = info.world_size
         seed_everything(bench.SEED, info.rank)
+        host_batch = bench.make_host_batch(info.rank, args.tokens)
+        dev_batch = {k: v.to(info.device) for k, v in host_batch.items()}
+        flush_buf = torch.zeros(64 * 1024 * 1024, device=info.device)
+    except Exception as exc:  # noqa: BLE001 - set-up of the reference's own stack failed: report, do not crash
+        if int(os.environ.get("RANK", "0")) == 0:
+            unavailable(f"reference set-up failed: {type(exc).__name__}: {exc}"[:300])
+        return
+    opt_mode = os.environ.get("DF3_REF_OPTIM", "train")
+
+    def build(checkpointing: bool, chunk: int):
+        """The reference's model / DDP / optimizer / EMA stack under one memory policy, and a step function over it."""
+        nonlocal opt_mode
         model_cfg = ModelConfig()
         model_cfg.msa_crop_size = bench.N_MSA
         if args.blocks:
             model_cfg.pairformer.num_layer = args.blocks
-        opt_mode = os.environ.get("DF3_REF_OPTIM", "train")
         o = model_cfg.optim
-        o.use_gradient_checkpointing = True
+        o.use_gradient_checkpointing = checkpointing
         if opt_mode == "train":  # the kernel flags of the reference's production recipe (configs/initial.yaml:396-418)
             try:
                 import triton  # noqa: F401
@@ -102,7 +118,6 @@ def run_reference(args, bench) -> None:
                 o.use_fused_transition_pair = True
             except ImportError:
                 opt_mode = "none (triton missing)"
-        chunk = int(os.environ.get("DF3_REF_DIFFUSION_CHUNK", "8"))
         train_cfg = TrainingConfig(**bench.shared_train_settings(args.tokens), diffusion_chunk_size=chunk,
                                    per_rank_grad_clip=False)  # fmt: skip
         model = DeepFold3(model_cfg).to(info.device)
@@ -116,28 +131,58 @@ def run_reference(args, bench) -> None:
         wrapped = WrappedOptimizer(optimizer=optimizer, scheduler=scheduler, scaler=scaler, model=model, dist_info=info,
                                    cfg=train_cfg)  # fmt: skip
         state = TrainState()
-        host_batch = bench.make_host_batch(info.rank, args.tokens)
-        dev_batch = {k: v.to(info.device) for k, v in host_batch.items()}
-        flush_buf = torch.zeros(64 * 1024 * 1024, device=info.device)
 
-    except Exception as exc:  # noqa: BLE001 - set-up of the reference's own stack failed: report, do not crash
-        if int(os.environ.get("RANK", "0")) == 0:
-            unavailable(f"reference set-up failed: {type(exc).__name__}: {exc}"[:300])
+        def one_step(i, features):
+            state.global_step = i
+            with torch.autocast("cuda", dtype=torch.bfloat16):
+                loss, *_ = training_step(ddp_model, features, cfg=train_cfg, model_cfg=model_cfg, global_step=i,
+                                         accumulator=accumulator, scaler=scaler, device=info.device)  # fmt: skip
+            wrapped.add_microstep_loss(loss)
+            with accumulator.step_context(is_sync_step=True):
+                if loss.requires_grad:
+                    scaled_backward(scaler, loss, 1)
+            result = wrapped.step_or_skip(state)
+            if result.advanced:
+                ema.update(model)
+            return loss
+
+        return one_step
+
+    ladder = [(False, 0), (False, 8), (True, 8)]
+    if os.environ.get("DF3_REF_POLICY") == "production":
+        ladder = [(True, 8)]
+    one_step, policy = None, None
+    for checkpointing, chunk in ladder:
+        fits = 1
+        try:
+            one_step = build(checkpointing, chunk)
+            for i in range(args.warmup):
+                one_step(i, dict(dev_batch))
+            torch.cuda.synchronize()
+        except torch.OutOfMemoryError:
+            fits = 0
+        except Exception as exc:  # noqa: BLE001
+            if info.rank == 0:
+                unavailable(f"reference step failed ({opt_mode}, checkpointing={checkpointing}, chunk={chunk}): "
+                            f"{type(exc).__name__}: {exc}"[:300])  # fmt: skip
+            return
+        if world > 1:  # every rank takes the same rung
+            flag = torch.tensor([fits], device=info.device)
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+            fits = int(flag.item())
+        if fits:
+            policy = (checkpointing, chunk)
+            break
+        one_step = None
+        import gc
+
+        gc.collect()
+        torch.cuda.empty_cache()
+        torch.cuda.reset_peak_memory_stats()
+    if policy is None:
+        if info.rank == 0:
+            unavailable("the reference ran out of memory under every memory policy, its production recipe included")
         return
-
-    def one_step(i, features):
-        state.global_step = i
-        with torch.autocast("cuda", dtype=torch.bfloat16):
-            loss, *_ = training_step(ddp_model, features, cfg=train_cfg, model_cfg=model_cfg, global_step=i,
-                                     accumulator=accumulator, scaler=scaler, device=info.device)  # fmt: skip
-        wrapped.add_microstep_loss(loss)
-        with accumulator.step_context(is_sync_step=True):
-            if loss.requires_grad:
-                scaled_backward(scaler, loss, 1)
-        result = wrapped.step_or_skip(state)
-        if result.advanced:
-            ema.update(model)
-        return loss
 
     def device_step(i):
         one_step(i, dict(dev_batch))
@@ -151,9 +196,6 @@ def run_reference(args, bench) -> None:
             dist.barrier()
 
     try:
-        for i in range(args.warmup):
-            device_step(i)
-        torch.cuda.synchronize()
         sampler = bench.ClockSampler(info.local_rank)
         sampler.start()
         times = bench.timed_loop(device_step, args.steps, args.warmup, sync, flush_buf)
@@ -168,7 +210,8 @@ def run_reference(args, bench) -> None:
     peak = torch.cuda.max_memory_allocated() / 2**30
     if info.rank == 0:
         bench.emit(args, "reference", step_ms, e2e_ms, clocks, 0, bench.batch_bytes(host_batch),
-                   {"reference_optim": opt_mode, "activation_checkpointing": True, "diffusion_chunk": chunk,
+                   {"reference_optim": opt_mode, "activation_checkpointing": policy[0], "diffusion_checkpointing": policy[0],
+                    "diffusion_chunk": policy[1],
                     "stubbed_imports": stubbed, "peak_mem_gib": round(peak, 1),
                     "recycles": [bench.recycles_for(args.warmup + i) for i in range(args.steps)]})  # fmt: skip
     if world > 1:

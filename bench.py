@@ -200,6 +200,13 @@ def shared_train_settings(tokens: int) -> dict:
     )  # fmt: skip
 
 
+def _graph_state(model) -> str:
+    cache = model.__dict__.get("_trunk_train_graphs")
+    if cache is None:
+        return "off"
+    return "failed, ran eagerly" if cache.failed else "forward + backward replayed from CUDA graphs"
+
+
 def run_ours(args):
     import torch
 
@@ -256,6 +263,8 @@ def run_ours(args):
              {"activation_checkpointing": model_cfg.optim.use_gradient_checkpointing,
               "diffusion_checkpointing": os.environ.get("DF3_DIFFUSION_CKPT") != "0", "diffusion_chunk": chunk,
               "grad_transport": trainer.grad_sync.transport if world > 1 else "none",
+              "optimizer_step": "one fused kernel" if trainer.grad_sync.fused_step_engine(trainer.optimizer) is not None else "classic",
+              "trunk_graphs": _graph_state(trainer.model),
               "peak_mem_gib": round(peak, 1), "recycles": [recycles_for(args.warmup + i) for i in range(args.steps)]})  # fmt: skip
     if world > 1:
         import torch.distributed as dist

@@ -4,18 +4,15 @@
 five little-endian int32 (scope length, name length, dtype length, rank, payload bytes) followed by the
 scope, the name, the dtype string, the shape and the raw array; bfloat16 is widened to float32.
 
-``convert_file`` turns the nested ``{scope: {name: array}}`` into this package's state dict through a
-name map: a JSON list of rules ``{"scope": regex, "name": regex, "key": template, "transpose": bool,
-"stack_axis": int | null}``. Layer-stacked arrays (haiku ``layer_stack``) are split along ``stack_axis``
-and ``{layer}`` in the template is replaced by the index; regex groups are available as ``{1}``, ``{2}``.
-The map for the published AF3 checkpoint is data, not code; it is not bundled here because it cannot be
-validated without the checkpoint. Compressed files need the ``zstandard`` package.
+``haiku_to_torch`` turns the nested ``{scope: {name: array}}`` into this package's state dict and
+``torch_to_haiku`` goes back. Both are driven by one table (``convert/af3_name_map.py``): which Haiku scope
+is which module, what kind of arrays it holds (a linear layer stored input-major or output-major, a layer
+norm, a bare gain, ...) and how many leading axes are layer stacks. Compressed files need the
+``zstandard`` package.
 """
 
 from __future__ import annotations
 
-import json
-import re
 import struct
 import sys
 
@@ -69,37 +66,21 @@ def read_af3_params(path: str) -> dict[str, dict[str, np.ndarray]]:
     return params
 
 
-def apply_name_map(params: dict, rules: list[dict]) -> dict[str, torch.Tensor]:
-    compiled = [(re.compile(r["scope"]), re.compile(r.get("name", ".*")), r) for r in rules]
-    out: dict[str, torch.Tensor] = {}
-    unmatched = []
-    for scope, entries in params.items():
-        for name, arr in entries.items():
-            for sre, nre, rule in compiled:
-                ms, mn = sre.fullmatch(scope), nre.fullmatch(name)
-                if not (ms and mn):
-                    continue
-                groups = (None,) + ms.groups() + mn.groups()  # "{1}" is the first regex group
-                t = torch.from_numpy(np.array(arr, copy=True)).float()
-                axis = rule.get("stack_axis")
-                pieces = [(None, t)] if axis is None else list(enumerate(t.unbind(axis)))
-                for layer, piece in pieces:
-                    if rule.get("transpose"):
-                        piece = piece.transpose(-1, -2)
-                    key = rule["key"].format(*groups, layer=layer)
-                    out[key] = piece.contiguous()
-                break
-            else:
-                unmatched.append(f"{scope}/{name}")
-    if unmatched:
-        raise KeyError(f"{len(unmatched)} arrays match no rule of the name map (first: {unmatched[:5]})")
-    return out
+def haiku_to_torch(params: dict) -> dict[str, torch.Tensor]:
+    """State dict from AF3's ``{scope: {name: array}}``; scopes the table does not know are reported with a warning."""
+    from .af3_name_map import haiku_to_torch as convert
+
+    return convert(params)
+
+
+def torch_to_haiku(state_dict: dict) -> dict:
+    """The inverse: AF3-layout ``{scope: {name: array}}`` (layers re-stacked) from a state dict of this model."""
+    from .af3_name_map import torch_to_haiku as convert
+
+    return convert(state_dict)
 
 
 def convert_file(path: str, name_map: str | None = None) -> dict[str, torch.Tensor]:
-    params = read_af3_params(path)
-    if name_map is None:
-        raise RuntimeError("AF3 conversion needs a name map (JSON rules from haiku scopes to state-dict keys): "
-                           "convert_file(path, name_map='af3_name_map.json')")  # fmt: skip
-    with open(name_map) as f:
-        return apply_name_map(params, json.load(f))
+    """``af3.bin`` / ``af3.bin.zst`` -> state dict. ``name_map`` is accepted for older call sites and ignored: the table
+    ships with the package."""
+    return haiku_to_torch(read_af3_params(path))

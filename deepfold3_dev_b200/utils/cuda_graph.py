@@ -284,8 +284,12 @@ class TrainGraphCache:
     def run(self, fn, inputs: dict, params, mode=None):
         if self.failed:
             return fn(**inputs)
+        # shapes, not dtypes: replay copies the inputs into the captured placeholders, which converts (the recycling
+        # inputs arrive as fp32 zeros on a step without recycles and as bf16 activations otherwise)
+        shapes = tuple((k, tuple(v.shape)) if isinstance(v, torch.Tensor) else (k, v if isinstance(v, (int, float, bool, str, type(None))) else type(v).__name__)
+                       for k, v in sorted(inputs.items()))  # fmt: skip
         key = (mode, torch.is_autocast_enabled("cuda"), tuple(sorted(k for k, v in inputs.items() if isinstance(v, torch.Tensor) and v.requires_grad)),
-               tree_signature(inputs))  # fmt: skip
+               shapes)  # fmt: skip
         g = self._graphs.get(key)
         if g is not None and g.stale():
             del self._graphs[key]
