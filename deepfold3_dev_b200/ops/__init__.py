@@ -202,12 +202,12 @@ def sigmoid_gate_mul(x, w, other):
 
 
 def head_bias_planes(x, w):
-    """Per-head additive attention bias ``[B, H, N, N]`` from the pair rows ``x [B, N, N, C]``, ``w [H, C]``."""
+    """Per-head additive attention bias ``[B, H, R, N]`` from the pair rows ``x [B, R, N, C]``, ``w [H, C]``."""
     nat = fused(x, "linear_planes")
     if nat is not None and nat.gemm_supported(x, w):
         _CENSUS["head_bias_planes:sm100"] += 1
-        B, N = x.shape[0], x.shape[1]
-        return nat.linear_planes(x, w).view(w.shape[0], B, N, N).transpose(0, 1)
+        B, R, N = x.shape[0], x.shape[1], x.shape[2]
+        return nat.linear_planes(x, w).view(w.shape[0], B, R, N).transpose(0, 1)
     _CENSUS["head_bias_planes:torch"] += 1
     return torch.nn.functional.linear(x, w).permute(0, 3, 1, 2)
 
@@ -234,10 +234,23 @@ def linear(x, w, b=None):
 
 
 def outer_product_mean(a, b, out_w, out_b, mask, eps: float = 1e-3, mask_i=None, mask_j=None):
+    """MSA outer-product mean. bf16 CUDA inputs with 8-aligned extents run as tensor-core products on the own GEMM
+    kernel (contraction over MSA rows, then the projection), blocked over tokens; everything else takes the fp32
+    statement."""
+    nat = fused(a, "matmul")
+    if (nat is not None and mask_i is None and mask_j is None and mask is not None and a.shape[1] % 8 == 0
+            and (a.shape[2] * a.shape[3]) % 8 == 0 and out_w.shape[-1] % 8 == 0):
+        _CENSUS["outer_product_mean:sm100"] += 1
+        return nat.outer_product_mean(a, b, out_w, out_b, mask, eps)
     _CENSUS["outer_product_mean:torch"] += 1
     return ref.outer_product_mean(a, b, out_w, out_b, mask, eps, mask_i, mask_j)
 
 
 def msa_weighted_average(w, v):
+    """Pair-weighted average over keys for every MSA row: on the GPU one batched tensor-core product per head."""
+    nat = fused(v, "matmul")
+    if nat is not None and v.shape[2] % 8 == 0 and (v.shape[1] * v.shape[4]) % 8 == 0:
+        _CENSUS["msa_weighted_average:sm100"] += 1
+        return nat.msa_weighted_average(w, v)
     _CENSUS["msa_weighted_average:torch"] += 1
     return ref.msa_weighted_average(w, v)

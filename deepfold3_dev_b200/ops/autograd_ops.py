@@ -518,6 +518,70 @@ def transition(x, ln_w, ln_b, w1, w2, eps: float = 1e-5):
     return _Transition.apply(x, ln_w, ln_b, w1, w2, eps)
 
 
+class _MatMul(torch.autograd.Function):
+    """Differentiable ``op(a) @ op(b)`` on the tcgen05 kernel (2-D or batched 3-D bf16 operands). An operand flagged
+    ``trans`` is handed over as stored, ``[.., K, M]`` / ``[.., N, K]``; neither the forward nor the two backward
+    products copy or transpose anything: a transposed operand is simply read MN-major by the tensor cores."""
+
+    @staticmethod
+    def forward(ctx, a, b, trans_a, trans_b):
+        ctx.save_for_backward(a, b)
+        ctx.flags = (trans_a, trans_b)
+        return mm(a, b, trans_a, trans_b)
+
+    @staticmethod
+    def backward(ctx, dc):
+        a, b = ctx.saved_tensors
+        ta, tb = ctx.flags
+        d = (dc if dc.dtype == BF16 else dc.to(BF16)).contiguous()
+        da = db = None
+        if ctx.needs_input_grad[0]:
+            da = mm(b, d, tb, True) if ta else mm(d, b, False, not tb)
+        if ctx.needs_input_grad[1]:
+            db = mm(d, a, True, ta) if tb else mm(a, d, not ta, False)
+        return da, db, None, None
+
+
+def matmul(a, b, trans_a: bool = False, trans_b: bool = False):
+    """Differentiable product on the own GEMM kernel; see ``_MatMul``."""
+    return _MatMul.apply(a, b, bool(trans_a), bool(trans_b))
+
+
+def msa_weighted_average(w, v):
+    """``out[b,s,q,h,:] = sum_k w[b,h,q,k] v[b,s,k,h,:]``: one [N, N] x [N, S * d] product per (batch, head), the pair
+    weights shared by all MSA rows (reference: model/attention.py:272-341)."""
+    B, S, N, H, D = v.shape
+    vp = v.permute(0, 3, 2, 1, 4).reshape(B * H, N, S * D)  # keys as rows, (row, channel) as columns
+    out = matmul(w.reshape(B * H, N, N).to(BF16), vp.to(BF16))
+    return out.view(B, H, N, S, D).permute(0, 3, 2, 1, 4)
+
+
+def outer_product_mean(a, b, out_w, out_b, mask, eps: float = 1e-3, row_chunk: int = 96):
+    """``(sum_s a[s,i,:] (x) b[s,j,:]) . out_w + out_b`` over valid rows, as two tensor-core products per block of
+    ``row_chunk`` tokens i: first the [chunk * E, S] x [S, N * E] contraction over the MSA rows, then, after bringing the
+    two feature axes together, the [chunk * N, E * E] x [E * E, C] projection. The full ``[N, N, E, E]`` outer product
+    never exists at once (reference: model/ops.py:683-785, tiled form model/tiled_linear.py:67-88)."""
+    B, S, N, E = a.shape
+    C = out_w.shape[-1]
+    w2 = out_w.reshape(E * E, C).to(BF16)  # a differentiable cast: the projection weight trains through it
+    a16, b16 = a.to(BF16), b.to(BF16)
+    m16 = mask.to(BF16)
+    outs = []
+    for bi in range(B):
+        bm = b16[bi].reshape(S, N * E)
+        count = mm(m16[bi], m16[bi], True, False, True)  # [N, N] valid rows per pair, exact in fp32
+        rows = []
+        for i0 in range(0, N, row_chunk):
+            i1 = min(N, i0 + row_chunk)
+            am = a16[bi, :, i0:i1].reshape(S, (i1 - i0) * E)
+            ab = matmul(am, bm, True, False)  # [(i, e), (j, f)]
+            ab = ab.view(i1 - i0, E, N, E).permute(0, 2, 1, 3).reshape((i1 - i0) * N, E * E)
+            rows.append(matmul(ab, w2).view(i1 - i0, N, C))
+        act = torch.cat(rows, 0) + out_b.to(BF16)
+        outs.append(act / (eps + count).unsqueeze(-1).to(act.dtype))
+    return torch.stack(outs, 0)
+
+
 class _PlaneContract(torch.autograd.Function):
     """Triangle contraction on channel-major planes ``[2, P, N, N]`` (a = planes[0], b = planes[1], P = channels x
     batch): outgoing ``act[p] = a[p] b[p]^T``, incoming ``act[p] = b[p]^T a[p]``. Forward and both operand gradients

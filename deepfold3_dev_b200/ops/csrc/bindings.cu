@@ -26,6 +26,7 @@ void df3_register_gemm(torch::Library& m);
 const char* df3_gemm_features();
 void df3_register_attention(torch::Library& m);
 void df3_register_peer(torch::Library& m);
+void df3_register_peer_exchange(torch::Library& m);
 #endif
 
 static std::string df3_features() {
@@ -58,5 +59,6 @@ TORCH_LIBRARY(df3, m) {
   df3_register_gemm(m);
   df3_register_attention(m);
   df3_register_peer(m);
+  df3_register_peer_exchange(m);
 #endif
 }

@@ -3,7 +3,7 @@
 //   C[b, m, n] = epilogue( sum_k A[b, m, k] * W[b or 0, n, k] )
 //
 // One CTA computes a 128 x BN tile. Warp 0 is the TMA producer (cp.async.bulk.tensor into 128-byte
-// swizzled shared memory, no cluster multicast), warp 1 allocates tensor memory and issues
+// swizzled shared memory, each copy for this CTA alone), warp 1 allocates tensor memory and issues
 // tcgen05.mma from one elected thread, warps 2-5 read the fp32 accumulator back with tcgen05.ld and
 // run the epilogue. Stages are handed over with mbarriers; every wait is bounded and reports through
 // a status word (df3::Status) instead of hanging.
@@ -903,5 +903,5 @@ void df3_register_gemm(torch::Library& m) {
 }
 
 const char* df3_gemm_features() {
-  return "gemm,matmul,gated_dual_linear,transition,pair_bias_attention,linear_planes,sigmoid_gate_mul,peer_reduce";
+  return "gemm,matmul,gated_dual_linear,transition,pair_bias_attention,linear_planes,sigmoid_gate_mul,peer_reduce,peer_exchange";
 }

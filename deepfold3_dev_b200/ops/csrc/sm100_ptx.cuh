@@ -1,5 +1,5 @@
-// Inline-PTX wrappers for the Blackwell (sm_100a) data path: mbarrier, TMA (cp.async.bulk.tensor,
-// never with cluster multicast), tcgen05 MMA / TMEM allocation / TMEM loads, and the shared-memory
+// Inline-PTX wrappers for the Blackwell (sm_100a) data path: mbarrier, TMA (cp.async.bulk.tensor, every
+// copy addressed to the issuing CTA alone), tcgen05 MMA / TMEM allocation / TMEM loads, and the shared-memory
 // and instruction descriptors of tcgen05.mma.
 //
 // Every wait is bounded: it polls up to a limit, then records a df3::Status code in the kernel's

@@ -18,7 +18,7 @@ loads and stores and no NCCL call:
     (reference sequence being replaced: training/optim.py:576-765, training/ema.py:77-90).
 
 No wait in these kernels is unbounded and none traps: a wait that runs out records a status code, the kernels leave
-peer memory alone and the step counts as skipped. NVLS multicast is not used, so a rank that left between steps
+peer memory alone and the step counts as skipped. NVLS is not used, so a rank that left between steps
 cannot fault the others.
 """
 

@@ -142,11 +142,135 @@ def peer_bench(info):
             print(f"PEER_BENCH world={w} {k}: {ms:.3f} ms  bus bandwidth {2 * (w - 1) / w * gb / ms * 1e3:.0f} GB/s", flush=True)
 
 
+def _pairformer_blocks(device, count, seed=5):
+    from deepfold3_dev_b200.models.evoformer import PairFormerBlock
+    from tests.helpers import wake_zero_init
+
+    torch.manual_seed(seed)
+    blocks = torch.nn.ModuleList(PairFormerBlock(128, 384) for _ in range(count)).eval()
+    wake_zero_init(blocks)
+    return blocks.to(device)
+
+
+def axial_exchange(info):
+    """Every re-layout on the peer-memory kernels equals its statement with NCCL collectives, bit for bit, over several
+    calls (the receive heap is reused and grows)."""
+    from deepfold3_dev_b200.parallel.axial import AxialComm
+
+    peer, coll = AxialComm(info, "peer"), AxialComm(info, "collective")
+    P, dev = info.world_size, info.device
+    g = torch.Generator(device=dev).manual_seed(11 + info.rank)
+    for n in (8, 32, 96):
+        N = n * P
+        z = torch.randn(2, n, N, 128, device=dev, generator=g).bfloat16()
+        torch.testing.assert_close(peer.transpose(z), coll.transpose(z), atol=0, rtol=0)
+        torch.testing.assert_close(peer.transpose(peer.transpose(z)), z, atol=0, rtol=0)
+        planes = torch.randn(2, 16 * P, 2, n, N, device=dev, generator=g).bfloat16()
+        mine = peer.rows_to_channels(planes)
+        torch.testing.assert_close(mine, coll.rows_to_channels(planes), atol=0, rtol=0)
+        back = peer.channels_to_rows(mine[0])
+        torch.testing.assert_close(back, coll.channels_to_rows(mine[0]), atol=0, rtol=0)
+        torch.testing.assert_close(back, planes[0], atol=0, rtol=0)
+        bias = torch.randn(2, 4, n, N, device=dev, generator=g)
+        torch.testing.assert_close(peer.all_gather(bias, 2), coll.all_gather(bias, 2), atol=0, rtol=0)
+    peer.check()
+    if info.rank == 0:
+        print("AXIAL_EXCHANGE ok bootstrap=%s heap=%d MiB" % (peer.peer().bootstrap, peer.peer().heap_bytes >> 20), flush=True)
+
+
+def axial_block(info):
+    """Two Pairformer blocks at full width on row shards (bf16, own kernels, peer transport) against the same blocks
+    unsharded on one GPU."""
+    from deepfold3_dev_b200.parallel.axial import AxialComm, sharded_pairformer_stack
+
+    dev, P = info.device, info.world_size
+    blocks = _pairformer_blocks(dev, 2)
+    B, N = 1, 256
+    torch.manual_seed(3)
+    pair, single = torch.randn(B, N, N, 128, device=dev), torch.randn(B, N, 384, device=dev)
+    seq_mask = torch.ones(B, N, device=dev)
+    seq_mask[0, -5:] = 0
+    pair_mask = seq_mask[:, :, None] * seq_mask[:, None, :]
+    with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
+        want_pair, want_single = pair.bfloat16(), single.bfloat16()
+        for blk in blocks:
+            want_pair, want_single = blk(want_pair, want_single, pair_mask, seq_mask)
+        results = {}
+        for transport in ("peer", "collective"):
+            comm = AxialComm(info, transport)
+            results[transport] = sharded_pairformer_stack(blocks, pair.bfloat16(), single.bfloat16(), pair_mask, seq_mask, comm)
+            comm.check()
+    for transport, (got_pair, got_single) in results.items():
+        for got, want, what in ((got_pair, want_pair, "pair"), (got_single, want_single, "single")):
+            err = (got.float() - want.float()).pow(2).mean().sqrt() / want.float().pow(2).mean().sqrt()
+            assert float(err) < 1e-2, (transport, what, float(err))
+    torch.testing.assert_close(results["peer"][0], results["collective"][0], atol=0, rtol=0)
+    if info.rank == 0:
+        print("AXIAL_BLOCK ok world=%d" % P, flush=True)
+
+
+def axial_bench(info):
+    """Device time per Pairformer block at a long token count: row-sharded over all ranks (peer kernels, NCCL) and, on
+    rank 0 alone, unsharded. Token count from DF3_AXIAL_TOKENS (default 3072)."""
+    from deepfold3_dev_b200.parallel.axial import AxialComm, sharded_pairformer_block
+
+    dev, P = info.device, info.world_size
+    N = int(os.environ.get("DF3_AXIAL_TOKENS", "3072"))
+    blocks = _pairformer_blocks(dev, 2)
+    torch.manual_seed(3)
+    single = torch.randn(1, N, 384, device=dev).bfloat16()
+    seq_mask = torch.ones(1, N, device=dev)
+    pair_mask = torch.ones(1, N, N, device=dev)
+    rows = torch.randn(1, N // P, N, 128, device=dev).bfloat16()
+    out = {}
+    with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
+        for transport in ("peer", "collective"):
+            comm = AxialComm(info, transport)
+            times = []
+            for it in range(5):
+                dist.barrier()
+                torch.cuda.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                z, s = rows, single
+                for blk in blocks:
+                    z, s = sharded_pairformer_block(blk, z, s, pair_mask, seq_mask, comm)
+                e1.record()
+                e1.synchronize()
+                if it >= 2:
+                    times.append(e0.elapsed_time(e1) / len(blocks))
+            comm.check()
+            t = torch.tensor([sum(times) / len(times)], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            out[transport] = float(t.item())
+            del z, s
+        torch.cuda.empty_cache()
+        if info.rank == 0 and os.environ.get("DF3_AXIAL_SINGLE", "1") != "0":
+            full = torch.randn(1, N, N, 128, device=dev).bfloat16()
+            times = []
+            for it in range(3):
+                torch.cuda.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                z, s = full, single
+                for blk in blocks:
+                    z, s = blk(z, s, pair_mask, seq_mask)
+                e1.record()
+                e1.synchronize()
+                if it >= 1:
+                    times.append(e0.elapsed_time(e1) / len(blocks))
+            out["one_gpu"] = sum(times) / len(times)
+    if info.rank == 0:
+        print("AXIAL_BENCH tokens=%d world=%d ms_per_block %s peak_gib=%.1f" % (
+            N, P, " ".join(f"{k}={v:.2f}" for k, v in out.items()), torch.cuda.max_memory_allocated() / 2**30), flush=True)
+
+
 def main():
     from deepfold3_dev_b200.parallel.dist import init_process_group
 
     info = init_process_group(timeout_s=120.0)
-    {"peer_reduce": peer_reduce, "peer_bench": peer_bench, "fused_step": fused_step}[sys.argv[1]](info)
+    {"peer_reduce": peer_reduce, "peer_bench": peer_bench, "fused_step": fused_step, "axial_exchange": axial_exchange,
+     "axial_block": axial_block, "axial_bench": axial_bench}[sys.argv[1]](info)
     dist.barrier()
     if info.rank == 0:
         print("WORKER_OK", sys.argv[1], flush=True)

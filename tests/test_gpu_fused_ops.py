@@ -138,3 +138,39 @@ def test_plane_layer_norm(nat, C, M):
     w, b = _leaf(C, seed=41), _leaf(C, seed=42, scale=0.1)
     _compare(lambda x, w, b: nat.plane_layer_norm(x, w, b, 1e-5),
              lambda x, w, b: F.layer_norm(x.float().t(), (C,), w, b), [x, w, b], tol=3e-2)
+
+
+@pytest.mark.parametrize("ta,tb", [(False, False), (False, True), (True, False), (True, True)])
+def test_differentiable_matmul_layouts(nat, ta, tb):
+    B, M, N, K = 3, 136, 72, 200
+    a = _leaf(B, K, M, seed=11, scale=0.2) if ta else _leaf(B, M, K, seed=11, scale=0.2)
+    b = _leaf(B, N, K, seed=12, scale=0.2) if tb else _leaf(B, K, N, seed=12, scale=0.2)
+
+    def eager(a, b):
+        A = a.bfloat16().float()
+        Bm = b.bfloat16().float()
+        return (A.transpose(1, 2) if ta else A) @ (Bm.transpose(1, 2) if tb else Bm)
+
+    _compare(lambda a, b: nat.matmul(a.bfloat16(), b.bfloat16(), ta, tb), eager, [a, b])
+
+
+def test_msa_weighted_average_and_outer_product_mean(nat):
+    from deepfold3_dev_b200 import ops
+    from deepfold3_dev_b200.ops import reference as ref
+
+    B, S, N, H, D = 1, 40, 72, 8, 8
+    w = torch.softmax(_leaf(B, H, N, N, seed=21).detach(), -1).requires_grad_(True)
+    v = _leaf(B, S, N, H, D, seed=22)
+    _compare(lambda w, v: ops.msa_weighted_average(w.bfloat16(), v.bfloat16()),
+             lambda w, v: ref.msa_weighted_average(w.bfloat16().float(), v.bfloat16().float()), [w, v])
+    E, C = 32, 128
+    a, b = _leaf(B, S, N, E, seed=23, scale=0.5), _leaf(B, S, N, E, seed=24, scale=0.5)
+    out_w, out_b = _leaf(E, E, C, seed=25, scale=0.05), _leaf(C, seed=26)
+    mask = (torch.rand(B, S, N, device="cuda") > 0.2).float()
+    ops.census(reset=True)
+    _compare(lambda a, b, ow, ob: ops.outer_product_mean((a * mask[..., None]).bfloat16(), (b * mask[..., None]).bfloat16(), ow, ob, mask),
+             lambda a, b, ow, ob: ref.outer_product_mean((a * mask[..., None]).bfloat16().float(), (b * mask[..., None]).bfloat16().float(),
+                                                         ow.bfloat16().float(), ob, mask), [a, b, out_w, out_b], tol=4e-2)
+    c = ops.census()
+    assert c.get("outer_product_mean:sm100", 0) == 1 and c.get("msa_weighted_average:sm100", 0) == 0  # census was reset in between
+    assert torch.ops.df3.gemm_status() == 0

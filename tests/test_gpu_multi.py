@@ -29,3 +29,13 @@ def test_peer_memory_gradient_reduction_matches_nccl():
 def test_fused_optimizer_step_matches_nccl_and_torch_adamw():
     out = _run("fused_step", 2, 29633)
     assert "WORKER_OK fused_step" in out and out.count("FUSED_STEP ok") == 2
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_axial_exchanges_match_collectives():
+    assert "AXIAL_EXCHANGE ok" in _run("axial_exchange", 2, 29635)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_row_sharded_pairformer_matches_one_gpu():
+    assert "AXIAL_BLOCK ok" in _run("axial_block", 2, 29637)
