@@ -90,7 +90,7 @@ def run_reference(args, bench) -> None:
         info = init_process_group(timeout_s=1800.0)
         world = info.world_size
         seed_everything(bench.SEED, info.rank)
-        host_batch = bench.make_host_batch(info.rank, args.tokens)
+        host_batch = bench.make_host_batch(info.rank, args.tokens, args.cfg["chains"])
         dev_batch = {k: v.to(info.device) for k, v in host_batch.items()}
         flush_buf = torch.zeros(64 * 1024 * 1024, device=info.device)
     except Exception as exc:  # noqa: BLE001 - set-up of the reference's own stack failed: report, do not crash
@@ -149,7 +149,7 @@ def run_reference(args, bench) -> None:
         return one_step
 
     ladder = [(False, 0), (False, 8), (True, 8)]
-    if os.environ.get("DF3_REF_POLICY") == "production":
+    if args.cfg.get("checkpointing") or os.environ.get("DF3_REF_POLICY") == "production":
         ladder = [(True, 8)]
     one_step, policy = None, None
     for checkpointing, chunk in ladder:
@@ -214,6 +214,98 @@ def run_reference(args, bench) -> None:
                     "diffusion_chunk": policy[1],
                     "stubbed_imports": stubbed, "peak_mem_gib": round(peak, 1),
                     "recycles": [bench.recycles_for(args.warmup + i) for i in range(args.steps)]})  # fmt: skip
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def run_reference_inference(args, bench) -> None:
+    """The inference configs on the reference: its ``DeepFold3`` with its own ``OptimConfig.inference()`` preset (row
+    chunking, tiled outer-product mean, its Triton kernels where importable). On several GPUs every process runs the whole
+    trunk and its share of the samples, which is how the reference spreads work over GPUs (independent processes)."""
+    if not os.path.isdir(os.path.join(REF_PATH, "deepfold3", "model")):
+        return unavailable("baseline/_ref does not hold the reference package (offline install missing)")
+    sys.path.insert(0, REF_PATH)
+    stubbed = _stub_missing()
+    try:
+        import torch
+        import torch.distributed as dist
+        from deepfold3.model.config import ModelConfig, OptimConfig
+        from deepfold3.model.model import DeepFold3
+        from deepfold3.training.distributed import init_process_group
+    except Exception as exc:  # noqa: BLE001
+        return unavailable(f"reference import failed: {type(exc).__name__}: {exc}"[:300])
+    if not torch.cuda.is_available():
+        return unavailable("no CUDA device")
+    c = args.cfg
+    if args.recycles >= 0:
+        c["recycles"] = args.recycles
+    if args.sampler_steps:
+        c["sampler_steps"] = args.sampler_steps
+    try:
+        info = init_process_group(timeout_s=1800.0)
+        world = info.world_size
+        cfg = ModelConfig()
+        cfg.optim = OptimConfig.inference()
+        cfg.msa_crop_size = bench.N_MSA
+        cfg.diffusion.steps = c["sampler_steps"]
+        cfg.diffusion.num_samples = c["samples"]
+        if args.blocks:
+            cfg.pairformer.num_layer = args.blocks
+        torch.manual_seed(0)
+        model = DeepFold3(cfg).to(info.device).eval()
+        host = bench.inference_features(args)
+        dev = {k: (v.to(info.device) if isinstance(v, torch.Tensor) else v) for k, v in host.items()}
+        flush_buf = torch.zeros(64 * 1024 * 1024, device=info.device)
+    except Exception as exc:  # noqa: BLE001
+        if int(os.environ.get("RANK", "0")) == 0:
+            unavailable(f"reference set-up failed: {type(exc).__name__}: {exc}"[:300])
+        return
+    share = len(range(info.rank, c["samples"], world))
+    d2h = [0]
+
+    def run(feats, seed, read):
+        if share == 0:
+            return
+        feats = {k: (v.to(info.device, non_blocking=True) if isinstance(v, torch.Tensor) else v) for k, v in feats.items()}
+        with torch.inference_mode(), torch.autocast("cuda", dtype=torch.bfloat16):
+            out = model(feats, seed=seed * world + info.rank, num_recycles=c["recycles"], num_samples=share)
+        if read:
+            got = [t.to("cpu", non_blocking=True) for t in (out.atom_positions, out.plddt, out.pae, out.pde)]
+            torch.cuda.synchronize()
+            d2h[0] = sum(t.numel() * t.element_size() for t in got)
+
+    def sync():
+        if world > 1:
+            dist.barrier()
+
+    try:
+        for i in range(args.warmup):
+            run(dev, i, False)
+        torch.cuda.synchronize()
+        torch.cuda.reset_peak_memory_stats()
+        sampler = bench.ClockSampler(info.local_rank)
+        sampler.start()
+        times = bench.timed_loop(lambda i: run(dev, i, False), args.steps, args.warmup, sync, flush_buf)
+        clocks = sampler.stop()
+        e2e_times = bench.timed_loop(lambda i: run(host, i, True), args.steps, args.warmup, sync, flush_buf)
+    except torch.OutOfMemoryError:
+        if info.rank == 0:
+            unavailable("reference did not complete: out of memory on one B200 with its inference preset")
+        return
+    except Exception as exc:  # noqa: BLE001
+        if info.rank == 0:
+            unavailable(f"reference prediction failed: {type(exc).__name__}: {exc}"[:300])
+        return
+    step_ms = bench.reduce_max(sum(times) / len(times), world)
+    e2e_ms = bench.reduce_max(sum(e2e_times) / len(e2e_times), world)
+    bytes_out = int(bench.reduce_max(float(d2h[0]), world))
+    peak = torch.cuda.max_memory_allocated() / 2**30
+    if info.rank == 0:
+        bench.emit_inference(args, "reference", step_ms, e2e_ms, clocks, 0, bench.batch_bytes(host), bytes_out,
+                             {"parallelism": f"{world} independent processes, samples dealt out" if world > 1 else "1 GPU",
+                              "reference_optim": "OptimConfig.inference()", "stubbed_imports": stubbed,
+                              "peak_mem_gib": round(peak, 1)})  # fmt: skip
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

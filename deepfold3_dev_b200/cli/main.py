@@ -293,7 +293,19 @@ def inference(msa, json_path, sequence, mol_type, output, templates_path, pdb_mm
     from ..data.inference_input import InferenceInput
     from ..inference.runner import run_job
 
+    dist_info = None
+    if int(os.environ.get("WORLD_SIZE", "1")) > 1:
+        # launched with one process per GPU: every prediction is spread over the GPUs (row-sharded trunk, samples dealt out)
+        from ..parallel.dist import init_process_group
+
+        dist_info = init_process_group(timeout_s=1800.0)
+        device = str(dist_info.device)
     model, cfg, device = _prepare_model(params, device, optim, snapshot, allow_missing_keys, det, ccd)
+    if dist_info is not None:
+        import torch.distributed as dist
+
+        for tensor in list(model.parameters()) + list(model.buffers()):
+            dist.broadcast(tensor.data, 0)
     if matmul_precision:
         torch.set_float32_matmul_precision(matmul_precision)
     if json_path:
@@ -315,7 +327,10 @@ def inference(msa, json_path, sequence, mol_type, output, templates_path, pdb_mm
                                    restraint_rigid, restraint_after_step, restraint_after_sigma, restraint_max_step)  # fmt: skip
         summaries = run_job(model, inp, out_dir, device, list(seeds) or None, num_recycles, num_samples,
                             getattr(torch, DTYPES[precision]), bucket, sample_chunk, logits_scheme=logits_scheme,
-                            guidance_terms=terms, restraint_kwargs=rkw, manifest_fields={"params": params, "optim": optim})  # fmt: skip
+                            guidance_terms=terms, restraint_kwargs=rkw, manifest_fields={"params": params, "optim": optim},
+                            dist_info=dist_info)  # fmt: skip
+        if dist_info is not None and dist_info.rank != 0:
+            continue
         if plot_confidences:
             _plot_outputs(out_dir)
         best = max(summaries, key=lambda s: s["ranking_score"])

@@ -79,21 +79,64 @@ def predict(model, features: dict, seed: int, num_recycles: int, num_samples: in
     return bucket.unpad_output(_concat_outputs(parts), n)
 
 
+def rank_samples(num_samples: int, rank: int, world: int) -> list[int]:
+    """Sample indices drawn by ``rank`` when one prediction is spread over ``world`` GPUs (round-robin)."""
+    return list(range(rank, num_samples, world))
+
+
+@torch.inference_mode()
+def predict_distributed(model, features: dict, seed: int, num_recycles: int, num_samples: int, dist_info, dtype=torch.bfloat16,
+                        use_bucket: bool = True, axial: bool = True, guidance_terms=None, restraint_kwargs=None):  # fmt: skip
+    """One prediction on all GPUs of a node. The trunk runs once, its Pairformer stack row-sharded over the ranks
+    (``parallel/axial.py``; every rank ends with the full pair tensor), then each rank draws its share of the samples -
+    sample ``i`` with the seed a single GPU uses for chunk ``i`` of a ``sample_chunk=1`` run, so the files do not depend
+    on the number of GPUs - and scores them with the confidence head. Returns ``(sample indices, output)`` for this
+    rank; ``output`` is ``None`` on ranks without a sample (the reference spreads whole jobs over processes instead:
+    bench/scripts/run_sweep.py:96-168)."""
+    device = dist_info.device
+    feats = {k: (v.to(device) if isinstance(v, torch.Tensor) else v) for k, v in features.items()}
+    n = int(feats["res_type"].shape[0])
+    if use_bucket:
+        feats, n = bucket.pad_features(feats)
+    if axial and dist_info.world_size > 1:
+        from ..parallel.axial import AxialComm
+
+        if getattr(model.evoformer, "_axial_comm", None) is None:
+            model.evoformer._axial_comm = AxialComm(dist_info)
+    amp = torch.autocast(device_type=torch.device(device).type, dtype=dtype, enabled=dtype != torch.float32)
+    kw = dict(restraint_kwargs or {})
+    mine = rank_samples(num_samples, dist_info.rank, dist_info.world_size)
+    with amp:
+        trunk = model.run_evoformer(feats, num_recycles, seed=seed)
+        comm = getattr(model.evoformer, "_axial_comm", None)
+        if comm is not None:
+            comm.check()
+        if not mine:
+            return mine, None
+        disto = model.distogram_head(trunk[0]["pair"])
+        parts = [model.sample_from_trunk(feats, trunk, seed=sample_chunk_seed(seed, i), num_samples=1,
+                                         guidance_terms=guidance_terms, distogram=disto, **kw) for i in mine]  # fmt: skip
+    return mine, bucket.unpad_output(_concat_outputs(parts), n)
+
+
 def write_seed(out_dir: str, job_name: str, seed: int, output, features: dict, chain_names, writer: BackgroundWriter,
-               logits_scheme: str = "f16", save_distogram: bool = True) -> list[dict]:  # fmt: skip
+               logits_scheme: str = "f16", save_distogram: bool = True, indices=None) -> list[dict]:  # fmt: skip
+    """Files of the samples in ``output``; ``indices`` are their numbers within the seed when ``output`` holds only a
+    subset (one prediction spread over several GPUs)."""
     host = logits_to_host(output)
     feats = {k: v.cpu() if isinstance(v, torch.Tensor) else v for k, v in features.items()}
     summaries = []
     S = host.atom_positions.shape[0]
-    for i in range(S):
-        d = sample_dir(out_dir, seed, i)
+    numbers = list(range(S)) if indices is None else list(indices)
+    for i, number in enumerate(numbers):
+        d = sample_dir(out_dir, seed, number)
         os.makedirs(d, exist_ok=True)
-        s = conf.sample_summary(i, seed, host.plddt[i].float(), host.pae[i].float(), host.pde[i].float(),
+        s = conf.sample_summary(number, seed, host.plddt[i].float(), host.pae[i].float(), host.pde[i].float(),
                                 host.atom_positions[i].float(), feats)  # fmt: skip
         summaries.append(s)
         one = dataclasses.replace(host, atom_positions=host.atom_positions[i : i + 1], atom_mask=host.atom_mask[i : i + 1],
                                   plddt=host.plddt[i : i + 1])  # fmt: skip
-        writer.submit(save_mmcif, os.path.join(d, "model.cif"), one, feats, title=f"{job_name} seed {seed} sample {i}",
+        writer.submit(save_mmcif, os.path.join(d, "model.cif"), one, feats, title=f"{job_name} seed {seed} sample {number}",
                       chain_names=chain_names)  # fmt: skip
         writer.submit(conf.save_confidences_json, os.path.join(d, "confidences.json"), s)
         heads = {"plddt": host.plddt[i], "pae": host.pae[i], "pde": host.pde[i]}
@@ -109,13 +152,18 @@ def write_seed(out_dir: str, job_name: str, seed: int, output, features: dict, c
 def run_job(model, inp, out_dir: str, device, seeds=None, num_recycles: int = 10, num_samples: int = 5,
             dtype=torch.bfloat16, use_bucket: bool = True, sample_chunk: int = 0, skip_existing: bool = False,
             logits_scheme: str = "f16", save_distogram: bool = True, guidance_terms=None, restraint_kwargs=None,
-            manifest_fields: dict | None = None) -> list[dict]:  # fmt: skip
-    """All seeds of one job; returns the per-sample summaries (also written as CSV / JSON)."""
+            manifest_fields: dict | None = None, dist_info=None) -> list[dict]:  # fmt: skip
+    """All seeds of one job; returns the per-sample summaries (also written as CSV / JSON). With a ``dist_info`` of more
+    than one rank every prediction is spread over the ranks (``predict_distributed``): each rank writes the sample
+    folders of its own samples, rank 0 the files that summarise the job."""
+    spread = dist_info is not None and dist_info.world_size > 1
+    main = not spread or dist_info.rank == 0
     os.makedirs(out_dir, exist_ok=True)
     manifest = new_manifest(job=inp.name, num_tokens=inp.num_tokens, num_samples=num_samples, num_recycles=num_recycles,
                             **(manifest_fields or {}))  # fmt: skip
     mpath = os.path.join(out_dir, "run_manifest.json")
-    write_manifest(mpath, manifest)
+    if main:
+        write_manifest(mpath, manifest)
     summaries, timings = [], {}
     census(reset=True)
     with BackgroundWriter() as writer:
@@ -124,13 +172,29 @@ def run_job(model, inp, out_dir: str, device, seeds=None, num_recycles: int = 10
                 logger.info("seed %d already complete, skipping", seed)
                 continue
             t0 = time.time()
-            out = predict(model, inp.features, seed, num_recycles, num_samples, device, dtype, use_bucket, sample_chunk,
-                          guidance_terms, restraint_kwargs)  # fmt: skip
+            indices = None
+            if spread:
+                indices, out = predict_distributed(model, inp.features, seed, num_recycles, num_samples, dist_info, dtype,
+                                                   use_bucket, True, guidance_terms, restraint_kwargs)  # fmt: skip
+            else:
+                out = predict(model, inp.features, seed, num_recycles, num_samples, device, dtype, use_bucket, sample_chunk,
+                              guidance_terms, restraint_kwargs)  # fmt: skip
             if torch.cuda.is_available() and torch.device(device).type == "cuda":
                 torch.cuda.synchronize()
             timings[f"seed-{seed}"] = time.time() - t0
-            summaries += write_seed(out_dir, inp.name, seed, out, inp.features, inp.chain_names, writer, logits_scheme,
-                                    save_distogram)  # fmt: skip
+            mine = []
+            if out is not None:
+                mine = write_seed(out_dir, inp.name, seed, out, inp.features, inp.chain_names, writer, logits_scheme,
+                                  save_distogram and main, indices)  # fmt: skip
+            if spread:
+                import torch.distributed as dist
+
+                gathered = [None] * dist_info.world_size
+                dist.all_gather_object(gathered, mine)
+                mine = sorted((s for part in gathered for s in part), key=lambda s: s.get("sample", 0))
+            summaries += mine
+    if not main:
+        return summaries
     if summaries:
         conf.save_ranking_scores_csv(os.path.join(out_dir, "ranking_scores.csv"), summaries)
         conf.save_summary_confidences_json(os.path.join(out_dir, f"{inp.name}_summary_confidences.json"), summaries, inp.name)

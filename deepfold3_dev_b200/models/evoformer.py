@@ -267,6 +267,17 @@ class Evoformer(nn.Module):
             single = single + self.prev_single_embedding(self.prev_single_embedding_layer_norm(prev_single))
         msa = self.msa_activations(msa_feat) + self.extra_msa_target_feat(target_feat).unsqueeze(-3)
 
+        comm = getattr(self, "_axial_comm", None)
+        if comm is not None and comm.world > 1 and not torch.is_grad_enabled() and pair.shape[-2] % comm.world == 0:
+            # inference on several GPUs: both stacks run on row shards of the pair tensor
+            from ..parallel.axial import sharded_trunk
+
+            b1 = (lambda t: t[None]) if pair.dim() == 3 else (lambda t: t)
+            msa, pair, single = sharded_trunk(self.msa_stack, self.trunk_pairformer, b1(msa), b1(pair), b1(single),
+                                              b1(msa_mask), b1(pair_mask), b1(seq_mask), comm)  # fmt: skip
+            if pair_mask.dim() == 2:
+                msa, pair, single = msa[0], pair[0], single[0]
+            return {"pair": pair, "single": single, "msa": msa, "target_feat": target_feat}
         use_ckpt = self._grad_checkpoint and torch.is_grad_enabled()
         for layer in self.msa_stack:
             if use_ckpt:

@@ -238,10 +238,11 @@ def outer_product_mean(a, b, out_w, out_b, mask, eps: float = 1e-3, mask_i=None,
     kernel (contraction over MSA rows, then the projection), blocked over tokens; everything else takes the fp32
     statement."""
     nat = fused(a, "matmul")
-    if (nat is not None and mask_i is None and mask_j is None and mask is not None and a.shape[1] % 8 == 0
-            and (a.shape[2] * a.shape[3]) % 8 == 0 and out_w.shape[-1] % 8 == 0):
+    have_masks = mask is not None or (mask_i is not None and mask_j is not None)
+    if (nat is not None and have_masks and a.shape[1] % 8 == 0 and (a.shape[2] * a.shape[3]) % 8 == 0 and a.shape[2] % 8 == 0
+            and b.shape[2] % 8 == 0 and out_w.shape[-1] % 8 == 0):
         _CENSUS["outer_product_mean:sm100"] += 1
-        return nat.outer_product_mean(a, b, out_w, out_b, mask, eps)
+        return nat.outer_product_mean(a, b, out_w, out_b, mask, eps, mask_i=mask_i, mask_j=mask_j)
     _CENSUS["outer_product_mean:torch"] += 1
     return ref.outer_product_mean(a, b, out_w, out_b, mask, eps, mask_i, mask_j)
 

@@ -556,27 +556,30 @@ def msa_weighted_average(w, v):
     return out.view(B, H, N, S, D).permute(0, 3, 2, 1, 4)
 
 
-def outer_product_mean(a, b, out_w, out_b, mask, eps: float = 1e-3, row_chunk: int = 96):
+def outer_product_mean(a, b, out_w, out_b, mask, eps: float = 1e-3, row_chunk: int = 96, mask_i=None, mask_j=None):
     """``(sum_s a[s,i,:] (x) b[s,j,:]) . out_w + out_b`` over valid rows, as two tensor-core products per block of
     ``row_chunk`` tokens i: first the [chunk * E, S] x [S, N * E] contraction over the MSA rows, then, after bringing the
     two feature axes together, the [chunk * N, E * E] x [E * E, C] projection. The full ``[N, N, E, E]`` outer product
-    never exists at once (reference: model/ops.py:683-785, tiled form model/tiled_linear.py:67-88)."""
-    B, S, N, E = a.shape
+    never exists at once (reference: model/ops.py:683-785, tiled form model/tiled_linear.py:67-88). ``a`` and ``b`` may
+    cover different token ranges (a block of the output); their row masks are then ``mask_i`` / ``mask_j``."""
+    B, S, Ni, E = a.shape
+    Nj = b.shape[2]
     C = out_w.shape[-1]
     w2 = out_w.reshape(E * E, C).to(BF16)  # a differentiable cast: the projection weight trains through it
     a16, b16 = a.to(BF16), b.to(BF16)
-    m16 = mask.to(BF16)
+    mi16 = (mask if mask_i is None else mask_i).to(BF16)
+    mj16 = (mask if mask_j is None else mask_j).to(BF16)
     outs = []
     for bi in range(B):
-        bm = b16[bi].reshape(S, N * E)
-        count = mm(m16[bi], m16[bi], True, False, True)  # [N, N] valid rows per pair, exact in fp32
+        bm = b16[bi].reshape(S, Nj * E)
+        count = mm(mi16[bi], mj16[bi], True, False, True)  # [Ni, Nj] valid rows per pair, exact in fp32
         rows = []
-        for i0 in range(0, N, row_chunk):
-            i1 = min(N, i0 + row_chunk)
+        for i0 in range(0, Ni, row_chunk):
+            i1 = min(Ni, i0 + row_chunk)
             am = a16[bi, :, i0:i1].reshape(S, (i1 - i0) * E)
             ab = matmul(am, bm, True, False)  # [(i, e), (j, f)]
-            ab = ab.view(i1 - i0, E, N, E).permute(0, 2, 1, 3).reshape((i1 - i0) * N, E * E)
-            rows.append(matmul(ab, w2).view(i1 - i0, N, C))
+            ab = ab.view(i1 - i0, E, Nj, E).permute(0, 2, 1, 3).reshape((i1 - i0) * Nj, E * E)
+            rows.append(matmul(ab, w2).view(i1 - i0, Nj, C))
         act = torch.cat(rows, 0) + out_b.to(BF16)
         outs.append(act / (eps + count).unsqueeze(-1).to(act.dtype))
     return torch.stack(outs, 0)

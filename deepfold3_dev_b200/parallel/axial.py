@@ -184,28 +184,34 @@ def _attention_rows(mod, z_rows, key_mask_rows, bias_full):
     return mod.out_proj(ops.sigmoid_gate_mul(zn, mod.to_g.weight, out))
 
 
+def _pair_updates(block, z, mask_rows, mask_cols, comm: AxialComm, gain, scale, transition_gain=1.0):
+    """The pair half of a trunk block (both triangle multiplies, both triangle attentions, the transition) on rows."""
+    z = z + gain * scale(_tri_mul_rows(block.tri_mul_out, z, mask_rows, comm))
+    z = z + gain * scale(_tri_mul_rows(block.tri_mul_in, z, mask_rows, comm))
+    if block.use_triangle_attention:
+        row, col = block.pair_attn_row, block.pair_attn_col
+        bias = comm.all_gather(ops.head_bias_planes(row.norm(z), row.pair_bias.weight), 2)  # [B, H, N, N]
+        z = z + gain * scale(_attention_rows(row, z, mask_rows, bias))
+        bias = comm.all_gather(ops.head_bias_planes(col.norm(z), col.pair_bias.weight), 2)
+        zt = comm.transpose(z)
+        z = z + comm.transpose(gain * scale(_attention_rows(col, zt, mask_cols, bias)))
+    return z + gain * transition_gain * scale(block.pair_transition(z))
+
+
+def _masks(pair_mask, comm: AxialComm):
+    rows = comm.rows(pair_mask.shape[-1])
+    # mask[i_local, j] for the row shard, mask[k, i_local] as the column shard sees it
+    return pair_mask[:, rows], pair_mask.transpose(1, 2)[:, rows].contiguous()
+
+
 @torch.no_grad()
 def sharded_pairformer_block(block, pair_rows, single, pair_mask, seq_mask, comm: AxialComm):
     """One Pairformer block on a row shard. ``pair_rows`` ``[B, n, N, C]`` are this rank's rows of the pair tensor,
     ``pair_mask`` ``[B, N, N]`` and the single track are replicated. Returns ``(pair_rows, single)``; gathering the
     rows of all ranks gives what ``block(pair, single, pair_mask, seq_mask)`` gives in eval mode."""
-    N = pair_mask.shape[-1]
-    rows = comm.rows(N)
-    mask_rows = pair_mask[:, rows]                               # [B, n, N]: mask[i_local, j]
-    mask_cols = pair_mask.transpose(1, 2)[:, rows].contiguous()  # [B, n, N]: mask[k, i_local] seen from the column shard
-    s = block.residual_out_scale
-    scale = block.branch_scaler
-    z = pair_rows
-    z = z + s * scale(_tri_mul_rows(block.tri_mul_out, z, mask_rows, comm))
-    z = z + s * scale(_tri_mul_rows(block.tri_mul_in, z, mask_rows, comm))
-    if block.use_triangle_attention:
-        row, col = block.pair_attn_row, block.pair_attn_col
-        bias = comm.all_gather(ops.head_bias_planes(row.norm(z), row.pair_bias.weight), 2)  # [B, H, N, N]
-        z = z + s * scale(_attention_rows(row, z, mask_rows, bias))
-        bias = comm.all_gather(ops.head_bias_planes(col.norm(z), col.pair_bias.weight), 2)
-        zt = comm.transpose(z)
-        z = z + comm.transpose(s * scale(_attention_rows(col, zt, mask_cols, bias)))
-    z = z + s * block.pair_transition_residual_gain * scale(block.pair_transition(z))
+    mask_rows, mask_cols = _masks(pair_mask, comm)
+    s, scale = block.residual_out_scale, block.branch_scaler
+    z = _pair_updates(block, pair_rows, mask_rows, mask_cols, comm, s, scale, block.pair_transition_residual_gain)
     if block.use_single_track:
         logits = block.single_to_pair(block.single_to_pair_norm(z)).movedim(-1, -3)  # [B, Hs, n, N]
         logits = comm.all_gather(logits.contiguous(), 2)
@@ -215,13 +221,55 @@ def sharded_pairformer_block(block, pair_rows, single, pair_mask, seq_mask, comm
 
 
 @torch.no_grad()
-def sharded_pairformer_stack(blocks, pair, single, pair_mask, seq_mask, comm: AxialComm, gather: bool = True):
-    """All ``blocks`` on row shards of ``pair`` ``[B, N, N, C]`` (every rank passes the same full tensor or its own rows
-    ``[B, n, N, C]``). With ``gather`` the full pair tensor is reassembled on every rank at the end."""
-    N = pair_mask.shape[-1]
+def sharded_evoformer_block(block, msa, pair_rows, msa_mask, pair_mask, comm: AxialComm):
+    """One MSA-stack block (reference: model/evoformer.py:84-177) with the pair tensor on row shards and the MSA
+    replicated: the outer-product mean is computed for this rank's rows only, the MSA attention weights come from the
+    local rows and are gathered (``[H, N, N]``), the MSA update itself is small and runs on every rank."""
+    from ..models.primitives import map_row_chunks
+
+    mask_rows, mask_cols = _masks(pair_mask, comm)
+    rows = comm.rows(pair_mask.shape[-1])
+    s = block.residual_out_scale
+    opm = block.outer_product
+    m = msa_mask.unsqueeze(-1)
+    x = opm.norm(msa)
+    a, b = opm.proj_a(x) * m.to(x.dtype), opm.proj_b(x) * m.to(x.dtype)
+    z = pair_rows + s * ops.outer_product_mean(a[:, :, rows], b, opm.out_w, opm.out_b, None, mask_i=msa_mask[:, :, rows],
+                                               mask_j=msa_mask)  # fmt: skip
+    ra = block.row_attn
+    logits = ra.pair_logits(ra.pair_norm(z)).permute(0, 3, 1, 2)  # [B, H, n, N]
+    col_mask = msa_mask.max(dim=-2).values
+    weights = torch.softmax(logits.float() + 1e9 * (col_mask.float() - 1.0)[:, None, None, :], dim=-1)
+    weights = comm.all_gather(weights.contiguous(), 2)
+    msa = msa + s * map_row_chunks(lambda part: ra._rows(part, weights), msa, ra.row_chunk)
+    msa = msa + s * map_row_chunks(block.msa_transition, msa, block.msa_row_chunk)
+    return msa, _pair_updates(block, z, mask_rows, mask_cols, comm, s, lambda t: t)
+
+
+def _shard_rows(pair, comm: AxialComm):
+    N = pair.shape[2]
     if N % comm.world:
         raise ValueError(f"axial sharding needs the token count ({N}) to be a multiple of the number of ranks ({comm.world})")
-    z = pair[:, comm.rows(N)].contiguous() if pair.shape[1] == N and comm.world > 1 else pair
+    return pair[:, comm.rows(N)].contiguous() if comm.world > 1 else pair
+
+
+@torch.no_grad()
+def sharded_pairformer_stack(blocks, pair, single, pair_mask, seq_mask, comm: AxialComm, gather: bool = True):
+    """All ``blocks`` on row shards of the full pair tensor ``[B, N, N, C]`` (the same on every rank). With ``gather``
+    the full pair tensor is reassembled on every rank at the end."""
+    z = _shard_rows(pair, comm)
     for block in blocks:
         z, single = sharded_pairformer_block(block, z, single, pair_mask, seq_mask, comm)
     return (comm.all_gather(z, 1) if gather else z), single
+
+
+@torch.no_grad()
+def sharded_trunk(msa_blocks, pairformer_blocks, msa, pair, single, msa_mask, pair_mask, seq_mask, comm: AxialComm):
+    """MSA stack then Pairformer stack of one trunk pass, the pair tensor sharded by rows from the first block to the
+    last; returns ``(msa, pair, single)`` with the full pair tensor on every rank."""
+    z = _shard_rows(pair, comm)
+    for block in msa_blocks:
+        msa, z = sharded_evoformer_block(block, msa, z, msa_mask, pair_mask, comm)
+    for block in pairformer_blocks:
+        z, single = sharded_pairformer_block(block, z, single, pair_mask, seq_mask, comm)
+    return msa, comm.all_gather(z, 1), single

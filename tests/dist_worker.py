@@ -113,28 +113,36 @@ def main():
             sys.exit(0 if "after_peer_exit" in str(exc) else 5)
         sys.exit(6)
     elif scenario == "axial_block":
-        from deepfold3_dev_b200.models.evoformer import PairFormerBlock
-        from deepfold3_dev_b200.parallel.axial import AxialComm, sharded_pairformer_stack
+        from deepfold3_dev_b200.models.evoformer import EvoformerBlock, PairFormerBlock
+        from deepfold3_dev_b200.parallel.axial import AxialComm, sharded_trunk
         from tests.helpers import wake_zero_init
 
         info = init_process_group(timeout_s=120, device="cpu")
         torch.manual_seed(5)
+        msa_blocks = torch.nn.ModuleList([EvoformerBlock(16, 32, num_msa_heads=4, num_pair_heads=2, outer_product_hidden=8)]).eval()
         blocks = torch.nn.ModuleList(
             PairFormerBlock(32, 48, num_pair_heads=2, num_single_heads=4, single_key_dim=48, single_value_dim=48) for _ in range(2)
         ).eval()
+        wake_zero_init(msa_blocks)
         wake_zero_init(blocks)
-        B, N = 2, 12 if info.world_size <= 4 else 4 * info.world_size
-        pair, single = torch.randn(B, N, N, 32), torch.randn(B, N, 48)
+        B, S, N = 2, 6, 12 if info.world_size <= 4 else 4 * info.world_size
+        pair, single, msa = torch.randn(B, N, N, 32), torch.randn(B, N, 48), torch.randn(B, S, N, 16)
         seq_mask = torch.ones(B, N)
         seq_mask[1, -2:] = 0
         pair_mask = seq_mask[:, :, None] * seq_mask[:, None, :]
+        msa_mask = seq_mask[:, None, :].expand(B, S, N).clone()
+        msa_mask[0, -1, :3] = 0
         with torch.no_grad():
-            want_pair, want_single = pair, single
+            want_msa, want_pair, want_single = msa, pair, single
+            for blk in msa_blocks:
+                want_msa, want_pair = blk(want_msa, want_pair, msa_mask, pair_mask)
             for blk in blocks:
                 want_pair, want_single = blk(want_pair, want_single, pair_mask, seq_mask)
-        got_pair, got_single = sharded_pairformer_stack(blocks, pair, single, pair_mask, seq_mask, AxialComm(info, "collective"))
+        got_msa, got_pair, got_single = sharded_trunk(msa_blocks, blocks, msa, pair, single, msa_mask, pair_mask, seq_mask,
+                                                      AxialComm(info, "collective"))  # fmt: skip
         torch.save({"pair_err": (got_pair - want_pair).abs().max(), "single_err": (got_single - want_single).abs().max(),
-                    "scale": want_pair.abs().max()}, os.path.join(out_dir, f"axial_rank{info.rank}.pt"))
+                    "msa_err": (got_msa - want_msa).abs().max(), "scale": want_pair.abs().max()},
+                   os.path.join(out_dir, f"axial_rank{info.rank}.pt"))  # fmt: skip
         torch.distributed.barrier()
         torch.distributed.destroy_process_group()
     else:
