@@ -88,9 +88,9 @@ def rank_samples(num_samples: int, rank: int, world: int) -> list[int]:
 def predict_distributed(model, features: dict, seed: int, num_recycles: int, num_samples: int, dist_info, dtype=torch.bfloat16,
                         use_bucket: bool = True, axial: bool = True, guidance_terms=None, restraint_kwargs=None):  # fmt: skip
     """One prediction on all GPUs of a node. The trunk runs once, its Pairformer stack row-sharded over the ranks
-    (``parallel/axial.py``; every rank ends with the full pair tensor), then each rank draws its share of the samples -
-    sample ``i`` with the seed a single GPU uses for chunk ``i`` of a ``sample_chunk=1`` run, so the files do not depend
-    on the number of GPUs - and scores them with the confidence head. Returns ``(sample indices, output)`` for this
+    (``parallel/axial.py``; every rank ends with the full pair tensor), then each rank draws its share of the samples as
+    one batch, seeded from (seed, rank) like chunk ``rank`` of a chunked single-GPU run, and scores them with the
+    confidence head. Returns ``(sample indices, output)`` for this
     rank; ``output`` is ``None`` on ranks without a sample (the reference spreads whole jobs over processes instead:
     bench/scripts/run_sweep.py:96-168)."""
     device = dist_info.device
@@ -114,9 +114,9 @@ def predict_distributed(model, features: dict, seed: int, num_recycles: int, num
         if not mine:
             return mine, None
         disto = model.distogram_head(trunk[0]["pair"])
-        parts = [model.sample_from_trunk(feats, trunk, seed=sample_chunk_seed(seed, i), num_samples=1,
-                                         guidance_terms=guidance_terms, distogram=disto, **kw) for i in mine]  # fmt: skip
-    return mine, bucket.unpad_output(_concat_outputs(parts), n)
+        out = model.sample_from_trunk(feats, trunk, seed=sample_chunk_seed(seed, dist_info.rank), num_samples=len(mine),
+                                      guidance_terms=guidance_terms, distogram=disto, **kw)  # fmt: skip
+    return mine, bucket.unpad_output(out, n)
 
 
 def write_seed(out_dir: str, job_name: str, seed: int, output, features: dict, chain_names, writer: BackgroundWriter,

@@ -289,17 +289,26 @@ class DiffusionTransformer(nn.Module):
         self.pair_chunk_budget = optim.pair_chunk_budget_bytes if optim is not None else 0
 
     def hoist_pair_logits(self, pair_cond, mask) -> tuple[torch.Tensor, ...]:
-        """Per super-block ``[B, sbs*H, N, N]`` fp32 logits with ``1e9 (mask - 1)`` added along keys."""
-        bias = 1e9 * (mask.float() - 1.0)[:, None, None, :]
+        """Per super-block ``[B, sbs*H, N, N]`` logits with ``1e9 (mask - 1)`` added along keys, as contiguous head
+        planes. They keep the dtype the projection produces (bf16 under autocast: widening them would add no
+        information, and the attention kernel stages bf16 bias tiles by TMA), fp32 otherwise."""
         rows = budget_rows(self.pair_chunk_budget, pair_cond.shape[-2], 4 * pair_cond.shape[-1])
-        if rows == 0 or torch.is_grad_enabled():
-            pn = ops.layer_norm(pair_cond, self.pair_norm_w, None)
-            return tuple(proj(pn).movedim(-1, -3).float() + bias for proj in self.pair_logits_proj)
-        return tuple(
-            map_row_chunks(lambda r, p=proj: p(ops.layer_norm(r, self.pair_norm_w, None)), pair_cond, rows)
-            .movedim(-1, -3).float() + bias
-            for proj in self.pair_logits_proj
-        )  # fmt: skip
+        if torch.is_grad_enabled():
+            rows = 0
+        N = pair_cond.shape[-3]
+
+        parts: list[list[torch.Tensor]] = [[] for _ in self.pair_logits_proj]
+        for lo in range(0, N, rows or N):
+            pn = ops.layer_norm(pair_cond[..., lo : lo + (rows or N), :, :], self.pair_norm_w, None)
+            for got, proj in zip(parts, self.pair_logits_proj):
+                got.append(ops.head_bias_planes(pn, proj.weight))  # [B, sbs*H, rows, N]
+        out = []
+        for got in parts:
+            logits = got[0] if len(got) == 1 else torch.cat(got, dim=-2)
+            dtype = logits.dtype if logits.dtype == torch.bfloat16 else torch.float32
+            bias = (1e9 * (mask.float() - 1.0))[:, None, None, :].to(dtype)
+            out.append((logits.to(dtype) + bias).contiguous())
+        return tuple(out)
 
     def run(self, act, single_cond, pair_logits):
         """``act`` ``[B, S, N, c]``, ``single_cond`` ``[B, S|1, N, cs]``, hoisted ``pair_logits``."""

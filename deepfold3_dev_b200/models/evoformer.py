@@ -20,6 +20,7 @@ from .primitives import (
     LayerNorm,
     LinearNoBias,
     block_residual_scale,
+    budget_rows,
     make_transition_block,
     map_pair_rows,
     map_pair_transition,
@@ -131,6 +132,18 @@ class PairFormerBlock(nn.Module):
         self.branch_scaler = make_branch_scaler(self.branch_scaler_kind)
         self.pair_dropout = pair_dropout
 
+    def _single_bias(self, pair):
+        """Pair bias of the single-track attention as contiguous head planes ``[B?, H, N, N]`` (the projection writes
+        them channel-major; row chunks under the inference byte budget)."""
+        lead = pair.dim() == 3
+        z = pair[None] if lead else pair
+        N = z.shape[1]
+        rows = 0 if torch.is_grad_enabled() else budget_rows(self.pair_chunk_budget, z.shape[-2], 4 * z.shape[-1])
+        parts = [ops.head_bias_planes(self.single_to_pair_norm(z[:, lo : lo + (rows or N)]), self.single_to_pair.weight)
+                 for lo in range(0, N, rows or N)]  # fmt: skip
+        logits = parts[0] if len(parts) == 1 else torch.cat(parts, dim=2)
+        return logits[0] if lead else logits
+
     def forward(self, pair, single, pair_mask, seq_mask):
         p, tr, s = self.pair_dropout, self.training, self.residual_out_scale
         s_pf = _gain(s) * self.pair_transition_residual_gain
@@ -151,10 +164,7 @@ class PairFormerBlock(nn.Module):
         b_pair_ffn = _gain(s_pf) * scale(map_pair_transition(self.pair_transition, pair, self.pair_chunk_budget, 4))
         pair = pair + b_pair_ffn
         if self.use_single_track:
-            logits = map_pair_rows(
-                lambda rows: self.single_to_pair(self.single_to_pair_norm(rows)), pair, self.pair_chunk_budget,
-                4 * pair.shape[-1],
-            ).movedim(-1, -3)  # fmt: skip
+            logits = self._single_bias(pair)
             b_single_attn = _gain(s) * scale(self.single_attn(single, seq_mask, logits))
             single = single + b_single_attn
             update = self.single_transition(single)

@@ -213,8 +213,8 @@ def sharded_pairformer_block(block, pair_rows, single, pair_mask, seq_mask, comm
     s, scale = block.residual_out_scale, block.branch_scaler
     z = _pair_updates(block, pair_rows, mask_rows, mask_cols, comm, s, scale, block.pair_transition_residual_gain)
     if block.use_single_track:
-        logits = block.single_to_pair(block.single_to_pair_norm(z)).movedim(-1, -3)  # [B, Hs, n, N]
-        logits = comm.all_gather(logits.contiguous(), 2)
+        logits = ops.head_bias_planes(block.single_to_pair_norm(z), block.single_to_pair.weight)  # [B, Hs, n, N]
+        logits = comm.all_gather(logits, 2)
         single = single + s * scale(block.single_attn(single, seq_mask, logits))
         single = single + s * block.single_transition_residual_gain * scale(block.single_transition(single))
     return z, single
