@@ -329,6 +329,88 @@ __global__ void __launch_bounds__(256) plane_layer_norm_fwd_kernel(const __nv_bf
   }
 }
 
+// The same with 16-byte accesses on both sides, for M % 8 == 0. A block owns 128 consecutive positions: every thread
+// fetches eight positions of a plane per load (a half-warp covers 256 contiguous bytes of the plane) into a bf16 tile
+// [C][130] (pitch 65 words: the column reads of the second phase hit 32 different banks), each warp then normalises
+// positions with lanes over channels into a dense [128][C] bf16 tile, which is exactly the block's contiguous piece of
+// the channel-last output and leaves with 16-byte stores.
+constexpr int kPlaneTileV = 128;
+constexpr int kPlanePitchV = 130;
+
+template <int KC>
+__global__ void __launch_bounds__(256) plane_layer_norm_fwd_vec_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ w,
+                                                                       const float* __restrict__ b, __nv_bfloat16* __restrict__ y,
+                                                                       float* __restrict__ mean_out, float* __restrict__ rstd_out,
+                                                                       int64_t M, float eps) {
+  constexpr int C = 32 * KC;
+  extern __shared__ __align__(16) unsigned char plane_smem[];
+  __nv_bfloat16* tin = reinterpret_cast<__nv_bfloat16*>(plane_smem);                       // [C][130]
+  __nv_bfloat16* tout = tin + C * kPlanePitchV + 8;                                          // [128][C], 16-byte aligned
+  float* stats = reinterpret_cast<float*>(tout + kPlaneTileV * C);                           // [4][128]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t m0 = (int64_t)blockIdx.x * kPlaneTileV;
+  const int chunk = threadIdx.x & 15;           // eight positions
+  const int64_t p0 = m0 + chunk * 8;
+  for (int c = threadIdx.x >> 4; c < C; c += 16) {
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (p0 < M) v = *reinterpret_cast<const uint4*>(x + (int64_t)c * M + p0);   // M % 8 == 0: the chunk is inside or outside
+    uint32_t* dst = reinterpret_cast<uint32_t*>(tin + c * kPlanePitchV + chunk * 8);
+    dst[0] = v.x; dst[1] = v.y; dst[2] = v.z; dst[3] = v.w;
+  }
+  float wv[KC], bv[KC];
+#pragma unroll
+  for (int k = 0; k < KC; ++k) {
+    wv[k] = w ? w[lane + 32 * k] : 1.f;
+    bv[k] = b ? b[lane + 32 * k] : 0.f;
+  }
+  __syncthreads();
+  // statistics: one thread per (position, half of the channels), consecutive lanes on consecutive positions; sums are
+  // taken about the position's first channel so that the single pass does not cancel; the two halves meet in shared memory
+  {
+    const int pidx = threadIdx.x & 127, half = threadIdx.x >> 7;
+    const float shift = __bfloat162float(tin[pidx]);
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll 8
+    for (int c = half * (C / 2); c < (half + 1) * (C / 2); ++c) {
+      const float d = __bfloat162float(tin[c * kPlanePitchV + pidx]) - shift;
+      s1 += d;
+      s2 += d * d;
+    }
+    stats[(half * 2 + 0) * kPlaneTileV + pidx] = s1;
+    stats[(half * 2 + 1) * kPlaneTileV + pidx] = s2;
+  }
+  __syncthreads();
+  if (threadIdx.x < kPlaneTileV) {
+    const int pidx = threadIdx.x;
+    const float s1 = stats[pidx] + stats[2 * kPlaneTileV + pidx];
+    const float s2 = stats[kPlaneTileV + pidx] + stats[3 * kPlaneTileV + pidx];
+    const float dm = s1 / C;
+    const float mean = __bfloat162float(tin[pidx]) + dm;
+    const float rstd = rsqrtf(fmaxf(s2 / C - dm * dm, 0.f) + eps);
+    stats[pidx] = mean;
+    stats[kPlaneTileV + pidx] = rstd;
+    if (m0 + pidx < M) {
+      mean_out[m0 + pidx] = mean;
+      rstd_out[m0 + pidx] = rstd;
+    }
+  }
+  __syncthreads();
+  for (int pidx = warp; pidx < kPlaneTileV; pidx += 8) {
+    if (m0 + pidx >= M) break;
+    const float mean = stats[pidx], rstd = stats[kPlaneTileV + pidx];
+#pragma unroll
+    for (int k = 0; k < KC; ++k) {
+      const float v = __bfloat162float(tin[(lane + 32 * k) * kPlanePitchV + pidx]);
+      tout[pidx * C + lane + 32 * k] = __float2bfloat16_rn((v - mean) * rstd * wv[k] + bv[k]);
+    }
+  }
+  __syncthreads();
+  const int64_t valid = (M - m0 < kPlaneTileV ? M - m0 : kPlaneTileV) * C / 8;   // 16-byte pieces of this block's output
+  uint4* dst = reinterpret_cast<uint4*>(y + m0 * C);
+  const uint4* src = reinterpret_cast<const uint4*>(tout);
+  for (int64_t i = threadIdx.x; i < valid; i += 256) dst[i] = src[i];
+}
+
 // Backward of the above: dy [M, C] channel-last, x planes [C, M] -> dx planes [C, M]; (dw, db) partials per block.
 template <int KC>
 __global__ void __launch_bounds__(256) plane_layer_norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
@@ -769,6 +851,25 @@ std::tuple<Tensor, Tensor, Tensor> df3_plane_layer_norm_fwd(const Tensor& x, con
   if (M == 0) return {y, mean, rstd};
   const float* wp = w.has_value() ? w->data_ptr<float>() : nullptr;
   const float* bp = b.has_value() ? b->data_ptr<float>() : nullptr;
+  if (M % 8 == 0 && (C == 64 || C == 128) && reinterpret_cast<uintptr_t>(x.data_ptr()) % 16 == 0) {
+    const unsigned vgrid = (unsigned)((M + df3::kPlaneTileV - 1) / df3::kPlaneTileV);
+    const size_t vsmem = ((size_t)C * df3::kPlanePitchV + 8 + (size_t)df3::kPlaneTileV * C) * 2 + 4 * df3::kPlaneTileV * sizeof(float);
+#define DF3_PLNV(KC)                                                                                               \
+  do {                                                                                                             \
+    auto k = df3::plane_layer_norm_fwd_vec_kernel<KC>;                                                             \
+    static bool attr = false;                                                                                      \
+    if (!attr) {                                                                                                   \
+      C10_CUDA_CHECK(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)vsmem));            \
+      attr = true;                                                                                                 \
+    }                                                                                                              \
+    k<<<vgrid, 256, vsmem, stream()>>>((const __nv_bfloat16*)x.data_ptr(), wp, bp, (__nv_bfloat16*)y.data_ptr(),   \
+                                       mean.data_ptr<float>(), rstd.data_ptr<float>(), M, (float)eps);             \
+  } while (0)
+    if (C == 64) DF3_PLNV(2); else DF3_PLNV(4);
+#undef DF3_PLNV
+    C10_CUDA_KERNEL_LAUNCH_CHECK();
+    return {y, mean, rstd};
+  }
   const unsigned grid = (unsigned)((M + df3::kPlaneTile - 1) / df3::kPlaneTile);
   const size_t smem = (size_t)C * 65 * sizeof(float);
 #define DF3_PLN(KC)                                                                                                \

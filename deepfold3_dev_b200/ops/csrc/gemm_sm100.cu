@@ -245,8 +245,14 @@ __device__ __forceinline__ bool tile_at(const GemmParams& p, long long i, TileCo
 // Persistent kernel: each CTA walks tiles t = blockIdx.x, blockIdx.x + gridDim.x, ... The accumulator is double
 // buffered in tensor memory, so the epilogue warps drain tile t while the MMA warp already works on tile t + 1, and
 // the shared-memory ring keeps running across tile boundaries.
+// The plain and sigmoid-gate epilogues at tile widths up to 128 are compiled for two CTAs per SM (at most 102
+// registers per thread): on the pair-shaped products (K = 128, a few thousand row tiles) the epilogue is the critical
+// path, and with ten warps per SM its tensor-memory and shared-memory latencies are exposed; a second CTA fills them.
 template <int BN, int EPI>
-__global__ void __launch_bounds__(kThreads) gemm_kernel(const __grid_constant__ CUtensorMap tmA,
+constexpr int min_ctas_per_sm() { return ((EPI == kPlain || EPI == kSigmoidMul) && BN <= 128) ? 2 : 1; }
+
+template <int BN, int EPI>
+__global__ void __launch_bounds__(kThreads, min_ctas_per_sm<BN, EPI>()) gemm_kernel(const __grid_constant__ CUtensorMap tmA,
                                                        const __grid_constant__ CUtensorMap tmB,
                                                        const __grid_constant__ CUtensorMap tmC, GemmParams p) {
   constexpr bool kDualA = (EPI == kGatedT);   // gate and proj rows of the stacked weight as two A tiles: transposed (channel-major) output
@@ -404,6 +410,19 @@ __global__ void __launch_bounds__(kThreads) gemm_kernel(const __grid_constant__ 
     TileCoord c;
     for (long long local = 0; ok && tile_at(p, local, c); ++local) {
       const int ab = (int)(local & 1);
+      if (kBwd || EPI == kSigmoidMul) {
+        // the epilogue's second operand of the next tile: ask for this thread's 128 bytes of it now, so that they are
+        // in L2 by the time the rows are read (the reads are one dependent load per chunk, nothing else hides them)
+        TileCoord nx;
+        if (tile_at(p, local + 1, nx)) {
+          const int prow = nx.m_tile * BM + row_in_tile;
+          const int pcol = nx.n_tile * kOutPerTile + chalf * 64;
+          if (prow < p.M && pcol < p.N) {
+            const __nv_bfloat16* src = p.mul + (long long)nx.batch * p.mul_batch_stride + (long long)prow * p.ld_mul + pcol;
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(src));
+          }
+        }
+      }
       if (!ptx::mbar_wait(&acc_full[ab], (uint32_t)(local >> 1) & 1u, p.status, kTimeoutMmaDone)) { ok = false; break; }
       ptx::tc_fence_after();
       const int row = c.m_tile * BM + row_in_tile;
@@ -438,24 +457,35 @@ __global__ void __launch_bounds__(kThreads) gemm_kernel(const __grid_constant__ 
             }
           } else if (EPI == kGated) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) a[j] = sigmoidf_(a[j]) * b[j] * rm;
+            for (int j = 0; j < 32; ++j) a[j] = sigmoid_fast(a[j]) * b[j] * rm;
           } else if (EPI == kGatedT) {
             // rows are output channels, columns are the input rows: the mask runs along the columns
+            if (mask_b != nullptr && n0 + 32 <= p.N && ((reinterpret_cast<uintptr_t>(mask_b + n0) & 15) == 0)) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const float mk = mask_b ? ((n0 + j < p.N) ? mask_b[n0 + j] : 0.f) : 1.f;
-              a[j] = sigmoidf_(a[j]) * b[j] * mk;
+              for (int g4 = 0; g4 < 8; ++g4) {
+                const float4 mk = *reinterpret_cast<const float4*>(mask_b + n0 + 4 * g4);
+                a[4 * g4 + 0] = sigmoid_fast(a[4 * g4 + 0]) * b[4 * g4 + 0] * mk.x;
+                a[4 * g4 + 1] = sigmoid_fast(a[4 * g4 + 1]) * b[4 * g4 + 1] * mk.y;
+                a[4 * g4 + 2] = sigmoid_fast(a[4 * g4 + 2]) * b[4 * g4 + 2] * mk.z;
+                a[4 * g4 + 3] = sigmoid_fast(a[4 * g4 + 3]) * b[4 * g4 + 3] * mk.w;
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                const float mk = mask_b ? ((n0 + j < p.N) ? mask_b[n0 + j] : 0.f) : 1.f;
+                a[j] = sigmoid_fast(a[j]) * b[j] * mk;
+              }
             }
           } else if (EPI == kSwiGLU) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) a[j] = a[j] * sigmoidf_(a[j]) * b[j];
+            for (int j = 0; j < 32; ++j) a[j] = a[j] * sigmoid_fast(a[j]) * b[j];
           } else if (kBwd) {
             const __nv_bfloat16* grow = p.mul + batch * p.mul_batch_stride + (long long)row * p.ld_mul + n0;
             float g[32];
             load_row32(grow, row < p.M, n0, p.N, g);
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
-              const float sg = sigmoidf_(a[j]);
+              const float sg = sigmoid_fast(a[j]);
               const float gj = g[j] * rm;
               const float da = EPI == kSwiGLUBwd ? gj * b[j] * sg * (1.f + a[j] * (1.f - sg)) : gj * b[j] * sg * (1.f - sg);
               const float dbv = EPI == kSwiGLUBwd ? gj * a[j] * sg : gj * sg;
@@ -469,7 +499,7 @@ __global__ void __launch_bounds__(kThreads) gemm_kernel(const __grid_constant__ 
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
               const float bv = (p.bias != nullptr && n0 + j < p.N) ? p.bias[n0 + j] : 0.f;
-              a[j] = sigmoidf_(a[j] + bv) * g[j];
+              a[j] = sigmoid_fast(a[j] + bv) * g[j];
             }
           }
         }
@@ -582,7 +612,8 @@ void launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
   int stages;
   size_t smem;
   if (p.b_resident) {
-    stages = 6;
+    // a short ring when that lets two CTAs share an SM (K = 128: weight 32 KiB + two A blocks + the store boxes)
+    stages = (min_ctas_per_sm<BN, EPI>() == 2 && 2 * S::kABytes + (size_t)p.kb_total * S::kBBytes + extra <= 110 * 1024) ? 2 : 6;
     smem = (size_t)stages * S::kABytes + (size_t)p.kb_total * S::kBBytes + extra;
   } else {
     // a deep ring when the K loop is long; short loops still get enough stages for the loads of the next tile to run
@@ -598,7 +629,7 @@ void launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
     attr_set = true;
   }
   // one CTA per SM, or two when both the shared memory and the tensor-memory columns allow it
-  const int per_sm = (smem <= 110 * 1024 && acc_cols <= 256) ? 2 : 1;
+  const int per_sm = (smem <= 110 * 1024 && acc_cols <= 256 && min_ctas_per_sm<BN, EPI>() == 2) ? 2 : 1;
   long long ctas = std::min<long long>(tiles, (long long)sms * per_sm);
   if (p.b_resident) {
     const long long groups = std::max<long long>(1, std::min<long long>((long long)sms * per_sm / p.n_tiles, (long long)p.m_tiles * p.batch));
@@ -689,7 +720,7 @@ Tensor gemm_impl(const Tensor& a3, const Tensor& w3, const c10::optional<Tensor>
   // accumulator width: the widest tile that the output needs
   int BN;
   if (dual) BN = N >= 128 ? 256 : (N >= 64 ? 128 : 64);
-  else BN = (epi == kPlain && N > 128 && K >= 512 && M > 2048) ? 256 : (N > 64 ? 128 : (N > 32 ? 64 : 32));
+  else BN = (epi == kPlain && N > 128 && K >= 512 && M * batch > 2048 && M >= 256) ? 256 : (N > 64 ? 128 : (N > 32 ? 64 : 32));
   if (o.b_mn && BN < 64) BN = 64;
   const int out_per_tile = dual ? BN / 2 : BN;
 

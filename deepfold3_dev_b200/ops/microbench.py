@@ -74,27 +74,27 @@ def bench_gemm(t: Timer):
     w1 = torch.randn(1024, 128, device="cuda").bfloat16() * 0.1
     o = torch.randn(rows, 128, device="cuda").bfloat16()
     io = lambda *n: 2 * rows * sum(n)  # noqa: E731 - bf16 bytes moved for the given channel counts
-    _report("gemm plain 147456x128->128", t(lambda: df3.gemm(x, w, None, None, None, 0, False)), t(lambda: x @ w.t()),
+    _report(f"gemm plain {rows}x128->128", t(lambda: df3.gemm(x, w, None, None, None, 0, False)), t(lambda: x @ w.t()),
             io(128, 128), 2 * rows * 128 * 128)  # fmt: skip
-    _report("gemm gated 147456x128->128", t(lambda: df3.gemm(x, w2, None, None, None, 1, False)),
+    _report(f"gemm gated {rows}x128->128", t(lambda: df3.gemm(x, w2, None, None, None, 1, False)),
             t(lambda: torch.sigmoid(x @ w2[:128].t()) * (x @ w2[128:].t())), io(128, 128), 2 * rows * 128 * 256)  # fmt: skip
-    _report("gemm swiglu 147456x128->512", t(lambda: df3.gemm(x, w1, None, None, None, 2, False)),
+    _report(f"gemm swiglu {rows}x128->512", t(lambda: df3.gemm(x, w1, None, None, None, 2, False)),
             t(lambda: ref.swiglu(x @ w1.t())), io(128, 512), 2 * rows * 128 * 1024)  # fmt: skip
-    _report("gemm sigmoid-mul 147456x128->128", t(lambda: df3.gemm(x, w, None, None, o, 3, False)),
+    _report(f"gemm sigmoid-mul {rows}x128->128", t(lambda: df3.gemm(x, w, None, None, o, 3, False)),
             t(lambda: torch.sigmoid(x @ w.t()) * o), io(128, 128, 128), 2 * rows * 128 * 128)  # fmt: skip
     w3 = torch.randn(384, 128, device="cuda").bfloat16() * 0.1
-    _report("gemm plain 147456x128->384", t(lambda: df3.gemm(x, w3, None, None, None, 0, False)), t(lambda: x @ w3.t()),
+    _report(f"gemm plain {rows}x128->384", t(lambda: df3.gemm(x, w3, None, None, None, 0, False)), t(lambda: x @ w3.t()),
             io(128, 384), 2 * rows * 128 * 384)  # fmt: skip
-    _report("gemm gated planes 147456x128->128", t(lambda: df3.gemm(x, w2, None, None, None, 1, True)),
+    _report(f"gemm gated planes {rows}x128->128", t(lambda: df3.gemm(x, w2, None, None, None, 1, True)),
             t(lambda: (torch.sigmoid(x @ w2[:128].t()) * (x @ w2[128:].t())).t().contiguous()), io(128, 128), 2 * rows * 128 * 256)  # fmt: skip
-    _report("matmul dx 147456x128 . 128x128", t(lambda: df3.matmul(o, w, False, False, False, 1)), t(lambda: o @ w),
+    _report(f"matmul dx {rows}x128 . 128x128", t(lambda: df3.matmul(o, w, False, False, False, 1)), t(lambda: o @ w),
             io(128, 128), 2 * rows * 128 * 128)  # fmt: skip
-    _report("matmul dw (147456x128)^T . 147456x128", t(lambda: df3.matmul(o, x, True, False, True, 0)), t(lambda: (o.t() @ x).float()),
+    _report(f"matmul dw ({rows}x128)^T . {rows}x128", t(lambda: df3.matmul(o, x, True, False, True, 0)), t(lambda: (o.t() @ x).float()),
             io(128, 128), 2 * rows * 128 * 128)  # fmt: skip
     pa, pb = torch.randn(128, N, N, device="cuda").bfloat16(), torch.randn(128, N, N, device="cuda").bfloat16()
-    _report("triangle contraction out 128x384^3", t(lambda: df3.matmul(pa, pb, False, True, False, 1)),
+    _report(f"triangle contraction out 128x{N}^3", t(lambda: df3.matmul(pa, pb, False, True, False, 1)),
             t(lambda: torch.bmm(pa, pb.transpose(1, 2))), 3 * 2 * 128 * N * N, 2 * 128 * N**3)  # fmt: skip
-    _report("triangle contraction in 128x384^3", t(lambda: df3.matmul(pb, pa, True, False, False, 1)),
+    _report(f"triangle contraction in 128x{N}^3", t(lambda: df3.matmul(pb, pa, True, False, False, 1)),
             t(lambda: torch.bmm(pb.transpose(1, 2), pa)), 3 * 2 * 128 * N * N, 2 * 128 * N**3)  # fmt: skip
     M = 8192
     A, B = torch.randn(M, M, device="cuda").bfloat16(), torch.randn(M, M, device="cuda").bfloat16()
@@ -126,9 +126,12 @@ def bench_elementwise(t: Timer):
     r = torch.randn_like(x)
     w = torch.ones(128, device="cuda")
     nb = x.numel() * 2
-    _report("layer_norm fwd 147456x128", t(lambda: torch.ops.df3.layer_norm_fwd(x, w, w, 1e-5)),
+    planes = torch.randn(128, N * N, device="cuda").bfloat16()
+    _report(f"plane_layer_norm fwd 128x{N * N}", t(lambda: torch.ops.df3.plane_layer_norm_fwd(planes, w, w, 1e-5)),
+            t(lambda: torch.nn.functional.layer_norm(planes.t(), (128,), w.bfloat16(), w.bfloat16())), 2 * nb, 0)  # fmt: skip
+    _report(f"layer_norm fwd {N * N}x128", t(lambda: torch.ops.df3.layer_norm_fwd(x, w, w, 1e-5)),
             t(lambda: torch.nn.functional.layer_norm(x, (128,), w.bfloat16(), w.bfloat16())), 2 * nb, 0)  # fmt: skip
-    _report("dropout_add rows 147456x128", t(lambda: ao.dropout_add(r, x, 0.25, -3, seed=1)),
+    _report(f"dropout_add rows {N * N}x128", t(lambda: ao.dropout_add(r, x, 0.25, -3, seed=1)),
             t(lambda: r + torch.nn.functional.dropout(x, 0.25)), 3 * nb, 0)  # fmt: skip
 
 
@@ -161,7 +164,10 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--op", default="all", choices=["all", "gemm", "attention", "elementwise", "streaming"])
     ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--tokens", type=int, default=384, help="token count of the pair-shaped cases (384: training crop, 1024: inference)")
     args = ap.parse_args()
+    global N
+    N = args.tokens
     native.require()
     t = Timer(args.iters)
     if args.op in ("all", "gemm"):
