@@ -1,0 +1,441 @@
+"""Dataset maintenance commands around a prepared training directory.
+
+Reference: scripts/prepare.py:554-1615 (``fetch-ccd``, ``build-ccd-cache``, ``export-complexes``, ``import-of3``,
+``import-msa``, ``import-paired-msa``, ``enrich-manifest``, ``drop-obsolete``, ``build-of3-cache``,
+``stamp-template-index-space``), scripts/pack.py, scripts/build_masks.py, scripts/refilter.py and
+scripts/warmup_triton.py. The commands keep the reference's names and options; what they do is stated on this
+package's own data layer (``data/types.py`` records, ``data/paths.py`` layout).
+"""
+
+from __future__ import annotations
+
+import glob
+import gzip
+import json
+import os
+import shutil
+
+import click
+import numpy as np
+
+from ..data import paths
+
+
+def _load(data_dir):
+    from ..data.types import load_manifest
+
+    path = paths.manifest(data_dir)
+    if not os.path.exists(path):
+        raise click.ClickException(f"{path} not found: run `prepare structures` first")
+    return path, load_manifest(path)
+
+
+def _chain_sequences(data_dir, records):
+    """``{msa_id: (one-letter sequence, mol_type)}`` of every polymer chain, read from the stored structures."""
+    from ..data import const
+    from ..data.types import Structure
+
+    out = {}
+    for rec in records:
+        want = {c.chain_id: c for c in rec.chains if c.mol_type != const.MOL_NONPOLYMER and c.msa_id not in out}
+        if not want:
+            continue
+        st = Structure.load(paths.structure(data_dir, rec.id))
+        seqs = st.chain_canonical_seqs or {}
+        for chain_id, c in want.items():
+            if chain_id in seqs:
+                out[c.msa_id] = (seqs[chain_id], c.mol_type)
+    return out
+
+
+# --------------------------------------------------------------------------------------------------------- chemical components
+@click.command("fetch-ccd")
+@click.option("--output", required=True, type=click.Path(), help="Directory to save components.cif.gz in.")
+@click.option("--from-file", type=click.Path(exists=True), default=None, help="Copy a local components.cif[.gz] instead of downloading.")
+@click.option("--url", default="https://files.wwpdb.org/pub/pdb/data/monomers/components.cif.gz", show_default=True)
+def fetch_ccd(output, from_file, url):
+    """Get the wwPDB chemical component dictionary (about 100 MB) for `build-ccd-cache`."""
+    os.makedirs(output, exist_ok=True)
+    if from_file:
+        dst = os.path.join(output, os.path.basename(from_file))
+        shutil.copyfile(from_file, dst)
+    else:
+        import urllib.request
+
+        dst = os.path.join(output, "components.cif.gz")
+        try:
+            with urllib.request.urlopen(url, timeout=60) as r, open(dst + ".part", "wb") as f:
+                shutil.copyfileobj(r, f)
+        except OSError as exc:
+            raise click.ClickException(f"download failed ({exc}); fetch the file elsewhere and pass --from-file") from exc
+        os.replace(dst + ".part", dst)
+    click.echo(f"CCD components saved to: {dst}")
+
+
+@click.command("build-ccd-cache")
+@click.option("--components-cif", required=True, type=click.Path(exists=True))
+@click.option("--output", required=True, type=click.Path(), help="JSON cache to write.")
+@click.option("--ref-pos", is_flag=True, help="ETKDG reference conformers (needs RDKit).")
+@click.option("--automorphisms", is_flag=True, help="Heavy-atom graph automorphisms of every ligand.")
+@click.option("--workers", default=1, type=int)
+def build_ccd_cache(components_cif, output, ref_pos, automorphisms, workers):
+    """One JSON with every component's atoms, ideal coordinates, charges, leaving atoms and bonds; with
+    --automorphisms also the atom permutations the ligand-permutation loss uses (graph search, no RDKit)."""
+    from ..data.ccd import export_table
+
+    if ref_pos:
+        try:
+            import rdkit  # noqa: F401
+        except ImportError as exc:
+            raise click.ClickException("--ref-pos generates conformers with RDKit, which is not installed; the cache "
+                                       "keeps the dictionary's ideal coordinates without it") from exc
+    n = export_table(components_cif, output, None)
+    if automorphisms:
+        from ..data.symmetry import graph_automorphisms
+
+        with open(output) as f:
+            table = json.load(f)
+        for comp in table.values():
+            heavy = [i for i, e in enumerate(comp["elements"]) if e != 1]
+            if not 1 < len(heavy) <= 64:
+                continue
+            index = {a: k for k, a in enumerate(heavy)}
+            bonds = [(index[a], index[b], o) for a, b, o in comp["bonds"] if a in index and b in index]
+            perms = graph_automorphisms([comp["elements"][i] for i in heavy], [(a, b) for a, b, _ in bonds], limit=1000,
+                                        orders=[o for _, _, o in bonds])  # fmt: skip
+            if len(perms) > 1:
+                comp["heavy_atoms"] = [comp["atoms"][i] for i in heavy]
+                comp["automorphisms"] = perms
+        with open(output, "w") as f:
+            json.dump(table, f)
+    click.echo(f"{n} components -> {output}")
+
+
+# --------------------------------------------------------------------------------------------------------- manifest tools
+@click.command("export-complexes")
+@click.option("--data-dir", required=True, type=click.Path(exists=True))
+@click.option("--output", required=True, type=click.Path())
+@click.option("--all-mol-types", is_flag=True, help="Include nucleic-acid chains, not just proteins.")
+def export_complexes(data_dir, output, all_mol_types):
+    """``{record id: [sequence, ...]}`` of every record with more than one qualifying chain (input of paired-MSA searches)."""
+    from ..data import const
+
+    _, records = _load(data_dir)
+    seqs = _chain_sequences(data_dir, records)
+    out = {}
+    for rec in records:
+        keep = [seqs[c.msa_id][0] for c in rec.chains
+                if c.msa_id in seqs and (all_mol_types or c.mol_type == const.MOL_PROTEIN)]  # fmt: skip
+        if len(keep) > 1:
+            out[rec.id] = keep
+    with open(output, "w") as f:
+        json.dump(out, f)
+    click.echo(f"{len(out)} complexes -> {output}")
+
+
+def _query_of(a3m_path):
+    opener = gzip.open if a3m_path.endswith(".gz") else open
+    with opener(a3m_path, "rt") as f:
+        seq = []
+        for line in f:
+            if line.startswith(">"):
+                if seq:
+                    break
+                continue
+            if line.startswith("#"):
+                continue
+            seq.append(line.strip())
+    return "".join(ch for ch in "".join(seq) if ch.isupper() or ch == "-").replace("-", "")
+
+
+def _store_alignment(src, dst_base, mol_type, keep_a3m):
+    from ..data.parse.a3m import msa_from_a3m_file
+
+    if os.path.exists(dst_base + ".npz"):
+        return False
+    os.makedirs(os.path.dirname(dst_base), exist_ok=True)
+    msa_from_a3m_file(src, mol_type).save(dst_base + ".npz")
+    if keep_a3m:
+        shutil.copyfile(src, dst_base + ".a3m")
+    return True
+
+
+@click.command("import-msa")
+@click.option("--data-dir", required=True, type=click.Path(exists=True))
+@click.option("--msa-dir", required=True, type=click.Path(exists=True), help="A3M files, any naming, scanned recursively.")
+@click.option("--workers", default=1, type=int, show_default=True)
+@click.option("--keep-a3m", is_flag=True)
+def import_msa(data_dir, msa_dir, workers, keep_a3m):
+    """Attach existing A3M files to the chains whose sequence equals the file's query; writes msa/<msa_id>.npz."""
+    _, records = _load(data_dir)
+    by_seq = {}
+    for msa_id, (seq, mol_type) in _chain_sequences(data_dir, records).items():
+        by_seq.setdefault(seq, []).append((msa_id, mol_type))
+    files = [p for p in glob.glob(os.path.join(msa_dir, "**", "*.a3m*"), recursive=True) if os.path.isfile(p)]
+    jobs = []
+    for path in files:
+        for msa_id, mol_type in by_seq.get(_query_of(path), ()):
+            jobs.append((path, os.path.join(data_dir, "msa", str(msa_id)), mol_type, keep_a3m))
+    if workers > 1 and len(jobs) > 1:
+        from concurrent.futures import ProcessPoolExecutor
+
+        with ProcessPoolExecutor(workers) as pool:
+            written = sum(pool.map(_store_alignment, *zip(*jobs)))
+    else:
+        written = sum(_store_alignment(*j) for j in jobs)
+    click.echo(f"{len(files)} alignments scanned, {len(jobs)} matched a chain, {written} written")
+
+
+@click.command("import-paired-msa")
+@click.option("--data-dir", required=True, type=click.Path(exists=True))
+@click.option("--paired-dir", required=True, type=click.Path(exists=True), help="<record id>/<msa_id>.paired.a3m")
+@click.option("--workers", default=1, type=int, show_default=True)
+@click.option("--keep-a3m", is_flag=True)
+def import_paired_msa(data_dir, paired_dir, workers, keep_a3m):
+    """Attach paired alignments made outside: rows of msa_paired/<record id>/<msa_id>.npz pair up across the chains of a record."""
+    path, records = _load(data_dir)
+    written = touched = 0
+    for rec in records:
+        src_dir = os.path.join(paired_dir, rec.id)
+        if not os.path.isdir(src_dir):
+            continue
+        for c in rec.chains:
+            src = os.path.join(src_dir, f"{c.msa_id}.paired.a3m")
+            if not os.path.exists(src):
+                continue
+            key = f"{rec.id}/{c.msa_id}"
+            written += _store_alignment(src, os.path.join(data_dir, "msa_paired", key), c.mol_type, keep_a3m)
+            if c.paired_msa_id != key:
+                c.paired_msa_id, touched = key, touched + 1
+    if touched:
+        from ..data.types import save_manifest
+
+        save_manifest(records, path)
+    click.echo(f"{written} paired alignments written, {touched} chains pointed at them")
+
+
+def _read_entries_idx(path):
+    """wwPDB entries.idx: IDCODE, HEADER, ACCESSION DATE (mm/dd/yy), COMPOUND, SOURCE, AUTHORS, RESOLUTION, EXPERIMENT TYPE."""
+    out = {}
+    with open(path, errors="replace") as f:
+        for line in f:
+            cols = line.rstrip("\n").split("\t")
+            if len(cols) < 8 or len(cols[0]) != 4:
+                continue
+            date = None
+            parts = cols[2].split("/")
+            if len(parts) == 3 and all(p.isdigit() for p in parts):
+                mm, dd, yy = (int(p) for p in parts)
+                date = f"{(1900 if yy >= 70 else 2000) + yy:04d}-{mm:02d}-{dd:02d}"
+            try:
+                res = float(cols[6].split(",")[0])
+            except ValueError:
+                res = None
+            out[cols[0].lower()] = {"resolution": res, "method": cols[7].strip() or None, "deposited": date}
+    return out
+
+
+@click.command("enrich-manifest")
+@click.option("--data-dir", required=True, type=click.Path(exists=True))
+@click.option("--idx", type=click.Path(exists=True), default=None, help="wwPDB derived_data/index/entries.idx")
+@click.option("--mmcif-cache", type=click.Path(exists=True), default=None, help="JSON written by `scan-mmcif`.")
+def enrich_manifest(data_dir, idx, mmcif_cache):
+    """Fill blank resolution / method / deposited / released fields of the manifest; fields already set are kept."""
+    from ..data.types import StructureInfo, save_manifest
+
+    if not idx and not mmcif_cache:
+        raise click.ClickException("give --idx and/or --mmcif-cache")
+    sources = []
+    if idx:
+        sources.append(_read_entries_idx(idx))
+    if mmcif_cache:
+        with open(mmcif_cache) as f:
+            rows = json.load(f)
+        rows = rows.values() if isinstance(rows, dict) else rows
+        sources.append({str(r["id"]).lower(): r for r in rows if "id" in r})
+    path, records = _load(data_dir)
+    filled = 0
+    for rec in records:
+        info = rec.structure_info or StructureInfo()
+        for table in sources:
+            row = table.get(rec.id.lower()[:4]) or table.get(rec.id.lower())
+            if not row:
+                continue
+            for field in ("resolution", "method", "deposited", "released"):
+                if getattr(info, field) in (None, "") and row.get(field) not in (None, ""):
+                    setattr(info, field, row[field])
+                    filled += 1
+        rec.structure_info = info
+    save_manifest(records, path)
+    click.echo(f"{filled} fields filled in {len(records)} records")
+
+
+@click.command("drop-obsolete")
+@click.option("--data-dir", required=True, type=click.Path(exists=True))
+@click.option("--ids-file", type=click.Path(exists=True), default=None, help="obsolete.dat or a JSON list of ids (default: download).")
+@click.option("--delete-files", is_flag=True, help="Also delete the dropped records' structure / mask files.")
+def drop_obsolete(data_dir, ids_file, delete_files):
+    """Remove records whose PDB entry has been made obsolete."""
+    from ..data.types import save_manifest
+
+    if ids_file:
+        with open(ids_file) as f:
+            text = f.read()
+    else:
+        import urllib.request
+
+        try:
+            with urllib.request.urlopen("https://files.wwpdb.org/pub/pdb/data/status/obsolete.dat", timeout=60) as r:
+                text = r.read().decode()
+        except OSError as exc:
+            raise click.ClickException(f"download failed ({exc}); pass --ids-file") from exc
+    if text.lstrip().startswith("["):
+        gone = {str(i).lower() for i in json.loads(text)}
+    else:  # "OBSLTE    31-JUL-94 116L     216L"
+        gone = {cols[2].lower() for cols in (line.split() for line in text.splitlines()) if len(cols) >= 3 and cols[0] == "OBSLTE"}
+    path, records = _load(data_dir)
+    keep = [r for r in records if r.id.lower()[:4] not in gone]
+    dropped = [r for r in records if r.id.lower()[:4] in gone]
+    save_manifest(keep, path)
+    if delete_files:
+        for r in dropped:
+            for p in (paths.structure(data_dir, r.id), paths.mask(data_dir, r.id), paths.features(data_dir, r.id)):
+                if os.path.exists(p):
+                    os.remove(p)
+    click.echo(f"{len(dropped)} obsolete records dropped, {len(keep)} kept")
+
+
+# --------------------------------------------------------------------------------------------------------- OpenFold 3 data
+@click.command("import-of3")
+@click.option("--of3-dir", required=True, type=click.Path(exists=True), help="<id>/<id>.npz or flat *.npz atom arrays.")
+@click.option("--output", required=True, type=click.Path())
+@click.option("--cache", type=click.Path(exists=True), default=None, help="OpenFold 3 dataset_cache.json (resolution, dates).")
+@click.option("--limit", type=int, default=None)
+def import_of3(of3_dir, output, cache, limit):
+    """Convert OpenFold 3 preprocessed structures (atom-array .npz) into this package's structures + manifest."""
+    from ..data.of3 import convert_directory
+
+    n, skipped = convert_directory(of3_dir, output, cache, limit)
+    click.echo(f"{n} structures imported into {output} ({skipped} skipped)")
+
+
+@click.command("build-of3-cache")
+@click.option("--cache-file", required=True, type=click.Path(exists=True))
+@click.option("--output", required=True, type=click.Path(), help="Directory for the columnar cache.")
+@click.option("--no-templates", is_flag=True)
+def build_of3_cache(cache_file, output, no_templates):
+    """Turn an OpenFold 3 dataset cache JSON into memory-mappable ``.npy`` columns (one open per worker instead of one
+    multi-gigabyte JSON parse per worker)."""
+    from ..data.of3 import build_columnar_cache
+
+    entries, chains = build_columnar_cache(cache_file, output, not no_templates)
+    click.echo(f"{entries} entries, {chains} chains -> {output}")
+
+
+@click.command("stamp-template-index-space")
+@click.option("--data-dir", required=True, type=click.Path(exists=True))
+@click.option("--space", type=click.Choice(["struct", "seqres"]), default="struct", show_default=True)
+@click.option("--workers", default=16, type=int, show_default=True)
+@click.option("--dry-run", is_flag=True)
+def stamp_template_index_space(data_dir, space, workers, dry_run):
+    """Record in every template index file which residue numbering its template-side positions use (positions among
+    the resolved residues, or positions in the full sequence), so that the loader need not be told per dataset."""
+    files = []
+    for sub in ("templates", "monomer_templates"):
+        files += glob.glob(os.path.join(data_dir, sub, "**", "*.json"), recursive=True)
+    changed = 0
+    for path in files:
+        with open(path) as f:
+            doc = json.load(f)
+        holder = doc if isinstance(doc, dict) else None
+        if holder is None:
+            doc = holder = {"hits": doc}
+        if holder.get("index_space") == space:
+            continue
+        if "index_space" in holder and holder["index_space"] != space:
+            raise click.ClickException(f"{path} is already stamped {holder['index_space']!r}")
+        changed += 1
+        if dry_run:
+            continue
+        holder["index_space"] = space
+        tmp = path + ".tmp"
+        with open(tmp, "w") as f:
+            json.dump(doc, f)
+        os.replace(tmp, path)
+    click.echo(f"{len(files)} index files, {changed} {'would be ' if dry_run else ''}stamped {space!r}")
+
+
+# --------------------------------------------------------------------------------------------------------- packs, kernels
+@click.command("pack")
+@click.argument("src_dir", type=click.Path(exists=True))
+@click.argument("out_dir", type=click.Path())
+@click.option("--shard-size", type=int, default=1 << 30, show_default=True, help="Bytes per tar shard.")
+def pack(src_dir, out_dir, shard_size):
+    """Bundle a directory of small files into tar shards with an index."""
+    from ..data.pack import build_pack
+
+    click.echo(f"{build_pack(src_dir, out_dir, shard_size)} files -> {out_dir}")
+
+
+@click.command("pack-verify")
+@click.argument("src_dir", type=click.Path(exists=True))
+@click.argument("pack_dir", type=click.Path(exists=True))
+@click.option("--sample", type=int, default=0, help="Check only this many files (0 = all).")
+def pack_verify(src_dir, pack_dir, sample):
+    """Compare every file of SRC_DIR byte for byte with what the pack returns for its name."""
+    from ..data.pack import Pack
+
+    pk = Pack(pack_dir)
+    names = sorted(n for n in os.listdir(src_dir) if os.path.isfile(os.path.join(src_dir, n)))
+    if sample:
+        names = names[:: max(1, len(names) // sample)][:sample]
+    bad = []
+    for name in names:
+        with open(os.path.join(src_dir, name), "rb") as f:
+            if not pk.exists(name) or pk.read_bytes(name) != f.read():
+                bad.append(name)
+    pk.close()
+    if bad:
+        raise click.ClickException(f"{len(bad)} of {len(names)} files differ or are missing, first: {bad[:5]}")
+    click.echo(f"{len(names)} files verified")
+
+
+@click.command("warmup-kernels")
+@click.option("--tokens", type=int, multiple=True, default=(384,), help="Token counts to run the pair-shaped kernels at.")
+@click.option("--build/--no-build", default=True, help="Compile the extension first if it is stale.")
+def warmup_kernels(tokens, build):
+    """Build (if needed) and load the sm_100a extension and run each kernel family once per token count, so that the
+    first training step or prediction pays no one-time cost (the reference's `warmup-triton` autotunes its Triton
+    kernels at this point; these kernels have nothing to tune)."""
+    import torch
+
+    from ..ops import build as ops_build
+    from ..ops import native
+
+    if build:
+        click.echo(ops_build.build())
+    nat = native.require()
+    if not torch.cuda.is_available():
+        raise click.ClickException("no CUDA device")
+    from .. import ops
+
+    for n in tokens:
+        z = torch.randn(1, n, n, 128, device="cuda").bfloat16()
+        mask = torch.ones(1, n, n, device="cuda")
+        w = torch.randn(256, 128, device="cuda") * 0.05
+        with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
+            z0 = ops.layer_norm(z, None, None)
+            ops.triangle_contract_norm(z0, w, w, mask, True, None, None)
+            ops.sigmoid_gate_mul(z0, w[:128], z0)
+            bias = ops.head_bias_planes(z0, w[:4])
+            qkv = ops.stacked_linear(z0, w[:128], w[:128], w[:128]).view(1, n, n, 3, 4, 32)
+            ops.grid_attention(qkv, bias, mask, 32**-0.5, False)
+            ops.transition(z, None, None, torch.randn(1024, 128, device="cuda") * 0.05, torch.randn(128, 512, device="cuda") * 0.05)
+        torch.cuda.synchronize()
+        click.echo(f"{n} tokens: ok")
+    nat.check_status()
+    click.echo(json.dumps(ops.census(), indent=1))
+
+
+COMMANDS = (fetch_ccd, build_ccd_cache, export_complexes, import_msa, import_paired_msa, enrich_manifest, drop_obsolete,
+            import_of3, build_of3_cache, stamp_template_index_space, pack, pack_verify, warmup_kernels)

@@ -142,7 +142,8 @@ def _inference_options(f):
         click.option("--device", default=None),
         click.option("--optim", type=click.Choice(["none", "inference", "inference-cueq", "train-matched"]), default="inference"),
         click.option("--precision", type=click.Choice(list(DTYPES)), default="bf16"),
-        click.option("--logits-scheme", type=click.Choice(["f16", "u8", "f32"]), default="f16"),
+        click.option("--logits-scheme", type=click.Choice(["float32", "float16", "int8", "int8_softmax", "int4_softmax", "f16", "u8", "f32"]),
+                     default="int8_softmax", show_default=True, help="How logits.npz stores the head logits (f16 / u8 / f32: earlier names)."),
         click.option("--bucket/--no-bucket", default=True),
         click.option("--sample-chunk", type=int, default=0),
         click.option("--guidance", "guidance", multiple=True,
@@ -503,6 +504,15 @@ def bench_kernels(op):
 from . import prepare as _prepare  # noqa: E402
 
 _prepare.register(cli)
+
+from . import dataset_tools as _dataset_tools  # noqa: E402
+
+for _command in _dataset_tools.COMMANDS:
+    cli.add_command(_command)
+# names the reference uses for commands that live in the `prepare` group here, and for its kernel warm-up
+cli.add_command(_prepare.masks, "build-masks")
+cli.add_command(_prepare.refilter, "refilter")
+cli.add_command(_dataset_tools.warmup_kernels, "warmup-triton")
 
 
 def main():

@@ -96,8 +96,14 @@ def select_tokens(feats: dict, keep: torch.Tensor) -> dict:
 
 
 def crop(feats: dict, max_tokens: int, max_atoms: int = 0, gen: torch.Generator | None = None, weights: dict | None = None,
-         strategy: str | None = None) -> tuple[dict, str]:  # fmt: skip
-    """Crop to the budgets; returns the cropped features and the strategy used."""
+         strategy: str | None = None, return_keep: bool = False):  # fmt: skip
+    """Crop to the budgets; returns the cropped features and the strategy used (with ``return_keep`` also the sorted
+    indices of the tokens kept, ``None`` when nothing was cut)."""
+    out = _crop(feats, max_tokens, max_atoms, gen, weights, strategy)
+    return out if return_keep else out[:2]
+
+
+def _crop(feats, max_tokens, max_atoms, gen, weights, strategy):
     gen = gen or torch.Generator().manual_seed(int(torch.randint(0, 2**31 - 1, (1,))))
     n = int(feats["res_type"].shape[0])
     w = weights or CROP_WEIGHTS
@@ -105,11 +111,11 @@ def crop(feats: dict, max_tokens: int, max_atoms: int = 0, gen: torch.Generator 
         names = list(w)
         strategy = names[int(torch.multinomial(torch.tensor([float(w[k]) for k in names]), 1, generator=gen))]
     if n <= max_tokens and (max_atoms <= 0 or int(feats["ref_mask"].sum()) <= max_atoms):
-        return feats, "none"
+        return feats, "none", None
     if strategy == "contiguous":
         keep = contiguous_crop(feats["asym_id"], max_tokens, gen)
     else:
         coords, valid = _center_coords(feats)
         keep = spatial_crop(coords.float(), valid, feats["asym_id"], max_tokens, gen, strategy == "spatial_interface")
     keep = apply_atom_budget(keep, feats["ref_mask"], max_atoms)
-    return select_tokens(feats, keep), strategy
+    return select_tokens(feats, keep), strategy, keep

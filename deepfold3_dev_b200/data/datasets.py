@@ -132,6 +132,17 @@ class BatchStream:
     def __init__(self, dataset, sampler, batch_size: int = 1, pad_tokens_to: int | None = None, max_retries: int = 20):
         self.dataset, self.sampler, self.batch_size = dataset, sampler, batch_size
         self.pad_tokens_to, self.max_retries, self.dropped = pad_tokens_to, max_retries, 0
+        self.served = self.retries = 0
+        self.errors: dict[str, int] = {}   # exception type -> how many examples it cost (reference: dataset.py:99-191)
+
+    def counters(self) -> dict:
+        """Log entries: examples served and dropped, retries, and the drop count per exception type."""
+        out = {"data/served": self.served, "data/dropped": self.dropped, "data/retries": self.retries}
+        out.update({f"data/dropped/{name}": n for name, n in sorted(self.errors.items())})
+        for key in ("msa_read", "msa_skipped"):
+            if hasattr(self.dataset, key):
+                out[f"data/{key}"] = getattr(self.dataset, key)
+        return out
 
     def __iter__(self):
         return self
@@ -139,14 +150,22 @@ class BatchStream:
     def __next__(self) -> dict:
         items = []
         while len(items) < self.batch_size:
-            for _ in range(self.max_retries):
+            for attempt in range(self.max_retries):
                 try:
                     items.append(self.dataset[next(self.sampler)])
+                    self.served += 1
+                    self.retries += attempt
                     break
                 except StopIteration:
                     raise
-                except Exception:  # noqa: BLE001 - a broken example must not stop the run
+                except Exception as exc:  # noqa: BLE001 - a broken example must not stop the run
                     self.dropped += 1
+                    name = type(exc).__name__
+                    self.errors[name] = self.errors.get(name, 0) + 1
+                    if self.errors[name] <= 3:
+                        import logging
+
+                        logging.getLogger(__name__).warning("dropping an example (%s: %s)", name, exc)
             else:
                 raise RuntimeError(f"{self.max_retries} consecutive examples failed to load")
         return collate(items, self.pad_tokens_to)
@@ -238,6 +257,7 @@ class StructureDataset:
         self.msa_dir = msa_dir or os.path.join(root, "msa")
         self.records = [r for r in load_manifest(os.path.join(root, "manifest.json")) if any(c.valid for c in r.chains)]
         self.records = apply_date_cutoff(self.records, cutoff_date, keep_after)
+        self.msa_read = self.msa_skipped = 0  # alignments opened / never opened because their chain was cropped away
 
     def __len__(self):
         return len(self.records)
@@ -276,40 +296,55 @@ class StructureDataset:
         return None
 
     def __getitem__(self, i: int) -> dict:
-        import random
-
-        from .featurize import featurize_structure
-        from .prepare.filters import select_interface_chains
         from .types import Structure
 
         rec = self.records[i % len(self.records)]
-        gen = torch.Generator().manual_seed(self.seed * 7_654_321 + i)
-        rng = random.Random(self.seed * 7_654_321 + i)
         st = Structure.load(os.path.join(self.root, "structures", f"{rec.id}.npz"))
-        valid = [c for c in rec.chains if c.valid]
-        faces = [f for f in rec.interfaces if f.valid]
-        if faces and rng.random() < 0.5:
-            f = rng.choice(faces)
-            anchor = ("interface", f.chain_1, f.chain_2)
-        else:
-            anchor = ("chain", rng.choice(valid).chain_id, -1)
-        keep = select_interface_chains(st, anchor, self.max_chains, rng=rng) & {c.chain_id for c in valid}
-        old_ids = sorted(keep)
-        sub = st.select_chains(old_ids)
-        msas = {}
-        for new_id, old in enumerate(old_ids):
-            m = self._msa(rec.chains[old])
-            if m is not None:
-                msas[new_id] = m
-        feats = featurize_structure(sub, None, unpaired_msa=msas, max_msa_rows=self.max_msa_rows)
-        feats, strategy = cropper.crop(feats, self.max_tokens, self.max_atoms, gen, self.crop_weights)
-        feats = rotate_reference_conformers(feats, gen)
-        info = rec.structure_info
-        feats["resolution"] = torch.tensor(float(info.resolution) if info and info.resolution else 0.0)
-        feats["is_distillation"] = torch.tensor(bool(self.is_distillation))
-        feats["_record_id"] = rec.id
-        feats["_crop"] = strategy
+        feats, read, skipped = featurize_record(
+            st, rec, lambda chain: self._msa(chain), max_tokens=self.max_tokens, max_atoms=self.max_atoms,
+            crop_weights=self.crop_weights, max_chains=self.max_chains, max_msa_rows=self.max_msa_rows,
+            seed=self.seed * 7_654_321 + i, is_distillation=self.is_distillation,
+        )  # fmt: skip
+        self.msa_read, self.msa_skipped = self.msa_read + read, self.msa_skipped + skipped
         return feats
+
+
+def featurize_record(st, rec, load_msa, *, max_tokens: int = 384, max_atoms: int = 0, crop_weights: dict | None = None,
+                     max_chains: int = 20, max_msa_rows: int = 16384, seed: int = 0, is_distillation: bool = False):
+    """One training example from a stored structure and its manifest record: pick the anchor chain or interface,
+    pre-crop large assemblies to the chains around it, featurise, crop to the token budget, read the alignments of
+    what survived (``load_msa(chain_info)`` -> ``MSA`` or ``None``), rotate the reference conformers. Returns the
+    features and the numbers of alignments read and skipped."""
+    import random
+
+    from .featurize import attach_cropped_msa, featurize_structure
+    from .prepare.filters import select_interface_chains
+
+    gen = torch.Generator().manual_seed(seed)
+    rng = random.Random(seed)
+    valid = [c for c in rec.chains if c.valid]
+    faces = [f for f in rec.interfaces if f.valid]
+    if faces and rng.random() < 0.5:
+        f = rng.choice(faces)
+        anchor = ("interface", f.chain_1, f.chain_2)
+    else:
+        anchor = ("chain", rng.choice(valid).chain_id, -1)
+    keep = select_interface_chains(st, anchor, max_chains, rng=rng) & {c.chain_id for c in valid}
+    old_ids = sorted(keep)
+    sub = st.select_chains(old_ids)
+    # crop first, then read alignments only for the chains (and columns) that survived
+    feats = featurize_structure(sub, None, max_msa_rows=max_msa_rows, with_msa=False)
+    chain_cols = feats.pop("_chain_cols")
+    feats, strategy, kept = cropper.crop(feats, max_tokens, max_atoms, gen, crop_weights, return_keep=True)
+    feats, read, skipped = attach_cropped_msa(feats, kept, chain_cols, lambda a: load_msa(rec.chains[old_ids[a]]),
+                                              max_msa_rows=max_msa_rows)  # fmt: skip
+    feats = rotate_reference_conformers(feats, gen)
+    info = rec.structure_info
+    feats["resolution"] = torch.tensor(float(info.resolution) if info and info.resolution else 0.0)
+    feats["is_distillation"] = torch.tensor(bool(is_distillation))
+    feats["_record_id"] = rec.id
+    feats["_crop"] = strategy
+    return feats, read, skipped
 
 
 def open_dataset(path: str, **kw):

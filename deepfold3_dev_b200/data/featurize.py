@@ -129,8 +129,10 @@ def msa_block(feats: dict, chain_cols: dict[int, tuple[int, int]], paired: dict[
 
 def featurize_structure(st: Structure, record: Record | None = None, paired_msa: dict[int, MSA] | None = None,
                         unpaired_msa: dict[int, MSA] | None = None, only_valid: bool = True,
-                        max_msa_rows: int = const.MAX_MSA_ROWS) -> dict:  # fmt: skip
-    """The unbatched, uncropped feature dict of one entry (tensors on CPU)."""
+                        max_msa_rows: int = const.MAX_MSA_ROWS, with_msa: bool = True) -> dict:  # fmt: skip
+    """The unbatched, uncropped feature dict of one entry (tensors on CPU). ``with_msa=False`` leaves the alignment
+    block out and returns the token range of every chain under ``"_chain_cols"`` instead, for callers that crop first
+    and read alignments only for what survives (``attach_cropped_msa``)."""
     keep = None
     if record is not None and only_valid:
         keep = {c.chain_id for c in record.chains if c.valid}
@@ -150,8 +152,41 @@ def featurize_structure(st: Structure, record: Record | None = None, paired_msa:
     feats["atom_gt_positions"] = gt * gt_mask.unsqueeze(-1)
     feats["atom_gt_mask"] = gt_mask
     feats["bond_matrix"] = token_bonds(st, atom_rows, feats).float().unsqueeze(-1)  # [N, N, 1], read by the trunk
-    feats.update(msa_block(feats, chain_cols, paired_msa, unpaired_msa, max_msa_rows))
+    if with_msa:
+        feats.update(msa_block(feats, chain_cols, paired_msa, unpaired_msa, max_msa_rows))
+    else:
+        feats["_chain_cols"] = dict(chain_cols)
     info = record.structure_info if record is not None else None
     feats["resolution"] = torch.tensor(float(info.resolution) if info and info.resolution else const.RESOLUTION_UNKNOWN)
     feats["is_distillation"] = torch.tensor(False)
     return feats
+
+
+def attach_cropped_msa(feats: dict, keep, chain_cols: dict[int, tuple[int, int]], load_msa, load_paired=None,
+                       max_msa_rows: int = const.MAX_MSA_ROWS) -> tuple[dict, int, int]:
+    """Alignment block of an example that was cropped first (reference: data/module/dataset.py:425-602).
+
+    ``feats`` are the cropped features, ``keep`` the sorted indices of the surviving tokens in the uncropped example
+    (``None``: nothing was cut) and ``chain_cols`` the uncropped token range of every chain. ``load_msa(asym_id)`` /
+    ``load_paired(asym_id)`` are called only for chains that still have tokens; their alignments are cut to the
+    surviving columns before rows are assembled, so a 384-token crop of a large assembly never reads the alignments
+    of the chains it dropped. Returns the features and how many alignments were read and skipped."""
+    n_all = max((e for _, e in chain_cols.values()), default=0)
+    keep_np = np.arange(n_all) if keep is None else np.asarray(keep)
+    new_cols, unpaired, paired, read, skipped = {}, {}, {}, 0, 0
+    for asym, (s, e) in chain_cols.items():
+        pos = np.flatnonzero((keep_np >= s) & (keep_np < e))
+        if len(pos) == 0:
+            skipped += 1
+            continue
+        new_cols[asym] = (int(pos[0]), int(pos[-1]) + 1)
+        cols = keep_np[pos] - s
+        for loader, store in ((load_msa, unpaired), (load_paired, paired)):
+            m = loader(asym) if loader is not None else None
+            if m is None or m.is_empty or m.sequences.shape[1] != e - s:
+                continue
+            read += 1
+            store[asym] = MSA(m.sequences[:, cols], m.mask[:, cols], m.deletion_matrix[:, cols])
+    out = dict(feats)
+    out.update(msa_block(out, new_cols, paired or None, unpaired or None, max_msa_rows))
+    return out, read, skipped

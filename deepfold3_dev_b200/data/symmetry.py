@@ -354,3 +354,62 @@ def apply_chain_permutation_tokens(gt_pos, atom_mask, asym_id, chain_assignment,
         return gt_pos.detach(), atom_mask.detach()
     index, keep = chain_permutation_index(asym_id, chain_assignment, sym_token_index, device=gt_pos.device)
     return gt_pos.index_select(-3, index).detach(), (atom_mask.index_select(0, index) & keep.unsqueeze(-1)).detach()
+
+
+def graph_automorphisms(elements, edges, limit: int = 1000, orders=None) -> list[list[int]]:
+    """Atom permutations of a ligand that keep its chemistry: ``perm[i]`` is the atom that takes the place of atom ``i``,
+    elements, bonds (and bond orders when given) preserved. The identity comes first; the search stops at ``limit``
+    permutations. This is what the ligand atom-permutation loss consumes as ``ligand_perms`` (reference:
+    data/symmetry/ligand_perms.py:110-172, there through RDKit substructure matching; here a direct search: colour
+    refinement by element and neighbourhood, then backtracking over atoms of equal colour)."""
+    n = len(elements)
+    adj: list[dict[int, int]] = [dict() for _ in range(n)]
+    for k, (a, b) in enumerate(edges):
+        order = 1 if orders is None else int(orders[k])
+        adj[a][b] = adj[b][a] = order
+    colour = [(int(e), len(adj[i])) for i, e in enumerate(elements)]
+    for _ in range(n):  # 1-dimensional Weisfeiler-Leman refinement until stable
+        sig = [(colour[i], tuple(sorted((colour[j], o) for j, o in adj[i].items()))) for i in range(n)]
+        ids = {s_: k for k, s_ in enumerate(sorted(set(sig)))}
+        new = [ids[s_] for s_ in sig]
+        if len(set(new)) == len(set(colour)):
+            colour = new
+            break
+        colour = new
+    # visit atoms so that each one (after the first of a component) touches an atom already placed
+    order_, seen = [], set()
+    for start in sorted(range(n), key=lambda i: (sum(1 for c in colour if c == colour[i]), i)):
+        if start in seen:
+            continue
+        queue = [start]
+        seen.add(start)
+        while queue:
+            i = queue.pop(0)
+            order_.append(i)
+            for j in sorted(adj[i]):
+                if j not in seen:
+                    seen.add(j)
+                    queue.append(j)
+    out: list[list[int]] = []
+    perm, used = [-1] * n, [False] * n
+
+    def place(depth: int) -> bool:
+        if depth == n:
+            out.append(list(perm))
+            return len(out) >= limit
+        i = order_[depth]
+        placed = order_[:depth]
+        for j in range(n):
+            if used[j] or colour[j] != colour[i]:
+                continue
+            if any(adj[i].get(k) != adj[j].get(perm[k]) for k in placed):
+                continue
+            perm[i], used[j] = j, True
+            if place(depth + 1):
+                return True
+            perm[i], used[j] = -1, False
+        return False
+
+    place(0)
+    out.sort(key=lambda p_: p_ != list(range(n)))
+    return out

@@ -120,7 +120,7 @@ def predict_distributed(model, features: dict, seed: int, num_recycles: int, num
 
 
 def write_seed(out_dir: str, job_name: str, seed: int, output, features: dict, chain_names, writer: BackgroundWriter,
-               logits_scheme: str = "f16", save_distogram: bool = True, indices=None) -> list[dict]:  # fmt: skip
+               logits_scheme: str = "int8_softmax", save_distogram: bool = True, indices=None) -> list[dict]:  # fmt: skip
     """Files of the samples in ``output``; ``indices`` are their numbers within the seed when ``output`` holds only a
     subset (one prediction spread over several GPUs)."""
     host = logits_to_host(output)
@@ -151,7 +151,7 @@ def write_seed(out_dir: str, job_name: str, seed: int, output, features: dict, c
 
 def run_job(model, inp, out_dir: str, device, seeds=None, num_recycles: int = 10, num_samples: int = 5,
             dtype=torch.bfloat16, use_bucket: bool = True, sample_chunk: int = 0, skip_existing: bool = False,
-            logits_scheme: str = "f16", save_distogram: bool = True, guidance_terms=None, restraint_kwargs=None,
+            logits_scheme: str = "int8_softmax", save_distogram: bool = True, guidance_terms=None, restraint_kwargs=None,
             manifest_fields: dict | None = None, dist_info=None) -> list[dict]:  # fmt: skip
     """All seeds of one job; returns the per-sample summaries (also written as CSV / JSON). With a ``dist_info`` of more
     than one rank every prediction is spread over the ranks (``predict_distributed``): each rank writes the sample

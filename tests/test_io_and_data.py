@@ -170,7 +170,7 @@ def test_bucket_pad_unpad_preserves_prediction():
     torch.testing.assert_close(b.atom_positions, a.atom_positions, atol=2e-3, rtol=1e-3)
 
 
-def test_af3_record_reader_and_name_map(tmp_path):
+def test_af3_record_reader(tmp_path):
     from deepfold3_dev_b200.convert import af3
 
     def record(scope, name, arr, dtype=None):
@@ -185,13 +185,7 @@ def test_af3_record_reader_and_name_map(tmp_path):
     path.write_bytes(record("trunk/stack/linear", "weights", w) + record("head/norm", "scale", bf, "bfloat16"))
     params = af3.read_af3_params(str(path))
     assert params["head/norm"]["scale"].tolist() == [1.5, -2.0]
-    rules = [{"scope": r"trunk/stack/(\w+)", "name": "weights", "key": "blocks.{layer}.{1}.weight", "transpose": True, "stack_axis": 0},
-             {"scope": "head/norm", "name": "scale", "key": "head.norm.weight"}]  # fmt: skip
-    state = af3.apply_name_map(params, rules)
-    assert set(state) == {"blocks.0.linear.weight", "blocks.1.linear.weight", "head.norm.weight"}
-    assert state["blocks.1.linear.weight"].shape == (4, 3) and state["blocks.1.linear.weight"][0, 0] == 12
-    with pytest.raises(KeyError):
-        af3.apply_name_map(params, rules[:1])
+    assert params["trunk/stack/linear"]["weights"].shape == (2, 3, 4) and params["trunk/stack/linear"]["weights"][1, 0, 0] == 12
 
 
 def test_inference_runner_writes_the_output_tree(tmp_path):
@@ -397,3 +391,153 @@ def test_species_pairing_atomisation_masks_and_io_cache(tmp_path):
     np.savez(tmp_path / "x.npz", a=np.arange(4))
     assert io_cache.read_npz(str(tmp_path / "x.npz"))["a"].tolist() == [0, 1, 2, 3]
     io_cache.set_drop_page_cache(False)
+
+
+def test_crop_before_alignment_load_equals_crop_after(tmp_path):
+    """Cropping first and reading only the surviving chains' alignments gives the features of the old order
+    (featurise with every alignment, then crop), and chains cropped away are never read."""
+    from deepfold3_dev_b200.data import cropper
+    from deepfold3_dev_b200.data.featurize import attach_cropped_msa, msa_block
+    from deepfold3_dev_b200.data.synthetic import synthetic_complex
+    from deepfold3_dev_b200.data.types import MSA
+
+    feats = synthetic_complex([("protein", 30), ("protein", 24), ("protein", 20)], num_msa=1, num_templates=0, seed=3)
+    feats = {k: v for k, v in feats.items() if k not in ("msa", "msa_mask", "deletion_matrix", "profile", "deletion_mean", "has_deletion", "deletion_value")}
+    cols = {0: (0, 30), 1: (30, 54), 2: (54, 74)}
+    rng = np.random.default_rng(0)
+    msas = {}
+    for a, (s, e) in cols.items():
+        seq = rng.integers(0, 20, size=(5, e - s)).astype(np.int8)
+        seq[0] = feats["res_type"][s:e].numpy()
+        msas[a] = MSA(seq, np.ones_like(seq, dtype=bool), rng.integers(0, 3, size=seq.shape).astype(np.int8))
+    full = dict(feats)
+    full.update(msa_block(full, cols, None, msas, 64))
+    gen = torch.Generator().manual_seed(5)
+    want, _, keep = cropper.crop(full, 40, 0, gen, strategy="contiguous", return_keep=True)
+    gen = torch.Generator().manual_seed(5)
+    bare, _, keep2 = cropper.crop(dict(feats), 40, 0, gen, strategy="contiguous", return_keep=True)
+    assert torch.equal(keep, keep2)
+    opened = []
+
+    def load(a):
+        opened.append(a)
+        return msas[a]
+
+    got, read, skipped = attach_cropped_msa(bare, keep2, cols, load, max_msa_rows=64)
+    alive = {a for a, (s, e) in cols.items() if bool(((keep >= s) & (keep < e)).any())}
+    assert set(opened) == alive and read == len(alive) and skipped == 3 - len(alive)
+    # rows of chains that were cropped away are all-gap rows in the crop-after features and absent here
+    keep_rows = (want["msa"] != 21).any(dim=1)
+    for key in ("msa", "deletion_matrix"):
+        assert torch.equal(got[key], want[key][keep_rows]), key
+
+
+def test_batch_stream_counts_drops_by_exception_type():
+    from deepfold3_dev_b200.data.datasets import BatchStream
+
+    class Flaky:
+        def __getitem__(self, i):
+            if i % 3 == 0:
+                raise KeyError("missing alignment")
+            if i % 5 == 0:
+                raise ValueError("no tokens")
+            return {"res_type": torch.zeros(4, dtype=torch.long), "x": torch.ones(4)}
+
+    stream = BatchStream(Flaky(), iter(range(100)), batch_size=2)
+    for _ in range(5):
+        next(stream)
+    c = stream.counters()
+    assert c["data/served"] == 10 and c["data/dropped"] == c["data/dropped/KeyError"] + c["data/dropped/ValueError"] > 0
+    assert c["data/retries"] == c["data/dropped"]
+
+
+def test_openfold3_atom_array_import_and_columnar_cache(tmp_path):
+    from deepfold3_dev_b200.data import of3
+    from deepfold3_dev_b200.data.types import Structure, load_manifest
+
+    names = ["N", "CA", "C", "O"]
+    rows = []
+    for chain, (res, n_res) in {"A": ("ALA", 3), "B": ("GLY", 2)}.items():
+        for r in range(n_res):
+            for a in names:
+                rows.append((chain, r + 1, res, a, a[0]))
+    rows += [("C", 1, "HEM", "FE", "FE"), ("C", 1, "HEM", "N1", "N")]
+    n = len(rows)
+    coord = np.cumsum(np.full((n, 3), 1.3, dtype=np.float32), axis=0)
+    src = tmp_path / "of3" / "1abc"
+    src.mkdir(parents=True)
+    np.savez(src / "1abc.npz", coord=coord, chain_id=np.array([r[0] for r in rows]), res_id=np.array([r[1] for r in rows]),
+             res_name=np.array([r[2] for r in rows]), atom_name=np.array([r[3] for r in rows]), element=np.array([r[4] for r in rows]),
+             molecule_type_id=np.array([0] * 20 + [3] * 2), bonds=np.array([[20, 21, 1], [0, 1, 1]]))  # fmt: skip
+    cache = {"structure_data": {"1abc": {"release_date": "2020-01-05", "resolution": 2.1, "experimental_method": "X-RAY DIFFRACTION",
+                                         "chains": {"A": {"cluster_id": "c7", "molecule_type": "PROTEIN", "template_ids": ["2xyz_A"]},
+                                                    "B": {"cluster_id": "c9", "molecule_type": "PROTEIN"},
+                                                    "C": {"cluster_id": "lig", "molecule_type": "LIGAND"}}}}}  # fmt: skip
+    (tmp_path / "cache.json").write_text(json.dumps(cache))
+    out = tmp_path / "train"
+    assert of3.convert_directory(str(tmp_path / "of3"), str(out), str(tmp_path / "cache.json")) == (1, 0)
+    rec = load_manifest(str(out / "manifest.json"))[0]
+    assert [c.mol_type for c in rec.chains] == [0, 0, 3] and [c.num_residues for c in rec.chains] == [3, 2, 1]
+    assert rec.chains[0].cluster_id == "c7" and rec.structure_info.resolution == 2.1 and rec.structure_info.released == "2020-01-05"
+    st = Structure.load(str(out / "structures" / "1abc.npz"))
+    assert len(st.atoms) == n and len(st.residues) == 6 and st.chain_canonical_seqs[0] == "AAA" and len(st.bonds) == 1
+    entries, chains = of3.build_columnar_cache(str(tmp_path / "cache.json"), str(tmp_path / "col"))
+    assert (entries, chains) == (1, 3)
+    col = of3.ColumnarCache(str(tmp_path / "col"))
+    e = col.entry(col.index_of("1ABC"))
+    assert e["resolution"] == pytest.approx(2.1) and e["chains"][0]["template_ids"] == ["2xyz_A"] and col.index_of("9zzz") == -1
+    assert list(col.select(max_release_date="2019-12-31")) == [] and list(col.select(max_release_date="2021-01-01", max_resolution=3.0)) == [0]
+    assert col.cluster_weights(np.array([0]))[0] == pytest.approx(3.0)
+
+
+def test_ligand_automorphisms_by_graph_search():
+    from deepfold3_dev_b200.data.symmetry import graph_automorphisms
+
+    ring = [(i, (i + 1) % 6) for i in range(6)]
+    perms = graph_automorphisms([6] * 6, ring)
+    assert len(perms) == 12 and perms[0] == list(range(6)) and all(sorted(p) == list(range(6)) for p in perms)
+    assert len(graph_automorphisms([6, 8, 8], [(0, 1), (0, 2)])) == 2                       # the two oxygens swap
+    assert len(graph_automorphisms([6, 8, 8], [(0, 1), (0, 2)], orders=[2, 1])) == 1        # not when the bond orders differ
+    assert len(graph_automorphisms([15, 8, 8, 8, 8], [(0, 1), (0, 2), (0, 3), (0, 4)])) == 24
+    assert len(graph_automorphisms([6] * 6, ring, limit=5)) == 5
+
+
+def test_logit_files_follow_the_reference_layout(tmp_path):
+    """Every scheme round-trips, the file is laid out as the reference documents it (payload per head under its own
+    name, ``_meta`` JSON with per-head scheme / shape / scale / clip / bin_axis), a file assembled by hand from that
+    description loads, and so does a file in this package's earlier layout."""
+    rng = np.random.RandomState(1)
+    pae = (rng.randn(3, 6, 6, 9) * 5).astype(np.float32)   # odd bin count: the 4-bit scheme pads a nibble
+    plddt = (rng.randn(3, 6, 50) * 3).astype(np.float32)
+    tol = {"float32": 1e-7, "float16": 1e-2, "int8": 6e-2, "int8_softmax": 3e-2, "int4_softmax": 0.3}
+    for scheme in logit_codec.SCHEMES:
+        path = str(tmp_path / f"{scheme}.npz")
+        logit_codec.save_logits(path, pae=pae, plddt=plddt, pde=None, scheme=scheme, extra={"token_chain": np.arange(6)},
+                                attrs={"seed": 7})  # fmt: skip
+        with np.load(path) as z:
+            assert set(z.files) == {"pae", "plddt", "token_chain", "_meta"}
+            meta = json.loads(bytes(z["_meta"]).decode())
+        assert meta["version"] == 1 and meta["attrs"] == {"seed": 7} and set(meta["heads"]) == {"pae", "plddt"}
+        assert meta["heads"]["pae"]["shape"] == [3, 6, 6, 9] and meta["heads"]["pae"]["scheme"] == scheme
+        back = logit_codec.load_logits(path)
+        assert back["token_chain"].tolist() == list(range(6)) and logit_codec.load_attrs(path) == {"seed": 7}
+        for name, ref in (("pae", pae), ("plddt", plddt)):
+            assert back[name].shape == ref.shape
+            assert np.abs(logit_codec.softmax(back[name]) - logit_codec.softmax(ref)).max() < tol[scheme], (scheme, name)
+    # a file put together by hand as the format is documented: uint8 levels, level 255 = row maximum, step = clip / 255
+    clip, levels = 16.0, 255
+    shifted = np.clip(plddt - plddt.max(-1, keepdims=True), -clip, 0)
+    payload = np.rint((shifted + clip) / (clip / levels)).astype(np.uint8)
+    meta = {"heads": {"plddt": {"scheme": "int8_softmax", "dtype": "float32", "shape": list(plddt.shape), "scale": clip / levels,
+                                "clip": clip, "bin_axis": 2}}, "attrs": {"sample": 1}, "version": 1}  # fmt: skip
+    hand = str(tmp_path / "hand.npz")
+    np.savez_compressed(hand, plddt=payload, _meta=np.frombuffer(json.dumps(meta).encode(), dtype=np.uint8))
+    got = logit_codec.load_logits(hand)
+    assert got.attrs == {"sample": 1} and np.abs(got["plddt"] - shifted).max() <= clip / levels / 2 + 1e-6
+    # the earlier layout of this package
+    old = str(tmp_path / "old.npz")
+    np.savez_compressed(old, __attrs__=np.frombuffer(json.dumps({"scheme": "f16", "clip": 30.0, "heads": ["pae"]}).encode(), dtype=np.uint8),
+                        **{"pae.payload": pae.astype(np.float16)})  # fmt: skip
+    assert np.abs(logit_codec.load_logits(old)["pae"] - pae).max() < 2e-2 and logit_codec.head_names(old) == ["pae"]
+    with pytest.raises(ValueError):
+        logit_codec.save_logits(str(tmp_path / "x.npz"), pae=pae, scheme="int3")
