@@ -61,6 +61,12 @@ def train(data_dir, output, params, resume, configs, lr, max_steps, max_tokens, 
           wandb_project, wandb_entity, overrides, datasets, synthetic, num_workers):  # fmt: skip
     """Train the model (one process per GPU; launch with torch.distributed.run for several)."""
     _setup_logging()
+    import faulthandler
+    import signal
+
+    faulthandler.enable()  # a fatal signal prints every thread's Python stack
+    if hasattr(signal, "SIGUSR1"):
+        faulthandler.register(signal.SIGUSR1, all_threads=True)  # `kill -USR1 <pid>`: where is this rank right now?
     from ..config.loader import build_configs
     from ..data import datasets as ds
     from ..data.samplers import MultiDatasetSampler, WeightedClusterSampler
@@ -84,7 +90,8 @@ def train(data_dir, output, params, resume, configs, lr, max_steps, max_tokens, 
         for d in getattr(tc, "extra_datasets", []) or []:
             if d.data_dir:
                 specs.append(f"{d.name or 'data'}:{d.data_dir}:{d.weight}:{d.strategy}:{int(d.is_distillation)}")
-                extra[d.data_dir] = {"cutoff_date": d.cutoff_date, "crop_weights": d.crop_weights}
+                extra[d.data_dir] = {"cutoff_date": d.cutoff_date, "crop_weights": d.crop_weights, "format": d.format,
+                                     "of3_cache_dir": d.of3_cache_dir}
     if synthetic or not specs:
         if not synthetic:
             raise click.ClickException("give --dataset / --data-dir, or --synthetic")
@@ -99,7 +106,7 @@ def train(data_dir, output, params, resume, configs, lr, max_steps, max_tokens, 
             weights.append(float(f[2]) if len(f) > 2 and f[2] else 1.0)
             distill = len(f) > 4 and f[4].lower() in ("1", "true", "distill")
             kw = {k: v for k, v in extra.get(path, {}).items() if v}
-            if "cutoff_date" in kw and not os.path.isdir(os.path.join(path, "structures")):
+            if "cutoff_date" in kw and kw.get("format", "df3") == "df3" and not os.path.isdir(os.path.join(path, "structures")):
                 kw.pop("cutoff_date")  # feature directories carry no dates; the cut-off is applied when they are prepared
             parts.append(ds.open_dataset(path, max_tokens=tc.max_tokens, max_atoms=tc.max_atoms, is_distillation=distill,
                                          seed=tc.seed, **kw))  # fmt: skip

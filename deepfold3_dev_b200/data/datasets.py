@@ -347,10 +347,21 @@ def featurize_record(st, rec, load_msa, *, max_tokens: int = 384, max_atoms: int
     return feats, read, skipped
 
 
-def open_dataset(path: str, **kw):
-    """A directory of ``.pt`` features, or the output of ``prepare structures`` (featurised on the fly)."""
+def open_dataset(path: str, format: str = "df3", of3_cache_dir: str = "", **kw):
+    """The dataset behind one entry of a recipe's ``datasets`` list (reference: training/data.py:40-561). ``df3``: a
+    directory of ``.pt`` features or the output of ``prepare structures`` (featurised on the fly); ``of3`` / ``of3pdb``:
+    an OpenFold 3 structure directory read in place, the latter with its columnar metadata cache (release-date cut-off,
+    cluster-balanced weights)."""
     from . import paths
 
+    if format in ("of3", "of3pdb"):
+        from .of3 import OF3StructureDataset
+
+        cutoff = kw.pop("cutoff_date", "") or None
+        kw.pop("keep_after", None)
+        return OF3StructureDataset(path, cache_dir=of3_cache_dir or None, max_release_date=cutoff, **kw)
+    if format != "df3":
+        raise ValueError(f"dataset format must be df3|of3|of3pdb, got {format!r}")
     if paths.is_prepared_root(path):
         return StructureDataset(path, **kw)
     return FeatureDirDataset(path, **kw)

@@ -312,17 +312,26 @@ class OF3StructureDataset:
 
     def __init__(self, of3_dir: str, cache_dir: str | None = None, msa_dir: str | None = None, max_tokens: int = 384,
                  max_atoms: int = 4096, max_msa_rows: int = 1024, max_release_date: str | None = None,
-                 max_resolution: float | None = None, seed: int = 0):  # fmt: skip
-        self.items = scan_structures(of3_dir)
+                 max_resolution: float | None = None, seed: int = 0, crop_weights: dict | None = None,
+                 is_distillation: bool = False):  # fmt: skip
+        structures = os.path.join(of3_dir, "structures")
+        self.items = scan_structures(structures if os.path.isdir(structures) else of3_dir)
         self.cache = ColumnarCache(cache_dir) if cache_dir else None
-        self.weights = None
+        self._weights = None
         if self.cache is not None:
             allowed = {self.cache.col["entry_id"][i].decode() for i in self.cache.select(max_release_date, max_resolution)}
             self.items = [it for it in self.items if it[0] in allowed]
-            idx = np.asarray([self.cache.index_of(pid) for pid, _ in self.items])
-            self.weights = self.cache.cluster_weights(idx)
+            idx = np.asarray([self.cache.index_of(pid) for pid, _ in self.items], dtype=np.int64)
+            self._weights = self.cache.cluster_weights(idx)
+        if msa_dir is None and os.path.isdir(os.path.join(of3_dir, "msa")):
+            msa_dir = os.path.join(of3_dir, "msa")
         self.msa_dir, self.max_tokens, self.max_atoms, self.max_msa_rows, self.seed = msa_dir, max_tokens, max_atoms, max_msa_rows, seed
-        self.dropped = 0
+        self.crop_weights, self.is_distillation = crop_weights, is_distillation
+        self.msa_read = self.msa_skipped = 0
+
+    def weights(self) -> list[float]:
+        """Sampling weights: cluster-balanced when the metadata cache is there, uniform otherwise."""
+        return [1.0] * len(self.items) if self._weights is None else [float(w) for w in self._weights]
 
     def __len__(self) -> int:
         return len(self.items)
@@ -338,8 +347,10 @@ class OF3StructureDataset:
                 e = self.cache.entry(i)
                 apply_cache_entry(rec, {"resolution": e["resolution"], "experimental_method": e["method"], "release_date": e["release_date"],
                                         "chains": {c["chain_name"]: c for c in e["chains"]}})  # fmt: skip
-        feats, _, _ = featurize_record(st, rec, self._msa, max_tokens=self.max_tokens, max_atoms=self.max_atoms,
-                                       max_msa_rows=self.max_msa_rows, seed=self.seed + index)  # fmt: skip
+        feats, read, skipped = featurize_record(st, rec, self._msa, max_tokens=self.max_tokens, max_atoms=self.max_atoms,
+                                                crop_weights=self.crop_weights, max_msa_rows=self.max_msa_rows,
+                                                seed=self.seed * 7_654_321 + index, is_distillation=self.is_distillation)  # fmt: skip
+        self.msa_read, self.msa_skipped = self.msa_read + read, self.msa_skipped + skipped
         return feats
 
     def _msa(self, chain):

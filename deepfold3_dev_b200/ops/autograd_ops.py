@@ -7,24 +7,33 @@ inputs are made contiguous here, so callers can pass views.
 from __future__ import annotations
 
 import collections
-import weakref
-
 import os
+import weakref
 
 import torch
 
 LAUNCHES: collections.Counter = collections.Counter()
 
 
+NVTX = os.environ.get("DF3_NVTX", "0") == "1"  # one NVTX range per kernel-op call: names the launches in a timeline
+
+
 class _Ops:
-    """``torch.ops.df3`` with a per-kernel launch count (read by the benchmark's ``gpu_launches``)."""
+    """``torch.ops.df3`` with a per-kernel launch count (read by the benchmark's ``gpu_launches``) and, with
+    ``DF3_NVTX=1``, an NVTX range ``df3::<op>`` around every call."""
 
     def __getattr__(self, name):
         op = getattr(torch.ops.df3, name)
 
         def call(*args, **kwargs):
             LAUNCHES[name] += 1
-            return op(*args, **kwargs)
+            if not NVTX:
+                return op(*args, **kwargs)
+            torch.cuda.nvtx.range_push(f"df3::{name}")
+            try:
+                return op(*args, **kwargs)
+            finally:
+                torch.cuda.nvtx.range_pop()
 
         return call
 
@@ -706,6 +715,6 @@ def grid_attention_packed(qkv, bias, key_mask, scale: float, transpose: bool):
 
 def check_status() -> None:
     """Raise if a kernel's bounded wait ran out since the last check (synchronises the device)."""
-    code = K.gemm_status()
+    code = K.gemm_status() or K.elementwise_status()
     if code != 0:
         raise RuntimeError(f"deepfold3_dev_b200: a kernel wait timed out (status {code}); results of this step are invalid")

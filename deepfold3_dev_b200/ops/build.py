@@ -31,8 +31,15 @@ def _stale() -> bool:
     return any(os.path.getmtime(d) > built for d in deps)
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
-    """Compile if needed and return the path of the shared object."""
+CHECKED_SO_PATH = os.path.join(HERE, "_df3_sm100_checked.so")
+
+
+def build(force: bool = False, verbose: bool = False, checked: bool = False) -> str:
+    """Compile if needed and return the path of the shared object. ``checked`` builds the debug variant
+    (``-DDF3_BOUNDS_CHECK``: index tests around the kernels' global accesses that record a status code instead of
+    touching memory out of range) as ``_df3_sm100_checked.so``; ``DF3_BOUNDS_CHECK=1`` makes ``ops/native.py`` load it."""
+    if checked:
+        return _build_checked(verbose)
     if not force and not _stale():
         return SO_PATH
     from torch.utils import cpp_extension
@@ -56,6 +63,23 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return SO_PATH
 
 
+def _build_checked(verbose: bool) -> str:
+    from torch.utils import cpp_extension
+
+    build_dir = BUILD_DIR + "_checked"
+    os.makedirs(build_dir, exist_ok=True)
+    os.environ.setdefault("TORCH_CUDA_ARCH_LIST", "10.0a")
+    os.environ.setdefault("MAX_JOBS", str(min(16, os.cpu_count() or 4)))
+    defines = ["-DDF3_WITH_GEMM", "-DDF3_BOUNDS_CHECK"]
+    cpp_extension.load(
+        name="_df3_sm100_checked", sources=sources(), extra_cflags=["-O3", "-std=c++17"] + defines,
+        extra_cuda_cflags=["-O3", "-std=c++17", "-lineinfo", "--use_fast_math"] + ARCH_FLAGS + defines,
+        build_directory=build_dir, is_python_module=False, verbose=verbose,
+    )  # fmt: skip
+    shutil.copy2(os.path.join(build_dir, "_df3_sm100_checked.so"), CHECKED_SO_PATH)
+    return CHECKED_SO_PATH
+
+
 if __name__ == "__main__":
-    path = build(force="--force" in sys.argv, verbose="-v" in sys.argv or "--verbose" in sys.argv)
+    path = build(force="--force" in sys.argv, verbose="-v" in sys.argv or "--verbose" in sys.argv, checked="--checked" in sys.argv)
     print(path)

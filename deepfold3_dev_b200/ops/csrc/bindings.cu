@@ -12,6 +12,7 @@ std::tuple<Tensor, Tensor, Tensor> df3_plane_layer_norm_fwd(const Tensor&, const
                                                             const c10::optional<Tensor>&, double);
 std::tuple<Tensor, Tensor> df3_plane_layer_norm_bwd(const Tensor&, const Tensor&, const c10::optional<Tensor>&, const Tensor&,
                                                     const Tensor&, bool);
+int64_t df3_elementwise_status();
 Tensor df3_swiglu_fwd(const Tensor&);
 Tensor df3_swiglu_bwd(const Tensor&, const Tensor&);
 Tensor df3_gated_bwd(const Tensor&, const Tensor&, const c10::optional<Tensor>&);
@@ -40,6 +41,14 @@ static std::string df3_features() {
 
 TORCH_LIBRARY(df3, m) {
   m.def("features() -> str", &df3_features);
+  m.def("elementwise_status() -> int", &df3_elementwise_status);
+  m.def("bounds_checked() -> bool", []() {
+#ifdef DF3_BOUNDS_CHECK
+    return true;
+#else
+    return false;
+#endif
+  });
   m.def("layer_norm_fwd(Tensor x, Tensor? w, Tensor? b, float eps) -> (Tensor, Tensor, Tensor)", &df3_layer_norm_fwd);
   m.def("layer_norm_bwd(Tensor dy, Tensor x, Tensor? w, Tensor mean, Tensor rstd, bool want_wb) -> (Tensor, Tensor)",
         &df3_layer_norm_bwd);

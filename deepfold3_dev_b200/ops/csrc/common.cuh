@@ -18,6 +18,19 @@ enum Status : int {
   kBadShape = 5,
 };
 
+// Debug build (-DDF3_BOUNDS_CHECK, `python -m deepfold3_dev_b200.ops.build --checked`): global accesses whose index a
+// kernel computes go through this test. An index outside [0, limit) records kBadShape in the status word and the
+// access is skipped; nothing traps. In the normal build the test is the constant true and costs nothing.
+#ifdef DF3_BOUNDS_CHECK
+__device__ __forceinline__ bool in_bounds(long long idx, long long limit, int* status) {
+  if (idx >= 0 && idx < limit) return true;
+  if (status != nullptr) atomicCAS(status, (int)kOk, (int)kBadShape);
+  return false;
+}
+#else
+__device__ __forceinline__ bool in_bounds(long long, long long, int*) { return true; }
+#endif
+
 template <typename T> __device__ __forceinline__ float to_float(T v);
 template <> __device__ __forceinline__ float to_float<float>(float v) { return v; }
 template <> __device__ __forceinline__ float to_float<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }

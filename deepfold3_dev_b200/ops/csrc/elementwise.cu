@@ -8,6 +8,12 @@
 #include "common.cuh"
 
 namespace df3 {
+// Status word of the element-wise kernels (they take no status argument): written only by the bounds checks of the
+// debug build, read by elementwise_status().
+__device__ int ew_status = 0;
+}  // namespace df3
+
+namespace df3 {
 
 constexpr int kLnMaxPerLane = 32;  // one warp per row, up to 32 * 32 = 1024 channels; kernels are
                                    // instantiated for 4 / 8 / 16 / 32 values per lane
@@ -83,7 +89,8 @@ __global__ void __launch_bounds__(256) layer_norm_fwd_vec_kernel(const __nv_bflo
     const int64_t row = row0 + r < rows ? row0 + r : rows - 1;  // tail rows re-read the last row; their stores are skipped
     const uint2* xr = reinterpret_cast<const uint2*>(x + row * C);
 #pragma unroll
-    for (int g = 0; g < G; ++g) raw[r][g] = xr[lane + 32 * g];
+    for (int g = 0; g < G; ++g)
+      raw[r][g] = in_bounds(row * C + 4 * (lane + 32 * g) + 3, rows * C, &ew_status) ? xr[lane + 32 * g] : make_uint2(0u, 0u);
   }
 #pragma unroll
   for (int r = 0; r < R; ++r) {
@@ -353,7 +360,8 @@ __global__ void __launch_bounds__(256) plane_layer_norm_fwd_vec_kernel(const __n
   const int64_t p0 = m0 + chunk * 8;
   for (int c = threadIdx.x >> 4; c < C; c += 16) {
     uint4 v = make_uint4(0u, 0u, 0u, 0u);
-    if (p0 < M) v = *reinterpret_cast<const uint4*>(x + (int64_t)c * M + p0);   // M % 8 == 0: the chunk is inside or outside
+    if (p0 < M && in_bounds((int64_t)c * M + p0 + 7, (int64_t)C * M, &ew_status))   // M % 8 == 0: the chunk is inside or outside
+      v = *reinterpret_cast<const uint4*>(x + (int64_t)c * M + p0);
     uint32_t* dst = reinterpret_cast<uint32_t*>(tin + c * kPlanePitchV + chunk * 8);
     dst[0] = v.x; dst[1] = v.y; dst[2] = v.z; dst[3] = v.w;
   }
@@ -408,7 +416,8 @@ __global__ void __launch_bounds__(256) plane_layer_norm_fwd_vec_kernel(const __n
   const int64_t valid = (M - m0 < kPlaneTileV ? M - m0 : kPlaneTileV) * C / 8;   // 16-byte pieces of this block's output
   uint4* dst = reinterpret_cast<uint4*>(y + m0 * C);
   const uint4* src = reinterpret_cast<const uint4*>(tout);
-  for (int64_t i = threadIdx.x; i < valid; i += 256) dst[i] = src[i];
+  for (int64_t i = threadIdx.x; i < valid; i += 256)
+    if (in_bounds(m0 * C / 8 + i, M * C / 8, &ew_status)) dst[i] = src[i];
 }
 
 // Backward of the above: dy [M, C] channel-last, x planes [C, M] -> dx planes [C, M]; (dw, db) partials per block.
@@ -956,6 +965,17 @@ std::tuple<Tensor, Tensor> df3_sigmoid_gate_bwd(const Tensor& dy, const Tensor& 
       (uint4*)d_other.data_ptr(), n8);
   C10_CUDA_KERNEL_LAUNCH_CHECK();
   return {dg, d_other};
+}
+
+// The element-wise kernels' status word: 0, or df3::kBadShape after a bounds check of the debug build failed.
+int64_t df3_elementwise_status() {
+  int code = 0;
+  C10_CUDA_CHECK(cudaMemcpyFromSymbol(&code, df3::ew_status, sizeof(int)));
+  if (code != 0) {
+    const int zero = 0;
+    C10_CUDA_CHECK(cudaMemcpyToSymbol(df3::ew_status, &zero, sizeof(int)));
+  }
+  return code;
 }
 
 Tensor df3_swiglu_fwd(const Tensor& x) {

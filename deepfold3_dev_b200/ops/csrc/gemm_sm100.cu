@@ -129,6 +129,7 @@ struct GemmParams {
   int tma_store;              // bf16 row-major output with 16-byte aligned rows: tiles leave through shared memory and TMA
   int bias_on_m, mask_on_n;
   long long mask_batch_stride;
+  long long c_elems;          // elements of the whole output (read by the debug build's bounds checks)
 };
 
 template <int BN, bool DUAL_A>
@@ -167,6 +168,7 @@ __device__ __forceinline__ void store_row32(const GemmParams& p, void* cbase, lo
     return;
   }
   __nv_bfloat16* dst = cb + (long long)row * p.ldc + n0;
+  if (p.c_elems > 0 && !in_bounds(batch_off + (long long)row * p.ldc + n0 + (n0 + 32 <= p.N ? 31 : p.N - n0 - 1), p.c_elems, p.status)) return;
   if (n0 + 32 <= p.N && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
 #pragma unroll
     for (int g = 0; g < 4; ++g) {
@@ -683,6 +685,7 @@ Tensor gemm_impl(const Tensor& a3, const Tensor& w3, const c10::optional<Tensor>
     if (out.numel() == 0) return out;
     GemmParams p{};
     p.C = out.data_ptr();
+    p.c_elems = out.numel();
     Tensor bias_f, mask_f;
     if (bias.has_value() && bias->defined()) {
       bias_f = bias->to(torch::kFloat32).contiguous();
@@ -776,6 +779,7 @@ Tensor gemm_impl(const Tensor& a3, const Tensor& w3, const c10::optional<Tensor>
           : o.channel_major ? torch::empty({batch, N, M}, opts)
                             : torch::empty({batch, M, out_cols}, o.out_fp32 ? opts.dtype(torch::kFloat32) : opts);
     p.C = out.data_ptr();
+    p.c_elems = out.numel();
     p.c_fp32 = o.out_fp32;
   }
   if (out.numel() == 0) return out;

@@ -42,6 +42,7 @@ struct XPeers {
 struct XPlan {
   uint32_t n0, n1, n2, inner;
   long long ss0, ss1, ss2, ds0, ds1, ds2, src_q, dst_base;
+  long long src_vecs, dst_vecs;   // extents of the source tensor and of one rank's result (read by the debug build's checks)
 };
 
 __global__ void exchange_entry_kernel(XPeers peers, int* __restrict__ status, int rank, int world, unsigned long long seq,
@@ -79,7 +80,7 @@ __device__ __forceinline__ void locate(const XPlan& pl, uint32_t per_q, uint32_t
 }
 
 __global__ void __launch_bounds__(512) exchange_push_kernel(const uint4* __restrict__ src, XPeers peers, XPlan pl,
-                                                          const int* __restrict__ status, unsigned int* __restrict__ done,
+                                                          int* __restrict__ status, unsigned int* __restrict__ done,
                                                           uint32_t per_q, int rank, int world, unsigned long long seq) {
   if (*reinterpret_cast<const volatile int*>(status) != kOk) return;
   const unsigned long long total = (unsigned long long)per_q * world;
@@ -96,7 +97,8 @@ __global__ void __launch_bounds__(512) exchange_push_kernel(const uint4* __restr
       if (idx < total) {
         long long s;
         locate(pl, per_q, (uint32_t)idx, rank, world, q[u], s, d[u]);
-        v[u] = src[s];
+        if (in_bounds(s, pl.src_vecs, status) && in_bounds(d[u], pl.dst_vecs, status)) v[u] = src[s];
+        else q[u] = -1;
       }
     }
 #pragma unroll
@@ -167,6 +169,8 @@ void df3_peer_exchange(const Tensor& src, Tensor out, const std::vector<int64_t>
   pl.ds0 = vec(dstr[0], "destination stride"); pl.ds1 = vec(dstr[1], "destination stride"); pl.ds2 = vec(dstr[2], "destination stride");
   pl.src_q = vec(src_q, "per-rank source offset");
   pl.dst_base = vec(dst_base, "destination offset");
+  pl.src_vecs = src.numel() * es / 16;
+  pl.dst_vecs = out.numel() * es / 16;
   TORCH_CHECK(counts[0] > 0 && counts[1] > 0 && counts[2] > 0 && pl.inner > 0, "peer_exchange: empty pattern");
   const int64_t per_q = counts[0] * counts[1] * counts[2] * (int64_t)pl.inner;
   TORCH_CHECK(per_q * world < (int64_t)1 << 32, "peer_exchange: more than 2^32 vectors in one exchange");

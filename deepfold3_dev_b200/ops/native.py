@@ -19,7 +19,10 @@ SO_NAME = "_df3_sm100.so"
 
 
 def so_path() -> str:
-    return os.path.join(os.path.dirname(os.path.abspath(__file__)), SO_NAME)
+    """The extension to load: the debug variant with index checks when ``DF3_BOUNDS_CHECK=1`` (built by
+    ``python -m deepfold3_dev_b200.ops.build --checked``), else the normal one."""
+    name = "_df3_sm100_checked.so" if os.environ.get("DF3_BOUNDS_CHECK", "0") == "1" else SO_NAME
+    return os.path.join(os.path.dirname(os.path.abspath(__file__)), name)
 
 
 def _load() -> None:

@@ -45,9 +45,17 @@ class ActivationRMSMeter:
         self._add(layer, "single", single_delta)
         self._add(layer, "pair", pair_delta)
 
-    def flush_to_dict(self, prefix: str = "act_rms") -> dict[str, float]:
-        rms = (self.sumsq / self.count.clamp(min=1)).sqrt().cpu()
-        seen = (self.count > 0).cpu()
+    def flush_to_dict(self, prefix: str = "act_rms", all_ranks: bool = True) -> dict[str, float]:
+        """Window statistics as log entries. In a multi-process run the sums of squares and counts are added over the
+        ranks first (one all-reduce of two small tensors), so the logged RMS describes the global batch and every
+        rank reports the same numbers (reference: training/activation_meter.py, its cross-rank reduction)."""
+        sumsq, count = self.sumsq, self.count
+        if all_ranks and torch.distributed.is_available() and torch.distributed.is_initialized() and torch.distributed.get_world_size() > 1:
+            both = torch.stack([sumsq.double(), count.double()])
+            torch.distributed.all_reduce(both)
+            sumsq, count = both[0], both[1]
+        rms = (sumsq / count.clamp(min=1)).sqrt().cpu()
+        seen = (count > 0).cpu()
         out = {}
         for j, name in enumerate(BRANCHES):
             vals = [float(rms[i, j]) for i in range(self.num_layers) if seen[i, j]]
