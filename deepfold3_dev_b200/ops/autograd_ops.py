@@ -280,6 +280,17 @@ def mm(a, b, trans_a: bool = False, trans_b: bool = False, out_fp32: bool = Fals
     instead of copying it. Falls back to torch for shapes the kernel does not take (extents not multiples of 8)."""
     if _mm_ok(a, b):
         return K.matmul(a, b, trans_a, trans_b, out_fp32, splits, out)
+    if out is None and all(t.is_cuda and t.dtype == BF16 and t.numel() > 0 and t.dim() in (2, 3) for t in (a, b)):
+        # a ragged extent (4 attention heads, an odd token count): zero rows / columns up to the next multiple of 8
+        # change nothing in the product, so pad the operand that needs it and cut the result back
+        def pad8(t):
+            r, c = (-t.shape[-2]) % 8, (-t.shape[-1]) % 8
+            return torch.nn.functional.pad(t, (0, c, 0, r)) if (r or c) else t
+
+        rows = a.shape[-1] if trans_a else a.shape[-2]
+        cols = b.shape[-2] if trans_b else b.shape[-1]
+        full = K.matmul(pad8(a), pad8(b), trans_a, trans_b, out_fp32, splits, None)
+        return full[..., :rows, :cols] if full.shape[-2:] == (rows, cols) else full[..., :rows, :cols].contiguous()
     A = a.transpose(-1, -2) if trans_a else a
     B = b.transpose(-1, -2) if trans_b else b
     r = torch.matmul(A, B)

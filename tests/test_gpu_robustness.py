@@ -106,19 +106,24 @@ def test_pairformer_block_reaches_no_library_matrix_product(nat):
     single = torch.randn(1, N, 384, device="cuda", requires_grad=True)
     seq_mask = torch.ones(1, N, device="cuda")
     pair_mask = torch.ones(1, N, N, device="cuda")
-    seen = set()
+    seen, where = set(), {}
+    keys = ("aten.mm", "aten.bmm", "aten.addmm", "aten.baddbmm", "aten.linear", "aten.matmul", "scaled_dot_product", "aten._addmm")
 
     class Watch(TorchDispatchMode):
         def __torch_dispatch__(self, func, types, args=(), kwargs=None):
-            seen.add(str(func))
+            name = str(func)
+            seen.add(name)
+            if any(k in name for k in keys) and name not in where:
+                import traceback
+
+                where[name] = [f"{f.filename.split('/')[-1]}:{f.lineno}" for f in traceback.extract_stack() if "deepfold3_dev_b200" in f.filename][-4:]
             return func(*args, **(kwargs or {}))
 
     with Watch(), torch.autocast("cuda", dtype=torch.bfloat16):
         p, s = block(pair, single, pair_mask, seq_mask)
         (p.float().square().mean() + s.float().square().mean()).backward()
-    library = {name for name in seen if any(key in name for key in ("aten.mm", "aten.bmm", "aten.addmm", "aten.baddbmm", "aten.linear",
-                                                                    "aten.matmul", "scaled_dot_product", "aten._addmm"))}  # fmt: skip
-    assert not library, f"library matrix products reached: {sorted(library)}"
+    library = {name for name in seen if any(key in name for key in keys)}
+    assert not library, f"library matrix products reached: {where}"
     assert any("df3" in name for name in seen)
     assert pair.grad is not None and bool(torch.isfinite(pair.grad).all())
 
