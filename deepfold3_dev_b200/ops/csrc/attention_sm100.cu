@@ -33,6 +33,8 @@ std::tuple<Tensor, Tensor, Tensor, Tensor> attention_bwd_fused(const Tensor& q, 
                                                                bool want_dbias, const c10::optional<Tensor>& dq_out,
                                                                const c10::optional<Tensor>& dk_out, const c10::optional<Tensor>& dv_out);
 Tensor status_word(int device);                       // gemm_sm100.cu
+Tensor df3_matmul_any(const Tensor& a, const Tensor& b, bool trans_a, bool trans_b, bool out_fp32, int64_t splits,
+                      const c10::optional<Tensor>& out);  // gemm_sm100.cu: the tcgen05 product for any extents
 CUtensorMap make_map_nd(const void* base, int rank, const int64_t* dims, const int64_t* strides_elems,
                         const int* box);              // gemm_sm100.cu
 
@@ -611,8 +613,8 @@ std::tuple<Tensor, Tensor, Tensor, Tensor> df3_attention_bwd(const Tensor& q, co
       Tensor o3 = doc[b].narrow(0, r0, n).reshape({n * H, N, D});
       Tensor s3 = s.narrow(0, 0, n).view({n * H, N, N});
       Tensor p3 = dp.narrow(0, 0, n).view({n * H, N, N});
-      at::bmm_out(s3, q3, k3.transpose(1, 2));
-      at::bmm_out(p3, o3, v3.transpose(1, 2));
+      df3_matmul_any(q3, k3, false, true, false, 1, s3);   // S = Q K^T
+      df3_matmul_any(o3, v3, false, true, false, 1, p3);   // dP = dO V^T
       c10::optional<Tensor> mm;
       if (has_mask) {
         Tensor mb = mask->select(0, mask->size(0) > 1 ? b : 0);
@@ -623,9 +625,9 @@ std::tuple<Tensor, Tensor, Tensor, Tensor> df3_attention_bwd(const Tensor& q, co
       Tensor dv3 = dv[b].narrow(0, r0, n).view({n * H, N, D});
       Tensor dq3 = dq[b].narrow(0, r0, n).view({n * H, N, D});
       Tensor dk3 = dk[b].narrow(0, r0, n).view({n * H, N, D});
-      at::bmm_out(dv3, s3.transpose(1, 2), o3);
-      at::bmm_out(dq3, p3, k3);
-      at::bmm_out(dk3, p3.transpose(1, 2), q3);
+      df3_matmul_any(s3, o3, true, false, false, 1, dv3);  // dV = P^T dO
+      df3_matmul_any(p3, k3, false, false, false, 1, dq3); // dQ = dS K
+      df3_matmul_any(p3, q3, true, false, false, 1, dk3);  // dK = dS^T Q
     }
   }
   if (!dbias.defined()) dbias = torch::empty({0}, bf.dtype(torch::kFloat32));

@@ -890,22 +890,47 @@ Tensor df3_matmul(const Tensor& a, const Tensor& b, bool trans_a, bool trans_b, 
 // Backward of y = x w^T (+ b) with bf16 operands: dx = dy w (in x's dtype), dw = dy^T x and db = sum dy in fp32.
 // Both products run on the tcgen05 kernel without transposing anything: dy is the K-major A operand of dx and the
 // MN-major A operand of dw; w and x are MN-major B operands. dw is a split-K launch with an order-fixed reduction.
+// The same product for any extents: an operand whose last two extents are not multiples of 8 (TMA rows have to be
+// 16-byte multiples) is zero-padded, which leaves the product unchanged, and the result is cut back. With `out` the
+// result lands in that tensor (directly when no padding was needed).
+Tensor matmul_any_impl(const Tensor& a, const Tensor& b, bool trans_a, bool trans_b, bool out_fp32, int64_t splits,
+                       const c10::optional<Tensor>& out = c10::nullopt) {
+  auto pad8 = [](const Tensor& t) {
+    const int64_t r = (8 - t.size(-2) % 8) % 8, c = (8 - t.size(-1) % 8) % 8;
+    return (r || c) ? at::constant_pad_nd(t, {0, c, 0, r}, 0) : t;
+  };
+  const Tensor a8 = pad8(a.contiguous()), b8 = pad8(b.contiguous());
+  const bool padded = a8.data_ptr() != a.data_ptr() || b8.data_ptr() != b.data_ptr() || !a.is_contiguous() || !b.is_contiguous();
+  const int64_t rows = trans_a ? a.size(-1) : a.size(-2), cols = trans_b ? b.size(-2) : b.size(-1);
+  if (out.has_value() && out->defined() && a8.size(-1) == a.size(-1) && a8.size(-2) == a.size(-2) && b8.size(-1) == b.size(-1) &&
+      b8.size(-2) == b.size(-2) && out->is_contiguous())
+    return df3_matmul(a8, b8, trans_a, trans_b, out_fp32, splits, out);
+  (void)padded;
+  Tensor full = df3_matmul(a8, b8, trans_a, trans_b, out_fp32, splits);
+  Tensor cut = full.narrow(-2, 0, rows).narrow(-1, 0, cols);
+  if (out.has_value() && out->defined()) {
+    out->copy_(cut.view(out->sizes()));
+    return *out;
+  }
+  return cut.contiguous();
+}
+
 std::tuple<Tensor, Tensor, Tensor> df3_linear_bwd(const Tensor& dy, const Tensor& x, const Tensor& w16, bool need_dx, bool need_dw,
                                                    bool need_db) {
   const int64_t n = w16.size(0), k = w16.size(1);
   Tensor d2 = dy.reshape({-1, n});
   if (d2.scalar_type() != torch::kBFloat16) d2 = d2.to(torch::kBFloat16);
   Tensor dx, dw, db;
-  const bool own = n % 8 == 0 && k % 8 == 0 && d2.size(0) > 0;
+  const bool any_rows = d2.size(0) > 0;
   if (need_dx) {
-    dx = own ? df3_matmul(d2, w16, false, false, false, 1) : at::mm(d2, w16);
+    dx = any_rows ? matmul_any_impl(d2, w16, false, false, false, 1) : torch::zeros({0, k}, d2.options());
     dx = dx.view(x.sizes());
     if (dx.scalar_type() != x.scalar_type()) dx = dx.to(x.scalar_type());
   }
   if (need_dw) {
     Tensor x2 = x.reshape({-1, k});
     if (x2.scalar_type() != torch::kBFloat16) x2 = x2.to(torch::kBFloat16);
-    dw = own ? df3_matmul(d2, x2, true, false, true, 0) : at::mm(d2.t(), x2).to(torch::kFloat32);
+    dw = any_rows ? matmul_any_impl(d2, x2, true, false, true, 0) : torch::zeros({n, k}, d2.options().dtype(torch::kFloat32));
   }
   if (need_db) db = d2.sum(0, false, torch::kFloat32);
   auto undef = [&](Tensor& t) { if (!t.defined()) t = torch::empty({0}, dy.options()); };
@@ -924,6 +949,11 @@ int64_t df3_gemm_status() {
 }
 
 }  // namespace
+
+Tensor df3_matmul_any(const Tensor& a, const Tensor& b, bool trans_a, bool trans_b, bool out_fp32, int64_t splits,
+                      const c10::optional<Tensor>& out) {
+  return matmul_any_impl(a, b, trans_a, trans_b, out_fp32, splits, out);
+}
 }  // namespace df3
 
 void df3_register_gemm(torch::Library& m) {

@@ -15,6 +15,8 @@
 //     call before any stream capture begins on that device.
 //   * every call on a device uses the same array: two calls that overlap in time (different streams
 //     or threads) race on it. Serialise them on one stream.
+//   * the caller must have made the buffers' device current (cudaSetDevice) before the call: the scratch array, the
+//     launch and the stream all belong to the current device, and the function does not switch devices.
 //   * nothing in the array has to start at zero: each launched block overwrites its own slice before
 //     the reduction reads it.
 // The function calls no cudaMalloc/cudaFree and no allocating library routine; all outputs are

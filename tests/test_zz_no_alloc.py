@@ -83,3 +83,30 @@ def test_allocates_nothing_and_rejects_oversize():
                                         dx.data_ptr(), dw.data_ptr(), db.data_ptr(), 4, 2048, 1, None)  # fmt: skip
     assert rc == -1
     assert b"2048" in lib.df3_no_alloc_last_error()
+
+
+@pytest.mark.parametrize("rows,channels", [(300, 1024), (50, 600), (37, 100)])
+def test_channel_counts_up_to_the_limit_and_odd_shapes(rows, channels):
+    """The widest supported row (1024 channels: the fixed scratch array is used to its end), a channel count that is
+    not a multiple of the vector width, and a small odd shape."""
+    lib = _lib()
+    for dtype in (torch.float32, torch.bfloat16):
+        x, dy, w, mean, rstd = _case(rows, channels, dtype, 11)
+        (dx, dw, db), (dx_ref, dw_ref, db_ref) = _run_both(lib, x, dy, w, mean, rstd)
+        tol = 2e-2 if dtype == torch.bfloat16 else 1e-5
+        torch.testing.assert_close(dx.float(), dx_ref.float(), rtol=tol, atol=tol)
+        torch.testing.assert_close(dw, dw_ref, rtol=1e-4, atol=1e-2 if dtype == torch.bfloat16 else 1e-3)
+        torch.testing.assert_close(db, db_ref, rtol=1e-4, atol=1e-2 if dtype == torch.bfloat16 else 1e-3)
+
+
+def test_parameter_gradients_may_be_left_out():
+    """``dw`` and ``db`` null together: only ``dx`` is computed, and it equals the ``dx`` of a full call."""
+    lib = _lib()
+    x, dy, w, mean, rstd = _case(513, 256, torch.bfloat16, 13)
+    (dx_full, _, _), _ = _run_both(lib, x, dy, w, mean, rstd)
+    dx = torch.full_like(x, float("nan"))
+    rc = lib.df3_layer_norm_bwd_noalloc(dy.data_ptr(), x.data_ptr(), w.data_ptr(), mean.data_ptr(), rstd.data_ptr(), dx.data_ptr(),
+                                        None, None, x.shape[0], x.shape[1], 1, torch.cuda.current_stream().cuda_stream)  # fmt: skip
+    assert rc == 0, lib.df3_no_alloc_last_error().decode()
+    torch.cuda.synchronize()
+    assert torch.equal(dx, dx_full)
