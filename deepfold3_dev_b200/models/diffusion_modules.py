@@ -310,8 +310,92 @@ class DiffusionTransformer(nn.Module):
             out.append((logits.to(dtype) + bias).contiguous())
         return tuple(out)
 
+    # ---- inference fast path -----------------------------------------------------------------------------------
+    # Without autograd the conditioning terms of all blocks (two AdaLN scale / shift pairs and two output gates per
+    # block, functions of the single conditioning only) come from two stacked products per denoiser call instead of six
+    # small ones per block, the q / k / v projections are one product, the output gate and SwiGLU ride in GEMM epilogues
+    # and every "a * b + c" is one addcmul: about 12 kernels per block instead of about 32 (the sampler at 1024 tokens
+    # is bound by kernel count, not by arithmetic). Same arithmetic as ``DiffusionTransformerBlock.run``; the AdaLN
+    # norm weights are folded into the stacked conditioning weights.
+    def _fast_weights(self):
+        from ..ops import autograd_ops as ao
+
+        layers = list(self.layers)
+        names = ("attn_cond_norm_w", "ffn_cond_norm_w")
+        mods = ("attn_cond_scale", "attn_cond_bias", "ffn_cond_scale", "ffn_cond_bias", "zero_cond", "ffn_zero_cond", "to_q",
+                "to_k", "to_v", "to_g", "out_proj", "ffn_linear1", "ffn_linear2")  # fmt: skip
+        sig = sum(getattr(ly, n)._version for ly in layers for n in names)
+        sig += sum(p._version for ly in layers for m in mods for p in getattr(ly, m).parameters())
+        hit = self.__dict__.get("_fast_cache")
+        if hit is not None and hit[0] == sig and hit[1]["wc"].device == layers[0].to_k.weight.device:
+            return hit[1]
+        bf = torch.bfloat16
+        with torch.no_grad():
+            c = layers[0].to_k.weight.shape[1]
+            wc, bc, wz, bz, per = [], [], [], [], []
+            for ly in layers:
+                wa, wf = ly.attn_cond_norm_w.float(), ly.ffn_cond_norm_w.float()
+                wc += [ly.attn_cond_scale.weight.float() * wa, ly.attn_cond_bias.weight.float() * wa,
+                       ly.ffn_cond_scale.weight.float() * wf, ly.ffn_cond_bias.weight.float() * wf]  # fmt: skip
+                zero = torch.zeros(c, device=wa.device)
+                bc += [ly.attn_cond_scale.bias.float(), zero, ly.ffn_cond_scale.bias.float(), zero]
+                wz += [ly.zero_cond.weight.float(), ly.ffn_zero_cond.weight.float()]
+                bz += [ly.zero_cond.bias.float(), ly.ffn_zero_cond.bias.float()]
+                qkv = torch.cat([ly.to_q.weight, ly.to_k.weight, ly.to_v.weight], 0).to(bf).contiguous()
+                qkv_b = torch.cat([ly.to_q.bias.float(), torch.zeros(ly.to_k.weight.shape[0] + ly.to_v.weight.shape[0], device=wa.device)])
+                per.append({"qkv": qkv, "qkv_b": qkv_b, "g": ly.to_g.weight.to(bf).contiguous(), "o": ly.out_proj.weight.to(bf).contiguous(),
+                            "w1": ly.ffn_linear1.weight.to(bf).contiguous(), "w2": ly.ffn_linear2.weight.to(bf).contiguous()})  # fmt: skip
+            out = {"wc": torch.cat(wc, 0).to(bf).contiguous(), "bc": torch.cat(bc).contiguous(), "wz": torch.cat(wz, 0).to(bf).contiguous(),
+                   "bz": torch.cat(bz).contiguous(), "per": per, "c": c}  # fmt: skip
+        if not torch.cuda.is_current_stream_capturing():  # tensors made inside a graph capture belong to that graph's pool
+            self.__dict__["_fast_cache"] = (sig, out)
+        return out
+
+    def _run_fast(self, act, single_cond, pair_logits):
+        from ..ops import autograd_ops as ao
+
+        W = self._fast_weights()
+        L, c = len(self.layers), W["c"]
+        ly0 = self.layers[0]
+        H, Dk, Dv, sbs = ly0.num_heads, ly0.key_dim_per_head, ly0.val_dim_per_head, self.super_block_size
+        B, S, N, _ = act.shape
+        bf = torch.bfloat16
+        cond16 = single_cond.to(bf)
+        cond = ao.K.gemm(ops.layer_norm(cond16).contiguous(), W["wc"], W["bc"], None, None, 0, False).view(*single_cond.shape[:-1], L, 4, c)
+        cond[..., 0::2, :].sigmoid_()                       # the two AdaLN scales of every block
+        gates = ao.K.gemm(cond16.contiguous(), W["wz"], W["bz"], None, None, 0, False).view(*single_cond.shape[:-1], L, 2, c).sigmoid_()
+        x = act.to(bf)
+        for i, ly in enumerate(self.layers):
+            w = W["per"][i]
+            logits = pair_logits[i // sbs][:, (i % sbs) * H : (i % sbs + 1) * H]
+            xn = torch.addcmul(cond[..., i, 1, :], cond[..., i, 0, :], ops.layer_norm(x))
+            qkv = ao.K.gemm(xn, w["qkv"], w["qkv_b"], None, None, 0, False)
+            q = qkv[..., : H * Dk].view(B, S, N, H, Dk).transpose(2, 3)
+            k = qkv[..., H * Dk : 2 * H * Dk].view(B, S, N, H, Dk).transpose(2, 3)
+            v = qkv[..., 2 * H * Dk :].view(B, S, N, H, Dv).transpose(2, 3)
+            out = ops.pair_bias_attention(q, k, v, logits, None, ly.scale, fp32_qk=True)
+            out = out.transpose(2, 3).reshape(B, S, N, H * Dv)
+            gated = ao.K.gemm(xn, w["g"], None, None, out.contiguous(), 3, False)          # sigmoid(xn Wg^T) * out
+            x = torch.addcmul(x, gates[..., i, 0, :], ao.K.gemm(gated, w["o"], None, None, None, 0, False))
+            xn = torch.addcmul(cond[..., i, 3, :], cond[..., i, 2, :], ops.layer_norm(x))
+            hidden = ao.K.gemm(xn, w["w1"], None, None, None, 2, False)                    # SwiGLU in the epilogue
+            x = torch.addcmul(x, gates[..., i, 1, :], ao.K.gemm(hidden, w["w2"], None, None, None, 0, False))
+        return ops.layer_norm(x, self.output_norm_w, None).to(act.dtype)
+
+    def _fast_ok(self, act, pair_logits) -> bool:
+        import os
+
+        if torch.is_grad_enabled() or not act.is_cuda or not ops.bf16_mode(act) or os.environ.get("DF3_DIFFUSION_FAST", "1") == "0":
+            return False
+        ly = self.layers[0]
+        nat = ops.fused(act.to(torch.bfloat16) if act.dtype != torch.bfloat16 else act, "gemm")
+        return (nat is not None and ly.to_k.weight.shape[1] % 64 == 0 and (ly.num_heads * ly.key_dim_per_head) % 8 == 0
+                and all(t.dtype == torch.bfloat16 for t in pair_logits))
+
     def run(self, act, single_cond, pair_logits):
         """``act`` ``[B, S, N, c]``, ``single_cond`` ``[B, S|1, N, cs]``, hoisted ``pair_logits``."""
+        if self._fast_ok(act, pair_logits):
+            return self._run_fast(act, single_cond, pair_logits)
         H, sbs = self.layers[0].num_heads, self.super_block_size
         cond_norm = ops.layer_norm(single_cond)
         for sb, logits in enumerate(pair_logits):
