@@ -170,10 +170,15 @@ def _tokenize_chain(chain, tok, asym, ent, sym):
         tok["atoms"].append(atoms)
 
     if isinstance(chain, LigandChainInput):
-        if chain.smiles and not chain.ccd_codes:
-            raise ValueError("SMILES ligands need a cheminformatics toolkit to build a conformer; give a CCD code with a "
-                             "conformer table instead")  # fmt: skip
-        for r, code in enumerate(chain.ccd_codes):
+        codes = list(chain.ccd_codes)
+        if chain.smiles and not codes:
+            # no dictionary entry: heavy-atom graph and an embedded conformer straight from the string
+            from .smiles import component_from_smiles
+
+            code, entry = component_from_smiles(chain.smiles)
+            ref_conformers._TABLE.setdefault(code, entry)
+            codes = [code]
+        for r, code in enumerate(codes):
             names, elements, charges, coords = _component(code)
             for a in range(len(names)):  # one token per atom, all sharing the residue index
                 add(const.RES_TYPE_ORDER["UNK"], const.MOL_NONPOLYMER, r, (code, [names[a]], [elements[a]], [charges[a]], coords[a : a + 1]))

@@ -541,3 +541,35 @@ def test_logit_files_follow_the_reference_layout(tmp_path):
     assert np.abs(logit_codec.load_logits(old)["pae"] - pae).max() < 2e-2 and logit_codec.head_names(old) == ["pae"]
     with pytest.raises(ValueError):
         logit_codec.save_logits(str(tmp_path / "x.npz"), pae=pae, scheme="int3")
+
+
+def test_smiles_ligands_without_a_toolkit():
+    """SMILES -> heavy-atom graph (charges, bond orders, rings, branches, dots) -> embedded conformer -> a prediction job
+    whose ligand has one token per atom and the bonds of the string."""
+    from deepfold3_dev_b200.data import smiles as smi
+    from deepfold3_dev_b200.data.parse.json_input import parse_json_input
+
+    el, ch, bonds, arom = smi.parse_smiles("CC(=O)Oc1ccccc1C(=O)[O-]")       # aspirin, deprotonated
+    assert el.count(6) == 9 and el.count(8) == 4 and sum(ch) == -1 and len(bonds) == 13
+    assert sum(1 for *_, o in bonds if o == 4) == 6 and sum(1 for *_, o in bonds if o == 2) == 2 and sum(arom) == 6
+    el, ch, bonds, _ = smi.parse_smiles("[NH3+][C@@H](C)C(=O)[O-].[Na+]")     # explicit H counts, stereo mark, a counter-ion
+    assert el == [7, 6, 6, 6, 8, 8, 11] and ch == [1, 0, 0, 0, 0, -1, 1] and len(bonds) == 5
+    assert len(smi.parse_smiles("C%12CCCCC%12")[2]) == 6 and len(smi.parse_smiles("N#Cc1ccccc1")[0]) == 8
+    for bad in ("C1CC", "C(C", "CQ", "C)"):
+        with pytest.raises(ValueError):
+            smi.parse_smiles(bad)
+    code, entry = smi.component_from_smiles("c1ccc2[nH]ccc2c1")               # indole: two fused rings
+    assert code == smi.component_from_smiles("c1ccc2[nH]ccc2c1")[0] and entry["atoms"][:2] == ["C1", "C2"]
+    x = np.asarray(entry["coords"])
+    for a, b, _ in entry["bonds"]:
+        assert 1.2 < np.linalg.norm(x[a] - x[b]) < 1.7
+    d = np.linalg.norm(x[:, None] - x[None], axis=-1) + 9 * np.eye(len(x))
+    assert d.min() > 1.1                                                       # no two atoms on top of each other
+    assert np.linalg.svd(x - x.mean(0), compute_uv=False)[2] < 0.5             # the fused ring system is flat
+    job = {"name": "lig", "modelSeeds": [1], "sequences": [{"protein": {"id": "A", "sequence": "MKTAYIAKQR"}},
+                                                             {"ligand": {"id": "L", "smiles": "CC(=O)Oc1ccccc1C(=O)O"}}]}
+    inp = InferenceInput.from_job(parse_json_input(job)[0], msa_crop_size=4)
+    f = inp.features
+    lig = f["mol_type"] == 3
+    assert int(lig.sum()) == 13 and int(f["ref_mask"][lig].sum()) == 13
+    assert int(f["bond_matrix"][lig][:, lig].sum()) == 2 * 13                   # 13 bonds, symmetric
