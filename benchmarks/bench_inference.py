@@ -3,8 +3,9 @@
 
     python benchmarks/bench_inference.py --tokens 1024 --samples 5 --recycles 10 --steps 200 [--impl ours|reference]
 
-Default config is the second headline metric: N = 1024 tokens (4 protein chains), 5 samples, 10 recycles,
-200 sampler steps, 1024 MSA rows, 4 templates, bf16 autocast, random-init weights, synthetic features.
+Default config is the second headline metric: N = 1024 tokens (3 protein chains + one 30-atom ligand), 5 samples,
+10 recycles, 200 sampler steps, 4096 MSA rows, no templates, bf16 autocast, random-init weights, synthetic features
+(the same job as ``bench.py --config infer1024``, which also runs it on several GPUs and reports end-to-end time).
 One untimed prediction warms kernels and (for this package) captures the sampler's CUDA graph; then
 ``--repeats`` predictions are timed with CUDA events and the median is reported on one JSON line.
 ``--impl reference`` runs the unmodified reference package from ``baseline/_ref`` with its ``inference``
@@ -25,12 +26,13 @@ sys.path.insert(0, ROOT)
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--tokens", type=int, default=1024)
-    ap.add_argument("--chains", type=int, default=4)
+    ap.add_argument("--chains", type=int, default=3, help="protein chains")
+    ap.add_argument("--ligand-atoms", type=int, default=30, help="atoms of the one ligand chain (0: no ligand)")
     ap.add_argument("--samples", type=int, default=5)
     ap.add_argument("--recycles", type=int, default=10)
     ap.add_argument("--steps", type=int, default=200)
-    ap.add_argument("--msa", type=int, default=1024)
-    ap.add_argument("--templates", type=int, default=4)
+    ap.add_argument("--msa", type=int, default=4096)
+    ap.add_argument("--templates", type=int, default=0)
     ap.add_argument("--repeats", type=int, default=2)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     args = ap.parse_args()
@@ -40,8 +42,10 @@ def main():
     from deepfold3_dev_b200.data.synthetic import split_lengths, synthetic_complex
 
     dev = torch.device("cuda", 0)
-    feats = synthetic_complex([("protein", n) for n in split_lengths(args.tokens, args.chains)], num_msa=args.msa,
-                              num_templates=args.templates, seed=11, with_gt=False)  # fmt: skip
+    chains = [("protein", n) for n in split_lengths(args.tokens - args.ligand_atoms, args.chains)]
+    if args.ligand_atoms:
+        chains.append(("ligand", args.ligand_atoms))
+    feats = synthetic_complex(chains, num_msa=args.msa, num_templates=args.templates, seed=11, with_gt=False)
     feats = {k: v.to(dev) for k, v in feats.items()}
     if args.impl == "reference":
         sys.path.insert(0, os.path.join(ROOT, "baseline", "_ref"))
@@ -88,7 +92,7 @@ def main():
     print(json.dumps({
         "metric": "inference seconds per prediction", "value": times[len(times) // 2], "unit": "s", "higher_is_better": False,
         "impl": args.impl, "dtype": "bf16", "data": "synthetic (random sequences, random-init weights)",
-        "config": {"tokens": args.tokens, "chains": args.chains, "samples": args.samples, "recycles": args.recycles,
+        "config": {"tokens": args.tokens, "chains": args.chains, "ligand_atoms": args.ligand_atoms, "samples": args.samples, "recycles": args.recycles,
                    "sampler_steps": args.steps, "msa_rows": args.msa, "templates": args.templates,
                    "peak_mem_gib": round(torch.cuda.max_memory_allocated() / 2**30, 2)},
         "all_s": times,

@@ -211,6 +211,17 @@ def adamw_ema_flat(p, g, m, v, ema, decay, scale, lr, b1, b2, eps, bc1, bc2, ema
 # with a library GEMM (nothing of size [rows, 2 * hidden] is kept between forward and backward).
 BF16 = torch.bfloat16
 _W16: dict = {}  # (data_ptr, shape) per weight -> (versions, bf16 tensor); emptied whenever parameters change
+
+
+def _cache_put(key, value, sources) -> None:
+    """Store a cast and tie its life to the tensors it was made from: when one of them is collected the entry goes too.
+    Keys are storage addresses, and the allocator hands a freed parameter's address (with an equal version counter) to
+    the next model built in the process; without the eviction that model would be served the old model's weights."""
+    if len(_W16) > 50000:
+        _W16.clear()
+    _W16[key] = value
+    for w in sources:
+        weakref.finalize(w, _W16.pop, key, None)
 _MIRROR: dict = {}  # (data_ptr, shape) of an fp32 parameter -> [bf16 view kept current by the optimizer, version]
 
 
@@ -260,9 +271,7 @@ def bf16_weight(*ws):
         parts = [p if p is not None else w.detach().to(BF16) for p, w in zip(parts, ws)]
         t = (parts[0] if len(parts) == 1 else torch.cat(parts, 0)).contiguous()
     if not capturing:  # a cast made inside a CUDA-graph capture belongs to that graph's pool
-        if len(_W16) > 50000:
-            _W16.clear()
-        _W16[key] = (sig, t)
+        _cache_put(key, (sig, t), ws)
     return t
 
 
@@ -333,7 +342,7 @@ def _stacked_gate_proj(w_gate, w_proj, deinterleave: bool):
         parts = [w.detach()[i::2] for w in (w_gate, w_proj) for i in (0, 1)]
         t = torch.cat(parts, 0).to(BF16).contiguous()
     if not capturing:
-        _W16[key] = (sig, t)
+        _cache_put(key, (sig, t), (w_gate, w_proj))
     return t
 
 

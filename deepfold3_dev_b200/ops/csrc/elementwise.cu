@@ -336,6 +336,85 @@ __global__ void __launch_bounds__(256) plane_layer_norm_fwd_kernel(const __nv_bf
   }
 }
 
+// LayerNorm forward for 128-channel bf16 rows (the pair tensor) with eight lanes per row: a warp normalises four rows at
+// once, every lane holds 16 channels (two 16-byte loads), and the two reductions take three shuffle steps over a group
+// of eight lanes instead of five over the warp, i.e. 1.5 shuffles per row instead of 10 (the shuffle unit, one warp
+// instruction per clock per SM, is what bounded the warp-per-row form below copy bandwidth). Two row groups per
+// iteration keep 2 KiB of loads in flight per warp.
+__global__ void __launch_bounds__(256) layer_norm_fwd_lane8_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ w,
+                                                                   const float* __restrict__ b, __nv_bfloat16* __restrict__ y,
+                                                                   float* __restrict__ mean_out, float* __restrict__ rstd_out,
+                                                                   int64_t rows, float eps) {
+  constexpr int C = 128, kGroups = 2;
+  const int lane = threadIdx.x & 31, sub = lane & 7, row_in_warp = lane >> 3;
+  float wv[16], bv[16];
+#pragma unroll
+  for (int v = 0; v < 2; ++v)
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const int c = (sub + 8 * v) * 8 + e;
+      wv[8 * v + e] = w ? w[c] : 1.f;
+      bv[8 * v + e] = b ? b[c] : 0.f;
+    }
+  const int64_t warp_id = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int64_t warp_stride = (int64_t)gridDim.x * (blockDim.x >> 5) * 4 * kGroups;
+  for (int64_t row0 = warp_id * 4 * kGroups; row0 < rows; row0 += warp_stride) {
+    uint4 raw[kGroups][2];
+#pragma unroll
+    for (int gidx = 0; gidx < kGroups; ++gidx) {
+      const int64_t want = row0 + gidx * 4 + row_in_warp;
+      const int64_t row = want < rows ? want : rows - 1;  // tail lanes re-read the last row; their stores are skipped
+      const uint4* xr = reinterpret_cast<const uint4*>(x + row * C);
+      raw[gidx][0] = xr[sub];
+      raw[gidx][1] = xr[sub + 8];
+    }
+#pragma unroll
+    for (int gidx = 0; gidx < kGroups; ++gidx) {
+      const int64_t row = row0 + gidx * 4 + row_in_warp;
+      float v[16];
+      float s = 0.f;
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const uint32_t ww[4] = {raw[gidx][h].x, raw[gidx][h].y, raw[gidx][h].z, raw[gidx][h].w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const __nv_bfloat162 pr = *reinterpret_cast<const __nv_bfloat162*>(&ww[e]);
+          v[8 * h + 2 * e] = __low2float(pr);
+          v[8 * h + 2 * e + 1] = __high2float(pr);
+          s += v[8 * h + 2 * e] + v[8 * h + 2 * e + 1];
+        }
+      }
+#pragma unroll
+      for (int o = 4; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+      const float mean = s * (1.f / C);
+      float q = 0.f;
+#pragma unroll
+      for (int k = 0; k < 16; ++k) q += (v[k] - mean) * (v[k] - mean);
+#pragma unroll
+      for (int o = 4; o > 0; o >>= 1) q += __shfl_xor_sync(0xffffffffu, q, o);
+      const float rstd = rsqrtf(q * (1.f / C) + eps);
+      if (row < rows) {
+        uint4* yr = reinterpret_cast<uint4*>(y + row * C);
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          uint32_t out[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int k = 8 * h + 2 * e;
+            const __nv_bfloat162 pr = __floats2bfloat162_rn((v[k] - mean) * rstd * wv[k] + bv[k], (v[k + 1] - mean) * rstd * wv[k + 1] + bv[k + 1]);
+            out[e] = *reinterpret_cast<const uint32_t*>(&pr);
+          }
+          yr[sub + 8 * h] = make_uint4(out[0], out[1], out[2], out[3]);
+        }
+        if (sub == 0) {
+          mean_out[row] = mean;
+          rstd_out[row] = rstd;
+        }
+      }
+    }
+  }
+}
+
 // The same with 16-byte accesses on both sides, for M % 8 == 0. A block owns 128 consecutive positions: every thread
 // fetches eight positions of a plane per load (a half-warp covers 256 contiguous bytes of the plane) into a bf16 tile
 // [C][130] (pitch 65 words: the column reads of the second phase hit 32 different banks), each warp then normalises
@@ -787,7 +866,11 @@ std::tuple<Tensor, Tensor, Tensor> df3_layer_norm_fwd(const Tensor& x, const c10
                                                        warps * 32, 0, stream()>>>(                                   \
       (const __nv_bfloat16*)x.data_ptr(), wp, bp, (__nv_bfloat16*)y.data_ptr(), mean.data_ptr<float>(),            \
       rstd.data_ptr<float>(), rows, (float)eps)
-  if (vec_ok && C == 128) DF3_LN_VEC(1);
+  if (vec_ok && C == 128 && reinterpret_cast<uintptr_t>(x.data_ptr()) % 16 == 0 && reinterpret_cast<uintptr_t>(y.data_ptr()) % 16 == 0)
+    df3::layer_norm_fwd_lane8_kernel<<<(unsigned)std::min<int64_t>((rows + 63) / 64, 148 * 16), 256, 0, stream()>>>(
+        (const __nv_bfloat16*)x.data_ptr(), wp, bp, (__nv_bfloat16*)y.data_ptr(), mean.data_ptr<float>(), rstd.data_ptr<float>(), rows,
+        (float)eps);
+  else if (vec_ok && C == 128) DF3_LN_VEC(1);
   else if (vec_ok && C == 256) DF3_LN_VEC(2);
   else if (vec_ok && C == 384) DF3_LN_VEC(3);
   else if (vec_ok && C == 512) DF3_LN_VEC(4);

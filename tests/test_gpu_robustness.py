@@ -162,3 +162,115 @@ print("CHECKED_OK")
     env = dict(os.environ, DF3_BOUNDS_CHECK="1", PYTHONPATH=root)
     out = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=600)
     assert out.returncode == 0 and "CHECKED_OK" in out.stdout, out.stdout[-2000:] + out.stderr[-2000:]
+
+
+# ---- forward attention and fused epilogues on hard inputs (cases after the reference's robustness suites for its
+# ---- fused attention and fused modules: magnitude sweeps, heavy tails, masked rows, head widths, ragged lengths)
+def _attention_reference(q, k, v, bias, mask, scale):
+    s = torch.einsum("brhid,brhjd->brhij", q.float(), k.float()) * scale
+    if bias is not None:
+        s = s + bias.float()[:, None]
+    if mask is not None:
+        s = s + 1e9 * (mask.float()[:, :, None, None, :] - 1.0)
+    return torch.einsum("brhij,brhjd->brhid", torch.softmax(s, dim=-1), v.float())
+
+
+def _close(got, want, atol, rtol):
+    torch.testing.assert_close(got.float(), want.float(), atol=atol, rtol=rtol)
+
+
+@pytest.mark.parametrize("D", [16, 24, 32, 48, 64])
+@pytest.mark.parametrize("N", [197, 264])
+def test_attention_forward_head_widths_and_ragged_lengths(nat, D, N):
+    g = torch.Generator(device="cuda").manual_seed(D + N)
+    q, k, v = (torch.randn(1, 3, 4, N, D, device="cuda", generator=g).bfloat16() for _ in range(3))
+    bias = torch.randn(1, 4, N, N, device="cuda", generator=g).bfloat16()
+    mask = (torch.rand(1, 3, N, device="cuda", generator=g) > 0.2).float()
+    mask[..., 0] = 1
+    out, _ = torch.ops.df3.attention_fwd(q, k, v, bias, mask, D**-0.5, False)
+    _close(out, _attention_reference(q, k, v, bias, mask, D**-0.5), atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("magnitude", [1e-2, 1.0, 30.0, 300.0, 1000.0])
+def test_attention_forward_logit_magnitude_sweep(nat, magnitude):
+    """From nearly uniform rows to rows where one key takes everything (|logit| up to 1000: the running maximum and the
+    rescaling have to carry it; a plain exp would overflow at 89)."""
+    g = torch.Generator(device="cuda").manual_seed(3)
+    N, D = 256, 32
+    q, k, v = (torch.randn(1, 2, 4, N, D, device="cuda", generator=g).bfloat16() for _ in range(3))
+    bias = (magnitude * torch.randn(1, 4, N, N, device="cuda", generator=g)).bfloat16()
+    out, _ = torch.ops.df3.attention_fwd(q, k, v, bias, None, D**-0.5, False)
+    assert bool(torch.isfinite(out).all())
+    _close(out, _attention_reference(q, k, v, bias, None, D**-0.5), atol=3e-2, rtol=3e-2)
+
+
+def test_attention_forward_heavy_tails_and_masked_rows(nat):
+    g = torch.Generator(device="cuda").manual_seed(4)
+    N, D = 200, 32
+    q, k, v = (torch.randn(1, 4, 4, N, D, device="cuda", generator=g) for _ in range(3))
+    q = (q * (1 + 20 * (torch.rand_like(q) > 0.99))).bfloat16()      # 1 % of the entries 20 times larger
+    k, v = k.bfloat16(), v.bfloat16()
+    bias = torch.randn(1, 4, N, N, device="cuda", generator=g).bfloat16()
+    mask = torch.ones(1, 4, N, device="cuda")
+    mask[0, 1] = 0               # a row with every key masked: uniform weights, finite output
+    mask[0, 2, 1:] = 0           # a row with one key left
+    out, _ = torch.ops.df3.attention_fwd(q, k, v, bias, mask, D**-0.5, False)
+    assert bool(torch.isfinite(out).all())
+    ref = _attention_reference(q, k, v, bias, mask, D**-0.5)
+    live = [0, 2, 3]   # the fully masked row has no defined answer once |logit| exceeds the fp32 spacing at 1e9 (64):
+    _close(out[:, live], ref[:, live], atol=4e-2, rtol=3e-2)   # every statement rounds the logits away differently
+    assert float(out[0, 1].abs().max()) <= float(v[0, 1].float().abs().max()) + 1e-2   # still a convex combination of V
+    _close(out[0, 2], v[0, 2, :, :1, :].expand_as(out[0, 2]), atol=1e-2, rtol=1e-2)   # the one visible key wins outright
+
+
+@pytest.mark.parametrize("magnitude", [1e-2, 1.0, 20.0, 200.0])
+def test_fused_epilogues_on_saturating_and_heavy_tailed_inputs(nat, magnitude):
+    """Gated, SwiGLU and sigmoid-gate epilogues when the pre-activations saturate the sigmoid (|x| up to hundreds) and
+    carry outliers: per-element agreement with the fp32 statement on bf16-rounded operands."""
+    g = torch.Generator(device="cuda").manual_seed(5)
+    x = torch.randn(1500, 128, device="cuda", generator=g)
+    x = (x * (1 + 10 * (torch.rand_like(x) > 0.995))).bfloat16()
+    w = (magnitude * 0.1 * torch.randn(256, 128, device="cuda", generator=g)).bfloat16()
+    xf, wf = x.float(), w.float()
+    gate, proj = xf @ wf[:128].t(), xf @ wf[128:].t()
+    scale = proj.abs().max().item()
+    got = torch.ops.df3.gemm(x, w, None, None, None, 1, False)
+    _close(got, torch.sigmoid(gate) * proj, atol=1e-2 * max(scale, 1e-3), rtol=2e-2)
+    got = torch.ops.df3.gemm(x, w, None, None, None, 2, False)
+    want = torch.nn.functional.silu(gate) * proj
+    _close(got, want, atol=1e-2 * max(want.abs().max().item(), 1e-3), rtol=2e-2)
+    other = torch.randn(1500, 128, device="cuda", generator=g).bfloat16()
+    got = torch.ops.df3.gemm(x, w[:128].contiguous(), None, None, other, 3, False)
+    _close(got, torch.sigmoid(gate) * other.float(), atol=2e-2, rtol=2e-2)
+    assert torch.ops.df3.gemm_status() == 0
+
+
+def test_model_path_with_a_ragged_token_count(nat):
+    """101 tokens (not a multiple of 8, 16 or 128) through a bf16 Pairformer block, forward and backward: finite, and
+    close to the fp32 PyTorch statement of the same block."""
+    from deepfold3_dev_b200.models.evoformer import PairFormerBlock
+    from tests.helpers import wake_zero_init
+
+    torch.manual_seed(1)
+    block = PairFormerBlock(128, 384).cuda().eval()
+    wake_zero_init(block)
+    N = 101
+    pair = torch.randn(1, N, N, 128, device="cuda", requires_grad=True)
+    single = torch.randn(1, N, 384, device="cuda", requires_grad=True)
+    seq_mask = torch.ones(1, N, device="cuda")
+    seq_mask[0, -4:] = 0
+    pair_mask = seq_mask[:, :, None] * seq_mask[:, None, :]
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        p, s = block(pair, single, pair_mask, seq_mask)
+    (p.float().square().mean() + s.float().square().mean()).backward()
+    assert bool(torch.isfinite(p).all()) and bool(torch.isfinite(pair.grad).all()) and bool(torch.isfinite(single.grad).all())
+    import os
+
+    os.environ["DF3_DISABLE_OPS"] = "gemm,matmul,gated_dual_linear,transition,pair_bias_attention,linear_planes,sigmoid_gate_mul,layer_norm,plane_layer_norm"
+    try:
+        with torch.no_grad():
+            p32, s32 = block(pair.detach(), single.detach(), pair_mask, seq_mask)
+    finally:
+        del os.environ["DF3_DISABLE_OPS"]
+    err = (p.float() - p32).pow(2).mean().sqrt() / p32.pow(2).mean().sqrt()
+    assert float(err) < 2e-2, float(err)
