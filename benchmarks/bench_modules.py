@@ -119,6 +119,9 @@ def main():
         rows.append(row)
         del inputs
         torch.cuda.empty_cache()
+    from deepfold3_dev_b200.ops import autograd_ops
+
+    autograd_ops.check_status()  # a kernel wait that ran out would make the timings meaningless
     if args.json:
         with open(args.json, "w") as f:
             json.dump(rows, f, indent=1)

@@ -193,6 +193,10 @@ def run_job(model, inp, out_dir: str, device, seeds=None, num_recycles: int = 10
                 dist.all_gather_object(gathered, mine)
                 mine = sorted((s for part in gathered for s in part), key=lambda s: s.get("sample", 0))
             summaries += mine
+    if torch.cuda.is_available() and torch.device(device).type == "cuda":
+        from ..ops import autograd_ops
+
+        autograd_ops.check_status()  # a kernel wait that ran out anywhere in the job makes its files suspect: fail loudly
     if not main:
         return summaries
     if summaries:
