@@ -252,37 +252,71 @@ def run_ours(args):
     from deepfold3_dev_b200.parallel.dist import barrier, init_process_group
     from deepfold3_dev_b200.training.trainer import Trainer
 
-    ckpt_default = "1" if args.cfg.get("checkpointing") else "0"
-    os.environ.setdefault("DF3_DIFFUSION_CKPT", ckpt_default)  # crop 384 keeps the denoiser activations of all 48 samples
     info = init_process_group(timeout_s=1800.0)
     world = info.world_size
     if world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
-    model_cfg = ModelConfig()
-    model_cfg.msa_crop_size = N_MSA
-    model_cfg.optim.use_gradient_checkpointing = os.environ.get("DF3_CKPT", ckpt_default) == "1"
-    if args.blocks:
-        model_cfg.pairformer.num_layer = args.blocks
-    chunk = int(os.environ.get("DF3_DIFFUSION_CHUNK", "8" if args.cfg.get("checkpointing") else "0"))
-    train_cfg = TrainingConfig(**shared_train_settings(args.tokens), diffusion_chunk_size=chunk,
-                               per_rank_grad_clip=False, output_dir="/tmp/df3_bench")  # fmt: skip
-    trainer = Trainer(train_cfg, model_cfg, dist_info=info)
     host_batch = make_host_batch(info.rank, args.tokens, args.cfg["chains"])
     dev_batch = {k: (v.to(info.device) if isinstance(v, torch.Tensor) else v) for k, v in host_batch.items()}
     flush_buf = torch.zeros(64 * 1024 * 1024, device=info.device)
+    # Memory policies (trunk checkpointing, denoiser checkpointing, diffusion chunk), fastest first; one that runs out of
+    # memory during warm-up is torn down and the next is built (all ranks move together). Crop 384 keeps everything
+    # resident; crop 768 recomputes the trunk and tries to keep the denoiser's activations before giving that up too.
+    # DF3_CKPT / DF3_DIFFUSION_CKPT / DF3_DIFFUSION_CHUNK pin one policy.
+    if args.cfg.get("checkpointing"):
+        ladder = [(True, False, 0), (True, True, 8)]
+    else:
+        ladder = [(False, False, 0)]
+    if any(k in os.environ for k in ("DF3_CKPT", "DF3_DIFFUSION_CKPT", "DF3_DIFFUSION_CHUNK")):
+        first = ladder[0]
+        ladder = [(os.environ.get("DF3_CKPT", "1" if first[0] else "0") == "1",
+                   os.environ.get("DF3_DIFFUSION_CKPT", "1" if first[1] else "0") != "0",
+                   int(os.environ.get("DF3_DIFFUSION_CHUNK", str(first[2]))))]  # fmt: skip
+    trainer = model_cfg = None
+    for trunk_ckpt, diff_ckpt, chunk in ladder:
+        os.environ["DF3_DIFFUSION_CKPT"] = "1" if diff_ckpt else "0"
+        model_cfg = ModelConfig()
+        model_cfg.msa_crop_size = N_MSA
+        model_cfg.optim.use_gradient_checkpointing = trunk_ckpt
+        if args.blocks:
+            model_cfg.pairformer.num_layer = args.blocks
+        train_cfg = TrainingConfig(**shared_train_settings(args.tokens), diffusion_chunk_size=chunk,
+                                   per_rank_grad_clip=False, output_dir="/tmp/df3_bench")  # fmt: skip
+        fits = 1
+        try:
+            trainer = Trainer(train_cfg, model_cfg, dist_info=info)
 
-    def device_step(i):
-        trainer.state.global_step = i
-        loss, _, _ = trainer.micro_step(dict(dev_batch), num_recycles=recycles_for(i))
-        trainer.engine.step_or_skip(trainer.state)
+            def device_step(i, trainer=trainer):
+                trainer.state.global_step = i
+                loss, _, _ = trainer.micro_step(dict(dev_batch), num_recycles=recycles_for(i))
+                trainer.engine.step_or_skip(trainer.state)
 
-    def e2e_step(i):
-        trainer.state.global_step = i
-        trainer.train_step(dict(host_batch), num_recycles=recycles_for(i))
+            def e2e_step(i, trainer=trainer):
+                trainer.state.global_step = i
+                trainer.train_step(dict(host_batch), num_recycles=recycles_for(i))
 
-    for i in range(args.warmup):
-        device_step(i)
-    torch.cuda.synchronize()
+            for i in range(args.warmup):
+                device_step(i)
+            torch.cuda.synchronize()
+        except torch.OutOfMemoryError:
+            fits = 0
+        if world > 1:
+            import torch.distributed as dist
+
+            flag = torch.tensor([fits], device=info.device)
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+            fits = int(flag.item())
+        if fits:
+            break
+        trainer = None
+        device_step = e2e_step = None
+        import gc
+
+        gc.collect()
+        torch.cuda.empty_cache()
+        torch.cuda.reset_peak_memory_stats()
+    if trainer is None:
+        raise SystemExit("out of memory under every memory policy")
     sampler = ClockSampler(info.local_rank)
     sampler.start()
     autograd_ops.launch_count(reset=True)
@@ -298,8 +332,7 @@ def run_ours(args):
     peak = torch.cuda.max_memory_allocated() / 2**30
     if info.is_main:
         emit(args, "ours", step_ms, e2e_ms, clocks, launches, batch_bytes(host_batch),
-             {"activation_checkpointing": model_cfg.optim.use_gradient_checkpointing,
-              "diffusion_checkpointing": os.environ.get("DF3_DIFFUSION_CKPT") != "0", "diffusion_chunk": chunk,
+             {"activation_checkpointing": trunk_ckpt, "diffusion_checkpointing": diff_ckpt, "diffusion_chunk": chunk,
               "grad_transport": trainer.grad_sync.transport if world > 1 else "none",
               "optimizer_step": "one fused kernel" if trainer.grad_sync.fused_step_engine(trainer.optimizer) is not None else "classic",
               "trunk_graphs": _graph_state(trainer.model),
