@@ -339,6 +339,9 @@ def featurize_record(st, rec, load_msa, *, max_tokens: int = 384, max_atoms: int
     feats, read, skipped = attach_cropped_msa(feats, kept, chain_cols, lambda a: load_msa(rec.chains[old_ids[a]]),
                                               max_msa_rows=max_msa_rows)  # fmt: skip
     feats = rotate_reference_conformers(feats, gen)
+    from .symmetry import symmetry_features
+
+    feats.update(symmetry_features(feats))  # exchangeable atoms and ligand automorphisms, indexed in the cropped example
     info = rec.structure_info
     feats["resolution"] = torch.tensor(float(info.resolution) if info and info.resolution else 0.0)
     feats["is_distillation"] = torch.tensor(bool(is_distillation))

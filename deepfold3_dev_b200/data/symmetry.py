@@ -143,8 +143,14 @@ def apply_ligand_token_permutation(pred_pos, gt_pos, atom_mask, perm_table):
     chosen.scatter_(-1, best_g, best_cost < 0.0)
     # a group index can be written by a ligand that does not own it only if that ligand's best cost is inf -> False
     row_on = chosen.index_select(-1, gid)  # [..., R]
+    # a token is listed once per permutation of its ligand, and at most one of those permutations is switched on: add
+    # the chosen move as a difference (rows that stay off add zero) instead of writing every row, where the last
+    # write of a repeated index would win
+    move = torch.where(row_on.unsqueeze(-1), g_src - g_dst, torch.zeros_like(g_dst))
     out = gt_pos.detach().clone()
-    out[..., dst, 0, :] = torch.where(row_on.unsqueeze(-1), g_src, g_dst)
+    first = out[..., :, 0, :].clone()
+    first.index_add_(-2, dst, move)
+    out[..., :, 0, :] = first
     return out
 
 
@@ -412,4 +418,52 @@ def graph_automorphisms(elements, edges, limit: int = 1000, orders=None) -> list
 
     place(0)
     out.sort(key=lambda p_: p_ != list(range(n)))
+    return out
+
+
+def symmetry_features(feats: dict, max_ligand_atoms: int = 64, max_perms: int = 32) -> dict:
+    """The permutation tables of one (cropped) example, built from its own features so that every index refers to the
+    tokens that survived the crop (reference: data/feature/featurizer.py training extras, symmetry/atom_perms.py,
+    symmetry/ligand_perms.py):
+
+    ``atom_swap_pairs`` ``[P, 3]``   (token, atom slot a, atom slot b) for the exchangeable atoms of standard residues;
+    ``ligand_perms``    ``[R, 4]``   (ligand, permutation, destination token, source token) for every non-identity
+                                     automorphism of each ligand whose atoms are all present in the crop.
+    """
+    from . import const
+
+    res_type = feats["res_type"].tolist()
+    mol_type = feats["mol_type"].tolist()
+    chars = feats["ref_atom_name_chars"]
+    mask = feats["ref_mask"]
+    names_of = lambda t: ["".join(chr(int(c) + 32) for c in chars[t, a]).strip() for a in range(int(mask[t].sum()))]  # noqa: E731
+    swaps = []
+    for t, (rt, mt) in enumerate(zip(res_type, mol_type)):
+        if mt == const.MOL_NONPOLYMER or int(mask[t].sum()) <= 1:
+            continue
+        name = const.RES_TYPE_INDEX_TO_NAME.get(int(rt))
+        if name in RESIDUE_SWAPS:
+            swaps += [(t, a, b) for a, b in build_residue_symmetry_pairs(name, names_of(t))]
+    out = {"atom_swap_pairs": torch.tensor(swaps, dtype=torch.long).reshape(-1, 3)}
+    # ligands: atom tokens of non-polymer chains grouped by (chain, residue)
+    groups: dict[tuple[int, int], list[int]] = {}
+    asym, resi = feats["asym_id"].tolist(), feats["residue_index"].tolist()
+    for t, mt in enumerate(mol_type):
+        if mt == const.MOL_NONPOLYMER and int(mask[t].sum()) == 1:
+            groups.setdefault((asym[t], resi[t]), []).append(t)
+    bonds = feats.get("bond_matrix")
+    rows = []
+    for lig, members in enumerate(groups.values()):
+        if not 1 < len(members) <= max_ligand_atoms or bonds is None:
+            continue
+        idx = torch.tensor(members)
+        sub = bonds[idx][:, idx].reshape(len(members), len(members)) > 0
+        edges = [(int(a), int(b)) for a, b in torch.nonzero(torch.triu(sub, 1)).tolist()]
+        if not edges:
+            continue
+        elements = feats["ref_element"][idx, 0].tolist()
+        perms = graph_automorphisms(elements, edges, limit=max_perms + 1)
+        for pid, perm in enumerate(perms[1:]):
+            rows += [(lig, pid, members[dst], members[src]) for dst, src in enumerate(perm) if dst != src]
+    out["ligand_perms"] = torch.tensor(rows, dtype=torch.long).reshape(-1, 4)
     return out

@@ -573,3 +573,40 @@ def test_smiles_ligands_without_a_toolkit():
     lig = f["mol_type"] == 3
     assert int(lig.sum()) == 13 and int(f["ref_mask"][lig].sum()) == 13
     assert int(f["bond_matrix"][lig][:, lig].sum()) == 2 * 13                   # 13 bonds, symmetric
+
+
+def test_permutation_tables_are_built_from_cropped_features():
+    """Exchangeable residue atoms and ligand automorphisms, indexed in the example they were computed from, and usable
+    by the ground-truth symmetry resolution: a prediction that equals the permuted ground truth costs nothing."""
+    from deepfold3_dev_b200.data.symmetry import apply_ligand_token_permutation, apply_token_atom_permutation, symmetry_features
+
+    f = synthetic_complex([("protein", 24), ("ligand", 6)], num_msa=2, num_templates=0, seed=4)
+    lig = torch.nonzero(f["mol_type"] == 3).flatten()
+    assert len(lig) == 6
+    # make the ligand a six-ring of carbons: 12 automorphisms
+    f["ref_element"][lig, 0] = 6
+    f["bond_matrix"] = torch.zeros(30, 30, 1)
+    for k in range(6):
+        a, b = int(lig[k]), int(lig[(k + 1) % 6])
+        f["bond_matrix"][a, b, 0] = f["bond_matrix"][b, a, 0] = 1.0
+    tables = symmetry_features(f)
+    perms = tables["ligand_perms"]
+    assert perms.shape[1] == 4 and int(perms[:, 1].max()) + 1 == 11 and set(perms[:, 2].tolist()) <= set(lig.tolist())
+    swaps = tables["atom_swap_pairs"]
+    names = lambda t, a: "".join(chr(int(c) + 32) for c in f["ref_atom_name_chars"][t, a]).strip()  # noqa: E731
+    swappable = {"ASP": {"OD1", "OD2"}, "GLU": {"OE1", "OE2"}, "PHE": {"CD1", "CD2", "CE1", "CE2"}, "TYR": {"CD1", "CD2", "CE1", "CE2"},
+                 "ARG": {"NH1", "NH2"}, "LEU": {"CD1", "CD2"}, "VAL": {"CG1", "CG2"}}  # fmt: skip
+    for t, a, b in swaps.tolist():
+        assert f["mol_type"][t] == 0 and {names(t, a), names(t, b)} <= set().union(*swappable.values())
+    # ground truth = prediction with the ring rotated by one position: the table finds the rotation and undoes it
+    gt = f["atom_gt_positions"].clone()
+    pred = gt.clone()
+    pred[lig, 0] = gt[lig.roll(1), 0]
+    fixed = apply_ligand_token_permutation(pred, gt, f["atom_gt_mask"], perms)
+    assert torch.allclose(fixed[lig, 0], pred[lig, 0])
+    if len(swaps):
+        t, a, b = swaps[0].tolist()
+        pred2 = gt.clone()
+        pred2[t, a], pred2[t, b] = gt[t, b], gt[t, a]
+        fixed2 = apply_token_atom_permutation(pred2, gt, f["atom_gt_mask"], swaps)
+        assert torch.allclose(fixed2[t, a], pred2[t, a]) and torch.allclose(fixed2[t, b], pred2[t, b])
