@@ -358,3 +358,98 @@ def test_component_dictionary_gz_and_json_table(tmp_path):
     finally:
         ref_conformers._TABLE.pop("ZZ1", None)
         ref_conformers._TABLE.pop("ZZ2", None)
+
+
+def test_dataset_tool_commands(tmp_path):
+    """The dataset maintenance commands on a one-entry prepared directory, through the command line."""
+    import json
+
+    from click.testing import CliRunner
+
+    from deepfold3_dev_b200.cli.main import cli
+    from deepfold3_dev_b200.data.types import Structure
+
+    src = tmp_path / "src"
+    src.mkdir()
+    (src / "one.cif").write_text(_mini_cif())
+    out = tmp_path / "out"
+    prepare_directory(str(src), str(out), StructureFilterConfig(min_residues=2))
+    rec = load_manifest(str(out / "manifest.json"))[0]
+    st = Structure.load(str(out / "structures" / "test.npz"))
+    seq = st.chain_canonical_seqs[rec.chains[0].chain_id]
+    run = CliRunner().invoke
+
+    # export-complexes: two protein copies -> one multimer entry
+    r = run(cli, ["export-complexes", "--data-dir", str(out), "--output", str(tmp_path / "cx.json")])
+    assert r.exit_code == 0, r.output
+    assert json.loads((tmp_path / "cx.json").read_text()) == {"test": [seq, seq]}
+
+    # import-msa: an A3M named anything, matched by its query sequence
+    a3m = tmp_path / "a3m" / "deep" / "whatever.a3m"
+    a3m.parent.mkdir(parents=True)
+    a3m.write_text(f">query\n{seq}\n>hit1\n{seq[:-1]}-\n>hit2\n{seq[0].lower()}{seq}\n")
+    r = run(cli, ["import-msa", "--data-dir", str(out), "--msa-dir", str(tmp_path / "a3m")])
+    assert r.exit_code == 0 and "1 written" in r.output, r.output
+    stored = MSA.load(str(out / "msa" / f"{rec.chains[0].msa_id}.npz"))
+    assert stored.sequences.shape == (2, len(seq))  # hit2 equals the query once its insertion is dropped: de-duplicated
+    r = run(cli, ["import-msa", "--data-dir", str(out), "--msa-dir", str(tmp_path / "a3m")])
+    assert "0 written" in r.output  # resume-safe: existing files stay
+
+    # import-paired-msa: <record>/<msa_id>.paired.a3m
+    paired = tmp_path / "paired" / "test"
+    paired.mkdir(parents=True)
+    (paired / f"{rec.chains[0].msa_id}.paired.a3m").write_text(f">query\n{seq}\n>p1\n{seq}\n")
+    r = run(cli, ["import-paired-msa", "--data-dir", str(out), "--paired-dir", str(tmp_path / "paired")])
+    assert r.exit_code == 0, r.output
+    after = load_manifest(str(out / "manifest.json"))[0]
+    assert after.chains[0].paired_msa_id == f"test/{rec.chains[0].msa_id}"
+    assert os.path.exists(out / "msa_paired" / "test" / f"{rec.chains[0].msa_id}.npz")
+
+    # enrich-manifest from an entries.idx line (id, header, date mm/dd/yy, compound, source, authors, resolution, method)
+    idx = tmp_path / "entries.idx"
+    idx.write_text("IDCODE, HEADER...\n-----\nTEST\tHYDROLASE\t03/15/99\tX\tY\tZ\t1.85\tX-RAY DIFFRACTION\n")
+    m = json.loads((out / "manifest.json").read_text())
+    m[0]["structure_info"].update(resolution=None, method=None, deposited=None)
+    (out / "manifest.json").write_text(json.dumps(m))
+    r = run(cli, ["enrich-manifest", "--data-dir", str(out), "--idx", str(idx)])
+    assert r.exit_code == 0 and "3 fields filled" in r.output, r.output
+    info = load_manifest(str(out / "manifest.json"))[0].structure_info
+    assert info.resolution == 1.85 and info.deposited == "1999-03-15" and info.method == "X-RAY DIFFRACTION"
+
+    # stamp-template-index-space: dry run changes nothing, the real run is idempotent
+    (out / "templates").mkdir()
+    (out / "templates" / "abc.json").write_text(json.dumps([{"pdb": "1abc", "chain": "A"}]))
+    r = run(cli, ["stamp-template-index-space", "--data-dir", str(out), "--dry-run"])
+    assert "1 would be stamped" in r.output and isinstance(json.loads((out / "templates" / "abc.json").read_text()), list)
+    r = run(cli, ["stamp-template-index-space", "--data-dir", str(out), "--space", "seqres"])
+    assert json.loads((out / "templates" / "abc.json").read_text())["index_space"] == "seqres"
+    r = run(cli, ["stamp-template-index-space", "--data-dir", str(out), "--space", "seqres"])
+    assert "0 stamped" in r.output
+    r = run(cli, ["stamp-template-index-space", "--data-dir", str(out), "--space", "struct"])
+    assert r.exit_code != 0  # already stamped with the other frame
+
+    # pack + pack-verify, then a corrupted source is caught
+    r = run(cli, ["pack", str(out / "structures"), str(tmp_path / "pk")])
+    assert r.exit_code == 0
+    assert run(cli, ["pack-verify", str(out / "structures"), str(tmp_path / "pk")]).exit_code == 0
+    with open(out / "structures" / "test.npz", "ab") as f:
+        f.write(b"x")
+    assert run(cli, ["pack-verify", str(out / "structures"), str(tmp_path / "pk")]).exit_code != 0
+
+    # drop-obsolete with a local id list, deleting the files
+    r = run(cli, ["drop-obsolete", "--data-dir", str(out), "--ids-file", str(tmp_path / "ids.json")])
+    assert r.exit_code != 0  # the id file has to exist
+    (tmp_path / "ids.json").write_text(json.dumps(["TEST"]))
+    r = run(cli, ["drop-obsolete", "--data-dir", str(out), "--ids-file", str(tmp_path / "ids.json"), "--delete-files"])
+    assert r.exit_code == 0 and "1 obsolete records dropped" in r.output
+    assert load_manifest(str(out / "manifest.json")) == [] and not os.path.exists(out / "structures" / "test.npz")
+
+    # the chemical component cache with automorphisms, and fetch-ccd from a local file
+    (tmp_path / "comp.cif").write_text(_PLM_CIF)
+    r = run(cli, ["fetch-ccd", "--output", str(tmp_path / "ccd"), "--from-file", str(tmp_path / "comp.cif")])
+    assert r.exit_code == 0 and os.path.exists(tmp_path / "ccd" / "comp.cif")
+    r = run(cli, ["build-ccd-cache", "--components-cif", str(tmp_path / "comp.cif"), "--output", str(tmp_path / "ccd.json"),
+                  "--automorphisms"])  # fmt: skip
+    assert r.exit_code == 0, r.output
+    table = json.loads((tmp_path / "ccd.json").read_text())
+    assert set(table) == {"ZZ1", "ZZ2"} and "automorphisms" not in table["ZZ1"]  # C(-O-)(=O)C: the two oxygens differ in bond order
