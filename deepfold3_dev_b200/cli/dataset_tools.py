@@ -368,25 +368,31 @@ def stamp_template_index_space(data_dir, space, workers, dry_run):
 # --------------------------------------------------------------------------------------------------------- packs, kernels
 @click.command("pack")
 @click.argument("src_dir", type=click.Path(exists=True))
-@click.argument("out_dir", type=click.Path())
+@click.argument("out_dir", type=click.Path(), required=False)
 @click.option("--shard-size", type=int, default=1 << 30, show_default=True, help="Bytes per tar shard.")
-def pack(src_dir, out_dir, shard_size):
-    """Bundle a directory of small files into tar shards with an index."""
-    from ..data.pack import build_pack
+@click.option("--include", multiple=True, help="Pack only paths under this prefix, e.g. structures/ (repeatable).")
+def pack(src_dir, out_dir, shard_size, include):
+    """Bundle the files under SRC_DIR (recursively) into tar shards with a sorted index. OUT_DIR defaults to
+    SRC_DIR/_pack, where the datasets find it by themselves; rerun after an interruption to continue."""
+    from ..data.pack import PACK_DIRNAME, build_pack
 
-    click.echo(f"{build_pack(src_dir, out_dir, shard_size)} files -> {out_dir}")
+    out_dir = out_dir or os.path.join(src_dir, PACK_DIRNAME)
+    click.echo(f"{build_pack(src_dir, out_dir, shard_size, include)} files -> {out_dir}")
 
 
 @click.command("pack-verify")
 @click.argument("src_dir", type=click.Path(exists=True))
-@click.argument("pack_dir", type=click.Path(exists=True))
+@click.argument("pack_dir", type=click.Path(exists=True), required=False)
 @click.option("--sample", type=int, default=0, help="Check only this many files (0 = all).")
-def pack_verify(src_dir, pack_dir, sample):
-    """Compare every file of SRC_DIR byte for byte with what the pack returns for its name."""
-    from ..data.pack import Pack
+@click.option("--checksums", is_flag=True, help="Also re-hash every shard against SHA256SUMS.")
+def pack_verify(src_dir, pack_dir, sample, checksums):
+    """Compare the files under SRC_DIR byte for byte with what the pack returns for their paths."""
+    from ..data.pack import PACK_DIRNAME, Pack, _sha256, _walk
 
+    pack_dir = pack_dir or os.path.join(src_dir, PACK_DIRNAME)
     pk = Pack(pack_dir)
-    names = sorted(n for n in os.listdir(src_dir) if os.path.isfile(os.path.join(src_dir, n)))
+    names = _walk(src_dir, pk.include)
+    total = len(names)
     if sample:
         names = names[:: max(1, len(names) // sample)][:sample]
     bad = []
@@ -397,6 +403,14 @@ def pack_verify(src_dir, pack_dir, sample):
     pk.close()
     if bad:
         raise click.ClickException(f"{len(bad)} of {len(names)} files differ or are missing, first: {bad[:5]}")
+    if not pk.legacy and not sample and len(pk) != total:
+        raise click.ClickException(f"the pack holds {len(pk)} files, the source {total}")
+    if checksums and os.path.exists(os.path.join(pack_dir, "SHA256SUMS")):
+        with open(os.path.join(pack_dir, "SHA256SUMS")) as f:
+            for line in f:
+                digest, rel = line.split()
+                if _sha256(os.path.join(pack_dir, rel)) != digest:
+                    raise click.ClickException(f"{rel}: checksum mismatch")
     click.echo(f"{len(names)} files verified")
 
 

@@ -38,52 +38,13 @@ def cli():
 
 
 # ------------------------------------------------------------------------------------------------ train
-@cli.command()
-@click.option("--data-dir", type=click.Path(), default=None, help="Directory of featurised examples (one dataset).")
-@click.option("--output", type=click.Path(), required=True)
-@click.option("--params", type=click.Path(), default=None, help="Initial weights (.safetensors / .pt).")
-@click.option("--resume", default=None, help="Checkpoint path, or 'auto' for the latest in --output.")
-@click.option("--config", "configs", multiple=True, type=click.Path(exists=True))
-@click.option("--lr", type=float, default=None)
-@click.option("--max-steps", type=int, default=None)
-@click.option("--max-tokens", type=int, default=None)
-@click.option("--grad-accum", type=int, default=None)
-@click.option("--seed", type=int, default=None)
-@click.option("--deterministic", is_flag=True)
-@click.option("--dtype", type=click.Choice(list(DTYPES)), default=None)
-@click.option("--wandb", "wandb_project", default=None)
-@click.option("--wandb-entity", default=None)
-@click.option("--override", "overrides", multiple=True, help="key=value on the training or model config.")
-@click.option("--dataset", "datasets", multiple=True, help="name:path[:weight[:strategy[:distill]]] (repeatable).")
-@click.option("--synthetic", is_flag=True, help="Train on generated examples of the configured crop size.")
-@click.option("--num-workers", type=int, default=None, help="Background data threads (default: training.num_workers).")
-def train(data_dir, output, params, resume, configs, lr, max_steps, max_tokens, grad_accum, seed, deterministic, dtype,
-          wandb_project, wandb_entity, overrides, datasets, synthetic, num_workers):  # fmt: skip
-    """Train the model (one process per GPU; launch with torch.distributed.run for several)."""
-    _setup_logging()
-    import faulthandler
-    import signal
-
-    faulthandler.enable()  # a fatal signal prints every thread's Python stack
-    if hasattr(signal, "SIGUSR1"):
-        faulthandler.register(signal.SIGUSR1, all_threads=True)  # `kill -USR1 <pid>`: where is this rank right now?
-    from ..config.loader import build_configs
+def build_training_stream(tc, mc, info, datasets, data_dir=None, synthetic=False, num_workers=None):
+    """``(stream, sampler)`` for the training loop: the datasets named on the command line (or in the config's mixture),
+    weighted cluster sampling per dataset, a weighted mixture over datasets, token-budget batching and a prefetch thread.
+    Shared by ``train`` and by the input-pipeline check of the cluster recipes."""
     from ..data import datasets as ds
     from ..data.samplers import MultiDatasetSampler, WeightedClusterSampler
-    from ..parallel.dist import init_process_group
-    from ..training.tracking import build_trackers
-    from ..training.trainer import Trainer, _plain
 
-    tc, mc = build_configs(list(configs), list(overrides))
-    tc.output_dir = output
-    for key, val in (("lr", lr), ("max_steps", max_steps), ("max_tokens", max_tokens), ("accumulate_grad_batches", grad_accum),
-                     ("seed", seed), ("dtype", dtype), ("params_path", params)):  # fmt: skip
-        if val is not None:
-            setattr(tc, key, val)
-    if deterministic:
-        tc.deterministic = True
-        apply_det_recipe()
-    info = init_process_group(tc.collective_timeout_s)
     specs = list(datasets) or ([f"data:{data_dir}"] if data_dir else [])
     extra = {}  # per-dataset settings that only the config file carries (date cut-off, crop weights)
     if not specs and not synthetic:
@@ -126,6 +87,54 @@ def train(data_dir, output, params, resume, configs, lr, max_steps, max_tokens, 
     if workers > 0 and not synthetic:
         base = stream
         stream = ds.PrefetchStream(lambda w: base, depth=max(2, getattr(tc, "prefetch_factor", 2) * workers), workers=1)
+    return stream, sampler
+
+
+@cli.command()
+@click.option("--data-dir", type=click.Path(), default=None, help="Directory of featurised examples (one dataset).")
+@click.option("--output", type=click.Path(), required=True)
+@click.option("--params", type=click.Path(), default=None, help="Initial weights (.safetensors / .pt).")
+@click.option("--resume", default=None, help="Checkpoint path, or 'auto' for the latest in --output.")
+@click.option("--config", "configs", multiple=True, type=click.Path(exists=True))
+@click.option("--lr", type=float, default=None)
+@click.option("--max-steps", type=int, default=None)
+@click.option("--max-tokens", type=int, default=None)
+@click.option("--grad-accum", type=int, default=None)
+@click.option("--seed", type=int, default=None)
+@click.option("--deterministic", is_flag=True)
+@click.option("--dtype", type=click.Choice(list(DTYPES)), default=None)
+@click.option("--wandb", "wandb_project", default=None)
+@click.option("--wandb-entity", default=None)
+@click.option("--override", "overrides", multiple=True, help="key=value on the training or model config.")
+@click.option("--dataset", "datasets", multiple=True, help="name:path[:weight[:strategy[:distill]]] (repeatable).")
+@click.option("--synthetic", is_flag=True, help="Train on generated examples of the configured crop size.")
+@click.option("--num-workers", type=int, default=None, help="Background data threads (default: training.num_workers).")
+def train(data_dir, output, params, resume, configs, lr, max_steps, max_tokens, grad_accum, seed, deterministic, dtype,
+          wandb_project, wandb_entity, overrides, datasets, synthetic, num_workers):  # fmt: skip
+    """Train the model (one process per GPU; launch with torch.distributed.run for several)."""
+    _setup_logging()
+    import faulthandler
+    import signal
+
+    faulthandler.enable()  # a fatal signal prints every thread's Python stack
+    if hasattr(signal, "SIGUSR1"):
+        faulthandler.register(signal.SIGUSR1, all_threads=True)  # `kill -USR1 <pid>`: where is this rank right now?
+    from ..config.loader import build_configs
+    from ..parallel.dist import init_process_group
+    from ..training.tracking import build_trackers
+    from ..training.trainer import Trainer, _plain
+
+    tc, mc = build_configs(list(configs), list(overrides))
+    tc.output_dir = output
+    for key, val in (("lr", lr), ("max_steps", max_steps), ("max_tokens", max_tokens), ("accumulate_grad_batches", grad_accum),
+                     ("seed", seed), ("dtype", dtype), ("params_path", params)):  # fmt: skip
+        if val is not None:
+            setattr(tc, key, val)
+    if deterministic:
+        tc.deterministic = True
+        apply_det_recipe()
+    info = init_process_group(tc.collective_timeout_s)
+    stream, sampler = build_training_stream(tc, mc, info, list(datasets), data_dir, synthetic, num_workers)
     trackers = build_trackers(output, info.is_main, wandb_project, wandb_entity, {"training": _plain(tc), "model": _plain(mc)})
     trainer = Trainer(tc, mc, train_loader=stream, sampler=sampler if hasattr(sampler, "state_dict") else None,
                       dist_info=info, trackers=trackers)  # fmt: skip

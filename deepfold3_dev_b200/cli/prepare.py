@@ -178,7 +178,7 @@ def pack(src_dir, out_dir, shard_size):
 
     units = {"K": 1 << 10, "M": 1 << 20, "G": 1 << 30}
     size = int(float(shard_size[:-1]) * units[shard_size[-1].upper()]) if shard_size[-1].upper() in units else int(shard_size)
-    click.echo(f"{build_pack(src_dir, out_dir, size)} shards -> {out_dir}")
+    click.echo(f"{build_pack(src_dir, out_dir, size)} files -> {out_dir}")
 
 
 @prepare.command("masks")

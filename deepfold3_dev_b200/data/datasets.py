@@ -15,7 +15,7 @@ import os
 
 import torch
 
-from . import cropper
+from . import cropper, io_cache, pack as packs
 from .synthetic import split_lengths, synthetic_complex
 
 PAD_VALUES = {"msa": 21}
@@ -55,13 +55,17 @@ class FeatureDirDataset:
     def __init__(self, root: str, max_tokens: int = 384, max_atoms: int = 0, crop_weights: dict | None = None,
                  is_distillation: bool = False, seed: int = 0, pack=None):  # fmt: skip
         self.root, self.max_tokens, self.max_atoms = root, max_tokens, max_atoms
-        self.crop_weights, self.is_distillation, self.seed, self.pack = crop_weights, is_distillation, seed, pack
+        self.crop_weights, self.is_distillation, self.seed = crop_weights, is_distillation, seed
+        self.pack = pack if pack is not None else packs.register(root)
         man = os.path.join(root, "manifest.json")
         if os.path.exists(man):
             with open(man) as f:
                 self.records = json.load(f)
         else:
-            self.records = [{"id": n[:-3]} for n in sorted(os.listdir(root)) if n.endswith(".pt")]
+            names = set(n for n in os.listdir(root) if n.endswith(".pt"))
+            if self.pack is not None:
+                names |= {k for k in self.pack.keys() if k.endswith(".pt") and "/" not in k}
+            self.records = [{"id": n[:-3]} for n in sorted(names)]
         self.bad = 0
 
     def __len__(self):
@@ -255,6 +259,9 @@ class StructureDataset:
         self.crop_weights, self.is_distillation, self.seed = crop_weights, is_distillation, seed
         self.max_chains, self.max_msa_rows = max_chains, max_msa_rows
         self.msa_dir = msa_dir or os.path.join(root, "msa")
+        packs.register(root)  # structures/ and msa/ may live in {root}/_pack
+        if msa_dir:
+            packs.register(os.path.dirname(os.path.abspath(msa_dir)))
         self.records = [r for r in load_manifest(os.path.join(root, "manifest.json")) if any(c.valid for c in r.chains)]
         self.records = apply_date_cutoff(self.records, cutoff_date, keep_after)
         self.msa_read = self.msa_skipped = 0  # alignments opened / never opened because their chain was cropped away
@@ -289,9 +296,9 @@ class StructureDataset:
         from .types import MSA
 
         base = os.path.join(self.msa_dir, str(chain.msa_id))
-        if os.path.exists(base + ".npz"):
+        if io_cache.exists(base + ".npz"):
             return MSA.load(base + ".npz")
-        if os.path.exists(base + ".a3m"):
+        if io_cache.exists(base + ".a3m"):
             return msa_from_a3m_file(base + ".a3m", chain.mol_type, self.max_msa_rows)
         return None
 

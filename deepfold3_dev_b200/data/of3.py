@@ -19,7 +19,7 @@ import os
 
 import numpy as np
 
-from . import const, paths
+from . import const, io_cache, paths
 from .io_cache import read_npz
 from .parse.mmcif import _element, find_interfaces, residue_type, sequence_hash
 from .types import ATOM_DTYPE, BOND_DTYPE, CHAIN_DTYPE, RESIDUE_DTYPE, ChainInfo, Record, Structure, StructureInfo, save_manifest
@@ -323,7 +323,10 @@ class OF3StructureDataset:
             self.items = [it for it in self.items if it[0] in allowed]
             idx = np.asarray([self.cache.index_of(pid) for pid, _ in self.items], dtype=np.int64)
             self._weights = self.cache.cluster_weights(idx)
-        if msa_dir is None and os.path.isdir(os.path.join(of3_dir, "msa")):
+        from . import pack as packs
+
+        packs.register(of3_dir)  # alignments may live in {of3_dir}/_pack
+        if msa_dir is None and io_cache.exists(os.path.join(of3_dir, "msa")):
             msa_dir = os.path.join(of3_dir, "msa")
         self.msa_dir, self.max_tokens, self.max_atoms, self.max_msa_rows, self.seed = msa_dir, max_tokens, max_atoms, max_msa_rows, seed
         self.crop_weights, self.is_distillation = crop_weights, is_distillation
@@ -361,8 +364,8 @@ class OF3StructureDataset:
         if not self.msa_dir:
             return None
         base = os.path.join(self.msa_dir, str(chain.msa_id))
-        if os.path.exists(base + ".npz"):
+        if io_cache.exists(base + ".npz"):
             return MSA.load(base + ".npz")
-        if os.path.exists(base + ".a3m"):
+        if io_cache.exists(base + ".a3m"):
             return msa_from_a3m_file(base + ".a3m", chain.mol_type, self.max_msa_rows)
         return None

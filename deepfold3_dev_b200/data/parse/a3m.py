@@ -92,7 +92,8 @@ def msa_from_a3m_file(path: str, mol_type: int, max_rows: int | None = None):
     """A3M file -> the array form stored next to prepared structures (``data.types.MSA``: int8 rows, mask, deletions)."""
     from ..types import MSA as ArrayMSA
 
-    with open(path) as f:
-        m = parse_a3m(f.read(), max_rows=max_rows)
+    from ..io_cache import read_text
+
+    m = parse_a3m(read_text(path), max_rows=max_rows)
     rows = np.stack([encode_sequence(s, mol_type) for s in m.sequences]).astype(np.int8)
     return ArrayMSA(rows, rows != const.MSA_GAP, np.clip(m.deletions, 0, 127).astype(np.int8))

@@ -31,7 +31,7 @@ import torch
 import torch.distributed as dist
 
 from .. import ops
-from .dist import DistInfo
+from .dist import DistInfo, on_one_node
 
 
 class AxialComm:
@@ -40,7 +40,9 @@ class AxialComm:
 
     def __init__(self, info: DistInfo, transport: str | None = None):
         self.info = info
-        default = "peer" if (info.is_distributed and info.backend == "nccl") else "collective"
+        default = "collective"
+        if info.is_distributed and info.backend == "nccl" and transport is None and "DF3_AXIAL_COMM" not in os.environ:
+            default = "peer" if on_one_node(info) else "collective"  # peer mappings exist only inside one host
         self.transport = transport or os.environ.get("DF3_AXIAL_COMM", default)
         if self.transport not in ("peer", "collective"):
             raise ValueError(f"axial transport must be peer|collective, got {self.transport!r}")

@@ -65,6 +65,26 @@ def init_process_group(timeout_s: float = 600.0, device: str | None = None) -> D
     return DistInfo(rank, local, world, dev, backend)
 
 
+_ONE_NODE: dict[int, bool] = {}
+
+
+def on_one_node(info: DistInfo) -> bool:
+    """True when every rank of the job runs on the same host (a collective call on first use; cached afterwards).
+
+    CUDA-IPC peer mappings exist only between the GPUs of one host, so the peer-memory transports are the default only
+    when this holds; a job that spans hosts reduces gradients through NCCL instead.
+    """
+    if not info.is_distributed:
+        return True
+    if info.world_size not in _ONE_NODE:
+        import socket
+
+        names: list = [None] * info.world_size
+        dist.all_gather_object(names, socket.gethostname())
+        _ONE_NODE[info.world_size] = len(set(names)) == 1
+    return _ONE_NODE[info.world_size]
+
+
 def destroy_process_group_safely(info: DistInfo) -> None:
     if info.is_distributed and dist.is_initialized():
         try:

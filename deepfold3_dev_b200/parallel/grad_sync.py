@@ -24,14 +24,16 @@ import os
 import torch
 import torch.distributed as dist
 
-from .dist import DistInfo
+from .dist import DistInfo, on_one_node
 
 
 class GradSync:
     def __init__(self, info: DistInfo, transport: str | None = None):
         self.info = info
-        # NCCL ranks on one node default to the peer-memory kernel; everything else to the collective
-        default = "peer" if (info.is_distributed and info.backend == "nccl") else "collective"
+        # NCCL ranks on one node default to the peer-memory kernel; everything else (CPU, several hosts) to the collective
+        default = "collective"
+        if info.is_distributed and info.backend == "nccl" and transport is None and "DF3_COMM" not in os.environ:
+            default = "peer" if on_one_node(info) else "collective"
         self.explicit = transport is not None or "DF3_COMM" in os.environ
         self.transport = transport or os.environ.get("DF3_COMM", default)
         self._peer = None

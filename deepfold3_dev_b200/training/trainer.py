@@ -189,6 +189,8 @@ class Trainer:
             skip_scheduler=cfg.skip_load_scheduler and not own_run,
             skip_step=cfg.skip_load_step and not own_run,
         )  # fmt: skip
+        if self.dist.is_main:
+            logger.info("resumed from %s at step %d", path, self.state.effective_step)
         # the YAML learning rate wins over the checkpoint's
         self.scheduler.base_lrs = [cfg.lr for _ in self.scheduler.base_lrs]
         self.scheduler._apply()
@@ -315,6 +317,8 @@ class Trainer:
             # resumed run starts on a full window (reference: training/trainer.py:1322-1345)
             self.optimizer.zero_grad()
             st.global_step -= st.global_step % acc
+        if stopped and self.dist.is_main:
+            logger.info("stop requested: writing checkpoint at step %d and leaving", st.effective_step)
         self.save_checkpoint("checkpoint_final.pt" if not stopped else None, background=False)
         self.ckpt.wait_for_io()
         self.ckpt.close()

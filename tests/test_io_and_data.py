@@ -142,10 +142,67 @@ def test_sampler_resume_sharding_collate_pack(tmp_path):
     assert pack.build_pack(str(src), str(tmp_path / "pk")) == 3
     pk = pack.Pack(str(tmp_path / "pk"))
     assert pk.exists("ex2.pt") and not pk.exists("nope") and pk.read_bytes("ex1.pt") == (src / "ex1.pt").read_bytes()
+    assert sorted(os.listdir(tmp_path / "pk")) == ["SHA256SUMS", "_build", "keys.npy", "loc.npy", "meta.json", "shards"]
     ds = datasets.FeatureDirDataset(str(src), max_tokens=48, pack=pk)
     batch = next(datasets.BatchStream(ds, samplers.WeightedClusterSampler(ds.weights(), seed=1), batch_size=2, pad_tokens_to=64))
     assert batch["res_type"].shape == (2, 64) and batch["msa"].shape == (2, 4, 64) and batch["seq_mask"].sum(-1).tolist() == [48, 48]
     assert (batch["msa"][:, :, 48:] == 21).all() and len(batch["_record_id"]) == 2
+
+
+def test_pack_is_transparent_to_loaders(tmp_path):
+    """A dataset root whose bulky subtrees were moved into ``_pack`` reads like the unpacked tree: nested keys, several
+    shards, authoritative misses, pass-through for files left outside, resumable build, the earlier index layout."""
+    import json
+    import shutil
+
+    import numpy as np
+
+    from deepfold3_dev_b200.data import io_cache
+    from deepfold3_dev_b200.data.parse.a3m import msa_from_a3m_file
+
+    root = tmp_path / "root"
+    (root / "structures" / "ab").mkdir(parents=True)
+    (root / "msa").mkdir()
+    rng = np.random.default_rng(0)
+    for i in range(5):
+        np.savez(root / "structures" / "ab" / f"{i}.npz", x=rng.normal(size=(50 + i, 3)))
+    (root / "msa" / "q.a3m").write_text(">q\nACDE\n>h\nAC-E\n")
+    (root / "manifest.json").write_text("[]")
+    try:
+        n = pack.build_pack(str(root), str(root / "_pack"), shard_bytes=3000, include=("structures/", "msa/"))
+        assert n == 6 and len(os.listdir(root / "_pack" / "shards")) >= 2
+        meta = json.loads((root / "_pack" / "meta.json").read_text())
+        assert meta["format"] == "deepfold3-pack" and meta["files"] == 6 and meta["include"] == ["structures/", "msa/"]
+        want = {i: io_cache.read_npz(str(root / "structures" / "ab" / f"{i}.npz"))["x"] for i in range(5)}
+        shutil.rmtree(root / "structures")
+        shutil.rmtree(root / "msa")
+        assert pack.register(str(root)) is not None
+        for i in range(5):
+            assert (io_cache.read_npz(str(root / "structures" / "ab" / f"{i}.npz"))["x"] == want[i]).all()
+        assert msa_from_a3m_file(str(root / "msa" / "q.a3m"), 0).sequences.shape == (2, 4)
+        assert io_cache.exists(str(root / "structures" / "ab" / "3.npz")) and io_cache.exists(str(root / "msa"))
+        assert not io_cache.exists(str(root / "structures" / "ab" / "9.npz"))
+        assert pack.lookup(str(root / "structures" / "zz.npz"))[2] == "miss" and pack.lookup(str(root / "manifest.json"))[2] == "pass"
+        assert io_cache.exists(str(root / "manifest.json"))
+        with pytest.raises(FileNotFoundError):
+            io_cache.read_bytes(str(root / "structures" / "ab" / "9.npz"))
+        # a rerun after the sources are gone keeps what the state file lists; new files go into further shards
+        (root / "msa").mkdir()
+        (root / "msa" / "r.a3m").write_text(">r\nAC\n")
+        assert pack.build_pack(str(root), str(root / "_pack"), shard_bytes=3000, include=("structures/", "msa/")) == 7
+        # the index layout of earlier versions of this package is still read
+        old = tmp_path / "old"
+        old.mkdir()
+        import tarfile
+
+        with tarfile.open(old / "shard-00000.tar", "w") as tar:
+            info = tar.gettarinfo(str(root / "manifest.json"), arcname="m.json")
+            with open(root / "manifest.json", "rb") as f:
+                tar.addfile(info, f)
+            (old / "index.json").write_text(json.dumps({"m.json": [0, tar.offset - 512, 2]}))
+        assert pack.Pack(str(old)).read_bytes("m.json") == b"[]"
+    finally:
+        pack.unregister_all()
 
 
 def test_bucket_pad_unpad_preserves_prediction():

@@ -1,6 +1,7 @@
 """Collapse-free softmax family and the single-track probe."""
 
 import json
+import os
 
 import torch
 import torch.nn.functional as F
@@ -94,3 +95,60 @@ def test_checkpoint_report_and_run_status(tmp_path):
     st = run_status(str(tmp_path / "run"))
     assert st["rows"] == 10 and st["last_step"] == 9 and abs(st["steps_per_hour"] - 1800.0) < 1e-6
     assert st["loss_recent_mean"] < st["loss_earlier_mean"] and st["non_finite_losses"] == 0
+
+
+def test_deploy_recipes_render_and_parse(tmp_path):
+    """The cluster recipes: shell files parse, manifests are valid YAML, the multi-node template renders with no token
+    left, the RDMA address map resolves an address against a stand-in for kubectl, and the collective check runs on gloo."""
+    import json
+    import subprocess
+    import sys
+
+    import yaml
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    dep = os.path.join(root, "deploy")
+    shells = [os.path.join(d, f) for d, _, fs in os.walk(dep) for f in fs if f.endswith((".sh", ".sbatch"))]
+    assert len(shells) >= 12
+    for path in shells:
+        assert subprocess.run(["bash", "-n", path], capture_output=True).returncode == 0, path
+    for name in ("trainjob.yaml", "comm-check.yaml", "plm-job.yaml"):
+        with open(os.path.join(dep, "k8s", name)) as f:
+            assert all(d["kind"] in ("PyTorchJob", "Job") for d in yaml.safe_load_all(f))
+    env = dict(os.environ, DRY_RUN="1", NODES="4", EXCLUDE_HOSTS="host-a,host-b", IB_HCA="=mlx5_0,mlx5_1", DF3_COMM_LOG="1")
+    out = subprocess.run(["bash", os.path.join(dep, "k8s", "submit.sh"), "My_Run", "--override", "max_steps=5"],
+                         capture_output=True, text=True, env=env)  # fmt: skip
+    assert out.returncode == 0 and "__" not in out.stdout.replace("__main__", ""), out.stderr
+    job = yaml.safe_load(out.stdout)
+    assert job["metadata"]["name"] == "my-run" and job["spec"]["pytorchReplicaSpecs"]["Worker"]["replicas"] == 3
+    pod = job["spec"]["pytorchReplicaSpecs"]["Master"]["template"]
+    terms = pod["spec"]["affinity"]["nodeAffinity"]["requiredDuringSchedulingIgnoredDuringExecution"]["nodeSelectorTerms"]
+    assert terms[0]["matchExpressions"][1]["values"] == ["host-a", "host-b"]
+    script = pod["spec"]["containers"][0]["args"][0]
+    assert "--override max_steps=5" in script and "DF3_NODES=4" in script and "DF3_COMM_LOG=1" in script
+    assert pod["spec"]["containers"][0]["resources"]["limits"] == {"nvidia.com/gpu": 8, "rdma/hca": 8}
+    # env.sh: several nodes -> NCCL gradient transport, RAS and flight recorder on, verbose logging only on request
+    probe = subprocess.run(["bash", "-c", f"DF3_NODES=2 DF3_COMM_LOG=1 source {dep}/env.sh && df3_describe_env"],
+                           capture_output=True, text=True)  # fmt: skip
+    assert "DF3_COMM=collective" in probe.stdout and "NCCL_RAS_ENABLE=1" in probe.stdout and "NCCL_DEBUG=INFO" in probe.stdout
+    quiet = subprocess.run(["bash", "-c", f"unset DF3_COMM; source {dep}/env.sh && df3_describe_env"], capture_output=True, text=True)
+    assert "NCCL_DEBUG=WARN" in quiet.stdout and "DF3_COMM=" not in quiet.stdout
+    # address map against a stand-in for kubectl
+    pods = {"items": [{"metadata": {"name": "my-run-worker-1", "annotations": {"k8s.v1.cni.cncf.io/network-status": json.dumps(
+        [{"name": "k8s", "ips": ["192.168.0.4"], "default": True}, {"name": "rdma-net", "ips": ["10.1.2.3"]}])}},
+        "spec": {"nodeName": "host-q"}, "status": {"phase": "Running"}}]}  # fmt: skip
+    (tmp_path / "pods.json").write_text(json.dumps(pods))
+    fake = tmp_path / "kubectl"
+    fake.write_text(f"#!/bin/bash\ncat {tmp_path}/pods.json\n")
+    fake.chmod(0o755)
+    res = subprocess.run(["bash", os.path.join(dep, "k8s", "rdma_ip_map.sh"), "my-run", "10.1.2.3"], capture_output=True,
+                         text=True, env=dict(os.environ, KUBECTL=str(fake)))  # fmt: skip
+    assert "10.1.2.3: host host-q, pod my-run-worker-1" in res.stdout, res.stdout + res.stderr
+    # collective check on two gloo ranks
+    table = tmp_path / "cc.json"
+    run = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--standalone", "--local-addr", "127.0.0.1",
+                          "--nproc-per-node", "2", os.path.join(dep, "comm_check.py"), "--sizes-mib", "1", "--iters", "2",
+                          "--warmup", "1", "--json", str(table)], capture_output=True, text=True, timeout=300)  # fmt: skip
+    assert run.returncode == 0, run.stderr[-2000:]
+    rows = json.loads(table.read_text())["rows"]
+    assert {r["op"] for r in rows} == {"all_reduce", "all_gather"} and all(r["busbw_gbs"] > 0 for r in rows)
