@@ -82,7 +82,8 @@ class ComplexLMTrainer:
         self.eval_views = build_views(cfg.data, cfg.eval_sources) if cfg.eval_sources else []
         if cfg.train.eval_cluster_disjoint and self.eval_views:
             drop_overlapping_clusters(self.eval_views, self.train_views)
-        self.stream = PackedComplexStream(self.train_views, cfg.data, cfg.data.seed, self.rank)
+        # no sources configured: the caller feeds train_step() with its own batches (benchmarks, tests)
+        self.stream = PackedComplexStream(self.train_views, cfg.data, cfg.data.seed, self.rank) if self.train_views else None
         self.amp = DTYPES[cfg.train.dtype] if self.device.type == "cuda" else torch.float32
         if self.world > 1:  # every rank starts from rank 0's weights
             for p in self.model.parameters():

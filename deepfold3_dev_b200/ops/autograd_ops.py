@@ -658,7 +658,37 @@ def attention_supported(q, k, v, bias) -> bool:
     d = q.shape[-1]
     # the chunked backward (rows beyond the fused kernel's tensor-memory budget) handles keys in pairs
     even = q.shape[-2] % 2 == 0 or not torch.is_grad_enabled() or K.attention_bwd_fused_supported(q.shape[-2], d)
-    return q.is_cuda and q.dim() == 5 and q.dtype == BF16 and k.dtype == BF16 and v.dtype == BF16 and d % 8 == 0 and d <= 64 and even
+    return (q.is_cuda and q.dim() == 5 and q.shape == k.shape and q.dtype == BF16 and k.dtype == BF16 and v.dtype == BF16
+            and d % 8 == 0 and d <= 64 and even)
+
+
+def window_attention_supported(q, k, v, bias) -> bool:
+    """Atom-window attention on the pair-bias attention kernel: ``q`` ``[B, S, W, H, Q, D]``, ``k``/``v``
+    ``[B, S, W, H, K, D]`` in bf16, ``bias`` ``[B, 1, W, H, Q, K]`` (shared by the S samples, key mask folded in).
+    Forward only: with gradients wanted the PyTorch statement runs under autograd."""
+    if torch.is_grad_enabled() and any(t.requires_grad for t in (q, k, v, bias)):
+        return False
+    if not (q.is_cuda and q.dim() == 6 and k.dim() == 6 and bias.dim() == 6 and k.shape == v.shape):
+        return False
+    if not (q.dtype == BF16 and k.dtype == BF16 and v.dtype == BF16 and bias.dtype in (BF16, torch.float32)):
+        return False
+    B, S, W, H, Q, D = q.shape
+    keys = k.shape[-2]
+    return (k.shape[:4] == q.shape[:4] and k.shape[-1] == D and D % 8 == 0 and D <= 64 and keys % 8 == 0
+            and tuple(bias.shape) == (B, 1, W, H, Q, keys))
+
+
+@torch.no_grad()
+def window_attention(q, k, v, bias, scale: float):
+    """One launch per batch element: windows become the kernel's batch axis and samples its row axis, so the bias tile of
+    a window (staged by TMA when bf16) serves all samples (reference: atom_cross_attn.py:764-769, there three library
+    calls over a materialised ``[.., H, Q, K]`` fp32 logit tensor). The 32 queries of a window fill a quarter of the
+    kernel's 128-row tile; the work is bound by launch count and memory traffic, not by the tensor pipe."""
+    outs = []
+    for b in range(q.shape[0]):
+        out, _ = K.attention_fwd(q[b].transpose(0, 1), k[b].transpose(0, 1), v[b].transpose(0, 1), bias[b, 0], None, scale, False)
+        outs.append(out.transpose(0, 1))  # [S, W, H, Q, D] in q's memory order
+    return outs[0].unsqueeze(0) if len(outs) == 1 else torch.stack(outs)
 
 
 class _Attention(torch.autograd.Function):

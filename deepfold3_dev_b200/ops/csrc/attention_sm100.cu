@@ -71,7 +71,8 @@ struct AttnParams {
   long long o_sb, o_sr, o_sh, o_sn;           // out strides (elements)
   long long bias_sb, bias_sh, bias_si;        // bias strides (last axis contiguous)
   long long mask_sb, mask_sr;                 // mask strides (last axis contiguous)
-  int B, R, H, N, D;
+  int B, R, H, N, D;       // N: keys per (b, r, h)
+  int NQ;                  // queries per (b, r, h); equals N for self-attention, 32 against 128 keys for atom windows
   int q_tiles;
   int bias_is_bf16;
   int bias_tma;            // bias tiles are staged through shared memory by TMA (bf16, contiguous keys, N % 8 == 0)
@@ -239,7 +240,7 @@ __global__ void __launch_bounds__(kThreads, 2) attention_fwd_kernel(const __grid
     const int half = (warp - 2) >> 2;
     const int row_in_tile = qd * 32 + lane;
     const int i = qt * BQ + row_in_tile;     // query index
-    const bool row_ok = i < p.N;
+    const bool row_ok = i < p.NQ;
     const uint32_t lane_off = (uint32_t)(qd * 32) << 16;
     const float* mask_row = p.mask ? p.mask + b * p.mask_sb + r * p.mask_sr : nullptr;
     const uint8_t* bias_row = nullptr;
@@ -414,16 +415,16 @@ __global__ void __launch_bounds__(kThreads, 2) attention_fwd_kernel(const __grid
           if (d0 + d < p.D) dst[d] = __float2bfloat16_rn(o_acc[d] * inv);
       }
       if (p.out32) {  // unrounded copy: delta = rowsum(dO o O) of the backward must not see the bf16 rounding of O
-        float* d32 = p.out32 + ((((long long)b * p.R + r) * p.H + h) * p.N + i) * p.D + d0;
+        float* d32 = p.out32 + ((((long long)b * p.R + r) * p.H + h) * p.NQ + i) * p.D + d0;
 #pragma unroll
         for (int d = 0; d < DH; ++d)
           if (d0 + d < p.D) d32[d] = o_acc[d] * inv;
       }
       if (p.lse && half == 0) {
         // kept apart: for a fully masked row the maximum is about -1.4e9, where adding log2(sum) would round away
-        const long long at = (((long long)b * p.R + r) * p.H + h) * p.N + i;
+        const long long at = (((long long)b * p.R + r) * p.H + h) * p.NQ + i;
         p.lse[at] = m_run;
-        p.lse[(long long)p.B * p.R * p.H * p.N + at] = log2f(l_run);
+        p.lse[(long long)p.B * p.R * p.H * p.NQ + at] = log2f(l_run);
       }
     }
   }
@@ -637,10 +638,11 @@ std::tuple<Tensor, Tensor, Tensor, Tensor> df3_attention_bwd(const Tensor& q, co
 std::tuple<Tensor, Tensor, Tensor> attention_fwd_impl(const Tensor& q_in, const Tensor& k_in, const Tensor& v_in,
                                                       const c10::optional<Tensor>& bias_in, const c10::optional<Tensor>& mask_in,
                                                       double scale, bool want_lse, bool want_out32) {
-  TORCH_CHECK(q_in.dim() == 5 && k_in.sizes() == q_in.sizes() && v_in.sizes() == q_in.sizes(), "attention: [B, R, H, N, D] q, k, v");
+  TORCH_CHECK(q_in.dim() == 5 && k_in.dim() == 5 && v_in.sizes() == k_in.sizes(), "attention: [B, R, H, N, D] q, k, v");
+  for (int d : {0, 1, 2, 4}) TORCH_CHECK(q_in.size(d) == k_in.size(d), "attention: q and k differ outside the token axis");
   TORCH_CHECK(q_in.is_cuda() && q_in.scalar_type() == torch::kBFloat16 && k_in.scalar_type() == torch::kBFloat16 &&
               v_in.scalar_type() == torch::kBFloat16, "attention: bf16 CUDA tensors");
-  const int64_t B = q_in.size(0), R = q_in.size(1), H = q_in.size(2), N = q_in.size(3), D = q_in.size(4);
+  const int64_t B = q_in.size(0), R = q_in.size(1), H = q_in.size(2), NQ = q_in.size(3), N = k_in.size(3), D = q_in.size(4);
   TORCH_CHECK(D % 8 == 0 && D <= 64, "attention: head width must be a multiple of 8, at most 64");
   c10::cuda::CUDAGuard guard(q_in.device());
   Tensor q = strides_ok(q_in) ? q_in : q_in.contiguous();
@@ -660,9 +662,9 @@ std::tuple<Tensor, Tensor, Tensor> attention_fwd_impl(const Tensor& q_in, const 
     out = torch::empty(sizes_perm, q.options()).permute(inverse);
     if (out.stride(4) != 1) out = torch::empty(q.sizes(), q.options());
   }
-  Tensor lse = torch::empty({want_lse ? 2 : 0, B, R, H, N}, q.options().dtype(torch::kFloat32));
-  Tensor out32 = want_out32 ? torch::empty({B, R, H, N, D}, q.options().dtype(torch::kFloat32)) : torch::empty({0}, q.options().dtype(torch::kFloat32));
-  if (out.numel() == 0) return {out, lse, out32};
+  Tensor lse = torch::empty({want_lse ? 2 : 0, B, R, H, NQ}, q.options().dtype(torch::kFloat32));
+  Tensor out32 = want_out32 ? torch::empty({B, R, H, NQ, D}, q.options().dtype(torch::kFloat32)) : torch::empty({0}, q.options().dtype(torch::kFloat32));
+  if (out.numel() == 0 || N == 0) return {out.zero_(), lse, out32};
 
   AttnParams p{};
   p.out = reinterpret_cast<__nv_bfloat16*>(out.data_ptr());
@@ -672,8 +674,8 @@ std::tuple<Tensor, Tensor, Tensor> attention_fwd_impl(const Tensor& q_in, const 
   Tensor bias, mask;
   if (bias_in.has_value() && bias_in->defined()) {
     bias = *bias_in;
-    TORCH_CHECK(bias.dim() == 4 && bias.size(1) == H && bias.size(2) == N && bias.size(3) == N &&
-                (bias.size(0) == B || bias.size(0) == 1), "attention: bias [B or 1, H, N, N]");
+    TORCH_CHECK(bias.dim() == 4 && bias.size(1) == H && bias.size(2) == NQ && bias.size(3) == N &&
+                (bias.size(0) == B || bias.size(0) == 1), "attention: bias [B or 1, H, queries, keys]");
     if (bias.scalar_type() != torch::kBFloat16 && bias.scalar_type() != torch::kFloat32) bias = bias.to(torch::kFloat32);
     if (bias.stride(3) != 1) bias = bias.contiguous();
     p.bias = bias.data_ptr();
@@ -693,14 +695,14 @@ std::tuple<Tensor, Tensor, Tensor> attention_fwd_impl(const Tensor& q_in, const 
   }
   Tensor status = status_word(q.device().index());
   p.status = status.data_ptr<int>();
-  p.B = (int)B; p.R = (int)R; p.H = (int)H; p.N = (int)N; p.D = (int)D;
-  p.q_tiles = (int)((N + BQ - 1) / BQ);
+  p.B = (int)B; p.R = (int)R; p.H = (int)H; p.N = (int)N; p.NQ = (int)NQ; p.D = (int)D;
+  p.q_tiles = (int)((NQ + BQ - 1) / BQ);
   p.scale_log2 = (float)scale * kLog2e;
   const CUtensorMap tq = qkv_map(q), tk = qkv_map(k), tv = qkv_map(v);
   CUtensorMap tbias = tq;  // placeholder when the bias is not staged by TMA
   if (p.bias && p.bias_is_bf16 && N % 8 == 0 && bias.stride(3) == 1 && bias.stride(2) % 8 == 0 && bias.stride(1) % 8 == 0 &&
       (bias.size(0) == 1 || bias.stride(0) % 8 == 0) && reinterpret_cast<uintptr_t>(bias.data_ptr()) % 16 == 0) {
-    const int64_t dims[4] = {N, N, H, bias.size(0)};
+    const int64_t dims[4] = {N, NQ, H, bias.size(0)};
     const int64_t strides[4] = {1, bias.stride(2), bias.stride(1), bias.size(0) > 1 ? bias.stride(0) : H * bias.stride(1)};
     const int box[4] = {64, 128, 1, 1};
     tbias = make_map_nd(bias.data_ptr(), 4, dims, strides, box);

@@ -968,5 +968,5 @@ void df3_register_gemm(torch::Library& m) {
 }
 
 const char* df3_gemm_features() {
-  return "gemm,matmul,gated_dual_linear,transition,pair_bias_attention,linear_planes,sigmoid_gate_mul,peer_reduce,peer_exchange";
+  return "gemm,matmul,gated_dual_linear,transition,pair_bias_attention,linear_planes,sigmoid_gate_mul,peer_reduce,peer_exchange,window_attention";
 }

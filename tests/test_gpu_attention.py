@@ -100,3 +100,40 @@ def test_grid_attention_packed_gradients(transpose, monkeypatch):
     assert torch.equal(o1, o2) and torch.allclose(g1, g2, atol=1e-6) and torch.allclose(b1, b2, atol=1e-6)
     for got, want in ((o1, o3), (g1, g3), (b1, b3)):
         assert (got - want).abs().max() <= 0.03 * want.abs().max() + 1e-3
+
+
+@pytest.mark.parametrize("bias_dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("S,W,Q,K,D", [(3, 5, 32, 128, 32), (2, 7, 32, 128, 16), (1, 3, 24, 72, 32), (2, 2, 160, 264, 32)])
+def test_window_attention_matches_reference(df3, bias_dtype, S, W, Q, K, D):
+    """Atom-window attention (few queries against more keys, bias per window shared by the samples, key mask folded
+    into the bias) through ``ops.window_attention`` against the fp32 statement; rows of a fully masked window stay finite."""
+    from deepfold3_dev_b200 import ops
+    from deepfold3_dev_b200.ops import reference as ref
+
+    H, B = 4, 1
+    g = torch.Generator(device="cuda").manual_seed(S * 100 + W)
+    # the model's layout: projections [B, S, W, tokens, H, D] with heads moved in front of tokens as a view
+    q = torch.randn(B, S, W, Q, H, D, device="cuda", generator=g).bfloat16().transpose(-2, -3)
+    k = torch.randn(B, S, W, K, H, D, device="cuda", generator=g).bfloat16().transpose(-2, -3)
+    v = torch.randn(B, S, W, K, H, D, device="cuda", generator=g).bfloat16().transpose(-2, -3)
+    keep = torch.rand(B, 1, W, 1, 1, K, device="cuda", generator=g) > 0.2
+    keep[..., 0] = True
+    keep[:, :, W - 1] = False  # one window without any live key
+    bias = (2 * torch.randn(B, 1, W, H, Q, K, device="cuda", generator=g) + 1e9 * (keep.float() - 1.0)).to(bias_dtype)
+    ops.census(reset=True)
+    with torch.no_grad():
+        out = ops.window_attention(q, k, v, bias, D**-0.5)
+    assert ops.census().get("window_attention:sm100", 0) == 1
+    want = ref.window_attention(q.float(), k.float(), v.float(), bias.float(), D**-0.5)
+    assert out.shape == want.shape and torch.isfinite(out.float()).all()
+    live = slice(0, W - 1)
+    err = (out.float() - want)[:, :, live].abs().max().item()
+    assert err < 0.03, err
+    # a window with every key masked gives the plain mean of v over the keys (all logits equal), like the statement
+    assert (out.float() - want)[:, :, W - 1].abs().max().item() < 0.05
+    # the output's memory order follows q, so the model's reshape to [B, S, W, Q, H * D] is a view
+    assert out.transpose(-2, -3).reshape(B, S, W, Q, H * D).data_ptr() == out.data_ptr()
+    # with gradients wanted the PyTorch statement runs (autograd), not the forward-only kernel
+    ops.census(reset=True)
+    ops.window_attention(q.clone().requires_grad_(True), k, v, bias, D**-0.5)
+    assert ops.census().get("window_attention:torch", 0) == 1
