@@ -111,6 +111,43 @@ def test_pairformer_block_fused_kernels_match_eager_bf16():
     assert torch.ops.df3.gemm_status() == 0
 
 
+@pytest.mark.parametrize("triangle_attention,single_track", [(False, False), (True, True)])
+def test_wide_pair_block_fused_kernels_match_eager_bf16(triangle_attention, single_track):
+    """The production recipe's block shape (pair width 256, 8 pair heads of 32; its stage-0 family also drops the
+    triangle attention layers and the single track): kernels against the eager bf16 statement, forward and gradients."""
+    from deepfold3_dev_b200.models.evoformer import PairFormerBlock
+
+    torch.manual_seed(5)
+    block = PairFormerBlock(256, 384, num_pair_heads=8, pair_dropout=0.0, use_triangle_attention=triangle_attention,
+                            use_single_track=single_track).cuda().train()  # fmt: skip
+    wake_zero_init(block)
+    N = 72
+    z = torch.randn(1, N, N, 256, device="cuda")
+    s = torch.randn(1, N, 384, device="cuda")
+    mask = torch.ones(1, N, N, device="cuda")
+    mask[:, :, -3:] = 0
+    mask[:, -3:, :] = 0
+    fused_names = "gated_dual_linear,transition,pair_bias_attention,linear_planes,sigmoid_gate_mul,gemm"
+    ops.census(reset=True)
+    zo_f, dz_f, g_f = _block_grads(block, z, s, mask, "")
+    seen = ops.census()
+    assert any(k.startswith("triangle") and k.endswith(":sm100") and n > 0 for k, n in seen.items()), seen
+    assert not any(k.startswith("triangle") and k.endswith(":torch") and n > 0 for k, n in seen.items()), seen
+    assert (seen.get("pair_bias_attention:sm100", 0) > 0) == (triangle_attention or single_track)
+    zo_e, dz_e, g_e = _block_grads(block, z, s, mask, fused_names)
+
+    def rel(a, b):
+        return ((a - b).norm() / (b.norm() + 1e-12)).item()
+
+    assert rel(zo_f - z, zo_e - z) < 3e-2
+    assert rel(dz_f, dz_e) < 5e-2
+    top = max(g.float().norm().item() for g in g_e.values())
+    for n in g_e:
+        diff = (g_f[n].float() - g_e[n].float()).norm().item()
+        assert diff <= 8e-2 * g_e[n].float().norm().item() + 2e-3 * top, (n, diff, g_e[n].float().norm().item())
+    assert torch.ops.df3.gemm_status() == 0
+
+
 def test_graphed_sampler_equals_eager_sampler(monkeypatch):
     """The CUDA-graph replay of the denoiser gives the sampler's eager result, also on a second (cached) call."""
     torch.manual_seed(1)

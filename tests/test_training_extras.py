@@ -152,3 +152,41 @@ def test_deploy_recipes_render_and_parse(tmp_path):
     assert run.returncode == 0, run.stderr[-2000:]
     rows = json.loads(table.read_text())["rows"]
     assert {r["op"] for r in rows} == {"all_reduce", "all_gather"} and all(r["busbw_gbs"] > 0 for r in rows)
+
+
+def test_every_shipped_config_loads():
+    """Each file under configs/ builds: the structure-model recipes (initial, stages 0-4, fine-tuning) through the
+    config loader with their `base:` chains, the language-model ones through theirs; the stage-0 family is the wide-pair
+    variant without triangle attention and without the Pairformer single track."""
+    import glob
+
+    import torch
+
+    from deepfold3_dev_b200.complexlm.config import load_experiment
+    from deepfold3_dev_b200.complexlm.model import ComplexLM
+    from deepfold3_dev_b200.config.loader import build_configs
+    from deepfold3_dev_b200.models.model import DeepFold3
+
+    root = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "configs")
+    files = sorted(glob.glob(os.path.join(root, "*.yaml")))
+    assert len(files) >= 16
+    sizes = {}
+    for path in files:
+        name = os.path.basename(path)[:-5]
+        if name.startswith("plm-"):
+            cfg = load_experiment(path)
+            with torch.device("meta"):
+                sizes[name] = sum(p.numel() for p in ComplexLM(cfg.model).parameters())
+        else:
+            tc, mc = build_configs([path], [])
+            assert tc.max_tokens >= 64 and mc.pairformer.num_layer >= 1, name
+            if name.startswith("stage"):
+                assert mc.pairformer.pair_channel == 256 and not mc.pairformer.use_single_track
+                assert not mc.evoformer.use_triangle_attention and mc.diffusion.conditioning_pair_channel == 256
+    assert sizes["plm-8m"] < sizes["plm-35m"] < sizes["plm-150m"] < sizes["plm-base"] and 6.5e8 < sizes["plm-base"] < 7e8
+    tc, mc = build_configs([os.path.join(root, "stage4.yaml")], [])
+    assert (tc.max_tokens, tc.max_atoms, mc.data.max_chains) == (768, 10368, 50) and tc.extra_datasets[0].format == "of3pdb"
+    with torch.device("meta"):
+        wide = DeepFold3(mc)
+    names = dict(wide.named_parameters())
+    assert not any(".pairformer." in n and "single_attn" in n for n in names)
