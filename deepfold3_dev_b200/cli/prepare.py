@@ -335,6 +335,82 @@ def evaluate(predicted, experimental, assembly):
     click.echo(json.dumps(compare_files(predicted, experimental, assembly), indent=1))
 
 
+@click.group("eval-sweep")
+def eval_sweep():
+    """Fold a benchmark set with checkpoints of a run, score it against experimental structures, follow the trajectory."""
+
+
+def _sweep_targets(inputs, truth, category, max_tokens):
+    from ..evaluation.sweep import discover_targets
+
+    targets = discover_targets(inputs, truth, set(category) or None, max_tokens)
+    if not targets:
+        raise click.ClickException(f"no job under {inputs}/<category>/*.json")
+    return targets
+
+
+@eval_sweep.command("run")
+@click.option("--inputs", type=click.Path(exists=True), required=True, help="inputs/<category>/<name>.json")
+@click.option("--run-dir", type=click.Path(), required=True)
+@click.option("--ckpt-dir", type=click.Path(exists=True), default=None, help="step_<N>.safetensors / checkpoint_<N>.pt")
+@click.option("--steps", default="0", help="Comma list of checkpoint steps, newest first is usual; 0 with no --ckpt-dir: random weights.")
+@click.option("--category", multiple=True)
+@click.option("--max-tokens", type=int, default=1024, show_default=True)
+@click.option("--gpus", default=None, help="Comma list of device indices (default: all visible).")
+@click.option("--seed", "seeds", default="42,43,44,45", show_default=True)
+@click.option("--num-samples", type=int, default=5, show_default=True)
+@click.option("--dry-run", is_flag=True, help="Print the per-GPU commands only.")
+@click.argument("extra", nargs=-1)
+def eval_sweep_run(inputs, run_dir, ckpt_dir, steps, category, max_tokens, gpus, seeds, num_samples, dry_run, extra):
+    """One prediction process per GPU over a length-balanced share of the targets; a re-run fills the gaps. Arguments
+    after `--` go to `inference-batch` unchanged."""
+    from ..evaluation.sweep import resolve_checkpoint, run_sweep
+
+    targets = _sweep_targets(inputs, None, category, max_tokens)
+    if gpus is None:
+        import torch
+
+        gpus = ",".join(str(i) for i in range(max(1, torch.cuda.device_count())))
+    failed = 0
+    for step in (int(s) for s in steps.split(",")):
+        params = resolve_checkpoint(ckpt_dir, step) if ckpt_dir else None
+        if ckpt_dir and params is None:
+            click.echo(f"step {step}: no checkpoint in {ckpt_dir}, skipped")
+            continue
+        click.echo(f"step {step}: {len(targets)} target(s), weights {params or 'random'}")
+        failed += run_sweep(targets, os.path.join(run_dir, "pred", f"step_{step}"), params, [int(g) for g in gpus.split(",")],
+                            [int(s) for s in seeds.split(",")], num_samples, list(extra), dry_run, click.echo)  # fmt: skip
+    if failed:
+        raise click.ClickException(f"{failed} prediction process(es) failed; see _gpu*.log under the pred directories")
+
+
+@eval_sweep.command("score")
+@click.option("--inputs", type=click.Path(exists=True), required=True)
+@click.option("--truth", type=click.Path(exists=True), required=True, help="Directory of experimental mmCIF files named like the jobs.")
+@click.option("--run-dir", type=click.Path(exists=True), required=True)
+@click.option("--steps", default=None, help="Comma list (default: every pred/step_* present).")
+@click.option("--category", multiple=True)
+@click.option("--max-tokens", type=int, default=1024, show_default=True)
+@click.option("--assembly", is_flag=True)
+def eval_sweep_score(inputs, truth, run_dir, steps, category, max_tokens, assembly):
+    """Score every predicted structure, then write per-step summaries and the trajectory over steps."""
+    import glob as _glob
+
+    from ..evaluation.sweep import score_step, summarize, trajectory
+
+    targets = _sweep_targets(inputs, truth, category, max_tokens)
+    found = sorted(int(os.path.basename(d)[5:]) for d in _glob.glob(os.path.join(run_dir, "pred", "step_*")))
+    for step in ([int(s) for s in steps.split(",")] if steps else found):
+        out = os.path.join(run_dir, "eval", f"step_{step}")
+        rows = score_step(os.path.join(run_dir, "pred", f"step_{step}"), targets, os.path.join(out, "scores.csv"), assembly, click.echo)
+        for row in summarize(rows, os.path.join(out, "summary.csv")):
+            if row["fold_class"] == "all":
+                click.echo(f"step {step} {row['category']}: {row['targets']} targets, lDDT mean {row['lddt_mean']:.3f} "
+                           f"oracle {row['lddt_oracle']:.3f}, TM mean {row['tm_score_mean']:.3f} oracle {row['tm_score_oracle']:.3f}")  # fmt: skip
+    traj = trajectory(run_dir, os.path.join(run_dir, "trajectory.csv"))
+    click.echo(f"{len(traj)} trajectory row(s) -> {os.path.join(run_dir, 'trajectory.csv')}")
+
+
 @click.command("prepare-templates")
 @click.option("--m8", "m8_path", type=click.Path(exists=True), required=True, help="Template search hits (mmseqs .m8 with CIGAR).")
 @click.option("--pdb-mmcif-dir", type=click.Path(exists=True), required=True)
@@ -382,6 +458,6 @@ def run_status_cmd(run_dir):
 
 
 def register(cli) -> None:
-    for cmd in (prepare, scan_mmcif, inspect_example, plm_prepare, plm_train, evaluate, prepare_templates, build_pdb_cache, inspect_checkpoint, run_status_cmd):
+    for cmd in (prepare, scan_mmcif, inspect_example, plm_prepare, plm_train, evaluate, eval_sweep, prepare_templates, build_pdb_cache, inspect_checkpoint, run_status_cmd):
         cli.add_command(cmd)
 

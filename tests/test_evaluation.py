@@ -81,3 +81,84 @@ def test_homologous_constructs_match_through_alignment():
         pytest.skip("reference example files not available")
     out = compare_files(a, b)  # two crystal forms of one protein whose constructs differ at the termini
     assert out["matched_chains"] >= 1 and out["tm_score"] > 0.9 and out["lddt"] > 0.8 and out["matched_atoms"] > 900
+
+
+def test_accuracy_sweep_plan_score_and_trajectory(tmp_path):
+    """The sweep harness on fabricated predictions: balanced shards, per-GPU command lines, scores per structure,
+    mean / oracle / top-ranked per target, category rows, trajectory over two checkpoint steps, fold classes."""
+    import csv
+    import json
+
+    from click.testing import CliRunner
+    from test_prepare import _mini_cif
+
+    from deepfold3_dev_b200.cli.main import cli
+    from deepfold3_dev_b200.evaluation import sweep
+
+    inputs, truth, run = tmp_path / "inputs", tmp_path / "truth", tmp_path / "run"
+    lengths = {"t1": 900, "t2": 300, "t3": 250, "t4": 200, "t5": 120}
+    for cat, names in (("monomer_protein", ["t1", "t2", "t3"]), ("interface_protein_protein", ["t4", "t5"])):
+        (inputs / cat).mkdir(parents=True)
+        for n in names:
+            (inputs / cat / f"{n}.json").write_text(json.dumps({"name": n, "sequences": [{"protein": {"id": ["A"], "sequence": "G" * lengths[n]}}]}))
+    truth.mkdir()
+    for n in lengths:
+        (truth / f"{n}.cif").write_text(_mini_cif())
+    targets = sweep.discover_targets(str(inputs), str(truth), max_tokens=1024)
+    assert [t.tokens for t in targets if t.name == "t1"] == [900] and all(t.truth for t in targets) and len(targets) == 5
+    assert len(sweep.discover_targets(str(inputs), str(truth), max_tokens=280)) == 3
+    shards = sweep.plan_shards(targets, 2)
+    assert [t.name for t in shards[0]] == ["t1"] and sorted(t.name for t in shards[1]) == ["t2", "t3", "t4", "t5"]
+    jobs = sweep.sweep_commands(targets, str(run / "pred" / "step_10"), "w.safetensors", [0, 3], [42, 43], num_samples=2, extra=["--num-recycles", "3"])
+    assert [env["CUDA_VISIBLE_DEVICES"] for env, _ in jobs] == ["0", "3"] and jobs[0][0]["OMP_NUM_THREADS"] == "8"
+    argv = jobs[1][1][0][2]
+    assert argv[argv.index("--seed") + 1] == "42" and "--skip-existing" in argv and argv[-2:] == ["--num-recycles", "3"]
+    assert len(jobs[1][1]) == 4  # two categories x two seeds on the second GPU
+    r = CliRunner().invoke(cli, ["eval-sweep", "run", "--inputs", str(inputs), "--run-dir", str(run), "--gpus", "0,1", "--dry-run",
+                                 "--seed", "7", "--", "--num-recycles", "2"])  # fmt: skip
+    assert r.exit_code == 0 and "inference-batch" in r.output and "--num-recycles 2" in r.output, r.output
+
+    # fabricated predictions: step 10 is worse (one sample displaced per residue), step 20 is exact
+    for step, noise in ((10, 3.0), (20, 0.0)):
+        for t in targets:
+            tdir = run / "pred" / f"step_{step}" / t.category / t.name
+            for sample in (0, 1):
+                d = tdir / f"seed-42_sample-{sample}"
+                d.mkdir(parents=True)
+                text = _mini_cif(shift=(1.0, 2.0, 3.0))
+                if noise and sample == 1:  # stretch the chain: x grows with the atom index
+                    out = []
+                    for line in text.splitlines():
+                        f = line.split()
+                        if f and f[0] == "ATOM" and len(f) > 11:
+                            f[9] = f"{float(f[9]) * (1.0 + noise):.3f}"
+                            line = " ".join(f)
+                        out.append(line)
+                    text = "\n".join(out) + "\n"
+                (d / "model.cif").write_text(text)
+            with open(tdir / "ranking_scores.csv", "w") as f:
+                f.write("seed,sample,ranking_score\n42,0,0.2\n42,1,0.9\n")  # the ranking prefers the distorted sample
+    r = CliRunner().invoke(cli, ["eval-sweep", "score", "--inputs", str(inputs), "--truth", str(truth), "--run-dir", str(run)])
+    assert r.exit_code == 0, r.output
+    with open(run / "eval" / "step_10" / "scores.csv") as f:
+        rows = list(csv.DictReader(f))
+    assert len(rows) == 10 and {r_["fold_class"] for r_ in rows} <= {"coil", "alpha", "beta", "mixed", "none"}
+    with open(run / "eval" / "step_10" / "summary.csv") as f:
+        summ = {(r_["category"], r_["fold_class"]): r_ for r_ in csv.DictReader(f)}
+    mono = summ[("monomer_protein", "all")]
+    assert int(mono["targets"]) == 3 and float(mono["lddt_oracle"]) == pytest.approx(1.0)
+    assert float(mono["lddt_mean"]) < float(mono["lddt_oracle"]) and float(mono["lddt_top"]) < float(mono["lddt_oracle"])
+    assert float(mono["rmsd_trace_oracle"]) < 1e-2 < float(mono["rmsd_trace_mean"])
+    with open(run / "trajectory.csv") as f:
+        traj = [r_ for r_ in csv.DictReader(f) if r_["category"] == "monomer_protein"]
+    assert [int(float(r_["step"])) for r_ in traj] == [10, 20] and float(traj[1]["lddt_mean"]) == pytest.approx(1.0)
+    assert float(traj[0]["lddt_mean"]) < float(traj[1]["lddt_mean"])
+
+    # fold classes from C-alpha geometry: an ideal helix, an extended strand, a helix followed by a strand
+    strand = np.stack([3.3 * np.arange(40), 0.9 * (np.arange(40) % 2), np.zeros(40)], 1)
+    assert sweep.fold_class(_helix(60))[0] == "alpha" and sweep.fold_class(strand)[0] == "beta"
+    assert sweep.fold_class(np.concatenate([_helix(40), strand + [0, 0, 80.0]]))[0] == "mixed"
+    assert sweep.fold_class(np.random.default_rng(0).normal(size=(50, 3)) * 8)[0] == "coil"
+    (tmp_path / "ck").mkdir()
+    (tmp_path / "ck" / "checkpoint_20.pt").write_text("")
+    assert sweep.resolve_checkpoint(str(tmp_path / "ck"), 20).endswith("checkpoint_20.pt") and sweep.resolve_checkpoint(str(tmp_path / "ck"), 30) is None
