@@ -61,6 +61,31 @@ def safe_norm(diff, eps: float = 1e-6):
     return _SafeNorm.apply(diff, eps)
 
 
+class _PairDifference(torch.autograd.Function):
+    """``x[pi] - x[pj]`` for row lists ``pi`` (ascending) and ``pj`` into ``x`` ``[A, F]``.
+
+    The backward of plain advanced indexing is an ``index_put`` with accumulation, which sorts the index list on every
+    call (9 ms per list for 1.4 M pairs x 48 samples on a B200). Here both gradients are segment sums: ``pi`` is already
+    grouped, ``pj`` is grouped by a permutation computed once per call on the index list alone. No atomics, so the result
+    does not depend on scheduling.
+    """
+
+    @staticmethod
+    def forward(ctx, x, pi, pj):
+        ctx.save_for_backward(pi, pj)
+        ctx.rows = x.shape[0]
+        return x.index_select(0, pi) - x.index_select(0, pj)
+
+    @staticmethod
+    def backward(ctx, grad):
+        pi, pj = ctx.saved_tensors
+        grad = grad.contiguous()
+        gi = torch.segment_reduce(grad, "sum", lengths=torch.bincount(pi, minlength=ctx.rows), axis=0, unsafe=True)
+        order = torch.argsort(pj, stable=True)
+        gj = torch.segment_reduce(grad.index_select(0, order), "sum", lengths=torch.bincount(pj, minlength=ctx.rows), axis=0, unsafe=True)
+        return gi - gj, None, None
+
+
 def express_coordinates_in_frame(rep_pos, frame_pos, eps: float = 1e-8):
     """``out[i, j] = R_i^T (rep[j] - b_i)`` with the frame of token ``i`` built from atoms ``(a, b, c)`` (AF3 Alg. 29)."""
     out_dtype = rep_pos.dtype
@@ -160,9 +185,11 @@ def smooth_lddt_loss(pred_pos, gt_pos, atom_mask, cutoffs=(0.5, 1.0, 2.0, 4.0), 
         gt_d = d[pi, pj]
         n_pairs = max(pi.numel(), 1)
     del d, pairs
-    pred = pred_pos.reshape(S, -1, 3)[:, flat]
-    err = (safe_norm(pred[:, pi] - pred[:, pj]) - gt_d.unsqueeze(0)).abs()
-    score = sum(torch.sigmoid(c - err).sum(-1) for c in cutoffs) / (n_pairs * len(cutoffs))
+    # atoms become rows, (sample, xyz) the row content: a pair is then one contiguous row read per side
+    rows = pred_pos.reshape(S, -1, 3)[:, flat].permute(1, 0, 2).reshape(-1, S * 3)
+    diff = _PairDifference.apply(rows, pi, pj).view(-1, S, 3)  # nonzero() lists pairs row-major, so pi ascends
+    err = (safe_norm(diff) - gt_d.unsqueeze(-1)).abs()
+    score = sum(torch.sigmoid(c - err).sum(0) for c in cutoffs) / (n_pairs * len(cutoffs))
     return (1.0 - score).mean()
 
 
