@@ -445,15 +445,41 @@ def convert(af3_params, output):
     click.echo(f"{len(state)} tensors -> {output}")
 
 
+def _mmseqs_options(fn):
+    """Options of the staged local pipeline, shared by ``msa`` and ``msa-batch``."""
+    for opt in reversed([
+        click.option("--db-dir", type=click.Path(), default=None,
+                     help="Directory with the ColabFold databases (uniref30_2302_db, colabfold_envdb_202108_db, pdb100_230517): "
+                          "runs the staged search / expand / re-align / filter pipeline."),
+        click.option("--use-env/--no-use-env", default=True, help="Also search the environmental database."),
+        click.option("--use-templates", is_flag=True, help="Also search the PDB sequences; writes an m8 table with CIGAR strings."),
+        click.option("--gpu", is_flag=True, help="GPU prefilter (databases made with makepaddedseqdb)."),
+        click.option("--gpu-server", is_flag=True, help="Use a running `mmseqs gpuserver` (deploy/msa/gpuserver.sh)."),
+        click.option("--threads", type=int, default=32, show_default=True),
+        click.option("--mmseqs", "mmseqs_binary", default="mmseqs", show_default=True),
+    ]):  # fmt: skip
+        fn = opt(fn)
+    return fn
+
+
+def _mmseqs_settings(db_dir, use_env, use_templates, gpu, gpu_server, threads, mmseqs_binary):
+    from ..data.msa.mmseqs_pipeline import MmseqsSettings
+
+    return MmseqsSettings(db_dir, use_env=use_env, use_templates=use_templates, gpu=gpu, gpu_server=gpu_server, threads=threads,
+                          binary=mmseqs_binary)  # fmt: skip
+
+
 @cli.command()
 @click.argument("fasta_or_sequence")
 @click.option("--output", type=click.Path(), required=True, help="A3M file to write.")
-@click.option("--db", default=None, help="Local MMseqs2 target database; without it the ColabFold API is used.")
+@click.option("--db", default=None, help="One local MMseqs2 target database (plain search); see also --db-dir.")
 @click.option("--cache-dir", type=click.Path(), default="~/.cache/deepfold3/msa")
 @click.option("--host", default=None, help="MSA server URL.")
-def msa(fasta_or_sequence, output, db, cache_dir, host):
-    """Search an alignment for one sequence (local mmseqs pipeline or the ColabFold MMseqs2 API)."""
-    from ..data.msa import search
+@_mmseqs_options
+def msa(fasta_or_sequence, output, db, cache_dir, host, db_dir, use_env, use_templates, gpu, gpu_server, threads, mmseqs_binary):
+    """Search an alignment for one sequence: the staged local pipeline (--db-dir), a plain local search (--db), or the
+    ColabFold MMseqs2 API."""
+    from ..data.msa import mmseqs_pipeline, search
     from ..data.parse.a3m import read_fasta_like
 
     seq = fasta_or_sequence
@@ -461,7 +487,15 @@ def msa(fasta_or_sequence, output, db, cache_dir, host):
         with open(seq) as f:
             seq = read_fasta_like(f.read())[1][0]
     cache = search.MsaCache(os.path.expanduser(cache_dir))
-    a3m = search.search_local(seq, db, cache) if db else search.search_server([seq], cache, host or search.DEFAULT_HOST)[0]
+    if db_dir:
+        settings = _mmseqs_settings(db_dir, use_env, use_templates, gpu, gpu_server, threads, mmseqs_binary)
+        res = mmseqs_pipeline.search_monomer_batch([seq], settings, cache)[0]
+        a3m = res["a3m"]
+        if use_templates:
+            with open(os.path.splitext(output)[0] + ".m8", "w") as f:
+                f.write(res["m8"])
+    else:
+        a3m = search.search_local(seq, db, cache) if db else search.search_server([seq], cache, host or search.DEFAULT_HOST)[0]
     with open(output, "w") as f:
         f.write(a3m)
     click.echo(f"{a3m.count('>')} rows -> {output}")
@@ -472,24 +506,52 @@ def msa(fasta_or_sequence, output, db, cache_dir, host):
 @click.option("--output-dir", type=click.Path(), required=True)
 @click.option("--db", default=None)
 @click.option("--cache-dir", type=click.Path(), default="~/.cache/deepfold3/msa")
-def msa_batch(inputs_file, output_dir, db, cache_dir):
-    """Search alignments for every distinct protein sequence of many jobs; writes ``{sha1}.a3m`` per sequence."""
+@click.option("--paired/--no-paired", default=False, help="With --db-dir: also write paired alignments per complex.")
+@_mmseqs_options
+def msa_batch(inputs_file, output_dir, db, cache_dir, paired, db_dir, use_env, use_templates, gpu, gpu_server, threads, mmseqs_binary):
+    """Search alignments for every distinct protein sequence of many jobs; writes ``{sha1}.a3m`` per sequence (and
+    ``{sha1}.m8`` with --use-templates, ``paired/{job}/{sha1}.a3m`` with --paired). With --db-dir all sequences go
+    through the databases in one pass."""
     import hashlib
 
-    from ..data.msa import search
+    from ..data.msa import mmseqs_pipeline, search
     from ..data.parse.json_input import ProteinChainInput, parse_json_input
 
     os.makedirs(output_dir, exist_ok=True)
     cache = search.MsaCache(os.path.expanduser(cache_dir))
-    seqs = set()
+    seqs: dict[str, None] = {}
+    complexes: dict[str, list[str]] = {}
     with open(inputs_file) as f:
         for line in f:
             if line.strip() and not line.startswith("#"):
                 for job in parse_json_input(line.strip()):
-                    seqs.update(c.sequence for c in job.chains if isinstance(c, ProteinChainInput) and not c.unpaired_msa)
+                    prot = [c for c in job.chains if isinstance(c, ProteinChainInput)]
+                    seqs.update(dict.fromkeys(c.sequence for c in prot if not c.unpaired_msa))
+                    complexes[job.name] = [c.sequence for c in prot]
+    sha = lambda s: hashlib.sha1(s.encode()).hexdigest()  # noqa: E731
+    if db_dir:
+        settings = _mmseqs_settings(db_dir, use_env, use_templates, gpu, gpu_server, threads, mmseqs_binary)
+        todo = list(seqs)
+        for s, res in zip(todo, mmseqs_pipeline.search_monomer_batch(todo, settings, cache)):
+            with open(os.path.join(output_dir, sha(s) + ".a3m"), "w") as f:
+                f.write(res["a3m"])
+            if use_templates:
+                with open(os.path.join(output_dir, sha(s) + ".m8"), "w") as f:
+                    f.write(res["m8"])
+        n_paired = 0
+        if paired:
+            names = [n for n, chains in complexes.items() if len(set(chains)) > 1]
+            for name, blocks in zip(names, mmseqs_pipeline.search_pair_batch([complexes[n] for n in names], settings, cache)):
+                os.makedirs(os.path.join(output_dir, "paired", name), exist_ok=True)
+                for s, block in zip(dict.fromkeys(complexes[name]), blocks):
+                    with open(os.path.join(output_dir, "paired", name, sha(s) + ".a3m"), "w") as f:
+                        f.write(block)
+                n_paired += 1
+        click.echo(f"{len(seqs)} sequences searched, {n_paired} complexes paired")
+        return
     for s in sorted(seqs):
         a3m = search.search_local(s, db, cache) if db else search.search_server([s], cache)[0]
-        with open(os.path.join(output_dir, hashlib.sha1(s.encode()).hexdigest() + ".a3m"), "w") as f:
+        with open(os.path.join(output_dir, sha(s) + ".a3m"), "w") as f:
             f.write(a3m)
     click.echo(f"{len(seqs)} sequences searched")
 

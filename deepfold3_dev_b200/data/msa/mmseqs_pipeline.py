@@ -76,13 +76,15 @@ _FILTER_MSA = ["--filter-msa", "1", "--filter-min-enable", "1000", "--diff", "30
                "--qsc", "0", "--max-seq-id", "0.95"]  # fmt: skip
 
 
-def _expand_align_filter(s, work, qdb, profile, db, tag, load, threads) -> list[list[str]]:
-    """expandaln -> align -> filterresult -> result2msa for one target database; the A3M database is ``<tag>.a3m``."""
+def _expand_align_filter(work, qdb, expand_from, realign_with, db, tag, load, threads) -> list[list[str]]:
+    """expandaln -> align -> filterresult -> result2msa for one target database; the A3M database is ``<tag>.a3m``.
+    ``expand_from`` is the query side of the search that produced ``res_<tag>``; ``realign_with`` the profile the
+    expanded hits are re-aligned against."""
     j = lambda n: os.path.join(work, n)  # noqa: E731
     return [
-        ["expandaln", qdb, db, j(f"res_{tag}"), db, j(f"res_{tag}_exp"), "--db-load-mode", load, "--threads", threads,
+        ["expandaln", expand_from, db, j(f"res_{tag}"), db, j(f"res_{tag}_exp"), "--db-load-mode", load, "--threads", threads,
          "--expansion-mode", "0", "-e", "inf", "--expand-filter-clusters", "1", "--max-seq-id", "0.95"],
-        ["align", profile, db, j(f"res_{tag}_exp"), j(f"res_{tag}_exp_realign"), "--db-load-mode", load, "--threads", threads,
+        ["align", realign_with, db, j(f"res_{tag}_exp"), j(f"res_{tag}_exp_realign"), "--db-load-mode", load, "--threads", threads,
          "-e", "10", "--max-accept", "1000000", "--alt-ali", "10", "-a"],
         ["filterresult", qdb, db, j(f"res_{tag}_exp_realign"), j(f"res_{tag}_exp_realign_filter"), "--db-load-mode", load,
          "--threads", threads, "--qid", "0", "--qsc", "0.8", "--diff", "0", "--max-seq-id", "1.0", "--filter-min-enable", "100"],
@@ -101,9 +103,9 @@ def plan_monomer(s: MmseqsSettings, work: str, fasta: str) -> list[list[str]]:
     plan = [
         ["createdb", fasta, qdb, "--shuffle", "0"],
         ["search", qdb, uniref, j("res_uniref"), j("tmp"), *_search_flags(s, load)],
-        ["mvdb", j("tmp/latest/profile_1"), prof],
+        ["mvdb", j("tmp/latest/profile_1"), prof],     # the profile of the last iteration: query side of everything below
         ["lndb", j("qdb_h"), j("prof_res_h")],
-        *_expand_align_filter(s, work, qdb, prof, uniref + suf, "uniref", load, threads),
+        *_expand_align_filter(work, qdb, qdb, prof, uniref + suf, "uniref", load, threads),
     ]
     merged = [j("uniref.a3m")]
     if s.use_templates:
@@ -117,15 +119,11 @@ def plan_monomer(s: MmseqsSettings, work: str, fasta: str) -> list[list[str]]:
     if s.use_env:
         esuf, eload = detect_db_mode(s.db_dir, s.env_db)
         env = os.path.join(s.db_dir, s.env_db)
+        # the environmental search starts from the UniRef profile; its hits are re-aligned against its own last profile
         plan += [
             ["search", prof, env, j("res_env"), j("tmp_env"), *_search_flags(s, eload)],
-            *_expand_align_filter(s, work, qdb, j("tmp_env/latest/profile_1"), env + esuf, "env", eload, threads)[0:1],
+            *_expand_align_filter(work, qdb, prof, j("tmp_env/latest/profile_1"), env + esuf, "env", eload, threads),
         ]
-        # the environmental hits are re-aligned against the profile of the environmental search itself
-        rest = _expand_align_filter(s, work, qdb, j("tmp_env/latest/profile_1"), env + esuf, "env", eload, threads)[1:]
-        rest[0][1] = j("tmp_env/latest/profile_1")
-        plan[-1][1] = prof  # expandaln starts from the UniRef profile
-        plan += rest
         merged.append(j("env.a3m"))
     plan += [["mergedbs", qdb, j("final.a3m"), *merged] if len(merged) > 1 else ["mvdb", merged[0], j("final.a3m")],
              ["unpackdb", j("final.a3m"), j("out"), "--unpack-name-mode", "0", "--unpack-suffix", ".a3m"]]  # fmt: skip

@@ -383,6 +383,92 @@ def test_msa_search_cache_and_fake_binary(tmp_path, monkeypatch):
         search.search_local("WWWW", "/db/uniref", cache, binary=str(fake))
 
 
+def test_staged_mmseqs_pipeline_with_a_stand_in_binary(tmp_path):
+    """The staged local pipeline against a stand-in for the ``mmseqs`` binary that records its calls and fabricates the
+    files the next stage reads: stage order, index / load-mode detection, GPU flags, one pass for a batch with
+    duplicates, template hits split by query, the cache, paired alignments with a row-count check, the CLI."""
+    import json
+    import stat
+
+    from click.testing import CliRunner
+
+    from deepfold3_dev_b200.cli.main import cli
+    from deepfold3_dev_b200.data.msa import mmseqs_pipeline as mp
+    from deepfold3_dev_b200.data.msa.search import MsaCache
+
+    db = tmp_path / "db"
+    db.mkdir()
+    (db / "uniref30_2302_db.idx").write_text("")  # UniRef has a precomputed index, the environmental database has none
+    log = tmp_path / "calls.log"
+    fake = tmp_path / "mmseqs"
+    fake.write_text(f"""#!/usr/bin/env python3
+import os, sys
+a = sys.argv[1:]
+open({str(log)!r}, "a").write(" ".join(a) + "\\n")
+cmd = a[0]
+def queries(work):
+    return [l[1:].strip() for l in open(os.path.join(work, "query.fasta")) if l.startswith(">")]
+if cmd == "unpackdb":
+    src, out = a[1], a[2]
+    work = os.path.dirname(src)
+    os.makedirs(out, exist_ok=True)
+    seqs = [l.strip() for l in open(os.path.join(work, "query.fasta")) if not l.startswith(">")]
+    for i, (q, s) in enumerate(zip(queries(work), seqs)):
+        rows = 3 if "pair" in os.path.basename(src) else 2 + i
+        open(os.path.join(out, f"{{i}}.a3m"), "w").write("".join(f">{{q if r == 0 else 'hit%d' % r}}\\n{{s}}\\n" for r in range(rows)) + "\\0")
+elif cmd == "convertalis":
+    work = os.path.dirname(a[4])
+    with open(a[4], "w") as f:
+        for q in queries(work):
+            f.write("\\t".join([q, "1abc_A", "0.9", "50", "2", "0", "1", "50", "3", "52", "1e-30", "200", "50M"]) + "\\n")
+""")
+    fake.chmod(fake.stat().st_mode | stat.S_IEXEC)
+
+    s = mp.MmseqsSettings(str(db), use_env=True, use_templates=True, gpu=True, threads=4, binary=str(fake))
+    assert mp.detect_db_mode(str(db), s.uniref_db) == (".idx", "2") and mp.detect_db_mode(str(db), s.env_db) == ("", "0")
+    plan = mp.plan_monomer(s, "/w", "/w/query.fasta")
+    assert [c[0] for c in plan] == ["createdb", "search", "mvdb", "lndb", "expandaln", "align", "filterresult", "result2msa", "search",
+                                    "convertalis", "search", "expandaln", "align", "filterresult", "result2msa", "mergedbs", "unpackdb"]  # fmt: skip
+    assert "--gpu" in plan[1] and "-s" not in plan[1] and plan[1][plan[1].index("--db-load-mode") + 1] == "2"
+    assert plan[4][2].endswith("uniref30_2302_db.idx") and plan[11][2].endswith("colabfold_envdb_202108_db")
+    assert plan[12][1] == "/w/tmp_env/latest/profile_1" and plan[10][1] == "/w/prof_res"
+    cpu = mp.plan_monomer(mp.MmseqsSettings(str(db), use_env=False), "/w", "/w/query.fasta")
+    assert "-s" in cpu[1] and cpu[-2][0] == "mvdb" and len(cpu) == 10
+
+    cache = MsaCache(str(tmp_path / "cache"))
+    res = mp.search_monomer_batch(["ACDEF", "GHIKL", "ACDEF"], s, cache)
+    assert [parse_a3m(r["a3m"]).sequences[0] for r in res] == ["ACDEF", "GHIKL", "ACDEF"] and res[0] is res[2]
+    assert res[1]["a3m"].count(">") == 3 and "\x00" not in res[1]["a3m"]
+    hits = mp.parse_m8(res[0]["m8"] + "broken line\n")
+    assert list(hits) == ["0"] and hits["0"][0].target == "1abc_A" and hits["0"][0].cigar == "50M" and hits["0"][0].t_start == 3
+    calls = log.read_text().splitlines()
+    assert sum(c.startswith("createdb") for c in calls) == 1  # one pass for the whole batch
+    log.write_text("")
+    again = mp.search_monomer_batch(["GHIKL", "MNPQR"], s, cache)  # the first comes from the cache, only the second is searched
+    assert again[0]["a3m"] == res[1]["a3m"] and parse_a3m(again[1]["a3m"]).sequences[0] == "MNPQR"
+    assert sum(c.startswith("createdb") for c in log.read_text().splitlines()) == 1
+
+    paired = mp.search_pair_batch([["ACDEF", "GHIKL", "ACDEF"], ["WWWWW"]], s, cache)
+    assert len(paired[0]) == 2 and all(b.count(">") == 3 for b in paired[0]) and paired[1] == [">101\nWWWWW\n"]
+    pair_plan = mp.plan_pair(s, "/w", "/w/query.fasta")
+    assert [c[0] for c in pair_plan].count("pairaln") == 2 and pair_plan[-2][-1] == "5"
+
+    jobs = tmp_path / "jobs.txt"
+    job = tmp_path / "cx.json"
+    job.write_text(json.dumps({"name": "cx", "sequences": [{"protein": {"id": ["A"], "sequence": "ACDEF"}}, {"protein": {"id": ["B"], "sequence": "GHIKL"}}]}))
+    jobs.write_text(f"{job}\n")
+    r = CliRunner().invoke(cli, ["msa-batch", "--inputs-file", str(jobs), "--output-dir", str(tmp_path / "out"), "--db-dir", str(db),
+                                 "--use-templates", "--paired", "--mmseqs", str(fake), "--cache-dir", str(tmp_path / "c2")])  # fmt: skip
+    assert r.exit_code == 0 and "2 sequences searched, 1 complexes paired" in r.output, r.output
+    import hashlib
+
+    key = hashlib.sha1(b"GHIKL").hexdigest()
+    assert (tmp_path / "out" / f"{key}.a3m").exists() and (tmp_path / "out" / f"{key}.m8").exists()
+    assert (tmp_path / "out" / "paired" / "cx" / f"{key}.a3m").read_text().count(">") == 3
+    with pytest.raises(RuntimeError, match="not on PATH"):
+        mp.run_plan([["version"]], binary=str(tmp_path / "absent"))
+
+
 def test_tiled_linear_is_transparent():
     from deepfold3_dev_b200.models.tiled_linear import TiledLinear
 
