@@ -158,6 +158,11 @@ def _inference_options(f):
         click.option("--device", default=None),
         click.option("--optim", type=click.Choice(["none", "inference", "inference-cueq", "train-matched"]), default="inference"),
         click.option("--precision", type=click.Choice(list(DTYPES)), default="bf16"),
+        click.option("--msa-search", type=click.Choice(["none", "server", "local"]), default="none", show_default=True,
+                     help="Search alignments (and template hits) for protein chains of a JSON job that carry none: the ColabFold "
+                          "MMseqs2 API, or the staged local pipeline over --msa-db-dir."),
+        click.option("--msa-db-dir", type=click.Path(), default=None, help="ColabFold databases for --msa-search local."),
+        click.option("--msa-cache-dir", type=click.Path(), default="~/.cache/deepfold3/msa", show_default=True),
         click.option("--logits-scheme", type=click.Choice(["float32", "float16", "int8", "int8_softmax", "int4_softmax", "f16", "u8", "f32"]),
                      default="int8_softmax", show_default=True, help="How logits.npz stores the head logits (f16 / u8 / f32: earlier names)."),
         click.option("--bucket/--no-bucket", default=True),
@@ -261,6 +266,21 @@ def _attach_templates(inp, hits_path: str, mmcif_dir: str | None, cache_dir: str
         inp.features.update(tpl.template_features(n, chains))
 
 
+def _msa_search_fn(mode: str, db_dir: str | None, cache_dir: str | None):
+    """The ``msa_search`` argument of ``parse_json_input`` for the ``--msa-search`` choice."""
+    from ..data.parse import json_input
+
+    if mode == "server":
+        return json_input.msa_search_from_server(cache_dir)
+    if mode == "local":
+        if not db_dir:
+            raise click.ClickException("--msa-search local needs --msa-db-dir")
+        from ..data.msa.mmseqs_pipeline import MmseqsSettings
+
+        return json_input.msa_search_local(MmseqsSettings(db_dir, use_templates=True), cache_dir)
+    return None
+
+
 def _plot_outputs(out_dir: str) -> None:
     from ..io.plot import plot_confidences
 
@@ -299,7 +319,7 @@ def _guidance_terms(specs):
 @click.option("--template-cache", type=click.Path(), default=None, help="Directory for the prepared template files.")
 @_inference_options
 def inference(msa, json_path, sequence, mol_type, output, templates_path, pdb_mmcif_dir, template_cache, params, num_recycles, num_samples, msa_crop_size, snapshot,
-              seeds, device, optim, precision, logits_scheme, bucket, sample_chunk, guidance, allow_guidance_overlap,
+              seeds, device, optim, precision, msa_search, msa_db_dir, msa_cache_dir, logits_scheme, bucket, sample_chunk, guidance, allow_guidance_overlap,
               restraints, restraint_pairs, repels, restraint_rigid, restraint_after_step, restraint_after_sigma,
               restraint_max_step, restraint_weight, msa_pairing, matmul_precision, plot_confidences,
               allow_missing_keys, ccd, det):  # fmt: skip
@@ -328,7 +348,8 @@ def inference(msa, json_path, sequence, mol_type, output, templates_path, pdb_mm
     if json_path:
         from ..data.parse.json_input import parse_json_input
 
-        inputs = [InferenceInput.from_job(job, msa_crop_size, msa_pairing) for job in parse_json_input(json_path)]
+        inputs = [InferenceInput.from_job(job, msa_crop_size, msa_pairing, pdb_mmcif_dir)
+                  for job in parse_json_input(json_path, msa_search=_msa_search_fn(msa_search, msa_db_dir, msa_cache_dir))]
     elif msa:
         inputs = [InferenceInput.from_a3m(msa, mol_type, msa_crop_size=msa_crop_size)]
     elif sequence:
@@ -361,9 +382,10 @@ def inference(msa, json_path, sequence, mol_type, output, templates_path, pdb_mm
 @click.option("--skip-existing/--no-skip-existing", default=True)
 @click.option("--save-distogram/--no-save-distogram", default=True)
 @click.option("--shard", default=None, help="I/N: take every N-th job starting at I (one process per GPU; default from RANK / WORLD_SIZE).")
+@click.option("--pdb-mmcif-dir", type=click.Path(exists=True), default=None, help="Local mmCIF mirror for template hits named by PDB id.")
 @_inference_options
-def inference_batch(inputs_file, output_template, skip_existing, save_distogram, shard, params, num_recycles, num_samples,
-                    msa_crop_size, snapshot, seeds, device, optim, precision, logits_scheme, bucket, sample_chunk,
+def inference_batch(inputs_file, output_template, skip_existing, save_distogram, shard, pdb_mmcif_dir, params, num_recycles, num_samples,
+                    msa_crop_size, snapshot, seeds, device, optim, precision, msa_search, msa_db_dir, msa_cache_dir, logits_scheme, bucket, sample_chunk,
                     guidance, allow_guidance_overlap, restraints, restraint_pairs, repels, restraint_rigid,
                     restraint_after_step, restraint_after_sigma, restraint_max_step, restraint_weight, msa_pairing,
                     matmul_precision, plot_confidences, allow_missing_keys, ccd, det):  # fmt: skip
@@ -394,10 +416,11 @@ def inference_batch(inputs_file, output_template, skip_existing, save_distogram,
     if part is not None:
         paths = paths[part[0] :: part[1]]
     done = failed = 0
+    search_fn = _msa_search_fn(msa_search, msa_db_dir, msa_cache_dir)
     for p in paths:
         try:
-            for job in parse_json_input(p):
-                inp = InferenceInput.from_job(job, msa_crop_size, msa_pairing)
+            for job in parse_json_input(p, msa_search=search_fn):
+                inp = InferenceInput.from_job(job, msa_crop_size, msa_pairing, pdb_mmcif_dir)
                 terms, rkw = _job_steering(inp, guidance, allow_guidance_overlap, restraints, restraint_pairs, repels,
                                            restraint_weight, restraint_rigid, restraint_after_step, restraint_after_sigma,
                                            restraint_max_step)  # fmt: skip

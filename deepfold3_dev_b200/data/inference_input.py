@@ -53,7 +53,8 @@ class InferenceInput:
         return [cls.from_job(job, msa_crop_size=msa_crop_size) for job in parse_json_input(path)]
 
     @classmethod
-    def from_job(cls, job: JobInput, msa_crop_size: int = 16384, msa_pairing: str = "auto") -> InferenceInput:
+    def from_job(cls, job: JobInput, msa_crop_size: int = 16384, msa_pairing: str = "auto",
+                 pdb_mmcif_dir: str | None = None) -> InferenceInput:  # fmt: skip
         if job.user_ccd:
             if "data_" in job.user_ccd and "\n" in job.user_ccd:
                 ref_conformers.load_component_text(job.user_ccd)
@@ -83,7 +84,7 @@ class InferenceInput:
                 asym += 1
         feats = _token_features(tok)
         feats.update(_msa_features(feats, chain_cols, chain_msas, msa_crop_size, msa_pairing))
-        feats.update(_template_features(feats, chain_cols, chain_msas))
+        feats.update(_template_features(feats, chain_cols, chain_msas, mmcif_dir=pdb_mmcif_dir, max_date=job.max_template_date))
         feats["bond_matrix"] = _bond_matrix(tok, chain_names, job.bonded_atom_pairs)
         return cls(feats, chain_names, job.name, list(job.seeds))
 
@@ -124,7 +125,8 @@ def _bond_matrix(tok, chain_names, bonded_atom_pairs) -> torch.Tensor:
     return out
 
 
-def _template_features(feats, chain_cols, chains, max_templates: int = 4) -> dict:
+def _template_features(feats, chain_cols, chains, max_templates: int = 4, mmcif_dir: str | None = None,
+                       max_date: str | None = None) -> dict:  # fmt: skip
     """Template features of the protein chains that list hits; each chain fills its own token columns."""
     from . import templates as tpl
 
@@ -134,7 +136,7 @@ def _template_features(feats, chain_cols, chains, max_templates: int = 4) -> dic
         hits = getattr(c, "templates", None)
         if not hits or e - s != len(getattr(c, "sequence", "")):
             continue
-        loaded = tpl.load_json_templates(hits, hits[0].get("_base_dir", "."), max_templates)
+        loaded = tpl.load_json_templates(hits, hits[0].get("_base_dir", "."), max_templates, mmcif_dir, max_date)
         if not loaded:
             continue
         part = tpl.template_features(e - s, loaded, max_templates, token_offset=s, num_tokens=N)

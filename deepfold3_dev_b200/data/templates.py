@@ -145,9 +145,13 @@ def template_chain_from_mmcif(path: str, chain_id: str | None, query_indices, te
     return TemplateChain(names, coords, mask, {int(q): int(t) for q, t in zip(query_indices, template_indices)})
 
 
-def load_json_templates(entries: list[dict], base_dir: str = ".", max_templates: int = 4) -> list[TemplateChain]:
-    """Hit list of a prediction job: ``[{"name" | "mmcifPath": file, "chainId", "queryIndices", "templateIndices"}]``
-    (an entry may instead carry the file's text under ``"mmcif"``). Unreadable hits are skipped."""
+def load_json_templates(entries: list[dict], base_dir: str = ".", max_templates: int = 4, mmcif_dir: str | None = None,
+                        max_date: str | None = None) -> list[TemplateChain]:
+    """Hit list of a prediction job: ``[{"name" | "mmcifPath": file, "chainId", "queryIndices", "templateIndices"}]``.
+    An entry may instead carry the file's text under ``"mmcif"``, or only a ``"pdbId"`` that is looked up in the local
+    mmCIF mirror ``mmcif_dir``. With ``max_date`` (YYYY-MM-DD) a hit released later is dropped: the entry's
+    ``"releaseDate"`` decides when present, else the release date in the structure file; a hit whose date cannot be
+    determined is kept. Unreadable hits are skipped."""
     import os
     import tempfile
 
@@ -163,8 +167,16 @@ def load_json_templates(entries: list[dict], base_dir: str = ".", max_templates:
             path = tmp.name
         elif path and not os.path.isabs(path):
             path = os.path.join(base_dir, path)
+        elif not path and e.get("pdbId") and mmcif_dir:
+            path = find_pdb_mmcif(str(e["pdbId"]), mmcif_dir)
         try:
             if path and os.path.exists(path):
+                if max_date and not e.get("releaseDate"):
+                    from .parse.mmcif import parse_mmcif
+
+                    released = getattr(parse_mmcif(path, use_assembly=False)[1].structure_info, "released", None)
+                    if released and str(released)[:10] > max_date:
+                        continue
                 hit = template_chain_from_mmcif(path, e.get("chainId"), e["queryIndices"], e["templateIndices"])
                 if hit is not None:
                     out.append(hit)

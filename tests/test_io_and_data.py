@@ -110,6 +110,93 @@ def test_a3m_and_json_dialects(tmp_path):
         InferenceInput.from_job(parse_json_input({"name": "l", "sequences": [{"ligand": {"id": "L", "ccdCodes": ["ATP"]}}]})[0])
 
 
+def test_job_dialect_details(tmp_path, caplog):
+    """Behaviour of the job parser beyond the happy path: seeds per dialect, key aliases, SMILES against component codes,
+    Protenix alignment directories, HHsearch hit files, user dictionaries from a path, the template date cut-off,
+    tolerant handling of malformed optional parts, errors for unusable jobs, alignment search on demand."""
+    import logging
+
+    from deepfold3_dev_b200.data.parse import json_input as ji
+
+    # seeds: the file formats fall back to 42, the server format draws one
+    assert parse_json_input({"sequences": [{"protein": {"id": "A", "sequence": "ACD"}}]})[0].seeds == [42]
+    drawn = parse_json_input([{"name": "s", "sequences": [{"proteinChain": {"sequence": "ACD", "count": 1}}]}])[0].seeds
+    assert len(drawn) == 1 and 0 <= drawn[0] < 2**32
+    # Protenix: chain-key aliases, alignment directory, ligand as component code or SMILES
+    pre = tmp_path / "msa" / "0"
+    pre.mkdir(parents=True)
+    (pre / "non_pairing.a3m").write_text(">q\nACDEF\n>u\nACDEF\n")
+    (pre / "pairing.a3m").write_text(">q\nACDEF\n>p\nAC-EF\n")
+    ptx = tmp_path / "ptx.json"
+    ptx.write_text(json.dumps([{"name": "p", "modelSeeds": [], "sequences": [
+        {"proteinChain": {"sequence": "acdef", "count": 2, "msa": {"precomputed_msa_dir": "msa/0"},
+                          "modifications": [{"ptmType": "CCD_SEP", "ptmPosition": 3}, {"ptmType": "TPO"}, "junk"]}},
+        {"rnaChain": {"sequence": "ACGU", "count": 1, "modifications": [{"modificationType": "2MG", "basePosition": 1}]}},
+        {"dnaChain": {"sequence": "ACGT", "count": 1}},
+        {"ligand": {"ligand": "CCD_ATP", "count": 1}}, {"ligand": {"ligand": "CC(=O)O", "count": 2}}]}]))  # fmt: skip
+    with caplog.at_level(logging.WARNING):
+        (job,) = parse_json_input(str(ptx))
+    prot, rna, dna, atp, smi = job.chains
+    assert job.dialect == "protenix" and job.seeds == [42] and job.num_chains == 7
+    assert prot.sequence == "ACDEF" and prot.ids == ["A", "B"] and prot.modifications == [("SEP", 3)]
+    assert prot.unpaired_msa.count(">") == 2 and "AC-EF" in prot.paired_msa
+    assert rna.mol_type == 2 and rna.modifications == [("2MG", 1)] and dna.mol_type == 1
+    assert atp.ccd_codes == ["ATP"] and atp.smiles is None and smi.smiles == "CC(=O)O" and smi.ccd_codes == [] and smi.ids == ["F", "G"]
+    assert sum("modification skipped" in r.message for r in caplog.records) == 2
+    # the server format names components with or without the prefix
+    srv = parse_json_input([{"name": "s", "modelSeeds": ["7"], "sequences": [{"proteinChain": {"sequence": "ACD", "count": 1}},
+                            {"ligand": {"ligand": "HEM", "count": 1}}, {"ion": {"ion": "CCD_MG", "count": 2}}]}])[0]  # fmt: skip
+    assert srv.dialect == "alphafoldserver" and srv.seeds == [7] and srv.chains[1].ccd_codes == ["HEM"] and srv.chains[2].ccd_codes == ["MG"]
+
+    # AF3: HHsearch hits, dictionary from a path, template date cut-off, malformed bonds
+    hhr = tmp_path / "hits.hhr"
+    hhr.write_text("Query q\n\nNo 1\n>1abc_B some protein\nProbab=99.0 E-value=1e-20 Score=100 Aligned_cols=4 Identities=50% Similarity=0.5 Sum_probs=3.5\n\n"
+                   "Q q 2 CDEF 5 (5)\nQ Consensus 2 cdef 5 (5)\nT Consensus 10 cdxf 13 (90)\nT 1abc_B 10 CD-F 13 (90)\n\n")
+    (tmp_path / "my.cif").write_text("data_LIG\n_chem_comp.id LIG\n")
+    af3 = tmp_path / "af3.json"
+    af3.write_text(json.dumps({"name": "t", "maxTemplateDate": "2020-01-01", "userCCDPath": "my.cif", "description": "demo",
+        "bondedAtomPairs": [[["A", 1, "CA"], ["L", 1, "C1"]], [["A", 1], ["L", 1, "C1"]], "x"],
+        "sequences": [{"protein": {"id": "A", "sequence": "ACDEF", "templatesPath": "hits.hhr", "description": "chain a"}},
+                      {"protein": {"id": "B", "sequence": "GHIKL", "templates": [
+                          {"mmcifPath": "old.cif", "queryIndices": [0], "templateIndices": [0], "releaseDate": "2019-05-05"},
+                          {"mmcifPath": "new.cif", "queryIndices": [0], "templateIndices": [0], "releaseDate": "2021-02-03"},
+                          {"mmcifPath": "undated.cif", "queryIndices": [0], "templateIndices": [0]}]}},
+                      {"ligand": {"id": "L", "smiles": "CCO"}}]}))  # fmt: skip
+    caplog.clear()
+    with caplog.at_level(logging.WARNING):
+        (job,) = parse_json_input(str(af3))
+    a, b, lig = job.chains
+    assert job.max_template_date == "2020-01-01" and job.user_ccd.startswith("data_LIG") and job.description == "demo" and a.description == "chain a"
+    assert len(job.bonded_atom_pairs) == 1 and sum("bondedAtomPairs entry skipped" in r.message for r in caplog.records) == 2
+    (hit,) = a.templates
+    assert (hit["pdbId"], hit["chainId"], hit["queryIndices"], hit["templateIndices"]) == ("1ABC", "B", [1, 2, 4], [9, 10, 11])
+    assert [h["mmcifPath"] for h in b.templates] == ["old.cif", "undated.cif"] and b.templates[0]["_base_dir"] == str(tmp_path)
+    assert parse_json_input({"maxTemplateDate": "soon", "sequences": [{"protein": {"id": "A", "sequence": "AC"}}]})[0].max_template_date is None
+
+    # unusable jobs and arguments
+    with pytest.raises(ValueError, match="no chains"):
+        parse_json_input({"name": "empty", "sequences": []})
+    with pytest.raises(ValueError, match="unknown sequence entry"):
+        parse_json_input({"name": "x", "sequences": [{"peptoid": {"sequence": "AA"}}]})
+    with pytest.raises(ValueError, match="msa_pairing"):
+        parse_json_input({"sequences": [{"protein": {"id": "A", "sequence": "AC"}}]}, msa_pairing="sometimes")
+
+    # alignment search on demand: once per job, distinct sequences without an alignment only
+    calls = []
+
+    def fake_search(seqs):
+        calls.append(list(seqs))
+        return [{"unpaired": f">q\n{s}\n>h\n{s}\n", "paired": None, "templates": [{"pdbId": "2XYZ", "chainId": "A", "queryIndices": [0],
+                 "templateIndices": [0], "releaseDate": "2030-01-01"}]} for s in seqs]  # fmt: skip
+
+    (job,) = parse_json_input({"name": "m", "maxTemplateDate": "2025-01-01", "sequences": [
+        {"protein": {"id": ["A", "B"], "sequence": "ACDEF"}}, {"protein": {"id": "C", "sequence": "GHIKL", "unpairedMsa": ">q\nGHIKL\n"}},
+        {"protein": {"id": "D", "sequence": "MNPQR"}}]}, msa_search=fake_search)  # fmt: skip
+    assert calls == [["ACDEF", "MNPQR"]] and job.chains[0].unpaired_msa.count(">") == 2 and job.chains[1].unpaired_msa.count(">") == 1
+    assert job.chains[0].templates == []  # the searched hit is newer than the job's cut-off
+    assert ji.detect_dialect({"dialect": "Protenix", "sequences": []}) == "protenix"
+
+
 def test_crops_keep_consistency():
     f = synthetic_complex([("protein", 60), ("protein", 50), ("ligand", 6)], num_msa=8, num_templates=2, seed=1)
     for strategy in ("contiguous", "spatial", "spatial_interface"):
