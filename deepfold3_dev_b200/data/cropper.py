@@ -1,10 +1,20 @@
 """Token crops of a featurised example (reference: data/crop/cropper.py:86-772).
 
-Three strategies with weights 0.2 / 0.4 / 0.4: contiguous (per-chain contiguous segments, AF-Multimer
-algorithm 1), spatial (the ``max_tokens`` tokens nearest to a reference token) and spatial-interface
-(the reference token is drawn among tokens within 15 Angstrom of another chain). Both a token and an
-atom budget apply. Cropping works on the feature dict: every token axis is re-indexed, MSA columns and
-template rows follow.
+Three strategies with weights 0.2 / 0.4 / 0.4, drawn independently of the sampler's anchor (AF3 SI 2.7):
+
+* contiguous: AF-Multimer algorithm 1: the chains are visited in random order and each contributes one contiguous
+  segment whose length is drawn so that the token budget can still be met;
+* spatial: the tokens nearest to a seed token, by the distance between token centre atoms;
+* spatial-interface: the same with the seed drawn among tokens within 15 Angstrom of a token of another chain.
+
+Only tokens whose centre atom is resolved are candidates of the two spatial strategies, so an unresolved stretch never
+fills a crop. The sampler's anchor (the weighted chain or interface that made this example be drawn) biases the seed
+only: a chain anchor restricts the seed pool to that chain, an interface anchor restricts interface seeds to tokens of
+the two chains that touch the other one. Both a token and an atom budget apply, in the order in which a strategy
+collects tokens (by distance, or chain by chain), so the budget never removes the tokens nearest to the seed. A crop
+must contain at least ``min_resolved`` resolved tokens (the rigid alignment inside the loss needs them); otherwise a
+new crop is drawn, up to ``max_attempts`` times. Cropping works on the feature dict: every token axis is re-indexed,
+MSA columns and template rows follow.
 """
 
 from __future__ import annotations
@@ -15,9 +25,12 @@ from ..models.bucket import _token_axes
 
 CROP_WEIGHTS = {"contiguous": 0.2, "spatial": 0.4, "spatial_interface": 0.4}
 INTERFACE_DISTANCE = 15.0
+MIN_RESOLVED = 4
+MAX_ATTEMPTS = 8
 
 
 def _center_coords(feats):
+    """Centre-atom position per token and whether that atom is resolved (always true for features without a ground truth)."""
     n = feats["res_type"].shape[0]
     pos = feats["atom_gt_positions"] if "atom_gt_positions" in feats else feats["ref_pos"]
     idx = feats["token_to_center_atom"].view(n, 1, 1).expand(n, 1, 3)
@@ -25,7 +38,22 @@ def _center_coords(feats):
     return pos.gather(1, idx).squeeze(1), ok.bool()
 
 
-def contiguous_crop(asym_id: torch.Tensor, max_tokens: int, gen: torch.Generator) -> torch.Tensor:
+def _atoms_per_token(feats) -> torch.Tensor:
+    return feats["ref_mask"].sum(-1).long()
+
+
+def _within_budgets(order: torch.Tensor, atoms: torch.Tensor, max_tokens: int, max_atoms: int) -> torch.Tensor:
+    """The longest prefix of ``order`` (token indices in collection order) that meets both budgets, sorted."""
+    order = order[:max_tokens]
+    if max_atoms > 0 and len(order):
+        fits = atoms[order].cumsum(0) <= max_atoms
+        # stop at the first token that would exceed the budget (no skipping ahead to smaller tokens)
+        order = order[: int(fits.long().cumprod(0).sum())]
+    return torch.sort(order).values
+
+
+def contiguous_crop(asym_id: torch.Tensor, max_tokens: int, gen: torch.Generator, atoms: torch.Tensor | None = None,
+                    max_atoms: int = 0) -> torch.Tensor:  # fmt: skip
     """Indices kept by the contiguous multi-chain crop (chains visited in random order)."""
     chains = torch.unique(asym_id)
     chains = chains[torch.randperm(len(chains), generator=gen)]
@@ -44,24 +72,49 @@ def contiguous_crop(asym_id: torch.Tensor, max_tokens: int, gen: torch.Generator
             keep.append(idx[start : start + size])
         if budget <= 0:
             break
-    return torch.sort(torch.cat(keep)).values if keep else torch.arange(min(max_tokens, len(asym_id)))
+    order = torch.cat(keep) if keep else torch.arange(min(max_tokens, len(asym_id)))
+    if atoms is None:
+        return torch.sort(order).values
+    return _within_budgets(order, atoms, max_tokens, max_atoms)
 
 
-def spatial_crop(coords, valid, asym_id, max_tokens: int, gen: torch.Generator, interface: bool) -> torch.Tensor:
-    cand = valid.clone()
-    if interface:
-        d = torch.cdist(coords, coords)
-        other = asym_id[:, None] != asym_id[None, :]
-        near = ((d < INTERFACE_DISTANCE) & other & valid[None, :]).any(-1) & valid
-        if bool(near.any()):
-            cand = near
-    pool = torch.nonzero(cand).flatten()
+def _seed_pool(pool: torch.Tensor, asym_id: torch.Tensor, anchor_chain: int | None) -> torch.Tensor:
+    """Seed candidates: the pool's tokens of the anchor chain when there are any, else the whole pool."""
+    if anchor_chain is not None:
+        mine = pool[asym_id[pool] == anchor_chain]
+        if len(mine):
+            return mine
+    return pool
+
+
+def spatial_crop(coords, valid, asym_id, max_tokens: int, gen: torch.Generator, interface: bool, atoms: torch.Tensor | None = None,
+                 max_atoms: int = 0, anchor=None) -> torch.Tensor:  # fmt: skip
+    """Nearest-neighbour crop around a seed. ``valid``: tokens with a resolved centre atom (the only candidates, unless
+    there are none). ``anchor``: ``("chain", a, _)`` or ``("interface", a, b)`` in ``asym_id`` numbering, or ``None``."""
+    n = len(asym_id)
+    pool = torch.nonzero(valid).flatten()
     if len(pool) == 0:
-        pool = torch.arange(len(asym_id))
-    ref = pool[int(torch.randint(0, len(pool), (1,), generator=gen))]
-    dist = (coords - coords[ref]).norm(dim=-1) + (~valid).float() * 1e6
-    dist = dist + torch.arange(len(dist)) * 1e-3  # deterministic tie-break
-    return torch.sort(torch.topk(dist, min(max_tokens, len(dist)), largest=False).indices).values
+        pool = torch.arange(n)
+    anchor_chain = int(anchor[1]) if anchor is not None else None
+    seeds = None
+    if interface and len(pool) >= 2:
+        pc, pa = coords[pool], asym_id[pool]
+        close = torch.cdist(pc, pc) < INTERFACE_DISTANCE
+        if anchor is not None and anchor[0] == "interface":
+            a, b = int(anchor[1]), int(anchor[2])
+            touches = ((pa == a)[:, None] & (pa == b)[None, :] & close).any(-1) | ((pa == b)[:, None] & (pa == a)[None, :] & close).any(-1)
+        else:
+            touches = (close & (pa[:, None] != pa[None, :])).any(-1)
+        if bool(touches.any()):
+            seeds = pool[touches]
+    if seeds is None:  # plain spatial crop, or no interface token of the wanted kind
+        seeds = _seed_pool(pool, asym_id, anchor_chain)
+    ref = seeds[int(torch.randint(0, len(seeds), (1,), generator=gen))]
+    dist = (coords[pool] - coords[ref]).norm(dim=-1) + torch.arange(len(pool)) * 1e-6  # index breaks ties
+    order = pool[torch.argsort(dist)]
+    if atoms is None:
+        return torch.sort(order[:max_tokens]).values
+    return _within_budgets(order, atoms, max_tokens, max_atoms)
 
 
 def apply_atom_budget(keep: torch.Tensor, ref_mask: torch.Tensor, max_atoms: int) -> torch.Tensor:
@@ -96,26 +149,42 @@ def select_tokens(feats: dict, keep: torch.Tensor) -> dict:
 
 
 def crop(feats: dict, max_tokens: int, max_atoms: int = 0, gen: torch.Generator | None = None, weights: dict | None = None,
-         strategy: str | None = None, return_keep: bool = False):  # fmt: skip
+         strategy: str | None = None, return_keep: bool = False, anchor=None, min_resolved: int = MIN_RESOLVED,
+         max_attempts: int = MAX_ATTEMPTS):  # fmt: skip
     """Crop to the budgets; returns the cropped features and the strategy used (with ``return_keep`` also the sorted
-    indices of the tokens kept, ``None`` when nothing was cut)."""
-    out = _crop(feats, max_tokens, max_atoms, gen, weights, strategy)
+    indices of the tokens kept, ``None`` when nothing was cut). ``anchor``: the sampler's chain or interface in
+    ``asym_id`` numbering (see the module text); ``strategy`` pins the strategy instead of drawing it."""
+    out = _crop(feats, max_tokens, max_atoms, gen, weights, strategy, anchor, min_resolved, max_attempts)
     return out if return_keep else out[:2]
 
 
-def _crop(feats, max_tokens, max_atoms, gen, weights, strategy):
+def _draw(w: dict, gen: torch.Generator) -> str:
+    names = list(w)
+    total = sum(float(w[k]) for k in names)
+    if total <= 0:
+        return "contiguous"
+    return names[int(torch.multinomial(torch.tensor([float(w[k]) for k in names]), 1, generator=gen))]
+
+
+def _crop(feats, max_tokens, max_atoms, gen, weights, strategy, anchor=None, min_resolved=MIN_RESOLVED, max_attempts=MAX_ATTEMPTS):
     gen = gen or torch.Generator().manual_seed(int(torch.randint(0, 2**31 - 1, (1,))))
     n = int(feats["res_type"].shape[0])
     w = weights or CROP_WEIGHTS
-    if strategy is None:
-        names = list(w)
-        strategy = names[int(torch.multinomial(torch.tensor([float(w[k]) for k in names]), 1, generator=gen))]
-    if n <= max_tokens and (max_atoms <= 0 or int(feats["ref_mask"].sum()) <= max_atoms):
+    drawn = strategy or _draw(w, gen)  # drawn even when nothing is cut, so the random stream does not depend on the size
+    atoms = _atoms_per_token(feats)
+    if n <= max_tokens and (max_atoms <= 0 or int(atoms.sum()) <= max_atoms):
         return feats, "none", None
-    if strategy == "contiguous":
-        keep = contiguous_crop(feats["asym_id"], max_tokens, gen)
-    else:
-        coords, valid = _center_coords(feats)
-        keep = spatial_crop(coords.float(), valid, feats["asym_id"], max_tokens, gen, strategy == "spatial_interface")
-    keep = apply_atom_budget(keep, feats["ref_mask"], max_atoms)
-    return select_tokens(feats, keep), strategy, keep
+    coords, resolved = _center_coords(feats)
+    coords = coords.float()
+    attempts = max_attempts if int(resolved.sum()) >= min_resolved else 1
+    keep, used = None, drawn
+    for attempt in range(max(1, attempts)):
+        used = drawn if attempt == 0 else (strategy or _draw(w, gen))
+        if used == "contiguous":
+            keep = contiguous_crop(feats["asym_id"], max_tokens, gen, atoms, max_atoms)
+        else:
+            keep = spatial_crop(coords, resolved, feats["asym_id"], max_tokens, gen, used == "spatial_interface", atoms,
+                                max_atoms, anchor)  # fmt: skip
+        if int(resolved[keep].sum()) >= min_resolved:
+            break
+    return select_tokens(feats, keep), used, keep

@@ -342,7 +342,10 @@ def featurize_record(st, rec, load_msa, *, max_tokens: int = 384, max_atoms: int
     # crop first, then read alignments only for the chains (and columns) that survived
     feats = featurize_structure(sub, None, max_msa_rows=max_msa_rows, with_msa=False)
     chain_cols = feats.pop("_chain_cols")
-    feats, strategy, kept = cropper.crop(feats, max_tokens, max_atoms, gen, crop_weights, return_keep=True)
+    # the anchor in the numbering of the featurised sub-structure (chains renumbered in the order of old_ids)
+    new_of_old = {c: k for k, c in enumerate(old_ids)}
+    crop_anchor = (anchor[0], new_of_old.get(anchor[1], -1), new_of_old.get(anchor[2], -1)) if anchor[1] in new_of_old else None
+    feats, strategy, kept = cropper.crop(feats, max_tokens, max_atoms, gen, crop_weights, return_keep=True, anchor=crop_anchor)
     feats, read, skipped = attach_cropped_msa(feats, kept, chain_cols, lambda a: load_msa(rec.chains[old_ids[a]]),
                                               max_msa_rows=max_msa_rows)  # fmt: skip
     feats = rotate_reference_conformers(feats, gen)

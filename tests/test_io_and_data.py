@@ -211,6 +211,60 @@ def test_crops_keep_consistency():
     assert used == "none" and same is f
 
 
+def test_crop_seeding_budgets_and_resolved_tokens():
+    """Spatial crops on a constructed geometry: unresolved tokens are never selected, the anchor chain / interface
+    decides where the seed falls, the atom budget cuts the farthest tokens (not the last by index), a crop with too
+    few resolved tokens is redrawn, and the contiguous crop meets its budget."""
+    n_a, n_b, n_c = 40, 40, 30
+    n = n_a + n_b + n_c
+    # three straight chains: A along x at y=0, B parallel at y=8 (touches A everywhere), C far away at y=200
+    xyz = torch.zeros(n, 3)
+    xyz[:n_a, 0] = torch.arange(n_a) * 3.8
+    xyz[n_a : n_a + n_b, 0] = torch.arange(n_b) * 3.8
+    xyz[n_a : n_a + n_b, 1] = 8.0
+    xyz[n_a + n_b :, 0] = torch.arange(n_c) * 3.8
+    xyz[n_a + n_b :, 1] = 200.0
+    asym = torch.cat([torch.zeros(n_a), torch.ones(n_b), torch.full((n_c,), 2)]).long()
+    resolved = torch.ones(n, dtype=torch.bool)
+    resolved[5:15] = False  # an unresolved stretch inside chain A
+    atoms = torch.full((n,), 5)
+    g = lambda s: torch.Generator().manual_seed(s)  # noqa: E731
+
+    for seed in range(6):
+        keep = cropper.spatial_crop(xyz, resolved, asym, 24, g(seed), False, atoms, 0, anchor=("chain", 2, -1))
+        assert (asym[keep] == 2).all() and len(keep) == 24  # seeded in the anchor chain, which is far from the others
+        keep = cropper.spatial_crop(xyz, resolved, asym, 24, g(seed), True, atoms, 0, anchor=("interface", 0, 1))
+        assert set(asym[keep].tolist()) == {0, 1} and resolved[keep].all()
+        keep = cropper.spatial_crop(xyz, resolved, asym, 30, g(seed), True, atoms, 0)
+        assert 2 not in asym[keep].tolist()  # chain C touches nothing, so it cannot hold an interface seed
+    # atom budget: 10 tokens x 5 atoms fit into 50 atoms, and they are the 10 nearest to the seed
+    keep = cropper.spatial_crop(xyz, resolved, asym, 24, g(1), False, atoms, 50, anchor=("chain", 2, -1))
+    full = cropper.spatial_crop(xyz, resolved, asym, 24, g(1), False, atoms, 0, anchor=("chain", 2, -1))
+    assert len(keep) == 10 and set(keep.tolist()) <= set(full.tolist())
+    span = xyz[keep, 0].max() - xyz[keep, 0].min()
+    assert float(span) <= 3.8 * 9 + 1e-3  # ten consecutive residues around the seed
+    # a large token does not get skipped in favour of smaller ones farther away
+    order = torch.tensor([3, 1, 2, 0])
+    assert cropper._within_budgets(order, torch.tensor([1, 1, 9, 1]), 4, 4).tolist() == [1, 3]
+    # contiguous: exactly the budget when the chains can fill it; atom budget in collection order
+    for seed in range(4):
+        keep = cropper.contiguous_crop(asym, 64, g(seed), atoms, 0)
+        assert len(keep) == 64 and keep.tolist() == sorted(keep.tolist())
+        assert len(cropper.contiguous_crop(asym, 64, g(seed), atoms, 100)) == 20
+
+    # through crop(): features with a ground truth whose chain B is entirely unresolved
+    f = synthetic_complex([("protein", 40), ("protein", 40), ("protein", 30)], num_msa=4, num_templates=0, seed=2)
+    f["atom_gt_mask"] = f["atom_gt_mask"].clone()
+    f["atom_gt_mask"][40:80] = False
+    for seed in range(5):
+        c, used, keep = cropper.crop(f, 32, 0, g(seed), strategy="spatial", return_keep=True)
+        assert not ((keep >= 40) & (keep < 80)).any() and c["res_type"].shape[0] == 32
+    # contiguous crops may land on the unresolved chain; the retry makes sure enough resolved tokens are in the crop
+    for seed in range(8):
+        c, used, keep = cropper.crop(f, 16, 0, g(seed), weights={"contiguous": 1.0, "spatial": 0.0, "spatial_interface": 0.0}, return_keep=True)
+        assert int(f["atom_gt_mask"][keep].any(-1).sum()) >= cropper.MIN_RESOLVED
+
+
 def test_sampler_resume_sharding_collate_pack(tmp_path):
     w = [1.0, 3.0, 0.5, 2.0]
     full = samplers.WeightedClusterSampler(w, seed=2, rank=0, world_size=1, block=8)
