@@ -265,31 +265,23 @@ class StructureDataset:
         self.records = [r for r in load_manifest(os.path.join(root, "manifest.json")) if any(c.valid for c in r.chains)]
         self.records = apply_date_cutoff(self.records, cutoff_date, keep_after)
         self.msa_read = self.msa_skipped = 0  # alignments opened / never opened because their chain was cropped away
+        self._anchors = None
 
     def __len__(self):
         return len(self.records)
 
-    def weights(self) -> list[float]:
-        from . import const
-        from .samplers import example_weight
+    def anchor_tables(self):
+        if self._anchors is None:
+            from .samplers import anchor_tables
 
-        sizes: dict = {}
-        for r in self.records:
-            for c in r.chains:
-                if c.valid:
-                    sizes[c.cluster_id] = sizes.get(c.cluster_id, 0) + 1
-        kind = {const.MOL_PROTEIN: "protein", const.MOL_DNA: "nucleic", const.MOL_RNA: "nucleic", const.MOL_NONPOLYMER: "ligand"}
-        out = []
-        for r in self.records:
-            chains = [{"type": kind[c.mol_type], "cluster_size": sizes[c.cluster_id]} for c in r.chains if c.valid]
-            faces = []
-            for f in r.interfaces:
-                if f.valid:
-                    a, b = r.chains[f.chain_1], r.chains[f.chain_2]
-                    t = "ligand" if "ligand" in (kind[a.mol_type], kind[b.mol_type]) else kind[a.mol_type]
-                    faces.append({"type": t, "cluster_size": min(sizes[a.cluster_id], sizes[b.cluster_id])})
-            out.append(example_weight(chains, faces))
-        return out
+            self._anchors = anchor_tables(self.records)
+        return self._anchors
+
+    def weights(self) -> list[float]:
+        """Record marginal of the AF3 weighting: the sum of the record's chain and interface anchor weights."""
+        from .samplers import record_weights
+
+        return record_weights(self.anchor_tables())
 
     def _msa(self, chain):
         from .parse.a3m import msa_from_a3m_file
@@ -311,14 +303,17 @@ class StructureDataset:
             st, rec, lambda chain: self._msa(chain), max_tokens=self.max_tokens, max_atoms=self.max_atoms,
             crop_weights=self.crop_weights, max_chains=self.max_chains, max_msa_rows=self.max_msa_rows,
             seed=self.seed * 7_654_321 + i, is_distillation=self.is_distillation,
+            anchors=self.anchor_tables()[i % len(self.records)],
         )  # fmt: skip
         self.msa_read, self.msa_skipped = self.msa_read + read, self.msa_skipped + skipped
         return feats
 
 
 def featurize_record(st, rec, load_msa, *, max_tokens: int = 384, max_atoms: int = 0, crop_weights: dict | None = None,
-                     max_chains: int = 20, max_msa_rows: int = 16384, seed: int = 0, is_distillation: bool = False):
-    """One training example from a stored structure and its manifest record: pick the anchor chain or interface,
+                     max_chains: int = 20, max_msa_rows: int = 16384, seed: int = 0, is_distillation: bool = False,
+                     anchors=None):
+    """One training example from a stored structure and its manifest record: pick the anchor chain or interface
+    (in proportion to the anchor weights of ``anchors = (anchor list, weights)`` when given, else uniformly),
     pre-crop large assemblies to the chains around it, featurise, crop to the token budget, read the alignments of
     what survived (``load_msa(chain_info)`` -> ``MSA`` or ``None``), rotate the reference conformers. Returns the
     features and the numbers of alignments read and skipped."""
@@ -331,7 +326,9 @@ def featurize_record(st, rec, load_msa, *, max_tokens: int = 384, max_atoms: int
     rng = random.Random(seed)
     valid = [c for c in rec.chains if c.valid]
     faces = [f for f in rec.interfaces if f.valid]
-    if faces and rng.random() < 0.5:
+    if anchors is not None and anchors[0]:
+        anchor = rng.choices(anchors[0], weights=anchors[1], k=1)[0]
+    elif faces and rng.random() < 0.5:
         f = rng.choice(faces)
         anchor = ("interface", f.chain_1, f.chain_2)
     else:

@@ -23,6 +23,62 @@ def example_weight(chains: list[dict], interfaces: list[dict] | None = None) -> 
     return max(w, 1e-8)
 
 
+def _alpha(mol_type: int) -> float:
+    from . import const
+
+    if mol_type == const.MOL_PROTEIN:
+        return ALPHA["protein"]
+    if mol_type in (const.MOL_RNA, const.MOL_DNA):
+        return ALPHA["nucleic"]
+    if mol_type == const.MOL_NONPOLYMER:
+        return ALPHA["ligand"]
+    return 1.0
+
+
+def anchor_tables(records) -> list[tuple[list[tuple[str, int, int]], list[float]]]:
+    """Per manifest record, the crop anchors it offers and their weights ``w_a`` (AF3 SI 2.5.1-2.5.3; reference:
+    data/sample/weighted.py:100-196). An anchor is ``("chain", chain_id, -1)`` with ``w = beta_chain * alpha(type) /
+    |chain cluster|`` or ``("interface", chain_1, chain_2)`` with ``w = beta_interface * (alpha_1 + alpha_2) /
+    |interface cluster|``; an interface cluster is the unordered pair of the two chains' clusters, and cluster sizes
+    count valid members over the whole record list. Drawing a record by the sum of its ``w_a`` (``record_weights``)
+    and then one of its anchors in proportion to ``w_a`` equals drawing from the flat table of all anchors.
+    """
+    chain_count: dict = {}
+    face_count: dict = {}
+    for r in records:
+        by_id = {c.chain_id: c for c in r.chains}
+        for c in r.chains:
+            if c.valid:
+                chain_count[c.cluster_id] = chain_count.get(c.cluster_id, 0) + 1
+        for f in r.interfaces:
+            a, b = by_id.get(f.chain_1), by_id.get(f.chain_2)
+            if f.valid and a is not None and b is not None and a.valid and b.valid:
+                key = frozenset((a.cluster_id, b.cluster_id))
+                face_count[key] = face_count.get(key, 0) + 1
+    out = []
+    for r in records:
+        by_id = {c.chain_id: c for c in r.chains}
+        anchors, weights = [], []
+        for c in r.chains:
+            if c.valid:
+                anchors.append(("chain", int(c.chain_id), -1))
+                weights.append(BETA_CHAIN * _alpha(c.mol_type) / max(1, chain_count.get(c.cluster_id, 1)))
+        for f in r.interfaces:
+            a, b = by_id.get(f.chain_1), by_id.get(f.chain_2)
+            if f.valid and a is not None and b is not None and a.valid and b.valid:
+                size = max(1, face_count.get(frozenset((a.cluster_id, b.cluster_id)), 1))
+                anchors.append(("interface", int(a.chain_id), int(b.chain_id)))
+                weights.append(BETA_INTERFACE * (_alpha(a.mol_type) + _alpha(b.mol_type)) / size)
+        out.append((anchors, weights))
+    return out
+
+
+def record_weights(tables) -> list[float]:
+    """The record marginal of ``anchor_tables``: the sum of a record's anchor weights (a record without a valid anchor
+    keeps a vanishing weight so that the sampler's distribution stays defined)."""
+    return [max(float(sum(w)), 1e-12) for _, w in tables]
+
+
 class WeightedClusterSampler:
     def __init__(self, weights, seed: int = 0, rank: int = 0, world_size: int = 1, block: int = 4096):
         self.weights = torch.as_tensor(weights, dtype=torch.double)

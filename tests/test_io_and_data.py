@@ -265,6 +265,34 @@ def test_crop_seeding_budgets_and_resolved_tokens():
         assert int(f["atom_gt_mask"][keep].any(-1).sum()) >= cropper.MIN_RESOLVED
 
 
+def test_anchor_weights_follow_cluster_sizes():
+    """Chain anchors weigh beta_chain * alpha / |chain cluster|, interface anchors beta_interface * (alpha_1 + alpha_2) /
+    |pair of chain clusters|; the record weight is their sum; invalid chains and interfaces offer no anchor."""
+    from deepfold3_dev_b200.data import const
+    from deepfold3_dev_b200.data.types import ChainInfo, InterfaceInfo, Record
+
+    def chain(i, mol, cluster, valid=True):
+        return ChainInfo(i, "ABCDEFG"[i], mol, cluster, f"m{i}", 50, valid=valid)
+
+    P, R, L = const.MOL_PROTEIN, const.MOL_RNA, const.MOL_NONPOLYMER
+    recs = [
+        Record("r0", [chain(0, P, "c1"), chain(1, P, "c2"), chain(2, L, "lig")], [InterfaceInfo(0, 1), InterfaceInfo(0, 2), InterfaceInfo(1, 2, valid=False)]),
+        Record("r1", [chain(0, P, "c1"), chain(1, P, "c2")], [InterfaceInfo(1, 0)]),  # the same pair of clusters, other order
+        Record("r2", [chain(0, R, "rna"), chain(1, P, "c1", valid=False)], [InterfaceInfo(0, 1)]),
+        Record("r3", [chain(0, P, "c9", valid=False)], []),
+    ]
+    tables = samplers.anchor_tables(recs)
+    a0 = dict(zip(tables[0][0], tables[0][1]))
+    assert a0[("chain", 0, -1)] == pytest.approx(0.5 * 3.0 / 2)  # cluster c1 has two valid members (r2's copy is invalid)
+    assert a0[("chain", 2, -1)] == pytest.approx(0.5 * 1.0 / 1)
+    assert a0[("interface", 0, 1)] == pytest.approx(1.0 * (3.0 + 3.0) / 2)  # {c1, c2} occurs in r0 and r1
+    assert a0[("interface", 0, 2)] == pytest.approx(1.0 * (3.0 + 1.0) / 1) and ("interface", 1, 2) not in a0
+    assert tables[2][0] == [("chain", 0, -1)] and tables[2][1] == [pytest.approx(0.5 * 3.0)]  # interface with an invalid chain: no anchor
+    assert tables[3] == ([], [])
+    w = samplers.record_weights(tables)
+    assert w[0] == pytest.approx(sum(tables[0][1])) and w[3] < 1e-9 and w[0] > w[1] > w[2] * 0.99
+
+
 def test_sampler_resume_sharding_collate_pack(tmp_path):
     w = [1.0, 3.0, 0.5, 2.0]
     full = samplers.WeightedClusterSampler(w, seed=2, rank=0, world_size=1, block=8)
