@@ -69,8 +69,10 @@ def build_training_stream(tc, mc, info, datasets, data_dir=None, synthetic=False
             kw = {k: v for k, v in extra.get(path, {}).items() if v}
             if "cutoff_date" in kw and kw.get("format", "df3") == "df3" and not os.path.isdir(os.path.join(path, "structures")):
                 kw.pop("cutoff_date")  # feature directories carry no dates; the cut-off is applied when they are prepared
+            d = mc.data
             parts.append(ds.open_dataset(path, max_tokens=tc.max_tokens, max_atoms=tc.max_atoms, is_distillation=distill,
-                                         seed=tc.seed, **kw))  # fmt: skip
+                                         seed=tc.seed, atomize_prob=d.atomize_prob, atomize_source=d.atomize_source,
+                                         atomize_max_residues=d.atomize_max_residues, **kw))  # fmt: skip
             logging.getLogger(__name__).info("dataset %s: %d examples from %s", name, len(parts[-1]), path)
         samplers = [WeightedClusterSampler(p.weights(), tc.seed + 17 * i, info.rank, info.world_size) for i, p in enumerate(parts)]
         sampler = MultiDatasetSampler(samplers, [len(p) for p in parts], weights, tc.seed)

@@ -70,6 +70,50 @@ RESIDUE_ATOMS.update(
         "N": _RIBOSE,
     }
 )
+# Covalent bonds between the heavy atoms of the standard residues (textbook chemistry; the component dictionary lists
+# the same). Needed when a standard residue is tokenised per atom: its atom tokens are then joined in the token bond
+# matrix like those of a ligand. Linking atoms to the neighbouring residues: C -> N (peptides), O3' -> P (nucleic acids).
+_BACKBONE_BONDS = (("N", "CA"), ("CA", "C"), ("C", "O"))
+_SIDE_CHAIN_BONDS: dict[str, tuple[tuple[str, str], ...]] = {
+    "ALA": (), "GLY": (), "UNK": (),
+    "ARG": (("CB", "CG"), ("CG", "CD"), ("CD", "NE"), ("NE", "CZ"), ("CZ", "NH1"), ("CZ", "NH2")),
+    "ASN": (("CB", "CG"), ("CG", "OD1"), ("CG", "ND2")),
+    "ASP": (("CB", "CG"), ("CG", "OD1"), ("CG", "OD2")),
+    "CYS": (("CB", "SG"),),
+    "GLN": (("CB", "CG"), ("CG", "CD"), ("CD", "OE1"), ("CD", "NE2")),
+    "GLU": (("CB", "CG"), ("CG", "CD"), ("CD", "OE1"), ("CD", "OE2")),
+    "HIS": (("CB", "CG"), ("CG", "ND1"), ("CG", "CD2"), ("ND1", "CE1"), ("CD2", "NE2"), ("CE1", "NE2")),
+    "ILE": (("CB", "CG1"), ("CB", "CG2"), ("CG1", "CD1")),
+    "LEU": (("CB", "CG"), ("CG", "CD1"), ("CG", "CD2")),
+    "LYS": (("CB", "CG"), ("CG", "CD"), ("CD", "CE"), ("CE", "NZ")),
+    "MET": (("CB", "CG"), ("CG", "SD"), ("SD", "CE")),
+    "PHE": (("CB", "CG"), ("CG", "CD1"), ("CG", "CD2"), ("CD1", "CE1"), ("CD2", "CE2"), ("CE1", "CZ"), ("CE2", "CZ")),
+    "PRO": (("CB", "CG"), ("CG", "CD"), ("CD", "N")),
+    "SER": (("CB", "OG"),),
+    "THR": (("CB", "OG1"), ("CB", "CG2")),
+    "TRP": (("CB", "CG"), ("CG", "CD1"), ("CG", "CD2"), ("CD1", "NE1"), ("NE1", "CE2"), ("CD2", "CE2"), ("CD2", "CE3"),
+            ("CE2", "CZ2"), ("CE3", "CZ3"), ("CZ2", "CH2"), ("CZ3", "CH2")),
+    "TYR": (("CB", "CG"), ("CG", "CD1"), ("CG", "CD2"), ("CD1", "CE1"), ("CD2", "CE2"), ("CE1", "CZ"), ("CE2", "CZ"), ("CZ", "OH")),
+    "VAL": (("CB", "CG1"), ("CB", "CG2")),
+}  # fmt: skip
+_SUGAR_BONDS = (("P", "OP1"), ("P", "OP2"), ("P", "O5'"), ("O5'", "C5'"), ("C5'", "C4'"), ("C4'", "O4'"), ("C4'", "C3'"),
+                ("C3'", "O3'"), ("C3'", "C2'"), ("C2'", "C1'"), ("C1'", "O4'"))  # fmt: skip
+_PURINE_BONDS = (("C1'", "N9"), ("N9", "C8"), ("C8", "N7"), ("N7", "C5"), ("C5", "C6"), ("C6", "N1"), ("N1", "C2"), ("C2", "N3"),
+                 ("N3", "C4"), ("C4", "C5"), ("C4", "N9"))  # fmt: skip
+_PYRIMIDINE_BONDS = (("C1'", "N1"), ("N1", "C2"), ("C2", "O2"), ("C2", "N3"), ("N3", "C4"), ("C4", "C5"), ("C5", "C6"), ("C6", "N1"))
+_BASE_BONDS = {"A": _PURINE_BONDS + (("C6", "N6"),), "G": _PURINE_BONDS + (("C6", "O6"), ("C2", "N2")),
+               "C": _PYRIMIDINE_BONDS + (("C4", "N4"),), "U": _PYRIMIDINE_BONDS + (("C4", "O4"),),
+               "T": _PYRIMIDINE_BONDS + (("C4", "O4"), ("C5", "C7"))}  # fmt: skip
+RESIDUE_BONDS: dict[str, tuple[tuple[str, str], ...]] = {
+    name: _BACKBONE_BONDS + ((("CA", "CB"),) if name != "GLY" else ()) + side for name, side in _SIDE_CHAIN_BONDS.items()
+}
+for _base in "AGCU":
+    RESIDUE_BONDS[_base] = _SUGAR_BONDS + (("C2'", "O2'"),) + _BASE_BONDS[_base]
+for _base in "AGCT":
+    RESIDUE_BONDS["D" + _base] = _SUGAR_BONDS + _BASE_BONDS[_base]
+RESIDUE_BONDS["N"] = _SUGAR_BONDS
+POLYMER_LINK = {MOL_PROTEIN: ("C", "N"), MOL_RNA: ("O3'", "P"), MOL_DNA: ("O3'", "P")}  # (atom of residue i, atom of residue i + 1)
+
 ELEMENT_NUMBER = {"H": 1, "C": 6, "N": 7, "O": 8, "F": 9, "P": 15, "S": 16, "CL": 17, "SE": 34, "BR": 35, "I": 53,
                   "MG": 12, "ZN": 30, "FE": 26, "CA": 20, "NA": 11, "K": 19, "MN": 25, "CU": 29, "CO": 27, "NI": 28}  # fmt: skip
 

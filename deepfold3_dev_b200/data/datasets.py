@@ -252,12 +252,14 @@ class StructureDataset:
 
     def __init__(self, root: str, max_tokens: int = 384, max_atoms: int = 0, crop_weights: dict | None = None,
                  is_distillation: bool = False, seed: int = 0, max_chains: int = 20, max_msa_rows: int = 16384,
-                 msa_dir: str | None = None, cutoff_date: str = "", keep_after: bool = False):  # fmt: skip
+                 msa_dir: str | None = None, cutoff_date: str = "", keep_after: bool = False, atomize_prob: float = 0.0,
+                 atomize_source: str = "random", atomize_max_residues: int = 0):  # fmt: skip
         from .types import load_manifest
 
         self.root, self.max_tokens, self.max_atoms = root, max_tokens, max_atoms
         self.crop_weights, self.is_distillation, self.seed = crop_weights, is_distillation, seed
         self.max_chains, self.max_msa_rows = max_chains, max_msa_rows
+        self.atomize = {"atomize_prob": atomize_prob, "atomize_source": atomize_source, "atomize_max_residues": atomize_max_residues}
         self.msa_dir = msa_dir or os.path.join(root, "msa")
         packs.register(root)  # structures/ and msa/ may live in {root}/_pack
         if msa_dir:
@@ -303,7 +305,7 @@ class StructureDataset:
             st, rec, lambda chain: self._msa(chain), max_tokens=self.max_tokens, max_atoms=self.max_atoms,
             crop_weights=self.crop_weights, max_chains=self.max_chains, max_msa_rows=self.max_msa_rows,
             seed=self.seed * 7_654_321 + i, is_distillation=self.is_distillation,
-            anchors=self.anchor_tables()[i % len(self.records)],
+            anchors=self.anchor_tables()[i % len(self.records)], **self.atomize,
         )  # fmt: skip
         self.msa_read, self.msa_skipped = self.msa_read + read, self.msa_skipped + skipped
         return feats
@@ -311,7 +313,7 @@ class StructureDataset:
 
 def featurize_record(st, rec, load_msa, *, max_tokens: int = 384, max_atoms: int = 0, crop_weights: dict | None = None,
                      max_chains: int = 20, max_msa_rows: int = 16384, seed: int = 0, is_distillation: bool = False,
-                     anchors=None):
+                     anchors=None, atomize_prob: float = 0.0, atomize_source: str = "random", atomize_max_residues: int = 0):
     """One training example from a stored structure and its manifest record: pick the anchor chain or interface
     (in proportion to the anchor weights of ``anchors = (anchor list, weights)`` when given, else uniformly),
     pre-crop large assemblies to the chains around it, featurise, crop to the token budget, read the alignments of
@@ -337,14 +339,15 @@ def featurize_record(st, rec, load_msa, *, max_tokens: int = 384, max_atoms: int
     old_ids = sorted(keep)
     sub = st.select_chains(old_ids)
     # crop first, then read alignments only for the chains (and columns) that survived
-    feats = featurize_structure(sub, None, max_msa_rows=max_msa_rows, with_msa=False)
-    chain_cols = feats.pop("_chain_cols")
+    atomize = _residues_to_atomize(sub, rng, atomize_prob, atomize_source, atomize_max_residues)
+    feats = featurize_structure(sub, None, max_msa_rows=max_msa_rows, with_msa=False, atomize=atomize)
+    chain_cols, token_col, chain_len = feats.pop("_chain_cols"), feats.pop("_token_col"), feats.pop("_chain_len")
     # the anchor in the numbering of the featurised sub-structure (chains renumbered in the order of old_ids)
     new_of_old = {c: k for k, c in enumerate(old_ids)}
     crop_anchor = (anchor[0], new_of_old.get(anchor[1], -1), new_of_old.get(anchor[2], -1)) if anchor[1] in new_of_old else None
     feats, strategy, kept = cropper.crop(feats, max_tokens, max_atoms, gen, crop_weights, return_keep=True, anchor=crop_anchor)
     feats, read, skipped = attach_cropped_msa(feats, kept, chain_cols, lambda a: load_msa(rec.chains[old_ids[a]]),
-                                              max_msa_rows=max_msa_rows)  # fmt: skip
+                                              max_msa_rows=max_msa_rows, token_col=token_col, chain_len=chain_len)  # fmt: skip
     feats = rotate_reference_conformers(feats, gen)
     from .symmetry import symmetry_features
 
@@ -355,6 +358,45 @@ def featurize_record(st, rec, load_msa, *, max_tokens: int = 384, max_atoms: int
     feats["_record_id"] = rec.id
     feats["_crop"] = strategy
     return feats, read, skipped
+
+
+def _residues_to_atomize(st, rng, prob: float, source: str = "random", max_residues: int = 0, interface_distance: float = 15.0) -> set[int]:
+    """Rows of ``st.residues`` to tokenise per atom in this example: every standard polymer residue with more than one
+    atom is picked with probability ``prob`` (``source="interface"``: only residues whose centre lies within
+    ``interface_distance`` of a residue of another chain), at most ``max_residues`` of them (0: no cap). Training only;
+    the crop that follows counts the extra tokens (reference: data/tokenize/atomize.py:109-131)."""
+    if prob <= 0.0:
+        return set()
+    import numpy as np
+
+    from . import const
+
+    if source not in ("random", "interface"):
+        raise ValueError(f"unknown atomize_source {source!r} (random | interface)")
+    eligible, centres, owners = [], [], []
+    xyz = st.coords()
+    for c in st.chains:
+        if int(c["mol_type"]) == const.MOL_NONPOLYMER:
+            continue
+        first = int(c["res_idx"])
+        for k, r in enumerate(st.residues[first : first + int(c["res_num"])]):
+            a0, n = int(r["atom_idx"]), int(r["atom_num"])
+            present = st.atoms["is_present"][a0 : a0 + n]
+            if bool(r["is_standard"]) and n > 1 and present.any():
+                eligible.append(first + k)
+                centres.append(xyz[a0 : a0 + n][present].mean(0))
+                owners.append(int(c["asym_id"]))
+    if not eligible:
+        return set()
+    if source == "interface":
+        pts, own = np.asarray(centres), np.asarray(owners)
+        d = np.linalg.norm(pts[:, None] - pts[None], axis=-1)
+        touch = ((d < interface_distance) & (own[:, None] != own[None])).any(-1)
+        eligible = [e for e, t in zip(eligible, touch) if t]
+    picked = [e for e in eligible if rng.random() < prob]
+    if max_residues > 0 and len(picked) > max_residues:
+        picked = rng.sample(picked, max_residues)
+    return set(picked)
 
 
 def open_dataset(path: str, format: str = "df3", of3_cache_dir: str = "", **kw):
@@ -374,4 +416,6 @@ def open_dataset(path: str, format: str = "df3", of3_cache_dir: str = "", **kw):
         raise ValueError(f"dataset format must be df3|of3|of3pdb, got {format!r}")
     if paths.is_prepared_root(path):
         return StructureDataset(path, **kw)
+    for key in ("atomize_prob", "atomize_source", "atomize_max_residues"):
+        kw.pop(key, None)  # stored feature files are already tokenised
     return FeatureDirDataset(path, **kw)

@@ -134,21 +134,23 @@ def _template_features(feats, chain_cols, chains, max_templates: int = 4, mmcif_
     merged = None
     for (s, e), c in zip(chain_cols, chains):
         hits = getattr(c, "templates", None)
-        if not hits or e - s != len(getattr(c, "sequence", "")):
+        L = len(getattr(c, "sequence", ""))
+        if not hits or L == 0:
             continue
         loaded = tpl.load_json_templates(hits, hits[0].get("_base_dir", "."), max_templates, mmcif_dir, max_date)
         if not loaded:
             continue
-        part = tpl.template_features(e - s, loaded, max_templates, token_offset=s, num_tokens=N)
+        # features per residue of the chain, then one copy per token of that residue (a modified residue is several
+        # atom tokens that all point at the residue's template column)
+        per_res = tpl.template_features(L, loaded, max_templates)
+        col = feats["residue_index"][s:e].clamp(0, L - 1)
         if merged is None:
-            merged = part
-            continue
-        cols = slice(s, e)
-        for k, v in part.items():
+            merged = tpl.template_features(0, [], max_templates, num_tokens=N)
+        for k, v in per_res.items():
             if k == "template_mask":
                 merged[k] = torch.maximum(merged[k], v)
             else:
-                merged[k][:, cols] = v[:, cols]
+                merged[k][:, s:e] = v.index_select(1, col)
     return merged or {}
 
 
@@ -255,12 +257,25 @@ def _msa_features(feats, chain_cols, chains, max_rows: int, msa_pairing: str = "
     query = feats["res_type"].clone()
     rows, dels = [query.numpy()], [np.zeros(N, dtype=np.int64)]
     # paired rows first (row i of every chain that has a paired alignment), then per-chain blocks
-    paired = [(cols, a3m_mod.parse_a3m(c.paired_msa)) for cols, c in zip(chain_cols, chains)
-              if getattr(c, "paired_msa", None) and cols[1] - cols[0] == len(getattr(c, "sequence", ""))]  # fmt: skip
+    # a chain's alignment has one column per residue; its tokens (one per residue, or several atom tokens for a modified
+    # residue) read the column of their residue
+    def col(s, e):
+        return feats["residue_index"][s:e].numpy()
+
+    def usable(c, cols):
+        return bool(getattr(c, "sequence", "")) and int(feats["mol_type"][cols[0]]) != const.MOL_NONPOLYMER
+
+    def width_ok(m, c):
+        return len(m.sequences) > 0 and len(m.sequences[0]) == len(c.sequence)
+
+    paired = [(cols, a3m_mod.parse_a3m(c.paired_msa), c) for cols, c in zip(chain_cols, chains)
+              if getattr(c, "paired_msa", None) and usable(c, cols)]  # fmt: skip
+    paired = [(cols, m) for cols, m, c in paired if width_ok(m, c)]
     if len(paired) <= 1 and msa_pairing in ("auto", "species"):
         # no explicit paired alignments: pair the unpaired ones by species when several distinct chains carry headers
-        cand = [(cols, a3m_mod.parse_a3m(c.unpaired_msa, dedup=False)) for cols, c in zip(chain_cols, chains)
-                if getattr(c, "unpaired_msa", None) and cols[1] - cols[0] == len(getattr(c, "sequence", ""))]  # fmt: skip
+        cand = [(cols, a3m_mod.parse_a3m(c.unpaired_msa, dedup=False), c) for cols, c in zip(chain_cols, chains)
+                if getattr(c, "unpaired_msa", None) and usable(c, cols)]  # fmt: skip
+        cand = [(cols, m) for cols, m, c in cand if width_ok(m, c)]
         if len({m.sequences[0] for _, m in cand}) > 1:
             from .msa.pairing import pair_by_species
 
@@ -273,20 +288,22 @@ def _msa_features(feats, chain_cols, chains, max_rows: int, msa_pairing: str = "
             row, d = np.full(N, const.MSA_GAP, dtype=np.int64), np.zeros(N, dtype=np.int64)
             for (s, e), m in paired:
                 mt = int(feats["mol_type"][s])
-                row[s:e] = a3m_mod.encode_sequence(m.sequences[r], mt)
-                d[s:e] = m.deletions[r]
+                row[s:e] = np.asarray(a3m_mod.encode_sequence(m.sequences[r], mt))[col(s, e)]
+                d[s:e] = np.asarray(m.deletions[r])[col(s, e)]
             rows.append(row)
             dels.append(d)
     for (s, e), c in zip(chain_cols, chains):
         text = getattr(c, "unpaired_msa", None)
-        if not text or e - s != len(getattr(c, "sequence", "")):
-            continue  # atomised chains and chains without an alignment contribute only the query row
+        if not text or not usable(c, (s, e)):
+            continue  # ligands and chains without an alignment contribute only the query row
         m = a3m_mod.parse_a3m(text, max_rows=max_rows)
+        if len(m.sequences[0]) != len(c.sequence):
+            continue  # an alignment of another sequence: its columns mean nothing here
         mt = int(feats["mol_type"][s])
         for r in range(1, len(m)):
             row, d = np.full(N, const.MSA_GAP, dtype=np.int64), np.zeros(N, dtype=np.int64)
-            row[s:e] = a3m_mod.encode_sequence(m.sequences[r], mt)
-            d[s:e] = m.deletions[r]
+            row[s:e] = np.asarray(a3m_mod.encode_sequence(m.sequences[r], mt))[col(s, e)]
+            d[s:e] = np.asarray(m.deletions[r])[col(s, e)]
             rows.append(row)
             dels.append(d)
             if len(rows) >= max_rows:

@@ -313,7 +313,9 @@ class OF3StructureDataset:
     def __init__(self, of3_dir: str, cache_dir: str | None = None, msa_dir: str | None = None, max_tokens: int = 384,
                  max_atoms: int = 4096, max_msa_rows: int = 1024, max_release_date: str | None = None,
                  max_resolution: float | None = None, seed: int = 0, crop_weights: dict | None = None,
-                 is_distillation: bool = False):  # fmt: skip
+                 is_distillation: bool = False, atomize_prob: float = 0.0, atomize_source: str = "random",
+                 atomize_max_residues: int = 0):  # fmt: skip
+        self.atomize = {"atomize_prob": atomize_prob, "atomize_source": atomize_source, "atomize_max_residues": atomize_max_residues}
         structures = os.path.join(of3_dir, "structures")
         self.items = scan_structures(structures if os.path.isdir(structures) else of3_dir)
         self.cache = ColumnarCache(cache_dir) if cache_dir else None
@@ -352,7 +354,8 @@ class OF3StructureDataset:
                                         "chains": {c["chain_name"]: c for c in e["chains"]}})  # fmt: skip
         feats, read, skipped = featurize_record(st, rec, self._msa, max_tokens=self.max_tokens, max_atoms=self.max_atoms,
                                                 crop_weights=self.crop_weights, max_msa_rows=self.max_msa_rows,
-                                                seed=self.seed * 7_654_321 + index, is_distillation=self.is_distillation)  # fmt: skip
+                                                seed=self.seed * 7_654_321 + index, is_distillation=self.is_distillation,
+                                                **self.atomize)  # fmt: skip
         self.msa_read, self.msa_skipped = self.msa_read + read, self.msa_skipped + skipped
         return feats
 

@@ -197,6 +197,44 @@ def test_job_dialect_details(tmp_path, caplog):
     assert ji.detect_dialect({"dialect": "Protenix", "sequences": []}) == "protenix"
 
 
+def test_modified_residue_keeps_alignment_and_template_columns(tmp_path):
+    """A chain with a modified residue is tokenised per atom at that residue; every token still reads the alignment and
+    template column of its residue (the chain must not fall back to a query-only alignment)."""
+    from test_prepare import _mini_cif
+
+    from deepfold3_dev_b200.data import ref_conformers
+
+    ref_conformers._TABLE["SEP"] = {"atoms": ["N", "CA", "C", "O", "CB", "OG", "P", "O1P", "O2P", "O3P"], "elements": [7, 6, 6, 8, 6, 8, 15, 8, 8, 8],
+                                    "charges": [0] * 10, "coords": [[float(i), 0.5 * i, 0.0] for i in range(10)]}  # fmt: skip
+    try:
+        (tmp_path / "t.cif").write_text(_mini_cif())
+        job = {"name": "m", "sequences": [
+            {"protein": {"id": "A", "sequence": "GASG", "modifications": [{"ptmType": "SEP", "ptmPosition": 3}],
+                         "unpairedMsa": ">q\nGASG\n>h1\nGTSG\n>h2\nG-SaG\n",
+                         "templates": [{"mmcifPath": "t.cif", "chainId": "A", "queryIndices": [0, 1, 2], "templateIndices": [0, 1, 2]}]}},
+            {"protein": {"id": "B", "sequence": "ACD", "unpairedMsa": ">q\nACD\n>h\nAGD\n"}}]}  # fmt: skip
+        p = tmp_path / "job.json"
+        p.write_text(json.dumps(job))
+        inp = InferenceInput.from_job(parse_json_input(str(p))[0], msa_pairing="none")
+        f = inp.features
+        # chain A: G, A, ten atom tokens of SEP, G  -> 13 tokens; chain B: 3
+        assert inp.num_tokens == 13 + 3 and f["residue_index"][:13].tolist() == [0, 1] + [2] * 10 + [3]
+        ser = const_res("SER")
+        assert f["msa"].shape[0] == 4  # query + two rows of A + one row of B
+        assert f["msa"][1, :13].tolist() == [const_res("GLY"), const_res("THR")] + [ser] * 10 + [const_res("GLY")]
+        assert f["msa"][2, 1] == 21 and f["deletion_matrix"][2, 12] == 1 and (f["msa"][1, 13:] == 21).all()
+        assert f["template_mask"][0] == 1 and f["template_aatype"][0, :13].tolist() == [const_res("GLY"), const_res("ALA")] + [ser] * 10 + [21]
+        assert f["template_pseudo_beta_mask"][0, 2:12].eq(1).all() and (f["template_aatype"][0, 13:] == 21).all()
+    finally:
+        ref_conformers._TABLE.pop("SEP", None)
+
+
+def const_res(name):
+    from deepfold3_dev_b200.data import const
+
+    return const.RES_TYPE_ORDER[name]
+
+
 def test_crops_keep_consistency():
     f = synthetic_complex([("protein", 60), ("protein", 50), ("ligand", 6)], num_msa=8, num_templates=2, seed=1)
     for strategy in ("contiguous", "spatial", "spatial_interface"):

@@ -208,6 +208,32 @@ def test_structure_dataset_on_the_fly(tmp_path):
     b = collate([x, d[1]])
     assert b["res_type"].shape == (2, 6) and b["bond_matrix"].shape == (2, 6, 6, 1)
 
+    # stochastic atomisation (training regulariser): every standard residue split into atom tokens that keep their
+    # residue's alignment column, residue index and reference frame; the crop budget counts the extra tokens
+    full = open_dataset(str(tmp_path / "out"), max_tokens=64, atomize_prob=1.0)[0]
+    plain = open_dataset(str(tmp_path / "out"), max_tokens=64)[0]
+    # per chain: GLY ALA SER resolved (4 + 5 + 6 atoms) and one unresolved GLY, which has no atoms to split and stays a
+    # residue token; plus the zinc ion
+    n_other = int((plain["mol_type"] != 0).sum())
+    assert plain["res_type"].shape[0] == 2 * 4 + n_other and full["res_type"].shape[0] == 2 * (15 + 1) + n_other
+    prot = (full["mol_type"] == 0) & (full["ref_mask"].sum(-1) == 1)
+    assert int(prot.sum()) == 30 and (full["res_type"][prot] == 20).all() and not full["frames_mask"][prot].any()
+    # chain A of the entry is GLY ALA SER (resolved part): 4 + 5 + 6 atom tokens reading alignment columns 0, 1, 2
+    first = full["asym_id"] == full["asym_id"][0]
+    assert full["msa"][1][first].tolist() == [7] * 4 + [0] * 5 + [21] * 6 + [7] and full["msa"][2][first].tolist() == [7] * 4 + [1] * 5 + [15] * 6 + [7]
+    assert full["residue_index"][first].unique_consecutive().numel() == 4
+    assert len(full["ref_space_uid"][first][:, 0].unique()) == 4  # one reference frame per residue
+    # bonds between the atom tokens of the chain: 3 (GLY) + 4 (ALA) + 5 (SER) inside the residues, two peptide links
+    inside = full["bond_matrix"][..., 0][first][:, first]
+    assert int(inside.sum()) == 2 * (3 + 4 + 5 + 2 + 1) and bool((inside == inside.T).all())  # + SER 3 to the residue token of GLY 4
+    assert inside[2, 4] == 1  # C of GLY 1 (third atom) to N of ALA 2 (first atom of the next residue)
+    capped = open_dataset(str(tmp_path / "out"), max_tokens=64, atomize_prob=1.0, atomize_max_residues=1)[0]
+    assert capped["res_type"].shape[0] < full["res_type"].shape[0] and int((capped["ref_mask"].sum(-1) == 1).sum()) > n_other
+    cropped = open_dataset(str(tmp_path / "out"), max_tokens=10, atomize_prob=1.0)[0]
+    assert cropped["res_type"].shape[0] == 10 and cropped["msa"].shape[1] == 10
+    with pytest.raises(ValueError, match="atomize_source"):
+        open_dataset(str(tmp_path / "out"), max_tokens=64, atomize_prob=0.5, atomize_source="sideways")[0]
+
 
 _PLM_CIF = """data_ZZ1
 _chem_comp.id ZZ1
