@@ -64,3 +64,19 @@ def maybe_atomize(feats: dict, gen: torch.Generator, p_example: float = 0.1, fra
     if p_example <= 0 or float(torch.rand((), generator=gen)) >= p_example:
         return feats
     return atomize_tokens(feats, select_residues_to_atomize(feats, gen, fraction, max_residues))
+
+
+def atomize_stored_features(feats: dict, gen: torch.Generator, prob: float, max_residues: int = 0) -> dict:
+    """The recipe's ``atomize_prob`` / ``atomize_max_residues`` for examples stored as feature files, which cannot be
+    tokenised again: every standard polymer residue token is picked with probability ``prob``, at most
+    ``max_residues`` (0: no cap). Examples built from structures are atomised at tokenisation instead
+    (``featurize.tokenize_structure``), where the residue's chemical bonds are also known; here the bond matrix keeps
+    the rows of the residue token it was copied from."""
+    if prob <= 0:
+        return feats
+    polymer = (feats["mol_type"] != const.MOL_NONPOLYMER) & feats["seq_mask"].bool() & (feats["ref_mask"].sum(-1) > 1)
+    idx = torch.nonzero(polymer).flatten()
+    idx = idx[torch.rand(len(idx), generator=gen) < prob]
+    if max_residues > 0 and len(idx) > max_residues:
+        idx = idx[torch.randperm(len(idx), generator=gen)[:max_residues]].sort().values
+    return atomize_tokens(feats, idx)

@@ -53,8 +53,10 @@ class FeatureDirDataset:
     """Directory of ``<id>.pt`` feature dicts plus optional ``manifest.json`` (``[{id, chains, interfaces, ...}]``)."""
 
     def __init__(self, root: str, max_tokens: int = 384, max_atoms: int = 0, crop_weights: dict | None = None,
-                 is_distillation: bool = False, seed: int = 0, pack=None):  # fmt: skip
+                 is_distillation: bool = False, seed: int = 0, pack=None, atomize_prob: float = 0.0,
+                 atomize_source: str = "random", atomize_max_residues: int = 0):  # fmt: skip
         self.root, self.max_tokens, self.max_atoms = root, max_tokens, max_atoms
+        self.atomize_prob, self.atomize_max_residues = atomize_prob, atomize_max_residues  # the source is always "random" here
         self.crop_weights, self.is_distillation, self.seed = crop_weights, is_distillation, seed
         self.pack = pack if pack is not None else packs.register(root)
         man = os.path.join(root, "manifest.json")
@@ -88,6 +90,10 @@ class FeatureDirDataset:
         rec = self.records[i % len(self.records)]
         gen = torch.Generator().manual_seed(self.seed * 7_654_321 + i)
         feats = self._load(rec)
+        if self.atomize_prob > 0:
+            from .atomize import atomize_stored_features
+
+            feats = atomize_stored_features(feats, gen, self.atomize_prob, self.atomize_max_residues)
         feats, strategy = cropper.crop(feats, self.max_tokens, self.max_atoms, gen, self.crop_weights)
         feats = rotate_reference_conformers(feats, gen)
         feats.setdefault("resolution", torch.tensor(float(rec.get("resolution", 0.0))))
@@ -416,6 +422,4 @@ def open_dataset(path: str, format: str = "df3", of3_cache_dir: str = "", **kw):
         raise ValueError(f"dataset format must be df3|of3|of3pdb, got {format!r}")
     if paths.is_prepared_root(path):
         return StructureDataset(path, **kw)
-    for key in ("atomize_prob", "atomize_source", "atomize_max_residues"):
-        kw.pop(key, None)  # stored feature files are already tokenised
     return FeatureDirDataset(path, **kw)

@@ -735,6 +735,13 @@ def test_species_pairing_atomisation_masks_and_io_cache(tmp_path):
     assert int(g["is_atomized"].sum()) == k and not g["frames_mask"][g["is_atomized"]].any()
     torch.testing.assert_close(g["atom_gt_positions"][g["is_atomized"], 0][0], f["atom_gt_positions"][2, 0])
     assert maybe_atomize(f, torch.Generator().manual_seed(0), p_example=0.0) is f
+    from deepfold3_dev_b200.data.atomize import atomize_stored_features
+
+    every = atomize_stored_features(f, torch.Generator().manual_seed(0), 1.0)
+    assert int(every["is_atomized"].sum()) == int(f["ref_mask"][(f["mol_type"] != 3) & (f["ref_mask"].sum(-1) > 1)].sum())
+    two = atomize_stored_features(f, torch.Generator().manual_seed(0), 1.0, max_residues=2)
+    assert len(torch.unique(two["residue_index"][two["is_atomized"]] * 100 + two["asym_id"][two["is_atomized"]])) == 2
+    assert atomize_stored_features(f, torch.Generator().manual_seed(0), 0.0) is f
     tm = TokenMask.fixed_from_chains(np.asarray([0, 0, 1, 1, 2]), [1])
     assert tm.loss_weight(5).tolist() == [1, 1, 0, 0, 1] and tm.select(np.asarray([2, 4])).get("fixed").tolist() == [True, False]
     io_cache.set_drop_page_cache(True)
