@@ -90,8 +90,6 @@ def parse_component(text: str, keep_hydrogens: bool = False) -> Component | None
     xyz = _floats(a, ("pdbx_model_Cartn_x_ideal", "pdbx_model_Cartn_y_ideal", "pdbx_model_Cartn_z_ideal"), n)
     if xyz is None:
         xyz = _floats(a, ("model_Cartn_x", "model_Cartn_y", "model_Cartn_z"), n)
-    if xyz is None:
-        xyz = np.zeros((n, 3), dtype=np.float32)
     symbols = a.get("type_symbol", ["C"] * n)
     keep = [i for i in range(n) if keep_hydrogens or symbols[i].upper() not in ("H", "D")]
     index = {a["atom_id"][i].strip('"'): k for k, i in enumerate(keep)}
@@ -103,10 +101,20 @@ def parse_component(text: str, keep_hydrogens: bool = False) -> Component | None
         i, j = index.get(x.strip('"')), index.get(y.strip('"'))
         if i is not None and j is not None:
             bonds.append((i, j, _ORDER.get(o.upper()[:4], 1)))
+    elements = [min(ATOMIC_NUMBER.get(symbols[i].upper(), 6), 127) for i in keep]
+    if xyz is None:
+        # neither ideal nor model coordinates (a few hundred dictionary entries): embed the heavy-atom graph from its
+        # bond list, as the reference does from the entry's SMILES descriptor with a toolkit (data/ccd.py:267-362)
+        from .smiles import embed_3d
+
+        aromatic_flag = a.get("pdbx_aromatic_flag", ["N"] * n)
+        heavy = embed_3d(elements, bonds, [aromatic_flag[i] == "Y" for i in keep], seed=sum(map(ord, block.name)) % 9973)
+        xyz = np.zeros((n, 3), dtype=np.float32)
+        xyz[keep] = heavy
     return Component(
         code=block.name.upper(), name=block.value("chem_comp", "name") or "",
         atoms=[a["atom_id"][i].strip('"') for i in keep],
-        elements=[min(ATOMIC_NUMBER.get(symbols[i].upper(), 6), 127) for i in keep],
+        elements=elements,
         charges=[int(float(charges[i])) if charges[i] not in MISSING else 0 for i in keep],
         coords=xyz[keep], leaving=[leaving[i] == "Y" for i in keep], bonds=bonds,
     )  # fmt: skip

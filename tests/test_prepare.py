@@ -293,6 +293,13 @@ def test_component_dictionary_lookup(tmp_path):
     assert np.allclose(c.coords[1], [1.25, 0, 0])  # ideal coordinates, not the model ones
     assert ccd.leaving_atom_sets(comps)["ZZ1"] == {"O2"} and ccd.atom_name_sets(comps)["ZZ1"] == {"C1", "O1", "O2", "C1'"}
     assert np.allclose(ccd.load_components(str(path))["ZZ2"].coords[0], [1, 2, 3])  # model coordinates as the fallback
+    # an entry without any coordinates is embedded from its bond graph: bonded atoms at bond length, none coincide
+    bare = _PLM_CIF.split("data_ZZ2")[0].replace("data_ZZ1", "data_ZZ7").replace("ZZ1 ", "ZZ7 ")
+    for number in ("9.0 9.0 9.0", "0.000 0.000 0.000", "1.250 0.000 0.000", "-0.600 1.100 0.000", "-0.800 -1.200 0.300", "-1.800 -1.200 0.300"):
+        bare = bare.replace(number, "? ? ?")
+    emb = ccd.parse_component(bare)
+    dist = np.linalg.norm(emb.coords[:, None] - emb.coords[None], axis=-1)
+    assert emb.atoms == c.atoms and all(1.1 < dist[i, j] < 1.7 for i, j, _ in emb.bonds) and dist[np.triu_indices(4, 1)].min() > 1.0
     ref_conformers.set_ccd_source(str(path))
     try:
         job = JobInput("lig", [ProteinChainInput(["A"], "GASG"), LigandChainInput(["L"], ["ZZ1"])])
