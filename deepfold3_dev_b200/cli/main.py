@@ -72,7 +72,11 @@ def build_training_stream(tc, mc, info, datasets, data_dir=None, synthetic=False
             d = mc.data
             parts.append(ds.open_dataset(path, max_tokens=tc.max_tokens, max_atoms=tc.max_atoms, is_distillation=distill,
                                          seed=tc.seed, atomize_prob=d.atomize_prob, atomize_source=d.atomize_source,
-                                         atomize_max_residues=d.atomize_max_residues, **kw))  # fmt: skip
+                                         atomize_max_residues=d.atomize_max_residues,
+                                         pdb_chain_cache_dir=getattr(tc, "pdb_chain_cache_dir", None) or None,
+                                         max_templates=d.max_templates, template_cutoff_days=d.template_cutoff_days,
+                                         max_template_date=d.max_template_date,
+                                         default_template_cutoff_date=d.default_template_cutoff_date, **kw))  # fmt: skip
             logging.getLogger(__name__).info("dataset %s: %d examples from %s", name, len(parts[-1]), path)
         samplers = [WeightedClusterSampler(p.weights(), tc.seed + 17 * i, info.rank, info.world_size) for i, p in enumerate(parts)]
         sampler = MultiDatasetSampler(samplers, [len(p) for p in parts], weights, tc.seed)

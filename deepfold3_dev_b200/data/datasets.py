@@ -259,13 +259,20 @@ class StructureDataset:
     def __init__(self, root: str, max_tokens: int = 384, max_atoms: int = 0, crop_weights: dict | None = None,
                  is_distillation: bool = False, seed: int = 0, max_chains: int = 20, max_msa_rows: int = 16384,
                  msa_dir: str | None = None, cutoff_date: str = "", keep_after: bool = False, atomize_prob: float = 0.0,
-                 atomize_source: str = "random", atomize_max_residues: int = 0):  # fmt: skip
+                 atomize_source: str = "random", atomize_max_residues: int = 0, pdb_chain_cache_dir: str | None = None,
+                 max_templates: int = 4, template_cutoff_days: int = 60, max_template_date: str | None = None,
+                 default_template_cutoff_date: str | None = None):  # fmt: skip
         from .types import load_manifest
 
         self.root, self.max_tokens, self.max_atoms = root, max_tokens, max_atoms
         self.crop_weights, self.is_distillation, self.seed = crop_weights, is_distillation, seed
         self.max_chains, self.max_msa_rows = max_chains, max_msa_rows
         self.atomize = {"atomize_prob": atomize_prob, "atomize_source": atomize_source, "atomize_max_residues": atomize_max_residues}
+        # templates: per-sequence hit lists under the dataset root, coordinates from a per-chain cache (`build-pdb-cache`)
+        self.pdb_chain_cache_dir, self.max_templates = pdb_chain_cache_dir, max_templates
+        self.template_cutoff_days, self.max_template_date = template_cutoff_days, max_template_date
+        self.default_template_cutoff_date = default_template_cutoff_date
+        self.templates_used = self.templates_dropped = 0
         self.msa_dir = msa_dir or os.path.join(root, "msa")
         packs.register(root)  # structures/ and msa/ may live in {root}/_pack
         if msa_dir:
@@ -291,6 +298,41 @@ class StructureDataset:
 
         return record_weights(self.anchor_tables())
 
+    def _templates(self, rec, chain, rng):
+        """Templates of one protein chain for this draw of the example (reference: data/module/dataset.py:772-870)."""
+        import json
+
+        from . import const
+        from . import templates as tpl
+
+        if chain.mol_type != const.MOL_PROTEIN:
+            return []
+        index = tpl.monomer_template_index(self.root, chain.msa_id)
+        if index is None:
+            return []
+        try:
+            hits = json.loads(io_cache.read_text(index))
+        except (OSError, ValueError):
+            self.templates_dropped += 1
+            return []
+        released = rec.structure_info.released if rec.structure_info else None
+        cutoff = tpl.template_cutoff(released, self.template_cutoff_days, self.max_template_date, self.default_template_cutoff_date)
+        out = []
+        for hit in tpl.sample_training_templates(hits, rec.id, cutoff, rng, self.max_templates):
+            pdb = str(hit.get("template_pdb_id") or hit.get("pdbId"))
+            chain_id = str(hit.get("template_chain_id") or hit.get("chainId") or "A")
+            path = tpl.chain_cache_path(self.pdb_chain_cache_dir, pdb, chain_id)
+            if path is None:
+                self.templates_dropped += 1
+                continue
+            try:
+                q, t = tpl.hit_index_pairs(hit)
+                out.append(tpl.load_template_chain(path, q, t))
+            except (KeyError, ValueError, OSError):
+                self.templates_dropped += 1
+        self.templates_used += len(out)
+        return out
+
     def _msa(self, chain):
         from .parse.a3m import msa_from_a3m_file
         from .types import MSA
@@ -312,6 +354,8 @@ class StructureDataset:
             crop_weights=self.crop_weights, max_chains=self.max_chains, max_msa_rows=self.max_msa_rows,
             seed=self.seed * 7_654_321 + i, is_distillation=self.is_distillation,
             anchors=self.anchor_tables()[i % len(self.records)], **self.atomize,
+            load_templates=(lambda chain, rng: self._templates(rec, chain, rng)) if self.pdb_chain_cache_dir else None,
+            max_templates=self.max_templates,
         )  # fmt: skip
         self.msa_read, self.msa_skipped = self.msa_read + read, self.msa_skipped + skipped
         return feats
@@ -319,7 +363,8 @@ class StructureDataset:
 
 def featurize_record(st, rec, load_msa, *, max_tokens: int = 384, max_atoms: int = 0, crop_weights: dict | None = None,
                      max_chains: int = 20, max_msa_rows: int = 16384, seed: int = 0, is_distillation: bool = False,
-                     anchors=None, atomize_prob: float = 0.0, atomize_source: str = "random", atomize_max_residues: int = 0):
+                     anchors=None, atomize_prob: float = 0.0, atomize_source: str = "random", atomize_max_residues: int = 0,
+                     load_templates=None, max_templates: int = 4):
     """One training example from a stored structure and its manifest record: pick the anchor chain or interface
     (in proportion to the anchor weights of ``anchors = (anchor list, weights)`` when given, else uniformly),
     pre-crop large assemblies to the chains around it, featurise, crop to the token budget, read the alignments of
@@ -327,7 +372,7 @@ def featurize_record(st, rec, load_msa, *, max_tokens: int = 384, max_atoms: int
     features and the numbers of alignments read and skipped."""
     import random
 
-    from .featurize import attach_cropped_msa, featurize_structure
+    from .featurize import attach_cropped_msa, attach_cropped_templates, featurize_structure
     from .prepare.filters import select_interface_chains
 
     gen = torch.Generator().manual_seed(seed)
@@ -354,6 +399,10 @@ def featurize_record(st, rec, load_msa, *, max_tokens: int = 384, max_atoms: int
     feats, strategy, kept = cropper.crop(feats, max_tokens, max_atoms, gen, crop_weights, return_keep=True, anchor=crop_anchor)
     feats, read, skipped = attach_cropped_msa(feats, kept, chain_cols, lambda a: load_msa(rec.chains[old_ids[a]]),
                                               max_msa_rows=max_msa_rows, token_col=token_col, chain_len=chain_len)  # fmt: skip
+    if load_templates is not None:  # ``load_templates(chain_info, rng)`` -> TemplateChain list of a protein chain
+        tfeats, _ = attach_cropped_templates(feats, kept, chain_cols, token_col, chain_len,
+                                             lambda a: load_templates(rec.chains[old_ids[a]], rng), max_templates)  # fmt: skip
+        feats.update(tfeats)
     feats = rotate_reference_conformers(feats, gen)
     from .symmetry import symmetry_features
 
@@ -412,6 +461,8 @@ def open_dataset(path: str, format: str = "df3", of3_cache_dir: str = "", **kw):
     cluster-balanced weights)."""
     from . import paths
 
+    template_keys = ("pdb_chain_cache_dir", "max_templates", "template_cutoff_days", "max_template_date", "default_template_cutoff_date")
+    template_kw = {k: kw.pop(k) for k in template_keys if k in kw}  # per-sequence hit lists exist for prepared roots only
     if format in ("of3", "of3pdb"):
         from .of3 import OF3StructureDataset
 
@@ -421,5 +472,5 @@ def open_dataset(path: str, format: str = "df3", of3_cache_dir: str = "", **kw):
     if format != "df3":
         raise ValueError(f"dataset format must be df3|of3|of3pdb, got {format!r}")
     if paths.is_prepared_root(path):
-        return StructureDataset(path, **kw)
+        return StructureDataset(path, **kw, **template_kw)
     return FeatureDirDataset(path, **kw)

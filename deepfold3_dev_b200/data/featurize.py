@@ -250,3 +250,35 @@ def attach_cropped_msa(feats: dict, keep, chain_cols: dict[int, tuple[int, int]]
     out = dict(feats)
     out.update(msa_block(out, new_cols, paired or None, unpaired or None, max_msa_rows))
     return out, read, skipped
+
+
+def attach_cropped_templates(feats: dict, keep, chain_cols: dict[int, tuple[int, int]], token_col, chain_len, load_templates,
+                             max_templates: int = 4) -> tuple[dict, int]:
+    """Template features of an example that was cropped first. ``load_templates(asym_id)`` returns the ``TemplateChain``
+    list of a chain (its query indices count residues of the chain) and is called only for chains that still have
+    tokens. Slot ``t`` of every chain shares row ``t`` of the template axis; the model only lets a template inform
+    pairs inside one chain. Returns the features (always ``max_templates`` rows) and the number of templates used."""
+    from . import templates as tpl
+
+    N = int(feats["res_type"].shape[0])
+    out = tpl.template_features(0, [], max_templates, num_tokens=N)
+    n_all = max((e for _, e in chain_cols.values()), default=0)
+    keep_np = np.arange(n_all) if keep is None else np.asarray(keep)
+    used = 0
+    for asym, (s, e) in chain_cols.items():
+        pos = np.flatnonzero((keep_np >= s) & (keep_np < e))
+        if len(pos) == 0:
+            continue
+        chains = load_templates(asym) or []
+        if not chains:
+            continue
+        per_res = tpl.template_features(int(chain_len[asym]), chains, max_templates)
+        cols = torch.as_tensor(np.asarray(token_col)[keep_np[pos]])
+        where = torch.as_tensor(pos)
+        for k, v in per_res.items():
+            if k == "template_mask":
+                out[k] = torch.maximum(out[k], v)
+            else:
+                out[k][:, where] = v.index_select(1, cols)
+        used += min(len(chains), max_templates)
+    return out, used

@@ -377,7 +377,7 @@ def msa_search_local(settings, cache_dir: str | None = None, paired: bool = True
             for per_query in mp.parse_m8(res["m8"]).values():
                 for h in per_query:
                     pdb, _, chain = h.target.partition("_")
-                    q, t = cigar_to_index_pairs(h.cigar, h.q_start - 1, h.t_start - 1)
+                    q, t = cigar_to_index_pairs(h.cigar, h.q_start, h.t_start)  # 1-based starts, as in the m8 table
                     hits.append({"pdbId": pdb.upper(), "chainId": chain or "A", "queryIndices": q, "templateIndices": t, "eValue": h.evalue})
             out.append({"unpaired": res["a3m"], "paired": pair, "templates": hits})
         return out

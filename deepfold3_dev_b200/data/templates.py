@@ -279,3 +279,91 @@ def prepare_job_templates(m8_text: str, mmcif_dir: str, out_dir: str, index: int
     with open(os.path.join(out_dir, f"templates_{index}.json"), "w") as f:
         json.dump(taken, f)
     return taken
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# templates of training examples (reference: data/module/dataset.py:748-900, data/prepare/template_search.py:110-216,
+# :504-509): per-sequence hit lists prepared once, filtered and sampled per example at load time
+# ---------------------------------------------------------------------------------------------------------------
+def monomer_template_index(root: str, msa_id: str) -> str | None:
+    """The hit list of a sequence: ``<root>/monomer_templates/<first two characters>/<msa_id>.json`` (the reference's
+    sharded layout) or ``<root>/templates/<msa_id>.json``; ``None`` when neither exists."""
+    from . import io_cache
+
+    import os
+
+    key = str(msa_id)
+    shard = key[:2].lower() if len(key) >= 2 else "__"
+    for path in (os.path.join(root, "monomer_templates", shard, f"{key}.json"), os.path.join(root, "templates", f"{key}.json")):
+        if io_cache.exists(path):
+            return path
+    return None
+
+
+def passes_hit_filters(hit: dict, query_length: int, max_subsequence_ratio: float = 0.95, min_hit_length: int = 10,
+                       min_align_ratio: float = 0.1) -> bool:  # fmt: skip
+    """AF3 SI 2.4 per-hit filters on an m8-style hit (1-based ``qstart qend tstart tend``, ``identity`` 0..1): the
+    template span has at least ``min_hit_length`` residues, the alignment covers at least ``min_align_ratio`` of the
+    query, and a near-identical hit (>= 0.99) spanning more than ``max_subsequence_ratio`` of the query is a copy of
+    the query and is dropped."""
+    span = int(hit["tend"]) - int(hit["tstart"]) + 1
+    aligned = int(hit["qend"]) - int(hit["qstart"]) + 1
+    q = max(int(query_length), 1)
+    if span < min_hit_length or aligned / q < min_align_ratio:
+        return False
+    return not (span / q > max_subsequence_ratio and float(hit.get("identity", 0.0)) >= 0.99)
+
+
+def template_cutoff(released: str | None, cutoff_days: int = 60, max_template_date: str | None = None,
+                    default_cutoff: str | None = None) -> str | None:  # fmt: skip
+    """Latest template release date an example may see: ``min(max_template_date, released - cutoff_days)``; an example
+    without a release date falls back to ``default_cutoff``. ``None`` means that no bound can be established, and the
+    caller must then use no template at all (a template newer than the example would leak its answer)."""
+    import datetime
+
+    per_record = default_cutoff
+    if released:
+        try:
+            per_record = (datetime.date.fromisoformat(str(released)[:10]) - datetime.timedelta(days=cutoff_days)).isoformat()
+        except ValueError:
+            pass
+    if per_record is None:
+        return max_template_date
+    return per_record if max_template_date is None else min(max_template_date, per_record)
+
+
+def sample_training_templates(hits: list[dict], record_id: str, cutoff: str | None, rng, max_templates: int = 4) -> list[dict]:
+    """Hits a training example may use: not the example's own entry, released (with a known date) on or before
+    ``cutoff``; then ``k = min(Uniform{0..n}, max_templates)`` of them drawn without replacement (AF3 SI 2.4). Accepts
+    the reference's hit records (``template_pdb_id``, ``template_chain_id``, ``release_date``) and this package's
+    (``pdbId``, ``chainId``, ``releaseDate``)."""
+    if cutoff is None:
+        return []
+    own = str(record_id).upper()
+    ok = []
+    for h in hits:
+        pdb = str(h.get("template_pdb_id") or h.get("pdbId") or "").upper()
+        date = h.get("release_date") or h.get("releaseDate")
+        if pdb and pdb != own and date and str(date)[:10] <= cutoff:
+            ok.append(h)
+    k = min(rng.randint(0, len(ok)), max_templates) if ok else 0
+    return rng.sample(ok, k) if k else []
+
+
+def hit_index_pairs(hit: dict) -> tuple[list[int], list[int]]:
+    """0-based (query, template) index lists of a hit: explicit lists, or a CIGAR string with 1-based starts."""
+    if "queryIndices" in hit:
+        return list(hit["queryIndices"]), list(hit["templateIndices"])
+    return cigar_to_index_pairs(hit["cigar"], int(hit["qstart"]), int(hit["tstart"]))
+
+
+def chain_cache_path(cache_dir: str, pdb_id: str, chain_id: str) -> str | None:
+    """``<cache>/<pdb>_<chain>.npz``, flat or under a two-character shard directory, in either letter case of the id."""
+    import os
+
+    for pdb in (pdb_id.lower(), pdb_id.upper()):
+        name = f"{pdb}_{chain_id}.npz"
+        for path in (os.path.join(cache_dir, name), os.path.join(cache_dir, pdb[1:3].lower(), name), os.path.join(cache_dir, pdb[:2].lower(), name)):
+            if os.path.exists(path):
+                return path
+    return None

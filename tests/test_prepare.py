@@ -235,6 +235,70 @@ def test_structure_dataset_on_the_fly(tmp_path):
         open_dataset(str(tmp_path / "out"), max_tokens=64, atomize_prob=0.5, atomize_source="sideways")[0]
 
 
+def test_training_templates_respect_dates_and_sampling(tmp_path):
+    """Templates of training examples: per-sequence hit list under the dataset root, coordinates from the per-chain
+    cache, release-date cut-off relative to the example (fail-closed), self-hits dropped, k = min(U{0..n}, max) sampled,
+    features placed on the surviving tokens of the chain."""
+    import json
+    import random
+
+    from deepfold3_dev_b200.data import templates as tpl
+    from deepfold3_dev_b200.data.datasets import StructureDataset
+
+    src = tmp_path / "src"
+    src.mkdir()
+    (src / "one.cif").write_text(_mini_cif())
+    out = tmp_path / "out"
+    prepare_directory(str(src), str(out), StructureFilterConfig(min_residues=2))
+    rec = load_manifest(str(out / "manifest.json"))[0]
+    assert rec.structure_info.released == "2020-01-02"
+    # the template entry: the same small structure under another id, moved in space
+    mirror = tmp_path / "mirror"
+    mirror.mkdir()
+    (mirror / "1abc.cif").write_text(_mini_cif(shift=(3.0, 0.0, 0.0)).replace("data_TEST", "data_1ABC").replace("_entry.id TEST", "_entry.id 1ABC"))
+    cache = tmp_path / "cache"
+    assert tpl.build_chain_cache(str(mirror), str(cache)) == 2
+    msa_id = str(rec.chains[0].msa_id)
+    hit = {"template_pdb_id": "1abc", "template_chain_id": "A", "identity": 0.5, "evalue": 1e-9, "qstart": 1, "qend": 3, "tstart": 1, "tend": 3, "cigar": "3M"}
+    hits = [dict(hit, release_date="2015-06-01"), dict(hit, template_pdb_id="test", release_date="2010-01-01"),
+            dict(hit, template_chain_id="B", release_date="2019-12-25"), dict(hit, template_chain_id="B", release_date=None)]
+    index = out / "monomer_templates" / msa_id[:2].lower() / f"{msa_id}.json"
+    index.parent.mkdir(parents=True)
+    index.write_text(json.dumps(hits))
+
+    # cut-off arithmetic: 60 days before the example, capped by the recipe's hard limit; nothing known -> no templates
+    assert tpl.template_cutoff("2020-01-02", 60) == "2019-11-03" and tpl.template_cutoff("2020-01-02", 60, "2018-01-01") == "2018-01-01"
+    assert tpl.template_cutoff(None, 60, None, "2017-05-05") == "2017-05-05" and tpl.template_cutoff(None, 60) is None
+    rng = random.Random(0)
+    picks = [tpl.sample_training_templates(hits, "test", "2019-11-03", rng, 4) for _ in range(40)]
+    assert {len(p) for p in picks} == {0, 1} and all(p[0]["release_date"] == "2015-06-01" for p in picks if p)
+    assert tpl.sample_training_templates(hits, "test", None, rng, 4) == []  # fail closed
+    assert {len(tpl.sample_training_templates(hits, "other", "2021-01-01", rng, 2)) for _ in range(60)} == {0, 1, 2}
+    assert tpl.passes_hit_filters(dict(hit, qend=50, tend=50), 100) and not tpl.passes_hit_filters(hit, 100)  # 3 residues: too short
+    assert not tpl.passes_hit_filters(dict(hit, qend=99, tend=99, identity=1.0), 100)  # a copy of the query
+
+    d = StructureDataset(str(out), max_tokens=64, pdb_chain_cache_dir=str(cache))
+    seen, placed = [], 0
+    for i in range(0, 24, 2):
+        x = d[i]
+        assert x["template_aatype"].shape == (4, x["res_type"].shape[0]) and x["template_mask"].shape == (4,)
+        seen.append(int(x["template_mask"].sum()))
+        for c in (0, 1):  # the two copies of the chain draw their templates independently and share the template rows
+            cols = x["asym_id"] == c
+            if bool((x["template_aatype"][0][cols] != 21).any()):
+                placed += 1
+                assert x["template_aatype"][0][cols].tolist()[:3] == [7, 0, 15] and x["template_pseudo_beta_mask"][0][cols][:3].eq(1).all()
+                assert (x["template_aatype"][0][cols][3:] == 21).all()  # the fourth residue is not aligned
+                assert x["template_backbone_mask"][0][cols][:3].eq(1).all() and seen[-1] == 1
+    assert set(seen) == {0, 1} and placed >= 2 and d.templates_used == placed
+    # an example without a release date and no configured fallback gets no template
+    for r in d.records:
+        r.structure_info.released = None
+    assert all(int(d[i]["template_mask"].sum()) == 0 for i in range(6))
+    d.default_template_cutoff_date = "2016-01-01"
+    assert any(int(d[i]["template_mask"].sum()) == 1 for i in range(12))
+
+
 _PLM_CIF = """data_ZZ1
 _chem_comp.id ZZ1
 _chem_comp.name 'TEST ACID'
