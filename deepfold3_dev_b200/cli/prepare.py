@@ -181,6 +181,45 @@ def pack(src_dir, out_dir, shard_size):
     click.echo(f"{build_pack(src_dir, out_dir, size)} files -> {out_dir}")
 
 
+@prepare.command("monomer-templates")
+@click.argument("data_dir", type=click.Path(exists=True))
+@click.option("--m8-dir", type=click.Path(exists=True), required=True, help="<msa_id>.m8 template search results (13 columns, CIGAR last).")
+@click.option("--release-dates", type=click.Path(exists=True), default=None, help="JSON {entry id: YYYY-MM-DD}.")
+@click.option("--pdb-mmcif-dir", type=click.Path(exists=True), default=None, help="Read release dates from a local mmCIF mirror instead.")
+@click.option("--max-hits", type=int, default=20, show_default=True)
+def monomer_templates(data_dir, m8_dir, release_dates, pdb_mmcif_dir, max_hits):
+    """Template hit lists per distinct sequence of a prepared dataset, for training (`monomer_templates/`)."""
+    from ..data import templates as tpl
+    from ..data.types import load_manifest
+
+    if release_dates:
+        with open(release_dates) as f:
+            dates = json.load(f)
+    elif pdb_mmcif_dir:
+        from ..data.parse.mmcif import read_structure_info
+
+        ids = set()
+        for name in os.listdir(m8_dir):
+            if name.endswith(".m8"):
+                with open(os.path.join(m8_dir, name)) as f:
+                    ids.update(line.split("\t")[1].partition("_")[0].lower() for line in f if "\t" in line)
+        dates = {}
+        for pdb in sorted(ids):
+            path = tpl.find_pdb_mmcif(pdb, pdb_mmcif_dir)
+            info = read_structure_info(path) if path else None
+            if info is not None and info.released:
+                dates[pdb] = info.released
+    else:
+        raise click.ClickException("give --release-dates or --pdb-mmcif-dir")
+    lengths = {}
+    manifest = os.path.join(data_dir, "manifest.json")
+    if os.path.exists(manifest):
+        for rec in load_manifest(manifest):
+            for c in rec.chains:
+                lengths[str(c.msa_id)] = int(c.num_residues)
+    tpl.build_monomer_template_index(data_dir, m8_dir, dates, lengths, max_hits, click.echo)
+
+
 @prepare.command("masks")
 @click.argument("data_dir", type=click.Path(exists=True))
 @click.option("--exclude-mol-type", "exclude", multiple=True, type=click.Choice(["protein", "dna", "rna", "ligand"]))

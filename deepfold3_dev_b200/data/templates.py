@@ -367,3 +367,48 @@ def chain_cache_path(cache_dir: str, pdb_id: str, chain_id: str) -> str | None:
             if os.path.exists(path):
                 return path
     return None
+
+
+def build_monomer_template_index(data_dir: str, m8_dir: str, release_dates: dict[str, str], lengths: dict[str, int] | None = None,
+                                 max_hits: int = 20, log=None) -> tuple[int, int]:
+    """``<m8_dir>/<msa_id>.m8`` (template search results per distinct sequence, 13 columns with CIGAR) ->
+    ``<data_dir>/monomer_templates/<shard>/<msa_id>.json``: the hits that pass the AF3 per-hit filters, best first, at
+    most ``max_hits`` per sequence, each with the release date of its entry (``release_dates``: entry id -> date; hits
+    of unknown date are written with ``null`` and never used in training). The date cut-off itself is applied per
+    example when it is loaded, because one sequence occurs in examples of different dates. Returns ``(sequences
+    written, hits written)`` (reference: data/prepare/template_search.py:181-216, :440-503)."""
+    import json
+    import os
+
+    written = total = 0
+    dates = {k.lower(): v for k, v in release_dates.items()}
+    for name in sorted(os.listdir(m8_dir)):
+        if not name.endswith(".m8"):
+            continue
+        msa_id = name[:-3]
+        with open(os.path.join(m8_dir, name)) as f:
+            rows = [line.rstrip("\n").split("\t") for line in f if line.strip()]
+        hits = []
+        for r in rows:
+            if len(r) < 13:
+                continue
+            pdb, _, chain = r[1].partition("_")
+            hit = {"template_pdb_id": pdb.lower(), "template_chain_id": chain or "A", "identity": float(r[2]), "evalue": float(r[10]),
+                   "qstart": int(r[6]), "qend": int(r[7]), "tstart": int(r[8]), "tend": int(r[9]), "cigar": r[12],
+                   "release_date": dates.get(pdb.lower()), "index_space": "seqres"}  # fmt: skip
+            qlen = (lengths or {}).get(msa_id, hit["qend"])
+            if passes_hit_filters(hit, qlen):
+                hits.append(hit)
+            if len(hits) >= max_hits:
+                break
+        if not hits:
+            continue
+        shard = msa_id[:2].lower() if len(msa_id) >= 2 else "__"
+        out = os.path.join(data_dir, "monomer_templates", shard)
+        os.makedirs(out, exist_ok=True)
+        with open(os.path.join(out, f"{msa_id}.json"), "w") as f:
+            json.dump(hits, f)
+        written, total = written + 1, total + len(hits)
+    if log:
+        log(f"{written} sequences, {total} template hits -> {os.path.join(data_dir, 'monomer_templates')}")
+    return written, total

@@ -277,6 +277,19 @@ def test_training_templates_respect_dates_and_sampling(tmp_path):
     assert tpl.passes_hit_filters(dict(hit, qend=50, tend=50), 100) and not tpl.passes_hit_filters(hit, 100)  # 3 residues: too short
     assert not tpl.passes_hit_filters(dict(hit, qend=99, tend=99, identity=1.0), 100)  # a copy of the query
 
+    # the index builder: m8 rows -> filtered, dated hit lists in the sharded layout
+    m8 = tmp_path / "m8"
+    m8.mkdir()
+    row = lambda t, ident, q2, t2, cigar: "\t".join(["q", t, str(ident), "50", "0", "0", "1", str(q2), "1", str(t2), "1e-9", "100", cigar])  # noqa: E731
+    (m8 / "seqx.m8").write_text("\n".join([row("2xyz_A", 0.4, 40, 40, "40M"), row("3abc_B", 1.0, 50, 50, "50M"), row("4def_C", 0.3, 4, 4, "4M"),
+                                            row("5ghi_A", 0.5, 30, 30, "30M")]) + "\n")
+    built = tmp_path / "built"
+    built.mkdir()
+    assert tpl.build_monomer_template_index(str(built), str(m8), {"2XYZ": "2001-02-03"}, {"seqx": 50}) == (1, 2)
+    got = json.loads((built / "monomer_templates" / "se" / "seqx.json").read_text())
+    assert [(h["template_pdb_id"], h["template_chain_id"], h["release_date"]) for h in got] == [("2xyz", "A", "2001-02-03"), ("5ghi", "A", None)]
+    assert tpl.hit_index_pairs(got[0]) == (list(range(40)), list(range(40)))
+
     d = StructureDataset(str(out), max_tokens=64, pdb_chain_cache_dir=str(cache))
     seen, placed = [], 0
     for i in range(0, 24, 2):
