@@ -114,6 +114,11 @@ for _base in "AGCT":
 RESIDUE_BONDS["N"] = _SUGAR_BONDS
 POLYMER_LINK = {MOL_PROTEIN: ("C", "N"), MOL_RNA: ("O3'", "P"), MOL_DNA: ("O3'", "P")}  # (atom of residue i, atom of residue i + 1)
 
+# Buffer, cryo-protectant and precipitant molecules that are dropped from X-ray entries (AF3 supplement 2.5.4, table 9):
+# they are not part of the biological assembly and would otherwise become spurious ligand tokens.
+CRYSTALLIZATION_AIDS = frozenset({"SO4", "GOL", "EDO", "PO4", "ACT", "PEG", "DMS", "TRS", "PGE", "PG4", "FMT", "EPE", "MPD",
+                                  "MES", "CD", "IOD"})  # fmt: skip
+
 ELEMENT_NUMBER = {"H": 1, "C": 6, "N": 7, "O": 8, "F": 9, "P": 15, "S": 16, "CL": 17, "SE": 34, "BR": 35, "I": 53,
                   "MG": 12, "ZN": 30, "FE": 26, "CA": 20, "NA": 11, "K": 19, "MN": 25, "CU": 29, "CO": 27, "NI": 28}  # fmt: skip
 

@@ -240,8 +240,10 @@ def _distance_bonds(xyz: np.ndarray, elements: np.ndarray) -> list[tuple[int, in
 
 
 def parse_mmcif(path: str, use_assembly: bool = True, assembly_id: str = "1", max_chains: int = 0,
-                component_atoms: dict[str, set[str]] | None = None) -> tuple[Structure, Record]:  # fmt: skip
+                component_atoms: dict[str, set[str]] | None = None, drop_crystallization_aids: bool = False) -> tuple[Structure, Record]:  # fmt: skip
     """Read one entry. ``component_atoms`` (component -> allowed atom names) drops atoms a dictionary does not know.
+    ``drop_crystallization_aids`` leaves out the non-polymer chains of an X-ray entry that consist of buffer or
+    precipitant molecules only (``const.CRYSTALLIZATION_AIDS``; reference: data/prepare/structure.py:782).
 
     ``max_chains`` > 0 refuses assemblies that would expand to more chains (raises ``ValueError`` before any work).
     """
@@ -275,6 +277,9 @@ def parse_mmcif(path: str, use_assembly: bool = True, assembly_id: str = "1", ma
             continue
         if mt == const.MOL_NONPOLYMER:
             layout = [(k[0], src["res"][k]["comp"], k) for k in src["order"]]
+            if drop_crystallization_aids and "X-RAY" in str(info.method or "").upper() and layout and all(
+                    comp.strip().upper() in const.CRYSTALLIZATION_AIDS for _, comp, _ in layout):  # fmt: skip
+                continue
         else:
             full = poly_seqs.get(ent)
             layout = [(num, mon, (num, "")) for num, mon in full] if full else [(k[0], src["res"][k]["comp"], k) for k in src["order"]]

@@ -40,6 +40,8 @@ class StructureFilterConfig:
     # whole-entry geometry check
     max_tight_clashes: int | None = None
     tight_clash_dist: float = 0.8
+    # X-ray entries: leave out ligand chains made of buffer / precipitant molecules only (AF3 supplement table 9)
+    drop_crystallization_aids: bool = True
 
 
 def _chain_residues(st: Structure, ci: ChainInfo) -> np.ndarray:

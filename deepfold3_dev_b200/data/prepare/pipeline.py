@@ -48,7 +48,8 @@ def process_entry(path: str, out_dir: str, cfg: StructureFilterConfig | None = N
     """Returns ``{"id", "status": "ok"|"rejected"|"error", "reason", "record", "sequences"}`` (JSON-friendly)."""
     cfg = cfg or StructureFilterConfig()
     try:
-        st, rec = parse_mmcif(path, use_assembly=use_assembly, max_chains=cfg.max_chains)
+        st, rec = parse_mmcif(path, use_assembly=use_assembly, max_chains=cfg.max_chains,
+                              drop_crystallization_aids=cfg.drop_crystallization_aids)
     except Exception as exc:  # noqa: BLE001 - one unreadable entry must not stop the run
         return {"id": os.path.basename(path), "status": "error", "reason": f"{type(exc).__name__}: {exc}"}
     polymers = sum(1 for c in rec.chains if c.mol_type != const.MOL_NONPOLYMER)

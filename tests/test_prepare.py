@@ -235,6 +235,17 @@ def test_structure_dataset_on_the_fly(tmp_path):
         open_dataset(str(tmp_path / "out"), max_tokens=64, atomize_prob=0.5, atomize_source="sideways")[0]
 
 
+def test_crystallization_aids_are_dropped_from_xray_entries(tmp_path):
+    sulfate = _mini_cif().replace(" ZN ZN . ZN C 2", " S S . SO4 C 2")
+    (tmp_path / "s.cif").write_text(sulfate)
+    (tmp_path / "n.cif").write_text(sulfate.replace("X-RAY DIFFRACTION", "SOLUTION NMR"))
+    (tmp_path / "z.cif").write_text(_mini_cif())
+    kept = lambda name, drop: [c.res_name for c in parse_mmcif(str(tmp_path / name), use_assembly=False, drop_crystallization_aids=drop)[1].chains]  # noqa: E731
+    assert kept("s.cif", False)[-1] == "SO4" and "SO4" not in kept("s.cif", True) and len(kept("s.cif", True)) == 2
+    assert kept("n.cif", True)[-1] == "SO4"  # only diffraction entries carry crystallisation additives
+    assert kept("z.cif", True)[-1] == "ZN"  # a real ligand stays
+
+
 def test_training_templates_respect_dates_and_sampling(tmp_path):
     """Templates of training examples: per-sequence hit list under the dataset root, coordinates from the per-chain
     cache, release-date cut-off relative to the example (fail-closed), self-hits dropped, k = min(U{0..n}, max) sampled,
