@@ -92,7 +92,7 @@ def sweep(device: torch.device, sizes_mib, iters: int, warmup: int, dtype=torch.
     return rows
 
 
-def peer_rows(device: torch.device, sizes_mib, iters: int, warmup: int):
+def peer_rows(device: torch.device, sizes_mib, iters: int, warmup: int, transport: str = "peer"):
     """The package's own one-node transports: gradient reduction and the rows<->channels exchange."""
     from deepfold3_dev_b200.parallel.axial import AxialComm
     from deepfold3_dev_b200.parallel.dist import DistInfo, on_one_node
@@ -101,16 +101,17 @@ def peer_rows(device: torch.device, sizes_mib, iters: int, warmup: int):
     info = DistInfo(rank, device.index or 0, world, device, dist.get_backend())
     if not on_one_node(info):
         return [{"op": "peer", "skipped": "ranks span several hosts"}]
-    comm = AxialComm(info, "peer")
+    comm = AxialComm(info, transport)
     rows = []
     for mib in sizes_mib:
         channels = 128
         n = int((mib * 2**20 / 2 / channels) ** 0.5) // world * world
         if n < world:
             continue
-        x = torch.randn(n // world, n, channels, device=device, dtype=torch.bfloat16)
-        for name, fn in {"peer_all_gather": lambda: comm.all_gather(x), "peer_transpose": lambda: comm.transpose(x),
-                         "peer_rows_to_channels": lambda: comm.rows_to_channels(x)}.items():  # fmt: skip
+        x = torch.randn(1, n // world, n, channels, device=device, dtype=torch.bfloat16)         # row shard [B, n, N, C]
+        planes = torch.randn(1, channels, 1, n // world, n, device=device, dtype=torch.bfloat16)  # channel planes [G, C, B, n, N]
+        for name, fn in {"peer_all_gather": lambda: comm.all_gather(x, 1), "peer_transpose": lambda: comm.transpose(x),
+                         "peer_rows_to_channels": lambda: comm.rows_to_channels(planes)}.items():  # fmt: skip
             seconds = _timed(fn, device, iters, warmup)
             nbytes = x.numel() * x.element_size() * (world if name == "peer_all_gather" else 1)
             alg = nbytes / seconds / 1e9
@@ -126,6 +127,8 @@ def main(argv=None) -> int:
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--peer", action="store_true", help="also time the package's peer-memory kernels (one node)")
+    ap.add_argument("--peer-transport", choices=["peer", "collective"], default="peer",
+                    help="exchange transport for --peer: the peer-memory kernels, or their collective statement (also runs on CPU)")
     ap.add_argument("--min-busbw", type=float, default=0.0, help="fail when the largest all-reduce is below this many GB/s")
     ap.add_argument("--json", type=str, default=None, help="write the table here (rank 0)")
     args = ap.parse_args(argv)
@@ -143,8 +146,8 @@ def main(argv=None) -> int:
     hosts: list = [None] * world
     dist.all_gather_object(hosts, (socket.gethostname(), torch.cuda.get_device_name(device) if use_cuda else "cpu"))
     rows = sweep(device, args.sizes_mib, args.iters, args.warmup)
-    if args.peer and use_cuda:
-        rows += peer_rows(device, args.sizes_mib, args.iters, args.warmup)
+    if args.peer and (use_cuda or args.peer_transport == "collective"):
+        rows += peer_rows(device, args.sizes_mib, args.iters, args.warmup, args.peer_transport)
 
     status = 0
     if rank == 0:

@@ -148,10 +148,12 @@ def test_deploy_recipes_render_and_parse(tmp_path):
     table = tmp_path / "cc.json"
     run = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--standalone", "--local-addr", "127.0.0.1",
                           "--nproc-per-node", "2", os.path.join(dep, "comm_check.py"), "--sizes-mib", "1", "--iters", "2",
-                          "--warmup", "1", "--json", str(table)], capture_output=True, text=True, timeout=300)  # fmt: skip
+                          "--warmup", "1", "--json", str(table), "--peer", "--peer-transport", "collective"],
+                         capture_output=True, text=True, timeout=300)  # fmt: skip
     assert run.returncode == 0, run.stderr[-2000:]
     rows = json.loads(table.read_text())["rows"]
-    assert {r["op"] for r in rows} == {"all_reduce", "all_gather"} and all(r["busbw_gbs"] > 0 for r in rows)
+    assert {r["op"] for r in rows} == {"all_reduce", "all_gather", "peer_all_gather", "peer_transpose", "peer_rows_to_channels"}
+    assert all(r["busbw_gbs"] > 0 for r in rows)
 
 
 def test_every_shipped_config_loads():
