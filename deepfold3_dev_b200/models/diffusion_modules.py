@@ -240,18 +240,21 @@ class DiffusionTransformerBlock(nn.Module):
         ``pair_logits`` ``[B, H, N, N]`` with the padding mask already added."""
         B, S, N, _ = x.shape
         H, Dk, Dv = self.num_heads, self.key_dim_per_head, self.val_dim_per_head
+        # adaptive LayerNorm and the gated residual updates go through ops.ada_norm / ops.gated_residual: one kernel each
+        # way under bf16 autocast on a GPU (the result of ada_norm is then the bf16 tensor the projections read), the
+        # same arithmetic written out in PyTorch everywhere else
         cn = cond_norm * self.attn_cond_norm_w
-        xn = torch.sigmoid(self.attn_cond_scale(cn)) * self.attn_norm(x) + self.attn_cond_bias(cn)
+        xn = ops.ada_norm(x, self.attn_cond_scale(cn), self.attn_cond_bias(cn), self.attn_norm.eps)
         q = self.to_q(xn).view(B, S, N, H, Dk).transpose(2, 3)
         k = self.to_k(xn).view(B, S, N, H, Dk).transpose(2, 3)
         v = self.to_v(xn).view(B, S, N, H, Dv).transpose(2, 3)
         out = ops.pair_bias_attention(q, k, v, pair_logits, None, self.scale, fp32_qk=True)
         out = out.transpose(2, 3).reshape(B, S, N, H * Dv) * torch.sigmoid(self.to_g(xn))
-        x = x + torch.sigmoid(self.zero_cond(single_cond)) * self.out_proj(out)
+        x = ops.gated_residual(x, self.zero_cond(single_cond), self.out_proj(out))
         cn = cond_norm * self.ffn_cond_norm_w
-        xn = torch.sigmoid(self.ffn_cond_scale(cn)) * self.ffn_norm(x) + self.ffn_cond_bias(cn)
+        xn = ops.ada_norm(x, self.ffn_cond_scale(cn), self.ffn_cond_bias(cn), self.ffn_norm.eps)
         ff = self.ffn_linear2(ops.swiglu(self.ffn_linear1(xn)))
-        return x + torch.sigmoid(self.ffn_zero_cond(single_cond)) * ff
+        return ops.gated_residual(x, self.ffn_zero_cond(single_cond), ff)
 
     def forward(self, x, mask, single_cond, pair_logits):
         """Reference-shaped call: ``x`` ``[B?, N, c]``, ``mask`` ``[B?, N]``, ``pair_logits`` ``[B?, H, N, N]``."""

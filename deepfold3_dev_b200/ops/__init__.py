@@ -201,6 +201,28 @@ def sigmoid_gate_mul(x, w, other):
     return torch.sigmoid(torch.nn.functional.linear(x, w)) * other
 
 
+def ada_norm(x, s_pre, t, eps: float = 1e-5):
+    """Adaptive LayerNorm ``sigmoid(s_pre) * LN(x) + t`` (LN without affine parameters; AF3 algorithm 26, the form
+    inside every diffusion transformer block). One kernel each way when the conditioning tensors are bf16 and shaped
+    like ``x``; the result is then bf16."""
+    nat = fused(x, "ada_norm")
+    if nat is not None and nat.ada_norm_supported(x, s_pre, t):
+        _CENSUS["ada_norm:sm100"] += 1
+        return nat.ada_norm(x, s_pre, t, eps)
+    _CENSUS["ada_norm:torch"] += 1
+    return torch.sigmoid(s_pre) * layer_norm(x, None, None, eps) + t
+
+
+def gated_residual(a, z, u):
+    """``a + sigmoid(z) * u``: a residual update behind a sigmoid gate."""
+    nat = fused(a, "ada_norm")
+    if nat is not None and nat.gated_residual_supported(a, z, u):
+        _CENSUS["gated_residual:sm100"] += 1
+        return nat.gated_residual(a, z, u)
+    _CENSUS["gated_residual:torch"] += 1
+    return a + torch.sigmoid(z) * u
+
+
 def head_bias_planes(x, w):
     """Per-head additive attention bias ``[B, H, R, N]`` from the pair rows ``x [B, R, N, C]``, ``w [H, C]``."""
     nat = fused(x, "linear_planes")

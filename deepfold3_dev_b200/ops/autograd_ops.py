@@ -502,6 +502,60 @@ def sigmoid_gate_mul(x, w, other):
     return _SigmoidGateMul.apply(x, w, other)
 
 
+class _AdaNorm(torch.autograd.Function):
+    """``sigmoid(s) * LN(x) + t`` in one kernel each way (LN without affine; ``x`` fp32 or bf16, ``s`` / ``t`` bf16, result
+    bf16: the tensor the following projections consume, so no cast kernel runs per projection)."""
+
+    @staticmethod
+    def forward(ctx, x, s, t, eps):
+        xc, sc = x.contiguous(), s.contiguous()
+        y, mean, rstd = K.ada_ln_fwd(xc, sc, t.contiguous(), eps)
+        ctx.save_for_backward(xc, sc, mean, rstd)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        xc, sc, mean, rstd = ctx.saved_tensors
+        d = dy if dy.dtype == BF16 else dy.to(BF16)
+        dx, ds = K.ada_ln_bwd(d.contiguous(), xc, sc, mean, rstd)
+        return dx, ds, d, None
+
+
+def ada_norm_supported(x, s, t) -> bool:
+    c = x.shape[-1]
+    return (x.is_cuda and x.dtype in (torch.float32, BF16) and s.dtype == BF16 and t.dtype == BF16 and s.shape == x.shape
+            and t.shape == x.shape and c % 2 == 0 and c <= 1024)
+
+
+def ada_norm(x, s, t, eps: float = 1e-5):
+    return _AdaNorm.apply(x, s, t, eps)
+
+
+class _GatedResidual(torch.autograd.Function):
+    """``a + sigmoid(z) * u``: the gated residual update of the diffusion transformer (``a`` fp32 or bf16, ``z`` / ``u`` bf16)."""
+
+    @staticmethod
+    def forward(ctx, a, z, u):
+        zc, uc = z.contiguous(), u.contiguous()
+        ctx.save_for_backward(zc, uc)
+        return K.gated_residual_fwd(a.contiguous(), zc, uc)
+
+    @staticmethod
+    def backward(ctx, dy):
+        zc, uc = ctx.saved_tensors
+        dz, du = K.gated_residual_bwd(dy.contiguous(), zc, uc)
+        return dy, dz, du
+
+
+def gated_residual_supported(a, z, u) -> bool:
+    return (a.is_cuda and a.dtype in (torch.float32, BF16) and z.dtype == BF16 and u.dtype == BF16 and z.shape == a.shape
+            and u.shape == a.shape and a.numel() % 2 == 0)
+
+
+def gated_residual(a, z, u):
+    return _GatedResidual.apply(a, z, u)
+
+
 class _Transition(torch.autograd.Function):
     """``swiglu(LN(x) w1^T) w2^T``: LN kernel, GEMM with the SwiGLU epilogue, output GEMM."""
 

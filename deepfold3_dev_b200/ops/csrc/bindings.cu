@@ -22,6 +22,8 @@ Tensor df3_dropout_shared(const c10::optional<Tensor>&, const Tensor&, int64_t, 
 void df3_adamw_ema(Tensor, const Tensor&, Tensor, Tensor, const c10::optional<Tensor>&, const Tensor&, const Tensor&,
                    double, double, double, double, double, double, double, const c10::optional<Tensor>&);
 
+void df3_register_ada_norm(torch::Library& m);
+
 #ifdef DF3_WITH_GEMM
 void df3_register_gemm(torch::Library& m);
 const char* df3_gemm_features();
@@ -31,7 +33,7 @@ void df3_register_peer_exchange(torch::Library& m);
 #endif
 
 static std::string df3_features() {
-  std::string f = "layer_norm,swiglu,dropout_add,adamw_ema,plane_layer_norm";
+  std::string f = "layer_norm,swiglu,dropout_add,adamw_ema,plane_layer_norm,ada_norm";
 #ifdef DF3_WITH_GEMM
   f += ",";
   f += df3_gemm_features();
@@ -64,6 +66,7 @@ TORCH_LIBRARY(df3, m) {
   m.def("adamw_ema(Tensor(a!) p, Tensor g, Tensor(b!) m, Tensor(c!) v, Tensor? ema, Tensor decay, Tensor scale, "
         "float lr, float b1, float b2, float eps, float bc1, float bc2, float ema_w, Tensor(d!)? p16=None) -> ()",
         &df3_adamw_ema);
+  df3_register_ada_norm(m);
 #ifdef DF3_WITH_GEMM
   df3_register_gemm(m);
   df3_register_attention(m);

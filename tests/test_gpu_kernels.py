@@ -44,6 +44,52 @@ def test_layer_norm_forward_backward(C, dtype, affine):
         torch.testing.assert_close(b.grad, b32.grad, **wtol)
 
 
+@pytest.mark.parametrize("C", [64, 130, 768, 1024])
+@pytest.mark.parametrize("x_dtype", [torch.float32, torch.bfloat16])
+def test_adaptive_layer_norm_and_gated_residual(C, x_dtype):
+    """``sigmoid(s) * LN(x) + t`` and ``a + sigmoid(z) * u`` in one kernel each way against the fp32 statement: values,
+    and the gradients of every operand (the residual stream is fp32 under autocast, the conditioning tensors bf16)."""
+    torch.manual_seed(C)
+    shape = (2, 5, 37, C)
+    x = (torch.randn(*shape, device=DEV) * 2 + 0.5).to(x_dtype).requires_grad_(True)
+    s = torch.randn(*shape, device=DEV).bfloat16().requires_grad_(True)
+    t = torch.randn(*shape, device=DEV).bfloat16().requires_grad_(True)
+    ops.census(reset=True)
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        y = ops.ada_norm(x, s, t, 1e-5)
+    assert ops.census().get("ada_norm:sm100", 0) == 1 and y.dtype == torch.bfloat16
+    w = torch.randn(*shape, device=DEV)
+    (y.float() * w).sum().backward()
+    x32, s32, t32 = (v.detach().float().requires_grad_(True) for v in (x, s, t))
+    want = torch.sigmoid(s32) * torch.nn.functional.layer_norm(x32, (C,), None, None, 1e-5) + t32
+    (want * w.bfloat16().float()).sum().backward()  # the incoming gradient reaches the kernel rounded to bf16
+    assert (y.float() - want).abs().max().item() < 0.04
+    for got, ref_t, name in ((x.grad, x32.grad, "x"), (s.grad, s32.grad, "s"), (t.grad, t32.grad, "t")):
+        scale = ref_t.abs().max().item()
+        assert got.dtype == (x_dtype if name == "x" else torch.bfloat16)
+        assert (got.float() - ref_t).abs().max().item() < 0.02 * scale + 1e-3, name
+
+    a = torch.randn(*shape, device=DEV).to(x_dtype).requires_grad_(True)
+    z = torch.randn(*shape, device=DEV).bfloat16().requires_grad_(True)
+    u = torch.randn(*shape, device=DEV).bfloat16().requires_grad_(True)
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        r = ops.gated_residual(a, z, u)
+    assert ops.census().get("gated_residual:sm100", 0) == 1 and r.dtype == x_dtype
+    (r.float() * w).sum().backward()
+    a32, z32, u32 = (v.detach().float().requires_grad_(True) for v in (a, z, u))
+    want = a32 + torch.sigmoid(z32) * u32
+    (want * (w.to(x_dtype).float())).sum().backward()
+    assert (r.float() - want).abs().max().item() < (1e-5 if x_dtype == torch.float32 else 0.04)
+    for got, ref_t, name in ((a.grad, a32.grad, "a"), (z.grad, z32.grad, "z"), (u.grad, u32.grad, "u")):
+        assert (got.float() - ref_t).abs().max().item() < 0.02 * ref_t.abs().max().item() + 1e-3, name
+    # shapes that do not match (a conditioning tensor shared by the samples) take the PyTorch statement
+    ops.census(reset=True)
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        ops.ada_norm(x.detach(), s.detach()[:, :1], t.detach()[:, :1])
+        ops.gated_residual(a.detach(), z.detach()[:, :1], u.detach())
+    assert ops.census().get("ada_norm:torch", 0) == 1 and ops.census().get("gated_residual:torch", 0) == 1
+
+
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
 def test_swiglu(dtype):
     torch.manual_seed(1)
