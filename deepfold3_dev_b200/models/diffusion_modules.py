@@ -243,16 +243,21 @@ class DiffusionTransformerBlock(nn.Module):
         # adaptive LayerNorm and the gated residual updates go through ops.ada_norm / ops.gated_residual: one kernel each
         # way under bf16 autocast on a GPU (the result of ada_norm is then the bf16 tensor the projections read), the
         # same arithmetic written out in PyTorch everywhere else
-        cn = cond_norm * self.attn_cond_norm_w
-        xn = ops.ada_norm(x, self.attn_cond_scale(cn), self.attn_cond_bias(cn), self.attn_norm.eps)
+        # the conditioning LayerNorm's weight is folded into the two projections that read it ((c * w) W^T = c (W * w)^T):
+        # a [c, cs] product instead of an element-wise pass over the [B, S, N, cs] activations, forward and backward
+        wa = self.attn_cond_norm_w
+        xn = ops.ada_norm(x, ops.linear(cond_norm, self.attn_cond_scale.weight * wa, self.attn_cond_scale.bias),
+                          ops.linear(cond_norm, self.attn_cond_bias.weight * wa), self.attn_norm.eps)
         q = self.to_q(xn).view(B, S, N, H, Dk).transpose(2, 3)
-        k = self.to_k(xn).view(B, S, N, H, Dk).transpose(2, 3)
-        v = self.to_v(xn).view(B, S, N, H, Dv).transpose(2, 3)
+        kv = ops.stacked_linear(xn, self.to_k.weight, self.to_v.weight)  # keys and values: one product
+        k = kv[..., : H * Dk].view(B, S, N, H, Dk).transpose(2, 3)
+        v = kv[..., H * Dk :].view(B, S, N, H, Dv).transpose(2, 3)
         out = ops.pair_bias_attention(q, k, v, pair_logits, None, self.scale, fp32_qk=True)
-        out = out.transpose(2, 3).reshape(B, S, N, H * Dv) * torch.sigmoid(self.to_g(xn))
+        out = ops.sigmoid_gate_mul(xn, self.to_g.weight, out.transpose(2, 3).reshape(B, S, N, H * Dv))  # gate in the GEMM epilogue
         x = ops.gated_residual(x, self.zero_cond(single_cond), self.out_proj(out))
-        cn = cond_norm * self.ffn_cond_norm_w
-        xn = ops.ada_norm(x, self.ffn_cond_scale(cn), self.ffn_cond_bias(cn), self.ffn_norm.eps)
+        wf = self.ffn_cond_norm_w
+        xn = ops.ada_norm(x, ops.linear(cond_norm, self.ffn_cond_scale.weight * wf, self.ffn_cond_scale.bias),
+                          ops.linear(cond_norm, self.ffn_cond_bias.weight * wf), self.ffn_norm.eps)
         ff = self.ffn_linear2(ops.swiglu(self.ffn_linear1(xn)))
         return ops.gated_residual(x, self.ffn_zero_cond(single_cond), ff)
 
