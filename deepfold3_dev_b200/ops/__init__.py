@@ -126,6 +126,10 @@ def window_attention(q, k, v, bias, scale: float):
     if nat is not None and nat.has("window_attention") and nat.window_attention_supported(q, k, v, bias):
         _CENSUS["window_attention:sm100"] += 1
         return nat.window_attention(q, k, v, bias, scale)
+    if (nat is not None and nat.has("window_attention") and torch.is_grad_enabled() and "window_attention_train" not in os.environ.get("DF3_DISABLE_OPS", "")
+            and nat.window_attention_train_supported(q, k, v, bias)):
+        _CENSUS["window_attention_train:sm100"] += 1
+        return nat.window_attention_train(q, k, v, bias, scale)
     _CENSUS["window_attention:torch"] += 1
     return ref.window_attention(q, k, v, bias, scale)
 

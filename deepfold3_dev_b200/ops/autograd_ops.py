@@ -770,6 +770,36 @@ def pair_bias_attention(q, k, v, bias, key_mask, scale: float):
     return _Attention.apply(q, k, v, bias, key_mask, float(scale))
 
 
+def window_attention_train_supported(q, k, v, bias) -> bool:
+    """Atom-window attention with gradients: the queries of a window are padded up to its key count and the call runs
+    on the training forward and the fused backward of the pair-bias attention (padded rows receive no gradient and
+    give none). Needs bf16 operands, more keys than queries, and a key count the fused backward holds in tensor memory."""
+    if not (q.is_cuda and q.dim() == 6 and k.dim() == 6 and bias.dim() == 6 and k.shape == v.shape):
+        return False
+    if not (q.dtype == BF16 and k.dtype == BF16 and v.dtype == BF16 and bias.dtype in (BF16, torch.float32)):
+        return False
+    B, S, W, H, Q, D = q.shape
+    keys = k.shape[-2]
+    return (k.shape[:4] == q.shape[:4] and k.shape[-1] == D and D % 8 == 0 and D <= 64 and keys % 8 == 0 and Q <= keys
+            and tuple(bias.shape) == (B, 1, W, H, Q, keys) and bool(K.attention_bwd_fused_supported(keys, D)))
+
+
+def window_attention_train(q, k, v, bias, scale: float):
+    """``q`` ``[B, S, W, H, Q, D]`` (a head-major view of the projection ``[B, S, W, Q, H, D]``), ``k`` / ``v``
+    ``[B, S, W, H, K, D]``, ``bias`` ``[B, 1, W, H, Q, K]``. Windows become the batch axis and samples the row axis of the
+    attention op, so the bias gradient is summed over the samples inside the backward kernel."""
+    B, S, W, H, Q, D = q.shape
+    keys = k.shape[-2]
+    outs = []
+    for b in range(B):
+        qb = q[b].permute(0, 1, 3, 2, 4)  # [S, W, Q, H, D]: the projection's own memory order when q is the usual view
+        qp = torch.nn.functional.pad(qb, (0, 0, 0, 0, 0, keys - Q)).permute(1, 0, 3, 2, 4)  # [W, S, H, keys, D]
+        bp = torch.nn.functional.pad(bias[b, 0], (0, 0, 0, keys - Q))  # [W, H, keys, keys]
+        out = pair_bias_attention(qp, k[b].transpose(0, 1), v[b].transpose(0, 1), bp, None, scale)  # [W, S, H, keys, D]
+        outs.append(out[..., :Q, :].transpose(0, 1))
+    return outs[0].unsqueeze(0) if len(outs) == 1 else torch.stack(outs)
+
+
 def _grid_heads(t, transpose: bool):
     """[B, N1, N2, H, D] -> [B, R, H, L, D] (a view): R is the axis attention does not mix."""
     return t.permute(0, 2, 3, 1, 4) if transpose else t.permute(0, 1, 3, 2, 4)

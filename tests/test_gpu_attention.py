@@ -137,3 +137,36 @@ def test_window_attention_matches_reference(df3, bias_dtype, S, W, Q, K, D):
     ops.census(reset=True)
     ops.window_attention(q.clone().requires_grad_(True), k, v, bias, D**-0.5)
     assert ops.census().get("window_attention:torch", 0) == 1
+
+
+@pytest.mark.parametrize("S,W,Q,K,D", [(3, 5, 32, 128, 32), (2, 3, 24, 72, 16)])
+def test_window_attention_gradients(df3, S, W, Q, K, D):
+    """Training path of the atom-window attention (queries padded to the key count, training forward + fused backward):
+    output and the gradients of q, k, v and of the bias (summed over the samples) against the fp32 statement."""
+    from deepfold3_dev_b200 import ops
+    from deepfold3_dev_b200.ops import reference as ref
+
+    H, B = 4, 1
+    g = torch.Generator(device="cuda").manual_seed(7 * S + W)
+    mk = lambda n: torch.randn(B, S, W, n, H, D, device="cuda", generator=g).bfloat16()  # noqa: E731
+    q0, k0, v0 = mk(Q), mk(K), mk(K)
+    keep = torch.rand(B, 1, W, 1, 1, K, device="cuda", generator=g) > 0.2
+    keep[..., 0] = True
+    b0 = (torch.randn(B, 1, W, H, Q, K, device="cuda", generator=g) + 1e9 * (keep.float() - 1.0)).bfloat16()
+    w = torch.randn(B, S, W, H, Q, D, device="cuda", generator=g)
+
+    def run(fn, cast):
+        leaves = [t.detach().clone().to(cast).requires_grad_(True) for t in (q0, k0, v0, b0)]
+        q, k, v, b = leaves
+        out = fn(q.transpose(-2, -3), k.transpose(-2, -3), v.transpose(-2, -3), b, D**-0.5)
+        (out.float() * w).sum().backward()
+        return out.detach().float(), [t.grad.float() for t in leaves]
+
+    ops.census(reset=True)
+    out, grads = run(ops.window_attention, torch.bfloat16)
+    assert ops.census().get("window_attention_train:sm100", 0) == 1
+    want, want_grads = run(ref.window_attention, torch.float32)
+    assert (out - want).abs().max().item() < 0.03
+    for got, ref_g, name in zip(grads, want_grads, "qkvb"):
+        scale = ref_g.abs().max().item()
+        assert torch.isfinite(got).all() and (got - ref_g).abs().max().item() < 0.03 * scale + 2e-2, (name, (got - ref_g).abs().max().item(), scale)
