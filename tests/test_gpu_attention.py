@@ -133,10 +133,10 @@ def test_window_attention_matches_reference(df3, bias_dtype, S, W, Q, K, D):
     assert (out.float() - want)[:, :, W - 1].abs().max().item() < 0.05
     # the output's memory order follows q, so the model's reshape to [B, S, W, Q, H * D] is a view
     assert out.transpose(-2, -3).reshape(B, S, W, Q, H * D).data_ptr() == out.data_ptr()
-    # with gradients wanted the PyTorch statement runs (autograd), not the forward-only kernel
+    # with gradients wanted the forward-only kernel is not used
     ops.census(reset=True)
     ops.window_attention(q.clone().requires_grad_(True), k, v, bias, D**-0.5)
-    assert ops.census().get("window_attention:torch", 0) == 1
+    assert ops.census().get("window_attention:sm100", 0) == 0
 
 
 @pytest.mark.parametrize("S,W,Q,K,D", [(3, 5, 32, 128, 32), (2, 3, 24, 72, 16)])
