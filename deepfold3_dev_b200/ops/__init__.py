@@ -126,7 +126,11 @@ def window_attention(q, k, v, bias, scale: float):
     if nat is not None and nat.has("window_attention") and nat.window_attention_supported(q, k, v, bias):
         _CENSUS["window_attention:sm100"] += 1
         return nat.window_attention(q, k, v, bias, scale)
-    if (nat is not None and nat.has("window_attention") and torch.is_grad_enabled() and "window_attention_train" not in os.environ.get("DF3_DISABLE_OPS", "")
+    # With gradients the kernels are opt-in (DF3_WINDOW_ATTENTION_TRAIN=1): padding the 32 queries of a window to its 128
+    # keys makes the training forward and the fused backward do four times the row work, and at crop 384 with 48 samples
+    # the step came out 6 ms slower than with the PyTorch statement (814.8 against 820.6 ms on one B200). What the
+    # kernels save is memory: no fp32 logit tensor per block is kept for the backward.
+    if (nat is not None and nat.has("window_attention") and torch.is_grad_enabled() and os.environ.get("DF3_WINDOW_ATTENTION_TRAIN", "0") == "1"
             and nat.window_attention_train_supported(q, k, v, bias)):
         _CENSUS["window_attention_train:sm100"] += 1
         return nat.window_attention_train(q, k, v, bias, scale)

@@ -140,12 +140,13 @@ def test_window_attention_matches_reference(df3, bias_dtype, S, W, Q, K, D):
 
 
 @pytest.mark.parametrize("S,W,Q,K,D", [(3, 5, 32, 128, 32), (2, 3, 24, 72, 16)])
-def test_window_attention_gradients(df3, S, W, Q, K, D):
+def test_window_attention_gradients(df3, S, W, Q, K, D, monkeypatch):
     """Training path of the atom-window attention (queries padded to the key count, training forward + fused backward):
     output and the gradients of q, k, v and of the bias (summed over the samples) against the fp32 statement."""
     from deepfold3_dev_b200 import ops
     from deepfold3_dev_b200.ops import reference as ref
 
+    monkeypatch.setenv("DF3_WINDOW_ATTENTION_TRAIN", "1")  # the kernels are opt-in for training (the default is the statement)
     H, B = 4, 1
     g = torch.Generator(device="cuda").manual_seed(7 * S + W)
     mk = lambda n: torch.randn(B, S, W, n, H, D, device="cuda", generator=g).bfloat16()  # noqa: E731
