@@ -32,8 +32,8 @@ class AtomBlockTerms:
     logit_bias: torch.Tensor  # [B, 1, W, H, Q, K] pair logits + key mask
     q_scale: torch.Tensor
     q_bias: torch.Tensor
-    k_scale: torch.Tensor
-    k_bias: torch.Tensor
+    k_scale: torch.Tensor  # key-side AdaLN scale and shift per QUERY slot [B, 1, W, Q, c]: a key is some window's query atom,
+    k_bias: torch.Tensor  # so keys and values are projected once per atom and gathered into the windows afterwards
     attn_gate: torch.Tensor
     ffn_scale: torch.Tensor
     ffn_bias: torch.Tensor
@@ -180,10 +180,12 @@ class AtomCrossAttTransformer(nn.Module):
         logits = self.pair_logits_proj(ops.layer_norm(pair_cond, self.pair_norm_w, None))  # [B, W, Q, K, nb*H]
         logits = logits.reshape(B, W, Q, K, nb, H).permute(4, 0, 1, 5, 2, 3)  # [nb, B, W, H, Q, K]
         key_bias = 1e9 * (keys_mask.to(logits.dtype) - 1.0)[:, :, None, None, :]
-        qn, kn = ops.layer_norm(queries_single), ops.layer_norm(keys_single)
+        # ``keys_single`` is ``queries_single`` gathered into the windows (``queries_to_keys``), and everything derived
+        # from it is row-wise, so the key-side terms are computed per atom and the gather is left to ``run``
+        qn = ops.layer_norm(queries_single)
         terms = []
         for i, (attn, ffn) in enumerate(zip(self.attn_blocks, self.ffn_blocks, strict=True)):
-            cq, ck, cf = qn * self.attn_cond_w[i], kn * self.k_cond_w[i], qn * self.ffn_cond_w[i]
+            cq, ck, cf = qn * self.attn_cond_w[i], qn * self.k_cond_w[i], qn * self.ffn_cond_w[i]
             vals = (
                 logits[i] + key_bias,
                 torch.sigmoid(self.attn_cond_scale[i](cq)),
@@ -204,12 +206,16 @@ class AtomCrossAttTransformer(nn.Module):
         H, D, K = self.num_heads, self.head_dim, layout.K
         scale = D**-0.5
         for i, (attn, ffn, t) in enumerate(zip(self.attn_blocks, self.ffn_blocks, terms, strict=True)):
-            keys_act = queries_to_keys(layout, queries_act, sample_axis=True)
-            xq = t.q_scale * self.attn_norms[i](queries_act) + t.q_bias
-            xk = t.k_scale * ops.layer_norm(keys_act) + t.k_bias
+            # LayerNorm and the key / value projections act on rows, and the keys of a window are a gather of query
+            # atoms (masked slots get a -1e9 logit bias), so they run once per atom (a quarter of the window-key rows)
+            # and the gather moves the projected keys and values: gather(f(x)) = f(gather(x)) for row-wise f
+            normed = self.attn_norms[i](queries_act)
+            xq = t.q_scale * normed + t.q_bias
+            xk = t.k_scale * normed + t.k_bias
             q = attn["to_q"](xq).view(B, S, W, Q, H, D).transpose(-2, -3)
-            k = attn["to_k"](xk).view(B, S, W, K, H, D).transpose(-2, -3)
-            v = attn["to_v"](xk).view(B, S, W, K, H, D).transpose(-2, -3)
+            kv = queries_to_keys(layout, ops.stacked_linear(xk, attn["to_k"].weight, attn["to_v"].weight), sample_axis=True)
+            k = kv[..., :C].view(B, S, W, K, H, D).transpose(-2, -3)
+            v = kv[..., C:].view(B, S, W, K, H, D).transpose(-2, -3)
             out = ops.window_attention(q, k, v, t.logit_bias, scale)  # [B, S, W, H, Q, D]
             out = out.transpose(-2, -3).reshape(B, S, W, Q, C)
             out = out * torch.sigmoid(attn["to_g"](xq))
