@@ -92,6 +92,13 @@ class ComplexLMTrainer:
             os.makedirs(output_dir, exist_ok=True)
             with open(os.path.join(output_dir, "config.json"), "w") as f:
                 json.dump(to_dict(cfg), f, indent=1)
+        if cfg.train.esmc_weights and not resume:  # warm start; a resumed run already carries trained weights
+            from .esmc import load_esmc
+
+            report = load_esmc(self.model, cfg.train.esmc_weights)
+            if self.rank == 0:
+                with open(os.path.join(output_dir, "esmc_warm_start.json"), "w") as f:
+                    json.dump(report, f, indent=1)
         if resume:
             self.load_checkpoint(resume)
 

@@ -163,6 +163,55 @@ def test_short_training_run_learns(tmp_path):
     assert tr2.step == 40 and json.load(open(os.path.join(tmp_path, "run", "config.json")))["model"]["d_model"] == 64
 
 
+def test_esmc_warm_start_copies_every_tensor(tmp_path):
+    """A stand-in ESM-C checkpoint (its parameter names, a 64-row token table) loads tensor for tensor: names translate,
+    the vocabulary axis takes the leading rows, nothing is left random; misfits and missing tensors are errors."""
+    from deepfold3_dev_b200.complexlm import esmc
+    from deepfold3_dev_b200.complexlm.config import load_experiment
+
+    cfg = _small(norm="layernorm", esmc_compat=True, mup=False)
+    model = ComplexLM(cfg)
+    inverse = {}
+    for name, p in model.named_parameters():
+        module, _, leaf = name.rpartition(".")
+        src = {"embed": "embed", "norm": "transformer.norm", "head.dense": "sequence_head.0", "head.norm": "sequence_head.2",
+               "head.out": "sequence_head.3"}.get(module)  # fmt: skip
+        if src is None:
+            i, rest = module.split(".")[1], ".".join(module.split(".")[2:])
+            src = f"transformer.blocks.{i}." + {"attn.norm": "attn.layernorm_qkv.0", "attn.qkv": "attn.layernorm_qkv.1", "attn.q_norm": "attn.q_ln",
+                                                 "attn.k_norm": "attn.k_ln", "attn.out_proj": "attn.out_proj", "ffn.norm": "ffn.0",
+                                                 "ffn.w_in": "ffn.1", "ffn.w_out": "ffn.3"}[rest]  # fmt: skip
+        inverse[f"{src}.{leaf}"] = name
+    assert all(esmc.translate(k) == v for k, v in inverse.items()) and esmc.translate("transformer.blocks.0.attn.rotary.inv_freq") is None
+    torch.manual_seed(1)
+    state = {}
+    for src, name in inverse.items():
+        p = dict(model.named_parameters())[name]
+        shape = (64, *p.shape[1:]) if name in ("embed.weight", "head.out.weight", "head.out.bias") else p.shape
+        state[src] = torch.randn(*shape)
+    state["transformer.blocks.0.attn.rotary.inv_freq"] = torch.ones(4)
+    path = tmp_path / "esmc.pth"
+    torch.save({"state_dict": state}, path)
+    report = esmc.load_esmc(model, str(path))
+    assert report["copied"] == len(inverse) and report["left_random"] == [] and report["unused_source"] == ["transformer.blocks.0.attn.rotary.inv_freq"]
+    got = dict(model.named_parameters())
+    assert torch.equal(got["embed.weight"], state["embed.weight"][:33]) and torch.equal(got["head.out.bias"], state["sequence_head.3.bias"][:33])
+    assert torch.equal(got["blocks.1.ffn.w_in.weight"], state["transformer.blocks.1.ffn.1.weight"])
+    del state["transformer.norm.weight"]
+    torch.save(state, path)
+    with pytest.raises(ValueError, match="got nothing"):
+        esmc.load_esmc(model, str(path))
+    assert esmc.load_esmc(model, str(path), strict=False)["left_random"] == ["norm.weight"]
+    state["transformer.blocks.0.ffn.1.weight"] = torch.zeros(3, 3)
+    torch.save(state, path)
+    with pytest.raises(ValueError, match="does not fit"):
+        esmc.load_esmc(model, str(path), strict=False)
+    with pytest.raises(ValueError, match="esmc_compat"):
+        esmc.load_esmc(ComplexLM(_small()), str(path))
+    big = load_experiment(os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "configs", "plm-esmc600m.yaml"))
+    assert esmc.matching_release(big.model) == "esmc-600m" and big.model.esmc_compat and not big.model.mup and big.train.lr == 1.0e-4
+
+
 def test_diagnostics_permutation_and_sinks():
     from deepfold3_dev_b200.complexlm.diagnostics import attention_sink_stats, permutation_sensitivity
 
