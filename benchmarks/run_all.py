@@ -23,6 +23,9 @@ STEPS = {
     "modules_backward": [sys.executable, "benchmarks/bench_modules.py", "--backward", "--json", "{out}/modules_backward.json"],
     "memory_inference": [sys.executable, "benchmarks/profile_memory.py", "--mode", "inference"],
     "memory_train": [sys.executable, "benchmarks/profile_memory.py", "--mode", "train", "--tokens", "128", "256", "384"],
+    "verify": [sys.executable, "benchmarks/verify.py", "--json", "{out}/verify.json"],
+    "pairformer_stack": [sys.executable, "benchmarks/bench_pairformer_stack.py", "--json", "{out}/pairformer_stack.json"],
+    "complexlm": [sys.executable, "benchmarks/bench_complexlm.py"],
     "inference": [sys.executable, "benchmarks/bench_inference.py"],
     "train_step": [sys.executable, "bench.py", "--steps", "5", "--warmup", "3"],
 }

@@ -3,6 +3,7 @@
 import json
 import os
 
+import pytest
 import torch
 import torch.nn.functional as F
 
@@ -192,3 +193,31 @@ def test_every_shipped_config_loads():
         wide = DeepFold3(mc)
     names = dict(wide.named_parameters())
     assert not any(".pairformer." in n and "single_attn" in n for n in names)
+
+
+def test_benchmark_plots(tmp_path):
+    """Row lists of the three benchmark kinds render to PNG files (needs matplotlib; without it the tool says so)."""
+    import sys
+
+    sys.path.insert(0, os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "benchmarks"))
+    import plot_results
+
+    files = {
+        "m.json": [{"module": "a", "tokens": 384, "backward": False, "ours_ms": 0.5, "eager_ms": 2.0, "speedup": 4.0}],
+        "p.json": [{"impl": "ours", "regime": "inference", "blocks": 8, "tokens": 384, "ms": 12.7},
+                   {"impl": "reference", "regime": "inference", "blocks": 8, "tokens": 384, "ms": 37.7}],
+        "v.json": [{"module": "a", "out_err_kernels": 1e-3, "out_err_pytorch_bf16": 2e-3, "grad_err_kernels": 3e-3, "grad_err_pytorch_bf16": 2e-3}],
+    }  # fmt: skip
+    for name, rows in files.items():
+        (tmp_path / name).write_text(json.dumps(rows))
+    try:
+        import matplotlib  # noqa: F401
+    except ImportError:
+        with pytest.raises(RuntimeError, match="matplotlib"):
+            plot_results.plot_file(str(tmp_path / "m.json"), str(tmp_path / "plots"))
+        return
+    for name in files:
+        assert os.path.getsize(plot_results.plot_file(str(tmp_path / name), str(tmp_path / "plots"))) > 1000
+    (tmp_path / "x.json").write_text(json.dumps([{"something": 1}]))
+    with pytest.raises(ValueError, match="unknown benchmark"):
+        plot_results.plot_file(str(tmp_path / "x.json"), str(tmp_path / "plots"))
