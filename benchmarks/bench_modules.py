@@ -21,8 +21,8 @@ import sys
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 sys.path.insert(0, ROOT)
 
-FUSED_FEATURES = ("gemm,gated_dual_linear,transition,pair_bias_attention,linear_planes,sigmoid_gate_mul,layer_norm,swiglu,"
-                  "dropout_add,plane_layer_norm")  # fmt: skip
+FUSED_FEATURES = ("gemm,matmul,gated_dual_linear,transition,pair_bias_attention,linear_planes,sigmoid_gate_mul,layer_norm,swiglu,"
+                  "dropout_add,plane_layer_norm,window_attention,ada_norm")  # fmt: skip
 
 
 def gpu_time(fn, warmup: int = 5, iters: int = 20) -> float:
