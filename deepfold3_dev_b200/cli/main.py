@@ -11,6 +11,7 @@ from __future__ import annotations
 
 import logging
 import os
+import re
 
 import click
 
@@ -38,10 +39,60 @@ def cli():
 
 
 # ------------------------------------------------------------------------------------------------ train
-def build_training_stream(tc, mc, info, datasets, data_dir=None, synthetic=False, num_workers=None):
+def _read_id_list(path):
+    """Record ids, one per line (blank lines and ``#`` comments skipped), lower-cased; ``None`` without a file."""
+    if not path:
+        return None
+    with open(path) as f:
+        return {line.split()[0].lower() for line in f if line.strip() and not line.startswith("#")}
+
+
+def _filter_ids(dataset, include, exclude) -> int:
+    """Keep the records of ``dataset`` named in ``include`` (when given) and not named in ``exclude``; returns how many
+    were dropped. Datasets without a record list (synthetic data) are left alone."""
+    records = getattr(dataset, "records", None)
+    if records is None or (include is None and exclude is None):
+        return 0
+    rid = lambda r: str(r["id"] if isinstance(r, dict) else r.id).lower()  # noqa: E731
+    kept = [r for r in records if (include is None or rid(r) in include) and (exclude is None or rid(r) not in exclude)]
+    dropped = len(records) - len(kept)
+    dataset.records = kept
+    if hasattr(dataset, "_anchors"):
+        dataset._anchors = None  # sampling weights follow the surviving records
+    return dropped
+
+
+class EvalLoader:
+    """A fixed, rank-strided set of evaluation examples, re-iterable: every call of the trainer's evaluation sees the
+    same examples (the datasets draw crops from a per-index seed), one example per batch."""
+
+    def __init__(self, parts, limit: int, rank: int, world: int):
+        from ..data import datasets as ds
+
+        self.collate = ds.collate
+        self.items = []
+        for p in parts:
+            self.items += [(p, i) for i in range(len(p))]
+        self.items = self.items[: max(0, limit)][rank::world]
+
+    def __len__(self):
+        return len(self.items)
+
+    def __iter__(self):
+        for part, i in self.items:
+            yield self.collate([part[i]])
+
+
+def build_training_stream(tc, mc, info, datasets, data_dir=None, synthetic=False, num_workers=None, include=None, exclude=None,
+                          eval_cutoff_date=None, return_eval: bool = False):
     """``(stream, sampler)`` for the training loop: the datasets named on the command line (or in the config's mixture),
     weighted cluster sampling per dataset, a weighted mixture over datasets, token-budget batching and a prefetch thread.
-    Shared by ``train`` and by the input-pipeline check of the cluster recipes."""
+    Shared by ``train`` and by the input-pipeline check of the cluster recipes.
+
+    A dataset is ``name:path[:weight[:strategy[:distill[:format[:tpl_struct_space]]]]]``. ``include`` / ``exclude`` are
+    sets of record ids. ``eval_cutoff_date`` splits structure datasets by release date: entries released on or before
+    it train, later ones form the evaluation set; with ``return_eval`` the result is ``(stream, sampler, eval_loader)``
+    (the evaluation loader also takes the recipe's ``eval_datasets``; ``None`` when there is nothing to evaluate on)."""
     from ..data import datasets as ds
     from ..data.samplers import MultiDatasetSampler, WeightedClusterSampler
 
@@ -53,6 +104,7 @@ def build_training_stream(tc, mc, info, datasets, data_dir=None, synthetic=False
                 specs.append(f"{d.name or 'data'}:{d.data_dir}:{d.weight}:{d.strategy}:{int(d.is_distillation)}")
                 extra[d.data_dir] = {"cutoff_date": d.cutoff_date, "crop_weights": d.crop_weights, "format": d.format,
                                      "of3_cache_dir": d.of3_cache_dir}
+    eval_parts = []
     if synthetic or not specs:
         if not synthetic:
             raise click.ClickException("give --dataset / --data-dir, or --synthetic")
@@ -67,17 +119,28 @@ def build_training_stream(tc, mc, info, datasets, data_dir=None, synthetic=False
             weights.append(float(f[2]) if len(f) > 2 and f[2] else 1.0)
             distill = len(f) > 4 and f[4].lower() in ("1", "true", "distill")
             kw = {k: v for k, v in extra.get(path, {}).items() if v}
-            if "cutoff_date" in kw and kw.get("format", "df3") == "df3" and not os.path.isdir(os.path.join(path, "structures")):
+            if len(f) > 5 and f[5]:
+                kw["format"] = f[5]
+            if eval_cutoff_date:
+                kw["cutoff_date"] = eval_cutoff_date
+            structured = kw.get("format", "df3") != "df3" or os.path.isdir(os.path.join(path, "structures"))
+            if "cutoff_date" in kw and not structured:
                 kw.pop("cutoff_date")  # feature directories carry no dates; the cut-off is applied when they are prepared
             d = mc.data
-            parts.append(ds.open_dataset(path, max_tokens=tc.max_tokens, max_atoms=tc.max_atoms, is_distillation=distill,
-                                         seed=tc.seed, atomize_prob=d.atomize_prob, atomize_source=d.atomize_source,
-                                         atomize_max_residues=d.atomize_max_residues,
-                                         pdb_chain_cache_dir=getattr(tc, "pdb_chain_cache_dir", None) or None,
-                                         max_templates=d.max_templates, template_cutoff_days=d.template_cutoff_days,
-                                         max_template_date=d.max_template_date,
-                                         default_template_cutoff_date=d.default_template_cutoff_date, **kw))  # fmt: skip
-            logging.getLogger(__name__).info("dataset %s: %d examples from %s", name, len(parts[-1]), path)
+            common = dict(max_tokens=tc.max_tokens, max_atoms=tc.max_atoms, is_distillation=distill, seed=tc.seed,
+                          pdb_chain_cache_dir=getattr(tc, "pdb_chain_cache_dir", None) or None, max_templates=d.max_templates,
+                          template_cutoff_days=d.template_cutoff_days, max_template_date=d.max_template_date,
+                          default_template_cutoff_date=d.default_template_cutoff_date)  # fmt: skip
+            parts.append(ds.open_dataset(path, atomize_prob=d.atomize_prob, atomize_source=d.atomize_source,
+                                         atomize_max_residues=d.atomize_max_residues, **common, **kw))  # fmt: skip
+            dropped = _filter_ids(parts[-1], include, exclude)
+            logging.getLogger(__name__).info("dataset %s: %d examples from %s%s", name, len(parts[-1]), path,
+                                             f" ({dropped} dropped by the id lists)" if dropped else "")  # fmt: skip
+            if eval_cutoff_date and structured and kw.get("format", "df3") == "df3":
+                later = ds.open_dataset(path, **common, **{**kw, "keep_after": True})  # no atomisation in evaluation
+                _filter_ids(later, include, exclude)
+                if len(later):
+                    eval_parts.append(later)
         samplers = [WeightedClusterSampler(p.weights(), tc.seed + 17 * i, info.rank, info.world_size) for i, p in enumerate(parts)]
         sampler = MultiDatasetSampler(samplers, [len(p) for p in parts], weights, tc.seed)
 
@@ -93,7 +156,16 @@ def build_training_stream(tc, mc, info, datasets, data_dir=None, synthetic=False
     if workers > 0 and not synthetic:
         base = stream
         stream = ds.PrefetchStream(lambda w: base, depth=max(2, getattr(tc, "prefetch_factor", 2) * workers), workers=1)
-    return stream, sampler
+    if not return_eval:
+        return stream, sampler
+    for d in getattr(tc, "eval_datasets", []) or []:  # evaluation sets named by the recipe
+        if d.data_dir and os.path.exists(d.data_dir):
+            kw = {k: v for k, v in {"cutoff_date": d.cutoff_date, "format": d.format, "of3_cache_dir": d.of3_cache_dir}.items() if v}
+            if kw.get("format", "df3") == "df3":
+                kw["keep_after"] = bool(d.cutoff_date)
+            eval_parts.append(ds.open_dataset(d.data_dir, max_tokens=tc.max_tokens, max_atoms=tc.max_atoms, seed=tc.seed, **kw))
+    loader = EvalLoader(eval_parts, int(getattr(tc, "eval_samples", 1024)), info.rank, info.world_size) if eval_parts else None
+    return stream, sampler, (loader if loader is not None and len(loader) else None)
 
 
 @cli.command()
@@ -115,8 +187,16 @@ def build_training_stream(tc, mc, info, datasets, data_dir=None, synthetic=False
 @click.option("--dataset", "datasets", multiple=True, help="name:path[:weight[:strategy[:distill]]] (repeatable).")
 @click.option("--synthetic", is_flag=True, help="Train on generated examples of the configured crop size.")
 @click.option("--num-workers", type=int, default=None, help="Background data threads (default: training.num_workers).")
+@click.option("--ccd", type=click.Path(exists=True), default=None, help="components.cif[.gz] or a JSON conformer table.")
+@click.option("--ccd-cache", type=click.Path(exists=True), default=None, help="JSON conformer table from build-ccd-cache.")
+@click.option("--include-list", type=click.Path(exists=True), default=None, help="Record ids to train on, one per line.")
+@click.option("--exclude-list", type=click.Path(exists=True), default=None, help="Record ids to leave out, one per line.")
+@click.option("--eval-cutoff-date", default=None, help="YYYY-MM-DD: structure entries released later form the evaluation set.")
+@click.option("--mmcif-dir", type=click.Path(exists=True), default=None,
+              help="Local mmCIF mirror: template chains missing from the per-chain cache are read from it.")
 def train(data_dir, output, params, resume, configs, lr, max_steps, max_tokens, grad_accum, seed, deterministic, dtype,
-          wandb_project, wandb_entity, overrides, datasets, synthetic, num_workers):  # fmt: skip
+          wandb_project, wandb_entity, overrides, datasets, synthetic, num_workers, ccd, ccd_cache, include_list,
+          exclude_list, eval_cutoff_date, mmcif_dir):  # fmt: skip
     """Train the model (one process per GPU; launch with torch.distributed.run for several)."""
     _setup_logging()
     import faulthandler
@@ -140,9 +220,19 @@ def train(data_dir, output, params, resume, configs, lr, max_steps, max_tokens, 
         tc.deterministic = True
         apply_det_recipe()
     info = init_process_group(tc.collective_timeout_s)
-    stream, sampler = build_training_stream(tc, mc, info, list(datasets), data_dir, synthetic, num_workers)
+    for table in (ccd, ccd_cache):
+        if table:
+            from ..data import ref_conformers
+
+            ref_conformers.set_ccd_source(table)  # a JSON table is read now, a components.cif is looked up per component
+    if mmcif_dir:
+        os.environ["DF3_TEMPLATE_MMCIF_DIR"] = mmcif_dir  # read by the datasets' template loader as the fallback source
+    stream, sampler, eval_loader = build_training_stream(
+        tc, mc, info, list(datasets), data_dir, synthetic, num_workers, include=_read_id_list(include_list),
+        exclude=_read_id_list(exclude_list), eval_cutoff_date=eval_cutoff_date, return_eval=True,
+    )  # fmt: skip
     trackers = build_trackers(output, info.is_main, wandb_project, wandb_entity, {"training": _plain(tc), "model": _plain(mc)})
-    trainer = Trainer(tc, mc, train_loader=stream, sampler=sampler if hasattr(sampler, "state_dict") else None,
+    trainer = Trainer(tc, mc, train_loader=stream, eval_loader=eval_loader, sampler=sampler if hasattr(sampler, "state_dict") else None,
                       dist_info=info, trackers=trackers)  # fmt: skip
     if resume == "auto":
         resume = trainer.ckpt.find_latest()
@@ -164,6 +254,9 @@ def _inference_options(f):
         click.option("--device", default=None),
         click.option("--optim", type=click.Choice(["none", "inference", "inference-cueq", "train-matched"]), default="inference"),
         click.option("--precision", type=click.Choice(list(DTYPES)), default="bf16"),
+        click.option("--hoist-sampler/--no-hoist-sampler", default=True,
+                     help="Compute everything that does not depend on the noise level once per prediction and replay the "
+                          "denoiser from a CUDA graph (default). --no-hoist-sampler runs the per-block statement eagerly."),
         click.option("--msa-search", type=click.Choice(["none", "server", "local"]), default="none", show_default=True,
                      help="Search alignments (and template hits) for protein chains of a JSON job that carry none: the ColabFold "
                           "MMseqs2 API, or the staged local pipeline over --msa-db-dir."),
@@ -272,6 +365,63 @@ def _attach_templates(inp, hits_path: str, mmcif_dir: str | None, cache_dir: str
         inp.features.update(tpl.template_features(n, chains))
 
 
+def _apply_hoist(hoist: bool) -> None:
+    if not hoist:
+        os.environ["DF3_GRAPH_SAMPLER"] = "0"
+        os.environ["DF3_DIFFUSION_FAST"] = "0"
+
+
+def parse_inputs_file(path: str) -> list[tuple[str, str | None, dict]]:
+    """Lines of an ``--inputs-file``: ``json_path [output_dir] [key=value ...]``, tab-separated when the line holds a tab,
+    else split on blanks; ``#`` starts a comment. Known keys: ``seeds=42,66`` (this job's seeds), and for a guidance
+    sweep ``group=NAME`` and ``pairs=H:A,L:A``. Returns ``[(json_path, output_dir or None, {key: value})]``."""
+    out = []
+    with open(path) as f:
+        for raw in f:
+            line = raw.split("#", 1)[0].strip()
+            if not line:
+                continue
+            fields = [x.strip() for x in line.split("\t")] if "\t" in line else line.split()
+            fields = [x for x in fields if x]
+            keyed = [x for x in fields[1:] if re.match(r"[a-z_]+=", x)]
+            plain = [x for x in fields[1:] if x not in keyed]
+            extras = dict(x.split("=", 1) for x in keyed)
+            out.append((fields[0], plain[0] if plain else None, extras))
+    return out
+
+
+def load_guidance_sweep(path: str) -> dict[str, list[tuple[str, tuple[str, ...]]]]:
+    """``{"groups": {GROUP: [{"name": N, "guidance": ["W@TARGET", ...]}, ...]}}`` -> ``{GROUP: [(name, specs)]}``. Every
+    entry is one guidance setting; its results go to the line's output directory with ``{cfg}`` replaced by the name."""
+    import json
+
+    with open(path) as f:
+        data = json.load(f)
+    groups = {}
+    for group, items in data["groups"].items():
+        entries = [(str(it["name"]), tuple(str(g) for g in it.get("guidance", ()))) for it in items]
+        names = [n for n, _ in entries]
+        if len(set(names)) != len(names):
+            raise click.UsageError(f"--guidance-sweep: duplicate entry names in group {group!r}")
+        groups[group] = entries
+    return groups
+
+
+def sweep_entries(groups, out_dir: str, extras: dict) -> list[tuple[str, str, tuple[str, ...]]]:
+    """``[(entry name, output directory, guidance specs)]`` for one inputs-file line under a guidance sweep."""
+    group = extras.get("group")
+    if group not in groups:
+        raise click.UsageError(f"--guidance-sweep: {out_dir} names group {group!r}; known groups: {sorted(groups)}")
+    if "{cfg}" not in out_dir:
+        raise click.UsageError(f"--guidance-sweep: the output directory {out_dir} has no {{cfg}} placeholder")
+    out = []
+    for name, specs in groups[group]:
+        if any("{pairs}" in t for t in specs) and not extras.get("pairs"):
+            raise click.UsageError(f"--guidance-sweep: entry {name!r} needs pairs=... on the line of {out_dir}")
+        out.append((name, out_dir.replace("{cfg}", name), tuple(t.replace("{pairs}", extras.get("pairs", "")) for t in specs)))
+    return out
+
+
 def _msa_search_fn(mode: str, db_dir: str | None, cache_dir: str | None):
     """The ``msa_search`` argument of ``parse_json_input`` for the ``--msa-search`` choice."""
     from ..data.parse import json_input
@@ -325,12 +475,13 @@ def _guidance_terms(specs):
 @click.option("--template-cache", type=click.Path(), default=None, help="Directory for the prepared template files.")
 @_inference_options
 def inference(msa, json_path, sequence, mol_type, output, templates_path, pdb_mmcif_dir, template_cache, params, num_recycles, num_samples, msa_crop_size, snapshot,
-              seeds, device, optim, precision, msa_search, msa_db_dir, msa_cache_dir, logits_scheme, bucket, sample_chunk, guidance, allow_guidance_overlap,
+              seeds, device, optim, precision, hoist_sampler, msa_search, msa_db_dir, msa_cache_dir, logits_scheme, bucket, sample_chunk, guidance, allow_guidance_overlap,
               restraints, restraint_pairs, repels, restraint_rigid, restraint_after_step, restraint_after_sigma,
               restraint_max_step, restraint_weight, msa_pairing, matmul_precision, plot_confidences,
               allow_missing_keys, ccd, det):  # fmt: skip
     """Predict the structure of one job."""
     _setup_logging()
+    _apply_hoist(hoist_sampler)
     import torch
 
     from ..data.inference_input import InferenceInput
@@ -389,9 +540,12 @@ def inference(msa, json_path, sequence, mol_type, output, templates_path, pdb_mm
 @click.option("--save-distogram/--no-save-distogram", default=True)
 @click.option("--shard", default=None, help="I/N: take every N-th job starting at I (one process per GPU; default from RANK / WORLD_SIZE).")
 @click.option("--pdb-mmcif-dir", type=click.Path(exists=True), default=None, help="Local mmCIF mirror for template hits named by PDB id.")
+@click.option("--guidance-sweep", type=click.Path(exists=True), default=None,
+              help="JSON of guidance settings per group; every inputs-file line names its group (group=...), its output "
+                   "directory carries {cfg}, and {pairs} in a guidance value takes the line's pairs=... Not with --guidance.")
 @_inference_options
-def inference_batch(inputs_file, output_template, skip_existing, save_distogram, shard, pdb_mmcif_dir, params, num_recycles, num_samples,
-                    msa_crop_size, snapshot, seeds, device, optim, precision, msa_search, msa_db_dir, msa_cache_dir, logits_scheme, bucket, sample_chunk,
+def inference_batch(inputs_file, output_template, skip_existing, save_distogram, shard, pdb_mmcif_dir, guidance_sweep, params, num_recycles, num_samples,
+                    msa_crop_size, snapshot, seeds, device, optim, precision, hoist_sampler, msa_search, msa_db_dir, msa_cache_dir, logits_scheme, bucket, sample_chunk,
                     guidance, allow_guidance_overlap, restraints, restraint_pairs, repels, restraint_rigid,
                     restraint_after_step, restraint_after_sigma, restraint_max_step, restraint_weight, msa_pairing,
                     matmul_precision, plot_confidences, allow_missing_keys, ccd, det):  # fmt: skip
@@ -417,26 +571,36 @@ def inference_batch(inputs_file, output_template, skip_existing, save_distogram,
         torch.set_float32_matmul_precision(matmul_precision)
     from ..data.parse.json_input import parse_json_input
 
-    with open(inputs_file) as f:
-        paths = [line.strip() for line in f if line.strip() and not line.startswith("#")]
+    _apply_hoist(hoist_sampler)
+    if guidance_sweep and guidance:
+        raise click.UsageError("--guidance-sweep and --guidance exclude each other")
+    groups = load_guidance_sweep(guidance_sweep) if guidance_sweep else None
+    lines = parse_inputs_file(inputs_file)
     if part is not None:
-        paths = paths[part[0] :: part[1]]
+        lines = lines[part[0] :: part[1]]
     done = failed = 0
     search_fn = _msa_search_fn(msa_search, msa_db_dir, msa_cache_dir)
-    for p in paths:
+    for p, line_out, extras in lines:
         try:
+            job_seeds = [int(x) for x in extras["seeds"].split(",")] if extras.get("seeds") else (list(seeds) or None)
             for job in parse_json_input(p, msa_search=search_fn):
                 inp = InferenceInput.from_job(job, msa_crop_size, msa_pairing, pdb_mmcif_dir)
-                terms, rkw = _job_steering(inp, guidance, allow_guidance_overlap, restraints, restraint_pairs, repels,
-                                           restraint_weight, restraint_rigid, restraint_after_step, restraint_after_sigma,
-                                           restraint_max_step)  # fmt: skip
-                out_dir = output_template.format(name=inp.name)
-                run_job(model, inp, out_dir, device, list(seeds) or None, num_recycles, num_samples,
-                        getattr(torch, DTYPES[precision]), bucket, sample_chunk, skip_existing, logits_scheme,
-                        save_distogram, terms, rkw, manifest_fields={"params": params, "input": p})  # fmt: skip
-                if plot_confidences:
-                    _plot_outputs(out_dir)
+                base_dir = (line_out or output_template).replace("{name}", inp.name)
+                # one run per guidance setting of the line's sweep group (each run computes its own trunk), or one run
+                runs = sweep_entries(groups, base_dir, extras) if groups is not None else [(None, base_dir, tuple(guidance))]
+                for cfg_name, out_dir, specs in runs:
+                    terms, rkw = _job_steering(inp, specs, allow_guidance_overlap, restraints, restraint_pairs, repels,
+                                               restraint_weight, restraint_rigid, restraint_after_step, restraint_after_sigma,
+                                               restraint_max_step)  # fmt: skip
+                    fields = {"params": params, "input": p} | ({"guidance_setting": cfg_name} if cfg_name else {})
+                    run_job(model, inp, out_dir, device, job_seeds, num_recycles, num_samples,
+                            getattr(torch, DTYPES[precision]), bucket, sample_chunk, skip_existing, logits_scheme,
+                            save_distogram, terms, rkw, manifest_fields=fields)  # fmt: skip
+                    if plot_confidences:
+                        _plot_outputs(out_dir)
                 done += 1
+        except click.UsageError:
+            raise
         except Exception as exc:  # noqa: BLE001 - one bad job must not stop the batch
             failed += 1
             logging.getLogger(__name__).exception("job %s failed: %s", p, exc)

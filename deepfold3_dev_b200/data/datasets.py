@@ -322,12 +322,19 @@ class StructureDataset:
             pdb = str(hit.get("template_pdb_id") or hit.get("pdbId"))
             chain_id = str(hit.get("template_chain_id") or hit.get("chainId") or "A")
             path = tpl.chain_cache_path(self.pdb_chain_cache_dir, pdb, chain_id)
-            if path is None:
-                self.templates_dropped += 1
-                continue
             try:
                 q, t = tpl.hit_index_pairs(hit)
-                out.append(tpl.load_template_chain(path, q, t))
+                if path is not None:
+                    out.append(tpl.load_template_chain(path, q, t))
+                    continue
+                # not in the per-chain cache: read the entry from the local mmCIF mirror, if one was named
+                mirror = os.environ.get("DF3_TEMPLATE_MMCIF_DIR")
+                src = tpl.find_pdb_mmcif(pdb, mirror) if mirror else None
+                chain_obj = tpl.template_chain_from_mmcif(src, chain_id, q, t) if src else None
+                if chain_obj is None:
+                    self.templates_dropped += 1
+                else:
+                    out.append(chain_obj)
             except (KeyError, ValueError, OSError):
                 self.templates_dropped += 1
         self.templates_used += len(out)

@@ -67,3 +67,42 @@ def test_inference_batch_shards_jobs(tmp_path, monkeypatch):
     assert sorted(os.listdir(tmp_path / "out")) == ["j1"] and "1 jobs done" in res.output
     bad = CliRunner().invoke(main.cli, ["inference-batch", "--inputs-file", str(tmp_path / "list.txt"), "--shard", "2/2"])
     assert bad.exit_code != 0
+
+
+def test_inference_batch_guidance_sweep_and_line_columns(tmp_path, monkeypatch):
+    main = importlib.import_module("deepfold3_dev_b200.cli.main")
+
+    def tiny(params, device, optim, snapshot, allow_missing_keys, det, ccd):
+        from deepfold3_dev_b200.models.model import DeepFold3
+
+        cfg = tiny_config()
+        cfg.diffusion.steps = 2
+        return DeepFold3(cfg).eval(), cfg, torch.device("cpu")
+
+    monkeypatch.setattr(main, "_prepare_model", tiny)
+    job = [{"name": "ab", "dialect": "deepfold3", "modelSeeds": [0],
+            "sequences": [{"protein": {"id": "H", "sequence": "MKTAYIAKQR"}}, {"protein": {"id": "A", "sequence": "GSHMSEQNNT"}}]}]  # fmt: skip
+    (tmp_path / "ab.json").write_text(json.dumps(job))
+    sweep = {"groups": {"antibody": [{"name": "plain", "guidance": []}, {"name": "iface2", "guidance": ["2.0@{pairs}"]}]}}
+    (tmp_path / "sweep.json").write_text(json.dumps(sweep))
+    out = tmp_path / "runs" / "{cfg}" / "ab"
+    (tmp_path / "list.txt").write_text(f"# json  out  columns\n{tmp_path / 'ab.json'}\t{out}\tgroup=antibody\tpairs=H:A\tseeds=5,6\n")
+    lines = main.parse_inputs_file(str(tmp_path / "list.txt"))
+    assert lines == [(str(tmp_path / "ab.json"), str(out), {"group": "antibody", "pairs": "H:A", "seeds": "5,6"})]
+    args = ["inference-batch", "--inputs-file", str(tmp_path / "list.txt"), "--guidance-sweep", str(tmp_path / "sweep.json"),
+            "--num-recycles", "0", "--num-samples", "1", "--precision", "fp32", "--no-bucket", "--no-hoist-sampler"]  # fmt: skip
+    res = CliRunner().invoke(main.cli, args)
+    assert res.exit_code == 0, res.output + repr(res.exception)
+    assert sorted(os.listdir(tmp_path / "runs")) == ["iface2", "plain"]
+    for name in ("iface2", "plain"):
+        run = tmp_path / "runs" / name / "ab"
+        assert {"seed-5_sample-0", "seed-6_sample-0"} <= set(os.listdir(run))  # the line's seeds, not the job's
+        assert json.loads((run / "run_manifest.json").read_text())["guidance_setting"] == name
+    # the sweep excludes --guidance, needs {cfg} in the directory, a known group, and pairs= where an entry uses {pairs}
+    assert CliRunner().invoke(main.cli, args + ["--guidance", "2.0"]).exit_code != 0
+    (tmp_path / "list.txt").write_text(f"{tmp_path / 'ab.json'}\t{tmp_path / 'flat'}\tgroup=antibody\tpairs=H:A\n")
+    assert CliRunner().invoke(main.cli, args).exit_code != 0
+    (tmp_path / "list.txt").write_text(f"{tmp_path / 'ab.json'}\t{out}\tgroup=other\n")
+    assert CliRunner().invoke(main.cli, args).exit_code != 0
+    (tmp_path / "list.txt").write_text(f"{tmp_path / 'ab.json'}\t{out}\tgroup=antibody\n")
+    assert CliRunner().invoke(main.cli, args).exit_code != 0

@@ -235,6 +235,47 @@ def test_structure_dataset_on_the_fly(tmp_path):
         open_dataset(str(tmp_path / "out"), max_tokens=64, atomize_prob=0.5, atomize_source="sideways")[0]
 
 
+def test_training_stream_id_lists_and_evaluation_split(tmp_path):
+    """The stream builder behind ``train``: include / exclude lists, the release-date split into training and evaluation
+    sets, the extended dataset spec, and an evaluation loader that yields the same examples on every pass."""
+    from deepfold3_dev_b200.cli.main import _read_id_list, build_training_stream
+    from deepfold3_dev_b200.config.schema import ModelConfig, TrainingConfig
+    from deepfold3_dev_b200.parallel.dist import DistInfo
+
+    src = tmp_path / "src"
+    src.mkdir()
+    for name, date in (("aaa1", "2019-05-01"), ("bbb2", "2020-06-01"), ("ccc3", "2022-03-01"), ("ddd4", "2023-01-01")):
+        (src / f"{name}.cif").write_text(_mini_cif().replace("data_TEST", f"data_{name.upper()}").replace("_entry.id TEST", f"_entry.id {name.upper()}")
+                                         .replace("2020-01-02", date))  # fmt: skip
+    out = tmp_path / "out"
+    prepare_directory(str(src), str(out), StructureFilterConfig(min_residues=2))
+    tc, mc = TrainingConfig(max_tokens=16, max_atoms=0, batch_size_per_rank=1, num_workers=0, eval_samples=8), ModelConfig()
+    spec = [f"pdb:{out}:1.0:weighted:0:df3"]
+
+    stream, sampler = build_training_stream(tc, mc, DistInfo(), spec)
+    batch = next(iter(stream))
+    assert batch["res_type"].shape == (1, 16) and batch["_record_id"][0] in ("aaa1", "bbb2", "ccc3", "ddd4")  # padded to the token budget
+
+    (tmp_path / "inc.txt").write_text("# ids\nAAA1\nbbb2 extra columns are ignored\n\nccc3\n")
+    (tmp_path / "exc.txt").write_text("bbb2\n")
+    inc, exc = _read_id_list(str(tmp_path / "inc.txt")), _read_id_list(str(tmp_path / "exc.txt"))
+    assert inc == {"aaa1", "bbb2", "ccc3"} and _read_id_list(None) is None
+    stream, _ = build_training_stream(tc, mc, DistInfo(), spec, include=inc, exclude=exc)
+    seen = {next(stream)["_record_id"][0] for _ in range(12)}
+    assert seen == {"aaa1", "ccc3"}
+
+    stream, _, loader = build_training_stream(tc, mc, DistInfo(), spec, eval_cutoff_date="2021-01-01", return_eval=True)
+    assert {next(stream)["_record_id"][0] for _ in range(12)} == {"aaa1", "bbb2"}
+    first = [b["_record_id"][0] for b in loader]
+    assert sorted(first) == ["ccc3", "ddd4"] and [b["_record_id"][0] for b in loader] == first  # re-iterable, same order
+    a, b = next(iter(loader)), next(iter(loader))
+    assert torch.equal(a["res_type"], b["res_type"]) and torch.equal(a["ref_pos"], b["ref_pos"])  # the same crop every time
+    # two ranks split the evaluation set; without a date split and without configured sets there is nothing to evaluate
+    halves = [build_training_stream(tc, mc, DistInfo(rank=r, world_size=2), spec, eval_cutoff_date="2021-01-01", return_eval=True)[2] for r in (0, 1)]
+    assert sorted(len(h) for h in halves) == [1, 1]
+    assert build_training_stream(tc, mc, DistInfo(), spec, return_eval=True)[2] is None
+
+
 def test_crystallization_aids_are_dropped_from_xray_entries(tmp_path):
     sulfate = _mini_cif().replace(" ZN ZN . ZN C 2", " S S . SO4 C 2")
     (tmp_path / "s.cif").write_text(sulfate)
