@@ -586,7 +586,8 @@ def inference_batch(inputs_file, output_template, skip_existing, save_distogram,
             for job in parse_json_input(p, msa_search=search_fn):
                 inp = InferenceInput.from_job(job, msa_crop_size, msa_pairing, pdb_mmcif_dir)
                 base_dir = (line_out or output_template).replace("{name}", inp.name)
-                # one run per guidance setting of the line's sweep group (each run computes its own trunk), or one run
+                # one run per guidance setting of the line's sweep group, all on one trunk per seed; or one run
+                shared = {} if groups is not None else None
                 runs = sweep_entries(groups, base_dir, extras) if groups is not None else [(None, base_dir, tuple(guidance))]
                 for cfg_name, out_dir, specs in runs:
                     terms, rkw = _job_steering(inp, specs, allow_guidance_overlap, restraints, restraint_pairs, repels,
@@ -595,7 +596,7 @@ def inference_batch(inputs_file, output_template, skip_existing, save_distogram,
                     fields = {"params": params, "input": p} | ({"guidance_setting": cfg_name} if cfg_name else {})
                     run_job(model, inp, out_dir, device, job_seeds, num_recycles, num_samples,
                             getattr(torch, DTYPES[precision]), bucket, sample_chunk, skip_existing, logits_scheme,
-                            save_distogram, terms, rkw, manifest_fields=fields)  # fmt: skip
+                            save_distogram, terms, rkw, manifest_fields=fields, trunk_cache=shared)  # fmt: skip
                     if plot_confidences:
                         _plot_outputs(out_dir)
                 done += 1

@@ -61,17 +61,27 @@ def seed_done(out_dir: str, seed: int, num_samples: int) -> bool:
 
 @torch.inference_mode()
 def predict(model, features: dict, seed: int, num_recycles: int, num_samples: int, device, dtype=torch.bfloat16,
-            use_bucket: bool = True, sample_chunk: int = 0, guidance_terms=None, restraint_kwargs=None):  # fmt: skip
-    """One seed: returns the unpadded ``DeepFold3Output`` with ``num_samples`` samples."""
-    feats = {k: (v.to(device) if isinstance(v, torch.Tensor) else v) for k, v in features.items()}
-    n = int(feats["res_type"].shape[0])
-    if use_bucket:
-        feats, n = bucket.pad_features(feats)
+            use_bucket: bool = True, sample_chunk: int = 0, guidance_terms=None, restraint_kwargs=None,
+            trunk_cache: dict | None = None):  # fmt: skip
+    """One seed: returns the unpadded ``DeepFold3Output`` with ``num_samples`` samples. ``trunk_cache`` (a dict the
+    caller owns) keeps the padded features, the trunk output and the distogram of every (seed, recycles) it has seen, so
+    that several guidance or restraint settings of one job run the trunk once per seed (reference:
+    scripts/inference_batch.py:360-460, one trunk shared by the entries of a guidance sweep)."""
     amp = torch.autocast(device_type=torch.device(device).type, dtype=dtype, enabled=dtype != torch.float32)
     kw = dict(restraint_kwargs or {})
+    key = (seed, num_recycles)
     with amp:
-        trunk = model.run_evoformer(feats, num_recycles, seed=seed)
-        disto = model.distogram_head(trunk[0]["pair"])
+        if trunk_cache is not None and key in trunk_cache:
+            feats, n, trunk, disto = trunk_cache[key]
+        else:
+            feats = {k: (v.to(device) if isinstance(v, torch.Tensor) else v) for k, v in features.items()}
+            n = int(feats["res_type"].shape[0])
+            if use_bucket:
+                feats, n = bucket.pad_features(feats)
+            trunk = model.run_evoformer(feats, num_recycles, seed=seed)
+            disto = model.distogram_head(trunk[0]["pair"])
+            if trunk_cache is not None:
+                trunk_cache[key] = (feats, n, trunk, disto)
         parts = []
         for ci, k in enumerate(sample_chunks(num_samples, sample_chunk)):
             parts.append(model.sample_from_trunk(feats, trunk, seed=sample_chunk_seed(seed, ci), num_samples=k,
@@ -152,7 +162,7 @@ def write_seed(out_dir: str, job_name: str, seed: int, output, features: dict, c
 def run_job(model, inp, out_dir: str, device, seeds=None, num_recycles: int = 10, num_samples: int = 5,
             dtype=torch.bfloat16, use_bucket: bool = True, sample_chunk: int = 0, skip_existing: bool = False,
             logits_scheme: str = "int8_softmax", save_distogram: bool = True, guidance_terms=None, restraint_kwargs=None,
-            manifest_fields: dict | None = None, dist_info=None) -> list[dict]:  # fmt: skip
+            manifest_fields: dict | None = None, dist_info=None, trunk_cache: dict | None = None) -> list[dict]:  # fmt: skip
     """All seeds of one job; returns the per-sample summaries (also written as CSV / JSON). With a ``dist_info`` of more
     than one rank every prediction is spread over the ranks (``predict_distributed``): each rank writes the sample
     folders of its own samples, rank 0 the files that summarise the job."""
@@ -178,7 +188,7 @@ def run_job(model, inp, out_dir: str, device, seeds=None, num_recycles: int = 10
                                                    use_bucket, True, guidance_terms, restraint_kwargs)  # fmt: skip
             else:
                 out = predict(model, inp.features, seed, num_recycles, num_samples, device, dtype, use_bucket, sample_chunk,
-                              guidance_terms, restraint_kwargs)  # fmt: skip
+                              guidance_terms, restraint_kwargs, trunk_cache)  # fmt: skip
             if torch.cuda.is_available() and torch.device(device).type == "cuda":
                 torch.cuda.synchronize()
             timings[f"seed-{seed}"] = time.time() - t0

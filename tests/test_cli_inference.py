@@ -72,12 +72,17 @@ def test_inference_batch_shards_jobs(tmp_path, monkeypatch):
 def test_inference_batch_guidance_sweep_and_line_columns(tmp_path, monkeypatch):
     main = importlib.import_module("deepfold3_dev_b200.cli.main")
 
+    trunk_runs = []
+
     def tiny(params, device, optim, snapshot, allow_missing_keys, det, ccd):
         from deepfold3_dev_b200.models.model import DeepFold3
 
         cfg = tiny_config()
         cfg.diffusion.steps = 2
-        return DeepFold3(cfg).eval(), cfg, torch.device("cpu")
+        model = DeepFold3(cfg).eval()
+        inner = model.run_evoformer
+        model.run_evoformer = lambda *a, **k: (trunk_runs.append(k.get("seed")), inner(*a, **k))[1]
+        return model, cfg, torch.device("cpu")
 
     monkeypatch.setattr(main, "_prepare_model", tiny)
     job = [{"name": "ab", "dialect": "deepfold3", "modelSeeds": [0],
@@ -94,6 +99,7 @@ def test_inference_batch_guidance_sweep_and_line_columns(tmp_path, monkeypatch):
     res = CliRunner().invoke(main.cli, args)
     assert res.exit_code == 0, res.output + repr(res.exception)
     assert sorted(os.listdir(tmp_path / "runs")) == ["iface2", "plain"]
+    assert sorted(trunk_runs) == [5, 6]  # two settings, two seeds: the trunk ran once per seed
     for name in ("iface2", "plain"):
         run = tmp_path / "runs" / name / "ab"
         assert {"seed-5_sample-0", "seed-6_sample-0"} <= set(os.listdir(run))  # the line's seeds, not the job's
