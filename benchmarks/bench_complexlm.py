@@ -103,6 +103,9 @@ def main(argv=None) -> int:
                "published_b200": PUBLISHED if args.token_budget == PUBLISHED["token_budget"] else None}  # fmt: skip
         if row["published_b200"]:
             row["x_vs_published"] = round(PUBLISHED["ms_per_step"] / ms, 2)
+        from deepfold3_dev_b200.ops import autograd_ops
+
+        autograd_ops.check_status()  # a kernel wait that ran out would make the figure meaningless: fail instead
         print(json.dumps(row), flush=True)
     return 0
 

@@ -351,11 +351,11 @@ def _attach_templates(inp, hits_path: str, mmcif_dir: str | None, cache_dir: str
             for h in parse_hhr(text):
                 pairs = sorted(h.query_to_hit_mapping.items())
                 rows.append({"pdb_id": h.pdb_id.lower(), "chainId": h.chain_id, "queryIndices": [q for q, _ in pairs],
-                             "templateIndices": [t for _, t in pairs]})  # fmt: skip
+                             "templateIndices": [t for _, t in pairs], "seq": h.hit_sequence.replace("-", "")})  # fmt: skip
             chains = []
             for r in rows:
                 src = tpl.find_pdb_mmcif(r["pdb_id"], mmcif_dir)
-                hit = tpl.template_chain_from_mmcif(src, r["chainId"], r["queryIndices"], r["templateIndices"]) if src else None
+                hit = tpl.template_chain_from_mmcif(src, r["chainId"], r["queryIndices"], r["templateIndices"], r["seq"]) if src else None
                 if hit is not None:
                     chains.append(hit)
         else:

@@ -220,7 +220,8 @@ def _templates(spec: dict, base_dir: str) -> list[dict]:
                 for h in parse_hhr(f.read()):
                     pairs = [(q, t) for q, t in zip(h.indices_query, h.indices_hit) if q != -1 and t != -1]
                     hits.append({"pdbId": h.pdb_id, "chainId": h.chain_id, "queryIndices": [q for q, _ in pairs],
-                                 "templateIndices": [t for _, t in pairs], "eValue": h.e_value})  # fmt: skip
+                                 "templateIndices": [t for _, t in pairs], "eValue": h.e_value,
+                                 "templateSequence": h.hit_sequence.replace("-", "")})  # fmt: skip
             root = os.path.dirname(path)
         else:
             with open(path) as f:

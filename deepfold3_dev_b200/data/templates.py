@@ -105,11 +105,44 @@ def parse_m8(text: str) -> list[dict]:
     return hits
 
 
-def template_chain_from_mmcif(path: str, chain_id: str | None, query_indices, template_indices) -> TemplateChain | None:
+def reconcile_hit_with_chain(mapping: dict[int, int], hit_sequence: str, hit_start: int, chain_sequence: str,
+                             min_identity: float = 0.5) -> dict[int, int] | None:  # fmt: skip
+    """Move a query -> target mapping from the sequence the search database holds to the sequence of the structure file.
+
+    Search tools align against a sequence database built from deposited SEQRES records; the structure file read later
+    may be a newer revision of the entry (residues added or removed at the ends, a corrected stretch), so a target
+    position of the hit need not be the same position of the chain. ``hit_sequence`` is the ungapped target residues of
+    the hit, the first of them at position ``hit_start`` (0-based) of the database sequence; ``mapping`` values count
+    positions of that database sequence. The hit residues are aligned to ``chain_sequence`` by longest common blocks:
+    positions inside a common block and inside an equally long substituted stretch are carried over, positions the
+    chain does not have are dropped. When the hit already sits at ``hit_start`` in the chain the mapping comes back
+    unchanged. ``None`` when fewer than ``min_identity`` of the hit's residues find their residue in the chain (the
+    wrong chain or entry). Same purpose as the reference's gap-insertion realignment
+    (data/parse/template_realign.py:21-163), which assumes the structure only loses residues relative to SEQRES.
+    """
+    import difflib
+
+    if chain_sequence[hit_start : hit_start + len(hit_sequence)] == hit_sequence:
+        return dict(mapping)
+    moved, same = {}, 0
+    for op, a0, a1, b0, b1 in difflib.SequenceMatcher(None, hit_sequence, chain_sequence, autojunk=False).get_opcodes():
+        if op == "equal" or (op == "replace" and a1 - a0 == b1 - b0):
+            same += (a1 - a0) if op == "equal" else 0
+            for k in range(a1 - a0):
+                moved[hit_start + a0 + k] = b0 + k
+    if not hit_sequence or same < min_identity * len(hit_sequence):
+        return None
+    return {q: moved[t] for q, t in mapping.items() if t in moved}
+
+
+def template_chain_from_mmcif(path: str, chain_id: str | None, query_indices, template_indices,
+                              hit_sequence: str | None = None, hit_start: int | None = None) -> TemplateChain | None:  # fmt: skip
     """One hit: ``template_indices`` count positions of the chain's full (SEQRES) sequence, 0-based.
 
     ``chain_id`` is matched against author chain names first, then label names; ``None`` takes the first protein chain.
-    Only protein chains give templates. Returns ``None`` when the chain is absent.
+    Only protein chains give templates. Returns ``None`` when the chain is absent. With ``hit_sequence`` (the hit's
+    ungapped target residues, starting at ``hit_start``, default the smallest template index) the indices are first
+    reconciled with the chain's own sequence (``reconcile_hit_with_chain``); a hit that does not fit the chain is dropped.
     """
     from .parse.mmcif import parse_mmcif
 
@@ -142,13 +175,21 @@ def template_chain_from_mmcif(path: str, chain_id: str | None, query_indices, te
             slot = order.get(a["name"].decode().strip())
             if slot is not None and a["is_present"]:
                 coords[k, slot], mask[k, slot] = xyz[a0 + j], True
-    return TemplateChain(names, coords, mask, {int(q): int(t) for q, t in zip(query_indices, template_indices)})
+    mapping = {int(q): int(t) for q, t in zip(query_indices, template_indices)}
+    if hit_sequence and mapping:
+        letters = "".join(const.PROTEIN_3TO1.get(nm, "X") for nm in names)
+        start = min(mapping.values()) if hit_start is None else int(hit_start)
+        mapping = reconcile_hit_with_chain(mapping, hit_sequence.replace("-", "").upper(), start, letters)
+        if not mapping:
+            return None
+    return TemplateChain(names, coords, mask, mapping)
 
 
 def load_json_templates(entries: list[dict], base_dir: str = ".", max_templates: int = 4, mmcif_dir: str | None = None,
                         max_date: str | None = None) -> list[TemplateChain]:
-    """Hit list of a prediction job: ``[{"name" | "mmcifPath": file, "chainId", "queryIndices", "templateIndices"}]``.
-    An entry may instead carry the file's text under ``"mmcif"``, or only a ``"pdbId"`` that is looked up in the local
+    """Hit list of a prediction job: ``[{"name" | "mmcifPath": file, "chainId", "queryIndices", "templateIndices"}]``;
+    with ``"templateSequence"`` (the target residues the search tool aligned, optionally ``"templateSequenceStart"``)
+    the indices are reconciled with the sequence of the structure file. An entry may instead carry the file's text under ``"mmcif"``, or only a ``"pdbId"`` that is looked up in the local
     mmCIF mirror ``mmcif_dir``. With ``max_date`` (YYYY-MM-DD) a hit released later is dropped: the entry's
     ``"releaseDate"`` decides when present, else the release date in the structure file; a hit whose date cannot be
     determined is kept. Unreadable hits are skipped."""
@@ -177,7 +218,8 @@ def load_json_templates(entries: list[dict], base_dir: str = ".", max_templates:
                     released = getattr(parse_mmcif(path, use_assembly=False)[1].structure_info, "released", None)
                     if released and str(released)[:10] > max_date:
                         continue
-                hit = template_chain_from_mmcif(path, e.get("chainId"), e["queryIndices"], e["templateIndices"])
+                hit = template_chain_from_mmcif(path, e.get("chainId"), e["queryIndices"], e["templateIndices"],
+                                                e.get("templateSequence"), e.get("templateSequenceStart"))
                 if hit is not None:
                     out.append(hit)
         except (ValueError, KeyError, IndexError):

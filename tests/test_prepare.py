@@ -615,3 +615,28 @@ def test_dataset_tool_commands(tmp_path):
     assert r.exit_code == 0, r.output
     table = json.loads((tmp_path / "ccd.json").read_text())
     assert set(table) == {"ZZ1", "ZZ2"} and "automorphisms" not in table["ZZ1"]  # C(-O-)(=O)C: the two oxygens differ in bond order
+
+
+def test_template_hit_is_reconciled_with_the_structure_sequence(tmp_path):
+    from deepfold3_dev_b200.data import const
+    from deepfold3_dev_b200.data.templates import reconcile_hit_with_chain, template_chain_from_mmcif
+
+    # the docstring case of the purpose: database sequence differs from the chain at the ends and in one stretch
+    chain = "XDEFGHKLMNPQRS"
+    db = "ABCDEFGHIJKLMNPQ"  # 3 extra residues in front of D, "IJ" where the chain has nothing
+    hit, start = db[3:], 3  # the hit covers db positions 3..15
+    mapping = {q: t for q, t in zip(range(10, 23), range(3, 16))}
+    moved = reconcile_hit_with_chain(mapping, hit, start, chain)
+    assert all(chain[moved[q]] == db[mapping[q]] for q in moved)  # every kept position points at the same residue
+    assert set(mapping) - set(moved) == {15, 16}  # the queries aligned to I and J have no residue in the chain
+    assert reconcile_hit_with_chain(mapping, hit, start, "WWWWWWWWWWWWWWWW") is None  # the wrong chain
+    same = reconcile_hit_with_chain({0: 1, 1: 2}, "DE", 1, chain)
+    assert same == {0: 1, 1: 2}  # already in place: untouched
+
+    # through the file reader: a hit whose database sequence lacks the chain's first three residues
+    path = os.path.join(EXAMPLES, "9m22_msa", "templates", "7yf1_A.cif")
+    full = template_chain_from_mmcif(path, "A", list(range(20)), list(range(20)))
+    letters = "".join(const.PROTEIN_3TO1.get(n, "X") for n in full.res_names)
+    shifted = template_chain_from_mmcif(path, "A", list(range(20)), list(range(20)), hit_sequence=letters[3:43], hit_start=0)
+    assert shifted.query_to_hit == {q: q + 3 for q in range(20)}
+    assert template_chain_from_mmcif(path, "A", list(range(20)), list(range(20)), hit_sequence="W" * 40, hit_start=0) is None
