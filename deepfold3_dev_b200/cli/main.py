@@ -130,7 +130,8 @@ def build_training_stream(tc, mc, info, datasets, data_dir=None, synthetic=False
             common = dict(max_tokens=tc.max_tokens, max_atoms=tc.max_atoms, is_distillation=distill, seed=tc.seed,
                           pdb_chain_cache_dir=getattr(tc, "pdb_chain_cache_dir", None) or None, max_templates=d.max_templates,
                           template_cutoff_days=d.template_cutoff_days, max_template_date=d.max_template_date,
-                          default_template_cutoff_date=d.default_template_cutoff_date)  # fmt: skip
+                          default_template_cutoff_date=d.default_template_cutoff_date,
+                          slow_sample_log_threshold_s=tc.slow_sample_log_threshold_s)  # fmt: skip
             parts.append(ds.open_dataset(path, atomize_prob=d.atomize_prob, atomize_source=d.atomize_source,
                                          atomize_max_residues=d.atomize_max_residues, **common, **kw))  # fmt: skip
             dropped = _filter_ids(parts[-1], include, exclude)

@@ -11,6 +11,7 @@ generates examples of the same schema for benchmarks and tests.
 from __future__ import annotations
 
 import json
+import logging
 import os
 
 import torch
@@ -19,6 +20,8 @@ from . import cropper, io_cache, pack as packs
 from .synthetic import split_lengths, synthetic_complex
 
 PAD_VALUES = {"msa": 21}
+
+logger = logging.getLogger(__name__)
 
 
 def rotate_reference_conformers(feats: dict, gen: torch.Generator) -> dict:
@@ -261,8 +264,10 @@ class StructureDataset:
                  msa_dir: str | None = None, cutoff_date: str = "", keep_after: bool = False, atomize_prob: float = 0.0,
                  atomize_source: str = "random", atomize_max_residues: int = 0, pdb_chain_cache_dir: str | None = None,
                  max_templates: int = 4, template_cutoff_days: int = 60, max_template_date: str | None = None,
-                 default_template_cutoff_date: str | None = None):  # fmt: skip
+                 default_template_cutoff_date: str | None = None, slow_sample_log_threshold_s: float = 0.0):  # fmt: skip
         from .types import load_manifest
+
+        self.slow_threshold_s = slow_sample_log_threshold_s
 
         self.root, self.max_tokens, self.max_atoms = root, max_tokens, max_atoms
         self.crop_weights, self.is_distillation, self.seed = crop_weights, is_distillation, seed
@@ -362,7 +367,7 @@ class StructureDataset:
             seed=self.seed * 7_654_321 + i, is_distillation=self.is_distillation,
             anchors=self.anchor_tables()[i % len(self.records)], **self.atomize,
             load_templates=(lambda chain, rng: self._templates(rec, chain, rng)) if self.pdb_chain_cache_dir else None,
-            max_templates=self.max_templates,
+            max_templates=self.max_templates, slow_threshold_s=self.slow_threshold_s,
         )  # fmt: skip
         self.msa_read, self.msa_skipped = self.msa_read + read, self.msa_skipped + skipped
         return feats
@@ -371,13 +376,19 @@ class StructureDataset:
 def featurize_record(st, rec, load_msa, *, max_tokens: int = 384, max_atoms: int = 0, crop_weights: dict | None = None,
                      max_chains: int = 20, max_msa_rows: int = 16384, seed: int = 0, is_distillation: bool = False,
                      anchors=None, atomize_prob: float = 0.0, atomize_source: str = "random", atomize_max_residues: int = 0,
-                     load_templates=None, max_templates: int = 4):
+                     load_templates=None, max_templates: int = 4, slow_threshold_s: float = 0.0):
     """One training example from a stored structure and its manifest record: pick the anchor chain or interface
     (in proportion to the anchor weights of ``anchors = (anchor list, weights)`` when given, else uniformly),
     pre-crop large assemblies to the chains around it, featurise, crop to the token budget, read the alignments of
     what survived (``load_msa(chain_info)`` -> ``MSA`` or ``None``), rotate the reference conformers. Returns the
-    features and the numbers of alignments read and skipped."""
+    features and the numbers of alignments read and skipped. With ``slow_threshold_s > 0`` an example that took longer
+    is reported in one ``SLOW_SAMPLE`` log line with the wall time of every phase (reference:
+    data/module/dataset.py:565-578)."""
     import random
+    import time
+
+    clock = [("start", time.perf_counter())]
+    mark = lambda name: clock.append((name, time.perf_counter()))  # noqa: E731
 
     from .featurize import attach_cropped_msa, attach_cropped_templates, featurize_structure
     from .prepare.filters import select_interface_chains
@@ -396,24 +407,35 @@ def featurize_record(st, rec, load_msa, *, max_tokens: int = 384, max_atoms: int
     keep = select_interface_chains(st, anchor, max_chains, rng=rng) & {c.chain_id for c in valid}
     old_ids = sorted(keep)
     sub = st.select_chains(old_ids)
+    mark("select_chains")
     # crop first, then read alignments only for the chains (and columns) that survived
     atomize = _residues_to_atomize(sub, rng, atomize_prob, atomize_source, atomize_max_residues)
     feats = featurize_structure(sub, None, max_msa_rows=max_msa_rows, with_msa=False, atomize=atomize)
     chain_cols, token_col, chain_len = feats.pop("_chain_cols"), feats.pop("_token_col"), feats.pop("_chain_len")
+    mark("featurize")
     # the anchor in the numbering of the featurised sub-structure (chains renumbered in the order of old_ids)
     new_of_old = {c: k for k, c in enumerate(old_ids)}
     crop_anchor = (anchor[0], new_of_old.get(anchor[1], -1), new_of_old.get(anchor[2], -1)) if anchor[1] in new_of_old else None
     feats, strategy, kept = cropper.crop(feats, max_tokens, max_atoms, gen, crop_weights, return_keep=True, anchor=crop_anchor)
+    mark("crop")
     feats, read, skipped = attach_cropped_msa(feats, kept, chain_cols, lambda a: load_msa(rec.chains[old_ids[a]]),
                                               max_msa_rows=max_msa_rows, token_col=token_col, chain_len=chain_len)  # fmt: skip
+    mark("msa")
     if load_templates is not None:  # ``load_templates(chain_info, rng)`` -> TemplateChain list of a protein chain
         tfeats, _ = attach_cropped_templates(feats, kept, chain_cols, token_col, chain_len,
                                              lambda a: load_templates(rec.chains[old_ids[a]], rng), max_templates)  # fmt: skip
         feats.update(tfeats)
+        mark("templates")
     feats = rotate_reference_conformers(feats, gen)
     from .symmetry import symmetry_features
 
     feats.update(symmetry_features(feats))  # exchangeable atoms and ligand automorphisms, indexed in the cropped example
+    mark("symmetry")
+    total = clock[-1][1] - clock[0][1]
+    if 0 < slow_threshold_s < total:
+        phases = " ".join(f"{name}={t1 - t0:.2f}s" for (_, t0), (name, t1) in zip(clock, clock[1:]))
+        logger.warning("SLOW_SAMPLE %s total=%.2fs tokens=%d chains=%d %s", rec.id, total, int(feats["res_type"].shape[0]),
+                       len(old_ids), phases)  # fmt: skip
     info = rec.structure_info
     feats["resolution"] = torch.tensor(float(info.resolution) if info and info.resolution else 0.0)
     feats["is_distillation"] = torch.tensor(bool(is_distillation))
@@ -468,7 +490,8 @@ def open_dataset(path: str, format: str = "df3", of3_cache_dir: str = "", **kw):
     cluster-balanced weights)."""
     from . import paths
 
-    template_keys = ("pdb_chain_cache_dir", "max_templates", "template_cutoff_days", "max_template_date", "default_template_cutoff_date")
+    template_keys = ("pdb_chain_cache_dir", "max_templates", "template_cutoff_days", "max_template_date", "default_template_cutoff_date",
+                     "slow_sample_log_threshold_s")  # fmt: skip
     template_kw = {k: kw.pop(k) for k in template_keys if k in kw}  # per-sequence hit lists exist for prepared roots only
     if format in ("of3", "of3pdb"):
         from .of3 import OF3StructureDataset

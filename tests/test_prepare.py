@@ -360,6 +360,19 @@ def test_training_templates_respect_dates_and_sampling(tmp_path):
     for r in d.records:
         r.structure_info.released = None
     assert all(int(d[i]["template_mask"].sum()) == 0 for i in range(6))
+    # an example slower than the configured threshold is reported with the time of every phase
+    import logging
+
+    slow = StructureDataset(str(out), max_tokens=64, pdb_chain_cache_dir=str(cache), slow_sample_log_threshold_s=1e-9)
+    lines = []
+    handler = logging.Handler()
+    handler.emit = lambda record: lines.append(record.getMessage())
+    logging.getLogger("deepfold3_dev_b200.data.datasets").addHandler(handler)
+    try:
+        slow[0]
+    finally:
+        logging.getLogger("deepfold3_dev_b200.data.datasets").removeHandler(handler)
+    assert len(lines) == 1 and lines[0].startswith("SLOW_SAMPLE ") and all(k in lines[0] for k in ("featurize=", "crop=", "msa=", "templates="))
     d.default_template_cutoff_date = "2016-01-01"
     assert any(int(d[i]["template_mask"].sum()) == 1 for i in range(12))
 
