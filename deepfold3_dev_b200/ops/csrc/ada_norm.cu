@@ -43,10 +43,11 @@ __device__ __forceinline__ void store2<__nv_bfloat16>(__nv_bfloat16* p, float a,
   *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b);
 }
 
-__device__ __forceinline__ float sigmoid_exact(float v) { return 1.f / (1.f + __expf(-v)); }
+// 2 ulp of fp32 from the fast divide: far below the bf16 rounding of every consumer, and a third of the instructions
+__device__ __forceinline__ float sigmoid_exact(float v) { return __fdividef(1.f, 1.f + __expf(-v)); }
 
 template <typename TX, int K>
-__global__ void __launch_bounds__(256) ada_ln_fwd_kernel(const TX* __restrict__ x, const __nv_bfloat16* __restrict__ s,
+__global__ void __launch_bounds__(128) ada_ln_fwd_kernel(const TX* __restrict__ x, const __nv_bfloat16* __restrict__ s,
                                                          const __nv_bfloat16* __restrict__ t, __nv_bfloat16* __restrict__ y,
                                                          float* __restrict__ mean_out, float* __restrict__ rstd_out,
                                                          int64_t rows, int C, float eps) {
@@ -54,14 +55,21 @@ __global__ void __launch_bounds__(256) ada_ln_fwd_kernel(const TX* __restrict__ 
   const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (row >= rows) return;
   const int64_t base = row * C;
+  // every load of the row is issued before the first reduction: the conditioning pairs wait in registers as raw bf16x2,
+  // so a row pays the memory latency once instead of once per phase
   float2 v[K];
+  __nv_bfloat162 sr[K], tr[K];
   float sum = 0.f;
 #pragma unroll
   for (int k = 0; k < K; ++k) {
     const int c = 2 * (lane + 32 * k);
-    v[k] = (c < C) ? load2<TX>(x + base + c) : make_float2(0.f, 0.f);
-    sum += v[k].x + v[k].y;
+    const bool in = c < C;
+    v[k] = in ? load2<TX>(x + base + c) : make_float2(0.f, 0.f);
+    sr[k] = in ? *reinterpret_cast<const __nv_bfloat162*>(s + base + c) : __nv_bfloat162();
+    tr[k] = in ? *reinterpret_cast<const __nv_bfloat162*>(t + base + c) : __nv_bfloat162();
   }
+#pragma unroll
+  for (int k = 0; k < K; ++k) sum += v[k].x + v[k].y;
   const float mean = warp_sum(sum) / C;
   float q = 0.f;
 #pragma unroll
@@ -77,7 +85,7 @@ __global__ void __launch_bounds__(256) ada_ln_fwd_kernel(const TX* __restrict__ 
   for (int k = 0; k < K; ++k) {
     const int c = 2 * (lane + 32 * k);
     if (c < C) {
-      const float2 sv = load2<__nv_bfloat16>(s + base + c), tv = load2<__nv_bfloat16>(t + base + c);
+      const float2 sv = __bfloat1622float2(sr[k]), tv = __bfloat1622float2(tr[k]);
       store2<__nv_bfloat16>(y + base + c, sigmoid_exact(sv.x) * (v[k].x - mean) * rstd + tv.x,
                             sigmoid_exact(sv.y) * (v[k].y - mean) * rstd + tv.y);
     }
@@ -90,7 +98,7 @@ __global__ void __launch_bounds__(256) ada_ln_fwd_kernel(const TX* __restrict__ 
 
 // dx = rstd * (g - mean(g) - xhat * mean(g * xhat)) with g = dy * sigmoid(s);  ds = dy * xhat * sig * (1 - sig)
 template <typename TX, int K>
-__global__ void __launch_bounds__(256) ada_ln_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const TX* __restrict__ x,
+__global__ void __launch_bounds__(128) ada_ln_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const TX* __restrict__ x,
                                                          const __nv_bfloat16* __restrict__ s, const float* __restrict__ mean_in,
                                                          const float* __restrict__ rstd_in, TX* __restrict__ dx,
                                                          __nv_bfloat16* __restrict__ ds, int64_t rows, int C) {
@@ -99,14 +107,24 @@ __global__ void __launch_bounds__(256) ada_ln_bwd_kernel(const __nv_bfloat16* __
   if (row >= rows) return;
   const int64_t base = row * C;
   const float mean = mean_in[row], rstd = rstd_in[row];
+  // all three operands of the row are requested before anything is computed or stored (one latency per row)
   float2 xh[K], g[K];
+  __nv_bfloat162 gr[K], sr[K];
+#pragma unroll
+  for (int k = 0; k < K; ++k) {
+    const int c = 2 * (lane + 32 * k);
+    const bool in = c < C;
+    xh[k] = in ? load2<TX>(x + base + c) : make_float2(0.f, 0.f);  // a constant: the loads must not wait for the statistics
+    gr[k] = in ? *reinterpret_cast<const __nv_bfloat162*>(dy + base + c) : __nv_bfloat162();
+    sr[k] = in ? *reinterpret_cast<const __nv_bfloat162*>(s + base + c) : __nv_bfloat162();
+  }
   float s1 = 0.f, s2 = 0.f;
 #pragma unroll
   for (int k = 0; k < K; ++k) {
     const int c = 2 * (lane + 32 * k);
     if (c < C) {
-      const float2 xv = load2<TX>(x + base + c), gv = load2<__nv_bfloat16>(dy + base + c), sv = load2<__nv_bfloat16>(s + base + c);
-      xh[k] = make_float2((xv.x - mean) * rstd, (xv.y - mean) * rstd);
+      const float2 gv = __bfloat1622float2(gr[k]), sv = __bfloat1622float2(sr[k]);
+      xh[k] = make_float2((xh[k].x - mean) * rstd, (xh[k].y - mean) * rstd);
       const float ga = sigmoid_exact(sv.x), gb = sigmoid_exact(sv.y);
       store2<__nv_bfloat16>(ds + base + c, gv.x * xh[k].x * ga * (1.f - ga), gv.y * xh[k].y * gb * (1.f - gb));
       g[k] = make_float2(gv.x * ga, gv.y * gb);
@@ -165,11 +183,11 @@ std::tuple<Tensor, Tensor, Tensor> ada_ln_fwd(const Tensor& x, const Tensor& s, 
   Tensor y = torch::empty_like(s);
   Tensor mean = torch::empty({rows}, x.options().dtype(torch::kFloat32)), rstd = torch::empty_like(mean);
   if (rows == 0) return {y, mean, rstd};
-  const unsigned grid = (unsigned)((rows + 7) / 8);
+  const unsigned grid = (unsigned)((rows + 3) / 4);  // four warps, one row each: small blocks keep more rows resident at ~95 registers
   cudaStream_t st = at::cuda::getCurrentCUDAStream();
   const int pairs = (C / 2 + 31) / 32;
 #define DF3_ADA_FWD(TX, K_)                                                                                                  \
-  ada_ln_fwd_kernel<TX, K_><<<grid, 256, 0, st>>>((const TX*)x.data_ptr(), (const __nv_bfloat16*)s.data_ptr(),              \
+  ada_ln_fwd_kernel<TX, K_><<<grid, 128, 0, st>>>((const TX*)x.data_ptr(), (const __nv_bfloat16*)s.data_ptr(),              \
                                                   (const __nv_bfloat16*)t.data_ptr(), (__nv_bfloat16*)y.data_ptr(),         \
                                                   mean.data_ptr<float>(), rstd.data_ptr<float>(), rows, C, (float)eps)
   if (x.scalar_type() == torch::kFloat32) {
@@ -191,11 +209,11 @@ std::tuple<Tensor, Tensor> ada_ln_bwd(const Tensor& dy, const Tensor& x, const T
   TORCH_CHECK(mean.numel() == rows && rstd.numel() == rows && mean.scalar_type() == torch::kFloat32, "ada_ln_bwd: statistics per row");
   Tensor dx = torch::empty_like(x), ds = torch::empty_like(s);
   if (rows == 0) return {dx, ds};
-  const unsigned grid = (unsigned)((rows + 7) / 8);
+  const unsigned grid = (unsigned)((rows + 3) / 4);  // four warps, one row each: small blocks keep more rows resident at ~95 registers
   cudaStream_t st = at::cuda::getCurrentCUDAStream();
   const int pairs = (C / 2 + 31) / 32;
 #define DF3_ADA_BWD(TX, K_)                                                                                                  \
-  ada_ln_bwd_kernel<TX, K_><<<grid, 256, 0, st>>>((const __nv_bfloat16*)dy.data_ptr(), (const TX*)x.data_ptr(),             \
+  ada_ln_bwd_kernel<TX, K_><<<grid, 128, 0, st>>>((const __nv_bfloat16*)dy.data_ptr(), (const TX*)x.data_ptr(),             \
                                                   (const __nv_bfloat16*)s.data_ptr(), mean.data_ptr<float>(),               \
                                                   rstd.data_ptr<float>(), (TX*)dx.data_ptr(), (__nv_bfloat16*)ds.data_ptr(), rows, C)
   if (x.scalar_type() == torch::kFloat32) {

@@ -160,9 +160,40 @@ def bench_streaming(t: Timer):
                                                                             0.1, 0.05, 1e-3, p16)), None, m * (4 * 10 + 2), 0)  # fmt: skip
 
 
+def bench_diffusion(t: Timer):
+    """Element-wise kernels of the diffusion transformer at the training shape (48 samples x N tokens x 768 channels:
+    the fp32 residual stream is 57 MB at N = 384, with its conditioning tensors well beyond L2), and the atom-window
+    attention (N * 24 / 32 windows of 32 queries x 128 keys, 4 heads of 32, bias shared by the samples)."""
+    S, C = 48, 768
+    x = torch.randn(S, N, C, device="cuda")
+    s, sh, dy = (torch.randn(S, N, C, device="cuda").bfloat16() for _ in range(3))
+    rows_bytes = x.numel()
+
+    def eager_ada():
+        return (torch.sigmoid(s.float()) * torch.nn.functional.layer_norm(x, (C,)) + sh.float()).bfloat16()
+
+    _report(f"ada_ln fwd {S * N}x{C}", t(lambda: torch.ops.df3.ada_ln_fwd(x, s, sh, 1e-5)), t(eager_ada), rows_bytes * (4 + 2 + 2 + 2), 0)
+    _, mean, rstd = torch.ops.df3.ada_ln_fwd(x, s, sh, 1e-5)
+    _report(f"ada_ln bwd {S * N}x{C}", t(lambda: torch.ops.df3.ada_ln_bwd(dy, x, s, mean, rstd)), None, rows_bytes * (2 + 4 + 2 + 4 + 2), 0)
+    _report(f"gated_residual fwd {S * N}x{C}", t(lambda: torch.ops.df3.gated_residual_fwd(x, s, sh)),
+            t(lambda: x + torch.sigmoid(s.float()) * sh.float()), rows_bytes * (4 + 2 + 2 + 4), 0)  # fmt: skip
+    _report(f"gated_residual bwd {S * N}x{C}", t(lambda: torch.ops.df3.gated_residual_bwd(x, s, sh)), None, rows_bytes * (4 + 2 + 2 + 2 + 2), 0)
+
+    from . import autograd_ops as ao
+
+    W, H, Q, Kk, D = N * 24 // 32, 4, 32, 128, 32
+    q = torch.randn(1, S, W, H, Q, D, device="cuda").bfloat16()
+    k, v = (torch.randn(1, S, W, H, Kk, D, device="cuda").bfloat16() for _ in range(2))
+    bias = torch.randn(1, 1, W, H, Q, Kk, device="cuda").bfloat16()
+    if ao.window_attention_supported(q, k, v, bias):
+        nbytes = 2 * (2 * q.numel() + k.numel() + v.numel() + bias.numel())
+        _report(f"window attention {S}x{W} windows", t(lambda: ao.window_attention(q, k, v, bias, D**-0.5)),
+                t(lambda: ref.window_attention(q, k, v, bias, D**-0.5)), nbytes, 4 * S * W * H * Q * Kk * D)  # fmt: skip
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", default="all", choices=["all", "gemm", "attention", "elementwise", "streaming"])
+    ap.add_argument("--op", default="all", choices=["all", "gemm", "attention", "elementwise", "streaming", "diffusion"])
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--tokens", type=int, default=384, help="token count of the pair-shaped cases (384: training crop, 1024: inference)")
     args = ap.parse_args()
@@ -178,6 +209,8 @@ def main():
         bench_elementwise(t)
     if args.op in ("all", "streaming"):
         bench_streaming(t)
+    if args.op in ("all", "diffusion"):
+        bench_diffusion(t)
     code = torch.ops.df3.gemm_status()
     print("kernel status word:", code)
     if code != 0:
