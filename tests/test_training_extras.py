@@ -221,3 +221,34 @@ def test_benchmark_plots(tmp_path):
     (tmp_path / "x.json").write_text(json.dumps([{"something": 1}]))
     with pytest.raises(ValueError, match="unknown benchmark"):
         plot_results.plot_file(str(tmp_path / "x.json"), str(tmp_path / "plots"))
+
+
+def test_guides_name_existing_commands_files_and_switches():
+    """Every command, source path and environment switch the guides mention exists in the package."""
+    import re
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    listing = subprocess.check_output([sys.executable, "-m", "deepfold3_dev_b200.cli", "--help"], cwd=root, text=True)
+    commands = {line.split()[0] for line in listing.split("Commands:")[1].splitlines() if line.startswith("  ") and line.split()}
+    sources = ""
+    for base, _, names in os.walk(root):
+        if any(part in base for part in ("/.git", "/_work", "/gpurun_out", "/baseline/_ref", "/build")):
+            continue
+        for n in names:
+            if n.endswith((".py", ".cu", ".cuh", ".h", ".sh")):
+                with open(os.path.join(base, n), errors="ignore") as f:
+                    sources += f.read()
+    guides = sorted(os.listdir(os.path.join(root, "docs")))
+    assert {"training.md", "inference.md", "data-pipeline.md", "kernels.md", "parallelism.md", "complex-lm.md"} <= set(guides)
+    prefixes = "deepfold3_dev_b200/|ops/|data/|models/|training/|parallel/|inference/|utils/|complexlm/|config/|evaluation/|benchmarks/|deploy/|configs/|tests/|profiles/"
+    for g in guides:
+        with open(os.path.join(root, "docs", g)) as f:
+            text = f.read()
+        for cmd in re.findall(r"deepfold3_dev_b200\.cli ([a-z][a-z0-9-]+)", text):
+            assert cmd in commands, (g, cmd)
+        for path in re.findall(rf"`((?:{prefixes})[A-Za-z0-9_./-]+\.(?:py|cu|cuh|h|yaml|md|sh))", text):
+            assert os.path.exists(os.path.join(root, path)) or os.path.exists(os.path.join(root, "deepfold3_dev_b200", path)), (g, path)
+        for var in set(re.findall(r"\b(DF3_[A-Z_]+|DEEPFOLD3_[A-Z_]+)\b", text)):
+            assert var in sources, (g, var)
