@@ -496,7 +496,128 @@ def run_status_cmd(run_dir):
     click.echo(json.dumps(run_status(run_dir), indent=1))
 
 
+@click.group("triage")
+def triage():
+    """Diagnostics for a run that misbehaves: non-finite values, diverging paths, gradient agreement, series, mirror images."""
+
+
+def _triage_model(config, overrides, params, tokens, seed):
+    """The model of a recipe (random weights unless ``params``) and one synthetic example of ``tokens`` tokens."""
+    import torch
+
+    from ..config.loader import build_configs
+    from ..data.synthetic import split_lengths, synthetic_complex
+    from ..models.model import DeepFold3
+
+    tc, mc = build_configs(list(config), list(overrides))
+    torch.manual_seed(seed)
+    model = DeepFold3(mc)
+    if params:
+        from ..training.checkpointing import load_pretrained_weights
+
+        load_pretrained_weights(model, params)
+    dev = torch.device("cuda", 0) if torch.cuda.is_available() else torch.device("cpu")
+    model.to(dev)
+    feats = synthetic_complex([("protein", n) for n in split_lengths(tokens, 2)], num_msa=min(mc.msa_crop_size, 64), seed=seed)
+    feats = {k: (v.to(dev) if torch.is_tensor(v) else v) for k, v in feats.items()}
+    return model, tc, mc, feats, dev
+
+
+@triage.command("activations")
+@click.option("--config", multiple=True, type=click.Path(exists=True))
+@click.option("--override", multiple=True)
+@click.option("--params", type=click.Path(exists=True), default=None)
+@click.option("--tokens", type=int, default=64, show_default=True)
+@click.option("--seed", type=int, default=0)
+@click.option("--compare-disabled", default=None, help="Run a second trace with DF3_DISABLE_OPS set to this list and report where the two part.")
+@click.option("--top", type=int, default=10, show_default=True)
+def triage_activations(config, override, params, tokens, seed, compare_disabled, top):
+    """Trace every submodule of one prediction-mode forward: first non-finite output, largest magnitudes, and with
+    --compare-disabled the first module where the kernel path and the PyTorch statement differ."""
+    import dataclasses
+
+    import torch
+
+    from ..utils import triage as T
+
+    model, _, mc, feats, dev = _triage_model(config, override, params, tokens, seed)
+    model.eval()
+
+    def run():
+        with torch.no_grad(), torch.autocast(dev.type, dtype=torch.bfloat16, enabled=dev.type == "cuda"):
+            model(dict(feats), seed=seed, num_recycles=1, num_samples=1)
+
+    rows = T.activation_trace(model, run)
+    bad = T.first_nonfinite(rows)
+    out = {"modules_called": len(rows), "first_nonfinite": dataclasses.asdict(bad) if bad else None,
+           "largest": [dataclasses.asdict(r) for r in T.largest_activations(rows, top)]}  # fmt: skip
+    if compare_disabled:
+        keep = os.environ.get("DF3_DISABLE_OPS")
+        os.environ["DF3_DISABLE_OPS"] = compare_disabled
+        try:
+            other = T.activation_trace(model, run)
+        finally:
+            if keep is None:
+                os.environ.pop("DF3_DISABLE_OPS", None)
+            else:
+                os.environ["DF3_DISABLE_OPS"] = keep
+        out["differences"] = T.diff_traces(rows, other)[:top]
+    click.echo(json.dumps(out, indent=1))
+
+
+@triage.command("grad-spread")
+@click.option("--config", multiple=True, type=click.Path(exists=True))
+@click.option("--override", multiple=True)
+@click.option("--params", type=click.Path(exists=True), default=None)
+@click.option("--tokens", type=int, default=64, show_default=True)
+@click.option("--examples", type=int, default=8, show_default=True)
+@click.option("--seed", type=int, default=0)
+def triage_grad_spread(config, override, params, tokens, examples, seed):
+    """Norms and directional agreement of per-example gradients over synthetic examples (one forward + backward each)."""
+    import torch
+
+    from ..data.synthetic import split_lengths, synthetic_complex
+    from ..training.engine import training_step
+    from ..utils import triage as T
+
+    model, tc, mc, _, dev = _triage_model(config, override, params, tokens, seed)
+    model.train()
+    spread = T.GradientSpread()
+    for i in range(examples):
+        feats = synthetic_complex([("protein", n) for n in split_lengths(tokens, 2)], num_msa=min(mc.msa_crop_size, 64), seed=seed + 1 + i)
+        batch = {k: (v.unsqueeze(0).to(dev) if torch.is_tensor(v) else [v]) for k, v in feats.items()}
+        model.zero_grad(set_to_none=True)
+        with torch.autocast(dev.type, dtype=torch.bfloat16, enabled=dev.type == "cuda"):
+            loss, *_ = training_step(model, batch, cfg=tc, model_cfg=mc, global_step=i, device=dev, num_recycles=1)
+        loss.backward()
+        spread.add(T.flat_gradient(model))
+    click.echo(json.dumps(spread.result(), indent=1))
+
+
+@triage.command("series")
+@click.argument("run_dir", type=click.Path(exists=True))
+@click.option("--prefix", default="act_rms", show_default=True)
+@click.option("--window", type=int, default=50, show_default=True)
+@click.option("--ceiling", type=float, default=None)
+def triage_series(run_dir, prefix, window, ceiling):
+    """Latest value, median and log-slope of every logged series with the prefix, fastest-growing first."""
+    from ..utils.triage import series_summary
+
+    click.echo(json.dumps(series_summary(run_dir, prefix, window, ceiling), indent=1))
+
+
+@triage.command("handedness")
+@click.argument("pred", type=click.Path(exists=True))
+@click.argument("ref", type=click.Path(exists=True))
+def triage_handedness(pred, ref):
+    """Is the predicted structure a mirror image of the reference? Per matched chain."""
+    from ..utils.triage import handedness_of_files
+
+    click.echo(json.dumps(handedness_of_files(pred, ref), indent=1))
+
+
 def register(cli) -> None:
-    for cmd in (prepare, scan_mmcif, inspect_example, plm_prepare, plm_train, evaluate, eval_sweep, prepare_templates, build_pdb_cache, inspect_checkpoint, run_status_cmd):
+    for cmd in (prepare, scan_mmcif, inspect_example, plm_prepare, plm_train, evaluate, eval_sweep, prepare_templates, build_pdb_cache, inspect_checkpoint, run_status_cmd,
+                triage):  # fmt: skip
         cli.add_command(cmd)
 

@@ -252,3 +252,77 @@ def test_guides_name_existing_commands_files_and_switches():
             assert os.path.exists(os.path.join(root, path)) or os.path.exists(os.path.join(root, "deepfold3_dev_b200", path)), (g, path)
         for var in set(re.findall(r"\b(DF3_[A-Z_]+|DEEPFOLD3_[A-Z_]+)\b", text)):
             assert var in sources, (g, var)
+
+
+def test_triage_finds_offender_divergence_gradient_agreement_series_and_mirror(tmp_path):
+    import json
+
+    import numpy as np
+    import torch
+    from click.testing import CliRunner
+
+    from deepfold3_dev_b200.utils import triage as T
+
+    class Net(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.a, self.b, self.c = torch.nn.Linear(4, 4), torch.nn.Linear(4, 4), torch.nn.Linear(4, 4)
+            self.poison = False
+
+        def forward(self, x):
+            h = self.b(self.a(x))
+            return self.c(h / 0.0 if self.poison else h)
+
+    net = Net()
+    x = torch.randn(3, 4)
+    clean = T.activation_trace(net, lambda: net(x))
+    assert [r.name for r in clean] == ["a", "b", "c"] and T.first_nonfinite(clean) is None
+    net.poison = True
+    bad = T.activation_trace(net, lambda: net(x))
+    assert T.first_nonfinite(bad).name == "c"  # a and b were still finite
+    net.poison = False
+    with torch.no_grad():
+        net.b.weight.mul_(3.0)
+    parted = T.diff_traces(clean, T.activation_trace(net, lambda: net(x)))
+    assert parted and parted[0]["name"] == "b"  # the first module whose magnitude moved
+    assert T.largest_activations(clean, 1)[0].abs_max == max(r.abs_max for r in clean)
+
+    # gradients that agree, then gradients that are independent
+    base = torch.randn(1000)
+    same, indep = T.GradientSpread(), T.GradientSpread()
+    for k in range(16):
+        same.add(base * (1 + 0.1 * k))
+        indep.add(torch.randn(1000))
+    a, b = same.result(), indep.result()
+    assert abs(a["resultant_length"] - 1) < 1e-9 and abs(a["mean_pairwise_cosine"] - 1) < 1e-9
+    assert abs(b["mean_pairwise_cosine"]) < 0.1 and b["resultant_length"] < 0.5 and abs(b["independent_baseline"] - 0.25) < 1e-12
+
+    # a growing series floats to the top
+    (tmp_path / "logs").mkdir()
+    with open(tmp_path / "logs" / "metrics.jsonl", "w") as f:
+        for step in range(0, 2000, 100):
+            f.write(json.dumps({"step": step, "train/act_rms/pair_max": 1.0 * np.exp(step / 1000), "train/act_rms/single_max": 2.0, "train/loss": 3.0}) + "\n")
+    rows = T.series_summary(str(tmp_path), "act_rms", ceiling=3.0)
+    assert [r["series"] for r in rows] == ["act_rms/pair_max", "act_rms/single_max"]
+    assert abs(rows[0]["log_slope_per_1k_steps"] - 1.0) < 1e-6 and rows[0]["above_ceiling"] and not rows[1]["above_ceiling"]
+
+    # a right-handed helix against itself and against its mirror image
+    t = np.arange(30) * np.deg2rad(100.0)
+    helix = np.stack([2.3 * np.cos(t), 2.3 * np.sin(t), 1.5 * np.arange(30)], -1)
+    rot, _ = np.linalg.qr(np.random.default_rng(0).normal(size=(3, 3)))
+    rot *= np.sign(np.linalg.det(rot))
+    ok = T.handedness(helix @ rot.T + 5.0, helix)
+    flipped = T.handedness((helix * np.array([1.0, 1.0, -1.0])) @ rot.T, helix)
+    assert not ok["mirror_image"] and ok["dihedral_sign_match"] == 1.0 and ok["rmsd_proper"] < 1e-6
+    assert flipped["mirror_image"] and flipped["dihedral_sign_match"] == 0.0 and flipped["rmsd_mirrored"] < 1e-6 < flipped["rmsd_proper"]
+
+    import importlib
+
+    cli_main = importlib.import_module("deepfold3_dev_b200.cli.main")
+    res = CliRunner().invoke(cli_main.cli, ["triage", "series", str(tmp_path), "--prefix", "act_rms"])
+    assert res.exit_code == 0 and "act_rms/pair_max" in res.output
+    cfg = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "configs", "smoke.yaml")
+    res = CliRunner().invoke(cli_main.cli, ["triage", "activations", "--config", cfg, "--tokens", "24", "--top", "3"])
+    assert res.exit_code == 0, res.output + repr(res.exception)
+    report = json.loads(res.output)
+    assert report["first_nonfinite"] is None and len(report["largest"]) == 3 and report["modules_called"] > 50
