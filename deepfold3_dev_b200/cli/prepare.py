@@ -594,6 +594,34 @@ def triage_grad_spread(config, override, params, tokens, examples, seed):
     click.echo(json.dumps(spread.result(), indent=1))
 
 
+@triage.command("distogram")
+@click.option("--config", multiple=True, type=click.Path(exists=True))
+@click.option("--override", multiple=True)
+@click.option("--params", type=click.Path(exists=True), default=None)
+@click.option("--example", type=click.Path(exists=True), default=None, help="A stored feature file (.pt) with ground truth; default: a synthetic complex.")
+@click.option("--tokens", type=int, default=64, show_default=True)
+@click.option("--recycles", type=int, default=1, show_default=True)
+@click.option("--seed", type=int, default=0)
+@click.option("--save", type=click.Path(), default=None, help="Write the true and expected distance maps as .npz.")
+def triage_distogram(config, override, params, example, tokens, recycles, seed, save):
+    """Distogram head against the true distances of one example: bin accuracy, cross-entropy, error of the expected distance."""
+    import torch
+
+    from ..utils.triage import distogram_agreement
+
+    model, _, _, feats, dev = _triage_model(config, override, params, tokens, seed)
+    if example:
+        feats = {k: (v.to(dev) if torch.is_tensor(v) else v) for k, v in torch.load(example, map_location="cpu", weights_only=False).items()}
+    with torch.autocast(dev.type, dtype=torch.bfloat16, enabled=dev.type == "cuda"):
+        out = distogram_agreement(model, feats, recycles, seed)
+    maps = {k: out.pop(k) for k in ("true_distance", "expected_distance") if k in out}
+    if save and maps:
+        import numpy as np
+
+        np.savez_compressed(save, **{k: v.numpy() for k, v in maps.items()})
+    click.echo(json.dumps(out, indent=1))
+
+
 @triage.command("series")
 @click.argument("run_dir", type=click.Path(exists=True))
 @click.option("--prefix", default="act_rms", show_default=True)

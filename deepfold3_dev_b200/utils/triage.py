@@ -200,6 +200,50 @@ def series_summary(run_dir: str, prefix: str = "act_rms", window: int = 50, ceil
 
 
 # ---------------------------------------------------------------------------------------------------------------
+# the distogram head against the true distances
+# ---------------------------------------------------------------------------------------------------------------
+@torch.no_grad()
+def distogram_agreement(model, feats: dict, num_recycles: int = 1, seed: int = 0, near: float = 20.0) -> dict:
+    """Trunk and distogram head only (no diffusion) on one example with ground truth: how often the most likely bin is
+    the true one (or next to it), the cross-entropy, and the mean absolute error of the expected distance over pairs
+    closer than ``near`` angstroms. A trunk that has learnt the fold shows here long before samples look right
+    (reference: scripts/check_distogram.py, there as heat maps). Returns the ``[N, N]`` true and expected distance
+    maps too, for plotting."""
+    was_training = model.training
+    model.eval()
+    try:
+        trunk = model.run_evoformer(feats, num_recycles, seed=seed)
+        pair = trunk[0]["pair"]
+        head = model.distogram_head
+        logits = head(pair).float()
+        expected = head.expected_distance(pair).float()
+    finally:
+        model.train(was_training)
+    while logits.dim() > 3:  # drop a leading batch axis of one
+        logits, expected = logits[0], expected[0]
+    n = logits.shape[0]
+    ar = torch.arange(n, device=logits.device)
+    rep = feats["token_to_rep_atom"].reshape(-1)[:n].long()
+    pos = feats["atom_gt_positions"].reshape(-1, *feats["atom_gt_positions"].shape[-2:])[:n][ar, rep].float()
+    ok = feats["atom_gt_mask"].reshape(-1, feats["atom_gt_mask"].shape[-1])[:n][ar, rep].bool()
+    d = torch.cdist(pos, pos)
+    valid = ok[:, None] & ok[None] & ~torch.eye(n, dtype=torch.bool, device=d.device)
+    breaks = torch.linspace(head.first_break, head.last_break, head.num_bins - 1, device=d.device)
+    target = torch.bucketize(d, breaks)
+    pred = logits.argmax(-1)
+    count = int(valid.sum())
+    if count == 0:
+        return {"pairs": 0}
+    nll = torch.nn.functional.cross_entropy(logits[valid], target[valid])
+    close = valid & (d < near)
+    return {"pairs": count, "bin_accuracy": float((pred == target)[valid].float().mean()),
+            "bin_within_one": float(((pred - target).abs() <= 1)[valid].float().mean()), "cross_entropy": float(nll),
+            "uniform_cross_entropy": math.log(head.num_bins),
+            "mae_expected_distance_near": float((expected - d).abs()[close].mean()) if bool(close.any()) else float("nan"),
+            "true_distance": d.cpu(), "expected_distance": expected.cpu()}  # fmt: skip
+
+
+# ---------------------------------------------------------------------------------------------------------------
 # handedness of a prediction
 # ---------------------------------------------------------------------------------------------------------------
 def _pseudo_dihedrals(ca: np.ndarray) -> np.ndarray:

@@ -326,3 +326,10 @@ def test_triage_finds_offender_divergence_gradient_agreement_series_and_mirror(t
     assert res.exit_code == 0, res.output + repr(res.exception)
     report = json.loads(res.output)
     assert report["first_nonfinite"] is None and len(report["largest"]) == 3 and report["modules_called"] > 50
+    res = CliRunner().invoke(cli_main.cli, ["triage", "distogram", "--config", cfg, "--tokens", "24", "--save", str(tmp_path / "maps.npz")])
+    assert res.exit_code == 0, res.output + repr(res.exception)
+    report = json.loads(res.output)
+    # the head's output layer starts at zero: every bin equally likely, so the cross-entropy is log(bins)
+    assert report["pairs"] == 24 * 23 and abs(report["cross_entropy"] - report["uniform_cross_entropy"]) < 1e-4
+    maps = np.load(tmp_path / "maps.npz")
+    assert maps["true_distance"].shape == maps["expected_distance"].shape == (24, 24)
