@@ -365,6 +365,93 @@ def stamp_template_index_space(data_dir, space, workers, dry_run):
     click.echo(f"{len(files)} index files, {changed} {'would be ' if dry_run else ''}stamped {space!r}")
 
 
+@click.command("backfill-template-dates")
+@click.option("--data-dir", required=True, type=click.Path(exists=True))
+@click.option("--release-dates", required=True, type=click.Path(exists=True),
+              help="JSON {entry id: YYYY-MM-DD}, or the table `scan-mmcif` writes (rows with id and released).")
+@click.option("--dry-run", is_flag=True)
+def backfill_template_dates(data_dir, release_dates, dry_run):
+    """Fill missing ``release_date`` fields of the template hit lists under DATA_DIR from a table of release dates.
+    Hit lists written without dates make the fail-closed date filter drop every template in training; this edits
+    the JSON in place instead of parsing the search results again."""
+    with open(release_dates) as f:
+        table = json.load(f)
+    if isinstance(table, list):
+        table = {str(r.get("id", "")): r.get("released") or r.get("release_date") for r in table if isinstance(r, dict)}
+    dates = {str(k).lower(): str(v)[:10] for k, v in table.items() if v}
+    files = []
+    for sub in ("templates", "monomer_templates"):
+        files += glob.glob(os.path.join(data_dir, sub, "**", "*.json"), recursive=True)
+    filled = unknown = touched = 0
+    for path in files:
+        with open(path) as f:
+            doc = json.load(f)
+        hits = doc.get("hits", []) if isinstance(doc, dict) else doc
+        changed = False
+        for h in hits:
+            if not isinstance(h, dict) or h.get("release_date"):
+                continue
+            entry = str(h.get("template_pdb_id") or h.get("pdb_id") or h.get("pdbId") or "").lower()
+            if entry in dates:
+                h["release_date"], changed, filled = dates[entry], True, filled + 1
+            else:
+                unknown += 1
+        if changed:
+            touched += 1
+            if not dry_run:
+                tmp = path + ".tmp"
+                with open(tmp, "w") as f:
+                    json.dump(doc, f)
+                os.replace(tmp, path)
+    click.echo(f"{len(files)} hit lists: {filled} dates {'would be ' if dry_run else ''}filled in {touched} files, {unknown} hits without a known date")
+
+
+@click.command("msa-worklist")
+@click.option("--data-dir", "data_dirs", required=True, multiple=True, type=click.Path(exists=True), help="Prepared dataset root (repeatable).")
+@click.option("--output", required=True, type=click.Path(), help="Directory for combined.fasta, complexes.json, stats.json.")
+def msa_worklist(data_dirs, output):
+    """What is still to be searched: protein sequences of the datasets that have no alignment yet (``combined.fasta``,
+    one entry per distinct sequence, named by its alignment id), and the heteromeric records whose chains lack a paired
+    alignment (``complexes.json``: ``{record id: [sequence, ...]}``), with counts in ``stats.json``. The two files are
+    the inputs of ``msa-batch``."""
+    from ..data import const
+
+    os.makedirs(output, exist_ok=True)
+    missing, complexes = {}, {}
+    stats = {"records": 0, "protein_sequences": 0, "with_alignment": 0, "heteromers": 0, "heteromers_paired": 0}
+    for data_dir in data_dirs:
+        _, records = _load(data_dir)
+        seqs = _chain_sequences(data_dir, records)
+        have = {m for m, (_, mol) in seqs.items() if mol == const.MOL_PROTEIN and paths.msa(data_dir, m) is not None}
+        protein = {m for m, (_, mol) in seqs.items() if mol == const.MOL_PROTEIN}
+        stats["records"] += len(records)
+        stats["protein_sequences"] += len(protein)
+        stats["with_alignment"] += len(have)
+        for m in sorted(protein - have):
+            missing.setdefault(m, seqs[m][0])
+        for rec in records:
+            chains = [c for c in rec.chains if c.mol_type == const.MOL_PROTEIN and c.msa_id in seqs]
+            if len({c.msa_id for c in chains}) < 2:
+                continue
+            stats["heteromers"] += 1
+            if all(getattr(c, "paired_msa_id", None) for c in chains):
+                stats["heteromers_paired"] += 1
+                continue
+            complexes[rec.id] = [seqs[c.msa_id][0] for c in chains]
+            for c in chains:  # a paired search needs the unpaired queries too
+                if c.msa_id not in have:
+                    missing.setdefault(c.msa_id, seqs[c.msa_id][0])
+    with open(os.path.join(output, "combined.fasta"), "w") as f:
+        for m, seq in missing.items():
+            f.write(f">{m}\n{seq}\n")
+    with open(os.path.join(output, "complexes.json"), "w") as f:
+        json.dump(complexes, f)
+    stats.update(sequences_to_search=len(missing), complexes_to_pair=len(complexes))
+    with open(os.path.join(output, "stats.json"), "w") as f:
+        json.dump(stats, f, indent=1)
+    click.echo(json.dumps(stats))
+
+
 # --------------------------------------------------------------------------------------------------------- packs, kernels
 @click.command("pack")
 @click.argument("src_dir", type=click.Path(exists=True))
@@ -452,4 +539,5 @@ def warmup_kernels(tokens, build):
 
 
 COMMANDS = (fetch_ccd, build_ccd_cache, export_complexes, import_msa, import_paired_msa, enrich_manifest, drop_obsolete,
-            import_of3, build_of3_cache, stamp_template_index_space, pack, pack_verify, warmup_kernels)
+            import_of3, build_of3_cache, stamp_template_index_space, backfill_template_dates, msa_worklist, pack, pack_verify,
+            warmup_kernels)

@@ -653,3 +653,46 @@ def test_template_hit_is_reconciled_with_the_structure_sequence(tmp_path):
     shifted = template_chain_from_mmcif(path, "A", list(range(20)), list(range(20)), hit_sequence=letters[3:43], hit_start=0)
     assert shifted.query_to_hit == {q: q + 3 for q in range(20)}
     assert template_chain_from_mmcif(path, "A", list(range(20)), list(range(20)), hit_sequence="W" * 40, hit_start=0) is None
+
+
+def test_template_date_backfill_and_alignment_worklist(tmp_path):
+    import importlib
+    import json
+
+    from click.testing import CliRunner
+
+    cli = importlib.import_module("deepfold3_dev_b200.cli.main").cli
+    src = tmp_path / "src"
+    src.mkdir()
+    (src / "one.cif").write_text(_mini_cif())
+    out = tmp_path / "out"
+    prepare_directory(str(src), str(out), StructureFilterConfig(min_residues=2))
+    # hit lists without dates: one plain list, one wrapped with its index space
+    (out / "monomer_templates" / "ab").mkdir(parents=True)
+    hits = [{"template_pdb_id": "1abc", "template_chain_id": "A", "release_date": None}, {"template_pdb_id": "9zzz", "release_date": None},
+            {"template_pdb_id": "2def", "release_date": "1999-01-01"}]  # fmt: skip
+    (out / "monomer_templates" / "ab" / "abcd.json").write_text(json.dumps(hits))
+    (out / "monomer_templates" / "ab" / "abce.json").write_text(json.dumps({"index_space": "struct", "hits": hits[:1]}))
+    (tmp_path / "dates.json").write_text(json.dumps({"1ABC": "2001-02-03", "2def": "2010-10-10"}))
+    args = ["backfill-template-dates", "--data-dir", str(out), "--release-dates", str(tmp_path / "dates.json")]
+    dry = CliRunner().invoke(cli, args + ["--dry-run"])
+    assert dry.exit_code == 0 and "2 dates would be filled in 2 files, 1 hits without a known date" in dry.output
+    assert json.loads((out / "monomer_templates" / "ab" / "abcd.json").read_text())[0]["release_date"] is None
+    assert CliRunner().invoke(cli, args).exit_code == 0
+    got = json.loads((out / "monomer_templates" / "ab" / "abcd.json").read_text())
+    assert [h["release_date"] for h in got] == ["2001-02-03", None, "1999-01-01"]  # present dates are kept
+    wrapped = json.loads((out / "monomer_templates" / "ab" / "abce.json").read_text())
+    assert wrapped["index_space"] == "struct" and wrapped["hits"][0]["release_date"] == "2001-02-03"
+
+    # nothing has an alignment yet: every distinct protein sequence is on the list; with one attached it drops off
+    res = CliRunner().invoke(cli, ["msa-worklist", "--data-dir", str(out), "--output", str(tmp_path / "todo")])
+    assert res.exit_code == 0, res.output + repr(res.exception)
+    stats = json.loads((tmp_path / "todo" / "stats.json").read_text())
+    fasta = (tmp_path / "todo" / "combined.fasta").read_text().split()
+    assert stats["with_alignment"] == 0 and stats["sequences_to_search"] == stats["protein_sequences"] == len(fasta) // 2 >= 1
+    msa_id = fasta[0][1:]
+    (out / "msa").mkdir(exist_ok=True)
+    (out / "msa" / f"{msa_id}.a3m").write_text(f">query\n{fasta[1]}\n")
+    CliRunner().invoke(cli, ["msa-worklist", "--data-dir", str(out), "--output", str(tmp_path / "todo")])
+    again = json.loads((tmp_path / "todo" / "stats.json").read_text())
+    assert again["with_alignment"] == 1 and again["sequences_to_search"] == stats["sequences_to_search"] - 1
