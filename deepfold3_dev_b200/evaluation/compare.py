@@ -144,6 +144,26 @@ def compare_files(pred_path: str, true_path: str, use_assembly: bool = False) ->
         out["tm_score"] = metrics.tm_score(P[trace], T[trace])
         out["gdt_ts"] = metrics.gdt_ts(P[trace], T[trace])
         out["rmsd_trace"] = metrics.rmsd(P[trace], T[trace])
+    # secondary structure from the C-alpha traces of the matched protein chains (residues in chain order)
+    from .secondary_structure import ss_agreement
+
+    per_chain, weights = [], []
+    for k, (p, _) in enumerate(pairs):
+        pick = trace & (chain_of == k)
+        if p["mol"] == const.MOL_PROTEIN and int(pick.sum()) >= 8:
+            per_chain.append(ss_agreement(P[pick], T[pick]))
+            weights.append(int(pick.sum()))
+    if per_chain:
+        w = np.asarray(weights, float)
+
+        def pooled(key):
+            vals = np.asarray([c[key] for c in per_chain], float)
+            ok = np.isfinite(vals)
+            return float((vals[ok] * w[ok]).sum() / w[ok].sum()) if ok.any() else float("nan")
+
+        out.update(ss_q3=pooled("q3"), ss_f1_helix=pooled("f1_helix"), ss_f1_strand=pooled("f1_strand"))
+        rec = [x for c in per_chain for x in c["helix_recovery"]]
+        out["helix_recovery"] = float(np.mean(rec)) if rec else float("nan")
     best = None
     for a, b in itertools.combinations(range(len(pairs)), 2):
         ra, rb = chain_of == a, chain_of == b

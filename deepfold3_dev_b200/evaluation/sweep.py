@@ -36,8 +36,9 @@ import time
 
 import numpy as np
 
-METRICS = ("lddt", "tm_score", "gdt_ts", "rmsd_trace", "dockq_mean")
-HIGHER_IS_BETTER = {"lddt": True, "tm_score": True, "gdt_ts": True, "rmsd_trace": False, "dockq_mean": True}
+METRICS = ("lddt", "tm_score", "gdt_ts", "rmsd_trace", "dockq_mean", "ss_q3", "ss_f1_helix", "ss_f1_strand", "helix_recovery")
+HIGHER_IS_BETTER = {"lddt": True, "tm_score": True, "gdt_ts": True, "rmsd_trace": False, "dockq_mean": True, "ss_q3": True,
+                    "ss_f1_helix": True, "ss_f1_strand": True, "helix_recovery": True}
 
 
 @dataclasses.dataclass

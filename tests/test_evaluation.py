@@ -162,3 +162,29 @@ def test_accuracy_sweep_plan_score_and_trajectory(tmp_path):
     (tmp_path / "ck").mkdir()
     (tmp_path / "ck" / "checkpoint_20.pt").write_text("")
     assert sweep.resolve_checkpoint(str(tmp_path / "ck"), 20).endswith("checkpoint_20.pt") and sweep.resolve_checkpoint(str(tmp_path / "ck"), 30) is None
+
+
+def test_secondary_structure_from_traces_and_helix_recovery():
+    import numpy as np
+
+    from deepfold3_dev_b200.evaluation.secondary_structure import assign_ss, runs, ss_agreement
+
+    t = np.arange(20) * np.deg2rad(100.0)
+    helix = np.stack([2.3 * np.cos(t), 2.3 * np.sin(t), 1.5 * np.arange(20)], -1)  # ideal alpha helix: 1.5 A rise, 100 degrees
+    k = np.arange(12)
+    strand = np.stack([3.3 * k, 0.9 * (k % 2), np.zeros(12)], -1) + helix[-1] + np.array([3.8, 0.0, 0.0])
+    trace = np.concatenate([helix, strand])
+    ss = assign_ss(trace)
+    assert "".join(ss) == "H" * 20 + "E" * 12 and runs(ss, "H") == [(0, 20)] and runs(ss, "E") == [(20, 32)]
+    walk = np.cumsum(np.random.default_rng(0).normal(size=(32, 3)) * 2.2, 0)
+    assert set(assign_ss(walk)) == {"C"}
+    same = ss_agreement(trace, trace)
+    assert same["q3"] == 1.0 and same["f1_helix"] == 1.0 and same["f1_strand"] == 1.0 and same["helix_recovery"] == [1.0]
+    lost = trace.copy()
+    lost[:20] = walk[:20]  # the helix is gone, the strand is kept
+    got = ss_agreement(lost, trace)
+    assert got["f1_helix"] == 0.0 and got["f1_strand"] == 1.0 and got["helix_recovery"] == [0.0] and got["q3"] == 12 / 32
+    half = trace.copy()
+    half[10:20] = walk[:10] + trace[9]  # the second half of the helix unravels
+    part = ss_agreement(half, trace)
+    assert 0.3 <= part["helix_recovery_mean"] <= 0.6 and 0 < part["f1_helix"] < 1
