@@ -38,7 +38,7 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 SEED = 101
 N_TOKENS, N_MSA, N_TEMPLATES, N_DIFFUSION = 384, 1024, 4, 48
-BASELINE_VALUE = None  # BASELINE.md publishes no B200 number for this metric
+BASELINE_VALUE = None  # no B200 number is published for this metric
 
 
 def _chains(kind_lengths):

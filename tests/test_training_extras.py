@@ -234,7 +234,7 @@ def test_guides_name_existing_commands_files_and_switches():
     commands = {line.split()[0] for line in listing.split("Commands:")[1].splitlines() if line.startswith("  ") and line.split()}
     sources = ""
     for base, _, names in os.walk(root):
-        if any(part in base for part in ("/.git", "/_work", "/gpurun_out", "/baseline/_ref", "/build")):
+        if any(part in base for part in ("/.git", "/_work", "_out", "/baseline/_ref", "/build")):
             continue
         for n in names:
             if n.endswith((".py", ".cu", ".cuh", ".h", ".sh")):
